@@ -1,0 +1,235 @@
+// Paged attention on CUDA cores: split-KV flash-decode, small-T verify, and the general
+// varlen causal kernel (sliding window, attention sinks, GQA sharing, logit soft-cap).
+//
+// One CTA owns (query tile, kv head, kv split).  Each 64-key K/V tile is staged in shared
+// memory once and shared by every (query token, query head) pair of the group; a warp runs
+// the online softmax for its pairs with one key per lane, so there is no per-key reduction.
+// Every split writes an un-normalised partial (acc, m, l); the combine kernel merges the
+// splits and folds the per-head sink into the denominator exactly once.
+//
+// KV cache layout: [block][kv_head][block_size][head_dim] bf16, block_size a multiple of 64.
+//
+// Reference parity: src/ops/attention.cpp:229-454 (naive / gpt-oss window + sink),
+// :685-1036 (split-K flash decode, sink folded in combine), :2456-2714 (wide tile prefill with
+// causal + window masks and whole-tile skipping).
+#include "common.cuh"
+#include "host_util.h"
+
+namespace mx {
+
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_TILE = 64;
+
+struct AttnParams {
+  const __nv_bfloat16* q;      // [Tq][n_q][hd]
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int* block_table;      // [B][max_blocks]
+  const int* seq_lens;         // [B] kv length including this step's tokens
+  const int* cu_q;             // [B+1]
+  float* o_part;               // [splits][Tq][n_q][hd]
+  float* ml_part;              // [splits][Tq][n_q][2]
+  int B, n_q, n_kv, max_blocks, block_size;
+  int q_tile;                  // query tokens per CTA
+  int max_q_tiles;             // per sequence
+  int n_splits;
+  int Tq;
+  int window;                  // 0 = full causal
+  float scale, softcap;
+};
+
+template <int HD, int PPW>
+__global__ void __launch_bounds__(ATT_WARPS * 32) attn_partial_kernel(const AttnParams p) {
+  constexpr int PAIRS = ATT_WARPS * PPW;
+  constexpr int KSTR = HD + 2;   // padded K row (elements): conflict-free one-key-per-lane reads
+  extern __shared__ uint8_t smem_raw[];
+  float* sq = reinterpret_cast<float*>(smem_raw);                                  // [PAIRS][HD]
+  __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(sq + PAIRS * HD);           // [64][KSTR]
+  __nv_bfloat16* sv = sk + ATT_TILE * KSTR;                                        // [64][HD]
+
+  const int b = blockIdx.x / p.max_q_tiles, qt = blockIdx.x % p.max_q_tiles;
+  const int kvh = blockIdx.y, split = blockIdx.z;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int t0 = qt * p.q_tile;
+  if (t0 >= q_len) return;
+  const int nt = min(p.q_tile, q_len - t0);
+  const int seq_len = p.seq_lens[b];
+  const int pos0 = seq_len - q_len + t0;          // absolute position of the tile's first query
+  const int gqa = p.n_q / p.n_kv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // kv range needed by this query tile, in whole 64-key tiles, then this split's share
+  const int kv_hi = min(seq_len, pos0 + nt);
+  const int kv_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int tile_lo = kv_lo / ATT_TILE, tile_hi = (kv_hi + ATT_TILE - 1) / ATT_TILE;
+  const int n_tiles = tile_hi - tile_lo;
+  const int per = (n_tiles + p.n_splits - 1) / p.n_splits;
+  const int my_lo = tile_lo + split * per, my_hi = min(tile_hi, my_lo + per);
+
+  const int total_pairs = nt * gqa;
+  for (int round0 = 0; round0 < total_pairs; round0 += PAIRS) {
+    __syncthreads();
+    // stage the queries of this round as fp32, pre-scaled
+    for (int i = threadIdx.x; i < PAIRS * HD; i += blockDim.x) {
+      const int pr = round0 + i / HD, d = i % HD;
+      float v = 0.f;
+      if (pr < total_pairs) {
+        const int tq = pr / gqa, hq = kvh * gqa + pr % gqa;
+        v = __bfloat162float(p.q[((size_t)(q_begin + t0 + tq) * p.n_q + hq) * HD + d]) * p.scale;
+      }
+      sq[i] = v;
+    }
+    float m[PPW], l[PPW], acc[PPW][HD / 32];
+#pragma unroll
+    for (int i = 0; i < PPW; ++i) {
+      m[i] = -1e30f; l[i] = 0.f;
+#pragma unroll
+      for (int j = 0; j < HD / 32; ++j) acc[i][j] = 0.f;
+    }
+    for (int tile = my_lo; tile < my_hi; ++tile) {
+      __syncthreads();
+      const int key0 = tile * ATT_TILE;
+      const int blk = p.block_table[(size_t)b * p.max_blocks + key0 / p.block_size];
+      const size_t base = (((size_t)blk * p.n_kv + kvh) * p.block_size + key0 % p.block_size) * HD;
+      for (int i = threadIdx.x; i < ATT_TILE * HD / 8; i += blockDim.x) {
+        const int r = i / (HD / 8), c = (i % (HD / 8)) * 8;
+        const uint4 kv4 = *reinterpret_cast<const uint4*>(p.k_cache + base + (size_t)r * HD + c);
+        uint32_t* kd = reinterpret_cast<uint32_t*>(sk + r * KSTR + c);
+        kd[0] = kv4.x; kd[1] = kv4.y; kd[2] = kv4.z; kd[3] = kv4.w;
+        *reinterpret_cast<uint4*>(sv + r * HD + c) = *reinterpret_cast<const uint4*>(p.v_cache + base + (size_t)r * HD + c);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int pi = 0; pi < PPW; ++pi) {
+        const int pl = warp * PPW + pi, pr = round0 + pl;
+        if (pr >= total_pairs) continue;
+        const int qpos = pos0 + pr / gqa;
+        const float* qv = sq + pl * HD;
+        float s[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int j = lane + 32 * half, kpos = key0 + j;
+          const uint32_t* kr = reinterpret_cast<const uint32_t*>(sk + j * KSTR);
+          float d = 0.f;
+#pragma unroll 8
+          for (int c = 0; c < HD / 2; ++c) {
+            const uint32_t kk = kr[c];
+            const float2 qq = *reinterpret_cast<const float2*>(qv + 2 * c);
+            d = fmaf(qq.x, bf16_lo(kk), d);
+            d = fmaf(qq.y, bf16_hi(kk), d);
+          }
+          if (p.softcap > 0.f) d = p.softcap * tanhf(d / p.softcap);
+          const bool ok = kpos < seq_len && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+          s[half] = ok ? d : -INFINITY;
+        }
+        const float tmax = warp_max(fmaxf(s[0], s[1]));
+        const float m_new = fmaxf(m[pi], tmax);
+        const float corr = __expf(m[pi] - m_new);
+        const float p0 = __expf(s[0] - m_new), p1 = __expf(s[1] - m_new);
+        l[pi] = l[pi] * corr + warp_sum(p0 + p1);
+        m[pi] = m_new;
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) acc[pi][j] *= corr;
+#pragma unroll 4
+        for (int j = 0; j < ATT_TILE; ++j) {
+          const float pj = __shfl_sync(0xffffffffu, j < 32 ? p0 : p1, j & 31);
+          const __nv_bfloat16* vr = sv + j * HD;
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) acc[pi][c] = fmaf(pj, __bfloat162float(vr[lane + 32 * c]), acc[pi][c]);
+        }
+      }
+    }
+    // write partials
+#pragma unroll
+    for (int pi = 0; pi < PPW; ++pi) {
+      const int pr = round0 + warp * PPW + pi;
+      if (pr >= total_pairs) continue;
+      const int tq = pr / gqa, hq = kvh * gqa + pr % gqa;
+      const size_t row = ((size_t)split * p.Tq + (q_begin + t0 + tq)) * p.n_q + hq;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) p.o_part[row * HD + lane + 32 * c] = acc[pi][c];
+      if (lane == 0) { p.ml_part[row * 2] = m[pi]; p.ml_part[row * 2 + 1] = l[pi]; }
+    }
+  }
+}
+
+// out[t][h][:] = sum_s acc_s e^{m_s - M} / (sum_s l_s e^{m_s - M} + e^{sink_h - M})
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                                           const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, int Tq, int n_q,
+                                                           int hd, int n_splits) {
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= Tq * n_q) return;
+  const int h = r % n_q;
+  float M = sinks ? sinks[h] : -1e30f;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml_part[((size_t)s * Tq * n_q + r) * 2]);
+  float L = sinks ? __expf(sinks[h] - M) : 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float* ml = ml_part + ((size_t)s * Tq * n_q + r) * 2;
+    L += ml[1] * __expf(ml[0] - M);
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int d = lane; d < hd; d += 32) {
+    float a = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const size_t row = (size_t)s * Tq * n_q + r;
+      a += o_part[row * hd + d] * __expf(ml_part[row * 2] - M);
+    }
+    out[(size_t)r * hd + d] = __float2bfloat16(a * inv);
+  }
+}
+
+template <int HD, int PPW>
+static int launch_partial(const AttnParams& p, cudaStream_t st) {
+  constexpr int PAIRS = ATT_WARPS * PPW;
+  const size_t smem = (size_t)PAIRS * HD * 4 + (size_t)ATT_TILE * (HD + 2) * 2 + (size_t)ATT_TILE * HD * 2;
+  auto kern = attn_partial_kernel<HD, PPW>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(p.B * p.max_q_tiles, p.n_kv, p.n_splits);
+  kern<<<grid, ATT_WARPS * 32, smem, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace mx
+
+using namespace mx;
+
+// Scratch: o_part needs n_splits*Tq*n_q*hd floats, ml_part n_splits*Tq*n_q*2 floats.
+// max_q_len is the longest query segment of the batch (host knows it from cu_q).
+MX_HOST_API int mx_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table, const int* seq_lens,
+                             const int* cu_q, const float* sinks, void* out, float* o_part, float* ml_part, int B, int Tq, int max_q_len,
+                             int n_q, int n_kv, int hd, int max_blocks, int block_size, int window, float scale, float softcap,
+                             int n_splits, cudaStream_t st) {
+  if (B <= 0 || Tq <= 0) return 0;
+  if (block_size % ATT_TILE) return -110;
+  if (n_q % n_kv) return -111;
+  const int gqa = n_q / n_kv;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.block_table = block_table; p.seq_lens = seq_lens; p.cu_q = cu_q; p.o_part = o_part; p.ml_part = ml_part;
+  p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.max_blocks = max_blocks; p.block_size = block_size;
+  p.n_splits = n_splits < 1 ? 1 : n_splits; p.Tq = Tq; p.window = window; p.scale = scale; p.softcap = softcap;
+  // pairs per warp: 1 for decode-sized work, 4 when there are many query tokens
+  const int ppw = (max_q_len * gqa > ATT_WARPS * 2) ? 4 : (max_q_len * gqa > ATT_WARPS ? 2 : 1);
+  const int pairs = ATT_WARPS * ppw;
+  p.q_tile = pairs / gqa > 0 ? pairs / gqa : 1;
+  if (p.q_tile > max_q_len) p.q_tile = max_q_len;
+  p.max_q_tiles = (max_q_len + p.q_tile - 1) / p.q_tile;
+  int rc;
+#define MX_ATT(HD_)                                                        \
+  (ppw == 4 ? launch_partial<HD_, 4>(p, st) : ppw == 2 ? launch_partial<HD_, 2>(p, st) : launch_partial<HD_, 1>(p, st))
+  switch (hd) {
+    case 64: rc = MX_ATT(64); break;
+    case 128: rc = MX_ATT(128); break;
+    case 256: rc = MX_ATT(256); break;
+    default: return -112;
+  }
+#undef MX_ATT
+  if (rc) return rc;
+  attn_combine_kernel<<<(Tq * n_q + 3) / 4, 128, 0, st>>>(o_part, ml_part, sinks, (__nv_bfloat16*)out, Tq, n_q, hd, p.n_splits);
+  return (int)cudaGetLastError();
+}

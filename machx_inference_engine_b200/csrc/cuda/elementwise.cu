@@ -1,0 +1,314 @@
+// Memory-bound glue kernels, each fusing what the reference ran as separate submits:
+//   embed           : dequantising row gather into the fp32 residual stream
+//   rmsnorm         : residual add (+bias) + RMSNorm (+ "1+w" form) -> bf16, one pass
+//   qkv_post        : bias + per-head QK RMSNorm + NEOX RoPE (table driven: llama3 factors and
+//                     YaRN are baked into the cos/sin tables) + Q|gate split + paged KV write
+//   glu             : SwiGLU / clamped OAI SwiGLU / GeGLU over 16-column interleaved gate|up
+//   gated_rmsnorm   : y = w * x / rms(x) * silu(z) per head (DeltaNet output norm)
+//   misc            : sigmoid gate multiply, scaled add, casts
+// Reference parity: src/ops/elementwise.cpp:29-786, src/ops/embedding.cpp:45-206,
+// src/core/kv_cache.cpp:107-133, src/ops/deltanet.cpp:41-81.
+#include "common.cuh"
+#include "dequant.cuh"
+#include "host_util.h"
+
+namespace mx {
+
+// ------------------------------------------------------------------ embed
+template <int FMT>
+__global__ void embed_kernel(WeightRef w, const int* __restrict__ ids, float* __restrict__ out, int H, int vocab, float scale) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const RowPtrs rp = row_ptrs<FMT>(w, id, H);
+  for (int kb = threadIdx.x; kb < H / 32; kb += blockDim.x) {
+    float v[32];
+    decode32_f32<FMT>(rp, kb, v);
+    float4* o = reinterpret_cast<float4*>(out + (size_t)t * H + kb * 32);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = make_float4(v[4 * i] * scale, v[4 * i + 1] * scale, v[4 * i + 2] * scale, v[4 * i + 3] * scale);
+  }
+}
+
+// ------------------------------------------------------------------ rmsnorm
+// x (fp32, [T,H]) += delta (bf16 or fp32, optional) + dbias (optional); out = norm(x) * w.
+// delta_scale multiplies delta (Granite residual scale).  If out_f32 != null the normalised row
+// is also written in fp32 (final norm feeding an fp32 consumer).
+template <typename DT>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(float* __restrict__ x, const DT* __restrict__ delta, const float* __restrict__ dbias,
+                                                      const float* __restrict__ w, __nv_bfloat16* __restrict__ out, float eps, int H,
+                                                      int one_plus_w, float delta_scale, int write_x) {
+  const int t = blockIdx.x;
+  float* xr = x + (size_t)t * H;
+  __shared__ float red[8];
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(xr + i);
+    if (delta) {
+      float d0, d1, d2, d3;
+      if constexpr (sizeof(DT) == 2) {
+        const uint2 dv = *reinterpret_cast<const uint2*>(delta + (size_t)t * H + i);
+        d0 = bf16_lo(dv.x); d1 = bf16_hi(dv.x); d2 = bf16_lo(dv.y); d3 = bf16_hi(dv.y);
+      } else {
+        const float4 dv = *reinterpret_cast<const float4*>(delta + (size_t)t * H + i);
+        d0 = dv.x; d1 = dv.y; d2 = dv.z; d3 = dv.w;
+      }
+      if (dbias) { d0 += dbias[i]; d1 += dbias[i + 1]; d2 += dbias[i + 2]; d3 += dbias[i + 3]; }
+      v.x += d0 * delta_scale; v.y += d1 * delta_scale; v.z += d2 * delta_scale; v.w += d3 * delta_scale;
+      if (write_x) *reinterpret_cast<float4*>(xr + i) = v;
+    }
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) red[0] = rsqrtf(v / H + eps);
+  }
+  __syncthreads();
+  const float inv = red[0];
+  if (!out) return;
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    // when the sum was not written back (write_x == 0 with delta) recompute it
+    float4 v = *reinterpret_cast<const float4*>(xr + i);
+    if (delta && !write_x) {
+      float d0, d1, d2, d3;
+      if constexpr (sizeof(DT) == 2) {
+        const uint2 dv = *reinterpret_cast<const uint2*>(delta + (size_t)t * H + i);
+        d0 = bf16_lo(dv.x); d1 = bf16_hi(dv.x); d2 = bf16_lo(dv.y); d3 = bf16_hi(dv.y);
+      } else {
+        const float4 dv = *reinterpret_cast<const float4*>(delta + (size_t)t * H + i);
+        d0 = dv.x; d1 = dv.y; d2 = dv.z; d3 = dv.w;
+      }
+      if (dbias) { d0 += dbias[i]; d1 += dbias[i + 1]; d2 += dbias[i + 2]; d3 += dbias[i + 3]; }
+      v.x += d0 * delta_scale; v.y += d1 * delta_scale; v.z += d2 * delta_scale; v.w += d3 * delta_scale;
+    }
+    float4 g = *reinterpret_cast<const float4*>(w + i);
+    if (one_plus_w) { g.x += 1.f; g.y += 1.f; g.z += 1.f; g.w += 1.f; }
+    uint2 o;
+    o.x = pack_bf16(v.x * inv * g.x, v.y * inv * g.y);
+    o.y = pack_bf16(v.z * inv * g.z, v.w * inv * g.w);
+    *reinterpret_cast<uint2*>(out + (size_t)t * H + i) = o;
+  }
+}
+
+// ------------------------------------------------------------------ qkv_post
+struct QkvPostParams {
+  const __nv_bfloat16* qkv;   // [T][q_cols + 2*n_kv*hd]
+  const float* bias;          // [q_cols + 2*n_kv*hd] or null
+  const float* q_norm_w;      // [hd] or null
+  const float* k_norm_w;      // [hd] or null
+  const int* positions;       // [T]
+  const float* rope_cos;      // [max_pos][n_rot/2]
+  const float* rope_sin;
+  const long long* slot_map;  // [T] slot = block*block_size + offset, <0: do not store
+  __nv_bfloat16* q_out;       // [T][n_q][hd]
+  __nv_bfloat16* gate_out;    // [T][n_q][hd] when q_gate != 0
+  __nv_bfloat16* k_cache;     // [blocks][n_kv][block_size][hd]
+  __nv_bfloat16* v_cache;
+  int T, n_q, n_kv, hd, n_rot, block_size;
+  int q_gate;                 // 1: q columns hold per-head [q(hd) | gate(hd)]
+  int norm_one_plus_w;
+  float eps;
+  int max_pos;
+};
+
+__global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
+  __shared__ float sh[4][512];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_total = p.n_q + 2 * p.n_kv;
+  const int unit = blockIdx.x * 4 + warp;
+  if (unit >= p.T * heads_total) return;
+  const int t = unit / heads_total, h = unit % heads_total;
+  const int hd = p.hd;
+  const int q_stride = p.q_gate ? 2 * hd : hd;
+  const int q_cols = p.n_q * q_stride;
+  const int row_cols = q_cols + 2 * p.n_kv * hd;
+  int kind, hh, col0;   // kind 0 q, 1 k, 2 v
+  if (h < p.n_q) { kind = 0; hh = h; col0 = h * q_stride; }
+  else if (h < p.n_q + p.n_kv) { kind = 1; hh = h - p.n_q; col0 = q_cols + hh * hd; }
+  else { kind = 2; hh = h - p.n_q - p.n_kv; col0 = q_cols + p.n_kv * hd + hh * hd; }
+  const __nv_bfloat16* src = p.qkv + (size_t)t * row_cols + col0;
+  float* v = sh[warp];
+  float ss = 0.f;
+  for (int i = lane; i < hd; i += 32) {
+    float x = __bfloat162float(src[i]);
+    if (p.bias) x += p.bias[col0 + i];
+    v[i] = x;
+    ss += x * x;
+  }
+  if (kind == 0 && p.q_gate) {
+    for (int i = lane; i < hd; i += 32) {
+      float g = __bfloat162float(src[hd + i]);
+      if (p.bias) g += p.bias[col0 + hd + i];
+      p.gate_out[((size_t)t * p.n_q + hh) * hd + i] = __float2bfloat16(g);
+    }
+  }
+  const float* nw = kind == 0 ? p.q_norm_w : (kind == 1 ? p.k_norm_w : nullptr);
+  if (nw) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / hd + p.eps);
+    for (int i = lane; i < hd; i += 32) v[i] = v[i] * inv * (p.norm_one_plus_w ? 1.f + nw[i] : nw[i]);
+  }
+  __syncwarp();
+  if (kind != 2 && p.n_rot > 0) {
+    const int half = p.n_rot / 2;
+    int pos = p.positions[t];
+    pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+    const float* cs = p.rope_cos + (size_t)pos * half;
+    const float* sn = p.rope_sin + (size_t)pos * half;
+    for (int i = lane; i < half; i += 32) {
+      const float a = v[i], b = v[i + half], c = cs[i], s = sn[i];
+      v[i] = a * c - b * s;
+      v[i + half] = a * s + b * c;
+    }
+    __syncwarp();
+  }
+  __nv_bfloat16* dst;
+  if (kind == 0) dst = p.q_out + ((size_t)t * p.n_q + hh) * hd;
+  else {
+    const long long slot = p.slot_map[t];
+    if (slot < 0) return;
+    const long long blk = slot / p.block_size, off = slot % p.block_size;
+    __nv_bfloat16* cache = kind == 1 ? p.k_cache : p.v_cache;
+    dst = cache + ((blk * p.n_kv + hh) * p.block_size + off) * hd;
+  }
+  for (int i = lane; i < hd; i += 32) dst[i] = __float2bfloat16(v[i]);
+}
+
+// ------------------------------------------------------------------ GLU over interleaved-16 columns
+__device__ __forceinline__ float glu_act(int act, float g, float u, float alpha, float limit) {
+  if (act == 1) return g / (1.f + __expf(-g)) * u;
+  if (act == 2) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + __expf(-alpha * g)) * (u + 1.f);
+  }
+  const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+  return 0.5f * g * (1.f + t) * u;
+}
+__global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long total_out, int F, int act,
+                           float alpha, float limit) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total_out) return;
+  const long long t = i / F;
+  const int f = (int)(i % F);
+  const __nv_bfloat16* row = in + t * 2 * F;
+  const int g = 32 * (f >> 4) + (f & 15);
+  out[i] = __float2bfloat16(glu_act(act, __bfloat162float(row[g]), __bfloat162float(row[g + 16]), alpha, limit));
+}
+
+// y[i] = x[i] * sigmoid(g[i])   (gated attention output, shared-expert gate uses the scalar form below)
+__global__ void sigmoid_mul_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = __float2bfloat16(__bfloat162float(x[i]) / (1.f + __expf(-__bfloat162float(g[i]))));
+}
+// out[t][:] (fp32) += scale_t * src[t][:], scale_t = sigmoid(gate_logit[t]) if gate_logit else 1
+__global__ void scaled_add_kernel(float* __restrict__ out, const __nv_bfloat16* __restrict__ src, const float* __restrict__ gate_logit, int H, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float s = gate_logit ? 1.f / (1.f + __expf(-gate_logit[i / H])) : 1.f;
+  out[i] += s * __bfloat162float(src[i]);
+}
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ a, __nv_bfloat16* __restrict__ b, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) b[i] = __float2bfloat16(a[i]);
+}
+
+// y[t,h,:] = w * x / rms(x) * silu(z)  over head_dim (one warp per (t,h))
+__global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ z, const float* __restrict__ w,
+                                                            __nv_bfloat16* __restrict__ y, int rows, int hd, float eps) {
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float* xr = x + (size_t)r * hd;
+  float ss = 0.f;
+  for (int i = lane; i < hd; i += 32) ss += xr[i] * xr[i];
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / hd + eps);
+  for (int i = lane; i < hd; i += 32) {
+    const float zz = __bfloat162float(z[(size_t)r * hd + i]);
+    y[(size_t)r * hd + i] = __float2bfloat16(xr[i] * inv * w[i] * (zz / (1.f + __expf(-zz))));
+  }
+}
+
+}  // namespace mx
+
+using namespace mx;
+
+MX_HOST_API int mx_embed(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const int* ids, float* out, int T,
+                         int H, int vocab, float scale, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 32) return -102;
+  WeightRef w{w0, w1, w2, w3};
+  const int threads = 128;
+  switch (wfmt) {
+    case WF_BF16: embed_kernel<WF_BF16><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
+    case WF_Q8: embed_kernel<WF_Q8><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
+    case WF_Q4K: embed_kernel<WF_Q4K><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
+    case WF_Q6K: embed_kernel<WF_Q6K><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
+    case WF_MXFP4: embed_kernel<WF_MXFP4><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
+    default: return -100;
+  }
+  return (int)cudaGetLastError();
+}
+
+// delta_is_f32: 0 -> bf16 delta, 1 -> fp32 delta.  write_x: store x+delta back into x.
+MX_HOST_API int mx_rmsnorm(float* x, const void* delta, int delta_is_f32, const float* dbias, const float* w, void* out_bf16, float eps,
+                           int T, int H, int one_plus_w, float delta_scale, int write_x, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 4) return -107;
+  if (delta_is_f32) rmsnorm_kernel<float><<<T, 256, 0, st>>>(x, (const float*)delta, dbias, w, (__nv_bfloat16*)out_bf16, eps, H, one_plus_w, delta_scale, write_x);
+  else rmsnorm_kernel<__nv_bfloat16><<<T, 256, 0, st>>>(x, (const __nv_bfloat16*)delta, dbias, w, (__nv_bfloat16*)out_bf16, eps, H, one_plus_w, delta_scale, write_x);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_qkv_post(const void* qkv, const float* bias, const float* q_norm_w, const float* k_norm_w, const int* positions,
+                            const float* rope_cos, const float* rope_sin, const long long* slot_map, void* q_out, void* gate_out,
+                            void* k_cache, void* v_cache, int T, int n_q, int n_kv, int hd, int n_rot, int block_size, int q_gate,
+                            int norm_one_plus_w, float eps, int max_pos, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (hd > 512) return -108;
+  QkvPostParams p;
+  p.qkv = (const __nv_bfloat16*)qkv; p.bias = bias; p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.positions = positions;
+  p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.slot_map = slot_map; p.q_out = (__nv_bfloat16*)q_out; p.gate_out = (__nv_bfloat16*)gate_out;
+  p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
+  p.T = T; p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.n_rot = n_rot; p.block_size = block_size; p.q_gate = q_gate;
+  p.norm_one_plus_w = norm_one_plus_w; p.eps = eps; p.max_pos = max_pos;
+  const int units = T * (n_q + 2 * n_kv);
+  qkv_post_kernel<<<(units + 3) / 4, 128, 0, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_glu(const void* in, void* out, long long T, int F, int act, float alpha, float limit, cudaStream_t st) {
+  const long long total = T * F;
+  if (total <= 0) return 0;
+  if (F % 16) return -104;
+  glu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, F, act, alpha, limit);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_sigmoid_mul(const void* x, const void* g, void* y, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  sigmoid_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)g, (__nv_bfloat16*)y, n);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_scaled_add(float* out, const void* src, const float* gate_logit, int H, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  scaled_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, (const __nv_bfloat16*)src, gate_logit, H, n);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_cast_f32_bf16(const float* a, void* b, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  cast_f32_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, (__nv_bfloat16*)b, n);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_gated_rmsnorm(const float* x, const void* z, const float* w, void* y, int rows, int hd, float eps, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  gated_rmsnorm_kernel<<<(rows + 3) / 4, 128, 0, st>>>(x, (const __nv_bfloat16*)z, w, (__nv_bfloat16*)y, rows, hd, eps);
+  return (int)cudaGetLastError();
+}

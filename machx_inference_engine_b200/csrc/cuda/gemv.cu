@@ -1,0 +1,247 @@
+// Decode-time GEMV family: y[m][n] = sum_k W[n][k] * x[m][k] (+bias), weights decoded in registers
+// from the runtime layouts (bf16 / Q8 / Q4_K / Q6_K planes / MXFP4 planes), 16-byte loads only.
+//
+//   dense mode : up to 8 activation rows share every decoded weight (T<=8: decode and MTP verify)
+//   expert mode: blockIdx.y selects a slot; slot -> expert id (device array) selects the weight slab
+//                and slot / x_div selects the activation row (MoE decode: gate/up and down GEMVs)
+//
+// A warp owns ROWS consecutive output rows; lanes stride over 32-element k-blocks, so each
+// weight byte is read exactly once and the activation chunk is reused across the warp's rows.
+// Optional fused epilogue: bias, gated activation over 16-row interleaved gate/up pairs.
+//
+// Reference parity: src/ops/gemv_q4k.cpp:72, gemv_q8dot.cpp:276-680, gemv_q6k.cpp:76-670,
+// gemv_mxfp4.cpp:94-323, gemv_fp16.cpp:64 and the batched-T verify kernels gemv_q8dot.cpp:391,499;
+// MoE decode pair moe_fused.cpp:101-541.
+#include "common.cuh"
+#include "dequant.cuh"
+#include "host_util.h"
+
+namespace mx {
+
+constexpr int GEMV_WARPS = 4;
+constexpr int GEMV_ROWS = 4;     // rows per warp
+constexpr int GEMV_MAX_M = 8;
+
+struct GemvParams {
+  WeightRef w;
+  const __nv_bfloat16* x;   // [M][K]
+  void* y;                  // [M or slots][N_out]
+  const float* bias;        // [N] or [E][N]
+  const int* slot_expert;   // expert mode: [slots]
+  const float* slot_scale;  // expert mode: optional per-slot multiplier on the output
+  int x_div;                // expert mode: activation row = slot / x_div
+  int M, N, K;
+  int out_f32;
+  int act;                  // 0 none, 1 swiglu, 2 swiglu_oai, 3 geglu (16-row interleaved gate/up)
+  float act_alpha, act_limit;
+};
+
+__device__ __forceinline__ float gemv_act(int act, float g, float u, float alpha, float limit) {
+  if (act == 1) return g / (1.f + __expf(-g)) * u;
+  if (act == 2) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + __expf(-alpha * g)) * (u + 1.f);
+  }
+  const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+  return 0.5f * g * (1.f + t) * u;
+}
+
+template <int FMT, int MM>
+__global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * GEMV_WARPS + warp) * GEMV_ROWS;
+  if (n0 >= p.N) return;
+  const int slot = blockIdx.y;
+  WeightRef w = p.w;
+  const __nv_bfloat16* x = p.x;
+  const float* bias = p.bias;
+  if (p.slot_expert) {
+    const int e = p.slot_expert[slot];
+    w = expert_weight<FMT>(p.w, e, p.N, p.K);
+    x += (size_t)(slot / p.x_div) * p.K;
+    if (bias) bias += (size_t)e * p.N;
+  }
+  float acc[GEMV_ROWS][MM];
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MM; ++m) acc[r][m] = 0.f;
+
+  RowPtrs rp[GEMV_ROWS];
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r) rp[r] = row_ptrs<FMT>(w, min(n0 + r, p.N - 1), p.K);
+
+  const int nkb = p.K / 32;
+  for (int kb = lane; kb < nkb; kb += 32) {
+    float wv[32];
+    if (MM == 1) {
+      // keep x in registers, stream the rows
+      float xv[32];
+      const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)kb * 32);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 v = __ldg(xp + i);
+        xv[8 * i + 0] = bf16_lo(v.x); xv[8 * i + 1] = bf16_hi(v.x); xv[8 * i + 2] = bf16_lo(v.y); xv[8 * i + 3] = bf16_hi(v.y);
+        xv[8 * i + 4] = bf16_lo(v.z); xv[8 * i + 5] = bf16_hi(v.z); xv[8 * i + 6] = bf16_lo(v.w); xv[8 * i + 7] = bf16_hi(v.w);
+      }
+#pragma unroll
+      for (int r = 0; r < GEMV_ROWS; ++r) {
+        decode32_f32<FMT>(rp[r], kb, wv);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s = fmaf(wv[i], xv[i], s);
+        acc[r][0] += s;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < GEMV_ROWS; ++r) {
+        decode32_f32<FMT>(rp[r], kb, wv);
+#pragma unroll
+        for (int m = 0; m < MM; ++m) {
+          if (m < p.M) {
+            const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * p.K + (size_t)kb * 32);
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 v = __ldg(xp + i);
+              s = fmaf(wv[8 * i + 0], bf16_lo(v.x), s); s = fmaf(wv[8 * i + 1], bf16_hi(v.x), s);
+              s = fmaf(wv[8 * i + 2], bf16_lo(v.y), s); s = fmaf(wv[8 * i + 3], bf16_hi(v.y), s);
+              s = fmaf(wv[8 * i + 4], bf16_lo(v.z), s); s = fmaf(wv[8 * i + 5], bf16_hi(v.z), s);
+              s = fmaf(wv[8 * i + 6], bf16_lo(v.w), s); s = fmaf(wv[8 * i + 7], bf16_hi(v.w), s);
+            }
+            acc[r][m] += s;
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MM; ++m) acc[r][m] = warp_sum(acc[r][m]);
+
+  if (lane != 0) return;
+  const float oscale = p.slot_scale ? p.slot_scale[slot] : 1.f;
+  const int rows_out = p.slot_expert ? 1 : p.M;
+#pragma unroll
+  for (int m = 0; m < MM; ++m) {
+    if (m >= rows_out) break;
+    const size_t orow = p.slot_expert ? (size_t)slot : (size_t)m;
+    if (p.act == 0) {
+      for (int r = 0; r < GEMV_ROWS && n0 + r < p.N; ++r) {
+        const float v = (acc[r][m] + (bias ? bias[n0 + r] : 0.f)) * oscale;
+        if (p.out_f32) ((float*)p.y)[orow * p.N + n0 + r] = v;
+        else ((__nv_bfloat16*)p.y)[orow * p.N + n0 + r] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+// Gated variant: a warp owns output features f0..f0+3 and reads the matching gate rows
+// (16-row interleave: feature f lives at row 32*(f/16) + f%16, its up row 16 further).
+template <int FMT>
+__global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_gated_kernel(const GemvParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int F = p.N / 2;
+  const int f0 = (blockIdx.x * GEMV_WARPS + warp) * GEMV_ROWS;
+  if (f0 >= F) return;
+  const int slot = blockIdx.y;
+  WeightRef w = p.w;
+  const __nv_bfloat16* x = p.x + (size_t)(p.slot_expert ? slot / p.x_div : slot) * p.K;
+  const float* bias = p.bias;
+  if (p.slot_expert) {
+    const int e = p.slot_expert[slot];
+    w = expert_weight<FMT>(p.w, e, p.N, p.K);
+    if (bias) bias += (size_t)e * p.N;
+  }
+  float ag[GEMV_ROWS], au[GEMV_ROWS];
+  RowPtrs rg[GEMV_ROWS], ru[GEMV_ROWS];
+  int grow[GEMV_ROWS];
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r) {
+    const int f = min(f0 + r, F - 1);
+    grow[r] = 32 * (f >> 4) + (f & 15);
+    rg[r] = row_ptrs<FMT>(w, grow[r], p.K);
+    ru[r] = row_ptrs<FMT>(w, grow[r] + 16, p.K);
+    ag[r] = au[r] = 0.f;
+  }
+  const int nkb = p.K / 32;
+  for (int kb = lane; kb < nkb; kb += 32) {
+    float xv[32], wv[32];
+    const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)kb * 32);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = __ldg(xp + i);
+      xv[8 * i + 0] = bf16_lo(v.x); xv[8 * i + 1] = bf16_hi(v.x); xv[8 * i + 2] = bf16_lo(v.y); xv[8 * i + 3] = bf16_hi(v.y);
+      xv[8 * i + 4] = bf16_lo(v.z); xv[8 * i + 5] = bf16_hi(v.z); xv[8 * i + 6] = bf16_lo(v.w); xv[8 * i + 7] = bf16_hi(v.w);
+    }
+#pragma unroll
+    for (int r = 0; r < GEMV_ROWS; ++r) {
+      decode32_f32<FMT>(rg[r], kb, wv);
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s = fmaf(wv[i], xv[i], s);
+      ag[r] += s;
+      decode32_f32<FMT>(ru[r], kb, wv);
+      s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s = fmaf(wv[i], xv[i], s);
+      au[r] += s;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r) { ag[r] = warp_sum(ag[r]); au[r] = warp_sum(au[r]); }
+  if (lane != 0) return;
+  for (int r = 0; r < GEMV_ROWS && f0 + r < F; ++r) {
+    const float g = ag[r] + (bias ? bias[grow[r]] : 0.f), u = au[r] + (bias ? bias[grow[r] + 16] : 0.f);
+    const float v = gemv_act(p.act, g, u, p.act_alpha, p.act_limit);
+    if (p.out_f32) ((float*)p.y)[(size_t)slot * F + f0 + r] = v;
+    else ((__nv_bfloat16*)p.y)[(size_t)slot * F + f0 + r] = __float2bfloat16(v);
+  }
+}
+
+template <int FMT>
+static int launch_gemv(const GemvParams& p, int slots, cudaStream_t st) {
+  if (p.act != 0) {
+    const int F = p.N / 2;
+    dim3 grid((F + GEMV_WARPS * GEMV_ROWS - 1) / (GEMV_WARPS * GEMV_ROWS), slots);
+    gemv_gated_kernel<FMT><<<grid, GEMV_WARPS * 32, 0, st>>>(p);
+    return (int)cudaGetLastError();
+  }
+  dim3 grid((p.N + GEMV_WARPS * GEMV_ROWS - 1) / (GEMV_WARPS * GEMV_ROWS), p.slot_expert ? slots : 1);
+  if (p.slot_expert || p.M == 1) gemv_kernel<FMT, 1><<<grid, GEMV_WARPS * 32, 0, st>>>(p);
+  else if (p.M <= 4) gemv_kernel<FMT, 4><<<grid, GEMV_WARPS * 32, 0, st>>>(p);
+  else gemv_kernel<FMT, 8><<<grid, GEMV_WARPS * 32, 0, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace mx
+
+// Dense: y[M][N] from x[M][K], M <= 8.   Expert: y[slots][N] with slot_expert != null.
+// With act != 0 the weight holds interleaved gate/up rows (N = 2F) and y is [rows][F]; in that
+// mode every activation row is a "slot" (dense callers pass slots = M and slot_expert = null).
+MX_HOST_API int mx_gemv(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const void* x, void* y,
+                        const float* bias, int M, int N, int K, int out_f32, int act, float act_alpha, float act_limit,
+                        const int* slot_expert, const float* slot_scale, int slots, int x_div, cudaStream_t stream) {
+  using namespace mx;
+  if (N <= 0 || K <= 0) return 0;
+  if (K % 32) return -102;
+  if ((wfmt == WF_Q4K || wfmt == WF_Q6K) && (K % 256)) return -103;
+  if (!slot_expert && act == 0 && (M < 1 || M > GEMV_MAX_M)) return -106;
+  GemvParams p;
+  p.w = WeightRef{w0, w1, w2, w3};
+  p.x = (const __nv_bfloat16*)x; p.y = y; p.bias = bias;
+  p.slot_expert = slot_expert; p.slot_scale = slot_scale; p.x_div = x_div > 0 ? x_div : 1;
+  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;
+  p.act = act; p.act_alpha = act_alpha; p.act_limit = act_limit;
+  const int ns = (slot_expert || act != 0) ? (slots > 0 ? slots : M) : 1;
+  switch (wfmt) {
+    case WF_BF16: return launch_gemv<WF_BF16>(p, ns, stream);
+    case WF_Q8: return launch_gemv<WF_Q8>(p, ns, stream);
+    case WF_Q4K: return launch_gemv<WF_Q4K>(p, ns, stream);
+    case WF_Q6K: return launch_gemv<WF_Q6K>(p, ns, stream);
+    case WF_MXFP4: return launch_gemv<WF_MXFP4>(p, ns, stream);
+    default: return -100;
+  }
+}

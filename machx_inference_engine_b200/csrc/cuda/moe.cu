@@ -1,0 +1,194 @@
+// Mixture-of-experts routing and token packing, entirely on the device (no host round trip):
+//   route    : top-k over router logits, weights = softmax over the selected logits (equal to
+//              softmax-over-all followed by top-k renormalisation) or plain softmax-over-all
+//   pack     : stable counting sort of (token, slot) pairs by expert, expert segments padded to
+//              128-row tiles; emits per-tile expert ids and the live tile count for the grouped GEMM
+//   gather   : activation rows -> expert-sorted packed rows (bf16), pad rows zeroed
+//   combine  : y[t] (+)= sum_k w[t,k] * packed_out[pos(t,k)]  (fixed order: deterministic)
+// Reference parity: src/ops/moe.cpp:30-80,268-291,371-429, host router src/model/gptoss.cpp:23-47,
+// host packer src/model/qwen3moe_pack.cpp:5-31, reduce src/ops/moe_fused.cpp:1937-1961.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace mx {
+
+constexpr int MOE_TILE = 128;
+
+// one warp per token; E <= 1024
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int K,
+                                                        int renorm, int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  float v[32];
+  const int per = (E + 31) / 32;
+  float mx_all = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = (i < per && e < E) ? logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f) : -INFINITY;
+    mx_all = fmaxf(mx_all, v[i]);
+  }
+  mx_all = warp_max(mx_all);
+  float denom_all = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) if (i < per) denom_all += __expf(v[i] - mx_all);
+  denom_all = warp_sum(denom_all);
+  float sel_sum = 0.f;
+  float my_w = 0.f; int my_e = 0;    // lane k keeps the k-th selection (K <= 32)
+  for (int k = 0; k < K; ++k) {
+    float best = -INFINITY; int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int e = lane + 32 * i;
+      if (i < per && (v[i] > best || (v[i] == best && e < bi))) { best = v[i]; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    const float pw = __expf(best - mx_all);
+    sel_sum += pw;
+    if (lane == k) { my_w = pw; my_e = bi; }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (lane + 32 * i == bi) v[i] = -INFINITY;
+  }
+  if (lane < K) {
+    topk_idx[(size_t)t * K + lane] = my_e;
+    topk_w[(size_t)t * K + lane] = my_w / (renorm ? sel_sum : denom_all);
+  }
+}
+
+// Single-CTA packer.  n = T*K pairs.  Outputs:
+//   counts[E], seg_start[E+1] (padded starts, multiples of 128), packed_token[P] (-1 = pad),
+//   pair_to_packed[n], tile_expert[max_tiles], num_tiles[1], packed_rows[1]
+// e_lo/e_hi restrict packing to the experts owned by this rank (expert parallelism): pairs routed
+// elsewhere get pair_to_packed = -1.
+__global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ topk_idx, int n, int K, int E, int e_lo, int e_hi,
+                                                        int* __restrict__ counts, int* __restrict__ seg_start, int* __restrict__ packed_token,
+                                                        int* __restrict__ pair_to_packed, int* __restrict__ tile_expert, int* __restrict__ num_tiles,
+                                                        int max_rows) {
+  __shared__ int s_cnt[1024];
+  __shared__ int s_start[1025];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = topk_idx[i];
+    if (e >= e_lo && e < e_hi) atomicAdd(&s_cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      s_start[e] = off;
+      const int padded = (s_cnt[e] + MOE_TILE - 1) / MOE_TILE * MOE_TILE;
+      for (int tix = 0; tix < padded / MOE_TILE; ++tix) tile_expert[tiles++] = e;
+      off += padded;
+    }
+    s_start[E] = off;
+    num_tiles[0] = tiles;
+    num_tiles[1] = off;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) { seg_start[e] = s_start[e]; if (e < E) counts[e] = s_cnt[e]; }
+  const int total = s_start[E];
+  for (int i = threadIdx.x; i < max_rows; i += blockDim.x) if (i < total) packed_token[i] = -1;
+  __syncthreads();
+  // stable placement: expert e's rows keep increasing pair order.  One warp per expert.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int e = e_lo + warp; e < e_hi; e += nwarps) {
+    if (s_cnt[e] == 0) continue;
+    int pos = s_start[e];
+    for (int base = 0; base < n; base += 32) {
+      const int i = base + lane;
+      const bool hit = i < n && topk_idx[i] == e;
+      const unsigned mask = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int dst = pos + __popc(mask & ((1u << lane) - 1));
+        packed_token[dst] = i / K;
+        pair_to_packed[i] = dst;
+      }
+      pos += __popc(mask);
+    }
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = topk_idx[i];
+    if (e < e_lo || e >= e_hi) pair_to_packed[i] = -1;
+  }
+}
+
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ packed_token, const int* __restrict__ total_rows,
+                                  __nv_bfloat16* __restrict__ xp, int H) {
+  const int r = blockIdx.x;
+  if (r >= total_rows[1]) return;
+  const int t = packed_token[r];
+  uint4* dst = reinterpret_cast<uint4*>(xp + (size_t)r * H);
+  if (t < 0) {
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// out[t][:] = (accumulate ? out : 0) + sum_k w[t,k] * yp[pair_to_packed[t,k]][:]
+template <typename OT>
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ yp, const int* __restrict__ pair_to_packed, const float* __restrict__ w,
+                                   OT* __restrict__ out, int H, int K, int accumulate) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int pos = pair_to_packed[(size_t)t * K + k];
+      if (pos < 0) continue;
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(yp + (size_t)pos * H + i);
+      const float ww = w[(size_t)t * K + k];
+      a0 = fmaf(ww, bf16_lo(v), a0);
+      a1 = fmaf(ww, bf16_hi(v), a1);
+    }
+    if constexpr (sizeof(OT) == 4) {
+      float* o = (float*)out + (size_t)t * H + i;
+      if (accumulate) { o[0] += a0; o[1] += a1; } else { o[0] = a0; o[1] = a1; }
+    } else {
+      *reinterpret_cast<uint32_t*>((__nv_bfloat16*)out + (size_t)t * H + i) = pack_bf16(a0, a1);
+    }
+  }
+}
+
+}  // namespace mx
+
+using namespace mx;
+
+MX_HOST_API int mx_moe_route(const float* logits, const float* bias, int T, int E, int K, int renorm, int* topk_idx, float* topk_w,
+                             cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (E > 1024 || K > 32 || K > E) return -120;
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, bias, T, E, K, renorm, topk_idx, topk_w);
+  return (int)cudaGetLastError();
+}
+
+// num_tiles must hold 2 ints: [0] live 128-row tiles, [1] packed row count.
+MX_HOST_API int mx_moe_pack(const int* topk_idx, int n_pairs, int K, int E, int e_lo, int e_hi, int* counts, int* seg_start,
+                            int* packed_token, int* pair_to_packed, int* tile_expert, int* num_tiles, int max_rows, cudaStream_t st) {
+  if (E > 1024) return -120;
+  moe_pack_kernel<<<1, 1024, 0, st>>>(topk_idx, n_pairs, K, E, e_lo, e_hi, counts, seg_start, packed_token, pair_to_packed, tile_expert,
+                                      num_tiles, max_rows);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_moe_gather(const void* x, const int* packed_token, const int* num_tiles, void* xp, int H, int max_rows, cudaStream_t st) {
+  if (max_rows <= 0) return 0;
+  if (H % 8) return -101;
+  moe_gather_kernel<<<max_rows, 128, 0, st>>>((const __nv_bfloat16*)x, packed_token, num_tiles, (__nv_bfloat16*)xp, H);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_moe_combine(const void* yp, const int* pair_to_packed, const float* w, void* out, int out_f32, int T, int H, int K,
+                               int accumulate, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 2) return -101;
+  if (out_f32) moe_combine_kernel<float><<<T, 256, 0, st>>>((const __nv_bfloat16*)yp, pair_to_packed, w, (float*)out, H, K, accumulate);
+  else moe_combine_kernel<__nv_bfloat16><<<T, 256, 0, st>>>((const __nv_bfloat16*)yp, pair_to_packed, w, (__nv_bfloat16*)out, H, K, accumulate);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,302 @@
+"""Launchers for the sm_100a kernels (``csrc/cuda``): torch tensors in, raw pointers out via ctypes.
+
+Every function has a twin with the same signature in :mod:`ops.ref`.  Nothing here falls back
+to PyTorch math: a missing or failing kernel raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .ref import ACT_GEGLU, ACT_NONE, ACT_SWIGLU, ACT_SWIGLU_OAI, MOE_TILE, MoePacking, moe_max_rows
+from .weights import QuantWeight, WFormat
+
+_vp = C.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _p(t: Optional[torch.Tensor]):
+    return _vp(0) if t is None else _vp(t.data_ptr())
+
+
+def _stream():
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+def _planes(w: QuantWeight):
+    return int(w.fmt), _p(w.p0), _p(w.p1), _p(w.p2), _p(w.p3)
+
+
+_launch_count = 0
+
+
+def launches() -> int:
+    """Number of kernel-launching calls made through this module (bench bookkeeping)."""
+    return _launch_count
+
+
+def _count(n=1):
+    global _launch_count
+    _launch_count += n
+
+
+def check_status():
+    """Synchronise and raise if any kernel recorded a bounded-wait timeout or bad argument."""
+    v = _lib.cuda().mx_status_read_and_clear()
+    if v:
+        names = {1: "TMA producer wait", 2: "MMA wait", 3: "epilogue wait", 4: "dequant producer wait", 5: "peer flag wait",
+                 6: "bad argument", 7: "softmax wait"}
+        raise KernelError(f"kernel status {v}: {names.get(v, 'unknown')} ran out of its time limit")
+
+
+def sm_count() -> int:
+    return _lib.cuda().mx_sm_count()
+
+
+# ------------------------------------------------------------------ elementwise
+def embed(w: QuantWeight, ids, scale: float = 1.0):
+    T = ids.numel()
+    out = torch.empty(T, w.K, dtype=torch.float32, device=ids.device)
+    fmt, p0, p1, p2, p3 = _planes(w)
+    _check(_lib.cuda().mx_embed(fmt, p0, p1, p2, p3, _p(ids), _p(out), T, w.K, w.N, C.c_float(scale), _stream()), "embed")
+    _count()
+    return out
+
+
+def rmsnorm(x, w, eps, delta=None, dbias=None, one_plus_w=False, delta_scale=1.0, write_x=True, want_out=True):
+    T, H = x.shape
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if want_out else None
+    is_f32 = 1 if (delta is not None and delta.dtype == torch.float32) else 0
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape == x.shape
+    _check(_lib.cuda().mx_rmsnorm(_p(x), _p(delta), is_f32, _p(dbias), _p(w), _p(out), C.c_float(eps), T, H, int(one_plus_w),
+                                  C.c_float(delta_scale), int(write_x), _stream()), "rmsnorm")
+    _count()
+    return out
+
+
+def glu(x, act, alpha=1.702, limit=7.0):
+    T, F2 = x.shape
+    out = torch.empty(T, F2 // 2, dtype=torch.bfloat16, device=x.device)
+    _check(_lib.cuda().mx_glu(_p(x), _p(out), C.c_longlong(T), F2 // 2, act, C.c_float(alpha), C.c_float(limit), _stream()), "glu")
+    _count()
+    return out
+
+
+def sigmoid_mul(x, g):
+    y = torch.empty_like(x)
+    _check(_lib.cuda().mx_sigmoid_mul(_p(x), _p(g), _p(y), C.c_longlong(x.numel()), _stream()), "sigmoid_mul")
+    _count()
+    return y
+
+
+def scaled_add(out, src, gate_logit=None):
+    _check(_lib.cuda().mx_scaled_add(_p(out), _p(src), _p(gate_logit), out.shape[-1], C.c_longlong(out.numel()), _stream()), "scaled_add")
+    _count()
+    return out
+
+
+def gated_rmsnorm(x, z, w, eps):
+    rows, hd = x.shape
+    y = torch.empty(rows, hd, dtype=torch.bfloat16, device=x.device)
+    _check(_lib.cuda().mx_gated_rmsnorm(_p(x), _p(z), _p(w), _p(y), rows, hd, C.c_float(eps), _stream()), "gated_rmsnorm")
+    _count()
+    return y
+
+
+def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_map, k_cache, v_cache, n_q, n_kv, hd, n_rot,
+             q_gate=False, norm_one_plus_w=False, eps=1e-6):
+    T = qkv.shape[0]
+    q = torch.empty(T, n_q, hd, dtype=torch.bfloat16, device=qkv.device)
+    gate = torch.empty(T, n_q, hd, dtype=torch.bfloat16, device=qkv.device) if q_gate else None
+    bs = k_cache.shape[2]
+    max_pos = rope_cos.shape[0] if rope_cos is not None else 1
+    _check(_lib.cuda().mx_qkv_post(_p(qkv), _p(bias), _p(q_norm_w), _p(k_norm_w), _p(positions), _p(rope_cos), _p(rope_sin),
+                                   _p(slot_map), _p(q), _p(gate), _p(k_cache), _p(v_cache), T, n_q, n_kv, hd, n_rot, bs, int(q_gate),
+                                   int(norm_one_plus_w), C.c_float(eps), max_pos, _stream()), "qkv_post")
+    _count()
+    return q, gate
+
+
+# ------------------------------------------------------------------ linear layers
+GEMV_MAX_M = 8
+
+
+def _pick_bn(M: int, N: int) -> int:
+    # small-M problems are weight-read bound: use narrow tiles so every SM streams weights
+    sms = 148
+    if M <= 128:
+        for bn in (128, 64, 32):
+            if (N + bn - 1) // bn >= sms:
+                return bn
+        return 32
+    tiles128 = ((M + 127) // 128) * ((N + 127) // 128)
+    return 128 if tiles128 >= sms else 64
+
+
+def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None):
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[-1] == w.K and w.E == 1
+    M = x.shape[0]
+    n_out = w.N // 2 if act != ACT_NONE else w.N
+    out = torch.empty(M, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    if M == 0:
+        return out
+    fmt, p0, p1, p2, p3 = _planes(w)
+    lib = _lib.cuda()
+    if M <= GEMV_MAX_M and row_scale is None:
+        _check(lib.mx_gemv(fmt, p0, p1, p2, p3, _p(x), _p(out), _p(bias), M, w.N, w.K, int(out_f32), act, C.c_float(act_alpha),
+                           C.c_float(act_limit), _vp(0), _vp(0), M, 1, _stream()), "gemv")
+    else:
+        _check(lib.mx_gemm(_p(x), fmt, p0, p1, p2, p3, 1, _p(out), n_out, int(out_f32), _p(bias), _p(row_scale), act,
+                           C.c_float(act_alpha), C.c_float(act_limit), M, w.N, w.K, _vp(0), _vp(0), _pick_bn(M, w.N), _stream()), "gemm")
+    _count()
+    return out
+
+
+def gemm(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None, bn=None):
+    """Always the tcgen05 path (tests and benches)."""
+    M = x.shape[0]
+    n_out = w.N // 2 if act != ACT_NONE else w.N
+    out = torch.empty(M, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    fmt, p0, p1, p2, p3 = _planes(w)
+    _check(_lib.cuda().mx_gemm(_p(x), fmt, p0, p1, p2, p3, 1, _p(out), n_out, int(out_f32), _p(bias), _p(row_scale), act,
+                               C.c_float(act_alpha), C.c_float(act_limit), M, w.N, w.K, _vp(0), _vp(0), bn or _pick_bn(M, w.N), _stream()), "gemm")
+    _count()
+    return out
+
+
+def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, bn=128):
+    P = xp.shape[0]
+    n_out = w.N // 2 if act != ACT_NONE else w.N
+    out = torch.empty(P, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=xp.device)
+    fmt, p0, p1, p2, p3 = _planes(w)
+    _check(_lib.cuda().mx_gemm(_p(xp), fmt, p0, p1, p2, p3, w.E, _p(out), n_out, int(out_f32), _p(bias), _vp(0), act, C.c_float(act_alpha),
+                               C.c_float(act_limit), P, w.N, w.K, _p(tile_expert), _p(num_tiles), bn, _stream()), "grouped gemm")
+    _count()
+    return out
+
+
+def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, slot_scale=None, out_f32=False):
+    S = slot_expert.numel()
+    n_out = w.N // 2 if act != ACT_NONE else w.N
+    out = torch.empty(S, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    fmt, p0, p1, p2, p3 = _planes(w)
+    _check(_lib.cuda().mx_gemv(fmt, p0, p1, p2, p3, _p(x), _p(out), _p(bias), 1, w.N, w.K, int(out_f32), act, C.c_float(act_alpha),
+                               C.c_float(act_limit), _p(slot_expert), _p(slot_scale), S, x_div, _stream()), "expert gemv")
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------ attention
+_attn_scratch: dict = {}
+
+
+def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0, n_splits=None):
+    Tq, n_q, hd = q.shape
+    n_kv, bs = k_cache.shape[1], k_cache.shape[2]
+    B = seq_lens.numel()
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    if n_splits is None:
+        # decode-sized problems: split the KV range so that ~2 CTAs per SM exist
+        ctas = B * n_kv * max(1, (max_q_len * (n_q // n_kv) + 31) // 32)
+        max_kv_tiles = max(1, (block_table.shape[1] * bs) // 64)
+        n_splits = max(1, min(max_kv_tiles, 32, (2 * 148) // max(ctas, 1)))
+    key = (q.device, n_splits * Tq * n_q * hd)
+    buf = _attn_scratch.get(q.device)
+    need = n_splits * Tq * n_q * (hd + 2)
+    if buf is None or buf.numel() < need:
+        buf = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+        _attn_scratch[q.device] = buf
+    o_part = buf[: n_splits * Tq * n_q * hd]
+    ml_part = buf[n_splits * Tq * n_q * hd: need]
+    out = torch.empty(Tq, n_q, hd, dtype=torch.bfloat16, device=q.device)
+    _check(_lib.cuda().mx_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), _p(seq_lens), _p(cu_q), _p(sinks), _p(out),
+                                    _p(o_part), _p(ml_part), B, Tq, int(max_q_len), n_q, n_kv, hd, block_table.shape[1], bs, int(window),
+                                    C.c_float(scale), C.c_float(softcap), int(n_splits), _stream()), "attention")
+    _count(2)
+    return out
+
+
+# ------------------------------------------------------------------ MoE
+def moe_route(logits, bias, k, renorm=True):
+    T, E = logits.shape
+    idx = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    _check(_lib.cuda().mx_moe_route(_p(logits), _p(bias), T, E, k, int(renorm), _p(idx), _p(w), _stream()), "moe_route")
+    _count()
+    return idx, w
+
+
+def moe_pack(topk_idx, E, e_lo=0, e_hi=None):
+    e_hi = E if e_hi is None else e_hi
+    T, K = topk_idx.shape
+    dev = topk_idx.device
+    n = T * K
+    max_rows = moe_max_rows(n, e_hi - e_lo)
+    counts = torch.empty(E, dtype=torch.int32, device=dev)
+    seg = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    packed_token = torch.empty(max_rows, dtype=torch.int32, device=dev)
+    pair_to_packed = torch.empty(n, dtype=torch.int32, device=dev)
+    tile_expert = torch.zeros(max_rows // MOE_TILE, dtype=torch.int32, device=dev)
+    num_tiles = torch.empty(2, dtype=torch.int32, device=dev)
+    _check(_lib.cuda().mx_moe_pack(_p(topk_idx), n, K, E, e_lo, e_hi, _p(counts), _p(seg), _p(packed_token), _p(pair_to_packed),
+                                   _p(tile_expert), _p(num_tiles), max_rows, _stream()), "moe_pack")
+    _count()
+    return MoePacking(counts, seg, packed_token, pair_to_packed, tile_expert, num_tiles, max_rows, K)
+
+
+def moe_gather(x, pk: MoePacking):
+    H = x.shape[1]
+    xp = torch.empty(pk.max_rows, H, dtype=torch.bfloat16, device=x.device)
+    _check(_lib.cuda().mx_moe_gather(_p(x), _p(pk.packed_token), _p(pk.num_tiles), _p(xp), H, pk.max_rows, _stream()), "moe_gather")
+    _count()
+    return xp
+
+
+def moe_combine(yp, pk: MoePacking, w, out=None, accumulate=False):
+    T, K = w.shape
+    H = yp.shape[1]
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.float32, device=yp.device)
+        accumulate = False
+    _check(_lib.cuda().mx_moe_combine(_p(yp), _p(pk.pair_to_packed), _p(w), _p(out), int(out.dtype == torch.float32), T, H, K,
+                                      int(accumulate), _stream()), "moe_combine")
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits):
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(_lib.cuda().mx_argmax(_p(logits), rows, V, logits.stride(0), _p(out), _stream()), "argmax")
+    _count()
+    return out
+
+
+def rep_penalty(logits, ids, penalty):
+    rows, V = logits.shape
+    _check(_lib.cuda().mx_rep_penalty(_p(logits), rows, V, logits.stride(0), _p(ids), ids.shape[1], _p(penalty), _stream()), "rep_penalty")
+    _count()
+    return logits
+
+
+def sample(logits, temperature, top_k, top_p, min_p, rng):
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(_lib.cuda().mx_sample(_p(logits), rows, V, logits.stride(0), _p(temperature), _p(top_k), _p(top_p), _p(min_p), _p(rng), _p(out),
+                                 _stream()), "sample")
+    _count()
+    return out

@@ -1,0 +1,362 @@
+"""Plain PyTorch fp32 twins of every kernel in ``csrc/cuda`` (same signatures as ``ops.cuda``).
+
+They are the numerical oracle of the GPU tests and the execution path on machines without a
+GPU (CPU plumbing runs, gloo multi-process tests).  Shapes, layouts (paged KV, 16-row gate/up
+interleave, packed MoE rows) and rounding points (bf16 activations) mirror the kernels.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .weights import QuantWeight
+
+ACT_NONE, ACT_SWIGLU, ACT_SWIGLU_OAI, ACT_GEGLU = 0, 1, 2, 3
+MOE_TILE = 128
+
+
+def _dense(w: QuantWeight) -> torch.Tensor:
+    if w._dense_cache is None:
+        w._dense_cache = w.dequantize(torch.float32)
+    return w._dense_cache
+
+
+def embed(w: QuantWeight, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    tbl = _dense(w)[0]
+    return tbl[ids.long().clamp(0, w.N - 1)] * scale
+
+
+def rmsnorm(x, w, eps, delta=None, dbias=None, one_plus_w=False, delta_scale=1.0, write_x=True, want_out=True):
+    if delta is not None:
+        d = delta.to(torch.float32)
+        if dbias is not None:
+            d = d + dbias
+        xs = x + d * delta_scale
+        if write_x:
+            x.copy_(xs)
+    else:
+        xs = x
+    if not want_out:
+        return None
+    g = (1.0 + w) if one_plus_w else w
+    inv = torch.rsqrt(xs.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return (xs * inv * g).to(torch.bfloat16)
+
+
+def _act(act, g, u, alpha, limit):
+    if act == ACT_SWIGLU:
+        return torch.nn.functional.silu(g) * u
+    if act == ACT_SWIGLU_OAI:
+        g = g.clamp(max=limit)
+        u = u.clamp(-limit, limit)
+        return g * torch.sigmoid(alpha * g) * (u + 1.0)
+    return torch.nn.functional.gelu(g, approximate="tanh") * u
+
+
+def _deinterleave16(y: torch.Tensor):
+    """[..., 2F] with 16-wide interleaved gate|up groups -> (gate [...,F], up [...,F])."""
+    F2 = y.shape[-1]
+    v = y.reshape(*y.shape[:-1], F2 // 32, 2, 16)
+    return v[..., 0, :].reshape(*y.shape[:-1], F2 // 2), v[..., 1, :].reshape(*y.shape[:-1], F2 // 2)
+
+
+def glu(x, act, alpha=1.702, limit=7.0):
+    g, u = _deinterleave16(x.to(torch.float32))
+    return _act(act, g, u, alpha, limit).to(torch.bfloat16)
+
+
+def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None):
+    y = x.to(torch.float32) @ _dense(w)[0].t()
+    if bias is not None:
+        y = y + bias
+    if act != ACT_NONE:
+        g, u = _deinterleave16(y)
+        y = _act(act, g, u, act_alpha, act_limit)
+    if row_scale is not None:
+        y = y * row_scale.unsqueeze(-1)
+    return y if out_f32 else y.to(torch.bfloat16)
+
+
+def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False):
+    """xp: packed rows [P,K]; tile t (rows 128t..128t+127) uses expert tile_expert[t] for t < num_tiles[0]."""
+    W = _dense(w)
+    P = xp.shape[0]
+    n_out = w.N // 2 if act != ACT_NONE else w.N
+    out = torch.zeros(P, n_out, dtype=torch.float32, device=xp.device)
+    nt = int(num_tiles[0])
+    te = tile_expert[:nt].tolist()
+    for t, e in enumerate(te):
+        rows = slice(t * MOE_TILE, min((t + 1) * MOE_TILE, P))
+        y = xp[rows].to(torch.float32) @ W[e].t()
+        if bias is not None:
+            y = y + bias[e]
+        if act != ACT_NONE:
+            g, u = _deinterleave16(y)
+            y = _act(act, g, u, act_alpha, act_limit)
+        out[rows] = y
+    return out if out_f32 else out.to(torch.bfloat16)
+
+
+def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, slot_scale=None, out_f32=False):
+    """y[s] = W[slot_expert[s]] @ x[s // x_div]."""
+    W = _dense(w)
+    S = slot_expert.numel()
+    rows = torch.arange(S, device=x.device) // x_div
+    xe = x.to(torch.float32)[rows]
+    y = torch.einsum("sk,snk->sn", xe, W[slot_expert.long()])
+    if bias is not None:
+        y = y + bias[slot_expert.long()]
+    if act != ACT_NONE:
+        g, u = _deinterleave16(y)
+        y = _act(act, g, u, act_alpha, act_limit)
+    if slot_scale is not None:
+        y = y * slot_scale.unsqueeze(-1)
+    return y if out_f32 else y.to(torch.bfloat16)
+
+
+def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_map, k_cache, v_cache, n_q, n_kv, hd, n_rot,
+             q_gate=False, norm_one_plus_w=False, eps=1e-6):
+    """Returns (q [T,n_q,hd] bf16, gate or None); writes K/V into the paged cache."""
+    T = qkv.shape[0]
+    x = qkv.to(torch.float32)
+    if bias is not None:
+        x = x + bias
+    q_stride = 2 * hd if q_gate else hd
+    qc = n_q * q_stride
+    qpart = x[:, :qc].reshape(T, n_q, q_stride)
+    gate = None
+    if q_gate:
+        gate = qpart[..., hd:].to(torch.bfloat16).contiguous()
+        qpart = qpart[..., :hd]
+    k = x[:, qc:qc + n_kv * hd].reshape(T, n_kv, hd)
+    v = x[:, qc + n_kv * hd:].reshape(T, n_kv, hd)
+
+    def norm(t, w):
+        if w is None:
+            return t
+        g = (1.0 + w) if norm_one_plus_w else w
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * g
+
+    qpart, k = norm(qpart, q_norm_w), norm(k, k_norm_w)
+    if n_rot > 0:
+        half = n_rot // 2
+        pos = positions.long().clamp(0, rope_cos.shape[0] - 1)
+        c, s = rope_cos[pos].unsqueeze(1), rope_sin[pos].unsqueeze(1)
+
+        def rope(t):
+            a, b = t[..., :half], t[..., half:n_rot]
+            return torch.cat([a * c - b * s, a * s + b * c, t[..., n_rot:]], dim=-1)
+
+        qpart, k = rope(qpart), rope(k)
+    bs = k_cache.shape[2]
+    ok = slot_map >= 0
+    blk, off = (slot_map[ok] // bs).long(), (slot_map[ok] % bs).long()
+    k_cache[blk, :, off] = k[ok].to(k_cache.dtype)
+    v_cache[blk, :, off] = v[ok].to(v_cache.dtype)
+    return qpart.to(torch.bfloat16).contiguous(), gate
+
+
+def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0, n_splits=1):
+    """q [Tq,n_q,hd]; caches [blocks,n_kv,bs,hd]; returns bf16 [Tq,n_q,hd]."""
+    Tq, n_q, hd = q.shape
+    n_kv, bs = k_cache.shape[1], k_cache.shape[2]
+    gqa = n_q // n_kv
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    out = torch.zeros(Tq, n_q, hd, dtype=torch.float32, device=q.device)
+    cu = cu_q.tolist()
+    for b in range(len(cu) - 1):
+        q0, q1 = cu[b], cu[b + 1]
+        if q1 <= q0:
+            continue
+        L = int(seq_lens[b])
+        nblk = (L + bs - 1) // bs
+        blocks = block_table[b, :nblk].long()
+        K = k_cache[blocks].permute(1, 0, 2, 3).reshape(n_kv, nblk * bs, hd)[:, :L].to(torch.float32)
+        V = v_cache[blocks].permute(1, 0, 2, 3).reshape(n_kv, nblk * bs, hd)[:, :L].to(torch.float32)
+        qq = q[q0:q1].to(torch.float32) * scale                                 # [t, n_q, hd]
+        Kh = K.repeat_interleave(gqa, dim=0)
+        Vh = V.repeat_interleave(gqa, dim=0)
+        s = torch.einsum("thd,hkd->htk", qq, Kh)
+        if softcap and softcap > 0:
+            s = softcap * torch.tanh(s / softcap)
+        qpos = torch.arange(L - (q1 - q0), L, device=q.device).unsqueeze(-1)
+        kpos = torch.arange(L, device=q.device).unsqueeze(0)
+        ok = kpos <= qpos
+        if window and window > 0:
+            ok = ok & (kpos > qpos - window)
+        s = s.masked_fill(~ok.unsqueeze(0), float("-inf"))
+        if sinks is not None:
+            sk = sinks.to(torch.float32).reshape(n_q, 1, 1).expand(n_q, q1 - q0, 1)
+            p = torch.softmax(torch.cat([s, sk], dim=-1), dim=-1)[..., :-1]
+        else:
+            p = torch.softmax(s, dim=-1)
+        out[q0:q1] = torch.einsum("htk,hkd->thd", p, Vh)
+    return out.to(torch.bfloat16)
+
+
+def sigmoid_mul(x, g):
+    return (x.to(torch.float32) * torch.sigmoid(g.to(torch.float32))).to(torch.bfloat16)
+
+
+def scaled_add(out, src, gate_logit=None):
+    s = src.to(torch.float32)
+    if gate_logit is not None:
+        s = s * torch.sigmoid(gate_logit).unsqueeze(-1)
+    out.add_(s)
+    return out
+
+
+def gated_rmsnorm(x, z, w, eps):
+    """x fp32 [rows,hd], z bf16 [rows,hd]."""
+    zz = z.to(torch.float32)
+    return (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w * torch.nn.functional.silu(zz)).to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------ MoE
+def moe_route(logits, bias, k, renorm=True):
+    x = logits.to(torch.float32)
+    if bias is not None:
+        x = x + bias
+    # descending value, ties -> lowest index (stable sort on -x)
+    order = torch.sort(-x, dim=-1, stable=True).indices[:, :k]
+    sel = torch.gather(x, 1, order)
+    if renorm:
+        w = torch.softmax(sel, dim=-1)
+    else:
+        w = torch.exp(sel - torch.logsumexp(x, dim=-1, keepdim=True))
+    return order.to(torch.int32), w
+
+
+@dataclass
+class MoePacking:
+    counts: torch.Tensor          # [E]
+    seg_start: torch.Tensor       # [E+1] padded segment starts
+    packed_token: torch.Tensor    # [max_rows] token of each packed row (-1 = pad)
+    pair_to_packed: torch.Tensor  # [T*K] packed row of each (token, slot) pair, -1 if not owned
+    tile_expert: torch.Tensor     # [max_tiles]
+    num_tiles: torch.Tensor       # [2]: live tiles, packed rows
+    max_rows: int
+    K: int
+
+
+def moe_max_rows(n_pairs: int, n_local_experts: int) -> int:
+    return (n_pairs + n_local_experts * (MOE_TILE - 1) + MOE_TILE - 1) // MOE_TILE * MOE_TILE
+
+
+def moe_pack(topk_idx, E, e_lo=0, e_hi=None):
+    e_hi = E if e_hi is None else e_hi
+    T, K = topk_idx.shape
+    dev = topk_idx.device
+    flat = topk_idx.reshape(-1).long()
+    n = flat.numel()
+    max_rows = moe_max_rows(n, e_hi - e_lo)
+    owned = (flat >= e_lo) & (flat < e_hi)
+    counts = torch.bincount(flat[owned], minlength=E)[:E]
+    padded = (counts + MOE_TILE - 1) // MOE_TILE * MOE_TILE
+    seg = torch.zeros(E + 1, dtype=torch.long, device=dev)
+    seg[1:] = torch.cumsum(padded, 0)
+    packed_token = torch.full((max_rows,), -1, dtype=torch.int32, device=dev)
+    pair_to_packed = torch.full((n,), -1, dtype=torch.int32, device=dev)
+    order = torch.sort(torch.where(owned, flat, torch.full_like(flat, E)), stable=True).indices
+    n_owned = int(owned.sum())
+    order = order[:n_owned]
+    e_sorted = flat[order]
+    rank_in_e = torch.arange(n_owned, device=dev) - torch.cumsum(counts, 0)[e_sorted] + counts[e_sorted]
+    dst = seg[e_sorted] + rank_in_e
+    packed_token[dst] = (order // K).to(torch.int32)
+    pair_to_packed[order] = dst.to(torch.int32)
+    tiles = (padded // MOE_TILE)
+    tile_expert = torch.repeat_interleave(torch.arange(E, device=dev), tiles).to(torch.int32)
+    max_tiles = max_rows // MOE_TILE
+    te = torch.zeros(max_tiles, dtype=torch.int32, device=dev)
+    te[: tile_expert.numel()] = tile_expert
+    num_tiles = torch.tensor([int(tiles.sum()), int(seg[E])], dtype=torch.int32, device=dev)
+    return MoePacking(counts.to(torch.int32), seg.to(torch.int32), packed_token, pair_to_packed, te, num_tiles, max_rows, K)
+
+
+def moe_gather(x, pk: MoePacking):
+    xp = torch.zeros(pk.max_rows, x.shape[1], dtype=x.dtype, device=x.device)
+    ok = pk.packed_token >= 0
+    xp[ok] = x[pk.packed_token[ok].long()]
+    return xp
+
+
+def moe_combine(yp, pk: MoePacking, w, out=None, accumulate=False):
+    """sum_k w[t,k] * yp[pos(t,k)] -> fp32 [T,H] (into ``out`` when given)."""
+    T, K = w.shape
+    pos = pk.pair_to_packed.reshape(T, K).long()
+    rows = yp.to(torch.float32)[pos.clamp_min(0)]                  # [T,K,H]
+    rows = rows * (pos >= 0).unsqueeze(-1) * w.unsqueeze(-1)
+    y = rows.sum(dim=1)
+    if out is None:
+        return y
+    if accumulate:
+        out.add_(y.to(out.dtype))
+    else:
+        out.copy_(y.to(out.dtype))
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits):
+    return torch.argmax(logits, dim=-1).to(torch.int32)   # first maximal index
+
+
+def rep_penalty(logits, ids, penalty):
+    for r in range(logits.shape[0]):
+        sel = ids[r][ids[r] >= 0].long()
+        if sel.numel() and float(penalty[r]) != 1.0:
+            v = logits[r, sel]
+            logits[r, sel] = torch.where(v > 0, v / penalty[r], v * penalty[r])
+    return logits
+
+
+def _xorshift(s: int) -> tuple[int, float]:
+    m = (1 << 64) - 1
+    s ^= s >> 12
+    s ^= (s << 25) & m
+    s ^= s >> 27
+    z = (s * 2685821657736338717) & m
+    return s, (z >> 40) / 16777216.0
+
+
+def sample(logits, temperature, top_k, top_p, min_p, rng):
+    """rng: int64/uint64-like tensor of xorshift states (updated in place).  Mirrors the kernel's order of cuts."""
+    CAP = 256
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    for r in range(rows):
+        t = float(temperature[r])
+        k = int(top_k[r])
+        if k <= 0 or k > CAP:
+            k = CAP
+        k = min(k, V)
+        if t <= 0:
+            out[r] = int(torch.argmax(logits[r]))
+            continue
+        order = torch.sort(-logits[r].to(torch.float32), stable=True).indices[:k]
+        vals = logits[r, order].to(torch.float32)
+        p = torch.exp((vals - vals[0]) / t)
+        keep = k
+        tp, mp = float(top_p[r]), float(min_p[r])
+        if 0 < tp < 1:
+            c = torch.cumsum(p / p.sum(), 0)
+            hit = torch.nonzero(c >= tp)
+            if hit.numel():
+                keep = int(hit[0]) + 1
+        if mp > 0:
+            n = 1
+            while n < keep and float(p[n]) >= mp * float(p[0]):
+                n += 1
+            keep = n
+        state = int(rng[r]) & ((1 << 64) - 1)
+        state, u = _xorshift(state)
+        rng[r] = state if state < (1 << 63) else state - (1 << 64)
+        u = u * float(p[:keep].sum())
+        c = torch.cumsum(p[:keep], 0)
+        hit = torch.nonzero(u < c)
+        out[r] = int(order[int(hit[0])]) if hit.numel() else int(order[keep - 1])
+    return out

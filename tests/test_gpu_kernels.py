@@ -1,0 +1,298 @@
+"""Numerics of every sm_100a kernel against the PyTorch fp32 oracle (ops.ref), small and ragged shapes.
+
+Mirrors the reference's per-kernel unit tests (tests/unit/*.cpp: attention_test, moe_test,
+gemv_q4k_test, mxfp4_dequant_test, sampler_test, elementwise_test) with the host scalar
+references replaced by ops.ref.
+"""
+import math
+
+import pytest
+import torch
+
+from machx_inference_engine_b200.ops import ref
+from machx_inference_engine_b200.ops.weights import WFormat, from_dense
+
+pytestmark = pytest.mark.gpu
+
+FMTS = [WFormat.BF16, WFormat.Q8, WFormat.Q4K, WFormat.Q6K, WFormat.MXFP4]
+
+
+def K():
+    from machx_inference_engine_b200.ops import cuda
+    return cuda
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+def make_weight(fmt, N, Kd, E=1, seed=0, scale=0.05):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    w = torch.randn(E, N, Kd, generator=g) * scale
+    return from_dense(w, fmt).to(dev())
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_dequant_layouts_roundtrip(fmt):
+    # the runtime layout decodes (on the GPU through embed) to what the torch decoder says
+    qw = make_weight(fmt, 64, 512)
+    ids = torch.arange(64, dtype=torch.int32, device=dev())
+    got = K().embed(qw, ids)
+    want = qw.dequantize()[0]
+    assert torch.allclose(got, want, rtol=0, atol=1e-6 * float(want.abs().max()) + 1e-7), rel_err(got, want)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_gemv(fmt, M):
+    N, Kd = 200, 768            # N not a multiple of the 16 rows per CTA
+    qw = make_weight(fmt, N, Kd)
+    x = (torch.randn(M, Kd, device=dev()) * 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device=dev())
+    got = K().linear(x, qw, bias=bias, out_f32=True)
+    want = ref.linear(x, qw, bias=bias, out_f32=True)
+    assert rel_err(got, want) < 2e-3
+
+
+@pytest.mark.parametrize("fmt", [WFormat.BF16, WFormat.MXFP4, WFormat.Q4K])
+def test_gemv_gated(fmt):
+    F, Kd = 96, 512
+    qw = make_weight(fmt, 2 * F, Kd)
+    x = (torch.randn(2, Kd, device=dev())).to(torch.bfloat16)
+    bias = torch.randn(2 * F, device=dev()) * 0.1
+    for act in (ref.ACT_SWIGLU, ref.ACT_SWIGLU_OAI, ref.ACT_GEGLU):
+        got = K().linear(x, qw, bias=bias, act=act, out_f32=True)
+        want = ref.linear(x, qw, bias=bias, act=act, out_f32=True)
+        assert rel_err(got, want) < 3e-3, act
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("shape", [(128, 128, 256), (200, 328, 512), (1000, 2880, 2816)])
+def test_gemm_tcgen05(fmt, shape):
+    M, N, Kd = shape
+    if fmt in (WFormat.Q4K, WFormat.Q6K) and Kd % 256:
+        pytest.skip("super-block formats need K % 256 == 0")
+    qw = make_weight(fmt, N, Kd)
+    x = (torch.randn(M, Kd, device=dev()) * 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device=dev())
+    for bn in (128, 64, 32):
+        got = K().gemm(x, qw, bias=bias, out_f32=True, bn=bn)
+        K().check_status()
+        want = ref.linear(x, qw, bias=bias, out_f32=True)
+        # weights pass through bf16 inside the tensor-core path
+        assert rel_err(got, want) < 6e-3, (bn, rel_err(got, want))
+
+
+def test_gemm_ragged_k_and_bf16_out():
+    M, N, Kd = 130, 72, 2880      # K = 45 * 64, N not a multiple of 32
+    qw = make_weight(WFormat.MXFP4, N, Kd)
+    x = (torch.randn(M, Kd, device=dev()) * 0.5).to(torch.bfloat16)
+    got = K().gemm(x, qw)
+    want = ref.linear(x, qw)
+    assert got.dtype == torch.bfloat16 and rel_err(got, want) < 1e-2
+    qw = make_weight(WFormat.BF16, N, 2888)     # K % 64 == 8: TMA zero fill on the last k tile
+    x = (torch.randn(M, 2888, device=dev()) * 0.5).to(torch.bfloat16)
+    assert rel_err(K().gemm(x, qw, out_f32=True), ref.linear(x, qw, out_f32=True)) < 6e-3
+
+
+@pytest.mark.parametrize("act", [ref.ACT_SWIGLU, ref.ACT_SWIGLU_OAI, ref.ACT_GEGLU])
+def test_gemm_gated_epilogue(act):
+    M, F, Kd = 300, 160, 512
+    qw = make_weight(WFormat.MXFP4, 2 * F, Kd)
+    x = (torch.randn(M, Kd, device=dev())).to(torch.bfloat16)
+    bias = torch.randn(2 * F, device=dev()) * 0.1
+    got = K().gemm(x, qw, bias=bias, act=act, out_f32=True)
+    want = ref.linear(x, qw, bias=bias, act=act, out_f32=True)
+    assert rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("fmt", [WFormat.MXFP4, WFormat.Q8, WFormat.BF16])
+def test_grouped_gemm_and_moe_pipeline(fmt):
+    T, H, F, E, topk = 300, 256, 128, 8, 2
+    torch.manual_seed(1)
+    x = (torch.randn(T, H, device=dev())).to(torch.bfloat16)
+    logits = torch.randn(T, E, device=dev())
+    rb = torch.randn(E, device=dev()) * 0.1
+    idx, w = K().moe_route(logits, rb, topk)
+    idx_r, w_r = ref.moe_route(logits, rb, topk)
+    assert torch.equal(idx, idx_r) and torch.allclose(w, w_r, atol=1e-5)
+    pk = K().moe_pack(idx, E)
+    pk_r = ref.moe_pack(idx, E)
+    assert torch.equal(pk.num_tiles, pk_r.num_tiles)
+    nrows = int(pk.num_tiles[1])
+    assert torch.equal(pk.packed_token[:nrows], pk_r.packed_token[:nrows])
+    assert torch.equal(pk.pair_to_packed, pk_r.pair_to_packed)
+    assert torch.equal(pk.tile_expert[: int(pk.num_tiles[0])], pk_r.tile_expert[: int(pk.num_tiles[0])])
+    xp = K().moe_gather(x, pk)
+    assert torch.equal(xp[:nrows], ref.moe_gather(x, pk_r)[:nrows])
+    gu = make_weight(fmt, 2 * F, H, E=E, seed=3)
+    dn = make_weight(fmt, H, F, E=E, seed=4)
+    gb = torch.randn(E, 2 * F, device=dev()) * 0.1
+    db = torch.randn(E, H, device=dev()) * 0.1
+    h = K().grouped_linear(xp, gu, pk.tile_expert, pk.num_tiles, bias=gb, act=ref.ACT_SWIGLU_OAI)
+    h_r = ref.grouped_linear(xp, gu, pk_r.tile_expert, pk_r.num_tiles, bias=gb, act=ref.ACT_SWIGLU_OAI)
+    live = pk.packed_token[:nrows] >= 0
+    assert rel_err(h[:nrows][live], h_r[:nrows][live]) < 1.5e-2
+    y = K().grouped_linear(h, dn, pk.tile_expert, pk.num_tiles, bias=db)
+    y_r = ref.grouped_linear(h_r, dn, pk_r.tile_expert, pk_r.num_tiles, bias=db)
+    out = K().moe_combine(y, pk, w)
+    out_r = ref.moe_combine(y_r, pk_r, w_r)
+    assert rel_err(out, out_r) < 2e-2
+    # expert-parallel packing: only experts [2,5) are owned
+    pk2, pk2_r = K().moe_pack(idx, E, 2, 5), ref.moe_pack(idx, E, 2, 5)
+    assert torch.equal(pk2.pair_to_packed, pk2_r.pair_to_packed) and torch.equal(pk2.num_tiles, pk2_r.num_tiles)
+
+
+def test_expert_gemv():
+    H, F, E = 512, 64, 8
+    gu = make_weight(WFormat.MXFP4, 2 * F, H, E=E, seed=5)
+    dn = make_weight(WFormat.MXFP4, H, F, E=E, seed=6)
+    x = torch.randn(2, H, device=dev()).to(torch.bfloat16)
+    slot_e = torch.tensor([1, 7, 3, 0, 2, 2, 5, 4], dtype=torch.int32, device=dev())   # 2 tokens x 4 slots
+    gb = torch.randn(E, 2 * F, device=dev()) * 0.1
+    h = K().expert_gemv(x, gu, slot_e, x_div=4, bias=gb, act=ref.ACT_SWIGLU_OAI)
+    h_r = ref.expert_gemv(x, gu, slot_e, x_div=4, bias=gb, act=ref.ACT_SWIGLU_OAI)
+    assert rel_err(h, h_r) < 1e-2
+    sc = torch.rand(8, device=dev())
+    y = K().expert_gemv(h, dn, slot_e, x_div=1, slot_scale=sc, out_f32=True)
+    y_r = ref.expert_gemv(h, dn, slot_e, x_div=1, slot_scale=sc, out_f32=True)
+    assert rel_err(y, y_r) < 5e-3
+
+
+def test_rmsnorm_residual_and_saturation():
+    T, H = 37, 2880
+    x = torch.randn(T, H, device=dev()) * 3
+    x[0, :8] = 70000.0           # beyond fp16 range: the fp32 residual stream needs no clamp
+    d = (torch.randn(T, H, device=dev())).to(torch.bfloat16)
+    db = torch.randn(H, device=dev())
+    w = torch.rand(H, device=dev()) + 0.5
+    for opw in (False, True):
+        xa, xb = x.clone(), x.clone()
+        got = K().rmsnorm(xa, w, 1e-5, delta=d, dbias=db, one_plus_w=opw)
+        want = ref.rmsnorm(xb, w, 1e-5, delta=d, dbias=db, one_plus_w=opw)
+        assert torch.allclose(xa, xb, atol=1e-5) and torch.isfinite(got.float()).all()
+        assert rel_err(got, want) < 5e-3
+    got = K().rmsnorm(x.clone(), w, 1e-5)
+    assert rel_err(got, ref.rmsnorm(x.clone(), w, 1e-5)) < 5e-3
+
+
+def test_glu_and_gates():
+    x = torch.randn(33, 2 * 48, device=dev()).to(torch.bfloat16) * 4
+    for act in (ref.ACT_SWIGLU, ref.ACT_SWIGLU_OAI, ref.ACT_GEGLU):
+        assert rel_err(K().glu(x, act), ref.glu(x, act)) < 1e-2
+    a = torch.randn(100, 64, device=dev()).to(torch.bfloat16)
+    g = torch.randn(100, 64, device=dev()).to(torch.bfloat16)
+    assert rel_err(K().sigmoid_mul(a, g), ref.sigmoid_mul(a, g)) < 1e-2
+    o1 = torch.randn(100, 64, device=dev())
+    o2 = o1.clone()
+    gl = torch.randn(100, device=dev())
+    K().scaled_add(o1, a, gl)
+    ref.scaled_add(o2, a, gl)
+    assert torch.allclose(o1, o2, atol=1e-4)
+    xx = torch.randn(50, 128, device=dev())
+    z = torch.randn(50, 128, device=dev()).to(torch.bfloat16)
+    w = torch.rand(128, device=dev())
+    assert rel_err(K().gated_rmsnorm(xx, z, w, 1e-6), ref.gated_rmsnorm(xx, z, w, 1e-6)) < 1e-2
+
+
+def _rope_tables(max_pos, n_rot, theta=10000.0):
+    inv = theta ** (-torch.arange(0, n_rot, 2, dtype=torch.float32) / n_rot)
+    ang = torch.arange(max_pos, dtype=torch.float32)[:, None] * inv[None]
+    return torch.cos(ang).to(dev()), torch.sin(ang).to(dev())
+
+
+@pytest.mark.parametrize("cfg", [dict(n_q=4, n_kv=2, hd=64, n_rot=64, gate=False, norm=False, bias=True),
+                                 dict(n_q=8, n_kv=2, hd=128, n_rot=128, gate=False, norm=True, bias=False),
+                                 dict(n_q=4, n_kv=1, hd=256, n_rot=64, gate=True, norm=True, bias=False)])
+def test_qkv_post(cfg):
+    T, bs, nblk = 19, 128, 4
+    n_q, n_kv, hd = cfg["n_q"], cfg["n_kv"], cfg["hd"]
+    cols = n_q * hd * (2 if cfg["gate"] else 1) + 2 * n_kv * hd
+    qkv = torch.randn(T, cols, device=dev()).to(torch.bfloat16)
+    bias = torch.randn(cols, device=dev()) if cfg["bias"] else None
+    qn = torch.rand(hd, device=dev()) if cfg["norm"] else None
+    kn = torch.rand(hd, device=dev()) if cfg["norm"] else None
+    pos = torch.arange(100, 100 + T, dtype=torch.int32, device=dev())
+    cos, sin = _rope_tables(256, cfg["n_rot"])
+    slots = (torch.arange(T, device=dev()) + 130).to(torch.int64)
+    slots[3] = -1
+    kc = [torch.zeros(nblk, n_kv, bs, hd, dtype=torch.bfloat16, device=dev()) for _ in range(2)]
+    vc = [torch.zeros_like(kc[0]) for _ in range(2)]
+    q1, g1 = K().qkv_post(qkv, bias, qn, kn, pos, cos, sin, slots, kc[0], vc[0], n_q, n_kv, hd, cfg["n_rot"], q_gate=cfg["gate"])
+    q2, g2 = ref.qkv_post(qkv, bias, qn, kn, pos, cos, sin, slots, kc[1], vc[1], n_q, n_kv, hd, cfg["n_rot"], q_gate=cfg["gate"])
+    assert rel_err(q1, q2) < 1e-2 and rel_err(kc[0], kc[1]) < 1e-2 and rel_err(vc[0], vc[1]) < 1e-2
+    if cfg["gate"]:
+        assert rel_err(g1, g2) < 1e-2
+
+
+def _paged_case(B, q_lens, kv_lens, n_q, n_kv, hd, bs=128, seed=0):
+    torch.manual_seed(seed)
+    max_blocks = max((L + bs - 1) // bs for L in kv_lens)
+    nblk = B * max_blocks + 1
+    kc = torch.randn(nblk, n_kv, bs, hd, device=dev()).to(torch.bfloat16)
+    vc = torch.randn(nblk, n_kv, bs, hd, device=dev()).to(torch.bfloat16)
+    perm = torch.randperm(nblk - 1)[: B * max_blocks].reshape(B, max_blocks) + 1
+    bt = perm.to(torch.int32).to(dev())
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev())
+    q = torch.randn(sum(q_lens), n_q, hd, device=dev()).to(torch.bfloat16)
+    sl = torch.tensor(kv_lens, dtype=torch.int32, device=dev())
+    return q, kc, vc, bt, sl, cu
+
+
+@pytest.mark.parametrize("hd,n_q,n_kv", [(64, 16, 2), (128, 8, 2), (256, 4, 1)])
+@pytest.mark.parametrize("window", [0, 128])
+def test_attention_decode_and_prefill(hd, n_q, n_kv, window):
+    sinks = torch.randn(n_q, device=dev())
+    # decode: 3 sequences, one query each, different context lengths; forced split counts
+    q, kc, vc, bt, sl, cu = _paged_case(3, [1, 1, 1], [1, 300, 515], n_q, n_kv, hd)
+    for splits in (1, 3, None):
+        got = K().attention(q, kc, vc, bt, sl, cu, 1, sinks=sinks, window=window, n_splits=splits)
+        want = ref.attention(q, kc, vc, bt, sl, cu, 1, sinks=sinks, window=window)
+        assert rel_err(got, want) < 1e-2, splits
+    # prefill / verify: ragged query lengths, causal, continuing an existing context
+    q, kc, vc, bt, sl, cu = _paged_case(3, [70, 5, 130], [70, 205, 400], n_q, n_kv, hd, seed=1)
+    got = K().attention(q, kc, vc, bt, sl, cu, 130, window=window, softcap=30.0)
+    want = ref.attention(q, kc, vc, bt, sl, cu, 130, window=window, softcap=30.0)
+    assert rel_err(got, want) < 1e-2
+    # algebraic identity: constant V rows -> output equals that constant when there is no sink
+    vc.fill_(0.25)
+    got = K().attention(q, kc, vc, bt, sl, cu, 130, window=window)
+    assert torch.allclose(got.float(), torch.full_like(got.float(), 0.25), atol=2e-3)
+
+
+def test_sampling():
+    V = 5003
+    logits = torch.randn(4, V, device=dev())
+    logits[0, 10] = logits[0, 4000] = 50.0       # tie -> lowest id
+    assert K().argmax(logits).tolist() == ref.argmax(logits).tolist() and int(K().argmax(logits)[0]) == 10
+    ids = torch.full((4, 6), -1, dtype=torch.int32, device=dev())
+    ids[0, :3] = torch.tensor([10, 77, 4000])
+    ids[2, :2] = torch.tensor([5, 6])
+    pen = torch.tensor([1.3, 1.0, 2.0, 1.1], device=dev())
+    a, b = logits.clone(), logits.clone()
+    K().rep_penalty(a, ids, pen)
+    ref.rep_penalty(b, ids, pen)
+    assert torch.allclose(a, b)
+    temp = torch.tensor([0.0, 0.8, 1.0, 1.5], device=dev())
+    top_k = torch.tensor([0, 40, 5, 0], dtype=torch.int32, device=dev())
+    top_p = torch.tensor([1.0, 0.9, 1.0, 0.5], device=dev())
+    min_p = torch.tensor([0.0, 0.0, 0.05, 0.0], device=dev())
+    rng1 = torch.tensor([1, 88172645463325252, 1234567, 99], dtype=torch.int64, device=dev())
+    rng2 = rng1.clone().cpu()
+    for _ in range(5):
+        got = K().sample(logits, temp, top_k, top_p, min_p, rng1)
+        want = ref.sample(logits.cpu(), temp.cpu(), top_k.cpu(), top_p.cpu(), min_p.cpu(), rng2)
+        assert got.cpu().tolist() == want.tolist()
+    assert rng1.cpu().tolist() == rng2.tolist()
+
+
+def test_run_twice_is_bit_identical():
+    qw = make_weight(WFormat.MXFP4, 512, 1024)
+    x = torch.randn(300, 1024, device=dev()).to(torch.bfloat16)
+    a, b = K().gemm(x, qw, out_f32=True), K().gemm(x, qw, out_f32=True)
+    assert torch.equal(a, b)
