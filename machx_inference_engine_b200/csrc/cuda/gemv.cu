@@ -116,6 +116,19 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams 
       }
     }
   }
+  if (FMT == WF_BF16 && (p.K & 31)) {
+    // ragged tail of a bf16 row (K % 32 != 0): one element per lane
+    const int k = nkb * 32 + lane;
+    if (k < p.K) {
+#pragma unroll
+      for (int r = 0; r < GEMV_ROWS; ++r) {
+        const float wv1 = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rp[r].p0)[k]);
+#pragma unroll
+        for (int m = 0; m < MM; ++m)
+          if (m < p.M) acc[r][m] = fmaf(wv1, __bfloat162float(x[(size_t)m * p.K + k]), acc[r][m]);
+      }
+    }
+  }
 #pragma unroll
   for (int r = 0; r < GEMV_ROWS; ++r)
 #pragma unroll
@@ -226,7 +239,7 @@ MX_HOST_API int mx_gemv(int wfmt, const void* w0, const void* w1, const void* w2
                         const int* slot_expert, const float* slot_scale, int slots, int x_div, cudaStream_t stream) {
   using namespace mx;
   if (N <= 0 || K <= 0) return 0;
-  if (K % 32) return -102;
+  if (K % 32 && !(wfmt == WF_BF16 && K % 8 == 0 && act == 0)) return -102;
   if ((wfmt == WF_Q4K || wfmt == WF_Q6K) && (K % 256)) return -103;
   if (!slot_expert && act == 0 && (M < 1 || M > GEMV_MAX_M)) return -106;
   GemvParams p;

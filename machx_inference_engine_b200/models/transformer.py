@@ -1,0 +1,429 @@
+"""One decoder-only graph for the attention-based families: dense Llama / Qwen2 / Qwen3 / Mistral /
+Phi-3 / Granite, Qwen3-MoE and gpt-oss (attention sinks, alternating sliding window, biased
+projections, clamped SwiGLU, MXFP4 experts).  Hybrid (gated-DeltaNet) layers plug in through
+``models/hybrid.py``.
+
+The graph is config-driven instead of one class per family: the reference copies its dense
+forward for every architecture (src/model/dense_transformer.cpp:381-744, gptoss.cpp:312-523,
+qwen3moe.cpp) and again for every parallel form (dense_tp.cpp, gptoss_tp.cpp, qwen3moe_tp.cpp);
+here parallelism is a property of the linear layers (:class:`ParallelCtx`).
+
+Per layer the launch sequence is
+  rmsnorm(+residual) -> qkv GEMM -> qkv_post (bias, QK-norm, RoPE, paged KV write) -> attention
+  -> o GEMM [-> all-reduce] -> rmsnorm(+residual) -> FFN (gate|up GEMM with fused activation,
+  down GEMM) or MoE (router GEMM, top-k, pack, gather, grouped GEMMs, combine) [-> all-reduce].
+The residual stream is fp32, activations bf16; nothing goes back to the host inside forward.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..formats.model_config import ModelConfig
+from ..ops import ACT_GEGLU, ACT_NONE, ACT_SWIGLU, ACT_SWIGLU_OAI, QuantWeight
+from ..parallel.comm import ParallelCtx
+from ..utils.rope import rope_tables
+
+KV_BLOCK = 128
+
+
+@dataclass
+class ForwardBatch:
+    """Device-side description of one step (prefill chunk(s), decode tokens, or a mix)."""
+    ids: torch.Tensor            # int32 [T]
+    positions: torch.Tensor      # int32 [T]
+    slot_map: torch.Tensor       # int64 [T]  block*KV_BLOCK + offset, <0 = do not cache
+    block_table: torch.Tensor    # int32 [B, max_blocks]
+    seq_lens: torch.Tensor       # int32 [B]  kv length after this step
+    cu_q: torch.Tensor           # int32 [B+1]
+    max_q_len: int
+    logit_rows: Optional[torch.Tensor] = None   # int64 rows of the T tokens that need logits (None: last of each sequence)
+    state_slots: Optional[torch.Tensor] = None  # int32 [B] recurrent-state slot per sequence (hybrid models)
+    q_lens_host: Optional[list] = None          # host copy of per-sequence query lengths (hybrid scan scheduling)
+    start_host: Optional[list] = None           # host copy of per-sequence start positions (0 = fresh state)
+    want_hidden: bool = False                   # also return the pre-final-norm hidden rows (MTP)
+
+    @property
+    def T(self) -> int:
+        return self.ids.numel()
+
+    @property
+    def B(self) -> int:
+        return self.seq_lens.numel()
+
+
+class KVCache:
+    """Paged KV: per attention layer ``k, v [num_blocks, n_kv_local, KV_BLOCK, head_dim]`` bf16.
+
+    The reference cache is contiguous per sequence (include/ie/kv_cache.hpp:27-114); pages make
+    continuous batching and block-level prefix sharing possible.
+    """
+
+    def __init__(self, n_layers: int, num_blocks: int, n_kv: int, head_dim: int, device, attn_layers: Optional[list[int]] = None):
+        self.num_blocks = num_blocks
+        self.block_size = KV_BLOCK
+        layers = attn_layers if attn_layers is not None else list(range(n_layers))
+        self.k = {l: torch.zeros(num_blocks, n_kv, KV_BLOCK, head_dim, dtype=torch.bfloat16, device=device) for l in layers}
+        self.v = {l: torch.zeros(num_blocks, n_kv, KV_BLOCK, head_dim, dtype=torch.bfloat16, device=device) for l in layers}
+
+    @staticmethod
+    def bytes_per_block(n_attn_layers: int, n_kv: int, head_dim: int) -> int:
+        return 2 * n_attn_layers * n_kv * KV_BLOCK * head_dim * 2
+
+    def copy_blocks(self, src: list[int], dst: list[int]) -> None:
+        if not src:
+            return
+        s = torch.tensor(src, dtype=torch.long, device=next(iter(self.k.values())).device)
+        d = torch.tensor(dst, dtype=torch.long, device=s.device)
+        for l in self.k:
+            self.k[l][d] = self.k[l][s]
+            self.v[l][d] = self.v[l][s]
+
+
+# ---------------------------------------------------------------------------------------------
+class Linear:
+    """y = x W^T (+b).  ``reduce`` marks a row-parallel layer whose output is a partial sum."""
+
+    def __init__(self, w: QuantWeight, bias: Optional[torch.Tensor] = None, act: int = ACT_NONE, act_alpha: float = 1.702,
+                 act_limit: float = 7.0, reduce: bool = False):
+        self.w, self.bias, self.act, self.act_alpha, self.act_limit, self.reduce = w, bias, act, act_alpha, act_limit, reduce
+
+    def __call__(self, x: torch.Tensor, par: Optional[ParallelCtx] = None, out_f32: bool = False) -> torch.Tensor:
+        if self.reduce and par is not None and par.enabled:
+            if par.fused is not None and x.is_cuda:
+                return par.fused.linear_all_reduce(x, self.w, self.bias)
+            y = ops.linear(x, self.w, bias=self.bias, out_f32=True)
+            return par.all_reduce(y)
+        return ops.linear(x, self.w, bias=self.bias, act=self.act, act_alpha=self.act_alpha, act_limit=self.act_limit, out_f32=out_f32)
+
+
+class MultiLinear:
+    """Column-concatenation of linears whose weights have different storage formats (e.g. Q4_K q/k with Q6_K v)."""
+
+    def __init__(self, parts: list[Linear]):
+        self.parts = parts
+
+    def __call__(self, x, par=None, out_f32=False):
+        return torch.cat([p(x, par, out_f32) for p in self.parts], dim=1)
+
+
+def _fuse_rows(ws: list[QuantWeight], biases: list[Optional[torch.Tensor]]):
+    if all(w.fmt == ws[0].fmt for w in ws):
+        b = None
+        if any(bb is not None for bb in biases):
+            b = torch.cat([bb if bb is not None else torch.zeros(w.N, device=w.device) for w, bb in zip(ws, biases)])
+        return Linear(QuantWeight.cat_rows(ws), b)
+    return MultiLinear([Linear(w, b) for w, b in zip(ws, biases)])
+
+
+def unpermute_llama_qk(w: QuantWeight, n_heads: int, head_dim: int) -> QuantWeight:
+    """GGUF ``llama`` files store Q/K rows interleaved for pairwise RoPE; the kernels rotate NEOX
+    half-splits, so rows are regrouped: dest h*hd + b*hd/2 + k  <-  src h*hd + 2k + b
+    (src/model/dense_transformer.cpp:24-32,130-137)."""
+    hd = head_dim
+    k = torch.arange(hd // 2)
+    src = torch.cat([2 * k, 2 * k + 1])                       # b = 0 block then b = 1 block
+    idx = (torch.arange(n_heads).unsqueeze(1) * hd + src.unsqueeze(0)).reshape(-1)
+    return w.select_rows(idx)
+
+
+class AttentionBlock:
+    def __init__(self, cfg: ModelConfig, layer: int, src, par: ParallelCtx, prefix: Optional[str] = None, q_gate: bool = False):
+        c = cfg
+        p = prefix or f"blk.{layer}"
+        hd, H = c.head_dim, c.hidden
+        tp = par.world if par.mode == "tp" else 1
+        self.layer = layer
+        self.q_gate = q_gate
+        self.n_q = c.n_heads // tp
+        if c.n_heads % tp:
+            raise ValueError(f"{c.n_heads} attention heads do not split over {tp} ranks")
+        # KV heads: shard when they divide, otherwise each rank keeps the one head its query heads use
+        if c.n_kv_heads >= tp:
+            if c.n_kv_heads % tp:
+                raise ValueError(f"{c.n_kv_heads} KV heads do not split over {tp} ranks")
+            self.n_kv = c.n_kv_heads // tp
+            kv_lo = par.rank * self.n_kv if tp > 1 else 0
+        else:
+            self.n_kv = 1
+            kv_lo = (par.rank * c.n_kv_heads) // tp
+        q_lo = (par.rank * self.n_q) if tp > 1 else 0
+        q_rows_per_head = hd * (2 if q_gate else 1)
+
+        if c.arch == "phi3" and not src.has(f"{p}.attn_q.weight"):
+            # Phi-3 files keep one fused attn_qkv matrix: q rows, then k rows, then v rows
+            nq_rows, nkv_rows = c.n_heads * hd, c.n_kv_heads * hd
+            fused = src.matrix(f"{p}.attn_qkv.weight", nq_rows + 2 * nkv_rows, H)
+            wq, wk, wv = fused.slice_rows(0, nq_rows), fused.slice_rows(nq_rows, nq_rows + nkv_rows), fused.slice_rows(nq_rows + nkv_rows, nq_rows + 2 * nkv_rows)
+        else:
+            wq = src.matrix(f"{p}.attn_q.weight", c.n_heads * q_rows_per_head, H)
+            wk = src.matrix(f"{p}.attn_k.weight", c.n_kv_heads * hd, H)
+            wv = src.matrix(f"{p}.attn_v.weight", c.n_kv_heads * hd, H)
+        if c.arch == "llama" and getattr(src, "r", None) is not None:
+            wq, wk = unpermute_llama_qk(wq, c.n_heads, hd), unpermute_llama_qk(wk, c.n_kv_heads, hd)
+        has_bias = c.arch in ("qwen2", "gpt-oss") and src.has(f"{p}.attn_q.bias")
+        bq = src.vector(f"{p}.attn_q.bias", c.n_heads * q_rows_per_head) if has_bias else None
+        bk = src.vector(f"{p}.attn_k.bias", c.n_kv_heads * hd) if has_bias else None
+        bv = src.vector(f"{p}.attn_v.bias", c.n_kv_heads * hd) if has_bias else None
+        sl = lambda w, lo, n: w.slice_rows(lo, lo + n)
+        sb = lambda b, lo, n: None if b is None else b[lo:lo + n].contiguous()
+        ws = [sl(wq, q_lo * q_rows_per_head, self.n_q * q_rows_per_head), sl(wk, kv_lo * hd, self.n_kv * hd), sl(wv, kv_lo * hd, self.n_kv * hd)]
+        bs = [sb(bq, q_lo * q_rows_per_head, self.n_q * q_rows_per_head), sb(bk, kv_lo * hd, self.n_kv * hd), sb(bv, kv_lo * hd, self.n_kv * hd)]
+        self.qkv = _fuse_rows(ws, bs)
+        wo = src.matrix(f"{p}.attn_output.weight", H, c.n_heads * hd)
+        bo = src.vector(f"{p}.attn_output.bias", H) if (c.arch == "gpt-oss" and src.has(f"{p}.attn_output.bias")) else None
+        if tp > 1:
+            wo = wo.slice_k(q_lo * hd, (q_lo + self.n_q) * hd)
+            bo = bo if par.rank == 0 else None              # added once, before the reduction
+        self.o = Linear(wo, bo, reduce=tp > 1)
+        qk_norm = c.arch in ("qwen3", "qwen3moe", "qwen3next", "qwen35", "qwen35moe") and src.has(f"{p}.attn_q_norm.weight")
+        self.q_norm = src.vector(f"{p}.attn_q_norm.weight", hd) if qk_norm else None
+        self.k_norm = src.vector(f"{p}.attn_k_norm.weight", hd) if qk_norm else None
+        self.sinks = None
+        if c.arch == "gpt-oss":
+            s = src.vector(f"{p}.attn_sinks.weight", c.n_heads)
+            self.sinks = s[q_lo:q_lo + self.n_q].contiguous()
+        self.window = c.layer_window(layer)
+        self.scale = c.attention_scale if c.attention_scale > 0 else 1.0 / math.sqrt(hd)
+        self.hd, self.n_rot, self.eps = hd, c.n_rot, c.rms_eps
+        self.norm_one_plus_w = c.arch in ("qwen3next", "qwen35", "qwen35moe")
+
+    def __call__(self, h: torch.Tensor, fb: ForwardBatch, kv: KVCache, rope, par: ParallelCtx) -> torch.Tensor:
+        qkv = self.qkv(h)
+        q, gate = ops.qkv_post(qkv, None, self.q_norm, self.k_norm, fb.positions, rope[0], rope[1], fb.slot_map, kv.k[self.layer],
+                               kv.v[self.layer], self.n_q, self.n_kv, self.hd, self.n_rot, q_gate=self.q_gate,
+                               norm_one_plus_w=self.norm_one_plus_w, eps=self.eps)
+        a = ops.attention(q, kv.k[self.layer], kv.v[self.layer], fb.block_table, fb.seq_lens, fb.cu_q, fb.max_q_len, sinks=self.sinks,
+                          window=self.window, scale=self.scale)
+        a = a.reshape(a.shape[0], self.n_q * self.hd)
+        if gate is not None:
+            a = ops.sigmoid_mul(a, gate.reshape(a.shape))
+        return self.o(a, par)
+
+
+class DenseFFN:
+    def __init__(self, cfg: ModelConfig, layer: int, src, par: ParallelCtx, prefix: Optional[str] = None, act: int = ACT_SWIGLU,
+                 ffn: Optional[int] = None, suffix: str = ""):
+        p = prefix or f"blk.{layer}"
+        H, F = cfg.hidden, ffn or cfg.ffn
+        tp = par.world if par.mode == "tp" else 1
+        if cfg.arch == "phi3" and not src.has(f"{p}.ffn_gate{suffix}.weight"):
+            up2 = src.matrix(f"{p}.ffn_up{suffix}.weight", 2 * F, H)            # fused gate|up rows
+            g, u = up2.slice_rows(0, F), up2.slice_rows(F, 2 * F)
+        else:
+            g = src.matrix(f"{p}.ffn_gate{suffix}.weight", F, H)
+            u = src.matrix(f"{p}.ffn_up{suffix}.weight", F, H)
+        d = src.matrix(f"{p}.ffn_down{suffix}.weight", H, F)
+        if tp > 1:
+            gran = max(d.k_granule(), 16)
+            lo, hi = _even_chunks(F, tp, gran)[par.rank]
+            g, u, d = g.slice_rows(lo, hi), u.slice_rows(lo, hi), d.slice_k(lo, hi)
+        if g.fmt == u.fmt:
+            self.gate_up = Linear(QuantWeight.interleave_gate_up(g, u), act=act)
+            self.split = None
+        else:
+            self.gate_up = None
+            self.split = (Linear(g), Linear(u))
+            self.act = act
+        self.down = Linear(d, reduce=tp > 1)
+
+    def __call__(self, h, par):
+        if self.gate_up is not None:
+            a = self.gate_up(h)
+        else:
+            g, u = self.split[0](h), self.split[1](h)
+            F = g.shape[1]
+            il = torch.cat([g.reshape(-1, F // 16, 16), u.reshape(-1, F // 16, 16)], dim=2).reshape(-1, 2 * F)
+            a = ops.glu(il.contiguous(), self.act)
+        return self.down(a, par)
+
+
+def _even_chunks(n: int, parts: int, gran: int) -> list[tuple[int, int]]:
+    """Split n (a multiple of gran) into `parts` contiguous ranges on gran boundaries, sizes differing by <= gran."""
+    blocks = n // gran
+    base, extra = divmod(blocks, parts)
+    out, lo = [], 0
+    for r in range(parts):
+        sz = (base + (1 if r < extra else 0)) * gran
+        out.append((lo, lo + sz))
+        lo += sz
+    return out
+
+
+class MoEFFN:
+    """Router -> top-k -> experts -> weighted combine, expert-parallel over the ranks of ``par``.
+
+    Every rank sees every token (activations are replicated under tensor parallelism), packs only
+    the pairs routed to its own experts and contributes a partial sum that the caller reduces.
+    """
+
+    def __init__(self, cfg: ModelConfig, layer: int, src, par: ParallelCtx, act: int, with_bias: bool, prefix: Optional[str] = None):
+        c = cfg
+        p = prefix or f"blk.{layer}"
+        H, F, E = c.hidden, c.expert_ffn, c.n_experts
+        ep = par.world if par.mode == "tp" else 1
+        if E % ep:
+            raise ValueError(f"{E} experts do not split over {ep} ranks")
+        self.E, self.K = E, c.n_experts_used
+        self.e_lo, self.e_hi = (par.rank * (E // ep), (par.rank + 1) * (E // ep)) if ep > 1 else (0, E)
+        rng = (self.e_lo, self.e_hi)
+        rw = src.matrix(f"{p}.ffn_gate_inp.weight", E, H)
+        self.router = Linear(rw if rw.fmt == ops.WFormat.BF16 else QuantWeight(**_as_bf16(rw)))
+        self.router_bias = src.vector(f"{p}.ffn_gate_inp.bias", E) if with_bias else None
+        g = src.matrix(f"{p}.ffn_gate_exps.weight", F, H, E, experts=rng)
+        u = src.matrix(f"{p}.ffn_up_exps.weight", F, H, E, experts=rng)
+        self.gate_up = QuantWeight.interleave_gate_up(g, u)
+        del g, u
+        self.down = src.matrix(f"{p}.ffn_down_exps.weight", H, F, E, experts=rng)
+        self.gu_bias = self.down_bias = None
+        if with_bias:
+            gb = src.table(f"{p}.ffn_gate_exps.bias", (E, F))[self.e_lo:self.e_hi]
+            ub = src.table(f"{p}.ffn_up_exps.bias", (E, F))[self.e_lo:self.e_hi]
+            n = self.e_hi - self.e_lo
+            self.gu_bias = torch.cat([gb.reshape(n, F // 16, 16), ub.reshape(n, F // 16, 16)], dim=2).reshape(n, 2 * F).contiguous()
+            self.down_bias = src.table(f"{p}.ffn_down_exps.bias", (E, H))[self.e_lo:self.e_hi].contiguous()
+        self.act = act
+        self.reduce = ep > 1
+        self._arange = {}
+
+    def __call__(self, h: torch.Tensor, par: ParallelCtx) -> torch.Tensor:
+        """Returns this rank's fp32 contribution [T, H] (already reduced when EP > 1)."""
+        T = h.shape[0]
+        logits = self.router(h, out_f32=True)
+        idx, w = ops.moe_route(logits, self.router_bias, self.K, True)
+        local = self.e_hi - self.e_lo
+        if T <= 8 and local == self.E:
+            # decode: one GEMV slot per (token, expert) pair, weights streamed once per pair
+            slot_e = idx.reshape(-1)
+            a = ops.expert_gemv(h, self.gate_up, slot_e, x_div=self.K, bias=self.gu_bias, act=self.act)
+            y = ops.expert_gemv(a, self.down, slot_e, x_div=1, bias=self.down_bias)
+            key = (T, h.device)
+            if key not in self._arange:
+                pk = ops.ref.MoePacking(None, None, torch.zeros(1, dtype=torch.int32, device=h.device),
+                                        torch.arange(T * self.K, dtype=torch.int32, device=h.device), None, None, T * self.K, self.K)
+                self._arange[key] = pk
+            out = ops.moe_combine(y, self._arange[key], w)
+        else:
+            pk = ops.moe_pack(idx, self.E, self.e_lo, self.e_hi)
+            xp = ops.moe_gather(h, pk)
+            te = pk.tile_expert - self.e_lo if self.e_lo else pk.tile_expert
+            a = ops.grouped_linear(xp, self.gate_up, te, pk.num_tiles, bias=self.gu_bias, act=self.act)
+            y = ops.grouped_linear(a, self.down, te, pk.num_tiles, bias=self.down_bias)
+            out = ops.moe_combine(y, pk, w)
+        if self.reduce:
+            out = par.all_reduce(out)
+        return out
+
+
+def _as_bf16(w: QuantWeight) -> dict:
+    d = w.dequantize(torch.bfloat16)
+    return dict(fmt=ops.WFormat.BF16, N=w.N, K=w.K, E=w.E, p0=d.contiguous())
+
+
+# ---------------------------------------------------------------------------------------------
+class TransformerModel:
+    def __init__(self, cfg: ModelConfig, src, device, par: Optional[ParallelCtx] = None, max_ctx: int = 8192):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.par = par or ParallelCtx()
+        c, par = cfg, self.par
+        self.max_ctx = max_ctx
+        tp = par.world if par.mode == "tp" else 1
+        self.embed_w = src.matrix("token_embd.weight", c.vocab, c.hidden)
+        self.tied = not src.has("output.weight") or c.tie_embeddings
+        head = self.embed_w if self.tied else src.matrix("output.weight", c.vocab, c.hidden)
+        self.vocab_lo, self.vocab_hi = 0, c.vocab
+        if tp > 1:
+            lo, hi = _even_chunks(c.vocab, tp, 16)[par.rank] if c.vocab % (16 * tp) == 0 else (0, c.vocab)
+            if (lo, hi) != (0, c.vocab):
+                head = head.slice_rows(lo, hi)
+                self.vocab_lo, self.vocab_hi = lo, hi
+        self.lm_head = Linear(head)
+        self.out_norm = src.vector("output_norm.weight", c.hidden)
+        ff = src.vector("rope_freqs.weight", c.n_rot // 2) if (c.arch == "llama" and getattr(src, "r", None) is not None and src.has("rope_freqs.weight")) else None
+        self.rope = rope_tables(max_ctx, c.n_rot, c.rope_theta, ff, c.rope_scaling_type, c.rope_scaling_factor, c.rope_orig_ctx,
+                                c.yarn_beta_fast, c.yarn_beta_slow, device=self.device)
+        self.one_plus_w = c.arch in ("qwen3next", "qwen35", "qwen35moe")
+        self.layers = []
+        for l in range(c.n_layers):
+            self.layers.append(self._build_layer(l, src))
+        self.attn_layers = [l for l in range(c.n_layers) if c.layer_is_full_attention(l)]
+        self.n_kv_local = self.layers[self.attn_layers[0]]["attn"].n_kv if self.attn_layers else 0
+
+    # ---- construction
+    def _build_layer(self, l: int, src) -> dict:
+        c, par = self.cfg, self.par
+        p = f"blk.{l}"
+        L = {"attn_norm": src.vector(f"{p}.attn_norm.weight", c.hidden)}
+        L["attn"] = AttentionBlock(c, l, src, par)
+        post = f"{p}.post_attention_norm.weight" if c.arch in ("gpt-oss",) else f"{p}.ffn_norm.weight"
+        L["ffn_norm"] = src.vector(post, c.hidden)
+        if c.arch == "gpt-oss":
+            L["moe"] = MoEFFN(c, l, src, par, ACT_SWIGLU_OAI, with_bias=True)
+        elif c.arch == "qwen3moe":
+            L["moe"] = MoEFFN(c, l, src, par, ACT_SWIGLU, with_bias=False)
+        else:
+            L["ffn"] = DenseFFN(c, l, src, par)
+        return L
+
+    def new_kv_cache(self, num_blocks: int) -> KVCache:
+        return KVCache(self.cfg.n_layers, num_blocks, self.n_kv_local, self.cfg.head_dim, self.device, self.attn_layers)
+
+    def weight_bytes(self) -> int:
+        n = self.embed_w.nbytes + (0 if self.tied else self.lm_head.w.nbytes)
+        for L in self.layers:
+            for v in L.values():
+                n += _bytes_of(v)
+        return n
+
+    # ---- forward
+    def forward(self, fb: ForwardBatch, kv: KVCache, state=None) -> torch.Tensor:
+        """Returns fp32 logits [rows, vocab] for ``fb.logit_rows`` (default: last token of each sequence)."""
+        c, par = self.cfg, self.par
+        x = ops.embed(self.embed_w, fb.ids, c.embedding_scale)
+        delta = None
+        rs = c.residual_scale
+        for li, L in enumerate(self.layers):
+            h = ops.rmsnorm(x, L["attn_norm"], c.rms_eps, delta=delta, one_plus_w=self.one_plus_w, delta_scale=rs)
+            a = self._mixer(li, L, h, fb, kv, state)
+            h2 = ops.rmsnorm(x, L["ffn_norm"], c.rms_eps, delta=a, one_plus_w=self.one_plus_w, delta_scale=rs)
+            delta = L["moe"](h2, par) if "moe" in L else L["ffn"](h2, par)
+            if "shexp" in L:
+                delta = L["shexp"](h2, delta, par)
+        rows = fb.logit_rows if fb.logit_rows is not None else (fb.cu_q[1:].long() - 1)
+        xr = x.index_select(0, rows)
+        dr = delta.index_select(0, rows).contiguous()
+        hidden = None
+        if fb.want_hidden:
+            hidden = xr + dr.to(torch.float32) * rs
+        hn = ops.rmsnorm(xr, self.out_norm, c.rms_eps, delta=dr, one_plus_w=self.one_plus_w, delta_scale=rs)
+        logits = self.lm_head(hn, out_f32=True)
+        if self.vocab_hi - self.vocab_lo != c.vocab:
+            logits = par.all_gather_cols(logits)
+        if c.logit_scale != 1.0:
+            logits = logits * c.logit_scale
+        if c.final_logit_softcap > 0:
+            logits = torch.tanh(logits / c.final_logit_softcap) * c.final_logit_softcap
+        return (logits, hidden) if fb.want_hidden else logits
+
+    def _mixer(self, li, L, h, fb, kv, state):
+        return L["attn"](h, fb, kv, self.rope, self.par)
+
+
+def _bytes_of(v) -> int:
+    if isinstance(v, torch.Tensor):
+        return v.numel() * v.element_size()
+    if isinstance(v, QuantWeight):
+        return v.nbytes
+    if isinstance(v, Linear):
+        return v.w.nbytes + (_bytes_of(v.bias) if v.bias is not None else 0)
+    if isinstance(v, MultiLinear):
+        return sum(_bytes_of(p) for p in v.parts)
+    if isinstance(v, (list, tuple)):
+        return sum(_bytes_of(i) for i in v)
+    if hasattr(v, "__dict__"):
+        return sum(_bytes_of(i) for i in vars(v).values() if isinstance(i, (torch.Tensor, QuantWeight, Linear, MultiLinear, tuple, list)))
+    return 0

@@ -11,6 +11,7 @@ import functools
 from . import ref
 from .ref import ACT_GEGLU, ACT_NONE, ACT_SWIGLU, ACT_SWIGLU_OAI, MOE_TILE, MoePacking, moe_max_rows
 from .weights import QuantWeight, WFormat, from_dense, from_ggml
+from ..utils.profiler import profiler as _prof
 
 _NAMES = [
     "embed", "rmsnorm", "glu", "sigmoid_mul", "scaled_add", "gated_rmsnorm", "qkv_post", "linear", "grouped_linear", "expert_gemv",
@@ -37,7 +38,13 @@ def _make(name):
     def op(*args, **kwargs):
         if _first_tensor(args, kwargs).is_cuda:
             from . import cuda
-            return getattr(cuda, name)(*args, **kwargs)
+            fn = getattr(cuda, name)
+            if _prof.enabled:
+                tag = name
+                if name == "linear":
+                    tag = "gemv" if args[0].shape[0] <= cuda.GEMV_MAX_M else "gemm"
+                return _prof.record(tag, fn, args, kwargs)
+            return fn(*args, **kwargs)
         return ref_fn(*args, **kwargs)
 
     return op

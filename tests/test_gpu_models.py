@@ -1,0 +1,55 @@
+"""End-to-end GPU checks: the kernel path against the CPU oracle on the same random-init model."""
+import pytest
+import torch
+
+from machx_inference_engine_b200.formats.model_config import preset
+from machx_inference_engine_b200.models import build_model
+from machx_inference_engine_b200.runtime.engine import EngineOptions, LLMEngine, SamplingParams
+
+pytestmark = pytest.mark.gpu
+
+
+def _cos(a, b):
+    a, b = a.float().flatten(), b.float().flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-12))
+
+
+@pytest.mark.parametrize("name,quant", [("tiny-llama", "q8_0"), ("tiny-llama", "q4_k_m"), ("tiny-gpt-oss", "mxfp4"), ("tiny-qwen3moe", "q4_k_m"),
+                                        ("tiny-qwen3", "bf16")])
+def test_greedy_tokens_match_cpu_oracle(name, quant):
+    cfg = preset(name)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (37, 260, 9)]
+    outs = {}
+    logits = {}
+    for dev in ("cpu", "cuda:0"):
+        model = build_model(cfg, torch.device(dev), quant=quant, max_ctx=1024)
+        eng = LLMEngine(model, EngineOptions(max_ctx=1024, max_batch_tokens=512, max_seqs=4, cuda_graphs=True))
+        outs[dev] = eng.generate(prompts, SamplingParams(max_tokens=12))
+    # the reference's TP test asks for cosine >= 0.999, same argmax, greedy tokens identical (tools/multi_gpu_tp_test.cpp);
+    # against an fp32 oracle near-ties can flip late tokens, so require the first tokens to agree and most of the rest
+    same = sum(int(a == b) for x, y in zip(outs["cpu"], outs["cuda:0"]) for a, b in zip(x, y))
+    total = sum(len(x) for x in outs["cpu"])
+    assert all(x[0] == y[0] for x, y in zip(outs["cpu"], outs["cuda:0"])), outs
+    assert same >= 0.8 * total, outs
+
+
+def test_logits_cosine_prefill_and_graph_decode():
+    from machx_inference_engine_b200.models.transformer import KV_BLOCK, ForwardBatch
+    cfg = preset("tiny-gpt-oss")
+    ids = torch.randint(0, cfg.vocab, (200,), generator=torch.Generator().manual_seed(1)).tolist()
+    res = {}
+    for dev in ("cpu", "cuda:0"):
+        d = torch.device(dev)
+        m = build_model(cfg, d, quant="mxfp4", max_ctx=512)
+        kv = m.new_kv_cache(6)
+        T = len(ids)
+        pos = torch.arange(T, dtype=torch.int32, device=d)
+        bt = torch.arange(1, 5, dtype=torch.int32, device=d).unsqueeze(0)
+        slot = bt[0][(pos // KV_BLOCK).long()].long() * KV_BLOCK + (pos % KV_BLOCK).long()
+        fb = ForwardBatch(torch.tensor(ids, dtype=torch.int32, device=d), pos, slot, bt, torch.tensor([T], dtype=torch.int32, device=d),
+                          torch.tensor([0, T], dtype=torch.int32, device=d), T, logit_rows=torch.arange(T, device=d))
+        res[dev] = m.forward(fb, kv).float().cpu()
+    assert _cos(res["cpu"], res["cuda:0"]) > 0.999
+    agree = (res["cpu"].argmax(-1) == res["cuda:0"].argmax(-1)).float().mean()
+    assert agree > 0.95
