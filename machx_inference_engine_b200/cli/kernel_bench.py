@@ -1,0 +1,169 @@
+"""Micro-benchmarks of single kernels on model-shaped problems (CUDA events, L2-sized inputs), and the
+small cases that the committed ``ncu`` summaries under ``profiles/`` were captured on.
+
+    python -m machx_inference_engine_b200.cli.kernel_bench moe_gemm --experts 128 --tokens 2048 --topk 4 --hidden 2880 --ffn 2880
+    python -m machx_inference_engine_b200.cli.kernel_bench gemm --m 2048 --n 5120 --k 2880 --fmt bf16
+    python -m machx_inference_engine_b200.cli.kernel_bench gemv --n 201088 --k 2880 --fmt q8
+    python -m machx_inference_engine_b200.cli.kernel_bench attention --tokens 2048 --heads 64 --kv-heads 8 --head-dim 64
+
+Each prints achieved TFLOP/s or GB/s and the fraction of the measured peak (MEASURED_PEAKS.json when
+present, otherwise the stated fallback).  Reference parity: bench/bench_{gemm_fp16,gemv_q4k,dequant,attention}.cpp.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def peaks() -> dict:
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "src": "fallback"}
+
+
+def timeit(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def report(name, ms_med, ms_min, flops=None, bytes_=None, extra=None):
+    pk = peaks()
+    out = {"kernel": name, "ms_median": round(ms_med, 4), "ms_min": round(ms_min, 4)}
+    if flops:
+        out["tflops"] = round(flops / ms_med / 1e9, 1)
+        out[f"frac_of_{pk['src']}_bf16_burst"] = round(flops / ms_med / 1e9 / pk["bf16_tflops"], 3)
+    if bytes_:
+        out["gbs"] = round(bytes_ / ms_med / 1e6, 1)
+        out[f"frac_of_{pk['src']}_hbm"] = round(bytes_ / ms_med / 1e6 / pk["hbm_gbs"], 3)
+    if extra:
+        out.update(extra)
+    print(json.dumps(out))
+
+
+def main(argv=None):
+    from ..ops import cuda as K
+    from ..ops import ref
+    from ..ops.weights import WFormat, from_dense
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "moe_gemm", "gemv", "expert_gemv", "attention", "rmsnorm"])
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--n", type=int, default=5120)
+    ap.add_argument("--k", type=int, default=2880)
+    ap.add_argument("--fmt", default="bf16")
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--topk", type=int, default=4)
+    ap.add_argument("--hidden", type=int, default=2880)
+    ap.add_argument("--ffn", type=int, default=2880)
+    ap.add_argument("--heads", type=int, default=64)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=0)
+    ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--layers", type=int, default=1, help="distinct weight copies cycled through so that weights are never L2-resident")
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda:0")
+    fmt = {"bf16": WFormat.BF16, "q8": WFormat.Q8, "q4k": WFormat.Q4K, "q6k": WFormat.Q6K, "mxfp4": WFormat.MXFP4}[a.fmt]
+    torch.manual_seed(0)
+
+    def weight(N, Kd, E=1):
+        parts = [from_dense(torch.randn(1, N, Kd, device=dev) * 0.02, fmt) for _ in range(E)]
+        if E == 1:
+            return parts[0]
+        from ..ops.weights import QuantWeight
+        planes = [None if parts[0].planes()[i] is None else torch.cat([p.planes()[i] for p in parts], 0).contiguous() for i in range(4)]
+        return QuantWeight(fmt, N, Kd, E, *planes)
+
+    if a.kernel == "gemm":
+        ws = [weight(a.n, a.k) for _ in range(a.layers)]
+        x = (torch.randn(a.m, a.k, device=dev) * 0.5).to(torch.float16 if fmt == WFormat.MXFP4 else torch.bfloat16)
+        i = [0]
+
+        def fn():
+            K.gemm(x, ws[i[0] % a.layers], bn=a.bn or None)
+            i[0] += 1
+        med, mn = timeit(fn, a.iters)
+        report(f"gemm[{a.fmt}] {a.m}x{a.n}x{a.k}", med, mn, flops=2.0 * a.m * a.n * a.k, bytes_=ws[0].nbytes + x.numel() * 2 + a.m * a.n * 2)
+    elif a.kernel == "moe_gemm":
+        T, E, H, F, k = a.tokens, a.experts, a.hidden, a.ffn, a.topk
+        gu = weight(2 * F, H, E)
+        dn = weight(H, F, E)
+        x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+        idx, w = K.moe_route(torch.randn(T, E, device=dev), None, k)
+        pk = K.moe_pack(idx, E)
+        f16 = fmt == WFormat.MXFP4
+        mid = torch.float16 if f16 else torch.bfloat16
+        xp = K.moe_gather(x, pk, f16=f16)
+        hmid = K.grouped_linear(xp, gu, pk.tile_expert, pk.num_tiles, act=ref.ACT_SWIGLU_OAI, out_dtype=mid)
+        med, mn = timeit(lambda: K.grouped_linear(xp, gu, pk.tile_expert, pk.num_tiles, act=ref.ACT_SWIGLU_OAI, out_dtype=mid), a.iters)
+        tiles = int(pk.num_tiles[0])
+        report(f"moe gate_up[{a.fmt}] T={T} E={E} top{k} {2 * F}x{H}", med, mn, flops=2.0 * T * k * 2 * F * H, bytes_=gu.nbytes,
+               extra={"m_tiles": tiles, "padded_rows": int(pk.num_tiles[1])})
+        med, mn = timeit(lambda: K.grouped_linear(hmid, dn, pk.tile_expert, pk.num_tiles), a.iters)
+        report(f"moe down[{a.fmt}] T={T} E={E} top{k} {H}x{F}", med, mn, flops=2.0 * T * k * F * H, bytes_=dn.nbytes)
+    elif a.kernel == "gemv":
+        ws = [weight(a.n, a.k) for _ in range(max(a.layers, 2))]
+        x = torch.randn(1, a.k, device=dev).to(torch.bfloat16)
+        i = [0]
+
+        def fn():
+            K.linear(x, ws[i[0] % len(ws)])
+            i[0] += 1
+        med, mn = timeit(fn, a.iters)
+        report(f"gemv[{a.fmt}] {a.n}x{a.k}", med, mn, bytes_=ws[0].nbytes)
+    elif a.kernel == "expert_gemv":
+        E, H, F, k = a.experts, a.hidden, a.ffn, a.topk
+        gu = weight(2 * F, H, E)
+        x = torch.randn(1, H, device=dev).to(torch.bfloat16)
+        se = torch.randperm(E, device=dev)[:k].to(torch.int32)
+        med, mn = timeit(lambda: K.expert_gemv(x, gu, se, x_div=k, act=ref.ACT_SWIGLU_OAI), a.iters)
+        report(f"expert_gemv gate_up[{a.fmt}] top{k} {2 * F}x{H}", med, mn, bytes_=gu.nbytes // E * k)
+    elif a.kernel == "attention":
+        T, nq, nkv, hd = a.tokens, a.heads, a.kv_heads, a.head_dim
+        ctx = a.ctx or T
+        nblk = (ctx + 127) // 128
+        kc = torch.randn(nblk + 1, nkv, 128, hd, device=dev).to(torch.bfloat16)
+        vc = torch.randn(nblk + 1, nkv, 128, hd, device=dev).to(torch.bfloat16)
+        bt = torch.arange(1, nblk + 1, dtype=torch.int32, device=dev).unsqueeze(0)
+        q = torch.randn(T, nq, hd, device=dev).to(torch.bfloat16)
+        sl = torch.tensor([ctx], dtype=torch.int32, device=dev)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        sinks = torch.zeros(nq, device=dev)
+        med, mn = timeit(lambda: K.attention(q, kc, vc, bt, sl, cu, T, sinks=sinks, window=a.window), a.iters)
+        # causal: each query attends to (ctx - T + its index + 1) keys; window clips that
+        keys = sum(min(ctx - T + i + 1, a.window or 10 ** 9) for i in range(T))
+        report(f"attention T={T} ctx={ctx} nq={nq} nkv={nkv} hd={hd} window={a.window}", med, mn, flops=4.0 * keys * nq * hd,
+               bytes_=2 * ctx * nkv * hd * 2 + 2 * T * nq * hd * 2)
+    elif a.kernel == "rmsnorm":
+        x = torch.randn(a.m, a.k, device=dev)
+        d = torch.randn(a.m, a.k, device=dev).to(torch.bfloat16)
+        w = torch.ones(a.k, device=dev)
+        med, mn = timeit(lambda: K.rmsnorm(x, w, 1e-5, delta=d), a.iters)
+        report(f"rmsnorm {a.m}x{a.k}", med, mn, bytes_=a.m * a.k * (4 + 4 + 2 + 2))
+    K.check_status()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

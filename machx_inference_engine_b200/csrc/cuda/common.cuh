@@ -33,7 +33,7 @@ enum WFormat : int {
   WF_Q8 = 1,     // int8 q[N][K] + fp16 d[N][K/32]
   WF_Q4K = 2,    // native ggml Q4_K blocks, [N][K/256] x 144 B
   WF_Q6K = 3,    // planes: lo4[N][K/2], hi2[N][K/4], int8 sc[N][K/16], fp16 d[N][K/256]
-  WF_MXFP4 = 4,  // planes: nib[N][K/2] (pair-interleaved nibbles), e8m0 e[N][K/32]
+  WF_MXFP4 = 4,  // planes: nib[N][K/2] (natural nibble order), e8m0 e[N][row stride padded to 16 B]
 };
 
 struct WeightRef {   // passed by value to kernels; unused planes are null
@@ -79,16 +79,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: about one second of SM clock, then the status word is set and false returned.
 // `abort_flag` (shared memory) lets the other roles of the CTA leave early once one role failed.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code, volatile int* abort_flag) {
+// `sleep_ns` > 0 backs off between polls so that waiting warps do not eat the issue slots of the
+// warps doing the work (roles that wait for a whole main loop pass a larger value).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code, volatile int* abort_flag,
+                                          uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  for (;;) {
+  for (uint32_t spins = 0;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > 2000000000ll) {
-      *abort_flag = 1;
-      atomicCAS(status, 0, code);
-      return false;
+    if (sleep_ns) __nanosleep(sleep_ns);
+    if ((spins & 15) == 15) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 2000000000ll) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
     }
   }
 }
@@ -171,6 +177,14 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// same with fp16 x fp16 operands (format code 0)
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  __half2 p = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
 }
 
 // 32 lanes x 32 columns of 32-bit: thread `lane` receives row (lane), columns c..c+31.

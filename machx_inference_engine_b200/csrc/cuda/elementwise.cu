@@ -233,9 +233,32 @@ __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const float* __restr
   }
 }
 
+// Decoder probe: every 32-bit word of `in` (eight E2M1 codes) is decoded twice, with the byte-permute
+// table path (bf16) and with the hardware conversion path (fp16); out[w][0..7] and out[w][8..15].
+__global__ void e2m1_probe_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t a[4], b[4];
+  e2m1x8_to_bf16x2(in[i], a);
+  e2m1x8_to_f16x2(in[i], b);
+  for (int j = 0; j < 4; ++j) {
+    out[(size_t)i * 16 + 2 * j] = bf16_lo(a[j]);
+    out[(size_t)i * 16 + 2 * j + 1] = bf16_hi(a[j]);
+    const __half2 h = *reinterpret_cast<const __half2*>(&b[j]);
+    out[(size_t)i * 16 + 8 + 2 * j] = __low2float(h);
+    out[(size_t)i * 16 + 8 + 2 * j + 1] = __high2float(h);
+  }
+}
+
 }  // namespace mx
 
 using namespace mx;
+
+MX_HOST_API int mx_e2m1_probe(const void* in, float* out, int n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  e2m1_probe_kernel<<<(n + 127) / 128, 128, 0, st>>>((const uint32_t*)in, out, n);
+  return (int)cudaGetLastError();
+}
 
 MX_HOST_API int mx_embed(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const int* ids, float* out, int T,
                          int H, int vocab, float scale, cudaStream_t st) {

@@ -35,24 +35,50 @@ struct GemmParams {
   const int* num_m_tiles_dev;   // grouped: live m-tile count (device), else null
   const int* tile_expert;       // grouped: expert id per m-tile, else null
   WeightRef w;
-  void* C;                      // bf16 or fp32, leading dimension ldc (elements)
+  void* C;                      // leading dimension ldc (elements)
   int ldc;
-  int out_f32;
+  int out_f32;                  // output kind: 0 bf16, 1 fp32, 2 fp16
   const float* bias;            // [N] or [E][N], nullable
   const float* row_scale;       // [M], nullable
   int act;
   float act_alpha, act_limit;
+  int group_m;                  // tile rasterisation group (see tile_coords)
   int* status;
 };
 
-template <int BN, int STAGES>
+constexpr int kRawDepth = 10;   // k-iterations of packed weight bytes kept in flight per producer thread
+
+// Shared-memory plan.  TMA-fed weights: one ring of SA stages holding an A tile and a B tile each.
+// Decoded weights: the A ring (SA deep, TMA) is decoupled from a short B ring (SB deep, written by
+// the decode warps) because their latencies differ; in front of the B ring sits the packed-byte
+// ring (kRawDepth deep) that hides HBM latency for the weights.
+template <int FMT, int BN, int SA, int SB>
 struct SmemLayout {
+  static constexpr bool kDequant = FMT != WF_BF16;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // + barriers + alignment slack
+  static constexpr int A_OFFSET = 0;
+  static constexpr int B_OFFSET = SA * A_BYTES;
+  static constexpr int NB = kDequant ? SB : SA;
+  static constexpr int BAR_OFFSET = B_OFFSET + NB * B_BYTES;
+  static constexpr int RAW_THREADS = 2 * BN;
+  static constexpr int RAW_STAGE = kDequant ? RAW_THREADS * RawSlot<FMT>::BYTES : 0;
+  static constexpr int RAW_OFFSET = BAR_OFFSET + 512;
+  static constexpr int TOTAL = RAW_OFFSET + kRawDepth * RAW_STAGE + 1024;   // + alignment slack
+  static_assert(TOTAL <= 232448, "shared memory plan exceeds 227 KB");
 };
+
+// Tile order.  Tiles are walked in groups of `group_m` m-tiles: inside a group the m index runs
+// fastest, then n.  group_m = 1 (grouped / MoE problems) keeps one m-tile's activations hot in L2
+// while its n-tiles stream the expert's weights exactly once; dense problems use a group of 8 so a
+// wave of CTAs shares both a band of A and a band of W.
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mt, int& nt) {
+  const int per_group = group_m * n_tiles;
+  const int g = t / per_group, r = t - g * per_group;
+  const int gm = min(group_m, m_tiles - g * group_m);
+  mt = g * group_m + r % gm;
+  nt = r / gm;
+}
 
 __device__ __forceinline__ float act_apply(int act, float g, float u, float alpha, float limit) {
   if (act == ACT_SWIGLU) return g / (1.f + __expf(-g)) * u;
@@ -66,29 +92,35 @@ __device__ __forceinline__ float act_apply(int act, float g, float u, float alph
   return 0.5f * g * (1.f + t) * u;
 }
 
-template <int FMT, int BN, int STAGES>
+template <int FMT, int BN, int SA, int SB>
 __global__ void __launch_bounds__(FMT == WF_BF16 ? 192 : 448, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<FMT, BN, SA, SB>;
   constexpr bool kDequant = FMT != WF_BF16;
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);   // power of two for BN in {32,64,128,256}
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
-  // barrier slots: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
-  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
-  const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  // barrier slots: full_a[SA], empty_a[SA], full_b[SB], empty_b[SB], tmem_full[2], tmem_empty[2]
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * SA;
+  const uint32_t bar_bfull = bar_empty + 8 * SA, bar_bempty = bar_bfull + 8 * SB;
+  const uint32_t bar_tfull = bar_bempty + 8 * SB, bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SA + 2 * SB + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert((2 * SA + 2 * SB + 4) * 8 + 8 <= 512, "barrier block too small");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, kDequant ? 1 + kNumDequantWarps * 32 : 1);
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < SB; ++s) {
+      mbar_init(bar_bfull + 8 * s, kNumDequantWarps * 32);
+      mbar_init(bar_bempty + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
@@ -111,29 +143,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int k_iters = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
-    // ------------------------------------------------ TMA producer
+    // ------------------------------------------------ TMA producer (A always, B when it is bf16)
     if (lane == 0) {
       prefetch_tmap(&tmap_a);
       if (!kDequant) prefetch_tmap(&tmap_b);
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int mt = t % m_tiles, nt = t / m_tiles;
+        int mt, nt;
+        tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
         const int e = p.tile_expert ? p.tile_expert[mt] : 0;
         for (int k = 0; k < k_iters; ++k, ++it) {
-          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          const uint32_t s = it % SA, ph = (it / SA) & 1;
           if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, p.status, ERR_MBAR_TIMEOUT_PRODUCER, abort_flag))) break;
-          const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
-          mbar_expect_tx(bar_full + 8 * s, kDequant ? L::A_BYTES : L::STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, bar_full + 8 * s, k * BK, mt * BM);
-          if (!kDequant) tma_load_3d(a_dst + L::A_BYTES, &tmap_b, bar_full + 8 * s, k * BK, nt * BN, e);
+          mbar_expect_tx(bar_full + 8 * s, kDequant ? L::A_BYTES : L::A_BYTES + L::B_BYTES);
+          tma_load_2d(smem_base + L::A_OFFSET + s * L::A_BYTES, &tmap_a, bar_full + 8 * s, k * BK, mt * BM);
+          if (!kDequant) tma_load_3d(smem_base + L::B_OFFSET + s * L::B_BYTES, &tmap_b, bar_full + 8 * s, k * BK, nt * BN, e);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
+      // MXFP4 weights are decoded to fp16, so that format runs fp16 x fp16 (activations arrive as fp16)
+      constexpr uint32_t idesc = FMT == WF_MXFP4 ? umma_idesc_f16(BM, BN, 0, 0) : umma_idesc_bf16(BM, BN, 0, 0);
       uint32_t it = 0, tile_n = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_n) {
@@ -142,16 +175,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int k = 0; k < k_iters; ++k, ++it) {
-          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          const uint32_t s = it % SA, ph = (it / SA) & 1;
+          const uint32_t sb = kDequant ? it % SB : s, phb = (it / SB) & 1;
           if (!(ok = mbar_wait(bar_full + 8 * s, ph, p.status, ERR_MBAR_TIMEOUT_MMA, abort_flag))) break;
+          if (kDequant && !(ok = mbar_wait(bar_bfull + 8 * sb, phb, p.status, ERR_MBAR_TIMEOUT_MMA, abort_flag))) break;
           tc_fence_after();
-          const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
-          const uint64_t a_desc = umma_desc_k_sw128(a_addr);
-          const uint64_t b_desc = umma_desc_k_sw128(a_addr + L::A_BYTES);
+          const uint64_t a_desc = umma_desc_k_sw128(smem_base + L::A_OFFSET + s * L::A_BYTES);
+          const uint64_t b_desc = umma_desc_k_sw128(smem_base + L::B_OFFSET + sb * L::B_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes per UMMA K step: +2 in the (addr>>4) field
             umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (k | kk) != 0);
           umma_commit(bar_empty + 8 * s);
+          if (kDequant) umma_commit(bar_bempty + 8 * sb);
         }
         if (ok) umma_commit(bar_tfull + 8 * acc);
       }
@@ -162,10 +197,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     uint32_t tile_n = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_n) {
-      const int mt = t % m_tiles, nt = t / m_tiles;
+      int mt, nt;
+      tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
       const int e = p.tile_expert ? p.tile_expert[mt] : 0;
       const uint32_t acc = tile_n & 1, acc_ph = (tile_n >> 1) & 1;
-      if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag))) break;
+      if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag, 256))) break;
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -187,7 +223,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (p.act == ACT_NONE) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= rs;
-          if (p.out_f32) {
+          if (p.out_f32 == 1) {
             float* out = (float*)p.C + (size_t)row * p.ldc + col0;
             if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
 #pragma unroll
@@ -196,14 +232,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = v[j];
             }
           } else {
+            const bool h = p.out_f32 == 2;
             __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + col0;
             if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8)
-                *reinterpret_cast<uint4*>(out + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
-                                                                pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+                *reinterpret_cast<uint4*>(out + j) = h ? make_uint4(pack_f16(v[j], v[j + 1]), pack_f16(v[j + 2], v[j + 3]),
+                                                                    pack_f16(v[j + 4], v[j + 5]), pack_f16(v[j + 6], v[j + 7]))
+                                                       : make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                                    pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
             } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) out[j] = __float2bfloat16(v[j]);
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                if (h) ((__half*)out)[j] = __float2half(v[j]); else out[j] = __float2bfloat16(v[j]);
+              }
             }
           }
         } else {
@@ -213,18 +254,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) o[j] = act_apply(p.act, v[j], v[16 + j], p.act_alpha, p.act_limit) * rs;
           const int on = p.N >> 1;
-          if (p.out_f32) {
+          if (p.out_f32 == 1) {
             float* out = (float*)p.C + (size_t)row * p.ldc + ocol0;
             for (int j = 0; j < 16 && ocol0 + j < on; ++j) out[j] = o[j];
           } else {
+            const bool h = p.out_f32 == 2;
             __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + ocol0;
             if (ocol0 + 16 <= on && (p.ldc & 7) == 0) {
 #pragma unroll
               for (int j = 0; j < 16; j += 8)
-                *reinterpret_cast<uint4*>(out + j) = make_uint4(pack_bf16(o[j], o[j + 1]), pack_bf16(o[j + 2], o[j + 3]),
-                                                                pack_bf16(o[j + 4], o[j + 5]), pack_bf16(o[j + 6], o[j + 7]));
+                *reinterpret_cast<uint4*>(out + j) = h ? make_uint4(pack_f16(o[j], o[j + 1]), pack_f16(o[j + 2], o[j + 3]),
+                                                                    pack_f16(o[j + 4], o[j + 5]), pack_f16(o[j + 6], o[j + 7]))
+                                                       : make_uint4(pack_bf16(o[j], o[j + 1]), pack_bf16(o[j + 2], o[j + 3]),
+                                                                    pack_bf16(o[j + 4], o[j + 5]), pack_bf16(o[j + 6], o[j + 7]));
             } else {
-              for (int j = 0; j < 16 && ocol0 + j < on; ++j) out[j] = __float2bfloat16(o[j]);
+              for (int j = 0; j < 16 && ocol0 + j < on; ++j) {
+                if (h) ((__half*)out)[j] = __float2half(o[j]); else out[j] = __float2bfloat16(o[j]);
+              }
             }
           }
         }
@@ -234,43 +280,72 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (kDequant) {
     // ------------------------------------------------ weight decode producers (8 warps)
+    // Thread d owns (row d>>1, k-half d&1) of every B tile.  Its packed bytes travel global ->
+    // private shared slot with cp.async, kRawDepth k-iterations ahead (across tile boundaries), so
+    // HBM latency is covered by the copies in flight instead of stalling the decode.
     const int d = threadIdx.x - (2 + kNumEpilogueWarps) * 32;   // 0..255
-    uint32_t it = 0;
-    bool ok = true;
-    constexpr int ROWS_PER_PASS = kNumDequantWarps * 32 / 2;      // two threads per row (32 k-elements each)
-    const int half = d & 1;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int mt = t % m_tiles, nt = t / m_tiles;
-      const int e = p.tile_expert ? p.tile_expert[mt] : 0;
-      const WeightRef we = p.tile_expert ? expert_weight<FMT>(p.w, e, p.N, p.K) : p.w;
-      for (int k = 0; k < k_iters; ++k, ++it) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag))) break;
-        uint8_t* b_tile = smem + s * L::STAGE_BYTES + L::A_BYTES;
-        const int kb = k * 2 + half;                              // 32-element block index along K
-        const bool k_ok = kb * 32 < p.K;
+    const int half = d & 1, rl = d >> 1;
+    const bool live = rl < BN;
+    uint8_t* raw_base = smem + L::RAW_OFFSET + (live ? d : 0) * RawSlot<FMT>::BYTES;
+    const uint32_t raw_base_u32 = smem_u32(raw_base);
+    const int k_blocks = p.K / 32;                 // valid 32-element blocks along K
+    // prefetch cursor: tile pt, k-iteration pk, ring slot ps; row pointers are recomputed once per tile
+    int pt = blockIdx.x, pk = 0, ps = 0;
+    RowPtrs prp = {nullptr, nullptr, nullptr, nullptr};
+    bool prow_ok = false;
+    auto prefetch_tile_setup = [&]() {
+      prow_ok = false;
+      if (pt < total_tiles && live) {
+        int pmt, pnt;
+        tile_coords(pt, m_tiles, p.num_n_tiles, p.group_m, pmt, pnt);
+        const int n = pnt * BN + rl;
+        if (n < p.N) {
+          const int pe = p.tile_expert ? p.tile_expert[pmt] : 0;
+          prp = row_ptrs<FMT>(p.tile_expert ? expert_weight<FMT>(p.w, pe, p.N, p.K) : p.w, n, p.K);
+          prow_ok = true;
+        }
+      }
+    };
+    auto issue_next = [&]() {
+      if (prow_ok && 2 * pk + half < k_blocks) raw_issue<FMT>(raw_base_u32 + ps * L::RAW_STAGE, prp, pk, half);
+      cp_async_commit();
+      ps = (ps + 1 == kRawDepth) ? 0 : ps + 1;
+      if (++pk == k_iters) { pk = 0; pt += gridDim.x; prefetch_tile_setup(); }
+    };
+    prefetch_tile_setup();
 #pragma unroll 1
-        for (int r0 = 0; r0 < BN; r0 += ROWS_PER_PASS) {
-          const int rl = r0 + (d >> 1);
-          if (rl < BN) {
-            const int n = nt * BN + rl;
-            uint32_t o[16];
-            if (n < p.N && k_ok) {
-              const RowPtrs rp = row_ptrs<FMT>(we, n, p.K);
-              decode32_bf16<FMT>(rp, kb, o);
-            } else {
+    for (int i = 0; i < kRawDepth - 1; ++i) issue_next();
+    uint32_t sb = 0, phb = 0;
+    int cs = 0;                                    // consume slot in the raw ring
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
+      const bool row_ok = live && nt * BN + rl < p.N;
+      for (int k = 0; k < k_iters; ++k) {
+        issue_next();
+        cp_async_wait<kRawDepth - 1>();          // this iteration's bytes have landed in the slot
+        if (!(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag, 20))) break;
+        if (live) {
+          uint8_t* b_tile = smem + L::B_OFFSET + sb * L::B_BYTES;
+          uint32_t o[16];
+          if (row_ok && 2 * k + half < k_blocks) {
+            raw_decode<FMT>(raw_base + cs * L::RAW_STAGE, k, half, o);
+          } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) o[j] = 0u;
-            }
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-              *reinterpret_cast<uint4*>(b_tile + sw128_offset(rl, 4 * half + c)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+            for (int j = 0; j < 16; ++j) o[j] = 0u;
           }
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(b_tile + sw128_offset(rl, raw_chunk<FMT>(half, c))) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
         }
         fence_proxy_async();
-        mbar_arrive(bar_full + 8 * s);
+        mbar_arrive(bar_bfull + 8 * sb);
+        cs = (cs + 1 == kRawDepth) ? 0 : cs + 1;
+        if (++sb == SB) { sb = 0; phb ^= 1; }
       }
     }
+    cp_async_wait<0>();
   }
 
   // ---------------------------------------------------- teardown
@@ -284,10 +359,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------------------------
-template <int FMT, int BN, int STAGES>
+template <int FMT, int BN, int SA, int SB>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
-  using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_kernel<FMT, BN, STAGES>;
+  using L = SmemLayout<FMT, BN, SA, SB>;
+  auto kern = gemm_kernel<FMT, BN, SA, SB>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -301,14 +376,16 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   return (int)cudaGetLastError();
 }
 
-template <int BN, int STAGES>
+// SA: depth of the TMA ring (A, plus B when the weights are bf16).  QA/QB: depths of the A ring and
+// of the decoded-B ring for quantised weights.
+template <int BN, int SA, int QA, int QB>
 static int dispatch_fmt(int fmt, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
   switch (fmt) {
-    case WF_BF16: return launch<WF_BF16, BN, STAGES>(ta, tb, p, st);
-    case WF_Q8: return launch<WF_Q8, BN, STAGES>(ta, tb, p, st);
-    case WF_Q4K: return launch<WF_Q4K, BN, STAGES>(ta, tb, p, st);
-    case WF_Q6K: return launch<WF_Q6K, BN, STAGES>(ta, tb, p, st);
-    case WF_MXFP4: return launch<WF_MXFP4, BN, STAGES>(ta, tb, p, st);
+    case WF_BF16: return launch<WF_BF16, BN, SA, 1>(ta, tb, p, st);
+    case WF_Q8: return launch<WF_Q8, BN, QA - 1, QB - 1>(ta, tb, p, st);
+    case WF_Q4K: return launch<WF_Q4K, BN, QA, QB>(ta, tb, p, st);
+    case WF_Q6K: return launch<WF_Q6K, BN, QA, QB>(ta, tb, p, st);
+    case WF_MXFP4: return launch<WF_MXFP4, BN, QA, QB>(ta, tb, p, st);
     default: return -100;
   }
 }
@@ -316,7 +393,9 @@ static int dispatch_fmt(int fmt, const CUtensorMap& ta, const CUtensorMap& tb, c
 }  // namespace mx
 
 // C[M, N(/2 with act)] = A[M,K] * W[(E,)N,K]^T.
-//   a          bf16 [M,K] row-major, 16-byte aligned, K % 8 == 0
+//   a          [M,K] row-major 16-bit activations, 16-byte aligned, K % 8 == 0: bf16, except fp16 when the
+//              weights are MXFP4 (that format is decoded to fp16 and multiplied in fp16 x fp16 mode)
+//   out_f32    output kind: 0 bf16, 1 fp32, 2 fp16
 //   wfmt/w0..w3  weight format and plane pointers (see WFormat); n_experts >= 1
 //   tile_expert / num_m_tiles_dev: grouped mode (both null for a plain GEMM)
 //   bn         32, 64 or 128 (tile width); the caller picks small tiles for small M
@@ -341,6 +420,7 @@ MX_HOST_API int mx_gemm(const void* a, int wfmt, const void* w0, const void* w1,
   p.C = c; p.ldc = ldc; p.out_f32 = out_f32;
   p.bias = bias; p.row_scale = row_scale;
   p.act = act; p.act_alpha = act_alpha; p.act_limit = act_limit;
+  p.group_m = tile_expert ? 1 : 8;
   p.status = status_word();
 
   CUtensorMap ta, tb;
@@ -361,9 +441,9 @@ MX_HOST_API int mx_gemm(const void* a, int wfmt, const void* w0, const void* w1,
     tb = ta;
   }
   switch (bn) {
-    case 128: return dispatch_fmt<128, 6>(wfmt, ta, tb, p, stream);
-    case 64: return dispatch_fmt<64, 8>(wfmt, ta, tb, p, stream);
-    case 32: return dispatch_fmt<32, 8>(wfmt, ta, tb, p, stream);
+    case 128: return dispatch_fmt<128, 6, 4, 4>(wfmt, ta, tb, p, stream);
+    case 64: return dispatch_fmt<64, 8, 6, 4>(wfmt, ta, tb, p, stream);
+    case 32: return dispatch_fmt<32, 8, 6, 4>(wfmt, ta, tb, p, stream);
     default: return -105;
   }
 }

@@ -118,8 +118,13 @@ __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ 
   }
 }
 
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+  __half2 h = __floats2half2_rn(bf16_lo(v), bf16_hi(v));
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// to_f16: convert the bf16 rows to fp16 while copying (MXFP4 expert GEMMs run in fp16 x fp16 mode)
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ packed_token, const int* __restrict__ total_rows,
-                                  __nv_bfloat16* __restrict__ xp, int H) {
+                                  __nv_bfloat16* __restrict__ xp, int H, int to_f16) {
   const int r = blockIdx.x;
   if (r >= total_rows[1]) return;
   const int t = packed_token[r];
@@ -128,7 +133,11 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
   } else {
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * H);
-    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+      uint4 v = src[i];
+      if (to_f16) { v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y); v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w); }
+      dst[i] = v;
+    }
   }
 }
 
@@ -177,10 +186,11 @@ MX_HOST_API int mx_moe_pack(const int* topk_idx, int n_pairs, int K, int E, int 
   return (int)cudaGetLastError();
 }
 
-MX_HOST_API int mx_moe_gather(const void* x, const int* packed_token, const int* num_tiles, void* xp, int H, int max_rows, cudaStream_t st) {
+MX_HOST_API int mx_moe_gather(const void* x, const int* packed_token, const int* num_tiles, void* xp, int H, int max_rows, int to_f16,
+                              cudaStream_t st) {
   if (max_rows <= 0) return 0;
   if (H % 8) return -101;
-  moe_gather_kernel<<<max_rows, 128, 0, st>>>((const __nv_bfloat16*)x, packed_token, num_tiles, (__nv_bfloat16*)xp, H);
+  moe_gather_kernel<<<max_rows, 128, 0, st>>>((const __nv_bfloat16*)x, packed_token, num_tiles, (__nv_bfloat16*)xp, H, to_f16);
   return (int)cudaGetLastError();
 }
 

@@ -15,10 +15,11 @@ def _graph_class(cfg: ModelConfig):
     return TransformerModel
 
 
-def build_model(cfg: ModelConfig, device, par: Optional[ParallelCtx] = None, quant: str = "q8_0", max_ctx: int = 8192, seed: int = 0):
+def build_model(cfg: ModelConfig, device, par: Optional[ParallelCtx] = None, quant: str = "q8_0", max_ctx: int = 8192, seed: int = 0,
+                gen_device=None):
     """Random-init weights of architecture ``cfg`` quantised with recipe ``quant`` directly on ``device``."""
     from .sources import SynthSource, default_policy
-    src = SynthSource(device, default_policy(cfg.arch, quant), seed=seed, n_layers=cfg.n_layers)
+    src = SynthSource(device, default_policy(cfg.arch, quant), seed=seed, n_layers=cfg.n_layers, gen_device=gen_device)
     return _graph_class(cfg)(cfg, src, device, par or ParallelCtx(), max_ctx=max_ctx)
 
 

@@ -99,8 +99,11 @@ class SynthSource:
     """Deterministic random weights.  Every tensor has its own seed derived from its name, so ranks
     that ask for different slices of the same tensor see consistent values."""
 
-    def __init__(self, device, policy: Callable[[str], WFormat], seed: int = 0, std: float = 0.02, n_layers: int = 32):
+    def __init__(self, device, policy: Callable[[str], WFormat], seed: int = 0, std: float = 0.02, n_layers: int = 32, gen_device=None):
         self.device = torch.device(device)
+        # random streams differ between CPU and CUDA generators: draw on ``gen_device`` (default: the
+        # target device) and move, so a CPU oracle and a GPU model can share identical weights
+        self.gen_device = torch.device(gen_device) if gen_device is not None else self.device
         self.policy = policy
         self.seed = seed
         self.std = std
@@ -113,7 +116,7 @@ class SynthSource:
         h = 1469598103934665603
         for ch in (name + f"#{extra}").encode():
             h = ((h ^ ch) * 1099511628211) & ((1 << 63) - 1)
-        g = torch.Generator(device=self.device)
+        g = torch.Generator(device=self.gen_device)
         g.manual_seed((h + self.seed) & ((1 << 63) - 1))
         return g
 
@@ -126,8 +129,8 @@ class SynthSource:
         parts = []
         # one expert at a time keeps the fp32 staging small (a 120b expert layer is 2.1 G elements)
         for e in range(lo, hi):
-            w = torch.randn(1, N, K, generator=self._gen(name, e), device=self.device, dtype=torch.float32) * self.std
-            parts.append(from_dense(w, fmt))
+            w = torch.randn(1, N, K, generator=self._gen(name, e), device=self.gen_device, dtype=torch.float32) * self.std
+            parts.append(from_dense(w, fmt).to(self.device) if self.gen_device != self.device else from_dense(w, fmt))
             del w
         if len(parts) == 1:
             return parts[0]
@@ -140,11 +143,11 @@ class SynthSource:
     def vector(self, name: str, n: int) -> torch.Tensor:
         g = self._gen(name)
         if name.endswith("norm.weight") or "_norm" in name:
-            return 1.0 + 0.05 * torch.randn(n, generator=g, device=self.device)
+            return (1.0 + 0.05 * torch.randn(n, generator=g, device=self.gen_device)).to(self.device)
         if name.endswith("ssm_a"):
-            return -torch.exp(torch.randn(n, generator=g, device=self.device) * 0.5)
-        return 0.02 * torch.randn(n, generator=g, device=self.device)
+            return (-torch.exp(torch.randn(n, generator=g, device=self.gen_device) * 0.5)).to(self.device)
+        return (0.02 * torch.randn(n, generator=g, device=self.gen_device)).to(self.device)
 
     def table(self, name: str, shape: tuple[int, ...]) -> torch.Tensor:
         g = self._gen(name)
-        return 0.1 * torch.randn(*shape, generator=g, device=self.device)
+        return (0.1 * torch.randn(*shape, generator=g, device=self.gen_device)).to(self.device)

@@ -146,6 +146,16 @@ def _pick_bn(M: int, N: int) -> int:
     return 128 if tiles128 >= sms else 64
 
 
+def _gemm_a(x, w: QuantWeight):
+    """Activations in the dtype the tensor-core path of this weight format multiplies in."""
+    want = torch.float16 if w.fmt == WFormat.MXFP4 else torch.bfloat16
+    return x if x.dtype == want else x.to(want)
+
+
+def _out_kind(dtype) -> int:
+    return {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}[dtype]
+
+
 def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None):
     assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[-1] == w.K and w.E == 1
     M = x.shape[0]
@@ -159,7 +169,8 @@ def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limi
         _check(lib.mx_gemv(fmt, p0, p1, p2, p3, _p(x), _p(out), _p(bias), M, w.N, w.K, int(out_f32), act, C.c_float(act_alpha),
                            C.c_float(act_limit), _vp(0), _vp(0), M, 1, _stream()), "gemv")
     else:
-        _check(lib.mx_gemm(_p(x), fmt, p0, p1, p2, p3, 1, _p(out), n_out, int(out_f32), _p(bias), _p(row_scale), act,
+        xa = _gemm_a(x, w)
+        _check(lib.mx_gemm(_p(xa), fmt, p0, p1, p2, p3, 1, _p(out), n_out, int(out_f32), _p(bias), _p(row_scale), act,
                            C.c_float(act_alpha), C.c_float(act_limit), M, w.N, w.K, _vp(0), _vp(0), _pick_bn(M, w.N), _stream()), "gemm")
     _count()
     return out
@@ -171,18 +182,23 @@ def gemm(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=
     n_out = w.N // 2 if act != ACT_NONE else w.N
     out = torch.empty(M, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     fmt, p0, p1, p2, p3 = _planes(w)
-    _check(_lib.cuda().mx_gemm(_p(x), fmt, p0, p1, p2, p3, 1, _p(out), n_out, int(out_f32), _p(bias), _p(row_scale), act,
+    xa = _gemm_a(x, w)
+    _check(_lib.cuda().mx_gemm(_p(xa), fmt, p0, p1, p2, p3, 1, _p(out), n_out, int(out_f32), _p(bias), _p(row_scale), act,
                                C.c_float(act_alpha), C.c_float(act_limit), M, w.N, w.K, _vp(0), _vp(0), bn or _pick_bn(M, w.N), _stream()), "gemm")
     _count()
     return out
 
 
-def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, bn=128):
+def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, bn=128,
+                   out_dtype=None):
+    """``out_dtype`` (bf16 / fp16 / fp32) overrides ``out_f32``; fp16 feeds a following MXFP4 GEMM without a cast."""
     P = xp.shape[0]
     n_out = w.N // 2 if act != ACT_NONE else w.N
-    out = torch.empty(P, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=xp.device)
+    odt = out_dtype or (torch.float32 if out_f32 else torch.bfloat16)
+    out = torch.empty(P, n_out, dtype=odt, device=xp.device)
     fmt, p0, p1, p2, p3 = _planes(w)
-    _check(_lib.cuda().mx_gemm(_p(xp), fmt, p0, p1, p2, p3, w.E, _p(out), n_out, int(out_f32), _p(bias), _vp(0), act, C.c_float(act_alpha),
+    xp = _gemm_a(xp, w)
+    _check(_lib.cuda().mx_gemm(_p(xp), fmt, p0, p1, p2, p3, w.E, _p(out), n_out, _out_kind(odt), _p(bias), _vp(0), act, C.c_float(act_alpha),
                                C.c_float(act_limit), P, w.N, w.K, _p(tile_expert), _p(num_tiles), bn, _stream()), "grouped gemm")
     _count()
     return out
@@ -257,15 +273,16 @@ def moe_pack(topk_idx, E, e_lo=0, e_hi=None):
     return MoePacking(counts, seg, packed_token, pair_to_packed, tile_expert, num_tiles, max_rows, K)
 
 
-def moe_gather(x, pk: MoePacking):
+def moe_gather(x, pk: MoePacking, f16=False):
     H = x.shape[1]
-    xp = torch.empty(pk.max_rows, H, dtype=torch.bfloat16, device=x.device)
-    _check(_lib.cuda().mx_moe_gather(_p(x), _p(pk.packed_token), _p(pk.num_tiles), _p(xp), H, pk.max_rows, _stream()), "moe_gather")
+    xp = torch.empty(pk.max_rows, H, dtype=torch.float16 if f16 else torch.bfloat16, device=x.device)
+    _check(_lib.cuda().mx_moe_gather(_p(x), _p(pk.packed_token), _p(pk.num_tiles), _p(xp), H, pk.max_rows, int(f16), _stream()), "moe_gather")
     _count()
     return xp
 
 
 def moe_combine(yp, pk: MoePacking, w, out=None, accumulate=False):
+    assert yp.dtype == torch.bfloat16
     T, K = w.shape
     H = yp.shape[1]
     if out is None:

@@ -80,7 +80,8 @@ def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limi
     return y if out_f32 else y.to(torch.bfloat16)
 
 
-def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False):
+def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, bn=128,
+                   out_dtype=None):
     """xp: packed rows [P,K]; tile t (rows 128t..128t+127) uses expert tile_expert[t] for t < num_tiles[0]."""
     W = _dense(w)
     P = xp.shape[0]
@@ -97,7 +98,7 @@ def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=AC
             g, u = _deinterleave16(y)
             y = _act(act, g, u, act_alpha, act_limit)
         out[rows] = y
-    return out if out_f32 else out.to(torch.bfloat16)
+    return out.to(out_dtype) if out_dtype is not None else (out if out_f32 else out.to(torch.bfloat16))
 
 
 def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, slot_scale=None, out_f32=False):
@@ -277,10 +278,10 @@ def moe_pack(topk_idx, E, e_lo=0, e_hi=None):
     return MoePacking(counts.to(torch.int32), seg.to(torch.int32), packed_token, pair_to_packed, te, num_tiles, max_rows, K)
 
 
-def moe_gather(x, pk: MoePacking):
-    xp = torch.zeros(pk.max_rows, x.shape[1], dtype=x.dtype, device=x.device)
+def moe_gather(x, pk: MoePacking, f16=False):
+    xp = torch.zeros(pk.max_rows, x.shape[1], dtype=torch.float16 if f16 else x.dtype, device=x.device)
     ok = pk.packed_token >= 0
-    xp[ok] = x[pk.packed_token[ok].long()]
+    xp[ok] = x[pk.packed_token[ok].long()].to(xp.dtype)
     return xp
 
 

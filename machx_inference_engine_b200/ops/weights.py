@@ -14,6 +14,9 @@ MXFP4     ``p0`` E2M1 codes [E,N,K/2] (natural order: byte i = e[2i] | e[2i+1]<<
           ``p1`` e8m0 exponent [E,N,K/32]
 ========  =====================================================================================
 
+The rows of the small scale planes (Q8 ``p1``, Q6K ``p3``, MXFP4 ``p1``) are zero-padded to 16 bytes
+so every row starts 16-byte aligned (the GEMM producers fetch them with 4-byte async copies).
+
 All repacks are plain torch ops, so they run on the GPU for large checkpoints and on the CPU in
 tests.  Reference parity: the load-time SoA repacks of src/model/gptoss.cpp:176-214,
 include/ie/quant_soa.hpp:33-157 and src/ops/gemv_q6_soa.cpp (bit-plane SoA); the layouts here
@@ -36,6 +39,21 @@ class WFormat(IntEnum):
     Q4K = 2
     Q6K = 3
     MXFP4 = 4
+
+
+def _pad_last(t: torch.Tensor, mult: int) -> torch.Tensor:
+    """Zero-pad the last dimension to a multiple of ``mult`` (scale planes keep 16-byte aligned rows)."""
+    n = t.shape[-1]
+    m = (n + mult - 1) // mult * mult
+    if m == n:
+        return t.contiguous()
+    out = torch.zeros(*t.shape[:-1], m, dtype=t.dtype, device=t.device)
+    out[..., :n] = t
+    return out
+
+
+# (plane index -> (elements of K per plane element, row padding multiple)) for the padded scale planes
+_AUX_PAD = {1: {1: (32, 8)}, 3: {3: (256, 8)}, 4: {1: (32, 16)}}     # WFormat value -> {plane: (k per elem, pad)}
 
 
 _E2M1 = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0])
@@ -104,12 +122,14 @@ class QuantWeight:
             WFormat.Q6K: (2, 4, 16, 256), WFormat.MXFP4: (2, 32, None, None),
         }[self.fmt]
         outs = []
-        for t, div in zip(self.planes(), per_elem):
+        pads = _AUX_PAD.get(int(self.fmt), {})
+        for i, (t, div) in enumerate(zip(self.planes(), per_elem)):
             if t is None:
                 outs.append(None)
             else:
                 a, b = int(round(lo / div)), int(round(hi / div))
-                outs.append(t[:, :, a:b].contiguous())
+                sl = t[:, :, a:b]
+                outs.append(_pad_last(sl, pads[i][1]) if i in pads else sl.contiguous())
         w = QuantWeight(self.fmt, self.N, hi - lo, self.E, *outs)
         return w
 
@@ -146,7 +166,7 @@ class QuantWeight:
         if self.fmt == WFormat.BF16:
             w = self.p0.to(torch.float32)
         elif self.fmt == WFormat.Q8:
-            w = self.p0.to(torch.float32).reshape(E, N, K // 32, 32) * self.p1.to(torch.float32).unsqueeze(-1)
+            w = self.p0.to(torch.float32).reshape(E, N, K // 32, 32) * self.p1[..., :K // 32].to(torch.float32).unsqueeze(-1)
         elif self.fmt == WFormat.Q4K:
             w = _dequant_q4k_blocks(self.p0.reshape(E, N, K // 256, 144))
         elif self.fmt == WFormat.Q6K:
@@ -161,13 +181,13 @@ class QuantWeight:
                 h[..., 9 + 2 * b] = (hb[..., b] >> 6) & 3
             q = (q | (h << 4)) - 32
             sc = self.p2.to(torch.float32).unsqueeze(-1)
-            d = self.p3.to(torch.float32).repeat_interleave(16, dim=-1).unsqueeze(-1)
+            d = self.p3[..., :K // 256].to(torch.float32).repeat_interleave(16, dim=-1).unsqueeze(-1)
             w = q.to(torch.float32) * sc * d
         elif self.fmt == WFormat.MXFP4:
             codes = self.p0.to(torch.int64)
             c = torch.stack([codes & 15, codes >> 4], dim=-1).reshape(E, N, K // 32, 32)
             vals = _E2M1.to(codes.device)[c]
-            w = vals * _e8m0_to_f32(self.p1).unsqueeze(-1)
+            w = vals * _e8m0_to_f32(self.p1[..., :K // 32]).unsqueeze(-1)
         else:  # pragma: no cover
             raise ValueError(self.fmt)
         return w.reshape(E, N, K).to(dtype)
@@ -213,7 +233,7 @@ def from_ggml(raw: torch.Tensor, ttype: int, N: int, K: int, E: int = 1, keep_q8
         b = raw.reshape(E, N, K // 32, 34)
         d = b[..., 0:2].contiguous().view(torch.float16).reshape(E, N, K // 32)
         q = b[..., 2:34].contiguous().view(torch.int8).reshape(E, N, K)
-        return QuantWeight(WFormat.Q8, N, K, E, q, d)
+        return QuantWeight(WFormat.Q8, N, K, E, q, _pad_last(d, 8))
     if t == GGMLType.Q4_K:
         return QuantWeight(WFormat.Q4K, N, K, E, raw.reshape(E, N, K // 256 * 144).contiguous())
     if t == GGMLType.Q6_K:
@@ -231,14 +251,14 @@ def from_ggml(raw: torch.Tensor, ttype: int, N: int, K: int, E: int = 1, keep_q8
         p1 = torch.stack(hb, dim=-1).reshape(E, N, K // 4).to(torch.uint8)
         p2 = b[..., 192:208].contiguous().view(torch.int8).reshape(E, N, K // 16)
         p3 = b[..., 208:210].contiguous().view(torch.float16).reshape(E, N, K // 256)
-        return QuantWeight(WFormat.Q6K, N, K, E, p0.contiguous(), p1.contiguous(), p2.contiguous(), p3.contiguous())
+        return QuantWeight(WFormat.Q6K, N, K, E, p0.contiguous(), p1.contiguous(), p2.contiguous(), _pad_last(p3, 8))
     if t == GGMLType.MXFP4:
         b = raw.reshape(E, N, K // 32, 17)
         e = b[..., 0].contiguous()
         qs = b[..., 1:17].to(torch.int32)
         c = torch.cat([qs & 15, qs >> 4], dim=-1)                                 # natural order codes [.., 32]
         p0 = (c[..., 0::2] | (c[..., 1::2] << 4)).to(torch.uint8).reshape(E, N, K // 2)
-        return QuantWeight(WFormat.MXFP4, N, K, E, p0.contiguous(), e)
+        return QuantWeight(WFormat.MXFP4, N, K, E, p0.contiguous(), _pad_last(e, 16))
     if t in (GGMLType.Q5_K, GGMLType.Q4_0):
         # rare formats: decode once on the host and keep bf16 (the reference also widens these at load)
         import numpy as np
@@ -264,7 +284,7 @@ def quantize_mxfp4(w: torch.Tensor) -> QuantWeight:
     code = idx | ((y < 0) & (idx > 0)).to(torch.int32) * 8
     code = code.reshape(E, N, K)
     p0 = (code[..., 0::2] | (code[..., 1::2] << 4)).to(torch.uint8).contiguous()
-    return QuantWeight(WFormat.MXFP4, N, K, E, p0, e.reshape(E, N, K // 32).to(torch.uint8).contiguous())
+    return QuantWeight(WFormat.MXFP4, N, K, E, p0, _pad_last(e.reshape(E, N, K // 32).to(torch.uint8), 16))
 
 
 def quantize_q8(w: torch.Tensor) -> QuantWeight:
@@ -274,7 +294,7 @@ def quantize_q8(w: torch.Tensor) -> QuantWeight:
     x = w.to(torch.float32).reshape(E, N, K // 32, 32)
     d = x.abs().amax(dim=-1, keepdim=True) / 127.0
     q = torch.where(d > 0, torch.round(x / d.clamp_min(1e-30)), torch.zeros_like(x)).clamp_(-127, 127)
-    return QuantWeight(WFormat.Q8, N, K, E, q.reshape(E, N, K).to(torch.int8).contiguous(), d.reshape(E, N, K // 32).to(torch.float16).contiguous())
+    return QuantWeight(WFormat.Q8, N, K, E, q.reshape(E, N, K).to(torch.int8).contiguous(), _pad_last(d.reshape(E, N, K // 32).to(torch.float16), 8))
 
 
 def quantize_q4k(w: torch.Tensor) -> QuantWeight:
@@ -334,7 +354,7 @@ def quantize_q6k(w: torch.Tensor) -> QuantWeight:
     hb = [h[..., 2 * b] | (h[..., 2 * b + 1] << 2) | (h[..., 8 + 2 * b] << 4) | (h[..., 9 + 2 * b] << 6) for b in range(4)]
     p1 = torch.stack(hb, dim=-1).reshape(E, N, K // 4).to(torch.uint8)
     return QuantWeight(WFormat.Q6K, N, K, E, p0.contiguous(), p1.contiguous(), sc.reshape(E, N, K // 16).to(torch.int8).contiguous(),
-                       d16.reshape(E, N, K // 256).contiguous())
+                       _pad_last(d16.reshape(E, N, K // 256), 8))
 
 
 def from_dense(w: torch.Tensor, fmt: WFormat) -> QuantWeight:

@@ -47,6 +47,28 @@ def test_dequant_layouts_roundtrip(fmt):
     assert torch.allclose(got, want, rtol=0, atol=1e-6 * float(want.abs().max()) + 1e-7), rel_err(got, want)
 
 
+def test_e2m1_decoders_bit_exact():
+    # both in-kernel E2M1 decoders (byte-permute tables -> bf16, hardware cvt -> fp16) against the code table,
+    # for every byte value in every byte lane (the reference checks its decoder the same way: tests/mxfp4_dequant_test.cpp)
+    import ctypes as C
+    from machx_inference_engine_b200 import _lib
+    vals = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6])
+    words = torch.randint(0, 2 ** 31 - 1, (4096,), dtype=torch.int64)
+    words[:256] = torch.arange(256) * 0x01010101 % (2 ** 32)
+    w32 = words.to(torch.int64).to(dev())
+    inp = (w32 & 0xFFFFFFFF).to(torch.int64)
+    packed = torch.empty(4096, dtype=torch.int32, device=dev())
+    packed.copy_(torch.where(inp >= 2 ** 31, inp - 2 ** 32, inp).to(torch.int32))
+    out = torch.empty(4096, 16, device=dev())
+    rc = _lib.cuda().mx_e2m1_probe(C.c_void_p(packed.data_ptr()), C.c_void_p(out.data_ptr()), 4096, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    codes = torch.stack([(inp >> (4 * j)) & 15 for j in range(8)], dim=1).cpu()
+    want = vals[codes]
+    got = out.cpu()
+    assert torch.equal(got[:, :8], want), "byte-permute decoder"
+    assert torch.equal(got[:, 8:], want), "hardware cvt decoder"
+
+
 @pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("M", [1, 3, 8])
 def test_gemv(fmt, M):

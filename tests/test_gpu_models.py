@@ -23,7 +23,7 @@ def test_greedy_tokens_match_cpu_oracle(name, quant):
     outs = {}
     logits = {}
     for dev in ("cpu", "cuda:0"):
-        model = build_model(cfg, torch.device(dev), quant=quant, max_ctx=1024)
+        model = build_model(cfg, torch.device(dev), quant=quant, max_ctx=1024, gen_device="cpu")
         eng = LLMEngine(model, EngineOptions(max_ctx=1024, max_batch_tokens=512, max_seqs=4, cuda_graphs=True))
         outs[dev] = eng.generate(prompts, SamplingParams(max_tokens=12))
     # the reference's TP test asks for cosine >= 0.999, same argmax, greedy tokens identical (tools/multi_gpu_tp_test.cpp);
@@ -41,7 +41,7 @@ def test_logits_cosine_prefill_and_graph_decode():
     res = {}
     for dev in ("cpu", "cuda:0"):
         d = torch.device(dev)
-        m = build_model(cfg, d, quant="mxfp4", max_ctx=512)
+        m = build_model(cfg, d, quant="mxfp4", max_ctx=512, gen_device="cpu")
         kv = m.new_kv_cache(6)
         T = len(ids)
         pos = torch.arange(T, dtype=torch.int32, device=d)
