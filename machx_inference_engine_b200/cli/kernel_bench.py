@@ -97,7 +97,7 @@ def main(argv=None):
 
     if a.kernel == "gemm":
         ws = [weight(a.n, a.k) for _ in range(a.layers)]
-        x = (torch.randn(a.m, a.k, device=dev) * 0.5).to(torch.float16 if fmt == WFormat.MXFP4 else torch.bfloat16)
+        x = (torch.randn(a.m, a.k, device=dev) * 0.5).to(torch.bfloat16)
         i = [0]
 
         def fn():
@@ -112,7 +112,7 @@ def main(argv=None):
         x = torch.randn(T, H, device=dev).to(torch.bfloat16)
         idx, w = K.moe_route(torch.randn(T, E, device=dev), None, k)
         pk = K.moe_pack(idx, E)
-        f16 = fmt == WFormat.MXFP4
+        f16 = False
         mid = torch.float16 if f16 else torch.bfloat16
         xp = K.moe_gather(x, pk, f16=f16)
         hmid = K.grouped_linear(xp, gu, pk.tile_expert, pk.num_tiles, act=ref.ACT_SWIGLU_OAI, out_dtype=mid)

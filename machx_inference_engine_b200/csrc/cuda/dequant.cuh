@@ -286,28 +286,32 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int FMT> struct RawSlot { static constexpr int BYTES = 32; };
-template <> struct RawSlot<WF_Q8> { static constexpr int BYTES = 48; };
+// Per producer thread and k-iteration: MAIN bytes (16-byte granules) and AUX bytes (scales) live in two
+// separate shared arrays, each indexed by thread, so neighbouring threads touch neighbouring banks.
+template <int FMT> struct RawSlot { static constexpr int MAIN = 16, AUX = 4; };
+template <> struct RawSlot<WF_Q8> { static constexpr int MAIN = 32, AUX = 4; };
+template <> struct RawSlot<WF_Q4K> { static constexpr int MAIN = 16, AUX = 16; };
+template <> struct RawSlot<WF_Q6K> { static constexpr int MAIN = 16, AUX = 16; };
 
 template <int FMT>
-__device__ __forceinline__ void raw_issue(uint32_t slot, const RowPtrs& rp, int kiter, int half) {
+__device__ __forceinline__ void raw_issue(uint32_t slot, uint32_t aux, const RowPtrs& rp, int kiter, int half) {
   const int kb = 2 * kiter + half;
   if constexpr (FMT == WF_MXFP4) {
     cp_async16(slot, rp.p0 + (size_t)kb * 16);
-    cp_async4(slot + 16, rp.p1 + ((2 * kiter) & ~3));
+    cp_async4(aux, rp.p1 + ((2 * kiter) & ~3));
   } else if constexpr (FMT == WF_Q8) {
     cp_async16(slot, rp.p0 + (size_t)kb * 32);
     cp_async16(slot + 16, rp.p0 + (size_t)kb * 32 + 16);
-    cp_async4(slot + 32, rp.p1 + 4 * kiter);
+    cp_async4(aux, rp.p1 + 4 * kiter);
   } else if constexpr (FMT == WF_Q4K) {
     const uint8_t* blk = rp.p0 + (size_t)(kiter >> 2) * 144;
     cp_async16(slot, blk + 16 + 32 * (kiter & 3) + 16 * half);
-    cp_async16(slot + 16, blk);
+    cp_async16(aux, blk);
   } else if constexpr (FMT == WF_Q6K) {
     cp_async16(slot, rp.p0 + (size_t)kb * 16);
-    cp_async8(slot + 16, rp.p1 + (size_t)kb * 8);
-    cp_async4(slot + 24, rp.p2 + 4 * kiter);
-    cp_async4(slot + 28, rp.p3 + ((2 * (kiter >> 2)) & ~3));
+    cp_async8(aux, rp.p1 + (size_t)kb * 8);
+    cp_async4(aux + 8, rp.p2 + 4 * kiter);
+    cp_async4(aux + 12, rp.p3 + ((2 * (kiter >> 2)) & ~3));
   }
 }
 
@@ -319,27 +323,29 @@ __device__ __forceinline__ int raw_chunk(int half, int c) {
 }
 
 template <int FMT>
-__device__ __forceinline__ void raw_decode(const uint8_t* slot, int kiter, int half, uint32_t (&o)[16]) {
+__device__ __forceinline__ void raw_decode(const uint8_t* slot, const uint8_t* aux, int kiter, int half, uint32_t (&o)[16]) {
   if constexpr (FMT == WF_MXFP4) {
-    // MXFP4 is decoded to fp16 (the GEMM runs its fp16 x fp16 mode for this format): one hardware
-    // cvt turns a byte (two E2M1 codes) into an f16x2, one multiply applies the power-of-two scale.
-    const uint32_t e = slot[16 + ((2 * kiter + half) & 3)];
-    const uint32_t s2 = e8m0_to_f16x2(e);
-    const __half2 sv = *reinterpret_cast<const __half2*>(&s2);
+    // Byte-permute table decode to bf16 (ALU pipe), then one packed multiply by the power-of-two scale.
+    // The hardware conversion (e2m1x8_to_f16x2) was measured slower here: it issues on the XU pipe,
+    // which saturates at a quarter of the rate this loop needs.
+    const uint32_t e = aux[(2 * kiter + half) & 3];
+    const uint32_t sb = e == 0 ? 0x0040u : (e << 7);
+    const uint32_t s2 = sb | (sb << 16);
+    const __nv_bfloat162 sv = *reinterpret_cast<const __nv_bfloat162*>(&s2);
     const uint4 v = *reinterpret_cast<const uint4*>(slot);
     const uint32_t q[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       uint32_t t[4];
-      e2m1x8_to_f16x2(q[i], t);
+      e2m1x8_to_bf16x2(q[i], t);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        __half2 pr = __hmul2(*reinterpret_cast<__half2*>(&t[j]), sv);
+        __nv_bfloat162 pr = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&t[j]), sv);
         o[4 * i + j] = *reinterpret_cast<uint32_t*>(&pr);
       }
     }
   } else if constexpr (FMT == WF_Q8) {
-    const float d = __half2float(*reinterpret_cast<const __half*>(slot + 32 + 2 * half));
+    const float d = __half2float(*reinterpret_cast<const __half*>(aux + 2 * half));
     const uint4 a = *reinterpret_cast<const uint4*>(slot), b = *reinterpret_cast<const uint4*>(slot + 16);
     const uint32_t q[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     const float c = -128.f * d;
@@ -352,7 +358,7 @@ __device__ __forceinline__ void raw_decode(const uint8_t* slot, int kiter, int h
       o[2 * i + 1] = pack_bf16(fmaf(f2, d, c), fmaf(f3, d, c));
     }
   } else if constexpr (FMT == WF_Q4K) {
-    const uint4 hdr = *reinterpret_cast<const uint4*>(slot + 16);
+    const uint4 hdr = *reinterpret_cast<const uint4*>(aux);
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
     const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
     const int j = kiter & 3;
@@ -372,10 +378,10 @@ __device__ __forceinline__ void raw_decode(const uint8_t* slot, int kiter, int h
     }
   } else if constexpr (FMT == WF_Q6K) {
     const int dsel = (2 * (kiter >> 2)) & 3;
-    const float d = __half2float(*reinterpret_cast<const __half*>(slot + 28 + dsel));
+    const float d = __half2float(*reinterpret_cast<const __half*>(aux + 12 + dsel));
     const uint4 lo = *reinterpret_cast<const uint4*>(slot);
-    const uint2 hi = *reinterpret_cast<const uint2*>(slot + 16);
-    const uint32_t scw = *reinterpret_cast<const unsigned short*>(slot + 24 + 2 * half);
+    const uint2 hi = *reinterpret_cast<const uint2*>(aux);
+    const uint32_t scw = *reinterpret_cast<const unsigned short*>(aux + 8 + 2 * half);
     const float ds0 = d * (float)(int8_t)(scw & 0xFF), ds1 = d * (float)(int8_t)(scw >> 8);
     const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w};
     const uint32_t hw[2] = {hi.x, hi.y};

@@ -18,6 +18,7 @@
 #include "common.cuh"
 #include "dequant.cuh"
 #include "host_util.h"
+#include <cstdlib>
 
 namespace mx {
 
@@ -43,6 +44,7 @@ struct GemmParams {
   int act;
   float act_alpha, act_limit;
   int group_m;                  // tile rasterisation group (see tile_coords)
+  int debug;
   int* status;
 };
 
@@ -62,7 +64,8 @@ struct SmemLayout {
   static constexpr int NB = kDequant ? SB : SA;
   static constexpr int BAR_OFFSET = B_OFFSET + NB * B_BYTES;
   static constexpr int RAW_THREADS = 2 * BN;
-  static constexpr int RAW_STAGE = kDequant ? RAW_THREADS * RawSlot<FMT>::BYTES : 0;
+  static constexpr int RAW_MAIN = kDequant ? RAW_THREADS * RawSlot<FMT>::MAIN : 0;     // per stage: main bytes, then aux bytes
+  static constexpr int RAW_STAGE = kDequant ? RAW_THREADS * (RawSlot<FMT>::MAIN + RawSlot<FMT>::AUX) : 0;
   static constexpr int RAW_OFFSET = BAR_OFFSET + 512;
   static constexpr int TOTAL = RAW_OFFSET + kRawDepth * RAW_STAGE + 1024;   // + alignment slack
   static_assert(TOTAL <= 232448, "shared memory plan exceeds 227 KB");
@@ -119,7 +122,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int s = 0; s < SB; ++s) {
-      mbar_init(bar_bfull + 8 * s, kNumDequantWarps * 32);
+      mbar_init(bar_bfull + 8 * s, kNumDequantWarps);      // one arrival per decode warp
       mbar_init(bar_bempty + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -156,6 +159,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         for (int k = 0; k < k_iters; ++k, ++it) {
           const uint32_t s = it % SA, ph = (it / SA) & 1;
           if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, p.status, ERR_MBAR_TIMEOUT_PRODUCER, abort_flag))) break;
+          if (p.debug & 64) { mbar_arrive(bar_full + 8 * s); continue; }
           mbar_expect_tx(bar_full + 8 * s, kDequant ? L::A_BYTES : L::A_BYTES + L::B_BYTES);
           tma_load_2d(smem_base + L::A_OFFSET + s * L::A_BYTES, &tmap_a, bar_full + 8 * s, k * BK, mt * BM);
           if (!kDequant) tma_load_3d(smem_base + L::B_OFFSET + s * L::B_BYTES, &tmap_b, bar_full + 8 * s, k * BK, nt * BN, e);
@@ -165,8 +169,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // MXFP4 weights are decoded to fp16, so that format runs fp16 x fp16 (activations arrive as fp16)
-      constexpr uint32_t idesc = FMT == WF_MXFP4 ? umma_idesc_f16(BM, BN, 0, 0) : umma_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
       uint32_t it = 0, tile_n = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_n) {
@@ -182,9 +185,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tc_fence_after();
           const uint64_t a_desc = umma_desc_k_sw128(smem_base + L::A_OFFSET + s * L::A_BYTES);
           const uint64_t b_desc = umma_desc_k_sw128(smem_base + L::B_OFFSET + sb * L::B_BYTES);
+          if (!(p.debug & 8)) {
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes per UMMA K step: +2 in the (addr>>4) field
             umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (k | kk) != 0);
+          }
           umma_commit(bar_empty + 8 * s);
           if (kDequant) umma_commit(bar_bempty + 8 * sb);
         }
@@ -201,14 +206,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
       const int e = p.tile_expert ? p.tile_expert[mt] : 0;
       const uint32_t acc = tile_n & 1, acc_ph = (tile_n >> 1) & 1;
-      if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag, 256))) break;
+      if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag))) break;
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const float rs = (p.row_scale && row_ok) ? p.row_scale[row] : 1.f;
       const float* bias = p.bias ? p.bias + (size_t)e * p.N : nullptr;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < ((p.debug & 32) ? 0 : BN); c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r);
         tmem_ld_wait();
@@ -286,8 +291,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int d = threadIdx.x - (2 + kNumEpilogueWarps) * 32;   // 0..255
     const int half = d & 1, rl = d >> 1;
     const bool live = rl < BN;
-    uint8_t* raw_base = smem + L::RAW_OFFSET + (live ? d : 0) * RawSlot<FMT>::BYTES;
-    const uint32_t raw_base_u32 = smem_u32(raw_base);
+    uint8_t* raw_base = smem + L::RAW_OFFSET + (live ? d : 0) * RawSlot<FMT>::MAIN;
+    uint8_t* aux_base = smem + L::RAW_OFFSET + L::RAW_MAIN + (live ? d : 0) * RawSlot<FMT>::AUX;
+    const uint32_t raw_base_u32 = smem_u32(raw_base), aux_base_u32 = smem_u32(aux_base);
     const int k_blocks = p.K / 32;                 // valid 32-element blocks along K
     // prefetch cursor: tile pt, k-iteration pk, ring slot ps; row pointers are recomputed once per tile
     int pt = blockIdx.x, pk = 0, ps = 0;
@@ -307,7 +313,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
     };
     auto issue_next = [&]() {
-      if (prow_ok && 2 * pk + half < k_blocks) raw_issue<FMT>(raw_base_u32 + ps * L::RAW_STAGE, prp, pk, half);
+      if (prow_ok && 2 * pk + half < k_blocks && !(p.debug & 2)) raw_issue<FMT>(raw_base_u32 + ps * L::RAW_STAGE, aux_base_u32 + ps * L::RAW_STAGE, prp, pk, half);
       cp_async_commit();
       ps = (ps + 1 == kRawDepth) ? 0 : ps + 1;
       if (++pk == k_iters) { pk = 0; pt += gridDim.x; prefetch_tile_setup(); }
@@ -325,22 +331,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int k = 0; k < k_iters; ++k) {
         issue_next();
         cp_async_wait<kRawDepth - 1>();          // this iteration's bytes have landed in the slot
-        if (!(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag, 20))) break;
+        if (!(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag))) break;
         if (live) {
           uint8_t* b_tile = smem + L::B_OFFSET + sb * L::B_BYTES;
           uint32_t o[16];
-          if (row_ok && 2 * k + half < k_blocks) {
-            raw_decode<FMT>(raw_base + cs * L::RAW_STAGE, k, half, o);
+          if (row_ok && 2 * k + half < k_blocks && !(p.debug & 1)) {
+            raw_decode<FMT>(raw_base + cs * L::RAW_STAGE, aux_base + cs * L::RAW_STAGE, k, half, o);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) o[j] = 0u;
           }
+          if (!(p.debug & 4)) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
             *reinterpret_cast<uint4*>(b_tile + sw128_offset(rl, raw_chunk<FMT>(half, c))) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+          }
         }
-        fence_proxy_async();
-        mbar_arrive(bar_bfull + 8 * sb);
+        // every lane publishes its generic-proxy stores to the async proxy, then one lane arrives for the warp
+        if (!(p.debug & 16)) fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_bfull + 8 * sb);
         cs = (cs + 1 == kRawDepth) ? 0 : cs + 1;
         if (++sb == SB) { sb = 0; phb ^= 1; }
       }
@@ -382,7 +392,7 @@ template <int BN, int SA, int QA, int QB>
 static int dispatch_fmt(int fmt, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
   switch (fmt) {
     case WF_BF16: return launch<WF_BF16, BN, SA, 1>(ta, tb, p, st);
-    case WF_Q8: return launch<WF_Q8, BN, QA - 1, QB - 1>(ta, tb, p, st);
+    case WF_Q8: return launch<WF_Q8, BN, QA - 1, QB - 2>(ta, tb, p, st);
     case WF_Q4K: return launch<WF_Q4K, BN, QA, QB>(ta, tb, p, st);
     case WF_Q6K: return launch<WF_Q6K, BN, QA, QB>(ta, tb, p, st);
     case WF_MXFP4: return launch<WF_MXFP4, BN, QA, QB>(ta, tb, p, st);
@@ -393,8 +403,7 @@ static int dispatch_fmt(int fmt, const CUtensorMap& ta, const CUtensorMap& tb, c
 }  // namespace mx
 
 // C[M, N(/2 with act)] = A[M,K] * W[(E,)N,K]^T.
-//   a          [M,K] row-major 16-bit activations, 16-byte aligned, K % 8 == 0: bf16, except fp16 when the
-//              weights are MXFP4 (that format is decoded to fp16 and multiplied in fp16 x fp16 mode)
+//   a          bf16 [M,K] row-major, 16-byte aligned, K % 8 == 0
 //   out_f32    output kind: 0 bf16, 1 fp32, 2 fp16
 //   wfmt/w0..w3  weight format and plane pointers (see WFormat); n_experts >= 1
 //   tile_expert / num_m_tiles_dev: grouped mode (both null for a plain GEMM)
@@ -421,6 +430,8 @@ MX_HOST_API int mx_gemm(const void* a, int wfmt, const void* w0, const void* w1,
   p.bias = bias; p.row_scale = row_scale;
   p.act = act; p.act_alpha = act_alpha; p.act_limit = act_limit;
   p.group_m = tile_expert ? 1 : 8;
+  { const char* dbg = getenv("MX_GEMM_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
+  { const char* g = getenv("MX_GEMM_GROUP"); if (g) p.group_m = atoi(g); }
   p.status = status_word();
 
   CUtensorMap ta, tb;
@@ -441,7 +452,7 @@ MX_HOST_API int mx_gemm(const void* a, int wfmt, const void* w0, const void* w1,
     tb = ta;
   }
   switch (bn) {
-    case 128: return dispatch_fmt<128, 6, 4, 4>(wfmt, ta, tb, p, stream);
+    case 128: return dispatch_fmt<128, 6, 4, 6>(wfmt, ta, tb, p, stream);
     case 64: return dispatch_fmt<64, 8, 6, 4>(wfmt, ta, tb, p, stream);
     case 32: return dispatch_fmt<32, 8, 6, 4>(wfmt, ta, tb, p, stream);
     default: return -105;

@@ -309,13 +309,9 @@ class MoEFFN:
             out = ops.moe_combine(y, self._arange[key], w)
         else:
             pk = ops.moe_pack(idx, self.E, self.e_lo, self.e_hi)
-            # MXFP4 experts multiply in fp16 x fp16: gather converts, the gate|up epilogue emits fp16 for the down GEMM
-            f16_in = self.gate_up.fmt == ops.WFormat.MXFP4
-            f16_mid = self.down.fmt == ops.WFormat.MXFP4
-            xp = ops.moe_gather(h, pk, f16=f16_in)
+            xp = ops.moe_gather(h, pk)
             te = pk.tile_expert - self.e_lo if self.e_lo else pk.tile_expert
-            a = ops.grouped_linear(xp, self.gate_up, te, pk.num_tiles, bias=self.gu_bias, act=self.act,
-                                   out_dtype=torch.float16 if f16_mid else torch.bfloat16)
+            a = ops.grouped_linear(xp, self.gate_up, te, pk.num_tiles, bias=self.gu_bias, act=self.act)
             y = ops.grouped_linear(a, self.down, te, pk.num_tiles, bias=self.down_bias)
             out = ops.moe_combine(y, pk, w)
         if self.reduce:

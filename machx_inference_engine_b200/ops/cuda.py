@@ -148,7 +148,7 @@ def _pick_bn(M: int, N: int) -> int:
 
 def _gemm_a(x, w: QuantWeight):
     """Activations in the dtype the tensor-core path of this weight format multiplies in."""
-    want = torch.float16 if w.fmt == WFormat.MXFP4 else torch.bfloat16
+    want = torch.bfloat16
     return x if x.dtype == want else x.to(want)
 
 
@@ -219,11 +219,29 @@ def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE
 _attn_scratch: dict = {}
 
 
+TC_PREFILL_MIN_Q = 64      # query segments at least this long take the tensor-core kernel
+
+
+def attention_prefill_tc(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None):
+    """tcgen05 FlashAttention (head_dim 64 / 128, page size 128)."""
+    Tq, n_q, hd = q.shape
+    n_kv, bs = k_cache.shape[1], k_cache.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    out = torch.empty(Tq, n_q, hd, dtype=torch.bfloat16, device=q.device)
+    _check(_lib.cuda().mx_attention_prefill_tc(_p(q), _p(k_cache), _p(v_cache), _p(block_table), _p(seq_lens), _p(cu_q), _p(sinks), _p(out),
+                                               seq_lens.numel(), Tq, int(max_q_len), n_q, n_kv, hd, block_table.shape[1], k_cache.shape[0], bs,
+                                               int(window), C.c_float(scale), _stream()), "attention_prefill_tc")
+    _count()
+    return out
+
+
 def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0, n_splits=None):
     Tq, n_q, hd = q.shape
     n_kv, bs = k_cache.shape[1], k_cache.shape[2]
     B = seq_lens.numel()
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    if max_q_len >= TC_PREFILL_MIN_Q and hd in (64, 128) and bs == 128 and not softcap and n_splits is None:
+        return attention_prefill_tc(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=sinks, window=window, scale=scale)
     if n_splits is None:
         # decode-sized problems: split the KV range so that ~2 CTAs per SM exist
         ctas = B * n_kv * max(1, (max_q_len * (n_q // n_kv) + 31) // 32)

@@ -287,6 +287,22 @@ def test_attention_decode_and_prefill(hd, n_q, n_kv, window):
     assert torch.allclose(got.float(), torch.full_like(got.float(), 0.25), atol=2e-3)
 
 
+@pytest.mark.parametrize("hd,n_q,n_kv", [(64, 16, 2), (128, 8, 2)])
+@pytest.mark.parametrize("window", [0, 128])
+@pytest.mark.parametrize("use_sinks", [False, True])
+def test_attention_prefill_tensor_core(hd, n_q, n_kv, window, use_sinks):
+    # tcgen05 FlashAttention against the oracle: ragged batch, fresh prompts and continued contexts,
+    # tiles on the diagonal, at the window edge and at the sequence end
+    sinks = torch.randn(n_q, device=dev()) if use_sinks else None
+    q, kc, vc, bt, sl, cu = _paged_case(4, [300, 64, 129, 128], [300, 700, 129, 1024], n_q, n_kv, hd, seed=2)
+    got = K().attention_prefill_tc(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window)
+    K().check_status()
+    want = ref.attention(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window)
+    assert rel_err(got, want) < 1.5e-2
+    # the dispatcher sends long query segments to the same kernel
+    assert torch.equal(K().attention(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window), got)
+
+
 def test_sampling():
     V = 5003
     logits = torch.randn(4, V, device=dev())
