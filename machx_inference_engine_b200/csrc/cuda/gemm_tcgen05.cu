@@ -190,8 +190,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes per UMMA K step: +2 in the (addr>>4) field
             umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (k | kk) != 0);
           }
-          umma_commit(bar_empty + 8 * s);
-          if (kDequant) umma_commit(bar_bempty + 8 * sb);
+          if (p.debug & 256) mbar_arrive(bar_empty + 8 * s); else umma_commit(bar_empty + 8 * s);
+          if (kDequant && !(p.debug & 128)) umma_commit(bar_bempty + 8 * sb);
         }
         if (ok) umma_commit(bar_tfull + 8 * acc);
       }
@@ -331,7 +331,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int k = 0; k < k_iters; ++k) {
         issue_next();
         cp_async_wait<kRawDepth - 1>();          // this iteration's bytes have landed in the slot
-        if (!(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag))) break;
+        if (!(p.debug & 128) && !(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag))) break;
         if (live) {
           uint8_t* b_tile = smem + L::B_OFFSET + sb * L::B_BYTES;
           uint32_t o[16];
