@@ -14,6 +14,9 @@
 // causal + window masks and whole-tile skipping).
 #include "common.cuh"
 #include "host_util.h"
+#include "mx_noalloc.h"
+
+#include <cstdio>
 
 namespace mx {
 
@@ -232,4 +235,54 @@ MX_HOST_API int mx_attention(const void* q, const void* k_cache, const void* v_c
   if (rc) return rc;
   attn_combine_kernel<<<(Tq * n_q + 3) / 4, 128, 0, st>>>(o_part, ml_part, sinks, (__nv_bfloat16*)out, Tq, n_q, hd, p.n_splits);
   return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (see mx_noalloc.h): the split-KV partials live in this fixed device array.
+// In host code the array's name is only a handle for cudaGetSymbolAddress; the kernels are given the
+// device address that call returns.
+static __device__ __align__(256) float g_noalloc_scratch[MX_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+float* g_noalloc_ptr[64] = {nullptr};        // per device, resolved on first use
+thread_local char g_noalloc_err[256] = "";
+}  // namespace
+
+MX_HOST_API const char* mx_attention_noalloc_error(void) { return g_noalloc_err; }
+
+MX_HOST_API int mx_attention_noalloc(const void* q, const void* k_cache, const void* v_cache, const int* block_table, const int* seq_lens,
+                                     const int* cu_q, const float* sinks, void* out, int B, int Tq, int max_q_len, int n_q, int n_kv, int hd,
+                                     int max_blocks, int block_size, int window, float scale, float softcap, int n_splits,
+                                     cudaStream_t stream) {
+  g_noalloc_err[0] = 0;
+  if (B <= 0 || Tq <= 0) return 0;
+  const int splits = n_splits < 1 ? 1 : n_splits;
+  const unsigned long long need = (unsigned long long)splits * Tq * n_q * (unsigned long long)(hd + 2);
+  if (need > MX_NOALLOC_SCRATCH_FLOATS) {
+    snprintf(g_noalloc_err, sizeof g_noalloc_err,
+             "mx_attention_noalloc: needs %llu scratch floats (n_splits %d x Tq %d x n_q %d x (head_dim %d + 2)) but the built-in scratch holds %u; "
+             "use fewer splits / tokens or call mx_attention with caller-provided scratch",
+             need, splits, Tq, n_q, hd, (unsigned)MX_NOALLOC_SCRATCH_FLOATS);
+    return MX_NOALLOC_E_TOO_LARGE;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    snprintf(g_noalloc_err, sizeof g_noalloc_err, "mx_attention_noalloc: cannot identify the current device (%s)", cudaGetErrorString(e));
+    return MX_NOALLOC_E_SYMBOL;
+  }
+  if (!g_noalloc_ptr[dev]) {
+    // once per device, with that device current: turn the symbol into a device address
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr) {
+      snprintf(g_noalloc_err, sizeof g_noalloc_err, "mx_attention_noalloc: cudaGetSymbolAddress failed on device %d (%s)", dev, cudaGetErrorString(e));
+      return MX_NOALLOC_E_SYMBOL;
+    }
+    g_noalloc_ptr[dev] = ptr;
+  }
+  float* o_part = g_noalloc_ptr[dev];
+  float* ml_part = o_part + (size_t)splits * Tq * n_q * hd;
+  return mx_attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, sinks, out, o_part, ml_part, B, Tq, max_q_len, n_q, n_kv, hd, max_blocks,
+                      block_size, window, scale, softcap, splits, stream);
 }

@@ -1,0 +1,84 @@
+"""The allocation-free attention entry point, called through its exported C symbol.
+
+Some hosts that embed the kernel library may not allocate device memory once they are running (all of
+HBM is already in their own pools, or they must stay clear of the driver's allocator lock).  For them the
+library ships ``mx_attention_noalloc``: same kernels as ``mx_attention`` but the split-KV scratch is a
+fixed array inside the library.  This test drives that symbol with ctypes only and checks it against the
+regular entry point, twice in a row (the scratch keeps the previous call's contents, which must not leak
+into the next result), and checks that an oversized request is refused with a readable message.
+"""
+import ctypes as C
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    from machx_inference_engine_b200 import _build
+    lib = C.CDLL(str(_build.CUDA_LIB))
+    lib.mx_attention_noalloc_error.restype = C.c_char_p
+    return lib
+
+
+def _case(seed, B, q_lens, kv_lens, n_q, n_kv, hd):
+    torch.manual_seed(seed)
+    dev = torch.device("cuda:0")
+    bs = 128
+    max_blocks = max((L + bs - 1) // bs for L in kv_lens)
+    nblk = B * max_blocks + 1
+    kc = torch.randn(nblk, n_kv, bs, hd, device=dev).to(torch.bfloat16)
+    vc = torch.randn(nblk, n_kv, bs, hd, device=dev).to(torch.bfloat16)
+    bt = (torch.randperm(nblk - 1)[: B * max_blocks].reshape(B, max_blocks) + 1).to(torch.int32).to(dev)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+    q = torch.randn(sum(q_lens), n_q, hd, device=dev).to(torch.bfloat16)
+    sl = torch.tensor(kv_lens, dtype=torch.int32, device=dev)
+    sinks = torch.randn(n_q, device=dev)
+    return q, kc, vc, bt, sl, cu, sinks
+
+
+def _call(lib, fn_name, case, n_q, n_kv, hd, max_q, splits, window, scratch=None):
+    q, kc, vc, bt, sl, cu, sinks = case
+    Tq = q.shape[0]
+    out = torch.empty_like(q)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    common_tail = (sl.numel(), Tq, max_q, n_q, n_kv, hd, bt.shape[1], 128, window, C.c_float(1.0 / math.sqrt(hd)), C.c_float(0.0), splits, st)
+    if fn_name == "mx_attention":
+        o_part, ml_part = scratch
+        rc = lib.mx_attention(p(q), p(kc), p(vc), p(bt), p(sl), p(cu), p(sinks), p(out), p(o_part), p(ml_part), *common_tail)
+    else:
+        rc = lib.mx_attention_noalloc(p(q), p(kc), p(vc), p(bt), p(sl), p(cu), p(sinks), p(out), *common_tail)
+    torch.cuda.synchronize()
+    return rc, out
+
+
+def test_noalloc_entry_point_matches_regular_one_twice_in_a_row():
+    lib = _lib()
+    n_q, n_kv, hd = 16, 2, 64
+    # call 1: decode-shaped, 5 splits.  call 2: a different, smaller problem that reuses the same scratch.
+    for seed, q_lens, kv_lens, max_q, splits, window in ((0, [1, 1, 1], [700, 130, 1025], 1, 5, 0), (1, [9, 1], [300, 77], 9, 2, 128)):
+        case = _case(seed, len(q_lens), q_lens, kv_lens, n_q, n_kv, hd)
+        Tq = case[0].shape[0]
+        o_part = torch.empty(splits * Tq * n_q * hd, device="cuda:0")
+        ml_part = torch.empty(splits * Tq * n_q * 2, device="cuda:0")
+        rc_ref, want = _call(lib, "mx_attention", case, n_q, n_kv, hd, max_q, splits, window, (o_part, ml_part))
+        rc, got = _call(lib, "mx_attention_noalloc", case, n_q, n_kv, hd, max_q, splits, window)
+        assert rc_ref == 0 and rc == 0, lib.mx_attention_noalloc_error()
+        err = float((got.float() - want.float()).norm() / want.float().norm())
+        assert err < 1e-2, err          # same kernels, same order of operations: in practice bit-identical
+        assert torch.equal(got, want)
+
+
+def test_noalloc_entry_point_refuses_oversized_requests():
+    lib = _lib()
+    n_q, n_kv, hd = 16, 2, 64
+    case = _case(2, 1, [4096], [4096], n_q, n_kv, hd)       # 8 splits x 4096 x 16 x 66 floats > 2 Mi floats
+    before = torch.cuda.memory_allocated()
+    rc, _ = _call(lib, "mx_attention_noalloc", case, n_q, n_kv, hd, 4096, 8, 0)
+    assert rc == -130
+    msg = lib.mx_attention_noalloc_error().decode()
+    assert "scratch" in msg and "2097152" in msg
+    assert torch.cuda.memory_allocated() - before <= case[0].numel() * 2 + 1024     # only the test's own output tensor
