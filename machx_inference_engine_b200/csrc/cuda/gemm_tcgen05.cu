@@ -393,8 +393,8 @@ static int dispatch_fmt(int fmt, const CUtensorMap& ta, const CUtensorMap& tb, c
   switch (fmt) {
     case WF_BF16: return launch<WF_BF16, BN, SA, 1>(ta, tb, p, st);
     case WF_Q8: return launch<WF_Q8, BN, QA - 1, QB - 2>(ta, tb, p, st);
-    case WF_Q4K: return launch<WF_Q4K, BN, QA, QB>(ta, tb, p, st);
-    case WF_Q6K: return launch<WF_Q6K, BN, QA, QB>(ta, tb, p, st);
+    case WF_Q4K: return launch<WF_Q4K, BN, QA, QB - 1>(ta, tb, p, st);
+    case WF_Q6K: return launch<WF_Q6K, BN, QA, QB - 1>(ta, tb, p, st);
     case WF_MXFP4: return launch<WF_MXFP4, BN, QA, QB>(ta, tb, p, st);
     default: return -100;
   }
