@@ -16,6 +16,7 @@
 // dequant_kernels.cpp) and the dispatcher in src/model/dense_dispatch.hpp:562-754, and the MoE
 // prefill GEMMs of src/ops/moe_fused.cpp:568-1961.  Ragged K and N are handled natively.
 #include "common.cuh"
+#include "comm.cuh"
 #include "dequant.cuh"
 #include "host_util.h"
 #include <cstdlib>
@@ -46,6 +47,7 @@ struct GemmParams {
   int group_m;                  // tile rasterisation group (see tile_coords)
   int debug;
   int* status;
+  PeerOut peer;                 // world > 0: the tile is stored into every rank's inbox (fused all-reduce), not into C
 };
 
 constexpr int kRawDepth = 10;   // k-iterations of packed weight bytes kept in flight per producer thread
@@ -143,6 +145,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int m_tiles = p.num_m_tiles_dev ? min(*p.num_m_tiles_dev, p.num_m_tiles) : p.num_m_tiles;
   const int total_tiles = m_tiles * p.num_n_tiles;
+  const int next_seq = p.peer.world ? *p.peer.seq + 1 : 0;
   const int k_iters = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
@@ -190,8 +193,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes per UMMA K step: +2 in the (addr>>4) field
             umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (k | kk) != 0);
           }
-          if (p.debug & 256) mbar_arrive(bar_empty + 8 * s); else umma_commit(bar_empty + 8 * s);
-          if (kDequant && !(p.debug & 128)) umma_commit(bar_bempty + 8 * sb);
+          umma_commit(bar_empty + 8 * s);
+          if (kDequant) umma_commit(bar_bempty + 8 * sb);
         }
         if (ok) umma_commit(bar_tfull + 8 * acc);
       }
@@ -228,8 +231,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (p.act == ACT_NONE) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= rs;
+          const int n_dst = p.peer.world ? p.peer.world : 1;
+          for (int dst = 0; dst < n_dst; ++dst) {
+          void* cbase = p.peer.world ? (void*)peer_slot(p.peer, dst, next_seq) : p.C;
           if (p.out_f32 == 1) {
-            float* out = (float*)p.C + (size_t)row * p.ldc + col0;
+            float* out = (float*)cbase + (size_t)row * p.ldc + col0;
             if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -238,7 +244,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           } else {
             const bool h = p.out_f32 == 2;
-            __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + col0;
+            __nv_bfloat16* out = (__nv_bfloat16*)cbase + (size_t)row * p.ldc + col0;
             if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8)
@@ -251,6 +257,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (h) ((__half*)out)[j] = __float2half(v[j]); else out[j] = __float2bfloat16(v[j]);
               }
             }
+          }
           }
         } else {
           // gate/up are interleaved in groups of 16 columns: [g0..g15 | u0..u15]; 16 outputs per 32 inputs
@@ -331,7 +338,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int k = 0; k < k_iters; ++k) {
         issue_next();
         cp_async_wait<kRawDepth - 1>();          // this iteration's bytes have landed in the slot
-        if (!(p.debug & 128) && !(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag))) break;
+        if (!(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag))) break;
         if (live) {
           uint8_t* b_tile = smem + L::B_OFFSET + sb * L::B_BYTES;
           uint32_t o[16];
@@ -366,6 +373,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (p.peer.world) peer_publish(p.peer, next_seq);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -409,10 +417,36 @@ static int dispatch_fmt(int fmt, const CUtensorMap& ta, const CUtensorMap& tb, c
 //   tile_expert / num_m_tiles_dev: grouped mode (both null for a plain GEMM)
 //   bn         32, 64 or 128 (tile width); the caller picks small tiles for small M
 // Returns 0 or a CUDA / driver error code.
+static int gemm_impl(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, int n_experts,
+                     void* c, int ldc, int out_f32, const float* bias, const float* row_scale, int act, float act_alpha,
+                     float act_limit, int M, int N, int K, const int* tile_expert, const int* num_m_tiles_dev, int bn,
+                     const mx::PeerOut* peer, cudaStream_t stream);
+
 MX_HOST_API int mx_gemm(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, int n_experts,
                         void* c, int ldc, int out_f32, const float* bias, const float* row_scale, int act, float act_alpha,
                         float act_limit, int M, int N, int K, const int* tile_expert, const int* num_m_tiles_dev, int bn,
                         cudaStream_t stream) {
+  return gemm_impl(a, wfmt, w0, w1, w2, w3, n_experts, c, ldc, out_f32, bias, row_scale, act, act_alpha, act_limit, M, N, K, tile_expert,
+                   num_m_tiles_dev, bn, nullptr, stream);
+}
+
+namespace mx { PeerOut make_peer_out(const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket); }
+
+// Row-parallel GEMM fused with the all-reduce: every tcgen05 output tile is stored (bf16 when out_kind == 0,
+// fp32 when 1) into slot [my_rank] of every rank's inbox straight from the epilogue registers; the last CTA
+// publishes the sequence number.  The consumer is mx_comm_rmsnorm_reduce / mx_comm_reduce.
+MX_HOST_API int mx_gemm_allreduce(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const float* bias,
+                                  int out_kind, int M, int N, int K, int bn, const void* const* inbox, int world, int my_rank,
+                                  long long slot_bytes, int* seq, int* ticket, cudaStream_t stream) {
+  if ((long long)M * N * (out_kind == 1 ? 4 : 2) > slot_bytes) return -140;
+  mx::PeerOut po = mx::make_peer_out(inbox, world, my_rank, slot_bytes, seq, ticket);
+  return gemm_impl(a, wfmt, w0, w1, w2, w3, 1, nullptr, N, out_kind, bias, nullptr, 0, 0.f, 0.f, M, N, K, nullptr, nullptr, bn, &po, stream);
+}
+
+static int gemm_impl(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, int n_experts,
+                     void* c, int ldc, int out_f32, const float* bias, const float* row_scale, int act, float act_alpha,
+                     float act_limit, int M, int N, int K, const int* tile_expert, const int* num_m_tiles_dev, int bn,
+                     const mx::PeerOut* peer, cudaStream_t stream) {
   using namespace mx;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (K % 8) return -101;
@@ -429,6 +463,7 @@ MX_HOST_API int mx_gemm(const void* a, int wfmt, const void* w0, const void* w1,
   p.C = c; p.ldc = ldc; p.out_f32 = out_f32;
   p.bias = bias; p.row_scale = row_scale;
   p.act = act; p.act_alpha = act_alpha; p.act_limit = act_limit;
+  if (peer) p.peer = *peer; else p.peer.world = 0;
   p.group_m = tile_expert ? 1 : 8;
   { const char* dbg = getenv("MX_GEMM_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
   { const char* g = getenv("MX_GEMM_GROUP"); if (g) p.group_m = atoi(g); }

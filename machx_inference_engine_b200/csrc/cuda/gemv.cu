@@ -13,6 +13,7 @@
 // gemv_mxfp4.cpp:94-323, gemv_fp16.cpp:64 and the batched-T verify kernels gemv_q8dot.cpp:391,499;
 // MoE decode pair moe_fused.cpp:101-541.
 #include "common.cuh"
+#include "comm.cuh"
 #include "dequant.cuh"
 #include "host_util.h"
 
@@ -34,6 +35,7 @@ struct GemvParams {
   int out_f32;
   int act;                  // 0 none, 1 swiglu, 2 swiglu_oai, 3 geglu (16-row interleaved gate/up)
   float act_alpha, act_limit;
+  PeerOut peer;             // world > 0: fp32 partials go to every rank's inbox instead of y (fused all-reduce)
 };
 
 __device__ __forceinline__ float gemv_act(int act, float g, float u, float alpha, float limit) {
@@ -51,7 +53,8 @@ template <int FMT, int MM>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = (blockIdx.x * GEMV_WARPS + warp) * GEMV_ROWS;
-  if (n0 >= p.N) return;
+  const int next_seq = p.peer.world ? *p.peer.seq + 1 : 0;
+  if (n0 < p.N) {
   const int slot = blockIdx.y;
   WeightRef w = p.w;
   const __nv_bfloat16* x = p.x;
@@ -134,7 +137,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams 
 #pragma unroll
     for (int m = 0; m < MM; ++m) acc[r][m] = warp_sum(acc[r][m]);
 
-  if (lane != 0) return;
+  if (lane == 0) {
   const float oscale = p.slot_scale ? p.slot_scale[slot] : 1.f;
   const int rows_out = p.slot_expert ? 1 : p.M;
 #pragma unroll
@@ -144,11 +147,17 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams 
     if (p.act == 0) {
       for (int r = 0; r < GEMV_ROWS && n0 + r < p.N; ++r) {
         const float v = (acc[r][m] + (bias ? bias[n0 + r] : 0.f)) * oscale;
-        if (p.out_f32) ((float*)p.y)[orow * p.N + n0 + r] = v;
+        if (p.peer.world) {
+          // fused all-reduce: the partial goes to slot [my_rank] of every rank's inbox
+          for (int d = 0; d < p.peer.world; ++d) reinterpret_cast<float*>(peer_slot(p.peer, d, next_seq))[orow * p.N + n0 + r] = v;
+        } else if (p.out_f32) ((float*)p.y)[orow * p.N + n0 + r] = v;
         else ((__nv_bfloat16*)p.y)[orow * p.N + n0 + r] = __float2bfloat16(v);
       }
     }
   }
+  }
+  }
+  if (p.peer.world) peer_publish(p.peer, next_seq);
 }
 
 // Gated variant: a warp owns output features f0..f0+3 and reads the matching gate rows
@@ -234,9 +243,30 @@ static int launch_gemv(const GemvParams& p, int slots, cudaStream_t st) {
 // Dense: y[M][N] from x[M][K], M <= 8.   Expert: y[slots][N] with slot_expert != null.
 // With act != 0 the weight holds interleaved gate/up rows (N = 2F) and y is [rows][F]; in that
 // mode every activation row is a "slot" (dense callers pass slots = M and slot_expert = null).
+static int gemv_impl(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const void* x, void* y,
+                     const float* bias, int M, int N, int K, int out_f32, int act, float act_alpha, float act_limit,
+                     const int* slot_expert, const float* slot_scale, int slots, int x_div, const mx::PeerOut* peer, cudaStream_t stream);
+
 MX_HOST_API int mx_gemv(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const void* x, void* y,
                         const float* bias, int M, int N, int K, int out_f32, int act, float act_alpha, float act_limit,
                         const int* slot_expert, const float* slot_scale, int slots, int x_div, cudaStream_t stream) {
+  return gemv_impl(wfmt, w0, w1, w2, w3, x, y, bias, M, N, K, out_f32, act, act_alpha, act_limit, slot_expert, slot_scale, slots, x_div, nullptr, stream);
+}
+
+namespace mx { PeerOut make_peer_out(const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket); }
+
+// Row-parallel GEMV fused with the all-reduce: fp32 partials [M][N] land in every rank's inbox (see comm.cuh).
+MX_HOST_API int mx_gemv_allreduce(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const void* x, const float* bias, int M,
+                                  int N, int K, const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket,
+                                  cudaStream_t stream) {
+  if ((long long)M * N * 4 > slot_bytes) return -140;
+  mx::PeerOut po = mx::make_peer_out(inbox, world, my_rank, slot_bytes, seq, ticket);
+  return gemv_impl(wfmt, w0, w1, w2, w3, x, nullptr, bias, M, N, K, 1, 0, 0.f, 0.f, nullptr, nullptr, 0, 1, &po, stream);
+}
+
+static int gemv_impl(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const void* x, void* y,
+                     const float* bias, int M, int N, int K, int out_f32, int act, float act_alpha, float act_limit,
+                     const int* slot_expert, const float* slot_scale, int slots, int x_div, const mx::PeerOut* peer, cudaStream_t stream) {
   using namespace mx;
   if (N <= 0 || K <= 0) return 0;
   if (K % 32 && !(wfmt == WF_BF16 && K % 8 == 0 && act == 0)) return -102;
@@ -248,6 +278,7 @@ MX_HOST_API int mx_gemv(int wfmt, const void* w0, const void* w1, const void* w2
   p.slot_expert = slot_expert; p.slot_scale = slot_scale; p.x_div = x_div > 0 ? x_div : 1;
   p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;
   p.act = act; p.act_alpha = act_alpha; p.act_limit = act_limit;
+  if (peer) p.peer = *peer; else p.peer.world = 0;
   const int ns = (slot_expert || act != 0) ? (slots > 0 ? slots : M) : 1;
   switch (wfmt) {
     case WF_BF16: return launch_gemv<WF_BF16>(p, ns, stream);

@@ -94,10 +94,11 @@ class Linear:
 
     def __call__(self, x: torch.Tensor, par: Optional[ParallelCtx] = None, out_f32: bool = False) -> torch.Tensor:
         if self.reduce and par is not None and par.enabled:
+            # the bias of a row-parallel layer is added once, after the reduction
             if par.fused is not None and x.is_cuda:
                 return par.fused.linear_all_reduce(x, self.w, self.bias)
-            y = ops.linear(x, self.w, bias=self.bias, out_f32=True)
-            return par.all_reduce(y)
+            y = par.all_reduce(ops.linear(x, self.w, out_f32=True))
+            return y if self.bias is None else y + self.bias
         return ops.linear(x, self.w, bias=self.bias, act=self.act, act_alpha=self.act_alpha, act_limit=self.act_limit, out_f32=out_f32)
 
 
@@ -178,7 +179,6 @@ class AttentionBlock:
         bo = src.vector(f"{p}.attn_output.bias", H) if (c.arch == "gpt-oss" and src.has(f"{p}.attn_output.bias")) else None
         if tp > 1:
             wo = wo.slice_k(q_lo * hd, (q_lo + self.n_q) * hd)
-            bo = bo if par.rank == 0 else None              # added once, before the reduction
         self.o = Linear(wo, bo, reduce=tp > 1)
         qk_norm = c.arch in ("qwen3", "qwen3moe", "qwen3next", "qwen35", "qwen35moe") and src.has(f"{p}.attn_q_norm.weight")
         self.q_norm = src.vector(f"{p}.attn_q_norm.weight", hd) if qk_norm else None
@@ -315,7 +315,7 @@ class MoEFFN:
             y = ops.grouped_linear(a, self.down, te, pk.num_tiles, bias=self.down_bias)
             out = ops.moe_combine(y, pk, w)
         if self.reduce:
-            out = par.all_reduce(out)
+            out = par.fused.push(out) if (par.fused is not None and out.is_cuda) else par.all_reduce(out)
         return out
 
 
@@ -387,15 +387,15 @@ class TransformerModel:
         delta = None
         rs = c.residual_scale
         for li, L in enumerate(self.layers):
-            h = ops.rmsnorm(x, L["attn_norm"], c.rms_eps, delta=delta, one_plus_w=self.one_plus_w, delta_scale=rs)
+            h = self._norm(x, L["attn_norm"], delta)
             a = self._mixer(li, L, h, fb, kv, state)
-            h2 = ops.rmsnorm(x, L["ffn_norm"], c.rms_eps, delta=a, one_plus_w=self.one_plus_w, delta_scale=rs)
+            h2 = self._norm(x, L["ffn_norm"], a)
             delta = L["moe"](h2, par) if "moe" in L else L["ffn"](h2, par)
             if "shexp" in L:
                 delta = L["shexp"](h2, delta, par)
         rows = fb.logit_rows if fb.logit_rows is not None else (fb.cu_q[1:].long() - 1)
         xr = x.index_select(0, rows)
-        dr = delta.index_select(0, rows).contiguous()
+        dr = delta.index_select(0, rows).contiguous()        # (a pending fused reduction is summed here)
         hidden = None
         if fb.want_hidden:
             hidden = xr + dr.to(torch.float32) * rs
@@ -408,6 +408,13 @@ class TransformerModel:
         if c.final_logit_softcap > 0:
             logits = torch.tanh(logits / c.final_logit_softcap) * c.final_logit_softcap
         return (logits, hidden) if fb.want_hidden else logits
+
+    def _norm(self, x, w, delta):
+        """Residual add + RMSNorm; a delta that still lives as per-rank partials in the collective inbox is summed here."""
+        c = self.cfg
+        if delta is not None and not isinstance(delta, torch.Tensor):
+            return self.par.fused.rmsnorm(x, w, c.rms_eps, delta, one_plus_w=self.one_plus_w, delta_scale=c.residual_scale)
+        return ops.rmsnorm(x, w, c.rms_eps, delta=delta, one_plus_w=self.one_plus_w, delta_scale=c.residual_scale)
 
     def _mixer(self, li, L, h, fb, kv, state):
         return L["attn"](h, fb, kv, self.rope, self.par)

@@ -1,0 +1,146 @@
+"""Peer-memory collectives fused into their producer and consumer kernels (product path for TP/EP).
+
+``FusedComm`` owns this rank's inbox (CUDA IPC allocation mapped by every peer over NVLink) and the
+peers' mappings.  A row-parallel projection is launched through :meth:`linear_all_reduce`: its GEMV
+(decode) or tcgen05 GEMM (prefill) epilogue stores the partial tile directly into every rank's inbox
+and the kernel's last CTA publishes a sequence number; nothing is written locally and no collective
+kernel runs.  The returned :class:`ReducedDelta` is consumed by ``ops.rmsnorm`` (the residual add +
+RMSNorm that follows every such projection), which waits for the peers' sequence numbers and sums
+the partials in rank order, or by :meth:`ReducedDelta.materialize`.
+
+The plain NCCL path (``ParallelCtx.all_reduce``) stays available as the measured baseline.
+Layout, ordering and the safety argument for the two-parity slot reuse are in ``csrc/cuda/comm.cuh``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+from ..ops import cuda as K
+from ..ops.weights import QuantWeight
+
+_vp = C.c_void_p
+
+
+@dataclass
+class ReducedDelta:
+    """A tensor [T, H] that exists as W partials in this rank's inbox until a consumer sums them."""
+    comm: "FusedComm"
+    T: int
+    H: int
+    bf16: bool
+    bias: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return (self.T, self.H)
+
+    def materialize(self) -> torch.Tensor:
+        return self.comm.reduce(self)
+
+    def index_select(self, dim: int, rows: torch.Tensor) -> torch.Tensor:
+        assert dim == 0
+        return self.materialize().index_select(0, rows)
+
+
+class FusedComm:
+    def __init__(self, par, device, slot_bytes: int):
+        self.par, self.device, self.world, self.rank = par, device, par.world, par.rank
+        self.slot_bytes = int(slot_bytes)
+        lib = _lib.cuda()
+        lib.mx_ipc_import.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+        total = 2 * self.world * self.slot_bytes + 4096
+        lib.mx_raw_alloc.restype = C.c_void_p
+        lib.mx_raw_alloc.argtypes = [C.c_longlong]
+        self._base = lib.mx_raw_alloc(total)          # dedicated cudaMalloc allocation, zero-filled
+        if not self._base:
+            raise MemoryError(f"cannot allocate the {total >> 20} MiB collective inbox")
+        h = C.create_string_buffer(64)
+        rc = lib.mx_ipc_export(_vp(self._base), h)
+        if rc != 0:
+            raise RuntimeError(f"cudaIpcGetMemHandle failed ({rc})")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (bytes(h.raw), 0), group=par.group)
+        self.peer_ptrs = []
+        self._opened = []
+        for r, (hb, off) in enumerate(handles):
+            if r == self.rank:
+                self.peer_ptrs.append(self._base)
+                continue
+            out = C.c_void_p()
+            rc = lib.mx_ipc_import(hb, C.byref(out))
+            if rc != 0:
+                raise RuntimeError(f"cudaIpcOpenMemHandle from rank {r} failed ({rc})")
+            self._opened.append(out.value)
+            self.peer_ptrs.append(out.value + off)
+        self._ptr_array = (C.c_void_p * self.world)(*self.peer_ptrs)
+        self.seq = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        par.barrier()
+
+    @classmethod
+    def create(cls, par, device, max_tokens: int = 4096, max_width: int = 8192) -> "FusedComm":
+        """Slots hold one [max_tokens, max_width] fp32 tensor (bf16 GEMM partials use half of it)."""
+        return cls(par, device, slot_bytes=max_tokens * max_width * 4)
+
+    # ---- producers -----------------------------------------------------------------------
+    def linear_all_reduce(self, x: torch.Tensor, w: QuantWeight, bias: Optional[torch.Tensor]) -> ReducedDelta:
+        M = x.shape[0]
+        fmt, p0, p1, p2, p3 = K._planes(w)
+        lib = _lib.cuda()
+        st = K._stream()
+        # the bias of a row-parallel layer is added once, by the consumer (rank 0 carries it)
+        if M <= K.GEMV_MAX_M:
+            K._check(lib.mx_gemv_allreduce(fmt, p0, p1, p2, p3, K._p(x), _vp(0), M, w.N, w.K, self._ptr_array, self.world, self.rank,
+                                           C.c_longlong(self.slot_bytes), K._p(self.seq), K._p(self.ticket), st), "gemv_allreduce")
+            bf16 = False
+        else:
+            bf16 = True
+            if M * w.N * 2 > self.slot_bytes:
+                raise ValueError(f"fused all-reduce slot too small for [{M},{w.N}]")
+            K._check(lib.mx_gemm_allreduce(K._p(x), fmt, p0, p1, p2, p3, _vp(0), 0, M, w.N, w.K, K._pick_bn(M, w.N), self._ptr_array, self.world,
+                                           self.rank, C.c_longlong(self.slot_bytes), K._p(self.seq), K._p(self.ticket), st), "gemm_allreduce")
+        K._count()
+        return ReducedDelta(self, M, w.N, bf16, bias)
+
+    def push(self, t: torch.Tensor) -> ReducedDelta:
+        """All-reduce of an existing tensor (fp32 or bf16, contiguous): push now, sum in the consumer."""
+        assert t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16)
+        nbytes = t.numel() * t.element_size()
+        K._check(_lib.cuda().mx_comm_push(K._p(t), C.c_longlong(nbytes), self._ptr_array, self.world, self.rank, C.c_longlong(self.slot_bytes),
+                                          K._p(self.seq), K._p(self.ticket), K._stream()), "comm_push")
+        K._count()
+        return ReducedDelta(self, t.shape[0], t.shape[1], t.dtype == torch.bfloat16)
+
+    # ---- consumers -----------------------------------------------------------------------
+    def reduce(self, d: ReducedDelta) -> torch.Tensor:
+        out = torch.empty(d.T, d.H, dtype=torch.float32, device=self.device)
+        K._check(_lib.cuda().mx_comm_reduce(_vp(self.peer_ptrs[self.rank]), self.world, C.c_longlong(self.slot_bytes), K._p(self.seq), int(d.bf16),
+                                            K._p(d.bias), K._p(out), C.c_longlong(d.T * d.H), d.H, K._stream()), "comm_reduce")
+        K._count()
+        return out
+
+    def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, d: ReducedDelta, one_plus_w: bool = False, delta_scale: float = 1.0,
+                want_out: bool = True) -> Optional[torch.Tensor]:
+        T, H = x.shape
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if want_out else None
+        K._check(_lib.cuda().mx_comm_rmsnorm_reduce(K._p(x), _vp(self.peer_ptrs[self.rank]), self.world, C.c_longlong(self.slot_bytes), K._p(self.seq),
+                                                    int(d.bf16), K._p(d.bias), K._p(w), K._p(out), C.c_float(eps), T, H, int(one_plus_w),
+                                                    C.c_float(delta_scale), K._stream()), "comm_rmsnorm_reduce")
+        K._count()
+        return out
+
+    def close(self) -> None:
+        lib = _lib.cuda()
+        for p in self._opened:
+            lib.mx_ipc_release(_vp(p))
+        self._opened = []
+        if self._base:
+            lib.mx_raw_free(_vp(self._base))
+            self._base = None

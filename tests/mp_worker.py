@@ -1,0 +1,64 @@
+"""Worker for the multi-process tests (launched with torch.distributed.run; gloo on CPU, NCCL on GPUs).
+
+Prints one JSON line on rank 0: greedy tokens of a tiny model under tensor/expert parallelism, so the
+parent test can compare them with the single-process run (the reference's multi_gpu_tp_test asks for
+identical greedy tokens: tools/multi_gpu_tp_test.cpp).
+"""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+from machx_inference_engine_b200.formats.model_config import preset
+from machx_inference_engine_b200.models import build_model
+from machx_inference_engine_b200.parallel.comm import init_from_env
+from machx_inference_engine_b200.runtime.engine import EngineOptions, LLMEngine, SamplingParams
+
+
+def main():
+    name, quant, device, comm = sys.argv[1], sys.argv[2], sys.argv[3], sys.argv[4]
+    par = init_from_env("cuda" if device == "cuda" else "cpu", timeout_s=120)
+    if device == "cuda":
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        if comm == "fused" and par.world > 1:
+            from machx_inference_engine_b200.parallel.fused import FusedComm
+            par.fused = FusedComm.create(par, dev, max_tokens=1024, max_width=4096)
+    else:
+        dev = torch.device("cpu")
+    cfg = preset(name)
+    model = build_model(cfg, dev, par, quant=quant, max_ctx=1024, gen_device="cpu")
+    eng = LLMEngine(model, EngineOptions(max_ctx=1024, max_batch_tokens=512, max_seqs=4))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (37, 260, 9)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=10))
+    # teacher-forced logits of every position of one prompt: prefill chunk, then single-token steps (the decode kernels)
+    from machx_inference_engine_b200.models.transformer import KV_BLOCK, ForwardBatch
+    ids = prompts[1]
+    kv = model.new_kv_cache(6)
+    bt = torch.arange(1, 5, dtype=torch.int32, device=dev).unsqueeze(0)
+
+    def fwd(lo, hi):
+        pos = torch.arange(lo, hi, dtype=torch.int32, device=dev)
+        slot = bt[0][(pos // KV_BLOCK).long()].long() * KV_BLOCK + (pos % KV_BLOCK).long()
+        fb = ForwardBatch(torch.tensor(ids[lo:hi], dtype=torch.int32, device=dev), pos, slot, bt, torch.tensor([hi], dtype=torch.int32, device=dev),
+                          torch.tensor([0, hi - lo], dtype=torch.int32, device=dev), hi - lo, logit_rows=torch.arange(hi - lo, device=dev))
+        return model.forward(fb, kv).float().cpu()
+    logits = torch.cat([fwd(0, 200)] + [fwd(i, i + 1) for i in range(200, 208)])
+    if par.rank == 0 and len(sys.argv) > 5:
+        torch.save(logits, sys.argv[5])
+    if device == "cuda":
+        from machx_inference_engine_b200.ops import cuda as K
+        K.check_status()
+    if par.rank == 0:
+        print("RESULT " + json.dumps({"world": par.world, "tokens": outs}))
+    if par.world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
