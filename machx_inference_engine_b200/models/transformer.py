@@ -178,7 +178,7 @@ class AttentionBlock:
         wo = src.matrix(f"{p}.attn_output.weight", H, c.n_heads * hd)
         bo = src.vector(f"{p}.attn_output.bias", H) if (c.arch == "gpt-oss" and src.has(f"{p}.attn_output.bias")) else None
         if tp > 1:
-            wo = wo.slice_k(q_lo * hd, (q_lo + self.n_q) * hd)
+            wo = wo.slice_k(q_lo * hd, (q_lo + self.n_q) * hd, requant=True)
         self.o = Linear(wo, bo, reduce=tp > 1)
         qk_norm = c.arch in ("qwen3", "qwen3moe", "qwen3next", "qwen35", "qwen35moe") and src.has(f"{p}.attn_q_norm.weight")
         self.q_norm = src.vector(f"{p}.attn_q_norm.weight", hd) if qk_norm else None
@@ -220,8 +220,10 @@ class DenseFFN:
         d = src.matrix(f"{p}.ffn_down{suffix}.weight", H, F)
         if tp > 1:
             gran = max(d.k_granule(), 16)
+            if F % gran or (F // gran) < tp:
+                gran = 32 if F % 32 == 0 else 16          # finer than the weight's blocks: the shard is re-encoded
             lo, hi = _even_chunks(F, tp, gran)[par.rank]
-            g, u, d = g.slice_rows(lo, hi), u.slice_rows(lo, hi), d.slice_k(lo, hi)
+            g, u, d = g.slice_rows(lo, hi), u.slice_rows(lo, hi), d.slice_k(lo, hi, requant=True)
         if g.fmt == u.fmt:
             self.gate_up = Linear(QuantWeight.interleave_gate_up(g, u), act=act)
             self.split = None

@@ -112,11 +112,16 @@ class QuantWeight:
     def k_granule(self) -> int:
         return {WFormat.BF16: 8, WFormat.Q8: 32, WFormat.Q4K: 256, WFormat.Q6K: 256, WFormat.MXFP4: 32}[self.fmt]
 
-    def slice_k(self, lo: int, hi: int) -> "QuantWeight":
-        """Input-dimension slice [lo, hi) (row-parallel shards); bounds must sit on block boundaries."""
+    def slice_k(self, lo: int, hi: int, requant: bool = False) -> "QuantWeight":
+        """Input-dimension slice [lo, hi) (row-parallel shards).  Bounds must sit on block boundaries; with
+        ``requant`` a slice that cuts a block is re-encoded instead (Q8 when the slice is a multiple of 32 wide,
+        else bf16) -- the case of a 256-element super-block format sharded finer than its blocks."""
         g = self.k_granule()
         if lo % g or hi % g:
-            raise ValueError(f"K slice [{lo},{hi}) is not aligned to the {g}-element blocks of {self.fmt.name}")
+            if not requant:
+                raise ValueError(f"K slice [{lo},{hi}) is not aligned to the {g}-element blocks of {self.fmt.name}")
+            dense = self.dequantize(torch.float32)[:, :, lo:hi].contiguous()
+            return from_dense(dense, WFormat.Q8 if (hi - lo) % 32 == 0 else WFormat.BF16)
         per_elem = {
             WFormat.BF16: (1, None, None, None), WFormat.Q8: (1, 32, None, None), WFormat.Q4K: (256 / 144, None, None, None),
             WFormat.Q6K: (2, 4, 16, 256), WFormat.MXFP4: (2, 32, None, None),

@@ -403,8 +403,11 @@ class LLMEngine:
         decode_only = all(n == 1 for _, n in plan) and len(sampled_rows) == len(plan)
         seqs = [plan[i][0] for i in sampled_rows]
         greedy = all(s.params.temperature <= 0 and s.params.repetition_penalty == 1.0 for s in seqs)
+        par = getattr(self.model, "par", None)
+        # graphs hold only this library's kernels: the NCCL baseline path (no fused collectives) runs eagerly
+        nccl_path = par is not None and par.enabled and par.fused is None
         use_graph = (decode_only and greedy and self.opts.cuda_graphs and self.device.type == "cuda" and self.state is None
-                     and len(plan) <= max(self.opts.graph_batch_sizes))
+                     and len(plan) <= max(self.opts.graph_batch_sizes) and not nccl_path)
         if use_graph:
             return self._run_graph(plan)
         host, max_q = self._build_batch(plan, sampled_rows)
