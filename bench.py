@@ -107,6 +107,12 @@ def main():
     from machx_inference_engine_b200.parallel.comm import init_from_env
     from machx_inference_engine_b200.runtime.engine import EngineOptions, LLMEngine, SamplingParams
 
+    t_start = time.time()
+
+    def note(msg):
+        if os.environ.get("MX_BENCH_VERBOSE"):
+            print(f"[bench +{time.time() - t_start:6.1f}s rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
     par = init_from_env("cuda")
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -117,6 +123,7 @@ def main():
         from machx_inference_engine_b200.parallel.fused import FusedComm
         par.fused = FusedComm.create(par, dev)
 
+    note("process group + comm ready")
     cfg = preset(args.model)
     quant = args.quant or ("mxfp4" if cfg.arch == "gpt-oss" else "q4_k_m" if cfg.arch == "llama" else "q8_0")
     P, D = args.prefill, args.decode
@@ -125,6 +132,7 @@ def main():
     model = build_model(cfg, dev, par, quant=quant, max_ctx=max_ctx, seed=0)
     torch.cuda.synchronize()
     build_s = time.time() - t0
+    note(f"model built in {build_s:.1f}s")
     eng = LLMEngine(model, EngineOptions(max_ctx=max_ctx, max_batch_tokens=max(P, 1), max_seqs=1, enable_prefix_cache=False))
 
     g = torch.Generator().manual_seed(1234)
@@ -150,7 +158,9 @@ def main():
 
     for i in range(args.warmup):
         prefill_once(i)
+        note(f"warmup prefill {i} done")
     barrier()
+    K.check_status()
     sampler = ClockSampler(local)
     sampler.start()
     l0 = K.launches()
@@ -162,6 +172,7 @@ def main():
     ev1.record()
     barrier()
     prefill_ms = reduce_max_ms(ev0.elapsed_time(ev1)) / args.steps
+    note(f"timed prefill done: {prefill_ms:.2f} ms/step")
     launches = K.launches() - l0
     clocks = sampler.stop()
 
@@ -173,6 +184,7 @@ def main():
         out = eng.generate([prompts[(args.warmup + i) % n_prompts]], SamplingParams(max_tokens=1))
     torch.cuda.synchronize()
     e2e_ms = reduce_max_ms((time.perf_counter() - w0) * 1e3) / args.steps
+    note("e2e prefill done")
     h2d = (eng.stats["h2d_bytes"] - h0) // args.steps
     d2h = (eng.stats["d2h_bytes"] - d0) // args.steps
 
@@ -181,6 +193,7 @@ def main():
     eng.step()
     for _ in range(4):
         eng.step()
+    note("decode warm-up done")
     barrier()
     ev0.record()
     w0 = time.perf_counter()
@@ -192,6 +205,7 @@ def main():
     torch.cuda.synchronize()
     dec_wall_ms = reduce_max_ms((time.perf_counter() - w0) * 1e3)
     dec_ms = reduce_max_ms(ev0.elapsed_time(ev1))
+    note("decode done")
     eng.abort(seq)
     K.check_status()
 
@@ -215,8 +229,13 @@ def main():
             "gpu_launches": int(launches), "clocks": clocks, "impl": "ours",
         }
         print(json.dumps(line))
+    sys.stdout.flush()
     if par.world > 1:
-        torch.distributed.destroy_process_group()
+        # all ranks are idle here; leave without running communicator / CUDA-graph destructors, whose teardown
+        # order across ranks is not defined (a captured NCCL all-gather made destroy_process_group wait for ever)
+        par.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
     return 0
 
 

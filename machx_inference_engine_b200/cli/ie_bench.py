@@ -118,8 +118,12 @@ def main(argv=None) -> int:
         print("# T_pp\tpp_ms\tpp_tok_s\ttg_ms_tok\ttg_tok_s\tpp_first_ms")
         for P, first, best, tgms in rows:
             print(f"{P}\t{best:.3f}\t{P / best * 1e3:.1f}\t{tgms:.3f}\t{(1e3 / tgms) if tgms > 0 else 0:.1f}\t{first:.3f}")
+    sys.stdout.flush()
     if par.world > 1:
-        torch.distributed.destroy_process_group()
+        par.barrier()
+        if cuda:
+            torch.cuda.synchronize()
+        os._exit(0)
     return 0
 
 
