@@ -31,6 +31,7 @@ struct GemvParams {
   const int* slot_expert;   // expert mode: [slots]
   const float* slot_scale;  // expert mode: optional per-slot multiplier on the output
   int x_div;                // expert mode: activation row = slot / x_div
+  int e_lo, e_hi;           // expert mode: experts owned by this rank (weights hold [e_lo, e_hi)); other slots yield zeros
   int M, N, K;
   int out_f32;
   int act;                  // 0 none, 1 swiglu, 2 swiglu_oai, 3 geglu (16-row interleaved gate/up)
@@ -59,11 +60,14 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams 
   WeightRef w = p.w;
   const __nv_bfloat16* x = p.x;
   const float* bias = p.bias;
+  bool owned = true;
   if (p.slot_expert) {
     const int e = p.slot_expert[slot];
-    w = expert_weight<FMT>(p.w, e, p.N, p.K);
+    owned = e >= p.e_lo && e < p.e_hi;
+    const int el = owned ? e - p.e_lo : 0;
+    w = expert_weight<FMT>(p.w, el, p.N, p.K);
     x += (size_t)(slot / p.x_div) * p.K;
-    if (bias) bias += (size_t)e * p.N;
+    if (bias) bias += (size_t)el * p.N;
   }
   float acc[GEMV_ROWS][MM];
 #pragma unroll
@@ -75,7 +79,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams 
 #pragma unroll
   for (int r = 0; r < GEMV_ROWS; ++r) rp[r] = row_ptrs<FMT>(w, min(n0 + r, p.N - 1), p.K);
 
-  const int nkb = p.K / 32;
+  const int nkb = owned ? p.K / 32 : 0;       // slots routed to another rank's expert contribute zeros
   for (int kb = lane; kb < nkb; kb += 32) {
     float wv[32];
     if (MM == 1) {
@@ -119,7 +123,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams 
       }
     }
   }
-  if (FMT == WF_BF16 && (p.K & 31)) {
+  if (FMT == WF_BF16 && (p.K & 31) && owned) {
     // ragged tail of a bf16 row (K % 32 != 0): one element per lane
     const int k = nkb * 32 + lane;
     if (k < p.K) {
@@ -146,7 +150,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams 
     const size_t orow = p.slot_expert ? (size_t)slot : (size_t)m;
     if (p.act == 0) {
       for (int r = 0; r < GEMV_ROWS && n0 + r < p.N; ++r) {
-        const float v = (acc[r][m] + (bias ? bias[n0 + r] : 0.f)) * oscale;
+        const float v = owned ? (acc[r][m] + (bias ? bias[n0 + r] : 0.f)) * oscale : 0.f;
         if (p.peer.world) {
           // fused all-reduce: the partial goes to slot [my_rank] of every rank's inbox
           for (int d = 0; d < p.peer.world; ++d) reinterpret_cast<float*>(peer_slot(p.peer, d, next_seq))[orow * p.N + n0 + r] = v;
@@ -172,10 +176,13 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_gated_kernel(const GemvP
   WeightRef w = p.w;
   const __nv_bfloat16* x = p.x + (size_t)(p.slot_expert ? slot / p.x_div : slot) * p.K;
   const float* bias = p.bias;
+  bool owned = true;
   if (p.slot_expert) {
     const int e = p.slot_expert[slot];
-    w = expert_weight<FMT>(p.w, e, p.N, p.K);
-    if (bias) bias += (size_t)e * p.N;
+    owned = e >= p.e_lo && e < p.e_hi;
+    const int el = owned ? e - p.e_lo : 0;
+    w = expert_weight<FMT>(p.w, el, p.N, p.K);
+    if (bias) bias += (size_t)el * p.N;
   }
   float ag[GEMV_ROWS], au[GEMV_ROWS];
   RowPtrs rg[GEMV_ROWS], ru[GEMV_ROWS];
@@ -188,7 +195,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_gated_kernel(const GemvP
     ru[r] = row_ptrs<FMT>(w, grow[r] + 16, p.K);
     ag[r] = au[r] = 0.f;
   }
-  const int nkb = p.K / 32;
+  const int nkb = owned ? p.K / 32 : 0;
   for (int kb = lane; kb < nkb; kb += 32) {
     float xv[32], wv[32];
     const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)kb * 32);
@@ -217,7 +224,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_gated_kernel(const GemvP
   if (lane != 0) return;
   for (int r = 0; r < GEMV_ROWS && f0 + r < F; ++r) {
     const float g = ag[r] + (bias ? bias[grow[r]] : 0.f), u = au[r] + (bias ? bias[grow[r] + 16] : 0.f);
-    const float v = gemv_act(p.act, g, u, p.act_alpha, p.act_limit);
+    const float v = owned ? gemv_act(p.act, g, u, p.act_alpha, p.act_limit) : 0.f;
     if (p.out_f32) ((float*)p.y)[(size_t)slot * F + f0 + r] = v;
     else ((__nv_bfloat16*)p.y)[(size_t)slot * F + f0 + r] = __float2bfloat16(v);
   }
@@ -253,6 +260,17 @@ MX_HOST_API int mx_gemv(int wfmt, const void* w0, const void* w1, const void* w2
   return gemv_impl(wfmt, w0, w1, w2, w3, x, y, bias, M, N, K, out_f32, act, act_alpha, act_limit, slot_expert, slot_scale, slots, x_div, nullptr, stream);
 }
 
+static int g_e_lo = 0, g_e_hi = 1 << 30;
+// Expert-parallel variant of the expert mode: the weight stack holds experts [e_lo, e_hi) only.
+MX_HOST_API int mx_gemv_experts(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const void* x, void* y,
+                                const float* bias, int N, int K, int out_f32, int act, float act_alpha, float act_limit,
+                                const int* slot_expert, const float* slot_scale, int slots, int x_div, int e_lo, int e_hi, cudaStream_t stream) {
+  g_e_lo = e_lo; g_e_hi = e_hi;
+  const int rc = gemv_impl(wfmt, w0, w1, w2, w3, x, y, bias, 1, N, K, out_f32, act, act_alpha, act_limit, slot_expert, slot_scale, slots, x_div, nullptr, stream);
+  g_e_lo = 0; g_e_hi = 1 << 30;
+  return rc;
+}
+
 namespace mx { PeerOut make_peer_out(const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket); }
 
 // Row-parallel GEMV fused with the all-reduce: fp32 partials [M][N] land in every rank's inbox (see comm.cuh).
@@ -276,6 +294,7 @@ static int gemv_impl(int wfmt, const void* w0, const void* w1, const void* w2, c
   p.w = WeightRef{w0, w1, w2, w3};
   p.x = (const __nv_bfloat16*)x; p.y = y; p.bias = bias;
   p.slot_expert = slot_expert; p.slot_scale = slot_scale; p.x_div = x_div > 0 ? x_div : 1;
+  p.e_lo = g_e_lo; p.e_hi = g_e_hi;
   p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;
   p.act = act; p.act_alpha = act_alpha; p.act_limit = act_limit;
   if (peer) p.peer = *peer; else p.peer.world = 0;

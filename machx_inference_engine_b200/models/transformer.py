@@ -298,11 +298,12 @@ class MoEFFN:
         logits = self.router(h, out_f32=True)
         idx, w = ops.moe_route(logits, self.router_bias, self.K, True)
         local = self.e_hi - self.e_lo
-        if T <= 8 and local == self.E:
-            # decode: one GEMV slot per (token, expert) pair, weights streamed once per pair
+        if T <= 8:
+            # decode: one GEMV slot per (token, expert) pair, weights streamed once per pair; under expert
+            # parallelism the slots of experts that live on other ranks contribute zero rows here
             slot_e = idx.reshape(-1)
-            a = ops.expert_gemv(h, self.gate_up, slot_e, x_div=self.K, bias=self.gu_bias, act=self.act)
-            y = ops.expert_gemv(a, self.down, slot_e, x_div=1, bias=self.down_bias)
+            a = ops.expert_gemv(h, self.gate_up, slot_e, x_div=self.K, bias=self.gu_bias, act=self.act, e_lo=self.e_lo)
+            y = ops.expert_gemv(a, self.down, slot_e, x_div=1, bias=self.down_bias, e_lo=self.e_lo)
             key = (T, h.device)
             if key not in self._arange:
                 pk = ops.ref.MoePacking(None, None, torch.zeros(1, dtype=torch.int32, device=h.device),

@@ -204,13 +204,16 @@ def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=AC
     return out
 
 
-def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, slot_scale=None, out_f32=False):
+def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, slot_scale=None, out_f32=False,
+                e_lo=0):
+    """``w`` holds experts [e_lo, e_lo + w.E); slots routed to other experts produce zero rows (expert parallelism)."""
     S = slot_expert.numel()
     n_out = w.N // 2 if act != ACT_NONE else w.N
     out = torch.empty(S, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     fmt, p0, p1, p2, p3 = _planes(w)
-    _check(_lib.cuda().mx_gemv(fmt, p0, p1, p2, p3, _p(x), _p(out), _p(bias), 1, w.N, w.K, int(out_f32), act, C.c_float(act_alpha),
-                               C.c_float(act_limit), _p(slot_expert), _p(slot_scale), S, x_div, _stream()), "expert gemv")
+    _check(_lib.cuda().mx_gemv_experts(fmt, p0, p1, p2, p3, _p(x), _p(out), _p(bias), w.N, w.K, int(out_f32), act, C.c_float(act_alpha),
+                                       C.c_float(act_limit), _p(slot_expert), _p(slot_scale), S, x_div, int(e_lo), int(e_lo) + w.E, _stream()),
+           "expert gemv")
     _count()
     return out
 

@@ -101,18 +101,23 @@ def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=AC
     return out.to(out_dtype) if out_dtype is not None else (out if out_f32 else out.to(torch.bfloat16))
 
 
-def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, slot_scale=None, out_f32=False):
-    """y[s] = W[slot_expert[s]] @ x[s // x_div]."""
+def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, slot_scale=None, out_f32=False,
+                e_lo=0):
+    """y[s] = W[slot_expert[s] - e_lo] @ x[s // x_div]; slots whose expert lies outside [e_lo, e_lo + E) give zero rows."""
     W = _dense(w)
     S = slot_expert.numel()
     rows = torch.arange(S, device=x.device) // x_div
     xe = x.to(torch.float32)[rows]
-    y = torch.einsum("sk,snk->sn", xe, W[slot_expert.long()])
+    se = slot_expert.long() - e_lo
+    owned = (se >= 0) & (se < w.E)
+    se = se.clamp(0, w.E - 1)
+    y = torch.einsum("sk,snk->sn", xe, W[se])
     if bias is not None:
-        y = y + bias[slot_expert.long()]
+        y = y + bias[se]
     if act != ACT_NONE:
         g, u = _deinterleave16(y)
         y = _act(act, g, u, act_alpha, act_limit)
+    y = y * owned.unsqueeze(-1)
     if slot_scale is not None:
         y = y * slot_scale.unsqueeze(-1)
     return y if out_f32 else y.to(torch.bfloat16)
