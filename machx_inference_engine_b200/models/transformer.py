@@ -43,6 +43,7 @@ class ForwardBatch:
     max_q_len: int
     logit_rows: Optional[torch.Tensor] = None   # int64 rows of the T tokens that need logits (None: last of each sequence)
     state_slots: Optional[torch.Tensor] = None  # int32 [B] recurrent-state slot per sequence (hybrid models)
+    state_slots_host: Optional[list] = None     # host copy of state_slots
     q_lens_host: Optional[list] = None          # host copy of per-sequence query lengths (hybrid scan scheduling)
     start_host: Optional[list] = None           # host copy of per-sequence start positions (0 = fresh state)
     want_hidden: bool = False                   # also return the pre-final-norm hidden rows (MTP)
@@ -190,7 +191,7 @@ class AttentionBlock:
         self.window = c.layer_window(layer)
         self.scale = c.attention_scale if c.attention_scale > 0 else 1.0 / math.sqrt(hd)
         self.hd, self.n_rot, self.eps = hd, c.n_rot, c.rms_eps
-        self.norm_one_plus_w = c.arch in ("qwen3next", "qwen35", "qwen35moe")
+        self.norm_one_plus_w = c.arch in ("qwen35", "qwen35moe")      # Qwen3-Next files store 1 + w already
 
     def __call__(self, h: torch.Tensor, fb: ForwardBatch, kv: KVCache, rope, par: ParallelCtx) -> torch.Tensor:
         qkv = self.qkv(h)
@@ -290,6 +291,7 @@ class MoEFFN:
             self.down_bias = src.table(f"{p}.ffn_down_exps.bias", (E, H))[self.e_lo:self.e_hi].contiguous()
         self.act = act
         self.reduce = ep > 1
+        self.shared = None          # optional always-on expert (hybrid families): its partial joins the sum before the reduction
         self._arange = {}
 
     def __call__(self, h: torch.Tensor, par: ParallelCtx) -> torch.Tensor:
@@ -317,6 +319,8 @@ class MoEFFN:
             a = ops.grouped_linear(xp, self.gate_up, te, pk.num_tiles, bias=self.gu_bias, act=self.act)
             y = ops.grouped_linear(a, self.down, te, pk.num_tiles, bias=self.down_bias)
             out = ops.moe_combine(y, pk, w)
+        if self.shared is not None:
+            out = self.shared.add_into(out, h)
         if self.reduce:
             out = par.fused.push(out) if (par.fused is not None and out.is_cuda) else par.all_reduce(out)
         return out
@@ -349,7 +353,7 @@ class TransformerModel:
         ff = src.vector("rope_freqs.weight", c.n_rot // 2) if (c.arch == "llama" and getattr(src, "r", None) is not None and src.has("rope_freqs.weight")) else None
         self.rope = rope_tables(max_ctx, c.n_rot, c.rope_theta, ff, c.rope_scaling_type, c.rope_scaling_factor, c.rope_orig_ctx,
                                 c.yarn_beta_fast, c.yarn_beta_slow, device=self.device)
-        self.one_plus_w = c.arch in ("qwen3next", "qwen35", "qwen35moe")
+        self.one_plus_w = c.arch in ("qwen35", "qwen35moe")
         self.layers = []
         for l in range(c.n_layers):
             self.layers.append(self._build_layer(l, src))
@@ -394,8 +398,6 @@ class TransformerModel:
             a = self._mixer(li, L, h, fb, kv, state)
             h2 = self._norm(x, L["ffn_norm"], a)
             delta = L["moe"](h2, par) if "moe" in L else L["ffn"](h2, par)
-            if "shexp" in L:
-                delta = L["shexp"](h2, delta, par)
         rows = fb.logit_rows if fb.logit_rows is not None else (fb.cu_q[1:].long() - 1)
         xr = x.index_select(0, rows)
         dr = delta.index_select(0, rows).contiguous()        # (a pending fused reduction is summed here)

@@ -116,6 +116,38 @@ def gated_rmsnorm(x, z, w, eps):
     return y
 
 
+def gated_rmsnorm_heads(x, z, w, eps, hd):
+    T = x.shape[0]
+    n_h = x.shape[1] // hd
+    assert x.dtype == torch.float32 and x.is_contiguous() and z.dtype == torch.bfloat16 and z.stride(1) == 1
+    y = torch.empty(T, n_h * hd, dtype=torch.bfloat16, device=x.device)
+    _check(_lib.cuda().mx_gated_rmsnorm_ld(_p(x), _p(z), z.stride(0), _p(w), _p(y), T, n_h, hd, C.c_float(eps), _stream()), "gated_rmsnorm")
+    _count()
+    return y
+
+
+def conv1d_silu(x, w, state, state_slots, cu_q, max_q_len, ckpt=None):
+    T, Cc = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.dtype == torch.float32 and w.is_contiguous() and state.dtype == torch.bfloat16
+    y = torch.empty(T, Cc, dtype=torch.bfloat16, device=x.device)
+    _check(_lib.cuda().mx_conv1d_silu(_p(x), x.stride(0), Cc, w.shape[1], _p(w), _p(state), _p(state_slots), _p(cu_q), cu_q.numel() - 1, T,
+                                      int(max_q_len), _p(y), _p(ckpt), _stream()), "conv1d_silu")
+    _count(1 if max_q_len == 1 else 2)
+    return y
+
+
+def deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, state_slots, cu_q, n_v, eps=1e-6, ckpt=None):
+    T = qkv.shape[0]
+    D = 128
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and ab.dtype == torch.bfloat16 and ab.stride(1) == 1 and state.dtype == torch.float32
+    out = torch.empty(T, n_v * D, dtype=torch.float32, device=qkv.device)
+    _check(_lib.cuda().mx_deltanet_scan(_p(qkv), qkv.stride(0), 0, n_k * D, 2 * n_k * D, _p(ab), ab.stride(0), _p(a_idx), _p(b_idx), _p(k_of_v),
+                                        _p(ssm_a), _p(dt_bias), _p(state), _p(state_slots), _p(cu_q), cu_q.numel() - 1, n_v, D,
+                                        C.c_float(1.0 / math.sqrt(D)), C.c_float(eps), _p(out), _p(ckpt), _stream()), "deltanet_scan")
+    _count()
+    return out
+
+
 def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_map, k_cache, v_cache, n_q, n_kv, hd, n_rot,
              q_gate=False, norm_one_plus_w=False, eps=1e-6):
     T = qkv.shape[0]

@@ -221,6 +221,81 @@ def gated_rmsnorm(x, z, w, eps):
     return (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w * torch.nn.functional.silu(zz)).to(torch.bfloat16)
 
 
+def gated_rmsnorm_heads(x, z, w, eps, hd):
+    """x fp32 [T, n_h*hd]; z bf16 [T, n_h*hd] (any row stride); per-head y = w * x/rms(x) * silu(z) -> bf16 [T, n_h*hd]."""
+    T = x.shape[0]
+    xx = x.reshape(T, -1, hd)
+    zz = z.to(torch.float32).reshape(T, -1, hd)
+    y = xx * torch.rsqrt(xx.pow(2).mean(-1, keepdim=True) + eps) * w * torch.nn.functional.silu(zz)
+    return y.reshape(T, -1).to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------ gated DeltaNet
+def conv1d_silu(x, w, state, state_slots, cu_q, max_q_len, ckpt=None):
+    """Depthwise causal conv + SiLU over packed variable-length sequences.
+
+    x bf16 [T, C] (any row stride); w fp32 [C, Kc], tap j multiplies input t-(Kc-1)+j; state bf16 [slots, Kc-1, C]
+    holds the Kc-1 inputs before each sequence's next token and is advanced in place; ckpt (optional, bf16
+    [T, Kc-1, C]) receives the state as it stands after every position."""
+    T, C = x.shape
+    Kc = w.shape[1]
+    y = torch.empty(T, C, dtype=torch.bfloat16, device=x.device)
+    cu = cu_q.tolist()
+    for b in range(len(cu) - 1):
+        t0, t1 = cu[b], cu[b + 1]
+        if t1 <= t0:
+            continue
+        slot = int(state_slots[b])
+        full = torch.cat([state[slot].to(torch.float32), x[t0:t1].to(torch.float32)], dim=0)      # [Kc-1+n, C]
+        win = full.unfold(0, Kc, 1)                                                               # [n, C, Kc]
+        acc = (win * w.unsqueeze(0)).sum(-1)
+        y[t0:t1] = torch.nn.functional.silu(acc).to(torch.bfloat16)
+        if ckpt is not None:
+            for i in range(t1 - t0):
+                ckpt[t0 + i] = full[i + 1:i + Kc].to(torch.bfloat16)
+        state[slot] = full[-(Kc - 1):].to(torch.bfloat16)
+    return y
+
+
+def deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, state_slots, cu_q, n_v, eps=1e-6, ckpt=None):
+    """Gated delta rule over packed sequences.
+
+    qkv bf16 [T, (2 n_k + n_v) * 128] = conv output (q heads | k heads | v heads); ab bf16 [T, *] holds the alpha / beta
+    logits of v-head h in columns a_idx[h] / b_idx[h]; k_of_v[h] = k-head feeding v-head h.  Per token:
+    q, k L2-normalised (q also scaled by 1/sqrt(128)); g = ssm_a * softplus(alpha + dt_bias); beta = sigmoid(.);
+    S <- e^g S;  d = (v - S^T k) beta;  S <- S + k d^T;  out = S^T q.   state fp32 [slots, n_v, 128 (v), 128 (k)]
+    is advanced in place; ckpt (optional fp32 [T, n_v, 128, 128]) receives S after every position.  Returns fp32 [T, n_v*128]."""
+    T, D = qkv.shape[0], 128
+    x = qkv.to(torch.float32)
+    q = x[:, :n_k * D].reshape(T, n_k, D)
+    k = x[:, n_k * D:2 * n_k * D].reshape(T, n_k, D)
+    v = x[:, 2 * n_k * D:].reshape(T, n_v, D)
+    q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + eps) / math.sqrt(D)
+    k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + eps)
+    kv = k_of_v.long()
+    q, k = q[:, kv], k[:, kv]
+    abf = ab.to(torch.float32)
+    g = ssm_a * torch.nn.functional.softplus(abf[:, a_idx.long()] + dt_bias)
+    beta = torch.sigmoid(abf[:, b_idx.long()])
+    out = torch.empty(T, n_v, D, dtype=torch.float32, device=qkv.device)
+    cu = cu_q.tolist()
+    for b in range(len(cu) - 1):
+        t0, t1 = cu[b], cu[b + 1]
+        if t1 <= t0:
+            continue
+        slot = int(state_slots[b])
+        S = state[slot].clone()
+        for t in range(t0, t1):
+            S = S * torch.exp(g[t]).reshape(n_v, 1, 1)
+            d = (v[t] - torch.einsum("hvk,hk->hv", S, k[t])) * beta[t].unsqueeze(-1)
+            S = S + d.unsqueeze(-1) * k[t].unsqueeze(1)
+            out[t] = torch.einsum("hvk,hk->hv", S, q[t])
+            if ckpt is not None:
+                ckpt[t] = S
+        state[slot] = S
+    return out.reshape(T, n_v * D)
+
+
 # ------------------------------------------------------------------ MoE
 def moe_route(logits, bias, k, renorm=True):
     x = logits.to(torch.float32)

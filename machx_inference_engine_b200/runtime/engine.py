@@ -58,6 +58,7 @@ class Sequence:
     finished: bool = False
     finish_reason: str = ""
     state_slot: int = -1
+    h_last: Optional[torch.Tensor] = None      # hidden state of the last computed position (speculative decoding)
     t_arrival: float = 0.0
     t_first_token: float = 0.0
     on_token: Optional[Callable] = None
@@ -285,8 +286,10 @@ class LLMEngine:
         self._ids = itertools.count()
         self._graphs: dict = {}
         self._graph_pool = None
-        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "graph_replays": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "graph_replays": 0, "h2d_bytes": 0, "d2h_bytes": 0,
+                      "spec_rounds": 0, "spec_drafted": 0, "spec_accepted": 0}
         self.eos_ids = set(o.eos_ids)
+        self.spec_k = o.spec_k if (o.spec_k > 0 and getattr(model, "mtp", None) is not None and self.state is not None) else 0
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids: list, params: Optional[SamplingParams] = None, on_token: Optional[Callable] = None) -> Sequence:
@@ -318,6 +321,10 @@ class LLMEngine:
                 raise OutOfBlocks("a waiting request cannot be scheduled: KV pool too small for its prompt")
             return []
         sampled_rows = [i for i, (s, n) in enumerate(plan) if s.n_computed + n == len(s.tokens)]
+        if self.spec_k and len(plan) == 1 and plan[0][1] == 1 and sampled_rows and self._spec_ok(plan[0][0]):
+            done = self._spec_step(plan[0][0])
+            if done is not None:
+                return done
         tokens = self._run(plan, sampled_rows)
         out = []
         for (seq, n) in plan:
@@ -415,10 +422,16 @@ class LLMEngine:
         fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], max_q,
                           logit_rows=dev["logit_rows"] if sampled_rows else dev["cu_q"][1:2].long() - 1)
         if self.state is not None:
-            fb.state_slots = torch.tensor([s.state_slot for s, _ in plan], dtype=torch.int32, device=self.device)
+            fb.state_slots_host = [s.state_slot for s, _ in plan]
+            fb.state_slots = torch.tensor(fb.state_slots_host, dtype=torch.int32, device=self.device)
             fb.q_lens_host = [n for _, n in plan]
             fb.start_host = [s.n_computed for s, _ in plan]
+        fb.want_hidden = bool(self.spec_k) and bool(sampled_rows)
         logits = self.model.forward(fb, self.kv, self.state) if self.state is not None else self.model.forward(fb, self.kv)
+        if fb.want_hidden:
+            logits, hidden = logits
+            for r, s in enumerate(seqs):
+                s.h_last = hidden[r:r + 1]
         if not sampled_rows:
             return []
         toks = self._sample(logits, seqs)
@@ -441,6 +454,65 @@ class LLMEngine:
         t, k, p, m = self._sampling_tensors(seqs)
         rng = torch.tensor([_seed_state(s.params.seed, s.seq_id, s.n_generated) for s in seqs], dtype=torch.int64)
         return ops.sample(logits, t.to(dev), k.to(dev), p.to(dev), m.to(dev), rng.to(dev))
+
+    # ------------------------------------------------------------------ MTP self-speculative decode (greedy, lossless)
+    def _spec_ok(self, seq: Sequence) -> bool:
+        p = seq.params
+        return (p.temperature <= 0 and p.repetition_penalty == 1.0 and getattr(seq, "h_last", None) is not None
+                and len(seq.tokens) + self.spec_k + 1 < self.opts.max_ctx)
+
+    def _spec_step(self, seq: Sequence):
+        """One draft-verify round (src/model/qwen35_dense.cpp:1168-1264): the MTP head drafts K tokens after the pending
+        token, ONE target forward over [pending, drafts] in checkpoint mode verifies them, the longest agreeing prefix plus
+        the target's own next token are committed, and the recurrent state is rolled back to the last accepted position."""
+        K = self.spec_k
+        p0 = seq.n_computed
+        if not self.sched._ensure_blocks(seq, p0 + K + 1):
+            return None
+        drafts = self.model.mtp.draft(seq.h_last, seq.tokens[-1], K)
+        base = list(seq.tokens)
+        seq.tokens = base + drafts
+        try:
+            host, max_q = self._build_batch([(seq, K + 1)], [])
+        finally:
+            seq.tokens = base
+        host["logit_rows"] = torch.arange(K + 1, dtype=torch.int64)
+        dev = self._to_device(host)
+        fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], max_q,
+                          logit_rows=dev["logit_rows"], want_hidden=True)
+        fb.state_slots_host = [seq.state_slot]
+        fb.state_slots = torch.tensor(fb.state_slots_host, dtype=torch.int32, device=self.device)
+        fb.q_lens_host, fb.start_host = [K + 1], [p0]
+        logits, hidden = self.model.forward(fb, self.kv, self.state, checkpoint=True)
+        targ = ops.argmax(logits).cpu().tolist()
+        self.stats["d2h_bytes"] += 4 * (K + 1)
+        n = 0
+        while n < K and drafts[n] == targ[n]:
+            n += 1
+        accepted = n + 1                       # verified input rows kept: the pending token and n drafts
+        if accepted < K + 1:
+            self.state.commit(seq.state_slot, accepted - 1)
+        seq.h_last = hidden[accepted - 1:accepted].clone()
+        seq.n_computed = p0 + accepted
+        self.stats["spec_rounds"] += 1
+        self.stats["spec_drafted"] += K
+        self.stats["spec_accepted"] += n
+        out = []
+        for tok in drafts[:n] + [targ[n]]:
+            if seq.n_generated == 0:
+                seq.t_first_token = time.perf_counter()
+            seq.tokens.append(tok)
+            self._check_finish(seq, tok)
+            if seq.on_token is not None:
+                seq.on_token(seq, tok)
+            out.append((seq, tok, seq.finished))
+            self.stats["decode_tokens"] += 1
+            if seq.finished:
+                break
+        if seq.finished:
+            self.sched.finish(seq)
+        self.stats["steps"] += 1
+        return out
 
     # ------------------------------------------------------------------ CUDA-graphed greedy decode
     def _run_graph(self, plan: list) -> list:

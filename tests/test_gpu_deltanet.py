@@ -1,0 +1,120 @@
+"""Gated-DeltaNet kernels (conv1d+SiLU, delta-rule scan, per-head gated RMSNorm) and the hybrid graph against the
+PyTorch fp32 oracle; mirrors tests/unit/deltanet_test.cpp, conv1d_test.cpp and the chunking validator of the reference."""
+import pytest
+import torch
+
+from machx_inference_engine_b200.formats.model_config import preset
+from machx_inference_engine_b200.models import build_model
+from machx_inference_engine_b200.ops import ref
+from machx_inference_engine_b200.runtime.engine import EngineOptions, LLMEngine, SamplingParams
+
+pytestmark = pytest.mark.gpu
+
+
+def K():
+    from machx_inference_engine_b200.ops import cuda
+    return cuda
+
+
+D = torch.device("cuda:0")
+
+
+def rel_err(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+@pytest.mark.parametrize("lens,Kc", [([37], 4), ([1, 1, 1], 4), ([5, 1, 130, 2], 4), ([3, 2], 3)])
+def test_conv1d_silu(lens, Kc):
+    torch.manual_seed(0)
+    C, pad = 384, 40
+    T, B = sum(lens), len(lens)
+    xw = torch.randn(T, C + pad).to(torch.bfloat16)
+    w = torch.randn(C, Kc)
+    st = torch.randn(B + 2, Kc - 1, C).to(torch.bfloat16)
+    slots = torch.tensor([i + 1 for i in range(B)], dtype=torch.int32)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    ck_ref = torch.zeros(T, Kc - 1, C, dtype=torch.bfloat16)
+    st_ref = st.clone()
+    want = ref.conv1d_silu(xw[:, :C], w, st_ref, slots, cu, max(lens), ckpt=ck_ref)
+    st_g, ck_g = st.to(D), torch.zeros(T, Kc - 1, C, dtype=torch.bfloat16, device=D)
+    got = K().conv1d_silu(xw.to(D)[:, :C], w.to(D), st_g, slots.to(D), cu.to(D), max(lens), ckpt=ck_g)
+    assert rel_err(got, want) < 1e-2
+    assert torch.equal(st_g.cpu(), st_ref)
+    assert torch.equal(ck_g.cpu(), ck_ref)
+
+
+@pytest.mark.parametrize("lens", [[1], [1, 1, 1, 1], [19], [16, 33, 1], [300]])
+def test_deltanet_scan(lens):
+    torch.manual_seed(1)
+    n_k, n_v, Dh = 2, 4, 128
+    T, B = sum(lens), len(lens)
+    qkv = torch.randn(T, (2 * n_k + n_v) * Dh).to(torch.bfloat16)
+    ab = torch.randn(T, 2 * n_v + 8).to(torch.bfloat16)
+    b_idx = torch.tensor([0, 1, 4, 5], dtype=torch.int32)          # fused per-k-head [beta, beta, alpha, alpha] groups
+    a_idx = b_idx + 2
+    k_of_v = torch.tensor([0, 0, 1, 1], dtype=torch.int32)
+    ssm_a = -torch.rand(n_v) - 0.05
+    dtb = torch.randn(n_v) * 0.2
+    slots = torch.tensor(list(range(B, 0, -1)), dtype=torch.int32)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    S0 = torch.randn(B + 1, n_v, Dh, Dh) * 0.05
+    S_ref, ck_ref = S0.clone(), torch.zeros(T, n_v, Dh, Dh)
+    want = ref.deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dtb, S_ref, slots, cu, n_v, ckpt=ck_ref)
+    S_g = S0.to(D)
+    use_ck = T <= 64
+    ck_g = torch.zeros(T, n_v, Dh, Dh, device=D) if use_ck else None
+    got = K().deltanet_scan(qkv.to(D), n_k, ab.to(D), a_idx.to(D), b_idx.to(D), k_of_v.to(D), ssm_a.to(D), dtb.to(D), S_g, slots.to(D), cu.to(D),
+                            n_v, ckpt=ck_g)
+    assert rel_err(got, want) < 2e-3
+    assert rel_err(S_g, S_ref) < 2e-3
+    if use_ck:
+        assert rel_err(ck_g, ck_ref) < 2e-3
+
+
+def test_gated_rmsnorm_heads_strided_z():
+    torch.manual_seed(2)
+    T, n_h, hd = 9, 4, 128
+    x = torch.randn(T, n_h * hd)
+    zw = torch.randn(T, 100 + n_h * hd + 12).to(torch.bfloat16)
+    w = torch.rand(hd) + 0.5
+    want = ref.gated_rmsnorm_heads(x, zw[:, 100:100 + n_h * hd], w, 1e-6, hd)
+    got = K().gated_rmsnorm_heads(x.to(D), zw.to(D)[:, 100:100 + n_h * hd], w.to(D), 1e-6, hd)
+    assert rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("spec_k", [0, 3])
+def test_hybrid_model_matches_cpu_oracle(spec_k):
+    cfg = preset("tiny-qwen3next")
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (37, 150)]
+    outs = {}
+    for dev in ("cpu", "cuda:0"):
+        model = build_model(cfg, torch.device(dev), quant="q8_0", max_ctx=512, gen_device="cpu")
+        eng = LLMEngine(model, EngineOptions(max_ctx=512, max_batch_tokens=64, max_seqs=2, spec_k=spec_k if dev != "cpu" else 0))
+        outs[dev] = [eng.generate([p], SamplingParams(max_tokens=10, ignore_eos=True))[0] for p in prompts]
+    assert all(x[0] == y[0] for x, y in zip(outs["cpu"], outs["cuda:0"])), outs
+    same = sum(int(a == b) for x, y in zip(outs["cpu"], outs["cuda:0"]) for a, b in zip(x, y))
+    assert same >= 0.7 * sum(len(x) for x in outs["cpu"]), outs
+
+
+def test_hybrid_logits_cosine():
+    from machx_inference_engine_b200.models.transformer import KV_BLOCK, ForwardBatch
+    cfg = preset("tiny-qwen3next")
+    ids = torch.randint(0, cfg.vocab, (200,), generator=torch.Generator().manual_seed(1)).tolist()
+    res = {}
+    for dev in ("cpu", "cuda:0"):
+        d = torch.device(dev)
+        m = build_model(cfg, d, quant="q8_0", max_ctx=512, gen_device="cpu")
+        kv, st = m.new_kv_cache(6), m.new_state(2)
+        T = len(ids)
+        pos = torch.arange(T, dtype=torch.int32, device=d)
+        bt = torch.arange(1, 5, dtype=torch.int32, device=d).unsqueeze(0)
+        slot = bt[0][(pos // KV_BLOCK).long()].long() * KV_BLOCK + (pos % KV_BLOCK).long()
+        fb = ForwardBatch(torch.tensor(ids, dtype=torch.int32, device=d), pos, slot, bt, torch.tensor([T], dtype=torch.int32, device=d),
+                          torch.tensor([0, T], dtype=torch.int32, device=d), T, logit_rows=torch.arange(T, device=d),
+                          state_slots=torch.tensor([1], dtype=torch.int32, device=d), state_slots_host=[1], start_host=[0])
+        res[dev] = m.forward(fb, kv, st).float().cpu()
+    a, b = res["cpu"].flatten(), res["cuda:0"].flatten()
+    assert float(torch.dot(a, b) / (a.norm() * b.norm())) > 0.998
+    assert (res["cpu"].argmax(-1) == res["cuda:0"].argmax(-1)).float().mean() > 0.9
