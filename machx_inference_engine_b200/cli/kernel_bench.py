@@ -64,7 +64,7 @@ def main(argv=None):
     from ..ops.weights import WFormat, from_dense
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "moe_gemm", "gemv", "expert_gemv", "attention", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm", "moe_gemm", "gemv", "expert_gemv", "attention", "rmsnorm", "deltanet"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=2880)
@@ -161,6 +161,25 @@ def main(argv=None):
         w = torch.ones(a.k, device=dev)
         med, mn = timeit(lambda: K.rmsnorm(x, w, 1e-5, delta=d), a.iters)
         report(f"rmsnorm {a.m}x{a.k}", med, mn, bytes_=a.m * a.k * (4 + 4 + 2 + 2))
+    elif a.kernel == "deltanet":
+        # Qwen3-Next layer geometry by default: 16 k-heads, 32 v-heads of width 128, conv kernel 4
+        T, n_k, n_v, Dh = a.tokens, a.kv_heads * 2 if a.kv_heads != 8 else 16, a.heads if a.heads != 64 else 32, 128
+        Cc = (2 * n_k + n_v) * Dh
+        xin = torch.randn(T, Cc, device=dev).to(torch.bfloat16)
+        cw = torch.randn(Cc, 4, device=dev)
+        cst = torch.zeros(1, 3, Cc, dtype=torch.bfloat16, device=dev)
+        slots = torch.zeros(1, dtype=torch.int32, device=dev)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        med, mn = timeit(lambda: K.conv1d_silu(xin, cw, cst, slots, cu, T), a.iters)
+        report(f"conv1d_silu T={T} C={Cc}", med, mn, bytes_=2 * T * Cc * 2)
+        ab = torch.randn(T, 2 * n_v, device=dev).to(torch.bfloat16)
+        ai = torch.arange(n_v, dtype=torch.int32, device=dev)
+        kv = (ai // (n_v // n_k)).to(torch.int32)
+        sa, db = -torch.rand(n_v, device=dev) - 0.05, torch.zeros(n_v, device=dev)
+        S = torch.zeros(1, n_v, Dh, Dh, device=dev)
+        med, mn = timeit(lambda: K.deltanet_scan(xin, n_k, ab, ai, ai + n_v, kv, sa, db, S, slots, cu, n_v), a.iters)
+        report(f"deltanet_scan T={T} n_k={n_k} n_v={n_v}", med, mn, flops=6.0 * T * n_v * Dh * Dh, bytes_=T * Cc * 2 + T * n_v * Dh * 4,
+               extra={"us_per_token": round(med * 1e3 / T, 3)})
     K.check_status()
     return 0
 

@@ -172,22 +172,36 @@ __global__ void __launch_bounds__(128) deltanet_scan_kernel(ScanParams p) {
     }
     __syncthreads();
     if (tc + DN_CH < t1) scan_prefetch(p, st, tc + DN_CH, min(DN_CH, t1 - tc - DN_CH), h, kh, vs);
+    // The recurrence S -> S^T k -> delta -> S is one dependent chain per token, so its latency is what counts:
+    // next token's k is fetched before the chain starts, and each 32-term dot runs as four independent partial sums.
+    float4 kn[8];
+    {
+      const float4* kk = reinterpret_cast<const float4*>(&sk[0][kq * DN_KSTR]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) kn[j] = kk[j];
+    }
     for (int i = 0; i < n; ++i) {
-      const float4* kk = reinterpret_cast<const float4*>(&sk[i][kq * DN_KSTR]);
-      const float4* qq = reinterpret_cast<const float4*>(&sq[i][kq * DN_KSTR]);
       float4 k4[8];
-      float sk_ = 0.f, sq_ = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) k4[j] = kn[j];
+      if (i + 1 < n) {
+        const float4* kk = reinterpret_cast<const float4*>(&sk[i + 1][kq * DN_KSTR]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) kn[j] = kk[j];
+      }
+      const float4* qq = reinterpret_cast<const float4*>(&sq[i][kq * DN_KSTR]);
+      float ak[4] = {0.f, 0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        k4[j] = kk[j];
         const float4 q4 = qq[j];
-        sk_ = fmaf(S[4 * j], k4[j].x, sk_); sk_ = fmaf(S[4 * j + 1], k4[j].y, sk_);
-        sk_ = fmaf(S[4 * j + 2], k4[j].z, sk_); sk_ = fmaf(S[4 * j + 3], k4[j].w, sk_);
-        sq_ = fmaf(S[4 * j], q4.x, sq_); sq_ = fmaf(S[4 * j + 1], q4.y, sq_);
-        sq_ = fmaf(S[4 * j + 2], q4.z, sq_); sq_ = fmaf(S[4 * j + 3], q4.w, sq_);
+        ak[0] = fmaf(S[4 * j], k4[j].x, ak[0]); ak[1] = fmaf(S[4 * j + 1], k4[j].y, ak[1]);
+        ak[2] = fmaf(S[4 * j + 2], k4[j].z, ak[2]); ak[3] = fmaf(S[4 * j + 3], k4[j].w, ak[3]);
+        aq[0] = fmaf(S[4 * j], q4.x, aq[0]); aq[1] = fmaf(S[4 * j + 1], q4.y, aq[1]);
+        aq[2] = fmaf(S[4 * j + 2], q4.z, aq[2]); aq[3] = fmaf(S[4 * j + 3], q4.w, aq[3]);
       }
-      sk_ += __shfl_xor_sync(0xffffffffu, sk_, 1); sk_ += __shfl_xor_sync(0xffffffffu, sk_, 2);
-      sq_ += __shfl_xor_sync(0xffffffffu, sq_, 1); sq_ += __shfl_xor_sync(0xffffffffu, sq_, 2);
+      float sk_ = (ak[0] + ak[1]) + (ak[2] + ak[3]), sq_ = (aq[0] + aq[1]) + (aq[2] + aq[3]);
+      sk_ += __shfl_xor_sync(0xffffffffu, sk_, 1); sq_ += __shfl_xor_sync(0xffffffffu, sq_, 1);
+      sk_ += __shfl_xor_sync(0xffffffffu, sk_, 2); sq_ += __shfl_xor_sync(0xffffffffu, sq_, 2);
       const float decay = sdecay[i];
       const float delta = (sv[i][c] - decay * sk_) * sbeta[i];
 #pragma unroll

@@ -280,7 +280,7 @@ class LLMEngine:
         self.max_blocks_per_seq = blocks_per_seq
         self.kv = model.new_kv_cache(nb)
         n_state = o.max_seqs if getattr(model, "needs_state", False) else 0
-        self.state = model.new_state(n_state) if n_state else None
+        self.state = model.new_state(n_state + 1) if n_state else None      # the extra slot absorbs graph-padding rows
         self.bm = BlockManager(nb, o.enable_prefix_cache and not n_state)
         self.sched = Scheduler(o, self.bm, n_state)
         self._ids = itertools.count()
@@ -383,7 +383,12 @@ class LLMEngine:
             if len(t) > mb:
                 raise ContextLengthExceeded("sequence outgrew the block table")
             bt[r, :len(t)] = torch.tensor(t, dtype=torch.int32)
+        extra = {}
+        if self.state is not None:
+            pad_slot = self.state.n_slots - 1
+            extra["state_slots"] = torch.tensor([s.state_slot for s, _ in plan] + [pad_slot] * max(0, pad_to - B), dtype=torch.int32)
         host = {
+            **extra,
             "ids": torch.tensor(ids, dtype=torch.int32), "positions": torch.tensor(pos, dtype=torch.int32),
             "slot_map": torch.tensor(slots, dtype=torch.int64), "block_table": bt, "seq_lens": torch.tensor(lens, dtype=torch.int32),
             "cu_q": torch.tensor(cu, dtype=torch.int32), "logit_rows": torch.tensor(logit_rows, dtype=torch.int64),
@@ -413,8 +418,9 @@ class LLMEngine:
         par = getattr(self.model, "par", None)
         # graphs hold only this library's kernels: the NCCL baseline path (no fused collectives) runs eagerly
         nccl_path = par is not None and par.enabled and par.fused is None
-        use_graph = (decode_only and greedy and self.opts.cuda_graphs and self.device.type == "cuda" and self.state is None
-                     and len(plan) <= max(self.opts.graph_batch_sizes) and not nccl_path)
+        use_graph = (decode_only and greedy and self.opts.cuda_graphs and self.device.type == "cuda"
+                     and (self.state is None or all(s.n_computed > 0 for s, _ in plan))
+                     and len(plan) <= max(self.opts.graph_batch_sizes) and not nccl_path and not self.spec_k)
         if use_graph:
             return self._run_graph(plan)
         host, max_q = self._build_batch(plan, sampled_rows)
@@ -423,7 +429,7 @@ class LLMEngine:
                           logit_rows=dev["logit_rows"] if sampled_rows else dev["cu_q"][1:2].long() - 1)
         if self.state is not None:
             fb.state_slots_host = [s.state_slot for s, _ in plan]
-            fb.state_slots = torch.tensor(fb.state_slots_host, dtype=torch.int32, device=self.device)
+            fb.state_slots = dev["state_slots"]
             fb.q_lens_host = [n for _, n in plan]
             fb.start_host = [s.n_computed for s, _ in plan]
         fb.want_hidden = bool(self.spec_k) and bool(sampled_rows)
@@ -481,7 +487,7 @@ class LLMEngine:
         fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], max_q,
                           logit_rows=dev["logit_rows"], want_hidden=True)
         fb.state_slots_host = [seq.state_slot]
-        fb.state_slots = torch.tensor(fb.state_slots_host, dtype=torch.int32, device=self.device)
+        fb.state_slots = dev["state_slots"]
         fb.q_lens_host, fb.start_host = [K + 1], [p0]
         logits, hidden = self.model.forward(fb, self.kv, self.state, checkpoint=True)
         targ = ops.argmax(logits).cpu().tolist()
@@ -535,18 +541,27 @@ class LLMEngine:
     def _capture(self, gb: int, host: dict) -> dict:
         dev = {k: v.to(self.device) for k, v in host.items()}
         fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], 1,
-                          logit_rows=dev["logit_rows"])
+                          logit_rows=dev["logit_rows"], state_slots=dev.get("state_slots"))
+        fwd = (lambda: self.model.forward(fb, self.kv, self.state)) if self.state is not None else (lambda: self.model.forward(fb, self.kv))
+        snap = None
+        if self.state is not None:
+            # the warm-up and capture forwards advance the recurrent state of the slots in this batch: put it back afterwards
+            slots = sorted(set(host["state_slots"].tolist()))
+            snap = {sl: self.state.snapshot(sl) for sl in slots}
         # warm up on a side stream (allocator, lazy kernel attributes), then capture
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
             for _ in range(2):
-                ops.argmax(self.model.forward(fb, self.kv))
+                ops.argmax(fwd())
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, pool=self._graph_pool):
-            out = ops.argmax(self.model.forward(fb, self.kv))
+            out = ops.argmax(fwd())
+        if snap is not None:
+            for sl, sn in snap.items():
+                self.state.restore(sl, sn)
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
         return {"graph": graph, "in": dev, "out": out}
