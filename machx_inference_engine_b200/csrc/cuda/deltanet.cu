@@ -8,8 +8,8 @@
 //   gated_rmsnorm   : y = w * o / rms(o) * silu(z) per 128-wide head, z read in place from the projection output
 // Reference parity: src/ops/conv1d.cpp:28-117, src/ops/deltanet.cpp:41-480 (sequential recurrence with one work-group
 // per (batch, v-head) and one state column per lane).  Here the state is split by value columns so a 32-head layer
-// fills 128 CTAs, the per-token reductions stay inside 4 lanes, and the state lives transposed ([v][k]) so that
-// every thread loads and stores one contiguous 128-byte run.
+// fills 128 CTAs, the per-token reductions stay inside 8 lanes, and the state lives transposed ([v][k]) so that
+// every thread loads and stores one contiguous 64-byte run.
 #include "common.cuh"
 #include "host_util.h"
 
@@ -75,9 +75,12 @@ __global__ void conv1d_state_kernel(const bf16* __restrict__ x, int ld, int C, i
 // ------------------------------------------------------------------ gated delta rule scan
 constexpr int DN_D = 128;        // key and value head width
 constexpr int DN_VSPLIT = 4;     // CTAs per (sequence, v-head)
-constexpr int DN_VC = DN_D / DN_VSPLIT;
+constexpr int DN_VC = DN_D / DN_VSPLIT;   // value columns per CTA
+constexpr int DN_LANES = 8;      // lanes that share one value column (each keeps DN_KPT key rows of it in registers)
+constexpr int DN_KPT = DN_D / DN_LANES;
+constexpr int DN_THREADS = DN_VC * DN_LANES;
 constexpr int DN_CH = 16;        // tokens staged per chunk
-constexpr int DN_KSTR = 36;      // smem stride of one 32-float key quarter (padded: the four quarters hit different banks)
+constexpr int DN_KSTR = 20;      // smem stride of one 16-float key slice (padded: the eight slices of a column hit different banks)
 
 struct ScanParams {
   const bf16* qkv; int ld; int q_off, k_off, v_off;     // conv output [T, ld]
@@ -92,14 +95,15 @@ struct ScanParams {
 };
 
 struct ScanStage {     // one chunk of raw inputs held in registers while the previous chunk is being scanned
-  uint2 q[4], k[4], v; float a, b;
+  uint2 q[2], k[2]; uint32_t v; float a, b;
 };
 
+// 8 warps: warp w stages tokens 2w and 2w+1 (lane l holds key elements 4l..4l+3 of q and k)
 __device__ __forceinline__ void scan_prefetch(const ScanParams& p, ScanStage& s, int tc, int n, int h, int kh, int vs) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const int tok = warp * 4 + r;
+  for (int r = 0; r < 2; ++r) {
+    const int tok = warp * 2 + r;
     if (tok < n) {
       const bf16* row = p.qkv + (size_t)(tc + tok) * p.ld + kh * DN_D + lane * 4;
       s.q[r] = *reinterpret_cast<const uint2*>(row + p.q_off);
@@ -107,8 +111,8 @@ __device__ __forceinline__ void scan_prefetch(const ScanParams& p, ScanStage& s,
     }
   }
   {
-    const int tok = tid >> 3, c4 = (tid & 7) * 4;
-    if (tok < n) s.v = *reinterpret_cast<const uint2*>(p.qkv + (size_t)(tc + tok) * p.ld + p.v_off + h * DN_D + vs * DN_VC + c4);
+    const int tok = tid >> 4, c2 = (tid & 15) * 2;
+    if (tok < n) s.v = *reinterpret_cast<const uint32_t*>(p.qkv + (size_t)(tc + tok) * p.ld + p.v_off + h * DN_D + vs * DN_VC + c2);
   }
   if (tid < n) {
     s.a = __bfloat162float(p.ab[(size_t)(tc + tid) * p.ab_ld + p.a_idx[h]]);
@@ -116,22 +120,24 @@ __device__ __forceinline__ void scan_prefetch(const ScanParams& p, ScanStage& s,
   }
 }
 
-__global__ void __launch_bounds__(128) deltanet_scan_kernel(ScanParams p) {
+__device__ __forceinline__ int dn_koff(int k) { return (k >> 4) * DN_KSTR + (k & 15); }     // key element -> padded smem offset
+
+__global__ void __launch_bounds__(DN_THREADS) deltanet_scan_kernel(ScanParams p) {
   const int h = blockIdx.x / DN_VSPLIT, vs = blockIdx.x % DN_VSPLIT, b = blockIdx.y;
   const int t0 = p.cu_q[b], t1 = p.cu_q[b + 1];
   if (t1 <= t0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = tid >> 2, kq = tid & 3, col = vs * DN_VC + c;
+  const int c = tid / DN_LANES, kq = tid % DN_LANES, col = vs * DN_VC + c;
   const int kh = p.k_of_v[h];
-  __shared__ __align__(16) float sq[DN_CH][4 * DN_KSTR];
-  __shared__ __align__(16) float sk[DN_CH][4 * DN_KSTR];
+  __shared__ __align__(16) float sq[DN_CH][DN_LANES * DN_KSTR];
+  __shared__ __align__(16) float sk[DN_CH][DN_LANES * DN_KSTR];
   __shared__ float sv[DN_CH][DN_VC];
   __shared__ float sdecay[DN_CH], sbeta[DN_CH], sqk[DN_CH];
 
-  float S[32];
-  float* sp = p.state + (((size_t)p.slots[b] * p.n_v + h) * DN_D + col) * DN_D + kq * 32;
+  float S[DN_KPT];
+  float* sp = p.state + (((size_t)p.slots[b] * p.n_v + h) * DN_D + col) * DN_D + kq * DN_KPT;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < DN_KPT / 4; ++j) {
     const float4 v = reinterpret_cast<const float4*>(sp)[j];
     S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
   }
@@ -142,8 +148,8 @@ __global__ void __launch_bounds__(128) deltanet_scan_kernel(ScanParams p) {
     const int n = min(DN_CH, t1 - tc);
     __syncthreads();                       // the previous chunk's shared tiles are no longer read
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int tok = warp * 4 + r;
+    for (int r = 0; r < 2; ++r) {
+      const int tok = warp * 2 + r;
       if (tok < n) {                       // warp-uniform
         const float q0 = bf16_lo(st.q[r].x), q1 = bf16_hi(st.q[r].x), q2 = bf16_lo(st.q[r].y), q3 = bf16_hi(st.q[r].y);
         const float k0 = bf16_lo(st.k[r].x), k1 = bf16_hi(st.k[r].x), k2 = bf16_lo(st.k[r].y), k3 = bf16_hi(st.k[r].y);
@@ -151,18 +157,15 @@ __global__ void __launch_bounds__(128) deltanet_scan_kernel(ScanParams p) {
         const float ssk = warp_sum(k0 * k0 + k1 * k1 + k2 * k2 + k3 * k3);
         const float dqk = warp_sum(q0 * k0 + q1 * k1 + q2 * k2 + q3 * k3);
         const float iq = rsqrtf(ssq + p.eps) * p.q_scale, ik = rsqrtf(ssk + p.eps);
-        const int o = (lane >> 3) * DN_KSTR + (lane & 7) * 4;
+        const int o = dn_koff(lane * 4);
         *reinterpret_cast<float4*>(&sq[tok][o]) = make_float4(q0 * iq, q1 * iq, q2 * iq, q3 * iq);
         *reinterpret_cast<float4*>(&sk[tok][o]) = make_float4(k0 * ik, k1 * ik, k2 * ik, k3 * ik);
         if (lane == 0) sqk[tok] = dqk * iq * ik;
       }
     }
     {
-      const int tok = tid >> 3, c4 = (tid & 7) * 4;
-      if (tok < n) {
-        sv[tok][c4] = bf16_lo(st.v.x); sv[tok][c4 + 1] = bf16_hi(st.v.x);
-        sv[tok][c4 + 2] = bf16_lo(st.v.y); sv[tok][c4 + 3] = bf16_hi(st.v.y);
-      }
+      const int tok = tid >> 4, c2 = (tid & 15) * 2;
+      if (tok < n) { sv[tok][c2] = bf16_lo(st.v); sv[tok][c2 + 1] = bf16_hi(st.v); }
     }
     if (tid < n) {
       const float x = st.a + dtb;
@@ -172,27 +175,16 @@ __global__ void __launch_bounds__(128) deltanet_scan_kernel(ScanParams p) {
     }
     __syncthreads();
     if (tc + DN_CH < t1) scan_prefetch(p, st, tc + DN_CH, min(DN_CH, t1 - tc - DN_CH), h, kh, vs);
-    // The recurrence S -> S^T k -> delta -> S is one dependent chain per token, so its latency is what counts:
-    // next token's k is fetched before the chain starts, and each 32-term dot runs as four independent partial sums.
-    float4 kn[8];
-    {
-      const float4* kk = reinterpret_cast<const float4*>(&sk[0][kq * DN_KSTR]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) kn[j] = kk[j];
-    }
+    // The recurrence S -> S^T k -> delta -> S is one dependent chain per token: every 16-term dot runs as four
+    // independent partial sums, and two warps per scheduler interleave their chains.
     for (int i = 0; i < n; ++i) {
-      float4 k4[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) k4[j] = kn[j];
-      if (i + 1 < n) {
-        const float4* kk = reinterpret_cast<const float4*>(&sk[i + 1][kq * DN_KSTR]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) kn[j] = kk[j];
-      }
+      const float4* kk = reinterpret_cast<const float4*>(&sk[i][kq * DN_KSTR]);
       const float4* qq = reinterpret_cast<const float4*>(&sq[i][kq * DN_KSTR]);
+      float4 k4[DN_KPT / 4];
       float ak[4] = {0.f, 0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < DN_KPT / 4; ++j) {
+        k4[j] = kk[j];
         const float4 q4 = qq[j];
         ak[0] = fmaf(S[4 * j], k4[j].x, ak[0]); ak[1] = fmaf(S[4 * j + 1], k4[j].y, ak[1]);
         ak[2] = fmaf(S[4 * j + 2], k4[j].z, ak[2]); ak[3] = fmaf(S[4 * j + 3], k4[j].w, ak[3]);
@@ -200,25 +192,28 @@ __global__ void __launch_bounds__(128) deltanet_scan_kernel(ScanParams p) {
         aq[2] = fmaf(S[4 * j + 2], q4.z, aq[2]); aq[3] = fmaf(S[4 * j + 3], q4.w, aq[3]);
       }
       float sk_ = (ak[0] + ak[1]) + (ak[2] + ak[3]), sq_ = (aq[0] + aq[1]) + (aq[2] + aq[3]);
-      sk_ += __shfl_xor_sync(0xffffffffu, sk_, 1); sq_ += __shfl_xor_sync(0xffffffffu, sq_, 1);
-      sk_ += __shfl_xor_sync(0xffffffffu, sk_, 2); sq_ += __shfl_xor_sync(0xffffffffu, sq_, 2);
+#pragma unroll
+      for (int m = 1; m < DN_LANES; m <<= 1) {
+        sk_ += __shfl_xor_sync(0xffffffffu, sk_, m);
+        sq_ += __shfl_xor_sync(0xffffffffu, sq_, m);
+      }
       const float decay = sdecay[i];
       const float delta = (sv[i][c] - decay * sk_) * sbeta[i];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < DN_KPT / 4; ++j) {
         S[4 * j] = fmaf(S[4 * j], decay, k4[j].x * delta); S[4 * j + 1] = fmaf(S[4 * j + 1], decay, k4[j].y * delta);
         S[4 * j + 2] = fmaf(S[4 * j + 2], decay, k4[j].z * delta); S[4 * j + 3] = fmaf(S[4 * j + 3], decay, k4[j].w * delta);
       }
       if (kq == 0) p.out[(size_t)(tc + i) * p.n_v * DN_D + h * DN_D + col] = decay * sq_ + delta * sqk[i];
       if (p.ckpt) {
-        float* cp = p.ckpt + ((((size_t)(tc + i)) * p.n_v + h) * DN_D + col) * DN_D + kq * 32;
+        float* cp = p.ckpt + ((((size_t)(tc + i)) * p.n_v + h) * DN_D + col) * DN_D + kq * DN_KPT;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(cp)[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+        for (int j = 0; j < DN_KPT / 4; ++j) reinterpret_cast<float4*>(cp)[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
       }
     }
   }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(sp)[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+  for (int j = 0; j < DN_KPT / 4; ++j) reinterpret_cast<float4*>(sp)[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
 }
 
 // ------------------------------------------------------------------ gated RMSNorm, z read through a row stride
@@ -269,7 +264,7 @@ MX_HOST_API int mx_deltanet_scan(const void* qkv, int ld, int q_off, int k_off, 
   p.ab = (const bf16*)ab; p.ab_ld = ab_ld; p.a_idx = a_idx; p.b_idx = b_idx; p.k_of_v = k_of_v;
   p.ssm_a = ssm_a; p.dt_bias = dt_bias; p.state = state; p.slots = slots; p.cu_q = cu_q; p.out = out; p.ckpt = ckpt;
   p.n_v = n_v; p.q_scale = q_scale; p.eps = eps;
-  deltanet_scan_kernel<<<dim3(n_v * DN_VSPLIT, B), 128, 0, st>>>(p);
+  deltanet_scan_kernel<<<dim3(n_v * DN_VSPLIT, B), DN_THREADS, 0, st>>>(p);
   return (int)cudaGetLastError();
 }
 

@@ -78,6 +78,19 @@ def test_chunked_prefill_matches_whole_prompt():
     assert cos > 0.9995
 
 
+def test_dense_hybrid_tiled_heads_chunked_and_spec():
+    """Qwen3.6-27B-style graph: dense FFN, (1 + w) norms, tiled k->v head repeat, separate alpha / beta projections."""
+    m = _model("tiny-qwen35")
+    assert m.one_plus_w and m.mtp is not None
+    prompt = [(i * 13 + 5) % m.cfg.vocab for i in range(41)]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    whole = LLMEngine(m, EngineOptions(max_ctx=512, max_seqs=2)).generate([prompt], sp)[0]
+    spec = LLMEngine(m, EngineOptions(max_ctx=512, max_seqs=2, spec_k=2)).generate([prompt], sp)[0]
+    assert whole == spec
+    chunked = LLMEngine(m, EngineOptions(max_ctx=512, max_seqs=2, max_batch_tokens=16)).generate([prompt], sp)[0]
+    assert chunked[:2] == whole[:2]
+
+
 def test_two_sequences_keep_separate_state():
     m = _model()
     p1 = [(i * 5 + 1) % m.cfg.vocab for i in range(21)]
