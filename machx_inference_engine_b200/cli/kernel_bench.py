@@ -28,10 +28,36 @@ def peaks() -> dict:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "src": "fallback"}
 
 
+GRAPH_REPS = 0      # > 0: capture that many back-to-back calls in a CUDA graph and report time per call (launch gaps of an
+                    # eager loop would otherwise dominate kernels of a few microseconds)
+
+
 def timeit(fn, iters=10, warmup=3):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if GRAPH_REPS > 0:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(GRAPH_REPS):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / GRAPH_REPS)
+        ts.sort()
+        return ts[len(ts) // 2], ts[0]
     ts = []
     for _ in range(iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -81,9 +107,14 @@ def main(argv=None):
     ap.add_argument("--ctx", type=int, default=0)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--graph-reps", type=int, default=0, help="time N back-to-back calls inside one CUDA graph (per-call time without launch gaps)")
+    ap.add_argument("--gemv-path", default="auto", choices=["auto", "register", "stream"], help="which decode GEMV kernel to time")
     ap.add_argument("--layers", type=int, default=1, help="distinct weight copies cycled through so that weights are never L2-resident")
     a = ap.parse_args(argv)
     dev = torch.device("cuda:0")
+    K.set_gemv_path(a.gemv_path)
+    global GRAPH_REPS
+    GRAPH_REPS = a.graph_reps
     fmt = {"bf16": WFormat.BF16, "q8": WFormat.Q8, "q4k": WFormat.Q4K, "q6k": WFormat.Q6K, "mxfp4": WFormat.MXFP4}[a.fmt]
     torch.manual_seed(0)
 
@@ -139,6 +170,10 @@ def main(argv=None):
         se = torch.randperm(E, device=dev)[:k].to(torch.int32)
         med, mn = timeit(lambda: K.expert_gemv(x, gu, se, x_div=k, act=ref.ACT_SWIGLU_OAI), a.iters)
         report(f"expert_gemv gate_up[{a.fmt}] top{k} {2 * F}x{H}", med, mn, bytes_=gu.nbytes // E * k)
+        dn = weight(H, F, E)
+        h = torch.randn(k, F, device=dev).to(torch.bfloat16)
+        med, mn = timeit(lambda: K.expert_gemv(h, dn, se, x_div=1), a.iters)
+        report(f"expert_gemv down[{a.fmt}] top{k} {H}x{F}", med, mn, bytes_=dn.nbytes // E * k)
     elif a.kernel == "attention":
         T, nq, nkv, hd = a.tokens, a.heads, a.kv_heads, a.head_dim
         ctx = a.ctx or T

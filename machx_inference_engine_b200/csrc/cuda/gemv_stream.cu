@@ -1,0 +1,521 @@
+// Streaming GEMV for decode (M <= 8 activation rows): persistent CTAs pull the weight matrix through a shared-memory
+// ring with bulk asynchronous copies (cp.async.bulk + mbarrier transaction counts), one producer warp feeding
+// 4-8 consumer warps.  A weight row block is one contiguous run per plane, so a stage is one or two bulk copies;
+// the bytes in flight per SM are set by the ring (about 100 KB), not by registers or occupancy, which is what a
+// 1-3 us kernel needs to get near HBM speed.  Formats: bf16, Q8 (int8 + fp16 scale per 32), MXFP4 (E2M1 nibbles +
+// e8m0 scale per 32).  MXFP4 rows are multiplied in packed fp16: the E2M1 codes become f16x2 words by byte permutes,
+// the activation row is staged once as f16 scaled into range, 16-term partial sums run in HFMA2 and are folded
+// into fp32 with the block scale.
+//
+// Modes (same contract as the register-streamed kernels in gemv.cu, which remain the path for Q4_K / Q6_K and for
+// shapes this kernel does not take):
+//   dense : y[m][n] for m < M, all rows share each decoded weight
+//   slots : one activation row per slot (MoE decode: slot -> expert id -> weight slab; slots of experts owned by
+//           another rank give zeros), optional gated activation over 16-row interleaved gate/up rows
+// Fused epilogues: bias, per-slot scale, SwiGLU / clamped SwiGLU / GeGLU, stores into every rank's all-reduce inbox.
+//
+// Reference parity: src/ops/gemv_fp16.cpp:64, gemv_q8dot.cpp:276-680, gemv_mxfp4.cpp:94-323, moe_fused.cpp:101-541.
+#include "common.cuh"
+#include "comm.cuh"
+#include "dequant.cuh"
+#include "host_util.h"
+
+namespace mx {
+
+constexpr int GS_MAX_STAGES = 4;
+constexpr int GS_MAX_XROWS = 8;
+
+template <int FMT> struct GsCfg;
+template <> struct GsCfg<WF_BF16> { static constexpr int WARPS = 4, RPW = 1; };
+template <> struct GsCfg<WF_Q8> { static constexpr int WARPS = 8, RPW = 1; };
+template <> struct GsCfg<WF_MXFP4> { static constexpr int WARPS = 8, RPW = 2; };
+
+struct GsParams {
+  WeightRef w;
+  const __nv_bfloat16* x;   // [n_xrows][K]
+  void* y;
+  const float* bias;
+  const int* slot_expert;
+  const float* slot_scale;
+  int x_div, e_lo, e_hi;
+  int M, N, K;
+  int out_f32, act;
+  float act_alpha, act_limit;
+  int slots;                // slot mode: number of slots; dense mode: 1
+  int slot_mode;            // 1: activation row = slot / x_div and one output row per slot
+  int n_xrows;
+  int KC, nkc;              // k chunk in elements (whole rows unless bf16 rows are very long) and chunks per row
+  int nblk;                 // row blocks (plain) or feature blocks (gated) per slot
+  int nst;                  // ring depth (2..4), chosen so that two CTAs fit an SM where possible
+  int* status;
+  PeerOut peer;
+};
+
+template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes0(int K) { return FMT == WF_BF16 ? K * 2 : (FMT == WF_Q8 ? K : K / 2); }
+template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes1(int K) {
+  return FMT == WF_BF16 ? 0 : (FMT == WF_Q8 ? q8_d_stride(K) * 2 : mxfp4_e_stride(K));
+}
+template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row0(int K, int KC) { return FMT == WF_BF16 ? KC * 2 : gs_row_bytes0<FMT>(K); }
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync(int nthreads) { asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory"); }
+
+__device__ __forceinline__ float gs_act(int act, float g, float u, float alpha, float limit) {
+  if (act == 1) return g / (1.f + __expf(-g)) * u;
+  if (act == 2) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + __expf(-alpha * g)) * (u + 1.f);
+  }
+  const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+  return 0.5f * g * (1.f + t) * u;
+}
+
+// Eight E2M1 codes (nibble i of w = code i) -> four f16x2 words (codes 0|1, 2|3, 4|5, 6|7) by byte permutes: every
+// E2M1 value is an f16 whose low byte is zero, so one 8-entry byte table holds the magnitudes and the sign lands on
+// bit 7 of the same byte.
+__device__ __forceinline__ void e2m1x8_to_f16x2_lut(uint32_t w, uint32_t (&o)[4]) {
+  const uint32_t se = __byte_perm(w << 4, 0u, 0xBA98);      // byte b = 0xFF if code 2b   is negative
+  const uint32_t so = __byte_perm(w, 0u, 0xBA98);           // byte b = 0xFF if code 2b+1 is negative
+  const uint32_t sel = w & 0x77777777u;
+  {
+    const uint32_t sg = __byte_perm(se, so, 0x5140);                     // signs of codes 0,1,2,3
+    const uint32_t hi = __byte_perm(0x3E3C3800u, 0x46444240u, sel) | (sg & 0x80808080u);
+    o[0] = __byte_perm(hi, 0u, 0x1404);
+    o[1] = __byte_perm(hi, 0u, 0x3424);
+  }
+  {
+    const uint32_t sg = __byte_perm(se, so, 0x7362);                     // signs of codes 4,5,6,7
+    const uint32_t hi = __byte_perm(0x3E3C3800u, 0x46444240u, sel >> 16) | (sg & 0x80808080u);
+    o[2] = __byte_perm(hi, 0u, 0x1404);
+    o[3] = __byte_perm(hi, 0u, 0x3424);
+  }
+}
+
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ float f16x2_sum(uint32_t v) {
+  const __half2 h = *reinterpret_cast<const __half2*>(&v);
+  return __low2float(h) + __high2float(h);
+}
+
+// signed byte i of (v ^ 0x80808080) as float: 2^23 + u is exact, so is the subtraction
+template <int I>
+__device__ __forceinline__ float s8_to_float(uint32_t vx) {
+  return __uint_as_float(__byte_perm(vx, 0x4B000000u, 0x7440 | I)) - 8388736.f;      // [b_I, 0, 0, 0x4B]
+}
+
+// ---- granules: the unit of work of a lane.  Lane l owns granules l, l+32, ... of every row, so consecutive lanes read
+// consecutive 16-byte words of the weight row (no bank conflicts) and, with one activation row, keep their slice of x
+// in registers for the whole kernel.
+template <int FMT> struct Gran;
+template <> struct Gran<WF_BF16> { static constexpr int GE = 8, XR = 4, NGMAX = 16; };     // 8 bf16 = one 16-byte word
+template <> struct Gran<WF_Q8> { static constexpr int GE = 16, XR = 8, NGMAX = 8; };       // 16 int8
+template <> struct Gran<WF_MXFP4> { static constexpr int GE = 32, XR = 16, NGMAX = 4; };   // 32 nibbles
+
+// The MXFP4 path keeps its f16 activation row in four planes (plane i holds elements 8i..8i+7 of every 32-element
+// granule), so that consecutive lanes read consecutive 16-byte words of each plane.
+template <int FMT>
+__device__ __forceinline__ void load_xg(const uint8_t* __restrict__ xrow, int g, int K, uint32_t (&xr)[Gran<FMT>::XR]) {
+  const uint4* p = reinterpret_cast<const uint4*>(xrow) + (FMT == WF_MXFP4 ? g : g * (Gran<FMT>::XR / 4));
+  const int step = FMT == WF_MXFP4 ? (K >> 5) : 1;
+#pragma unroll
+  for (int i = 0; i < Gran<FMT>::XR / 4; ++i) {
+    const uint4 v = p[i * step];
+    xr[4 * i] = v.x; xr[4 * i + 1] = v.y; xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
+  }
+}
+
+// decoded weight granule, ready to be multiplied with any number of activation rows
+template <int FMT> struct WG;
+template <> struct WG<WF_BF16> { uint4 v; };
+template <> struct WG<WF_Q8> { float w[16]; float d; };
+template <> struct WG<WF_MXFP4> { uint32_t t[16]; float sc; };
+
+template <int FMT>
+__device__ __forceinline__ void decode_g(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, int g, WG<FMT>& o) {
+  if constexpr (FMT == WF_BF16) {
+    o.v = reinterpret_cast<const uint4*>(w0)[g];
+  } else if constexpr (FMT == WF_Q8) {
+    const uint4 a = reinterpret_cast<const uint4*>(w0)[g];
+    o.d = __half2float(reinterpret_cast<const __half*>(w1)[g >> 1]);
+    const uint32_t q[4] = {a.x ^ 0x80808080u, a.y ^ 0x80808080u, a.z ^ 0x80808080u, a.w ^ 0x80808080u};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o.w[4 * i] = s8_to_float<0>(q[i]); o.w[4 * i + 1] = s8_to_float<1>(q[i]); o.w[4 * i + 2] = s8_to_float<2>(q[i]); o.w[4 * i + 3] = s8_to_float<3>(q[i]);
+    }
+  } else {
+    const uint4 v = reinterpret_cast<const uint4*>(w0)[g];
+    o.sc = e8m0_f32(w1[g]);
+    const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t t4[4];
+      e2m1x8_to_f16x2_lut(q[i], t4);
+      o.t[4 * i] = t4[0]; o.t[4 * i + 1] = t4[1]; o.t[4 * i + 2] = t4[2]; o.t[4 * i + 3] = t4[3];
+    }
+  }
+}
+
+template <int FMT>
+__device__ __forceinline__ float dot_g(const WG<FMT>& w, const uint32_t (&xr)[Gran<FMT>::XR], float xscale) {
+  if constexpr (FMT == WF_BF16) {
+    float s = bf16_lo(w.v.x) * bf16_lo(xr[0]);
+    s = fmaf(bf16_hi(w.v.x), bf16_hi(xr[0]), s);
+    s = fmaf(bf16_lo(w.v.y), bf16_lo(xr[1]), s); s = fmaf(bf16_hi(w.v.y), bf16_hi(xr[1]), s);
+    s = fmaf(bf16_lo(w.v.z), bf16_lo(xr[2]), s); s = fmaf(bf16_hi(w.v.z), bf16_hi(xr[2]), s);
+    s = fmaf(bf16_lo(w.v.w), bf16_lo(xr[3]), s); s = fmaf(bf16_hi(w.v.w), bf16_hi(xr[3]), s);
+    return s;
+  } else if constexpr (FMT == WF_Q8) {
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      s0 = fmaf(w.w[2 * i], bf16_lo(xr[i]), s0);
+      s1 = fmaf(w.w[2 * i + 1], bf16_hi(xr[i]), s1);
+    }
+    return (s0 + s1) * w.d;
+  } else {
+    uint32_t a0 = 0u, a1 = 0u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a0 = hfma2_u32(w.t[2 * i], xr[2 * i], a0);
+      a1 = hfma2_u32(w.t[2 * i + 1], xr[2 * i + 1], a1);
+    }
+    return (f16x2_sum(a0) + f16x2_sum(a1)) * (w.sc * xscale);
+  }
+}
+
+// one weight row (one k chunk of it) against MM activation rows; CACHED: the lane's x granules are in registers
+template <int FMT, int MM, bool CACHED, int NG>
+__device__ __forceinline__ void gs_row(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, int ng, int lane,
+                                       const uint32_t (&xc)[CACHED ? NG : 1][Gran<FMT>::XR], const uint8_t* __restrict__ xs, int K, int k0,
+                                       const float* __restrict__ xscale, float (&acc)[MM]) {
+  if constexpr (CACHED) {
+#pragma unroll
+    for (int j = 0; j < NG; ++j) {
+      const int g = lane + 32 * j;
+      if (g < ng) {
+        WG<FMT> wg;
+        decode_g<FMT>(w0, w1, g, wg);
+        acc[0] += dot_g<FMT>(wg, xc[j], 1.f);
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int g = lane; g < ng; g += 32) {
+      WG<FMT> wg;
+      decode_g<FMT>(w0, w1, g, wg);
+      {
+#pragma unroll
+        for (int m = 0; m < MM; ++m) {
+          uint32_t xr[Gran<FMT>::XR];
+          load_xg<FMT>(xs + ((size_t)m * K + k0) * 2, g, K, xr);
+          acc[m] += dot_g<FMT>(wg, xr, FMT == WF_MXFP4 ? xscale[m] : 1.f);
+        }
+      }
+    }
+  }
+}
+
+// NG: granules per lane and row chunk (compile time, so the activation slice stays in registers); two CTAs per SM
+template <int FMT, int MM, bool GATED, int NG>
+__global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_kernel(const GsParams p) {
+  constexpr int WARPS = GsCfg<FMT>::WARPS, RPW = GsCfg<FMT>::RPW, RB = WARPS * RPW, FB = RB / 2;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = p.K;
+  const int g0 = gs_row_bytes0<FMT>(K), g1 = gs_row_bytes1<FMT>(K);      // global row strides
+  const int r0b = gs_stage_row0<FMT>(K, p.KC), r1b = g1;                 // bytes per row inside a stage
+  const int plane1_off = RB * r0b;
+  const int stage_bytes = RB * (r0b + r1b);
+  const int x_bytes = (p.n_xrows * K * 2 + 15) & ~15;
+  uint8_t* xs = smem;
+  uint8_t* stages = smem + x_bytes;
+  const int NST = p.nst;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stages + NST * stage_bytes);
+  float* xscale = reinterpret_cast<float*>(bars + 2 * GS_MAX_STAGES);
+  volatile int* abort_flag = reinterpret_cast<int*>(xscale + GS_MAX_XROWS);
+  const uint32_t bar0 = smem_u32(bars);
+  const int next_seq = p.peer.world ? *p.peer.seq + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(bar0 + 8 * s, 1);
+      mbar_init(bar0 + 8 * (GS_MAX_STAGES + s), WARPS);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const int units = p.slots * p.nblk;
+  const int F = p.N / 2;
+
+  if (warp == WARPS) {
+    // ------------------------------------------------------------ producer: one lane issues the bulk copies
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int slot = u / p.nblk, blk = u - slot * p.nblk;
+        const uint8_t* b0 = (const uint8_t*)p.w.p0;
+        const uint8_t* b1 = (const uint8_t*)p.w.p1;
+        if (p.slot_expert) {
+          const int e = p.slot_expert[slot];
+          if (e < p.e_lo || e >= p.e_hi) continue;
+          b0 += (size_t)(e - p.e_lo) * p.N * g0;
+          b1 += (size_t)(e - p.e_lo) * p.N * g1;
+        }
+        for (int kc = 0; kc < p.nkc && ok; ++kc, ++it) {
+          const int s = it % NST;
+          const uint32_t full = bar0 + 8 * s, empty = bar0 + 8 * (GS_MAX_STAGES + s);
+          if (it >= NST) ok = mbar_wait(empty, ((it / NST) & 1) ^ 1, p.status, ERR_MBAR_TIMEOUT_PRODUCER, abort_flag);
+          if (!ok) break;
+          const uint32_t dst = smem_u32(stages + (size_t)s * stage_bytes);
+          if (GATED) {
+            const int f0 = blk * FB, nf = min(FB, F - f0);
+            const int grow = 32 * (f0 >> 4) + (f0 & 15);
+            mbar_expect_tx(full, 2u * nf * (r0b + r1b));
+            bulk_g2s(dst, b0 + (size_t)grow * g0, nf * r0b, full);
+            bulk_g2s(dst + FB * r0b, b0 + (size_t)(grow + 16) * g0, nf * r0b, full);
+            if (r1b) {
+              bulk_g2s(dst + plane1_off, b1 + (size_t)grow * g1, nf * r1b, full);
+              bulk_g2s(dst + plane1_off + FB * r1b, b1 + (size_t)(grow + 16) * g1, nf * r1b, full);
+            }
+          } else {
+            const int row0 = blk * RB, nr = min(RB, p.N - row0);
+            mbar_expect_tx(full, (uint32_t)nr * (r0b + r1b));
+            if (p.nkc == 1) {
+              bulk_g2s(dst, b0 + (size_t)row0 * g0, nr * r0b, full);
+            } else {
+              for (int r = 0; r < nr; ++r) bulk_g2s(dst + r * r0b, b0 + (size_t)(row0 + r) * g0 + (size_t)kc * r0b, r0b, full);
+            }
+            if (r1b) bulk_g2s(dst + plane1_off, b1 + (size_t)row0 * g1, nr * r1b, full);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ consumers
+    // stage the activation rows once (bf16 as they are; MXFP4 path: f16 scaled so that the row maximum sits near 2^9)
+    if constexpr (FMT == WF_MXFP4) {
+      // one warp per activation row; a lane keeps its 16-byte chunks in registers between the maximum and the conversion
+      for (int m = warp; m < p.n_xrows; m += WARPS) {
+        const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)m * K);
+        const int nch = K >> 3;
+        constexpr int CH = 16;                                   // chunks per lane: K <= 4096 (checked by the host)
+        uint4 v[CH];
+        float mx = 0.f;
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const int c = lane + 32 * i;
+          v[i] = c < nch ? __ldg(xr + c) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const uint32_t q[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mx = fmaxf(mx, fmaxf(fabsf(bf16_lo(q[j])), fabsf(bf16_hi(q[j]))));
+        }
+        mx = warp_max(mx);
+        int ex = 0;
+        if (mx > 0.f) { frexpf(mx, &ex); }                       // mx = f * 2^ex, f in [0.5, 1)
+        // x * 2^sh has its maximum in [2^8, 2^9): sixteen products of magnitude <= 6 * 2^9 cannot overflow an f16 sum
+        const int sh = max(-24, min(24, 9 - ex));
+        const float up = exp2f((float)sh);
+        uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * K * 2);
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const int c = lane + 32 * i;
+          if (c < nch) {
+            const uint32_t q[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __half2 h = __floats2half2_rn(bf16_lo(q[j]) * up, bf16_hi(q[j]) * up);
+              o[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            dst[(c & 3) * (K >> 5) + (c >> 2)] = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        if (lane == 0) xscale[m] = exp2f((float)-sh);
+      }
+    } else {
+      const int n16 = p.n_xrows * K / 8;
+      for (int i = threadIdx.x; i < n16; i += WARPS * 32) reinterpret_cast<uint4*>(xs)[i] = __ldg(reinterpret_cast<const uint4*>(p.x) + i);
+    }
+    consumer_sync(WARPS * 32);
+
+    int it = 0;
+    bool ok = true;
+    constexpr bool CACHED = MM == 1 && FMT != WF_MXFP4;      // MXFP4 decoding needs the registers: x comes from shared memory
+    uint32_t xc[CACHED ? NG : 1][Gran<FMT>::XR];
+    int x_tag = -1;                                         // (activation row, k chunk) held in xc
+    const int ng = p.KC / Gran<FMT>::GE;
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const int slot = u / p.nblk, blk = u - slot * p.nblk;
+      bool owned = true;
+      int el = 0;
+      if (p.slot_expert) {
+        const int e = p.slot_expert[slot];
+        owned = e >= p.e_lo && e < p.e_hi;
+        el = owned ? e - p.e_lo : 0;
+      }
+      const int xrow = p.slot_mode ? slot / p.x_div : 0;
+      const uint8_t* xbase = xs + (size_t)xrow * K * 2;
+      float acc[GATED ? 2 : RPW][MM];
+#pragma unroll
+      for (int r = 0; r < (GATED ? 2 : RPW); ++r)
+#pragma unroll
+        for (int m = 0; m < MM; ++m) acc[r][m] = 0.f;
+      if (owned && ok) {
+        for (int kc = 0; kc < p.nkc; ++kc, ++it) {
+          if (CACHED && x_tag != xrow * p.nkc + kc) {
+            x_tag = xrow * p.nkc + kc;
+#pragma unroll
+            for (int j = 0; j < NG; ++j)
+              if (lane + 32 * j < ng) load_xg<FMT>(xbase + (size_t)kc * p.KC * 2, lane + 32 * j, K, xc[j]);
+          }
+          const int s = it % NST;
+          ok = mbar_wait(bar0 + 8 * s, (it / NST) & 1, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag);
+          if (!ok) break;
+          const uint8_t* st = stages + (size_t)s * stage_bytes;
+#pragma unroll
+          for (int r = 0; r < (GATED ? 2 : RPW); ++r) {
+            // gated: the warp owns one feature of the block; its gate row sits at `warp`, its up row FB rows further
+            const int srow = GATED ? (r == 0 ? 0 : FB) + warp : warp * RPW + r;
+            gs_row<FMT, MM, CACHED, NG>(st + (size_t)srow * r0b, st + plane1_off + (size_t)srow * r1b, ng, lane, xc, xbase, K, kc * p.KC,
+                                    xscale + xrow, acc[r]);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar0 + 8 * (GS_MAX_STAGES + s));
+        }
+      }
+      // ---- epilogue of this unit
+#pragma unroll
+      for (int r = 0; r < (GATED ? 2 : RPW); ++r)
+#pragma unroll
+        for (int m = 0; m < MM; ++m) acc[r][m] = warp_sum(acc[r][m]);
+      if (lane == 0) {
+        const float oscale = p.slot_scale ? p.slot_scale[slot] : 1.f;
+        if (GATED) {
+          const int f = blk * FB + warp;
+          if (f < F) {
+            const int grow = 32 * (f >> 4) + (f & 15);
+            const float* bias = p.bias ? p.bias + (size_t)el * p.N : nullptr;
+            const float g = acc[0][0] + (bias ? bias[grow] : 0.f), uu = acc[1][0] + (bias ? bias[grow + 16] : 0.f);
+            const float v = owned ? gs_act(p.act, g, uu, p.act_alpha, p.act_limit) * oscale : 0.f;
+            if (p.out_f32) ((float*)p.y)[(size_t)slot * F + f] = v;
+            else ((__nv_bfloat16*)p.y)[(size_t)slot * F + f] = __float2bfloat16(v);
+          }
+        } else {
+#pragma unroll
+          for (int r = 0; r < RPW; ++r) {
+            const int n = blk * RB + warp * RPW + r;
+            if (n >= p.N) continue;
+            const float* bias = p.bias ? p.bias + (size_t)el * p.N : nullptr;
+#pragma unroll
+            for (int m = 0; m < MM; ++m) {
+              if (!p.slot_mode && m >= p.M) break;
+              const size_t orow = p.slot_mode ? (size_t)slot : (size_t)m;
+              const float v = owned ? (acc[r][m] + (bias ? bias[n] : 0.f)) * oscale : 0.f;
+              if (p.peer.world) {
+                for (int d = 0; d < p.peer.world; ++d) reinterpret_cast<float*>(peer_slot(p.peer, d, next_seq))[orow * p.N + n] = v;
+              } else if (p.out_f32) ((float*)p.y)[orow * p.N + n] = v;
+              else ((__nv_bfloat16*)p.y)[orow * p.N + n] = __float2bfloat16(v);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (p.peer.world) peer_publish(p.peer, next_seq);
+}
+
+template <int FMT, int MM, bool GATED, int NG>
+static int gs_launch(const GsParams& p, int smem, cudaStream_t st) {
+  constexpr int THREADS = (GsCfg<FMT>::WARPS + 1) * 32;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(gemv_stream_kernel<FMT, MM, GATED, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr_done = true;
+  }
+  const int units = p.slots * p.nblk;
+  const int per_sm = smem <= 113 * 1024 ? 2 : 1;
+  const int grid = min(units, sm_count() * per_sm);
+  gemv_stream_kernel<FMT, MM, GATED, NG><<<grid, THREADS, smem, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
+template <int FMT, int NG>
+static int gs_dispatch_ng(GsParams& p, int smem, bool gated, cudaStream_t st) {
+  if (gated) return gs_launch<FMT, 1, true, NG>(p, smem, st);
+  if (p.slot_mode || p.M == 1) return gs_launch<FMT, 1, false, NG>(p, smem, st);
+  if (FMT == WF_MXFP4) return 1;
+  if (p.M <= 2) return gs_launch<FMT, 2, false, NG>(p, smem, st);
+  if (p.M <= 4) return gs_launch<FMT, 4, false, NG>(p, smem, st);
+  return gs_launch<FMT, 8, false, NG>(p, smem, st);
+}
+
+template <int FMT>
+static int gs_dispatch(GsParams& p, cudaStream_t st) {
+  constexpr int WARPS = GsCfg<FMT>::WARPS, RPW = GsCfg<FMT>::RPW, RB = WARPS * RPW;
+  const bool gated = p.act != 0;
+  p.KC = p.K; p.nkc = 1;
+  if (FMT == WF_BF16 && p.K > 4096) {
+    int n = (p.K + 4095) / 4096;
+    while (n < 64 && (p.K % n || (p.K / n) % 8)) ++n;
+    if (p.K % n) return 1;
+    p.nkc = n; p.KC = p.K / n;
+  }
+  if (p.KC / Gran<FMT>::GE > 32 * Gran<FMT>::NGMAX || p.KC % Gran<FMT>::GE) return 1;
+  if (FMT == WF_MXFP4 && p.K > 4096) return 1;
+  p.nblk = gated ? (p.N / 2 + RB / 2 - 1) / (RB / 2) : (p.N + RB - 1) / RB;
+  const int stage = RB * (gs_stage_row0<FMT>(p.K, p.KC) + gs_row_bytes1<FMT>(p.K));
+  const int fixed = ((p.n_xrows * p.K * 2 + 15) & ~15) + 2 * GS_MAX_STAGES * 8 + GS_MAX_XROWS * 4 + 16;
+  p.nst = GS_MAX_STAGES;
+  while (p.nst > 2 && fixed + p.nst * stage > 113 * 1024) --p.nst;        // two CTAs per SM when three stages still fit
+  if (fixed + p.nst * stage > 113 * 1024) p.nst = min(GS_MAX_STAGES, max(2, (200 * 1024 - fixed) / stage));
+  const int smem = fixed + p.nst * stage;
+  if (smem > 200 * 1024 || p.nst < 2) return 1;
+  // granules per lane: 3/4 of the maximum covers K <= 3072 with a quarter fewer registers
+  constexpr int NGS = Gran<FMT>::NGMAX * 3 / 4;
+  if (p.KC / Gran<FMT>::GE <= 32 * NGS) return gs_dispatch_ng<FMT, NGS>(p, smem, gated, st);
+  return gs_dispatch_ng<FMT, Gran<FMT>::NGMAX>(p, smem, gated, st);
+}
+
+// Returns 0 when the kernel was launched, 1 when the shape / format is not taken by this path (the caller falls
+// back to the register-streamed kernels), a CUDA error code otherwise.
+int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const float* bias, int M, int N, int K, int out_f32, int act,
+                    float act_alpha, float act_limit, const int* slot_expert, const float* slot_scale, int slots, int x_div, int e_lo,
+                    int e_hi, const PeerOut* peer, cudaStream_t st) {
+  if (wfmt != WF_BF16 && wfmt != WF_Q8 && wfmt != WF_MXFP4) return 1;
+  if (K % 32 && !(wfmt == WF_BF16 && K % 8 == 0)) return 1;
+  if (act != 0 && wfmt != WF_MXFP4) return 1;                // gated epilogue: one feature per warp needs RPW == 2
+  if (act != 0 && (N % 32)) return 1;
+  GsParams p;
+  p.w = w; p.x = (const __nv_bfloat16*)x; p.y = y; p.bias = bias; p.slot_expert = slot_expert; p.slot_scale = slot_scale;
+  p.x_div = x_div > 0 ? x_div : 1; p.e_lo = e_lo; p.e_hi = e_hi; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.act = act;
+  p.act_alpha = act_alpha; p.act_limit = act_limit; p.status = status_word();
+  p.slot_mode = (slot_expert != nullptr || act != 0) ? 1 : 0;
+  p.slots = p.slot_mode ? (slots > 0 ? slots : M) : 1;
+  p.n_xrows = p.slot_mode ? (p.slots + p.x_div - 1) / p.x_div : M;
+  if (p.n_xrows < 1 || p.n_xrows > GS_MAX_XROWS) return 1;
+  // every plane row must start on a 16-byte boundary for the bulk copies
+  const int rb0 = wfmt == WF_BF16 ? K * 2 : (wfmt == WF_Q8 ? K : K / 2);
+  if (rb0 % 16) return 1;
+  if (((uintptr_t)w.p0 & 15) || (w.p1 && ((uintptr_t)w.p1 & 15)) || ((uintptr_t)x & 15)) return 1;
+  if (peer) p.peer = *peer; else p.peer.world = 0;
+  switch (wfmt) {
+    case WF_BF16: return gs_dispatch<WF_BF16>(p, st);
+    case WF_Q8: return gs_dispatch<WF_Q8>(p, st);
+    default: return gs_dispatch<WF_MXFP4>(p, st);
+  }
+}
+
+}  // namespace mx

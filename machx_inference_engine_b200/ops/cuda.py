@@ -61,6 +61,13 @@ def check_status():
         raise KernelError(f"kernel status {v}: {names.get(v, 'unknown')} ran out of its time limit")
 
 
+def set_gemv_path(path) -> None:
+    """Which decode GEMV kernel runs: "auto" (per case, the default), "register" (register-streamed kernels only) or
+    "stream" (the bulk-copy streaming kernel wherever it applies); booleans mean register / auto."""
+    code = {"auto": 0, "register": 1, "stream": 2, True: 1, False: 0}[path]
+    _lib.cuda().mx_gemv_set_path(code)
+
+
 def sm_count() -> int:
     return _lib.cuda().mx_sm_count()
 

@@ -186,6 +186,61 @@ def test_expert_gemv():
     assert rel_err(y, y_r) < 5e-3
 
 
+@pytest.mark.parametrize("fmt", [WFormat.BF16, WFormat.Q8, WFormat.MXFP4])
+def test_streaming_gemv_matches_register_gemv_and_oracle(fmt):
+    """The bulk-copy streaming kernel and the register-streamed kernel are two implementations of one contract."""
+    k = K()
+    for (M, N, Kd) in [(1, 2880, 2880), (1, 200, 4096), (3, 515, 1024), (8, 96, 2880), (1, 64, 14336)]:
+        if fmt == WFormat.MXFP4 and M > 1:
+            continue
+        w = make_weight(fmt, N, Kd, seed=N)
+        x = (torch.randn(M, Kd, device=dev()) * 3).to(torch.bfloat16)
+        bias = torch.randn(N, device=dev())
+        want = ref.linear(x, w, bias=bias, out_f32=True)
+        k.set_gemv_path("stream")
+        a = k.linear(x, w, bias=bias, out_f32=True)
+        k.set_gemv_path("register")
+        b = k.linear(x, w, bias=bias, out_f32=True)
+        k.set_gemv_path("auto")
+        k.check_status()
+        assert rel_err(a, want) < 4e-3, (M, N, Kd)
+        assert rel_err(b, want) < 4e-3, (M, N, Kd)
+    # activations with a large dynamic range (fp16 staging of the MXFP4 path must not overflow or flush them)
+    if fmt == WFormat.MXFP4:
+        w = make_weight(fmt, 256, 2880, seed=5)
+        x = torch.randn(1, 2880, device=dev())
+        x[0, ::97] *= 3000.0
+        x[0, 1::2] *= 1e-3
+        x = x.to(torch.bfloat16)
+        k.set_gemv_path("stream")
+        got = k.linear(x, w, out_f32=True)
+        k.set_gemv_path("auto")
+        assert rel_err(got, ref.linear(x, w, out_f32=True)) < 4e-3
+
+
+def test_streaming_expert_gemv_with_foreign_experts():
+    k = K()
+    E, H, F, topk = 8, 512, 256, 4
+    gu = make_weight(WFormat.MXFP4, 2 * F, H, E=E, seed=1)
+    dn = make_weight(WFormat.MXFP4, H, F, E=E, seed=2)
+    gub, dnb = torch.randn(E, 2 * F, device=dev()), torch.randn(E, H, device=dev())
+    x = torch.randn(2, H, device=dev()).to(torch.bfloat16)
+    se = torch.tensor([1, 6, 2, 7, 0, 3, 5, 2], dtype=torch.int32, device=dev())
+    for path, (e_lo, e_hi) in [("stream", (0, 8)), ("stream", (2, 6)), ("auto", (2, 6))]:
+        k.set_gemv_path(path)
+        g, d = gu.slice_experts(e_lo, e_hi), dn.slice_experts(e_lo, e_hi)
+        gb, db = gub[e_lo:e_hi].contiguous(), dnb[e_lo:e_hi].contiguous()
+        a = k.expert_gemv(x, g, se, x_div=topk, bias=gb, act=ref.ACT_SWIGLU_OAI, e_lo=e_lo)
+        want = ref.expert_gemv(x, g, se, x_div=topk, bias=gb, act=ref.ACT_SWIGLU_OAI, e_lo=e_lo)
+        assert rel_err(a, want) < 1e-2
+        y = k.expert_gemv(want, d, se, x_div=1, bias=db, e_lo=e_lo, out_f32=True)
+        assert rel_err(y, ref.expert_gemv(want, d, se, x_div=1, bias=db, e_lo=e_lo, out_f32=True)) < 5e-3
+        foreign = [i for i, e in enumerate(se.tolist()) if not (e_lo <= e < e_hi)]
+        assert all(float(y[i].abs().max()) == 0.0 for i in foreign)
+    k.set_gemv_path("auto")
+    k.check_status()
+
+
 def test_rmsnorm_residual_and_saturation():
     T, H = 37, 2880
     x = torch.randn(T, H, device=dev()) * 3
