@@ -19,7 +19,6 @@
 #include "comm.cuh"
 #include "dequant.cuh"
 #include "host_util.h"
-#include <cstdlib>
 
 namespace mx {
 
@@ -45,7 +44,6 @@ struct GemmParams {
   int act;
   float act_alpha, act_limit;
   int group_m;                  // tile rasterisation group (see tile_coords)
-  int debug;
   int* status;
   PeerOut peer;                 // world > 0: the tile is stored into every rank's inbox (fused all-reduce), not into C
 };
@@ -102,6 +100,12 @@ __global__ void __launch_bounds__(FMT == WF_BF16 ? 192 : 448, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   using L = SmemLayout<FMT, BN, SA, SB>;
   constexpr bool kDequant = FMT != WF_BF16;
+  // k-blocks per barrier handshake.  The single MMA-issuing thread pays a fixed cost per wait / commit pair, which at one
+  // 64-wide k-block per handshake exceeded the tensor time of a 128x128 tile: TMA-fed (bf16) weights hand over two blocks
+  // at once (measured 973 -> 1103 TFLOP/s at 8192^3).  Decoded weights are bound by the decode warps, not by the
+  // handshake (no gain measured), and keep the finer ring.
+  constexpr int KS = (!kDequant && SA % 2 == 0) ? 2 : 1;
+  constexpr int LA = SA / KS, LB = (kDequant ? SB : SA) / KS;      // logical ring depths
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);   // power of two for BN in {32,64,128,256}
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -147,6 +151,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int total_tiles = m_tiles * p.num_n_tiles;
   const int next_seq = p.peer.world ? *p.peer.seq + 1 : 0;
   const int k_iters = (p.K + BK - 1) / BK;
+  const int kl_iters = (k_iters + KS - 1) / KS;
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer (A always, B when it is bf16)
@@ -159,13 +164,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         int mt, nt;
         tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
         const int e = p.tile_expert ? p.tile_expert[mt] : 0;
-        for (int k = 0; k < k_iters; ++k, ++it) {
-          const uint32_t s = it % SA, ph = (it / SA) & 1;
+        for (int kl = 0; kl < kl_iters; ++kl, ++it) {
+          const uint32_t s = it % LA, ph = (it / LA) & 1;
           if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, p.status, ERR_MBAR_TIMEOUT_PRODUCER, abort_flag))) break;
-          if (p.debug & 64) { mbar_arrive(bar_full + 8 * s); continue; }
-          mbar_expect_tx(bar_full + 8 * s, kDequant ? L::A_BYTES : L::A_BYTES + L::B_BYTES);
-          tma_load_2d(smem_base + L::A_OFFSET + s * L::A_BYTES, &tmap_a, bar_full + 8 * s, k * BK, mt * BM);
-          if (!kDequant) tma_load_3d(smem_base + L::B_OFFSET + s * L::B_BYTES, &tmap_b, bar_full + 8 * s, k * BK, nt * BN, e);
+          mbar_expect_tx(bar_full + 8 * s, KS * (kDequant ? L::A_BYTES : L::A_BYTES + L::B_BYTES));
+#pragma unroll
+          for (int j = 0; j < KS; ++j) {
+            // a k-block past the end of K is fetched all the same: the out-of-range box arrives as zeros
+            const int k = kl * KS + j;
+            const uint32_t ps = s * KS + j;
+            tma_load_2d(smem_base + L::A_OFFSET + ps * L::A_BYTES, &tmap_a, bar_full + 8 * s, k * BK, mt * BM);
+            if (!kDequant) tma_load_3d(smem_base + L::B_OFFSET + ps * L::B_BYTES, &tmap_b, bar_full + 8 * s, k * BK, nt * BN, e);
+          }
         }
       }
     }
@@ -180,18 +190,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (!(ok = mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, p.status, ERR_MBAR_TIMEOUT_MMA, abort_flag))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int k = 0; k < k_iters; ++k, ++it) {
-          const uint32_t s = it % SA, ph = (it / SA) & 1;
-          const uint32_t sb = kDequant ? it % SB : s, phb = (it / SB) & 1;
+        for (int kl = 0; kl < kl_iters; ++kl, ++it) {
+          const uint32_t s = it % LA, ph = (it / LA) & 1;
+          const uint32_t sb = kDequant ? it % LB : s, phb = (it / LB) & 1;
           if (!(ok = mbar_wait(bar_full + 8 * s, ph, p.status, ERR_MBAR_TIMEOUT_MMA, abort_flag))) break;
           if (kDequant && !(ok = mbar_wait(bar_bfull + 8 * sb, phb, p.status, ERR_MBAR_TIMEOUT_MMA, abort_flag))) break;
           tc_fence_after();
-          const uint64_t a_desc = umma_desc_k_sw128(smem_base + L::A_OFFSET + s * L::A_BYTES);
-          const uint64_t b_desc = umma_desc_k_sw128(smem_base + L::B_OFFSET + sb * L::B_BYTES);
-          if (!(p.debug & 8)) {
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes per UMMA K step: +2 in the (addr>>4) field
-            umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (k | kk) != 0);
+          for (int j = 0; j < KS; ++j) {
+            const uint64_t a_desc = umma_desc_k_sw128(smem_base + L::A_OFFSET + (s * KS + j) * L::A_BYTES);
+            const uint64_t b_desc = umma_desc_k_sw128(smem_base + L::B_OFFSET + (sb * KS + j) * L::B_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes per UMMA K step: +2 in the (addr>>4) field
+              umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kl | j | kk) != 0);
           }
           umma_commit(bar_empty + 8 * s);
           if (kDequant) umma_commit(bar_bempty + 8 * sb);
@@ -216,7 +227,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const float rs = (p.row_scale && row_ok) ? p.row_scale[row] : 1.f;
       const float* bias = p.bias ? p.bias + (size_t)e * p.N : nullptr;
 #pragma unroll 1
-      for (int c0 = 0; c0 < ((p.debug & 32) ? 0 : BN); c0 += 32) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r);
         tmem_ld_wait();
@@ -320,7 +331,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
     };
     auto issue_next = [&]() {
-      if (prow_ok && 2 * pk + half < k_blocks && !(p.debug & 2)) raw_issue<FMT>(raw_base_u32 + ps * L::RAW_STAGE, aux_base_u32 + ps * L::RAW_STAGE, prp, pk, half);
+      if (prow_ok && 2 * pk + half < k_blocks) raw_issue<FMT>(raw_base_u32 + ps * L::RAW_STAGE, aux_base_u32 + ps * L::RAW_STAGE, prp, pk, half);
       cp_async_commit();
       ps = (ps + 1 == kRawDepth) ? 0 : ps + 1;
       if (++pk == k_iters) { pk = 0; pt += gridDim.x; prefetch_tile_setup(); }
@@ -335,31 +346,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int mt, nt;
       tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
       const bool row_ok = live && nt * BN + rl < p.N;
-      for (int k = 0; k < k_iters; ++k) {
-        issue_next();
-        cp_async_wait<kRawDepth - 1>();          // this iteration's bytes have landed in the slot
+      for (int kl = 0; kl < kl_iters && ok; ++kl) {
         if (!(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag))) break;
-        if (live) {
-          uint8_t* b_tile = smem + L::B_OFFSET + sb * L::B_BYTES;
+#pragma unroll
+        for (int j = 0; j < KS; ++j) {
+          const int k = kl * KS + j;
           uint32_t o[16];
-          if (row_ok && 2 * k + half < k_blocks && !(p.debug & 1)) {
-            raw_decode<FMT>(raw_base + cs * L::RAW_STAGE, aux_base + cs * L::RAW_STAGE, k, half, o);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) o[j] = 0u;
+          bool have = false;
+          if (k < k_iters) {
+            issue_next();
+            cp_async_wait<kRawDepth - 1>();          // this iteration's bytes have landed in the slot
+            if (live && row_ok && 2 * k + half < k_blocks) {
+              raw_decode<FMT>(raw_base + cs * L::RAW_STAGE, aux_base + cs * L::RAW_STAGE, k, half, o);
+              have = true;
+            }
+            cs = (cs + 1 == kRawDepth) ? 0 : cs + 1;
           }
-          if (!(p.debug & 4)) {
+          if (live) {
+            if (!have) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            *reinterpret_cast<uint4*>(b_tile + sw128_offset(rl, raw_chunk<FMT>(half, c))) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+              for (int i = 0; i < 16; ++i) o[i] = 0u;
+            }
+            uint8_t* b_tile = smem + L::B_OFFSET + (sb * KS + j) * L::B_BYTES;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              *reinterpret_cast<uint4*>(b_tile + sw128_offset(rl, raw_chunk<FMT>(half, c))) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
           }
         }
         // every lane publishes its generic-proxy stores to the async proxy, then one lane arrives for the warp
-        if (!(p.debug & 16)) fence_proxy_async();
+        fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_bfull + 8 * sb);
-        cs = (cs + 1 == kRawDepth) ? 0 : cs + 1;
-        if (++sb == SB) { sb = 0; phb ^= 1; }
+        if (++sb == LB) { sb = 0; phb ^= 1; }
       }
     }
     cp_async_wait<0>();
@@ -465,8 +483,6 @@ static int gemm_impl(const void* a, int wfmt, const void* w0, const void* w1, co
   p.act = act; p.act_alpha = act_alpha; p.act_limit = act_limit;
   if (peer) p.peer = *peer; else p.peer.world = 0;
   p.group_m = tile_expert ? 1 : 8;
-  { const char* dbg = getenv("MX_GEMM_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
-  { const char* g = getenv("MX_GEMM_GROUP"); if (g) p.group_m = atoi(g); }
   p.status = status_word();
 
   CUtensorMap ta, tb;

@@ -65,17 +65,36 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 //   pair_to_packed[n], tile_expert[max_tiles], num_tiles[1], packed_rows[1]
 // e_lo/e_hi restrict packing to the experts owned by this rank (expert parallelism): pairs routed
 // elsewhere get pair_to_packed = -1.
+// Stable counting sort in three passes: every warp owns a contiguous chunk of the pair list and histograms it
+// (hist[warp][expert] in shared memory), a scan over the warps turns the histograms into per-warp write cursors,
+// and each warp walks its chunk again placing 32 pairs per step (rank among equal experts by __match_any_sync).
+// Rows of an expert therefore keep increasing pair order and the result does not depend on timing.
 __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ topk_idx, int n, int K, int E, int e_lo, int e_hi,
                                                         int* __restrict__ counts, int* __restrict__ seg_start, int* __restrict__ packed_token,
                                                         int* __restrict__ pair_to_packed, int* __restrict__ tile_expert, int* __restrict__ num_tiles,
                                                         int max_rows) {
+  extern __shared__ int s_hist[];            // [nwarps][E]
   __shared__ int s_cnt[1024];
   __shared__ int s_start[1025];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int chunk = ((n + nwarps - 1) / nwarps + 31) & ~31;
+  const int c0 = warp * chunk, c1 = min(n, c0 + chunk);
+  for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) s_hist[i] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = topk_idx[i];
-    if (e >= e_lo && e < e_hi) atomicAdd(&s_cnt[e], 1);
+  for (int base = c0; base < c1; base += 32) {
+    const int i = base + lane;
+    const int e = i < c1 ? topk_idx[i] : -1;
+    if (e >= e_lo && e < e_hi) atomicAdd(&s_hist[warp * E + e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < nwarps; ++w) {
+      const int c = s_hist[w * E + e];
+      s_hist[w * E + e] = run;
+      run += c;
+    }
+    s_cnt[e] = run;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -95,26 +114,23 @@ __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ 
   const int total = s_start[E];
   for (int i = threadIdx.x; i < max_rows; i += blockDim.x) if (i < total) packed_token[i] = -1;
   __syncthreads();
-  // stable placement: expert e's rows keep increasing pair order.  One warp per expert.
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int e = e_lo + warp; e < e_hi; e += nwarps) {
-    if (s_cnt[e] == 0) continue;
-    int pos = s_start[e];
-    for (int base = 0; base < n; base += 32) {
-      const int i = base + lane;
-      const bool hit = i < n && topk_idx[i] == e;
-      const unsigned mask = __ballot_sync(0xffffffffu, hit);
-      if (hit) {
-        const int dst = pos + __popc(mask & ((1u << lane) - 1));
-        packed_token[dst] = i / K;
-        pair_to_packed[i] = dst;
-      }
-      pos += __popc(mask);
+  for (int base = c0; base < c1; base += 32) {
+    const int i = base + lane;
+    const int e = i < c1 ? topk_idx[i] : -1;
+    const bool owned = e >= e_lo && e < e_hi;
+    const unsigned m = __match_any_sync(0xffffffffu, owned ? e : E + lane);
+    int cur = 0;
+    if (owned) cur = s_hist[warp * E + e];
+    __syncwarp();
+    if (owned) {
+      const int dst = s_start[e] + cur + __popc(m & ((1u << lane) - 1));
+      packed_token[dst] = i / K;
+      pair_to_packed[i] = dst;
+      if (lane == 31 - __clz(m)) s_hist[warp * E + e] = cur + __popc(m);      // the highest lane of the group advances the cursor
+    } else if (i < c1) {
+      pair_to_packed[i] = -1;
     }
-  }
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = topk_idx[i];
-    if (e < e_lo || e >= e_hi) pair_to_packed[i] = -1;
+    __syncwarp();
   }
 }
 
@@ -181,7 +197,10 @@ MX_HOST_API int mx_moe_route(const float* logits, const float* bias, int T, int 
 MX_HOST_API int mx_moe_pack(const int* topk_idx, int n_pairs, int K, int E, int e_lo, int e_hi, int* counts, int* seg_start,
                             int* packed_token, int* pair_to_packed, int* tile_expert, int* num_tiles, int max_rows, cudaStream_t st) {
   if (E > 1024) return -120;
-  moe_pack_kernel<<<1, 1024, 0, st>>>(topk_idx, n_pairs, K, E, e_lo, e_hi, counts, seg_start, packed_token, pair_to_packed, tile_expert,
+  const int pack_smem = 32 * E * (int)sizeof(int);
+  static bool pack_attr = false;
+  if (!pack_attr) { cudaFuncSetAttribute(moe_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * (int)sizeof(int)); pack_attr = true; }
+  moe_pack_kernel<<<1, 1024, pack_smem, st>>>(topk_idx, n_pairs, K, E, e_lo, e_hi, counts, seg_start, packed_token, pair_to_packed, tile_expert,
                                       num_tiles, max_rows);
   return (int)cudaGetLastError();
 }

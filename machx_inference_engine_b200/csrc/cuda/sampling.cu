@@ -53,6 +53,43 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __res
   if (threadIdx.x == 0) out[blockIdx.x] = best.i;
 }
 
+// Wide vocabularies: ARGMAX_CHUNKS CTAs per row reduce a slice each into a device scratch slot, and the last CTA of a
+// row to finish (ticket counter) reduces the partials.  `better` is a total order, so the result does not depend on
+// which CTA comes last.  The scratch is shared by all launches: callers issue argmax on one stream at a time.
+constexpr int ARGMAX_CHUNKS = 32;
+constexpr int ARGMAX_MAX_ROWS = 1024;
+__device__ ValIdx g_argmax_part[ARGMAX_MAX_ROWS * ARGMAX_CHUNKS];
+__device__ unsigned g_argmax_ticket[ARGMAX_MAX_ROWS];
+
+__global__ void __launch_bounds__(SAMP_THREADS) argmax_split_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out) {
+  __shared__ ValIdx sh[32];
+  __shared__ bool last;
+  const int r = blockIdx.y, c = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS, lo = c * per, hi = min(V, lo + per);
+  ValIdx best{-INFINITY, 0x7fffffff};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better(best, ValIdx{row[i], i});
+  best = block_argmax(best, sh);
+  if (threadIdx.x == 0) {
+    g_argmax_part[r * ARGMAX_CHUNKS + c] = best;
+    __threadfence();
+    last = atomicAdd(&g_argmax_ticket[r], 1u) == ARGMAX_CHUNKS - 1;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < 32) {
+    __threadfence();
+    ValIdx y = threadIdx.x < ARGMAX_CHUNKS ? g_argmax_part[r * ARGMAX_CHUNKS + threadIdx.x] : ValIdx{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ValIdx z;
+      z.v = __shfl_xor_sync(0xffffffffu, y.v, o);
+      z.i = __shfl_xor_sync(0xffffffffu, y.i, o);
+      y = better(y, z);
+    }
+    if (threadIdx.x == 0) { out[r] = y.i; g_argmax_ticket[r] = 0; }
+  }
+}
+
 // ids: [rows][max_ids] padded with -1; each id must appear at most once per row.
 __global__ void rep_penalty_kernel(float* __restrict__ logits, int V, int ld, const int* __restrict__ ids, int max_ids, const float* __restrict__ penalty) {
   const int r = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -147,7 +184,8 @@ using namespace mx;
 
 MX_HOST_API int mx_argmax(const float* logits, int rows, int V, int ld, int* out, cudaStream_t st) {
   if (rows <= 0) return 0;
-  argmax_kernel<<<rows, SAMP_THREADS, 0, st>>>(logits, V, ld, out);
+  if (V >= 32768 && rows <= ARGMAX_MAX_ROWS) argmax_split_kernel<<<dim3(ARGMAX_CHUNKS, rows), 256, 0, st>>>(logits, V, ld, out);
+  else argmax_kernel<<<rows, SAMP_THREADS, 0, st>>>(logits, V, ld, out);
   return (int)cudaGetLastError();
 }
 

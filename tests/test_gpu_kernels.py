@@ -241,6 +241,19 @@ def test_streaming_expert_gemv_with_foreign_experts():
     k.check_status()
 
 
+@pytest.mark.parametrize("E,K_top,T,rng", [(128, 4, 2048, (0, 128)), (512, 10, 700, (0, 512)), (8, 2, 5, (2, 6)), (32, 4, 1, (0, 32))])
+def test_moe_pack_is_a_stable_counting_sort(E, K_top, T, rng):
+    g = torch.Generator().manual_seed(E + T)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K_top] for _ in range(T)]).to(torch.int32).to(dev())
+    got = K().moe_pack(idx, E, rng[0], rng[1])
+    want = ref.moe_pack(idx.cpu(), E, rng[0], rng[1])
+    assert int(got.num_tiles[0]) == int(want.num_tiles[0]) and int(got.num_tiles[1]) == int(want.num_tiles[1])
+    rows = int(want.num_tiles[1])
+    assert torch.equal(got.packed_token[:rows].cpu(), want.packed_token[:rows])
+    assert torch.equal(got.pair_to_packed.cpu(), want.pair_to_packed)
+    assert torch.equal(got.tile_expert[:int(want.num_tiles[0])].cpu(), want.tile_expert[:int(want.num_tiles[0])])
+
+
 def test_rmsnorm_residual_and_saturation():
     T, H = 37, 2880
     x = torch.randn(T, H, device=dev()) * 3
@@ -363,6 +376,13 @@ def test_sampling():
     logits = torch.randn(4, V, device=dev())
     logits[0, 10] = logits[0, 4000] = 50.0       # tie -> lowest id
     assert K().argmax(logits).tolist() == ref.argmax(logits).tolist() and int(K().argmax(logits)[0]) == 10
+    # wide vocabulary: split reduction, ties across chunk borders still go to the lowest id, repeated calls reuse the scratch
+    wide = torch.randn(3, 201088, device=dev())
+    wide[1, 200000] = wide[1, 777] = 60.0
+    wide[2, 201087] = 70.0
+    for _ in range(3):
+        got = K().argmax(wide).tolist()
+        assert got == ref.argmax(wide).tolist() and got[1] == 777 and got[2] == 201087
     ids = torch.full((4, 6), -1, dtype=torch.int32, device=dev())
     ids[0, :3] = torch.tensor([10, 77, 4000])
     ids[2, :2] = torch.tensor([5, 6])
