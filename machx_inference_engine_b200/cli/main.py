@@ -105,7 +105,7 @@ def main(argv=None) -> int:
         from ..server.openai_server import run_openai_server
         if par.rank != 0:
             return _follower_loop(eng, par)
-        return run_openai_server(eng, eng.model_id, a.host, a.port)
+        return run_openai_server(eng, eng.model_id, a.host, a.port, par=par)
     # ---- REPL
     from ..runtime.engine import SamplingParams
     from ..tokenizer.templates import ChatTurn
@@ -134,7 +134,9 @@ def main(argv=None) -> int:
 def _follower_loop(eng, par) -> int:
     """Ranks > 0 of a multi-GPU server: they execute the same steps as rank 0.  Rank 0 broadcasts every admitted request
     (token ids + sampling) before the step that first schedules it; followers mirror the scheduler deterministically."""
-    raise SystemExit("multi-GPU serving is driven through runtime.multi.serve_spmd (one HTTP front end on rank 0)")
+    from ..runtime.api import EngineLoop
+    EngineLoop(eng, par).run()
+    return 0
 
 
 if __name__ == "__main__":

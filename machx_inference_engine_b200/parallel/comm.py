@@ -26,6 +26,7 @@ class ParallelCtx:
     group: Optional[object] = None
     fused: Optional[object] = None          # parallel.fused.FusedComm when the peer-memory path is on
     mode: str = "tp"                        # "tp": tensor/expert parallel, "pp": layer split
+    _ctrl: Optional[object] = None          # gloo group for host-side control messages (step plans)
 
     @property
     def enabled(self) -> bool:
@@ -59,6 +60,29 @@ class ParallelCtx:
     def barrier(self) -> None:
         if self.world > 1:
             dist.barrier(group=self.group)
+
+    def control_group(self):
+        """A gloo group over the same ranks: control-plane objects travel over TCP on the host, so ranks that wait for
+        the next step plan block in a socket read instead of spinning a GPU."""
+        if self.world == 1:
+            return None
+        if self._ctrl is None:
+            self._ctrl = dist.new_group(backend="gloo") if dist.get_backend() != "gloo" else (self.group or dist.group.WORLD)
+        return self._ctrl
+
+    def broadcast_object(self, obj, src: int = 0):
+        if self.world == 1:
+            return obj
+        box = [obj if self.rank == src else None]
+        dist.broadcast_object_list(box, src=src, group=self.control_group())
+        return box[0]
+
+    def send(self, t: torch.Tensor, dst: int) -> None:
+        dist.send(t, dst=dst, group=self.group)
+
+    def recv(self, t: torch.Tensor, src: int) -> torch.Tensor:
+        dist.recv(t, src=src, group=self.group)
+        return t
 
     def shard(self, n: int) -> tuple[int, int]:
         """Even [lo, hi) share of n items for this rank (n must divide)."""

@@ -163,11 +163,19 @@ class StreamState:
 
 class EngineLoop(threading.Thread):
     """Owns the LLMEngine on one thread; any number of client threads submit requests and receive token callbacks.
-    One bad request (too long, aborted client) never disturbs the others in the batch."""
+    One bad request (too long, aborted client) never disturbs the others in the batch.
 
-    def __init__(self, eng: Engine):
+    Multi-GPU serving is SPMD: every rank runs this loop over its shard of the model.  Rank 0 owns the HTTP front end;
+    before each iteration it broadcasts the step plan -- requests admitted and aborted since the last one, and whether to
+    step, idle or stop -- over the host-side control group, and every rank applies it in the same order.  Schedulers and
+    samplers are deterministic functions of that history (logits are bit-identical on all ranks after the rank-ordered
+    reductions), so the ranks stay in lockstep without exchanging tokens.  (The reference drives all GPUs from one host
+    thread, include/ie/engine.hpp:146-265; ranks > 0 call :meth:`run` directly as their whole job.)"""
+
+    def __init__(self, eng: Engine, par=None):
         super().__init__(daemon=True, name="engine-loop")
         self.eng = eng
+        self.par = par if (par is not None and par.world > 1) else None
         self.inbox: queue.Queue = queue.Queue()
         self.wake = threading.Event()
         self.stopping = False
@@ -187,51 +195,78 @@ class EngineLoop(threading.Thread):
         self.stopping = True
         self.wake.set()
 
+    def _plan(self, live: dict) -> dict:
+        """Rank 0: drain the inbox into a step plan.  Requests that cannot fit the context are answered here and never
+        reach the other ranks."""
+        new, tickets = [], []
+        while True:
+            try:
+                tk = self.inbox.get_nowait()
+            except queue.Empty:
+                break
+            self.metrics["requests"] += 1
+            if len(tk["ids"]) == 0 or len(tk["ids"]) >= self.eng.llm.opts.max_ctx - 8:
+                self.metrics["errors"] += 1
+                tk["on_done"](GenerateResult(finish_reason="context_length_exceeded", prompt_tokens=len(tk["ids"]),
+                                             error=f"prompt of {len(tk['ids'])} tokens does not fit the context of {self.eng.llm.opts.max_ctx}"))
+                continue
+            new.append((tk["ids"], tk["sp"]))
+            tickets.append(tk)
+        aborts = [sid for sid, (tk, st, t0) in live.items() if tk is not None and tk["abort"] and not tk["seq"].finished]
+        return {"new": new, "abort": aborts, "stop": self.stopping, "_tickets": tickets}
+
     def run(self) -> None:
         llm = self.eng.llm
         live: dict = {}
-        while not self.stopping:
-            # admit new requests
-            while True:
-                try:
-                    tk = self.inbox.get_nowait()
-                except queue.Empty:
-                    break
-                self.metrics["requests"] += 1
-                st = StreamState(self.eng, tk["on_text"])
-                t0 = time.perf_counter()
-                try:
-                    seq = llm.add_request(tk["ids"], tk["sp"], on_token=lambda s, t, st=st: st.on_token(t))
-                except ContextLengthExceeded as e:
-                    self.metrics["errors"] += 1
-                    tk["on_done"](GenerateResult(finish_reason="context_length_exceeded", error=str(e), prompt_tokens=len(tk["ids"])))
-                    continue
-                tk["seq"] = seq
-                live[seq.seq_id] = (tk, st, t0)
-            for sid, (tk, st, t0) in list(live.items()):
-                if tk["abort"] and not tk["seq"].finished:
-                    llm.abort(tk["seq"])
+        lead = self.par is None or self.par.rank == 0
+        while True:
+            plan = self._plan(live) if lead else None
+            if self.par is not None:
+                wire = None if plan is None else {k: v for k, v in plan.items() if k != "_tickets"}
+                wire = self.par.broadcast_object(wire, src=0)
+                plan = plan if lead else {**wire, "_tickets": [None] * len(wire["new"])}
+            if plan["stop"]:
+                break
+            for (ids, sp), tk in zip(plan["new"], plan["_tickets"]):
+                st = StreamState(self.eng, tk["on_text"] if tk else None)
+                seq = llm.add_request(ids, sp, on_token=(lambda s, t, st=st: st.on_token(t)) if tk else None)
+                if tk is not None:
+                    tk["seq"] = seq
+                    live[seq.seq_id] = (tk, st, time.perf_counter())
+                else:
+                    live[seq.seq_id] = (None, seq, 0.0)          # follower rank: keeps the sequence itself
+            for sid in plan["abort"]:
+                ent = live.get(sid)
+                seq = ent[0]["seq"] if (ent and ent[0] is not None) else (ent[1] if ent else None)
+                if seq is not None and not seq.finished:
+                    llm.abort(seq)
             self.metrics["queue_depth"] = len(llm.sched.waiting)
             if llm.has_work():
                 try:
                     llm.step()
                 except OutOfBlocks as e:
                     # shed the request that holds the most blocks; the rest of the batch continues
-                    victim = max((v[0]["seq"] for v in live.values() if not v[0]["seq"].finished), key=lambda s: len(s.tokens), default=None)
+                    seqs_live = [(v[0]["seq"] if v[0] is not None else v[1]) for v in live.values()]
+                    victim = max((s_ for s_ in seqs_live if not s_.finished), key=lambda s_: (len(s_.tokens), -s_.seq_id), default=None)
                     if victim is not None:
                         victim.finish_reason = "error"
                         llm.abort(victim)
                         victim.finish_reason = "error"
                 except Exception as e:      # a failed step fails the requests that were running, not the server
                     for tk, st, t0 in live.values():
-                        if not tk["seq"].finished:
-                            llm.abort(tk["seq"])
-                            tk["seq"].finish_reason = "error"
+                        seq = tk["seq"] if tk is not None else st
+                        if not seq.finished:
+                            llm.abort(seq)
+                            seq.finish_reason = "error"
                     print(f"[engine-loop] step failed: {e!r}", file=sys.stderr)
-            else:
-                self.wake.wait(timeout=0.05)
+            elif lead:
+                self.wake.wait(timeout=0.05 if self.par is None else 0.005)
                 self.wake.clear()
             for sid, (tk, st, t0) in list(live.items()):
+                if tk is None:                      # follower rank: nothing to report, just forget finished sequences
+                    if st.finished:
+                        del live[sid]
+                    continue
                 seq = tk["seq"]
                 if seq.finished:
                     res = st.result(seq, t0)

@@ -131,9 +131,10 @@ def make_handler(eng: Engine, loop: EngineLoop, model_id: str):
     return Handler
 
 
-def run_openai_server(eng: Engine, model_id: str, host: str = "127.0.0.1", port: int = 11435, ready: threading.Event | None = None):
-    """Binds first, then announces (a bind failure exits before any 'listening' line is printed)."""
-    loop = EngineLoop(eng)
+def run_openai_server(eng: Engine, model_id: str, host: str = "127.0.0.1", port: int = 11435, ready: threading.Event | None = None, par=None):
+    """Binds first, then announces (a bind failure exits before any 'listening' line is printed).  With ``par`` (a
+    multi-GPU job) this is rank 0's side of the SPMD serving loop; the other ranks run ``EngineLoop(eng, par).run()``."""
+    loop = EngineLoop(eng, par)
     try:
         httpd = ThreadingHTTPServer((host, port), make_handler(eng, loop, model_id))
     except OSError as e:

@@ -66,6 +66,35 @@ def test_tp2_on_cpu_ranks_matches_single_rank(name, quant):
     _close(one, two, cos=0.999, arg=0.95)
 
 
+def _run_spmd(world, mode, timeout=240):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    worker = os.path.join(HERE, "spmd_worker.py")
+    cmd = ([sys.executable, worker, mode] if world == 1 else
+           [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+            "--master-port", str(_free_port()), worker, mode])
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    for line in r.stdout.splitlines():
+        if line.startswith("RESULT "):
+            return json.loads(line[7:])
+    raise AssertionError(f"worker failed rc={r.returncode}\n{r.stdout[-2000:]}\n{r.stderr[-3000:]}")
+
+
+def test_spmd_serving_two_ranks_matches_one_rank():
+    """`ie serve --gpus N`: rank 0 admits requests and broadcasts step plans, the other ranks mirror them."""
+    one = _run_spmd(1, "serve")
+    two = _run_spmd(2, "serve")
+    assert one["ok"] and two["ok"] and two["world"] == 2
+    assert two["long"] == "context_length_exceeded" and two["gone"] == "abort"
+    assert two["a"][:3] == one["a"][:3] and two["b"][:3] == one["b"][:3] and len(two["a"]) == 8
+
+
+def test_rank_that_leaves_is_detected_not_waited_for():
+    """Failure detection on the host: a rank exits between steps; the survivor's next control-plane message ends with
+    an error inside the process-group timeout instead of blocking for ever."""
+    res = _run_spmd(2, "die", timeout=120)
+    assert res["detected"], res
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("name,quant", [("tiny-llama", "q4_k_m"), ("tiny-gpt-oss", "mxfp4"), ("tiny-qwen3moe", "q4_k_m")])
 def test_tp2_on_gpus_fused_and_nccl_match_single_gpu(name, quant):
