@@ -241,8 +241,8 @@ class HybridModel(TransformerModel):
     def __init__(self, cfg: ModelConfig, src, device, par: Optional[ParallelCtx] = None, max_ctx: int = 8192):
         super().__init__(cfg, src, device, par, max_ctx)
         self.one_plus_w = cfg.arch in ("qwen35", "qwen35moe")       # Qwen3-Next files already hold 1 + w
-        self.lin_layers = [l for l in range(cfg.n_layers) if not cfg.layer_is_full_attention(l)]
-        self.mtp = MtpHead(self, src) if (cfg.nextn_predict_layers > 0 and src.has(f"blk.{cfg.n_layers}.nextn.eh_proj.weight")) else None
+        self.lin_layers = [l for l in self.layer_ids if not cfg.layer_is_full_attention(l)]
+        self.mtp = MtpHead(self, src) if (cfg.nextn_predict_layers > 0 and not self.pp and src.has(f"blk.{cfg.n_layers}.nextn.eh_proj.weight")) else None
 
     def _build_layer(self, l: int, src) -> dict:
         c, par = self.cfg, self.par
@@ -262,7 +262,7 @@ class HybridModel(TransformerModel):
         return L
 
     def new_state(self, n_slots: int) -> DeltaNetState:
-        lin = self.layers[self.lin_layers[0]]["lin"]
+        lin = next(L["lin"] for L in self.layers if "lin" in L)
         return DeltaNetState(self.lin_layers, n_slots, lin.n_v, lin.C, lin.Kc, self.device)
 
     def forward(self, fb: ForwardBatch, kv: KVCache, state: Optional[DeltaNetState] = None, checkpoint: bool = False):

@@ -339,26 +339,32 @@ class TransformerModel:
         c, par = cfg, self.par
         self.max_ctx = max_ctx
         tp = par.world if par.mode == "tp" else 1
-        self.embed_w = src.matrix("token_embd.weight", c.vocab, c.hidden)
+        # layer split (pipeline) plan: contiguous layer ranges, embedding on the first rank, head on the last
+        # (LayerPlan::contiguous, src/model/dense_split.cpp:24-33)
+        self.pp = par.mode == "pp" and par.world > 1
+        self.layer_lo, self.layer_hi = ((par.rank * c.n_layers) // par.world, ((par.rank + 1) * c.n_layers) // par.world) if self.pp else (0, c.n_layers)
+        self.first_stage, self.last_stage = (not self.pp or par.rank == 0), (not self.pp or par.rank == par.world - 1)
         self.tied = not src.has("output.weight") or c.tie_embeddings
-        head = self.embed_w if self.tied else src.matrix("output.weight", c.vocab, c.hidden)
+        self.embed_w = src.matrix("token_embd.weight", c.vocab, c.hidden) if (self.first_stage or (self.last_stage and self.tied)) else None
+        head = None
+        if self.last_stage:
+            head = self.embed_w if self.tied else src.matrix("output.weight", c.vocab, c.hidden)
         self.vocab_lo, self.vocab_hi = 0, c.vocab
         if tp > 1:
             lo, hi = _even_chunks(c.vocab, tp, 16)[par.rank] if c.vocab % (16 * tp) == 0 else (0, c.vocab)
             if (lo, hi) != (0, c.vocab):
                 head = head.slice_rows(lo, hi)
                 self.vocab_lo, self.vocab_hi = lo, hi
-        self.lm_head = Linear(head)
+        self.lm_head = Linear(head) if head is not None else None
         self.out_norm = src.vector("output_norm.weight", c.hidden)
         ff = src.vector("rope_freqs.weight", c.n_rot // 2) if (c.arch == "llama" and getattr(src, "r", None) is not None and src.has("rope_freqs.weight")) else None
         self.rope = rope_tables(max_ctx, c.n_rot, c.rope_theta, ff, c.rope_scaling_type, c.rope_scaling_factor, c.rope_orig_ctx,
                                 c.yarn_beta_fast, c.yarn_beta_slow, device=self.device)
         self.one_plus_w = c.arch in ("qwen35", "qwen35moe")
-        self.layers = []
-        for l in range(c.n_layers):
-            self.layers.append(self._build_layer(l, src))
-        self.attn_layers = [l for l in range(c.n_layers) if c.layer_is_full_attention(l)]
-        self.n_kv_local = self.layers[self.attn_layers[0]]["attn"].n_kv if self.attn_layers else 0
+        self.layer_ids = list(range(self.layer_lo, self.layer_hi))
+        self.layers = [self._build_layer(l, src) for l in self.layer_ids]
+        self.attn_layers = [l for l in self.layer_ids if c.layer_is_full_attention(l)]
+        self.n_kv_local = next((L["attn"].n_kv for L in self.layers if "attn" in L), 0)
 
     # ---- construction
     def _build_layer(self, l: int, src) -> dict:
@@ -380,7 +386,7 @@ class TransformerModel:
         return KVCache(self.cfg.n_layers, num_blocks, self.n_kv_local, self.cfg.head_dim, self.device, self.attn_layers)
 
     def weight_bytes(self) -> int:
-        n = self.embed_w.nbytes + (0 if self.tied else self.lm_head.w.nbytes)
+        n = (self.embed_w.nbytes if self.embed_w is not None else 0) + (0 if (self.tied or self.lm_head is None) else self.lm_head.w.nbytes)
         for L in self.layers:
             for v in L.values():
                 n += _bytes_of(v)
@@ -389,15 +395,25 @@ class TransformerModel:
     # ---- forward
     def forward(self, fb: ForwardBatch, kv: KVCache, state=None) -> torch.Tensor:
         """Returns fp32 logits [rows, vocab] for ``fb.logit_rows`` (default: last token of each sequence)."""
-        c, par = self.cfg, self.par
+        if self.pp:
+            return self._forward_pipeline(fb, kv, state)
+        c = self.cfg
         x = ops.embed(self.embed_w, fb.ids, c.embedding_scale)
-        delta = None
-        rs = c.residual_scale
+        x, delta = self._run_layers(x, None, fb, kv, state)
+        return self._head(x, delta, fb)
+
+    def _run_layers(self, x, delta, fb, kv, state):
+        par = self.par
         for li, L in enumerate(self.layers):
             h = self._norm(x, L["attn_norm"], delta)
             a = self._mixer(li, L, h, fb, kv, state)
             h2 = self._norm(x, L["ffn_norm"], a)
             delta = L["moe"](h2, par) if "moe" in L else L["ffn"](h2, par)
+        return x, delta
+
+    def _head(self, x, delta, fb):
+        c, par = self.cfg, self.par
+        rs = c.residual_scale
         rows = fb.logit_rows if fb.logit_rows is not None else (fb.cu_q[1:].long() - 1)
         xr = x.index_select(0, rows)
         dr = delta.index_select(0, rows).contiguous()        # (a pending fused reduction is summed here)
@@ -413,6 +429,63 @@ class TransformerModel:
         if c.final_logit_softcap > 0:
             logits = torch.tanh(logits / c.final_logit_softcap) * c.final_logit_softcap
         return (logits, hidden) if fb.want_hidden else logits
+
+    # ---- layer-split (pipeline) forward
+    def _forward_pipeline(self, fb: ForwardBatch, kv: KVCache, state=None):
+        """Each rank runs its contiguous layer range.  A single long prefill chunk is cut into token micro-batches that
+        flow through the stages back to back (stage r works on micro-batch i while stage r+1 works on i-1; causal
+        attention only needs the earlier micro-batches' KV, which that stage has already written), so the stages
+        overlap instead of running strictly one after the other as in the reference (src/model/dense_split.cpp:258:
+        one residual hand-off per boundary, serial).  The residual crosses a boundary as one fp32 [T, H] message over
+        NCCL point-to-point; the last stage's logits are broadcast so that every rank samples the same token."""
+        c, par = self.cfg, self.par
+        if fb.want_hidden:
+            raise NotImplementedError("speculative decoding is not combined with the layer split")
+        rows = fb.logit_rows if fb.logit_rows is not None else (fb.cu_q[1:].long() - 1)
+        n_rows = rows.numel()
+        out = None
+        pieces = self._micro_batches(fb)
+        last_logits = []
+        for mb, keep in pieces:
+            if self.first_stage:
+                x = ops.embed(self.embed_w, mb.ids, c.embedding_scale)
+            else:
+                x = torch.empty(mb.T, c.hidden, dtype=torch.float32, device=self.device)
+                par.recv(x, par.rank - 1)
+            x, delta = self._run_layers(x, None, mb, kv, state)
+            if not self.last_stage:
+                d = delta if isinstance(delta, torch.Tensor) else delta.materialize()
+                x = x + d.to(torch.float32) * c.residual_scale
+                par.send(x.contiguous(), par.rank + 1)
+            elif keep:
+                last_logits.append(self._head(x, delta, mb))
+        logits = torch.empty(n_rows, c.vocab, dtype=torch.float32, device=self.device)
+        if self.last_stage:
+            logits.copy_(torch.cat(last_logits, dim=0) if len(last_logits) > 1 else last_logits[0])
+        par.broadcast(logits, src=par.world - 1)
+        return logits
+
+    def _micro_batches(self, fb: ForwardBatch, min_tokens: int = 256):
+        """[(ForwardBatch, has_logit_rows)].  Only a single-sequence prefill chunk is cut (into world-size pieces of at
+        least ``min_tokens``); mixed batches and decode steps go through whole."""
+        n = self.par.world
+        if fb.B != 1 or fb.T < 2 * min_tokens or fb.logit_rows is None or fb.state_slots is not None:
+            return [(fb, True)]
+        T = fb.T
+        per = max(min_tokens, (T + n - 1) // n)
+        per = (per + 127) // 128 * 128
+        kv_end = int(fb.seq_lens[0])
+        start = kv_end - T
+        out, rows = [], fb.logit_rows
+        for lo in range(0, T, per):
+            hi = min(T, lo + per)
+            sel = (rows >= lo) & (rows < hi)
+            lr = (rows[sel] - lo)
+            mb = ForwardBatch(fb.ids[lo:hi], fb.positions[lo:hi], fb.slot_map[lo:hi], fb.block_table,
+                              torch.tensor([start + hi], dtype=torch.int32, device=fb.ids.device),
+                              torch.tensor([0, hi - lo], dtype=torch.int32, device=fb.ids.device), hi - lo, logit_rows=lr if lr.numel() else None)
+            out.append((mb, lr.numel() > 0))
+        return out
 
     def _norm(self, x, w, delta):
         """Residual add + RMSNorm; a delta that still lives as per-rank partials in the collective inbox is summed here."""

@@ -104,4 +104,6 @@ def init_from_env(device_type: str = "cuda", timeout_s: int = 600) -> ParallelCt
         if device_type == "cuda":
             torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
         dist.init_process_group(backend=backend, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
-    return ParallelCtx(rank=rank, world=world, group=dist.group.WORLD)
+    # MX_PARALLEL=pp selects the layer split (pipeline) instead of tensor/expert parallelism
+    mode = "pp" if os.environ.get("MX_PARALLEL", "tp").lower() == "pp" else "tp"
+    return ParallelCtx(rank=rank, world=world, group=dist.group.WORLD, mode=mode)

@@ -21,6 +21,8 @@ from machx_inference_engine_b200.runtime.engine import EngineOptions, LLMEngine,
 def main():
     name, quant, device, comm = sys.argv[1], sys.argv[2], sys.argv[3], sys.argv[4]
     par = init_from_env("cuda" if device == "cuda" else "cpu", timeout_s=120)
+    if comm == "pp":
+        par.mode = "pp"
     if device == "cuda":
         dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(dev)
@@ -41,13 +43,28 @@ def main():
     kv = model.new_kv_cache(6)
     bt = torch.arange(1, 5, dtype=torch.int32, device=dev).unsqueeze(0)
 
+    hybrid = getattr(model, "needs_state", False)
+    st = model.new_state(2) if hybrid else None
+
     def fwd(lo, hi):
         pos = torch.arange(lo, hi, dtype=torch.int32, device=dev)
         slot = bt[0][(pos // KV_BLOCK).long()].long() * KV_BLOCK + (pos % KV_BLOCK).long()
         fb = ForwardBatch(torch.tensor(ids[lo:hi], dtype=torch.int32, device=dev), pos, slot, bt, torch.tensor([hi], dtype=torch.int32, device=dev),
                           torch.tensor([0, hi - lo], dtype=torch.int32, device=dev), hi - lo, logit_rows=torch.arange(hi - lo, device=dev))
+        if hybrid:
+            fb.state_slots, fb.state_slots_host, fb.start_host = torch.tensor([1], dtype=torch.int32, device=dev), [1], [lo]
+            return model.forward(fb, kv, st).float().cpu()
         return model.forward(fb, kv).float().cpu()
     logits = torch.cat([fwd(0, 200)] + [fwd(i, i + 1) for i in range(200, 208)])
+    if comm == "pp":
+        # a long single-sequence chunk goes through the stages as token micro-batches: same logits as one piece
+        ids = (ids * 3)[:600]
+        kv = model.new_kv_cache(8)
+        bt = torch.arange(1, 7, dtype=torch.int32, device=dev).unsqueeze(0)
+        whole = fwd(0, 600)
+        model._micro_batches = lambda fb, min_tokens=256: [(fb, True)]
+        kv = model.new_kv_cache(8)
+        logits = torch.cat([logits, whole, fwd(0, 600)])
     if par.rank == 0 and len(sys.argv) > 5:
         torch.save(logits, sys.argv[5])
     if device == "cuda":

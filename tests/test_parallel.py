@@ -66,6 +66,20 @@ def test_tp2_on_cpu_ranks_matches_single_rank(name, quant):
     _close(one, two, cos=0.999, arg=0.95)
 
 
+@pytest.mark.parametrize("name,quant", [("tiny-llama", "q8_0"), ("tiny-qwen3next", "q8_0")])
+def test_layer_split_on_cpu_ranks_matches_single_rank(name, quant):
+    """Pipeline (layer split) over two gloo ranks: same logits as one rank; micro-batched prefill equals whole-chunk prefill."""
+    one = _run(1, name, quant, "cpu")
+    two = _run(2, name, quant, "cpu", comm="pp")
+    n = one["logits"].shape[0]
+    pp = {"logits": two["logits"][:n], "tokens": two["tokens"]}
+    _close(one, pp, cos=0.9999, arg=0.97)
+    rest = two["logits"][n:]
+    if rest.numel():
+        half = rest.shape[0] // 2
+        assert torch.allclose(rest[:half], rest[half:], atol=2e-2, rtol=2e-2)
+
+
 def _run_spmd(world, mode, timeout=240):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
     worker = os.path.join(HERE, "spmd_worker.py")
