@@ -35,6 +35,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kprofile", action="store_true", help="per-op device time of one prefill")
     ap.add_argument("--kprofile-decode", action="store_true", help="per-op device time of the decode steps")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--spec-k", type=int, default=0, help="MTP self-speculative decode with this draft length (models with an MTP head)")
     ap.add_argument("--baseline-comm", action="store_true")
     ap.add_argument("--device", default="cuda")
     args = ap.parse_args(argv)
@@ -63,7 +64,7 @@ def main(argv=None) -> int:
         quant = args.quant or ("mxfp4" if cfg.arch == "gpt-oss" else "q4_k_m")
         model = build_model(cfg, dev, par, quant=quant, max_ctx=max_ctx)
     cfg = model.cfg
-    eng = LLMEngine(model, EngineOptions(max_ctx=max_ctx, max_batch_tokens=max(lens), max_seqs=1, enable_prefix_cache=False,
+    eng = LLMEngine(model, EngineOptions(max_ctx=max_ctx, max_batch_tokens=max(lens), max_seqs=1, enable_prefix_cache=False, spec_k=args.spec_k,
                                          cuda_graphs=cuda and not args.no_graphs and not args.kprofile_decode))
 
     def sync():
@@ -89,7 +90,7 @@ def main(argv=None) -> int:
         ids = synthetic_ids(P, cfg.vocab)
         pp = []
         for rep in range(max(1, args.repeat)):
-            seq = eng.add_request(ids, SamplingParams(max_tokens=args.decode + args.warmup_decode + 1, ignore_eos=True))
+            seq = eng.add_request(ids, SamplingParams(max_tokens=(args.decode + args.warmup_decode + 1) * (1 + args.spec_k), ignore_eos=True))
             if args.kprofile and rep == max(1, args.repeat) - 1:
                 profiler.start()
             pp.append(timed(eng.step))
@@ -104,16 +105,22 @@ def main(argv=None) -> int:
         if args.kprofile_decode:
             profiler.start()
 
+        gen0 = seq.n_generated
+
         def dec():
             for _ in range(args.decode):
                 eng.step()
         tg = timed(dec) if args.decode > 0 else 0.0
+        n_dec = max(seq.n_generated - gen0, 1)           # speculative rounds emit more than one token per step
         if args.kprofile_decode:
             profiler.stop()
             if par.rank == 0:
                 print(f"# kprofile decode ctx={P} steps={args.decode}\n" + KernelProfiler.format(profiler.harvest()), file=sys.stderr)
         eng.abort(seq)
-        rows.append((P, pp[0], min(pp), tg / max(args.decode, 1)))
+        rows.append((P, pp[0], min(pp), tg / n_dec))
+        if args.spec_k and par.rank == 0:
+            st = eng.stats
+            print(f"# spec: {st['spec_rounds']} rounds, {st['spec_accepted']}/{st['spec_drafted']} drafts accepted, {n_dec} tokens in {args.decode} steps", file=sys.stderr)
     if par.rank == 0:
         print("# T_pp\tpp_ms\tpp_tok_s\ttg_ms_tok\ttg_tok_s\tpp_first_ms")
         for P, first, best, tgms in rows:

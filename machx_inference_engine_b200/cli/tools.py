@@ -1,0 +1,206 @@
+"""Small validation and measurement tools (one entry point, sub-commands):
+
+    python -m machx_inference_engine_b200.cli.tools perplexity   --gguf M.gguf --text FILE | --tokens FILE [--ctx 2048]
+    python -m machx_inference_engine_b200.cli.tools det-probe    --gguf M.gguf | --model NAME  [--runs 3]
+    python -m machx_inference_engine_b200.cli.tools prompt-bench --gguf M.gguf [--runs 3]
+    python -m machx_inference_engine_b200.cli.tools chunk-check  --gguf M.gguf | --model NAME [--chunks 64,256]
+    python -m machx_inference_engine_b200.cli.tools soak         --gguf M.gguf | --model NAME --seconds 60
+
+Reference parity (behaviour, not code): tools/ie_perplexity.cpp (streaming negative log-likelihood), tools/ie_det_probe.cpp and
+ie_bug_monitor.cpp (run-to-run bit identity), tools/ie_prompt_bench.cpp (fixed prompts, first run discarded, median),
+tools/ie_validate_chunking.cpp (chunked prefill against whole-prompt prefill), scripts/soak_1h.sh (completions per hour, failures).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+PROMPTS = [
+    "Explain how a hash table handles collisions.",
+    "Write a short poem about the sea at night.",
+    "Summarise the causes of the French Revolution in three sentences.",
+    "What is the difference between a process and a thread?",
+    "Give me a recipe for a simple vegetable soup.",
+]
+
+
+def _load(a, max_ctx=4096, **opts):
+    from ..formats.model_config import preset
+    from ..models import build_model
+    from ..runtime.api import Engine
+    from ..runtime.engine import EngineOptions
+    dev = torch.device(a.device if (a.device != "cuda" or torch.cuda.is_available()) else "cpu")
+    eo = EngineOptions(max_ctx=max_ctx, **opts)
+    if a.gguf:
+        return Engine.load(a.gguf, dev, eo)
+    cfg = preset(a.model)
+    quant = a.quant or ("mxfp4" if cfg.arch == "gpt-oss" else "q8_0")
+    return Engine(build_model(cfg, dev, quant=quant, max_ctx=max_ctx), None, eo)
+
+
+def _all_logits(eng, ids, chunk):
+    """Teacher-forced logits [len(ids), vocab] obtained through the engine's scheduler with prefill chunks of `chunk` tokens."""
+    from ..runtime.engine import EngineOptions, LLMEngine, SamplingParams
+    m = eng.model
+    llm = LLMEngine(m, EngineOptions(max_ctx=eng.llm.opts.max_ctx, max_batch_tokens=chunk, max_seqs=1, enable_prefix_cache=False, cuda_graphs=False))
+    orig_build = llm._build_batch
+
+    def build(plan, sampled_rows, pad_to=0):          # ask for the logits of every row of every chunk
+        host, mq = orig_build(plan, sampled_rows, pad_to)
+        host["logit_rows"] = torch.arange(sum(k for _, k in plan), dtype=torch.int64)
+        return host, mq
+    llm._build_batch = build
+    llm._sample = lambda logits, seqs: torch.zeros(len(seqs), dtype=torch.int32)
+    grabbed = []
+    m_forward = m.forward
+
+    def grab(fb, *args, **kw):
+        if fb.logit_rows is None or fb.logit_rows.numel() != fb.T:
+            fb.logit_rows = torch.arange(fb.T, device=fb.ids.device)
+        out = m_forward(fb, *args, **kw)
+        grabbed.append((out[0] if isinstance(out, tuple) else out).float().cpu())
+        return out
+    m.forward = grab
+    seq = llm.add_request(list(ids), SamplingParams(max_tokens=1, ignore_eos=True))
+    try:
+        while not seq.finished:
+            llm.step()
+    finally:
+        m.forward = m_forward
+    return torch.cat(grabbed)[:len(ids)]
+
+
+def cmd_perplexity(a) -> int:
+    eng = _load(a, max_ctx=a.ctx + 128)
+    if a.tokens:
+        ids = [int(t) for t in open(a.tokens).read().split()]
+    elif a.text:
+        ids = eng.tok.encode(open(a.text, encoding="utf-8").read())
+    else:
+        g = torch.Generator().manual_seed(0)
+        ids = torch.randint(0, eng.cfg.vocab, (a.ctx,), generator=g).tolist()
+    nll, n = 0.0, 0
+    for lo in range(0, len(ids) - 1, a.ctx):
+        window = ids[lo:lo + a.ctx + 1]
+        if len(window) < 2:
+            break
+        logits = _all_logits(eng, window[:-1], a.chunk)
+        lp = torch.log_softmax(logits, dim=-1)
+        tgt = torch.tensor(window[1:])
+        nll -= float(lp[torch.arange(len(tgt)), tgt].sum())
+        n += len(tgt)
+    print(json.dumps({"tokens": n, "nll_per_token": round(nll / max(n, 1), 5), "perplexity": round(math.exp(nll / max(n, 1)), 4)}))
+    return 0
+
+
+def cmd_det_probe(a) -> int:
+    """The same prompt run several times must give bit-identical logits (reductions are in fixed order everywhere)."""
+    eng = _load(a, max_ctx=1024)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, eng.cfg.vocab, (a.tokens_n,), generator=g).tolist()
+    ref, diffs = None, []
+    for r in range(a.runs):
+        lg = _all_logits(eng, ids, a.chunk)
+        if ref is None:
+            ref = lg
+        else:
+            diffs.append(int((lg != ref).sum()))
+    ok = all(d == 0 for d in diffs)
+    print(json.dumps({"runs": a.runs, "positions": len(ids), "mismatching_logits_per_run": diffs, "bit_identical": ok}))
+    return 0 if ok else 1
+
+
+def cmd_chunk_check(a) -> int:
+    eng = _load(a, max_ctx=2048)
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, eng.cfg.vocab, (a.tokens_n,), generator=g).tolist()
+    whole = _all_logits(eng, ids, len(ids))
+    out = {}
+    for c in [int(x) for x in a.chunks.split(",")]:
+        lg = _all_logits(eng, ids, c)
+        cos = torch.nn.functional.cosine_similarity(whole, lg, dim=1)
+        out[str(c)] = {"cos_min": round(float(cos.min()), 6), "argmax_agree": round(float((whole.argmax(-1) == lg.argmax(-1)).float().mean()), 4)}
+    print(json.dumps({"positions": len(ids), "vs_whole_prompt": out}))
+    return 0 if all(v["cos_min"] > 0.99 for v in out.values()) else 1
+
+
+def cmd_prompt_bench(a) -> int:
+    from ..runtime.engine import SamplingParams
+    from ..tokenizer.templates import ChatTurn
+    eng = _load(a, max_ctx=4096)
+    rows = []
+    for p in PROMPTS:
+        pf, dc = [], []
+        for r in range(a.runs + 1):
+            if eng.tok is not None:
+                res = eng.chat([ChatTurn("user", p)], SamplingParams(max_tokens=a.max_tokens, temperature=0.0, ignore_eos=True))
+            else:
+                res = eng.generate([ord(ch) % eng.cfg.vocab for ch in p], SamplingParams(max_tokens=a.max_tokens, temperature=0.0, ignore_eos=True))
+            if r:                                   # the first run warms caches and graphs
+                pf.append(res.prefill_tok_s)
+                dc.append(res.decode_tok_s)
+        rows.append({"prompt": p[:32], "prefill_tok_s": round(statistics.median(pf), 1), "decode_tok_s": round(statistics.median(dc), 1)})
+    print(json.dumps({"runs": a.runs, "prompts": rows, "decode_tok_s_median": round(statistics.median(r["decode_tok_s"] for r in rows), 1)}))
+    return 0
+
+
+def cmd_soak(a) -> int:
+    from ..runtime.api import EngineLoop
+    from ..runtime.engine import SamplingParams
+    eng = _load(a, max_ctx=2048, max_seqs=8)
+    loop = EngineLoop(eng)
+    loop.start()
+    g = torch.Generator().manual_seed(3)
+    stats = {"ok": 0, "failed": 0, "tokens": 0}
+    lock = threading.Lock()
+    inflight = threading.Semaphore(a.concurrency)
+    t_end = time.time() + a.seconds
+
+    def done(res):
+        with lock:
+            good = res.finish_reason in ("length", "stop") and res.completion_tokens > 0
+            stats["ok" if good else "failed"] += 1
+            stats["tokens"] += res.completion_tokens
+        inflight.release()
+    while time.time() < t_end:
+        inflight.acquire()
+        n = int(torch.randint(8, 600, (1,), generator=g))
+        ids = torch.randint(0, eng.cfg.vocab, (n,), generator=g).tolist()
+        loop.submit(ids, SamplingParams(max_tokens=int(torch.randint(4, 64, (1,), generator=g)), temperature=0.0, ignore_eos=True), None, done)
+    for _ in range(a.concurrency):
+        inflight.acquire()
+    loop.stop()
+    print(json.dumps({"seconds": a.seconds, "completions": stats["ok"], "failures": stats["failed"], "tokens_out": stats["tokens"],
+                      "completions_per_hour": round(stats["ok"] * 3600 / a.seconds)}))
+    return 0 if stats["failed"] == 0 else 1
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="ie-tools")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    def common(p):
+        p.add_argument("--gguf", default=None)
+        p.add_argument("--model", default="tiny-llama")
+        p.add_argument("--quant", default=None)
+        p.add_argument("--device", default="cuda")
+        p.add_argument("--chunk", type=int, default=512)
+    p = sub.add_parser("perplexity"); common(p); p.add_argument("--text"); p.add_argument("--tokens"); p.add_argument("--ctx", type=int, default=2048)
+    p = sub.add_parser("det-probe"); common(p); p.add_argument("--runs", type=int, default=3); p.add_argument("--tokens-n", type=int, default=300)
+    p = sub.add_parser("chunk-check"); common(p); p.add_argument("--chunks", default="64,256"); p.add_argument("--tokens-n", type=int, default=700)
+    p = sub.add_parser("prompt-bench"); common(p); p.add_argument("--runs", type=int, default=3); p.add_argument("--max-tokens", type=int, default=64)
+    p = sub.add_parser("soak"); common(p); p.add_argument("--seconds", type=float, default=60); p.add_argument("--concurrency", type=int, default=4)
+    a = ap.parse_args(argv)
+    return {"perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
+            "soak": cmd_soak}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
