@@ -8,6 +8,7 @@
 // Reference parity: src/ops/moe.cpp:30-80,268-291,371-429, host router src/model/gptoss.cpp:23-47,
 // host packer src/model/qwen3moe_pack.cpp:5-31, reduce src/ops/moe_fused.cpp:1937-1961.
 #include "common.cuh"
+#include "comm.cuh"
 #include "host_util.h"
 
 namespace mx {
@@ -181,9 +182,47 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ yp, const i
   }
 }
 
+// Combine fused with the expert-parallel all-reduce: the weighted sum of this rank's expert outputs is stored straight into
+// slot [my_rank] of every rank's inbox (bf16 or fp32), and the last CTA publishes the sequence number (see comm.cuh).
+template <typename OT>
+__global__ void moe_combine_push_kernel(const __nv_bfloat16* __restrict__ yp, const int* __restrict__ pair_to_packed, const float* __restrict__ w,
+                                        int H, int K, PeerOut po) {
+  const int t = blockIdx.x;
+  const int next_seq = *po.seq + 1;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int pos = pair_to_packed[(size_t)t * K + k];
+      if (pos < 0) continue;
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(yp + (size_t)pos * H + i);
+      const float ww = w[(size_t)t * K + k];
+      a0 = fmaf(ww, bf16_lo(v), a0);
+      a1 = fmaf(ww, bf16_hi(v), a1);
+    }
+    for (int d = 0; d < po.world; ++d) {
+      if constexpr (sizeof(OT) == 4) *reinterpret_cast<float2*>(reinterpret_cast<float*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) = make_float2(a0, a1);
+      else *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) = pack_bf16(a0, a1);
+    }
+  }
+  peer_publish(po, next_seq);
+}
+
+PeerOut make_peer_out(const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket);
+
 }  // namespace mx
 
 using namespace mx;
+
+MX_HOST_API int mx_moe_combine_push(const void* yp, const int* pair_to_packed, const float* w, int out_f32, int T, int H, int K,
+                                    const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 2) return -101;
+  if ((long long)T * H * (out_f32 ? 4 : 2) > slot_bytes) return -140;
+  PeerOut po = make_peer_out(inbox, world, my_rank, slot_bytes, seq, ticket);
+  if (out_f32) moe_combine_push_kernel<float><<<T, 256, 0, st>>>((const __nv_bfloat16*)yp, pair_to_packed, w, H, K, po);
+  else moe_combine_push_kernel<__nv_bfloat16><<<T, 256, 0, st>>>((const __nv_bfloat16*)yp, pair_to_packed, w, H, K, po);
+  return (int)cudaGetLastError();
+}
 
 MX_HOST_API int mx_moe_route(const float* logits, const float* bias, int T, int E, int K, int renorm, int* topk_idx, float* topk_w,
                              cudaStream_t st) {

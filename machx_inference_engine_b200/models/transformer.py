@@ -300,6 +300,8 @@ class MoEFFN:
         logits = self.router(h, out_f32=True)
         idx, w = ops.moe_route(logits, self.router_bias, self.K, True)
         local = self.e_hi - self.e_lo
+        # expert parallelism on the peer-memory path: the combine writes its partial into every rank's inbox itself
+        fuse_push = self.reduce and par.fused is not None and h.is_cuda and self.shared is None
         if T <= 8:
             # decode: one GEMV slot per (token, expert) pair, weights streamed once per pair; under expert
             # parallelism the slots of experts that live on other ranks contribute zero rows here
@@ -311,6 +313,8 @@ class MoEFFN:
                 pk = ops.ref.MoePacking(None, None, torch.zeros(1, dtype=torch.int32, device=h.device),
                                         torch.arange(T * self.K, dtype=torch.int32, device=h.device), None, None, T * self.K, self.K)
                 self._arange[key] = pk
+            if fuse_push:
+                return par.fused.moe_combine_push(y, self._arange[key].pair_to_packed, w)
             out = ops.moe_combine(y, self._arange[key], w)
         else:
             pk = ops.moe_pack(idx, self.E, self.e_lo, self.e_hi)
@@ -318,6 +322,8 @@ class MoEFFN:
             te = pk.tile_expert - self.e_lo if self.e_lo else pk.tile_expert
             a = ops.grouped_linear(xp, self.gate_up, te, pk.num_tiles, bias=self.gu_bias, act=self.act)
             y = ops.grouped_linear(a, self.down, te, pk.num_tiles, bias=self.down_bias)
+            if fuse_push:
+                return par.fused.moe_combine_push(y, pk.pair_to_packed, w)
             out = ops.moe_combine(y, pk, w)
         if self.shared is not None:
             out = self.shared.add_into(out, h)

@@ -118,6 +118,17 @@ class FusedComm:
         K._count()
         return ReducedDelta(self, t.shape[0], t.shape[1], t.dtype == torch.bfloat16)
 
+    def moe_combine_push(self, yp: torch.Tensor, pair_to_packed: torch.Tensor, w: torch.Tensor) -> ReducedDelta:
+        """MoE combine fused with the expert-parallel all-reduce: sum_k w[t,k] * yp[pos(t,k)] goes straight into every rank's
+        inbox (fp32 for decode-sized batches, bf16 for prefill, like the row-parallel GEMM partials)."""
+        T, Kt = w.shape
+        H = yp.shape[1]
+        f32 = T <= K.GEMV_MAX_M
+        K._check(_lib.cuda().mx_moe_combine_push(K._p(yp), K._p(pair_to_packed), K._p(w), int(f32), T, H, Kt, self._ptr_array, self.world, self.rank,
+                                                 C.c_longlong(self.slot_bytes), K._p(self.seq), K._p(self.ticket), K._stream()), "moe_combine_push")
+        K._count()
+        return ReducedDelta(self, T, H, not f32)
+
     # ---- consumers -----------------------------------------------------------------------
     def reduce(self, d: ReducedDelta) -> torch.Tensor:
         out = torch.empty(d.T, d.H, dtype=torch.float32, device=self.device)
