@@ -161,8 +161,9 @@ def main():
         note(f"warmup prefill {i} done")
     barrier()
     K.check_status()
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local)       # samples through the timed prefill, the end-to-end pass and the timed decode
     sampler.start()
+    time.sleep(0.35)                    # let nvidia-smi come up: a five-step region can be shorter than its first sample
     l0 = K.launches()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -174,7 +175,6 @@ def main():
     prefill_ms = reduce_max_ms(ev0.elapsed_time(ev1)) / args.steps
     note(f"timed prefill done: {prefill_ms:.2f} ms/step")
     launches = K.launches() - l0
-    clocks = sampler.stop()
 
     # ---------------- end-to-end prefill through the public API with host wall clock (includes H2D of ids, D2H of the token)
     h0, d0 = eng.stats["h2d_bytes"], eng.stats["d2h_bytes"]
@@ -206,6 +206,7 @@ def main():
     dec_wall_ms = reduce_max_ms((time.perf_counter() - w0) * 1e3)
     dec_ms = reduce_max_ms(ev0.elapsed_time(ev1))
     note("decode done")
+    clocks = sampler.stop()
     eng.abort(seq)
     K.check_status()
 

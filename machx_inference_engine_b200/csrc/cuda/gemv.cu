@@ -230,6 +230,133 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_gated_kernel(const GemvP
   }
 }
 
+// Batched-decode MoE GEMV: blockIdx.y is a local expert; its weights are streamed once and multiplied with every row of
+// the compact packing that was routed to it (GRP_MM rows per pass; more rows take further passes).  A warp owns four weight
+// rows: four outputs in plain mode, or the gate and up rows of two features in gated mode.
+constexpr int GRP_MM = 8;
+
+struct GroupParams {
+  WeightRef w;
+  const __nv_bfloat16* x;    // rows addressed through x_index (gate|up: token rows in place) or by packed position (down)
+  const int* x_index;        // [packed rows] or null
+  __nv_bfloat16* y;          // [packed rows][N_out]
+  const float* bias;         // [E_local][N] or null
+  const int* counts;         // [E] rows per expert
+  const int* seg_start;      // [E+1] first packed row of each expert
+  int e_lo, N, K, act;
+  float act_alpha, act_limit;
+};
+
+template <int FMT, bool GATED>
+__global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_group_kernel(const GroupParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int el = blockIdx.y, e = p.e_lo + el;
+  const int cnt = p.counts[e];
+  if (cnt == 0) return;
+  const int start = p.seg_start[e];
+  const int unit = blockIdx.x * GEMV_WARPS + warp;          // plain: 4 consecutive rows; gated: 2 consecutive features
+  const int F = p.N / 2;
+  int rows[4];
+  if (GATED) {
+    const int f0 = unit * 2;
+    if (f0 >= F) return;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int f = min(f0 + j, F - 1);
+      rows[j] = 32 * (f >> 4) + (f & 15);
+      rows[2 + j] = rows[j] + 16;
+    }
+  } else {
+    if (unit * 4 >= p.N) return;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) rows[j] = min(unit * 4 + j, p.N - 1);
+  }
+  const WeightRef w = expert_weight<FMT>(p.w, el, p.N, p.K);
+  const float* bias = p.bias ? p.bias + (size_t)el * p.N : nullptr;
+  RowPtrs rp[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) rp[r] = row_ptrs<FMT>(w, rows[r], p.K);
+  const int nkb = p.K / 32;
+  for (int pass = 0; pass < cnt; pass += GRP_MM) {
+    const int mc = min(GRP_MM, cnt - pass);
+    const __nv_bfloat16* xr[GRP_MM];
+#pragma unroll
+    for (int m = 0; m < GRP_MM; ++m) {
+      const int pr = start + pass + min(m, mc - 1);
+      xr[m] = p.x + (size_t)(p.x_index ? p.x_index[pr] : pr) * p.K;
+    }
+    float acc[4][GRP_MM];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int m = 0; m < GRP_MM; ++m) acc[r][m] = 0.f;
+    for (int kb = lane; kb < nkb; kb += 32) {
+      float wv[4][32];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) decode32_f32<FMT>(rp[r], kb, wv[r]);
+#pragma unroll
+      for (int m = 0; m < GRP_MM; ++m) {
+        if (m < mc) {
+          const uint4* xp = reinterpret_cast<const uint4*>(xr[m] + (size_t)kb * 32);
+          float xv[32];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 v = __ldg(xp + i);
+            xv[8 * i + 0] = bf16_lo(v.x); xv[8 * i + 1] = bf16_hi(v.x); xv[8 * i + 2] = bf16_lo(v.y); xv[8 * i + 3] = bf16_hi(v.y);
+            xv[8 * i + 4] = bf16_lo(v.z); xv[8 * i + 5] = bf16_hi(v.z); xv[8 * i + 6] = bf16_lo(v.w); xv[8 * i + 7] = bf16_hi(v.w);
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) s = fmaf(wv[r][i], xv[i], s);
+            acc[r][m] += s;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int m = 0; m < GRP_MM; ++m) acc[r][m] = warp_sum(acc[r][m]);
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < GRP_MM; ++m) {
+        if (m >= mc) break;
+        const size_t orow = (size_t)(start + pass + m);
+        if (GATED) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int f = unit * 2 + j;
+            if (f >= F) break;
+            const float g = acc[j][m] + (bias ? bias[rows[j]] : 0.f), u = acc[2 + j][m] + (bias ? bias[rows[2 + j]] : 0.f);
+            p.y[orow * F + f] = __float2bfloat16(gemv_act(p.act, g, u, p.act_alpha, p.act_limit));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = unit * 4 + j;
+            if (n >= p.N) break;
+            p.y[orow * p.N + n] = __float2bfloat16(acc[j][m] + (bias ? bias[n] : 0.f));
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int FMT>
+static int launch_group(const GroupParams& p, int n_experts, cudaStream_t st) {
+  if (p.act != 0) {
+    const int units = (p.N / 2 + 1) / 2;
+    gemv_group_kernel<FMT, true><<<dim3((units + GEMV_WARPS - 1) / GEMV_WARPS, n_experts), GEMV_WARPS * 32, 0, st>>>(p);
+  } else {
+    const int units = (p.N + 3) / 4;
+    gemv_group_kernel<FMT, false><<<dim3((units + GEMV_WARPS - 1) / GEMV_WARPS, n_experts), GEMV_WARPS * 32, 0, st>>>(p);
+  }
+  return (int)cudaGetLastError();
+}
+
 template <int FMT>
 static int launch_gemv(const GemvParams& p, int slots, cudaStream_t st) {
   if (p.act != 0) {
@@ -258,6 +385,28 @@ MX_HOST_API int mx_gemv(int wfmt, const void* w0, const void* w1, const void* w2
                         const float* bias, int M, int N, int K, int out_f32, int act, float act_alpha, float act_limit,
                         const int* slot_expert, const float* slot_scale, int slots, int x_div, cudaStream_t stream) {
   return gemv_impl(wfmt, w0, w1, w2, w3, x, y, bias, M, N, K, out_f32, act, act_alpha, act_limit, slot_expert, slot_scale, slots, x_div, nullptr, stream);
+}
+
+// Expert-major GEMV over a compact packing (see gemv_group_kernel).  counts / seg_start are indexed by global expert id.
+MX_HOST_API int mx_gemv_group(int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const void* x, const int* x_index, void* y,
+                              const float* bias, int N, int K, int act, float act_alpha, float act_limit, const int* counts, const int* seg_start,
+                              int e_lo, int n_experts, cudaStream_t stream) {
+  using namespace mx;
+  if (N <= 0 || K <= 0 || n_experts <= 0) return 0;
+  if (K % 32) return -102;
+  if ((wfmt == WF_Q4K || wfmt == WF_Q6K) && (K % 256)) return -103;
+  if (act != 0 && (N % 32)) return -104;
+  GroupParams p;
+  p.w = WeightRef{w0, w1, w2, w3}; p.x = (const __nv_bfloat16*)x; p.x_index = x_index; p.y = (__nv_bfloat16*)y; p.bias = bias;
+  p.counts = counts; p.seg_start = seg_start; p.e_lo = e_lo; p.N = N; p.K = K; p.act = act; p.act_alpha = act_alpha; p.act_limit = act_limit;
+  switch (wfmt) {
+    case WF_BF16: return launch_group<WF_BF16>(p, n_experts, stream);
+    case WF_Q8: return launch_group<WF_Q8>(p, n_experts, stream);
+    case WF_Q4K: return launch_group<WF_Q4K>(p, n_experts, stream);
+    case WF_Q6K: return launch_group<WF_Q6K>(p, n_experts, stream);
+    case WF_MXFP4: return launch_group<WF_MXFP4>(p, n_experts, stream);
+    default: return -100;
+  }
 }
 
 static int g_e_lo = 0, g_e_hi = 1 << 30;

@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ topk_idx, int n, int K, int E, int e_lo, int e_hi,
                                                         int* __restrict__ counts, int* __restrict__ seg_start, int* __restrict__ packed_token,
                                                         int* __restrict__ pair_to_packed, int* __restrict__ tile_expert, int* __restrict__ num_tiles,
-                                                        int max_rows) {
+                                                        int max_rows, int tile) {
   extern __shared__ int s_hist[];            // [nwarps][E]
   __shared__ int s_cnt[1024];
   __shared__ int s_start[1025];
@@ -102,8 +102,9 @@ __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ 
     int off = 0, tiles = 0;
     for (int e = 0; e < E; ++e) {
       s_start[e] = off;
-      const int padded = (s_cnt[e] + MOE_TILE - 1) / MOE_TILE * MOE_TILE;
-      for (int tix = 0; tix < padded / MOE_TILE; ++tix) tile_expert[tiles++] = e;
+      // tile = 128: segments padded to whole GEMM tiles and a tile -> expert map; tile = 1: compact segments (GEMV path)
+      const int padded = (s_cnt[e] + tile - 1) / tile * tile;
+      if (tile > 1) for (int tix = 0; tix < padded / tile; ++tix) tile_expert[tiles++] = e;
       off += padded;
     }
     s_start[E] = off;
@@ -234,13 +235,13 @@ MX_HOST_API int mx_moe_route(const float* logits, const float* bias, int T, int 
 
 // num_tiles must hold 2 ints: [0] live 128-row tiles, [1] packed row count.
 MX_HOST_API int mx_moe_pack(const int* topk_idx, int n_pairs, int K, int E, int e_lo, int e_hi, int* counts, int* seg_start,
-                            int* packed_token, int* pair_to_packed, int* tile_expert, int* num_tiles, int max_rows, cudaStream_t st) {
-  if (E > 1024) return -120;
+                            int* packed_token, int* pair_to_packed, int* tile_expert, int* num_tiles, int max_rows, int tile, cudaStream_t st) {
+  if (E > 1024 || (tile != 1 && tile != MOE_TILE)) return -120;
   const int pack_smem = 32 * E * (int)sizeof(int);
   static bool pack_attr = false;
   if (!pack_attr) { cudaFuncSetAttribute(moe_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * (int)sizeof(int)); pack_attr = true; }
   moe_pack_kernel<<<1, 1024, pack_smem, st>>>(topk_idx, n_pairs, K, E, e_lo, e_hi, counts, seg_start, packed_token, pair_to_packed, tile_expert,
-                                      num_tiles, max_rows);
+                                      num_tiles, max_rows, tile);
   return (int)cudaGetLastError();
 }
 

@@ -14,7 +14,7 @@ from .weights import QuantWeight, WFormat, from_dense, from_ggml
 from ..utils.profiler import profiler as _prof
 
 _NAMES = [
-    "embed", "rmsnorm", "glu", "sigmoid_mul", "scaled_add", "gated_rmsnorm", "qkv_post", "linear", "grouped_linear", "expert_gemv",
+    "embed", "rmsnorm", "glu", "sigmoid_mul", "scaled_add", "gated_rmsnorm", "qkv_post", "linear", "grouped_linear", "expert_gemv", "expert_group_gemv",
     "attention", "gated_rmsnorm_heads", "conv1d_silu", "deltanet_scan", "moe_route", "moe_pack", "moe_gather", "moe_combine", "argmax", "rep_penalty", "sample",
 ]
 

@@ -315,22 +315,36 @@ def moe_route(logits, bias, k, renorm=True):
     return idx, w
 
 
-def moe_pack(topk_idx, E, e_lo=0, e_hi=None):
+def moe_pack(topk_idx, E, e_lo=0, e_hi=None, tile=MOE_TILE):
     e_hi = E if e_hi is None else e_hi
     T, K = topk_idx.shape
     dev = topk_idx.device
     n = T * K
-    max_rows = moe_max_rows(n, e_hi - e_lo)
+    max_rows = moe_max_rows(n, e_hi - e_lo) if tile > 1 else max(n, 1)
     counts = torch.empty(E, dtype=torch.int32, device=dev)
     seg = torch.empty(E + 1, dtype=torch.int32, device=dev)
     packed_token = torch.empty(max_rows, dtype=torch.int32, device=dev)
     pair_to_packed = torch.empty(n, dtype=torch.int32, device=dev)
-    tile_expert = torch.zeros(max_rows // MOE_TILE, dtype=torch.int32, device=dev)
+    tile_expert = torch.zeros(max(max_rows // MOE_TILE, 1), dtype=torch.int32, device=dev)
     num_tiles = torch.empty(2, dtype=torch.int32, device=dev)
     _check(_lib.cuda().mx_moe_pack(_p(topk_idx), n, K, E, e_lo, e_hi, _p(counts), _p(seg), _p(packed_token), _p(pair_to_packed),
-                                   _p(tile_expert), _p(num_tiles), max_rows, _stream()), "moe_pack")
+                                   _p(tile_expert), _p(num_tiles), max_rows, int(tile), _stream()), "moe_pack")
     _count()
     return MoePacking(counts, seg, packed_token, pair_to_packed, tile_expert, num_tiles, max_rows, K)
+
+
+def expert_group_gemv(x, w: QuantWeight, pk: MoePacking, x_index=None, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, e_lo=0):
+    """Batched-decode MoE GEMV over a compact packing (``moe_pack(..., tile=1)``): every local expert streams its weights once
+    and multiplies them with all rows routed to it (8 rows per pass).  Row r of the output belongs to packed position r;
+    its input is ``x[x_index[r]]`` (gate|up reads the token rows in place) or ``x[r]`` (down)."""
+    P = pk.max_rows
+    n_out = w.N // 2 if act != ACT_NONE else w.N
+    out = torch.empty(P, n_out, dtype=torch.bfloat16, device=x.device)
+    fmt, p0, p1, p2, p3 = _planes(w)
+    _check(_lib.cuda().mx_gemv_group(fmt, p0, p1, p2, p3, _p(x), _p(x_index), _p(out), _p(bias), w.N, w.K, act, C.c_float(act_alpha),
+                                     C.c_float(act_limit), _p(pk.counts), _p(pk.seg_start), int(e_lo), w.E, _stream()), "gemv_group")
+    _count()
+    return out
 
 
 def moe_gather(x, pk: MoePacking, f16=False):

@@ -327,16 +327,17 @@ def moe_max_rows(n_pairs: int, n_local_experts: int) -> int:
     return (n_pairs + n_local_experts * (MOE_TILE - 1) + MOE_TILE - 1) // MOE_TILE * MOE_TILE
 
 
-def moe_pack(topk_idx, E, e_lo=0, e_hi=None):
+def moe_pack(topk_idx, E, e_lo=0, e_hi=None, tile=MOE_TILE):
+    """``tile`` = 128: segments padded to GEMM tiles; ``tile`` = 1: compact segments (batched-decode GEMV path)."""
     e_hi = E if e_hi is None else e_hi
     T, K = topk_idx.shape
     dev = topk_idx.device
     flat = topk_idx.reshape(-1).long()
     n = flat.numel()
-    max_rows = moe_max_rows(n, e_hi - e_lo)
+    max_rows = moe_max_rows(n, e_hi - e_lo) if tile > 1 else max(n, 1)
     owned = (flat >= e_lo) & (flat < e_hi)
     counts = torch.bincount(flat[owned], minlength=E)[:E]
-    padded = (counts + MOE_TILE - 1) // MOE_TILE * MOE_TILE
+    padded = (counts + tile - 1) // tile * tile
     seg = torch.zeros(E + 1, dtype=torch.long, device=dev)
     seg[1:] = torch.cumsum(padded, 0)
     packed_token = torch.full((max_rows,), -1, dtype=torch.int32, device=dev)
@@ -349,9 +350,9 @@ def moe_pack(topk_idx, E, e_lo=0, e_hi=None):
     dst = seg[e_sorted] + rank_in_e
     packed_token[dst] = (order // K).to(torch.int32)
     pair_to_packed[order] = dst.to(torch.int32)
-    tiles = (padded // MOE_TILE)
+    tiles = (padded // MOE_TILE) if tile > 1 else torch.zeros_like(padded)
     tile_expert = torch.repeat_interleave(torch.arange(E, device=dev), tiles).to(torch.int32)
-    max_tiles = max_rows // MOE_TILE
+    max_tiles = max(max_rows // MOE_TILE, 1)
     te = torch.zeros(max_tiles, dtype=torch.int32, device=dev)
     te[: tile_expert.numel()] = tile_expert
     num_tiles = torch.tensor([int(tiles.sum()), int(seg[E])], dtype=torch.int32, device=dev)
@@ -363,6 +364,30 @@ def moe_gather(x, pk: MoePacking, f16=False):
     ok = pk.packed_token >= 0
     xp[ok] = x[pk.packed_token[ok].long()].to(xp.dtype)
     return xp
+
+
+def expert_group_gemv(x, w: QuantWeight, pk: MoePacking, x_index=None, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, e_lo=0):
+    """y[r] = W[expert of packed row r] @ x[x_index[r] or r] over a compact packing; bf16 [max_rows, N_out]."""
+    W = _dense(w)
+    P = pk.max_rows
+    n_out = w.N // 2 if act != ACT_NONE else w.N
+    out = torch.zeros(P, n_out, dtype=torch.float32, device=x.device)
+    xf = x.to(torch.float32)
+    for el in range(w.E):
+        e = e_lo + el
+        c, s0 = int(pk.counts[e]), int(pk.seg_start[e])
+        if c == 0:
+            continue
+        rows = torch.arange(s0, s0 + c, device=x.device)
+        xin = xf[x_index[rows].long()] if x_index is not None else xf[rows]
+        y = xin @ W[el].T
+        if bias is not None:
+            y = y + bias[el]
+        if act != ACT_NONE:
+            g, u = _deinterleave16(y)
+            y = _act(act, g, u, act_alpha, act_limit)
+        out[rows] = y
+    return out.to(torch.bfloat16)
 
 
 def moe_combine(yp, pk: MoePacking, w, out=None, accumulate=False):

@@ -177,6 +177,7 @@ class EngineOptions:
     graph_batch_sizes: tuple = (1, 2, 4, 8, 16, 32, 64)
     eos_ids: tuple = ()
     spec_k: int = 0                     # MTP draft length (hybrid models with an MTP head)
+    prefill_graphs: bool = True         # replay single-sequence prefill chunks of 512/1024/2048/4096/8192 tokens (or the full step budget) as CUDA graphs
 
 
 class Scheduler:
@@ -423,6 +424,10 @@ class LLMEngine:
                      and len(plan) <= max(self.opts.graph_batch_sizes) and not nccl_path and not self.spec_k)
         if use_graph:
             return self._run_graph(plan)
+        if (self.opts.cuda_graphs and self.opts.prefill_graphs and self.device.type == "cuda" and not nccl_path and len(plan) == 1
+                and (plan[0][1] in (512, 1024, 2048, 4096, 8192) or (plan[0][1] == self.opts.max_batch_tokens and plan[0][1] % KV_BLOCK == 0
+                                                                      and plan[0][1] >= 256)) and not self.spec_k):
+            return self._run_prefill_graph(plan, sampled_rows, seqs)
         host, max_q = self._build_batch(plan, sampled_rows)
         dev = self._to_device(host)
         fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], max_q,
@@ -533,16 +538,51 @@ class LLMEngine:
             g["in"][k].copy_(v.pin_memory(), non_blocking=True)
             self.stats["h2d_bytes"] += v.numel() * v.element_size()
         g["graph"].replay()
+        from ..ops import cuda as kernels
+        kernels._count(g["kernels"])
         self.stats["graph_replays"] += 1
         out = g["out"].cpu()
         self.stats["d2h_bytes"] += out.numel() * 4
         return out[:B].tolist()
 
-    def _capture(self, gb: int, host: dict) -> dict:
+    # ------------------------------------------------------------------ CUDA-graphed prefill chunks
+    def _run_prefill_graph(self, plan: list, sampled_rows: list, seqs: list) -> list:
+        """A single-sequence prefill chunk of n tokens (n a multiple of the KV block) has fixed shapes: its whole forward is one
+        graph replay.  With tensor parallelism the per-kernel GPU time shrinks with the rank count while the host cost of
+        ~500 launches does not, so an eager prefill becomes launch-bound; the graph removes that floor."""
+        seq, n = plan[0]
+        host, max_q = self._build_batch(plan, [0])            # always one logit row: the chunk's last token
+        key = ("prefill", n)
+        g = self._graphs.get(key)
+        if self.state is not None and seq.n_computed == 0:
+            self.state.reset([seq.state_slot])
+        if g is None:
+            g = self._capture(n, host, prefill_tokens=n)
+            self._graphs[key] = g
+        for k, v in host.items():
+            g["in"][k].copy_(v.pin_memory(), non_blocking=True)
+            self.stats["h2d_bytes"] += v.numel() * v.element_size()
+        g["graph"].replay()
+        from ..ops import cuda as kernels
+        kernels._count(g["kernels"])
+        self.stats["graph_replays"] += 1
+        if not sampled_rows:
+            return []
+        toks = self._sample(g["logits"], seqs).cpu()
+        self.stats["d2h_bytes"] += toks.numel() * 4
+        return toks.tolist()
+
+    def _capture(self, gb: int, host: dict, prefill_tokens: int = 0) -> dict:
         dev = {k: v.to(self.device) for k, v in host.items()}
-        fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], 1,
+        fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], prefill_tokens or 1,
                           logit_rows=dev["logit_rows"], state_slots=dev.get("state_slots"))
         fwd = (lambda: self.model.forward(fb, self.kv, self.state)) if self.state is not None else (lambda: self.model.forward(fb, self.kv))
+        if prefill_tokens:
+            return self._capture_with(fwd, dev, host, argmax=False)
+        return self._capture_with(fwd, dev, host, argmax=True)
+
+    def _capture_with(self, fwd, dev: dict, host: dict, argmax: bool) -> dict:
+        post = ops.argmax if argmax else (lambda t: t)
         snap = None
         if self.state is not None:
             # the warm-up and capture forwards advance the recurrent state of the slots in this batch: put it back afterwards
@@ -553,18 +593,21 @@ class LLMEngine:
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
             for _ in range(2):
-                ops.argmax(fwd())
+                post(fwd())
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        from ..ops import cuda as kernels
+        n0 = kernels.launches()
         with torch.cuda.graph(graph, pool=self._graph_pool):
-            out = ops.argmax(fwd())
+            out = post(fwd())
+        n_kernels = kernels.launches() - n0          # kernels recorded in the graph: every replay launches them again
         if snap is not None:
             for sl, sn in snap.items():
                 self.state.restore(sl, sn)
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        return {"graph": graph, "in": dev, "out": out}
+        return {"graph": graph, "in": dev, "out": out, "logits": out, "kernels": n_kernels}
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: list, params: Optional[SamplingParams] = None) -> list:

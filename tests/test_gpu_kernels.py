@@ -254,6 +254,39 @@ def test_moe_pack_is_a_stable_counting_sort(E, K_top, T, rng):
     assert torch.equal(got.tile_expert[:int(want.num_tiles[0])].cpu(), want.tile_expert[:int(want.num_tiles[0])])
 
 
+@pytest.mark.parametrize("fmt", [WFormat.MXFP4, WFormat.Q8, WFormat.Q4K])
+def test_expert_group_gemv_batched_decode(fmt):
+    """Compact packing + expert-major GEMV (the MoE path for decode batches of 9..512 tokens) against the oracle, including an
+    expert with more than eight rows (two passes), empty experts and an expert-parallel shard."""
+    k = K()
+    E, H, F, topk, T = 16, 512, 256, 4, 40
+    gu = make_weight(fmt, 2 * F, H, E=E, seed=3)
+    dn = make_weight(fmt, H, F, E=E, seed=4)
+    gub, dnb = torch.randn(E, 2 * F, device=dev()), torch.randn(E, H, device=dev())
+    g = torch.Generator().manual_seed(9)
+    idx = torch.stack([torch.randperm(E - 3, generator=g)[:topk] for _ in range(T)]).to(torch.int32)     # experts 13..15 stay empty
+    idx[:20, 0] = 2                                                                                      # expert 2 gets >= 20 rows
+    idx[:20, 1:] = torch.stack([torch.randperm(E - 4, generator=g)[:topk - 1] + 3 for _ in range(20)]).to(torch.int32)
+    idx = idx.to(dev())
+    x = torch.randn(T, H, device=dev()).to(torch.bfloat16)
+    for e_lo, e_hi in [(0, E), (0, 8)]:
+        pk = k.moe_pack(idx, E, e_lo, e_hi, tile=1)
+        pk_ref = ref.moe_pack(idx.cpu(), E, e_lo, e_hi, tile=1)
+        n_rows = int(pk_ref.num_tiles[1])
+        assert torch.equal(pk.pair_to_packed.cpu(), pk_ref.pair_to_packed) and torch.equal(pk.packed_token[:n_rows].cpu(), pk_ref.packed_token[:n_rows])
+        gs, ds = gu.slice_experts(e_lo, e_hi), dn.slice_experts(e_lo, e_hi)
+        gb, db = gub[e_lo:e_hi].contiguous(), dnb[e_lo:e_hi].contiguous()
+        a = k.expert_group_gemv(x, gs, pk, x_index=pk.packed_token, bias=gb, act=ref.ACT_SWIGLU_OAI, e_lo=e_lo)
+        a_ref = ref.expert_group_gemv(x, gs, pk, x_index=pk.packed_token, bias=gb, act=ref.ACT_SWIGLU_OAI, e_lo=e_lo)
+        assert rel_err(a[:n_rows], a_ref[:n_rows]) < 1e-2
+        y = k.expert_group_gemv(a_ref, ds, pk, bias=db, e_lo=e_lo)
+        y_ref = ref.expert_group_gemv(a_ref, ds, pk, bias=db, e_lo=e_lo)
+        assert rel_err(y[:n_rows], y_ref[:n_rows]) < 1e-2
+        w = torch.rand(T, topk, device=dev())
+        assert rel_err(k.moe_combine(y_ref, pk, w), ref.moe_combine(y_ref, pk, w)) < 1e-3
+    k.check_status()
+
+
 def test_rmsnorm_residual_and_saturation():
     T, H = 37, 2880
     x = torch.randn(T, H, device=dev()) * 3

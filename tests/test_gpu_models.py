@@ -53,3 +53,38 @@ def test_logits_cosine_prefill_and_graph_decode():
     assert _cos(res["cpu"], res["cuda:0"]) > 0.999
     agree = (res["cpu"].argmax(-1) == res["cuda:0"].argmax(-1)).float().mean()
     assert agree > 0.95
+
+
+def test_batched_decode_moe_path_matches_single_sequence():
+    """Sixteen sequences decoding together, on the grouped-GEMM path and on the expert-major GEMV path; each must produce what
+    it produces alone."""
+    cfg = preset("tiny-gpt-oss")
+    model = build_model(cfg, torch.device("cuda:0"), quant="mxfp4", max_ctx=512, gen_device="cpu")
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab, (int(n),), generator=g).tolist() for n in torch.randint(5, 60, (16,), generator=g)]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    alone = [LLMEngine(model, EngineOptions(max_ctx=512, max_seqs=1)).generate([p], sp)[0] for p in prompts[:6]]
+    for limit in (0, 64):
+        for L in model.layers:
+            L["moe"].group_gemv_max_tokens = limit
+        together = LLMEngine(model, EngineOptions(max_ctx=512, max_seqs=16, max_batch_tokens=2048)).generate(prompts, sp)
+        same = sum(int(a == b) for x, y in zip(alone, together) for a, b in zip(x, y))
+        assert all(x[0] == y[0] for x, y in zip(alone, together)) and same >= 0.8 * sum(len(x) for x in alone), limit
+
+
+@pytest.mark.parametrize("name,quant", [("tiny-gpt-oss", "mxfp4"), ("tiny-qwen3next", "q8_0")])
+def test_graphed_prefill_chunks_match_eager(name, quant):
+    """Prompts whose chunks have graphable sizes (512 / 1024 tokens) go through CUDA-graph replays, twice, and must produce the
+    tokens of the eager path."""
+    cfg = preset(name)
+    model = build_model(cfg, torch.device("cuda:0"), quant=quant, max_ctx=2048, gen_device="cpu")
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (512, 1024 + 37, 512)]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    eager = LLMEngine(model, EngineOptions(max_ctx=2048, max_seqs=1, max_batch_tokens=1024, prefill_graphs=False, enable_prefix_cache=False))
+    graph = LLMEngine(model, EngineOptions(max_ctx=2048, max_seqs=1, max_batch_tokens=1024, prefill_graphs=True, enable_prefix_cache=False))
+    for p in prompts:
+        a = eager.generate([p], sp)[0]
+        b = graph.generate([p], sp)[0]
+        assert a == b
+    assert graph.stats["graph_replays"] >= 3 + 3 * 4
