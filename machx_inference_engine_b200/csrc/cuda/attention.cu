@@ -43,6 +43,7 @@ struct AttnParams {
 
 template <int HD, int PPW>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_partial_kernel(const AttnParams p) {
+  pdl_prologue();
   constexpr int PAIRS = ATT_WARPS * PPW;
   constexpr int KSTR = HD + 2;   // padded K row (elements): conflict-free one-key-per-lane reads
   extern __shared__ uint8_t smem_raw[];
@@ -160,6 +161,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_partial_kernel(const Attn
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                                                            const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, int Tq, int n_q,
                                                            int hd, int n_splits) {
+  pdl_prologue();
   const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= Tq * n_q) return;
   const int h = r % n_q;
@@ -193,7 +195,7 @@ static int launch_partial(const AttnParams& p, cudaStream_t st) {
     configured = true;
   }
   dim3 grid(p.B * p.max_q_tiles, p.n_kv, p.n_splits);
-  kern<<<grid, ATT_WARPS * 32, smem, st>>>(p);
+  launch_pdl(kern, dim3(grid), dim3(ATT_WARPS * 32), smem, st, p);
   return (int)cudaGetLastError();
 }
 
@@ -233,7 +235,7 @@ MX_HOST_API int mx_attention(const void* q, const void* k_cache, const void* v_c
   }
 #undef MX_ATT
   if (rc) return rc;
-  attn_combine_kernel<<<(Tq * n_q + 3) / 4, 128, 0, st>>>(o_part, ml_part, sinks, (__nv_bfloat16*)out, Tq, n_q, hd, p.n_splits);
+  launch_pdl(attn_combine_kernel, dim3((Tq * n_q + 3) / 4), dim3(128), 0, st, o_part, ml_part, sinks, (__nv_bfloat16*)out, Tq, n_q, hd, p.n_splits);
   return (int)cudaGetLastError();
 }
 

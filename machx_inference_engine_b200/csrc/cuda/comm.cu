@@ -42,6 +42,7 @@ __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
 }
 
 __global__ void push_kernel(const uint4* __restrict__ src, long long n16, PeerOut po) {
+  pdl_prologue();
   const int next_seq = *po.seq + 1;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
     const uint4 v = src[i];
@@ -50,14 +51,59 @@ __global__ void push_kernel(const uint4* __restrict__ src, long long n16, PeerOu
   peer_publish(po, next_seq);
 }
 
-// out[t][:] = sum_r slot_r[t][:] (+bias)
+// Reduce-scatter owner step: this rank sums the W partials of its rows [row0, row1) and stores the reduced rows as bf16
+// into every rank's gather region; the last CTA publishes the gather flags.
+template <typename ST>
+__global__ void __launch_bounds__(256) rs_gather_kernel(const uint8_t* __restrict__ inbox, PeerOut po, const float* __restrict__ bias, int row0,
+                                                        int row1, int H, int* status) {
+  pdl_prologue();
+  const int s = *po.seq;
+  const int world = po.world;
+  const int* flags = reinterpret_cast<const int*>(inbox + 2ll * world * po.slot_bytes);
+  const bool ok = wait_all_flags(flags, world, s, status);
+  const uint8_t* base = inbox + (long long)(s & 1) * world * po.slot_bytes;
+  const long long goff = gather_offset(world, po.slot_bytes) + (long long)(s & 1) * po.slot_bytes;
+  for (int t = row0 + blockIdx.x; t < row1 && ok; t += gridDim.x) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        const float4 d = load4<ST>(reinterpret_cast<const ST*>(base + r * po.slot_bytes) + (size_t)t * H + i);
+        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+      }
+      if (bias) { a.x += bias[i]; a.y += bias[i + 1]; a.z += bias[i + 2]; a.w += bias[i + 3]; }
+      const uint2 o = make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+      for (int d = 0; d < world; ++d) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(po.inbox[d] + goff) + (size_t)t * H + i) = o;
+    }
+  }
+  // publish: same ticket scheme as peer_publish, into the gather flags
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+    const unsigned prev = atomicAdd((unsigned*)po.ticket, 1u);
+    if (prev == total - 1) {
+      *po.ticket = 0;
+      __threadfence_system();
+      for (int r = 0; r < world; ++r) {
+        int* gflags = reinterpret_cast<int*>(po.inbox[r] + gather_flags_offset(world, po.slot_bytes));
+        st_release_sys(gflags + po.my_rank, s);
+      }
+    }
+  }
+}
+
+// out[t][:] = sum_r slot_r[t][:] (+bias).  gathered: the single bf16 tensor of the gather region (bias already added).
 template <typename ST>
 __global__ void __launch_bounds__(256) reduce_kernel(const uint8_t* __restrict__ inbox, int world, long long slot_bytes, const int* __restrict__ seq,
-                                                     const float* __restrict__ bias, float* __restrict__ out, long long n, int H, int* status) {
+                                                     const float* __restrict__ bias, float* __restrict__ out, long long n, int H, int* status,
+                                                     int gathered) {
+  pdl_prologue();
   const int s = *seq;
-  const int* flags = reinterpret_cast<const int*>(inbox + 2ll * world * slot_bytes);
+  const int* flags = reinterpret_cast<const int*>(inbox + (gathered ? gather_flags_offset(world, slot_bytes) : 2ll * world * slot_bytes));
   if (!wait_all_flags(flags, world, s, status)) return;
-  const uint8_t* base = inbox + (long long)(s & 1) * world * slot_bytes;
+  const uint8_t* base = gathered ? inbox + gather_offset(world, slot_bytes) + (long long)(s & 1) * slot_bytes
+                                 : inbox + (long long)(s & 1) * world * slot_bytes;
+  if (gathered) world = 1;
   for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < world; ++r) {
@@ -74,11 +120,14 @@ template <typename ST>
 __global__ void __launch_bounds__(256) rmsnorm_reduce_kernel(float* __restrict__ x, const uint8_t* __restrict__ inbox, int world, long long slot_bytes,
                                                              const int* __restrict__ seq, const float* __restrict__ dbias, const float* __restrict__ w,
                                                              __nv_bfloat16* __restrict__ out, float eps, int H, int one_plus_w, float delta_scale,
-                                                             int* status) {
+                                                             int* status, int gathered) {
+  pdl_prologue();
   const int s = *seq;
-  const int* flags = reinterpret_cast<const int*>(inbox + 2ll * world * slot_bytes);
+  const int* flags = reinterpret_cast<const int*>(inbox + (gathered ? gather_flags_offset(world, slot_bytes) : 2ll * world * slot_bytes));
   if (!wait_all_flags(flags, world, s, status)) return;
-  const uint8_t* base = inbox + (long long)(s & 1) * world * slot_bytes;
+  const uint8_t* base = gathered ? inbox + gather_offset(world, slot_bytes) + (long long)(s & 1) * slot_bytes
+                                 : inbox + (long long)(s & 1) * world * slot_bytes;
+  if (gathered) world = 1;
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * H;
   __shared__ float red[8];
@@ -163,31 +212,45 @@ MX_HOST_API int mx_comm_push(const void* src, long long n_bytes, const void* con
   const long long n16 = n_bytes / 16;
   int grid = (int)((n16 + 255) / 256);
   grid = grid < 1 ? 1 : (grid > 2 * sm_count() ? 2 * sm_count() : grid);
-  push_kernel<<<grid, 256, 0, st>>>((const uint4*)src, n16, po);
+  launch_pdl(push_kernel, dim3(grid), dim3(256), 0, st, (const uint4*)src, n16, po);
   return (int)cudaGetLastError();
 }
 
 // slot_is_bf16: element type of the slots.  n = T*H elements (multiple of 4).
+MX_HOST_API long long mx_comm_inbox_bytes(int world, long long slot_bytes) { return inbox_total_bytes(world, slot_bytes); }
+
+// Owner step of the reduce-scatter form: rows [row0, row1) of this rank, slots hold bf16 or fp32 partials.
+MX_HOST_API int mx_comm_rs_gather(const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket, int slot_is_bf16,
+                                  const float* bias, int row0, int row1, int H, cudaStream_t st) {
+  if (H % 4) return -107;
+  PeerOut po = make_peer_out(inbox, world, my_rank, slot_bytes, seq, ticket);
+  const int rows = row1 - row0;
+  const int grid = rows < 1 ? 1 : (rows > 4 * sm_count() ? 4 * sm_count() : rows);
+  if (slot_is_bf16) launch_pdl(rs_gather_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const uint8_t*)inbox[my_rank], po, bias, row0, row1, H, status_word());
+  else launch_pdl(rs_gather_kernel<float>, dim3(grid), dim3(256), 0, st, (const uint8_t*)inbox[my_rank], po, bias, row0, row1, H, status_word());
+  return (int)cudaGetLastError();
+}
+
 MX_HOST_API int mx_comm_reduce(const void* my_inbox, int world, long long slot_bytes, const int* seq, int slot_is_bf16, const float* bias, float* out,
-                               long long n, int H, cudaStream_t st) {
+                               long long n, int H, int gathered, cudaStream_t st) {
   if (n % 4 || H % 4) return -107;
   int grid = (int)((n / 4 + 255) / 256);
   grid = grid < 1 ? 1 : (grid > 4 * sm_count() ? 4 * sm_count() : grid);
-  if (slot_is_bf16) reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const uint8_t*)my_inbox, world, slot_bytes, seq, bias, out, n, H, status_word());
-  else reduce_kernel<float><<<grid, 256, 0, st>>>((const uint8_t*)my_inbox, world, slot_bytes, seq, bias, out, n, H, status_word());
+  if (slot_is_bf16) launch_pdl(reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const uint8_t*)my_inbox, world, slot_bytes, seq, bias, out, n, H, status_word(), gathered);
+  else launch_pdl(reduce_kernel<float>, dim3(grid), dim3(256), 0, st, (const uint8_t*)my_inbox, world, slot_bytes, seq, bias, out, n, H, status_word(), gathered);
   return (int)cudaGetLastError();
 }
 
 MX_HOST_API int mx_comm_rmsnorm_reduce(float* x, const void* my_inbox, int world, long long slot_bytes, const int* seq, int slot_is_bf16,
                                        const float* dbias, const float* w, void* out_bf16, float eps, int T, int H, int one_plus_w,
-                                       float delta_scale, cudaStream_t st) {
+                                       float delta_scale, int gathered, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 4) return -107;
   if (slot_is_bf16)
-    rmsnorm_reduce_kernel<__nv_bfloat16><<<T, 256, 0, st>>>(x, (const uint8_t*)my_inbox, world, slot_bytes, seq, dbias, w, (__nv_bfloat16*)out_bf16,
-                                                              eps, H, one_plus_w, delta_scale, status_word());
+    launch_pdl(rmsnorm_reduce_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, st, x, (const uint8_t*)my_inbox, world, slot_bytes, seq, dbias, w, (__nv_bfloat16*)out_bf16,
+                                                              eps, H, one_plus_w, delta_scale, status_word(), gathered);
   else
-    rmsnorm_reduce_kernel<float><<<T, 256, 0, st>>>(x, (const uint8_t*)my_inbox, world, slot_bytes, seq, dbias, w, (__nv_bfloat16*)out_bf16, eps, H,
-                                                    one_plus_w, delta_scale, status_word());
+    launch_pdl(rmsnorm_reduce_kernel<float>, dim3(T), dim3(256), 0, st, x, (const uint8_t*)my_inbox, world, slot_bytes, seq, dbias, w, (__nv_bfloat16*)out_bf16, eps, H,
+                                                    one_plus_w, delta_scale, status_word(), gathered);
   return (int)cudaGetLastError();
 }

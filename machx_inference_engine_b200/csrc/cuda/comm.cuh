@@ -32,7 +32,18 @@ struct PeerOut {
   long long slot_bytes;
   int* seq;                    // this rank's sequence word (device, local)
   int* ticket;                 // CTA arrival counter (device, local)
+  int rs_rows;                 // > 0: reduce-scatter form, row t goes only to rank min(t / rs_rows, world - 1)
 };
+
+// Reduce-scatter form (prefill-sized collectives).  Writing every partial to every rank moves (W-1) full [T,H] tensors
+// per rank; instead a producer sends each row only to the rank that owns it, the owner sums the W partials of its rows
+// and broadcasts the reduced rows (bf16) into every rank's gather region, and the consumer reads that single tensor:
+// 2 (W-1)/W [T,H] per rank.  The gather region [2 parities][slot_bytes] and its W flags follow the inbox flags.
+__device__ __forceinline__ int peer_first(const PeerOut& po, int row) { return po.rs_rows > 0 ? min(row / po.rs_rows, po.world - 1) : 0; }
+__device__ __forceinline__ int peer_count(const PeerOut& po) { return po.rs_rows > 0 ? 1 : po.world; }
+__host__ __device__ __forceinline__ long long gather_offset(int world, long long slot_bytes) { return 2ll * world * slot_bytes + 4096; }
+__host__ __device__ __forceinline__ long long gather_flags_offset(int world, long long slot_bytes) { return gather_offset(world, slot_bytes) + 2 * slot_bytes; }
+__host__ __device__ __forceinline__ long long inbox_total_bytes(int world, long long slot_bytes) { return gather_flags_offset(world, slot_bytes) + 4096; }
 
 __device__ __forceinline__ long long inbox_flags_offset(int world, long long slot_bytes) { return 2ll * world * slot_bytes; }
 

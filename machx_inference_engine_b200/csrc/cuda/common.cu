@@ -63,6 +63,9 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+static bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
+void set_pdl(bool on) { g_pdl = on; }
 }  // namespace mx
 
 // Reads the status word of the current device and clears it.  Synchronises the device.
@@ -81,3 +84,6 @@ MX_HOST_API const char* mx_cuda_last_error() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
 }
+
+// Programmatic dependent launch for the decode-chain kernels; off (the default) = plain stream order.
+MX_HOST_API void mx_set_pdl(int on) { mx::set_pdl(on != 0); }

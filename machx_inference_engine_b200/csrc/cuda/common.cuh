@@ -56,6 +56,15 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Kernels of the decode chain are launched with the programmatic-stream-serialization attribute (host_util.h: launch_pdl).
+// pdl_launch_dependents() lets the next kernel's CTAs be scheduled as soon as every CTA of this grid has started;
+// pdl_wait() blocks until the previous grid has completed and its memory is visible.  Everything that reads or writes
+// memory touched by other kernels must come after pdl_wait(); without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() { pdl_launch_dependents(); pdl_wait(); }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

@@ -24,6 +24,7 @@ __global__ void __launch_bounds__(128) conv1d_silu_kernel(const bf16* __restrict
                                                           bf16* __restrict__ state, const int* __restrict__ slots,
                                                           const int* __restrict__ cu_q, int B, bf16* __restrict__ y,
                                                           bf16* __restrict__ ckpt, int fuse_state) {
+  pdl_prologue();
   const int t = blockIdx.y;
   const int c = (blockIdx.x * 128 + threadIdx.x) * 2;
   if (c >= C) return;
@@ -58,6 +59,7 @@ __global__ void __launch_bounds__(128) conv1d_silu_kernel(const bf16* __restrict
 // pair of a sequence and walks p upwards, so an old entry is read (at p + q_len) before it is overwritten.
 __global__ void conv1d_state_kernel(const bf16* __restrict__ x, int ld, int C, int Kc, bf16* __restrict__ state, const int* __restrict__ slots,
                                     const int* __restrict__ cu_q) {
+  pdl_prologue();
   const int b = blockIdx.y;
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
   if (c >= C) return;
@@ -123,6 +125,7 @@ __device__ __forceinline__ void scan_prefetch(const ScanParams& p, ScanStage& s,
 __device__ __forceinline__ int dn_koff(int k) { return (k >> 4) * DN_KSTR + (k & 15); }     // key element -> padded smem offset
 
 __global__ void __launch_bounds__(DN_THREADS) deltanet_scan_kernel(ScanParams p) {
+  pdl_prologue();
   const int h = blockIdx.x / DN_VSPLIT, vs = blockIdx.x % DN_VSPLIT, b = blockIdx.y;
   const int t0 = p.cu_q[b], t1 = p.cu_q[b + 1];
   if (t1 <= t0) return;
@@ -220,6 +223,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_scan_kernel(ScanParams p)
 __global__ void __launch_bounds__(128) gated_rmsnorm_ld_kernel(const float* __restrict__ x, const bf16* __restrict__ z, int z_ld,
                                                                const float* __restrict__ w, bf16* __restrict__ y, int T, int n_h, int hd,
                                                                float eps) {
+  pdl_prologue();
   const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= T * n_h) return;
   const int t = r / n_h, h = r % n_h;
@@ -245,10 +249,10 @@ MX_HOST_API int mx_conv1d_silu(const void* x, int ld, int C, int Kc, const float
   if (Kc < 2 || Kc > 8 || (C & 1) || (ld & 1)) return -101;
   const int fuse = max_q_len == 1;
   dim3 grid((C / 2 + 127) / 128, T);
-  conv1d_silu_kernel<<<grid, 128, 0, st>>>((const bf16*)x, ld, C, Kc, w, (bf16*)state, slots, cu_q, B, (bf16*)y, (bf16*)ckpt, fuse);
+  launch_pdl(conv1d_silu_kernel, dim3(grid), dim3(128), 0, st, (const bf16*)x, ld, C, Kc, w, (bf16*)state, slots, cu_q, B, (bf16*)y, (bf16*)ckpt, fuse);
   if (!fuse) {
     dim3 g2((C / 2 + 127) / 128, B);
-    conv1d_state_kernel<<<g2, 128, 0, st>>>((const bf16*)x, ld, C, Kc, (bf16*)state, slots, cu_q);
+    launch_pdl(conv1d_state_kernel, dim3(g2), dim3(128), 0, st, (const bf16*)x, ld, C, Kc, (bf16*)state, slots, cu_q);
   }
   return (int)cudaGetLastError();
 }
@@ -264,13 +268,13 @@ MX_HOST_API int mx_deltanet_scan(const void* qkv, int ld, int q_off, int k_off, 
   p.ab = (const bf16*)ab; p.ab_ld = ab_ld; p.a_idx = a_idx; p.b_idx = b_idx; p.k_of_v = k_of_v;
   p.ssm_a = ssm_a; p.dt_bias = dt_bias; p.state = state; p.slots = slots; p.cu_q = cu_q; p.out = out; p.ckpt = ckpt;
   p.n_v = n_v; p.q_scale = q_scale; p.eps = eps;
-  deltanet_scan_kernel<<<dim3(n_v * DN_VSPLIT, B), DN_THREADS, 0, st>>>(p);
+  launch_pdl(deltanet_scan_kernel, dim3(dim3(n_v * DN_VSPLIT, B)), dim3(DN_THREADS), 0, st, p);
   return (int)cudaGetLastError();
 }
 
 MX_HOST_API int mx_gated_rmsnorm_ld(const float* x, const void* z, int z_ld, const float* w, void* y, int T, int n_h, int hd, float eps,
                                     cudaStream_t st) {
   if (T <= 0) return 0;
-  gated_rmsnorm_ld_kernel<<<(T * n_h + 3) / 4, 128, 0, st>>>(x, (const bf16*)z, z_ld, w, (bf16*)y, T, n_h, hd, eps);
+  launch_pdl(gated_rmsnorm_ld_kernel, dim3((T * n_h + 3) / 4), dim3(128), 0, st, x, (const bf16*)z, z_ld, w, (bf16*)y, T, n_h, hd, eps);
   return (int)cudaGetLastError();
 }

@@ -17,6 +17,7 @@ namespace mx {
 // ------------------------------------------------------------------ embed
 template <int FMT>
 __global__ void embed_kernel(WeightRef w, const int* __restrict__ ids, float* __restrict__ out, int H, int vocab, float scale) {
+  pdl_prologue();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -38,6 +39,7 @@ template <typename DT>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(float* __restrict__ x, const DT* __restrict__ delta, const float* __restrict__ dbias,
                                                       const float* __restrict__ w, __nv_bfloat16* __restrict__ out, float eps, int H,
                                                       int one_plus_w, float delta_scale, int write_x) {
+  pdl_prologue();
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * H;
   __shared__ float red[8];
@@ -116,6 +118,7 @@ struct QkvPostParams {
 };
 
 __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
+  pdl_prologue();
   __shared__ float sh[4][512];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_total = p.n_q + 2 * p.n_kv;
@@ -191,6 +194,7 @@ __device__ __forceinline__ float glu_act(int act, float g, float u, float alpha,
 }
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long total_out, int F, int act,
                            float alpha, float limit) {
+  pdl_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total_out) return;
   const long long t = i / F;
@@ -202,17 +206,20 @@ __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* 
 
 // y[i] = x[i] * sigmoid(g[i])   (gated attention output, shared-expert gate uses the scalar form below)
 __global__ void sigmoid_mul_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ y, long long n) {
+  pdl_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) y[i] = __float2bfloat16(__bfloat162float(x[i]) / (1.f + __expf(-__bfloat162float(g[i]))));
 }
 // out[t][:] (fp32) += scale_t * src[t][:], scale_t = sigmoid(gate_logit[t]) if gate_logit else 1
 __global__ void scaled_add_kernel(float* __restrict__ out, const __nv_bfloat16* __restrict__ src, const float* __restrict__ gate_logit, int H, long long n) {
+  pdl_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float s = gate_logit ? 1.f / (1.f + __expf(-gate_logit[i / H])) : 1.f;
   out[i] += s * __bfloat162float(src[i]);
 }
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ a, __nv_bfloat16* __restrict__ b, long long n) {
+  pdl_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) b[i] = __float2bfloat16(a[i]);
 }
@@ -220,6 +227,7 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ a, __nv_bfloat16*
 // y[t,h,:] = w * x / rms(x) * silu(z)  over head_dim (one warp per (t,h))
 __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ z, const float* __restrict__ w,
                                                             __nv_bfloat16* __restrict__ y, int rows, int hd, float eps) {
+  pdl_prologue();
   const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= rows) return;
   const float* xr = x + (size_t)r * hd;
@@ -236,6 +244,7 @@ __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(const float* __restr
 // Decoder probe: every 32-bit word of `in` (eight E2M1 codes) is decoded twice, with the byte-permute
 // table path (bf16) and with the hardware conversion path (fp16); out[w][0..7] and out[w][8..15].
 __global__ void e2m1_probe_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, int n) {
+  pdl_prologue();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   uint32_t a[4], b[4];
@@ -256,7 +265,7 @@ using namespace mx;
 
 MX_HOST_API int mx_e2m1_probe(const void* in, float* out, int n, cudaStream_t st) {
   if (n <= 0) return 0;
-  e2m1_probe_kernel<<<(n + 127) / 128, 128, 0, st>>>((const uint32_t*)in, out, n);
+  launch_pdl(e2m1_probe_kernel, dim3((n + 127) / 128), dim3(128), 0, st, (const uint32_t*)in, out, n);
   return (int)cudaGetLastError();
 }
 
@@ -267,11 +276,11 @@ MX_HOST_API int mx_embed(int wfmt, const void* w0, const void* w1, const void* w
   WeightRef w{w0, w1, w2, w3};
   const int threads = 128;
   switch (wfmt) {
-    case WF_BF16: embed_kernel<WF_BF16><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
-    case WF_Q8: embed_kernel<WF_Q8><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
-    case WF_Q4K: embed_kernel<WF_Q4K><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
-    case WF_Q6K: embed_kernel<WF_Q6K><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
-    case WF_MXFP4: embed_kernel<WF_MXFP4><<<T, threads, 0, st>>>(w, ids, out, H, vocab, scale); break;
+    case WF_BF16: launch_pdl(embed_kernel<WF_BF16>, dim3(T), dim3(threads), 0, st, w, ids, out, H, vocab, scale); break;
+    case WF_Q8: launch_pdl(embed_kernel<WF_Q8>, dim3(T), dim3(threads), 0, st, w, ids, out, H, vocab, scale); break;
+    case WF_Q4K: launch_pdl(embed_kernel<WF_Q4K>, dim3(T), dim3(threads), 0, st, w, ids, out, H, vocab, scale); break;
+    case WF_Q6K: launch_pdl(embed_kernel<WF_Q6K>, dim3(T), dim3(threads), 0, st, w, ids, out, H, vocab, scale); break;
+    case WF_MXFP4: launch_pdl(embed_kernel<WF_MXFP4>, dim3(T), dim3(threads), 0, st, w, ids, out, H, vocab, scale); break;
     default: return -100;
   }
   return (int)cudaGetLastError();
@@ -282,8 +291,8 @@ MX_HOST_API int mx_rmsnorm(float* x, const void* delta, int delta_is_f32, const 
                            int T, int H, int one_plus_w, float delta_scale, int write_x, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 4) return -107;
-  if (delta_is_f32) rmsnorm_kernel<float><<<T, 256, 0, st>>>(x, (const float*)delta, dbias, w, (__nv_bfloat16*)out_bf16, eps, H, one_plus_w, delta_scale, write_x);
-  else rmsnorm_kernel<__nv_bfloat16><<<T, 256, 0, st>>>(x, (const __nv_bfloat16*)delta, dbias, w, (__nv_bfloat16*)out_bf16, eps, H, one_plus_w, delta_scale, write_x);
+  if (delta_is_f32) launch_pdl(rmsnorm_kernel<float>, dim3(T), dim3(256), 0, st, x, (const float*)delta, dbias, w, (__nv_bfloat16*)out_bf16, eps, H, one_plus_w, delta_scale, write_x);
+  else launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, st, x, (const __nv_bfloat16*)delta, dbias, w, (__nv_bfloat16*)out_bf16, eps, H, one_plus_w, delta_scale, write_x);
   return (int)cudaGetLastError();
 }
 
@@ -300,7 +309,7 @@ MX_HOST_API int mx_qkv_post(const void* qkv, const float* bias, const float* q_n
   p.T = T; p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.n_rot = n_rot; p.block_size = block_size; p.q_gate = q_gate;
   p.norm_one_plus_w = norm_one_plus_w; p.eps = eps; p.max_pos = max_pos;
   const int units = T * (n_q + 2 * n_kv);
-  qkv_post_kernel<<<(units + 3) / 4, 128, 0, st>>>(p);
+  launch_pdl(qkv_post_kernel, dim3((units + 3) / 4), dim3(128), 0, st, p);
   return (int)cudaGetLastError();
 }
 
@@ -308,30 +317,30 @@ MX_HOST_API int mx_glu(const void* in, void* out, long long T, int F, int act, f
   const long long total = T * F;
   if (total <= 0) return 0;
   if (F % 16) return -104;
-  glu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, F, act, alpha, limit);
+  launch_pdl(glu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, F, act, alpha, limit);
   return (int)cudaGetLastError();
 }
 
 MX_HOST_API int mx_sigmoid_mul(const void* x, const void* g, void* y, long long n, cudaStream_t st) {
   if (n <= 0) return 0;
-  sigmoid_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)g, (__nv_bfloat16*)y, n);
+  launch_pdl(sigmoid_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)g, (__nv_bfloat16*)y, n);
   return (int)cudaGetLastError();
 }
 
 MX_HOST_API int mx_scaled_add(float* out, const void* src, const float* gate_logit, int H, long long n, cudaStream_t st) {
   if (n <= 0) return 0;
-  scaled_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, (const __nv_bfloat16*)src, gate_logit, H, n);
+  launch_pdl(scaled_add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, out, (const __nv_bfloat16*)src, gate_logit, H, n);
   return (int)cudaGetLastError();
 }
 
 MX_HOST_API int mx_cast_f32_bf16(const float* a, void* b, long long n, cudaStream_t st) {
   if (n <= 0) return 0;
-  cast_f32_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, (__nv_bfloat16*)b, n);
+  launch_pdl(cast_f32_bf16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, a, (__nv_bfloat16*)b, n);
   return (int)cudaGetLastError();
 }
 
 MX_HOST_API int mx_gated_rmsnorm(const float* x, const void* z, const float* w, void* y, int rows, int hd, float eps, cudaStream_t st) {
   if (rows <= 0) return 0;
-  gated_rmsnorm_kernel<<<(rows + 3) / 4, 128, 0, st>>>(x, (const __nv_bfloat16*)z, w, (__nv_bfloat16*)y, rows, hd, eps);
+  launch_pdl(gated_rmsnorm_kernel, dim3((rows + 3) / 4), dim3(128), 0, st, x, (const __nv_bfloat16*)z, w, (__nv_bfloat16*)y, rows, hd, eps);
   return (int)cudaGetLastError();
 }

@@ -242,8 +242,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (p.act == ACT_NONE) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= rs;
-          const int n_dst = p.peer.world ? p.peer.world : 1;
-          for (int dst = 0; dst < n_dst; ++dst) {
+          const int n_dst = p.peer.world ? peer_count(p.peer) : 1;
+          const int dst0 = p.peer.world ? peer_first(p.peer, row) : 0;
+          for (int dst = dst0; dst < dst0 + n_dst; ++dst) {
           void* cbase = p.peer.world ? (void*)peer_slot(p.peer, dst, next_seq) : p.C;
           if (p.out_f32 == 1) {
             float* out = (float*)cbase + (size_t)row * p.ldc + col0;
@@ -455,9 +456,10 @@ namespace mx { PeerOut make_peer_out(const void* const* inbox, int world, int my
 // publishes the sequence number.  The consumer is mx_comm_rmsnorm_reduce / mx_comm_reduce.
 MX_HOST_API int mx_gemm_allreduce(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, const float* bias,
                                   int out_kind, int M, int N, int K, int bn, const void* const* inbox, int world, int my_rank,
-                                  long long slot_bytes, int* seq, int* ticket, cudaStream_t stream) {
+                                  long long slot_bytes, int* seq, int* ticket, int rs_rows, cudaStream_t stream) {
   if ((long long)M * N * (out_kind == 1 ? 4 : 2) > slot_bytes) return -140;
   mx::PeerOut po = mx::make_peer_out(inbox, world, my_rank, slot_bytes, seq, ticket);
+  po.rs_rows = rs_rows;
   return gemm_impl(a, wfmt, w0, w1, w2, w3, 1, nullptr, N, out_kind, bias, nullptr, 0, 0.f, 0.f, M, N, K, nullptr, nullptr, bn, &po, stream);
 }
 

@@ -52,6 +52,7 @@ __device__ __forceinline__ float gemv_act(int act, float g, float u, float alpha
 
 template <int FMT, int MM>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams p) {
+  pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = (blockIdx.x * GEMV_WARPS + warp) * GEMV_ROWS;
   const int next_seq = p.peer.world ? *p.peer.seq + 1 : 0;
@@ -168,6 +169,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_kernel(const GemvParams 
 // (16-row interleave: feature f lives at row 32*(f/16) + f%16, its up row 16 further).
 template <int FMT>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_gated_kernel(const GemvParams p) {
+  pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int F = p.N / 2;
   const int f0 = (blockIdx.x * GEMV_WARPS + warp) * GEMV_ROWS;
@@ -249,6 +251,7 @@ struct GroupParams {
 
 template <int FMT, bool GATED>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_group_kernel(const GroupParams p) {
+  pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int el = blockIdx.y, e = p.e_lo + el;
   const int cnt = p.counts[e];
@@ -349,10 +352,10 @@ template <int FMT>
 static int launch_group(const GroupParams& p, int n_experts, cudaStream_t st) {
   if (p.act != 0) {
     const int units = (p.N / 2 + 1) / 2;
-    gemv_group_kernel<FMT, true><<<dim3((units + GEMV_WARPS - 1) / GEMV_WARPS, n_experts), GEMV_WARPS * 32, 0, st>>>(p);
+    launch_pdl(gemv_group_kernel<FMT, true>, dim3(dim3((units + GEMV_WARPS - 1) / GEMV_WARPS, n_experts)), dim3(GEMV_WARPS * 32), 0, st, p);
   } else {
     const int units = (p.N + 3) / 4;
-    gemv_group_kernel<FMT, false><<<dim3((units + GEMV_WARPS - 1) / GEMV_WARPS, n_experts), GEMV_WARPS * 32, 0, st>>>(p);
+    launch_pdl(gemv_group_kernel<FMT, false>, dim3(dim3((units + GEMV_WARPS - 1) / GEMV_WARPS, n_experts)), dim3(GEMV_WARPS * 32), 0, st, p);
   }
   return (int)cudaGetLastError();
 }
@@ -362,13 +365,13 @@ static int launch_gemv(const GemvParams& p, int slots, cudaStream_t st) {
   if (p.act != 0) {
     const int F = p.N / 2;
     dim3 grid((F + GEMV_WARPS * GEMV_ROWS - 1) / (GEMV_WARPS * GEMV_ROWS), slots);
-    gemv_gated_kernel<FMT><<<grid, GEMV_WARPS * 32, 0, st>>>(p);
+    launch_pdl(gemv_gated_kernel<FMT>, dim3(grid), dim3(GEMV_WARPS * 32), 0, st, p);
     return (int)cudaGetLastError();
   }
   dim3 grid((p.N + GEMV_WARPS * GEMV_ROWS - 1) / (GEMV_WARPS * GEMV_ROWS), p.slot_expert ? slots : 1);
-  if (p.slot_expert || p.M == 1) gemv_kernel<FMT, 1><<<grid, GEMV_WARPS * 32, 0, st>>>(p);
-  else if (p.M <= 4) gemv_kernel<FMT, 4><<<grid, GEMV_WARPS * 32, 0, st>>>(p);
-  else gemv_kernel<FMT, 8><<<grid, GEMV_WARPS * 32, 0, st>>>(p);
+  if (p.slot_expert || p.M == 1) launch_pdl(gemv_kernel<FMT, 1>, dim3(grid), dim3(GEMV_WARPS * 32), 0, st, p);
+  else if (p.M <= 4) launch_pdl(gemv_kernel<FMT, 4>, dim3(grid), dim3(GEMV_WARPS * 32), 0, st, p);
+  else launch_pdl(gemv_kernel<FMT, 8>, dim3(grid), dim3(GEMV_WARPS * 32), 0, st, p);
   return (int)cudaGetLastError();
 }
 

@@ -242,7 +242,11 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
   float* xscale = reinterpret_cast<float*>(bars + 2 * GS_MAX_STAGES);
   volatile int* abort_flag = reinterpret_cast<int*>(xscale + GS_MAX_XROWS);
   const uint32_t bar0 = smem_u32(bars);
-  const int next_seq = p.peer.world ? *p.peer.seq + 1 : 0;
+  // Programmatic dependent launch: the weights are not produced by any kernel, so the producer warp starts to fill the ring
+  // while the previous kernel is still running; everything that depends on earlier kernels (activations, expert ids, the
+  // collective's sequence word, all global stores) comes after pdl_wait().
+  pdl_launch_dependents();
+  int next_seq = 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) {
@@ -261,6 +265,7 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
     if (lane == 0) {
       int it = 0;
       bool ok = true;
+      if (p.slot_expert) pdl_wait();          // the expert ids come from the router kernel
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const int slot = u / p.nblk, blk = u - slot * p.nblk;
         const uint8_t* b0 = (const uint8_t*)p.w.p0;
@@ -302,6 +307,8 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
     }
   } else {
     // ------------------------------------------------------------ consumers
+    pdl_wait();
+    next_seq = p.peer.world ? *p.peer.seq + 1 : 0;
     // stage the activation rows once (bf16 as they are; MXFP4 path: f16 scaled so that the row maximum sits near 2^9)
     if constexpr (FMT == WF_MXFP4) {
       // one warp per activation row; a lane keeps its 16-byte chunks in registers between the maximum and the conversion
@@ -434,7 +441,10 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
       }
     }
   }
-  if (p.peer.world) peer_publish(p.peer, next_seq);
+  if (p.peer.world) {
+    pdl_wait();                               // (producer warp: its lanes take part in the block-wide publish)
+    peer_publish(p.peer, next_seq);
+  }
 }
 
 template <int FMT, int MM, bool GATED, int NG>
@@ -448,7 +458,7 @@ static int gs_launch(const GsParams& p, int smem, cudaStream_t st) {
   const int units = p.slots * p.nblk;
   const int per_sm = smem <= 113 * 1024 ? 2 : 1;
   const int grid = min(units, sm_count() * per_sm);
-  gemv_stream_kernel<FMT, MM, GATED, NG><<<grid, THREADS, smem, st>>>(p);
+  launch_pdl(gemv_stream_kernel<FMT, MM, GATED, NG>, dim3(grid), dim3(THREADS), (size_t)smem, st, p);
   return (int)cudaGetLastError();
 }
 

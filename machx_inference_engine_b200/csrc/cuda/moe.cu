@@ -18,6 +18,7 @@ constexpr int MOE_TILE = 128;
 // one warp per token; E <= 1024
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int K,
                                                         int renorm, int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+  pdl_prologue();
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   float v[32];
@@ -74,6 +75,7 @@ __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ 
                                                         int* __restrict__ counts, int* __restrict__ seg_start, int* __restrict__ packed_token,
                                                         int* __restrict__ pair_to_packed, int* __restrict__ tile_expert, int* __restrict__ num_tiles,
                                                         int max_rows, int tile) {
+  pdl_prologue();
   extern __shared__ int s_hist[];            // [nwarps][E]
   __shared__ int s_cnt[1024];
   __shared__ int s_start[1025];
@@ -143,6 +145,7 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
 // to_f16: convert the bf16 rows to fp16 while copying (MXFP4 expert GEMMs run in fp16 x fp16 mode)
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ packed_token, const int* __restrict__ total_rows,
                                   __nv_bfloat16* __restrict__ xp, int H, int to_f16) {
+  pdl_prologue();
   const int r = blockIdx.x;
   if (r >= total_rows[1]) return;
   const int t = packed_token[r];
@@ -163,6 +166,7 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int
 template <typename OT>
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ yp, const int* __restrict__ pair_to_packed, const float* __restrict__ w,
                                    OT* __restrict__ out, int H, int K, int accumulate) {
+  pdl_prologue();
   const int t = blockIdx.x;
   for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
     float a0 = 0.f, a1 = 0.f;
@@ -188,6 +192,7 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ yp, const i
 template <typename OT>
 __global__ void moe_combine_push_kernel(const __nv_bfloat16* __restrict__ yp, const int* __restrict__ pair_to_packed, const float* __restrict__ w,
                                         int H, int K, PeerOut po) {
+  pdl_prologue();
   const int t = blockIdx.x;
   const int next_seq = *po.seq + 1;
   for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
@@ -200,7 +205,8 @@ __global__ void moe_combine_push_kernel(const __nv_bfloat16* __restrict__ yp, co
       a0 = fmaf(ww, bf16_lo(v), a0);
       a1 = fmaf(ww, bf16_hi(v), a1);
     }
-    for (int d = 0; d < po.world; ++d) {
+    const int d0 = peer_first(po, t);
+    for (int d = d0; d < d0 + peer_count(po); ++d) {
       if constexpr (sizeof(OT) == 4) *reinterpret_cast<float2*>(reinterpret_cast<float*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) = make_float2(a0, a1);
       else *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) = pack_bf16(a0, a1);
     }
@@ -215,13 +221,15 @@ PeerOut make_peer_out(const void* const* inbox, int world, int my_rank, long lon
 using namespace mx;
 
 MX_HOST_API int mx_moe_combine_push(const void* yp, const int* pair_to_packed, const float* w, int out_f32, int T, int H, int K,
-                                    const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket, cudaStream_t st) {
+                                    const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket, int rs_rows,
+                                    cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 2) return -101;
   if ((long long)T * H * (out_f32 ? 4 : 2) > slot_bytes) return -140;
   PeerOut po = make_peer_out(inbox, world, my_rank, slot_bytes, seq, ticket);
-  if (out_f32) moe_combine_push_kernel<float><<<T, 256, 0, st>>>((const __nv_bfloat16*)yp, pair_to_packed, w, H, K, po);
-  else moe_combine_push_kernel<__nv_bfloat16><<<T, 256, 0, st>>>((const __nv_bfloat16*)yp, pair_to_packed, w, H, K, po);
+  po.rs_rows = rs_rows;
+  if (out_f32) launch_pdl(moe_combine_push_kernel<float>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)yp, pair_to_packed, w, H, K, po);
+  else launch_pdl(moe_combine_push_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)yp, pair_to_packed, w, H, K, po);
   return (int)cudaGetLastError();
 }
 
@@ -229,7 +237,7 @@ MX_HOST_API int mx_moe_route(const float* logits, const float* bias, int T, int 
                              cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > 1024 || K > 32 || K > E) return -120;
-  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, bias, T, E, K, renorm, topk_idx, topk_w);
+  launch_pdl(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, st, logits, bias, T, E, K, renorm, topk_idx, topk_w);
   return (int)cudaGetLastError();
 }
 
@@ -240,7 +248,7 @@ MX_HOST_API int mx_moe_pack(const int* topk_idx, int n_pairs, int K, int E, int 
   const int pack_smem = 32 * E * (int)sizeof(int);
   static bool pack_attr = false;
   if (!pack_attr) { cudaFuncSetAttribute(moe_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * (int)sizeof(int)); pack_attr = true; }
-  moe_pack_kernel<<<1, 1024, pack_smem, st>>>(topk_idx, n_pairs, K, E, e_lo, e_hi, counts, seg_start, packed_token, pair_to_packed, tile_expert,
+  launch_pdl(moe_pack_kernel, dim3(1), dim3(1024), pack_smem, st, topk_idx, n_pairs, K, E, e_lo, e_hi, counts, seg_start, packed_token, pair_to_packed, tile_expert,
                                       num_tiles, max_rows, tile);
   return (int)cudaGetLastError();
 }
@@ -249,7 +257,7 @@ MX_HOST_API int mx_moe_gather(const void* x, const int* packed_token, const int*
                               cudaStream_t st) {
   if (max_rows <= 0) return 0;
   if (H % 8) return -101;
-  moe_gather_kernel<<<max_rows, 128, 0, st>>>((const __nv_bfloat16*)x, packed_token, num_tiles, (__nv_bfloat16*)xp, H, to_f16);
+  launch_pdl(moe_gather_kernel, dim3(max_rows), dim3(128), 0, st, (const __nv_bfloat16*)x, packed_token, num_tiles, (__nv_bfloat16*)xp, H, to_f16);
   return (int)cudaGetLastError();
 }
 
@@ -257,7 +265,7 @@ MX_HOST_API int mx_moe_combine(const void* yp, const int* pair_to_packed, const 
                                int accumulate, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 2) return -101;
-  if (out_f32) moe_combine_kernel<float><<<T, 256, 0, st>>>((const __nv_bfloat16*)yp, pair_to_packed, w, (float*)out, H, K, accumulate);
-  else moe_combine_kernel<__nv_bfloat16><<<T, 256, 0, st>>>((const __nv_bfloat16*)yp, pair_to_packed, w, (__nv_bfloat16*)out, H, K, accumulate);
+  if (out_f32) launch_pdl(moe_combine_kernel<float>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)yp, pair_to_packed, w, (float*)out, H, K, accumulate);
+  else launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)yp, pair_to_packed, w, (__nv_bfloat16*)out, H, K, accumulate);
   return (int)cudaGetLastError();
 }

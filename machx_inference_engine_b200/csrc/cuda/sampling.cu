@@ -45,6 +45,7 @@ __device__ __forceinline__ ValIdx block_argmax(ValIdx x, ValIdx* sh) {
 }
 
 __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out) {
+  pdl_prologue();
   __shared__ ValIdx sh[32];
   const float* row = logits + (size_t)blockIdx.x * ld;
   ValIdx best{-INFINITY, 0x7fffffff};
@@ -62,6 +63,7 @@ __device__ ValIdx g_argmax_part[ARGMAX_MAX_ROWS * ARGMAX_CHUNKS];
 __device__ unsigned g_argmax_ticket[ARGMAX_MAX_ROWS];
 
 __global__ void __launch_bounds__(SAMP_THREADS) argmax_split_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out) {
+  pdl_prologue();
   __shared__ ValIdx sh[32];
   __shared__ bool last;
   const int r = blockIdx.y, c = blockIdx.x;
@@ -92,6 +94,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_split_kernel(const float*
 
 // ids: [rows][max_ids] padded with -1; each id must appear at most once per row.
 __global__ void rep_penalty_kernel(float* __restrict__ logits, int V, int ld, const int* __restrict__ ids, int max_ids, const float* __restrict__ penalty) {
+  pdl_prologue();
   const int r = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= max_ids) return;
   const float pen = penalty[r];
@@ -114,6 +117,7 @@ struct SampleParams {
 };
 
 __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const SampleParams p) {
+  pdl_prologue();
   __shared__ ValIdx sh[32];
   __shared__ float win_v[SAMP_CAP];
   __shared__ int win_i[SAMP_CAP];
@@ -184,15 +188,15 @@ using namespace mx;
 
 MX_HOST_API int mx_argmax(const float* logits, int rows, int V, int ld, int* out, cudaStream_t st) {
   if (rows <= 0) return 0;
-  if (V >= 32768 && rows <= ARGMAX_MAX_ROWS) argmax_split_kernel<<<dim3(ARGMAX_CHUNKS, rows), 256, 0, st>>>(logits, V, ld, out);
-  else argmax_kernel<<<rows, SAMP_THREADS, 0, st>>>(logits, V, ld, out);
+  if (V >= 32768 && rows <= ARGMAX_MAX_ROWS) launch_pdl(argmax_split_kernel, dim3(dim3(ARGMAX_CHUNKS, rows)), dim3(256), 0, st, logits, V, ld, out);
+  else launch_pdl(argmax_kernel, dim3(rows), dim3(SAMP_THREADS), 0, st, logits, V, ld, out);
   return (int)cudaGetLastError();
 }
 
 MX_HOST_API int mx_rep_penalty(float* logits, int rows, int V, int ld, const int* ids, int max_ids, const float* penalty, cudaStream_t st) {
   if (rows <= 0 || max_ids <= 0) return 0;
   dim3 grid((max_ids + 255) / 256, rows);
-  rep_penalty_kernel<<<grid, 256, 0, st>>>(logits, V, ld, ids, max_ids, penalty);
+  launch_pdl(rep_penalty_kernel, dim3(grid), dim3(256), 0, st, logits, V, ld, ids, max_ids, penalty);
   return (int)cudaGetLastError();
 }
 
@@ -200,6 +204,6 @@ MX_HOST_API int mx_sample(const float* logits, int rows, int V, int ld, const fl
                           const float* min_p, unsigned long long* rng, int* out, cudaStream_t st) {
   if (rows <= 0) return 0;
   SampleParams p{logits, V, ld, temperature, top_k, top_p, min_p, rng, out};
-  sample_kernel<<<rows, SAMP_THREADS, 0, st>>>(p);
+  launch_pdl(sample_kernel, dim3(rows), dim3(SAMP_THREADS), 0, st, p);
   return (int)cudaGetLastError();
 }

@@ -68,6 +68,12 @@ def set_gemv_path(path) -> None:
     _lib.cuda().mx_gemv_set_path(code)
 
 
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for the decode-chain kernels (default off): the next kernel's CTAs are scheduled while
+    the previous kernel drains and the streaming GEMV prefetches its weights before its inputs exist."""
+    _lib.cuda().mx_set_pdl(1 if on else 0)
+
+
 def sm_count() -> int:
     return _lib.cuda().mx_sm_count()
 

@@ -35,6 +35,8 @@ class ReducedDelta:
     H: int
     bf16: bool
     bias: Optional[torch.Tensor] = None
+    rs_rows: int = 0            # > 0: reduce-scatter form (rows per owner); the owner step has to run before a consumer
+    gathered: bool = False      # the owner step has been issued: consumers read the gather region
 
     @property
     def shape(self):
@@ -54,7 +56,8 @@ class FusedComm:
         self.slot_bytes = int(slot_bytes)
         lib = _lib.cuda()
         lib.mx_ipc_import.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
-        total = 2 * self.world * self.slot_bytes + 4096
+        lib.mx_comm_inbox_bytes.restype = C.c_longlong
+        total = int(lib.mx_comm_inbox_bytes(self.world, C.c_longlong(self.slot_bytes)))
         lib.mx_raw_alloc.restype = C.c_void_p
         lib.mx_raw_alloc.argtypes = [C.c_longlong]
         self._base = lib.mx_raw_alloc(total)          # dedicated cudaMalloc allocation, zero-filled
@@ -89,6 +92,25 @@ class FusedComm:
         """Slots hold one [max_tokens, max_width] fp32 tensor (bf16 GEMM partials use half of it)."""
         return cls(par, device, slot_bytes=max_tokens * max_width * 4)
 
+    # Collectives of at least this many rows per rank take the reduce-scatter form (each row goes to its owner only, the
+    # owner sums and re-broadcasts bf16 rows): 2 (W-1)/W [T,H] on the wire instead of (W-1) [T,H].  Pays from 4 ranks up.
+    RS_MIN_ROWS_PER_RANK = 64
+    RS_MIN_WORLD = 99           # off until enabled (set to 4 to take the reduce-scatter form from four ranks up)
+
+    def _rs_rows(self, T: int) -> int:
+        if self.world < self.RS_MIN_WORLD or T < self.RS_MIN_ROWS_PER_RANK * self.world:
+            return 0
+        return (T + self.world - 1) // self.world
+
+    def _owner_step(self, d: ReducedDelta) -> None:
+        if d.rs_rows and not d.gathered:
+            row0 = min(self.rank * d.rs_rows, d.T) if self.rank < self.world - 1 else min((self.world - 1) * d.rs_rows, d.T)
+            row1 = min(row0 + d.rs_rows, d.T) if self.rank < self.world - 1 else d.T
+            K._check(_lib.cuda().mx_comm_rs_gather(self._ptr_array, self.world, self.rank, C.c_longlong(self.slot_bytes), K._p(self.seq),
+                                                   K._p(self.ticket), int(d.bf16), K._p(d.bias), row0, row1, d.H, K._stream()), "comm_rs_gather")
+            K._count()
+            d.gathered = True
+
     # ---- producers -----------------------------------------------------------------------
     def linear_all_reduce(self, x: torch.Tensor, w: QuantWeight, bias: Optional[torch.Tensor]) -> ReducedDelta:
         M = x.shape[0]
@@ -104,8 +126,11 @@ class FusedComm:
             bf16 = True
             if M * w.N * 2 > self.slot_bytes:
                 raise ValueError(f"fused all-reduce slot too small for [{M},{w.N}]")
+            rs = self._rs_rows(M)
             K._check(lib.mx_gemm_allreduce(K._p(x), fmt, p0, p1, p2, p3, _vp(0), 0, M, w.N, w.K, K._pick_bn(M, w.N), self._ptr_array, self.world,
-                                           self.rank, C.c_longlong(self.slot_bytes), K._p(self.seq), K._p(self.ticket), st), "gemm_allreduce")
+                                           self.rank, C.c_longlong(self.slot_bytes), K._p(self.seq), K._p(self.ticket), rs, st), "gemm_allreduce")
+            K._count()
+            return ReducedDelta(self, M, w.N, bf16, bias, rs_rows=rs)
         K._count()
         return ReducedDelta(self, M, w.N, bf16, bias)
 
@@ -124,16 +149,19 @@ class FusedComm:
         T, Kt = w.shape
         H = yp.shape[1]
         f32 = T <= K.GEMV_MAX_M
+        rs = 0 if f32 else self._rs_rows(T)
         K._check(_lib.cuda().mx_moe_combine_push(K._p(yp), K._p(pair_to_packed), K._p(w), int(f32), T, H, Kt, self._ptr_array, self.world, self.rank,
-                                                 C.c_longlong(self.slot_bytes), K._p(self.seq), K._p(self.ticket), K._stream()), "moe_combine_push")
+                                                 C.c_longlong(self.slot_bytes), K._p(self.seq), K._p(self.ticket), rs, K._stream()), "moe_combine_push")
         K._count()
-        return ReducedDelta(self, T, H, not f32)
+        return ReducedDelta(self, T, H, not f32, rs_rows=rs)
 
     # ---- consumers -----------------------------------------------------------------------
     def reduce(self, d: ReducedDelta) -> torch.Tensor:
         out = torch.empty(d.T, d.H, dtype=torch.float32, device=self.device)
-        K._check(_lib.cuda().mx_comm_reduce(_vp(self.peer_ptrs[self.rank]), self.world, C.c_longlong(self.slot_bytes), K._p(self.seq), int(d.bf16),
-                                            K._p(d.bias), K._p(out), C.c_longlong(d.T * d.H), d.H, K._stream()), "comm_reduce")
+        self._owner_step(d)
+        g = int(d.gathered)
+        K._check(_lib.cuda().mx_comm_reduce(_vp(self.peer_ptrs[self.rank]), self.world, C.c_longlong(self.slot_bytes), K._p(self.seq), 1 if g else int(d.bf16),
+                                            None if g else K._p(d.bias), K._p(out), C.c_longlong(d.T * d.H), d.H, g, K._stream()), "comm_reduce")
         K._count()
         return out
 
@@ -141,9 +169,11 @@ class FusedComm:
                 want_out: bool = True) -> Optional[torch.Tensor]:
         T, H = x.shape
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if want_out else None
+        self._owner_step(d)
+        g = int(d.gathered)
         K._check(_lib.cuda().mx_comm_rmsnorm_reduce(K._p(x), _vp(self.peer_ptrs[self.rank]), self.world, C.c_longlong(self.slot_bytes), K._p(self.seq),
-                                                    int(d.bf16), K._p(d.bias), K._p(w), K._p(out), C.c_float(eps), T, H, int(one_plus_w),
-                                                    C.c_float(delta_scale), K._stream()), "comm_rmsnorm_reduce")
+                                                    1 if g else int(d.bf16), None if g else K._p(d.bias), K._p(w), K._p(out), C.c_float(eps), T, H,
+                                                    int(one_plus_w), C.c_float(delta_scale), g, K._stream()), "comm_rmsnorm_reduce")
         K._count()
         return out
 

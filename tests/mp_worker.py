@@ -26,9 +26,11 @@ def main():
     if device == "cuda":
         dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(dev)
-        if comm == "fused" and par.world > 1:
+        if comm in ("fused", "fused-rs") and par.world > 1:
             from machx_inference_engine_b200.parallel.fused import FusedComm
             par.fused = FusedComm.create(par, dev, max_tokens=1024, max_width=4096)
+            if comm == "fused-rs":          # force the reduce-scatter form (normally from 4 ranks up) so that two GPUs exercise it
+                par.fused.RS_MIN_WORLD, par.fused.RS_MIN_ROWS_PER_RANK = 2, 16
     else:
         dev = torch.device("cpu")
     cfg = preset(name)

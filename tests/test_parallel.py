@@ -123,3 +123,6 @@ def test_tp2_on_gpus_fused_and_nccl_match_single_gpu(name, quant):
         _close(one, other, cos=0.995 if moe else 0.999, arg=0.93 if moe else 0.95)
     # the two parallel paths sum the same partials: they should agree almost everywhere
     _close(nccl, fused, cos=0.995 if moe else 0.9995, arg=0.93 if moe else 0.97)
+    # reduce-scatter form of the fused collective (owner sums its rows and re-broadcasts them as bf16)
+    rs = _run(2, name, quant, "cuda", "fused-rs")
+    _close(one, rs, cos=0.995 if moe else 0.999, arg=0.93 if moe else 0.95)
