@@ -33,7 +33,7 @@ BASELINE_DECODE_TOK_S = {"gpt-oss-120b": 32.05, "gpt-oss-20b": 58.3, "llama-3-8b
 
 def reference_arm():
     # The reference is a C++20/SYCL (icpx, Level-Zero) project for Intel Arc with no Python packaging;
-    # `pip install /root/reference` fails ("neither setup.py nor pyproject.toml"), and no SYCL compiler,
+    # a pip install of its source tree fails ("neither setup.py nor pyproject.toml"), and no SYCL compiler,
     # oneAPI runtime or Intel GPU exists on this box, so its public path (ie-bench) cannot run here.
     print(json.dumps({"impl": "reference", "unavailable": "reference is C++/SYCL for Intel Arc (no setup.py/pyproject.toml; needs icpx + Level-Zero + an Intel GPU); it has no CUDA path to run on a B200"}))
     return 0
@@ -95,6 +95,8 @@ def main():
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--decode", type=int, default=128)
     ap.add_argument("--baseline-comm", action="store_true", help="plain NCCL all-reduce instead of the fused GEMM+all-reduce kernels")
+    ap.add_argument("--pdl", type=int, default=-1, help="1/0: programmatic dependent launch for the decode chain (default: the library's setting)")
+    ap.add_argument("--reduce-scatter", type=int, default=-1, help="ranks from which prefill collectives take the reduce-scatter form (default: the library's)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -123,6 +125,10 @@ def main():
         from machx_inference_engine_b200.parallel.fused import FusedComm
         par.fused = FusedComm.create(par, dev)
 
+    if args.pdl >= 0:
+        K.set_pdl(bool(args.pdl))
+    if args.reduce_scatter >= 0 and par.fused is not None:
+        par.fused.RS_MIN_WORLD = args.reduce_scatter
     note("process group + comm ready")
     cfg = preset(args.model)
     quant = args.quant or ("mxfp4" if cfg.arch == "gpt-oss" else "q4_k_m" if cfg.arch == "llama" else "q8_0")

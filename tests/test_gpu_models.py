@@ -88,3 +88,26 @@ def test_graphed_prefill_chunks_match_eager(name, quant):
         b = graph.generate([p], sp)[0]
         assert a == b
     assert graph.stats["graph_replays"] >= 3 + 3 * 4
+
+
+def test_programmatic_dependent_launch_gives_identical_tokens():
+    """The decode chain with programmatic dependent launch (kernels scheduled early, streaming GEMV prefetching its weights before
+    its inputs exist) must not change a single token, eagerly or inside CUDA graphs."""
+    from machx_inference_engine_b200.ops import cuda as K
+    cfg = preset("tiny-gpt-oss")
+    model = build_model(cfg, torch.device("cuda:0"), quant="mxfp4", max_ctx=512, gen_device="cpu")
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (19, 140)]
+    sp = SamplingParams(max_tokens=24, ignore_eos=True)
+    outs = {}
+    try:
+        for pdl in (False, True):
+            K.set_pdl(pdl)
+            for graphs in (False, True):
+                eng = LLMEngine(model, EngineOptions(max_ctx=512, max_seqs=2, cuda_graphs=graphs))
+                outs[(pdl, graphs)] = eng.generate(prompts, sp)
+            K.check_status()
+    finally:
+        K.set_pdl(False)
+    assert outs[(True, False)] == outs[(False, False)]
+    assert outs[(True, True)] == outs[(False, True)]
