@@ -269,6 +269,13 @@ def preset(name: str) -> ModelConfig:
         "qwen3.6-27b": ModelConfig(arch="qwen35", n_layers=64, hidden=5120, n_heads=24, n_kv_heads=4, head_dim=256, ffn=17408, vocab=248320,
                                    rms_eps=1e-6, rope_theta=1e7, n_rot=64, ctx_train=262144, full_attn_interval=4, ssm_inner=6144,
                                    ssm_state=128, ssm_n_k_heads=16, ssm_n_v_heads=48, ssm_conv_kernel=4, nextn_predict_layers=1),
+        "tiny-qwen2": ModelConfig(arch="qwen2", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=2048,
+                                  rms_eps=1e-6, rope_theta=1e6, n_rot=64, ctx_train=4096),
+        "tiny-phi3": ModelConfig(arch="phi3", n_layers=2, hidden=256, n_heads=4, n_kv_heads=4, head_dim=64, ffn=512, vocab=2048,
+                                 rms_eps=1e-5, rope_theta=10000.0, n_rot=64, ctx_train=4096),
+        "tiny-granite": ModelConfig(arch="granite", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=2048,
+                                    rms_eps=1e-5, rope_theta=10000.0, n_rot=64, ctx_train=4096, embedding_scale=12.0, residual_scale=0.22,
+                                    attention_scale=0.0078125, logit_scale=0.125),
         "tiny-qwen3": ModelConfig(arch="qwen3", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=2048,
                                   rms_eps=1e-6, rope_theta=1e6, n_rot=64, ctx_train=4096),
     }

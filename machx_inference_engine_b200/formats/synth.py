@@ -102,6 +102,8 @@ def tensor_plan(c: ModelConfig) -> list:
     q_gate = c.is_hybrid
 
     def attention(p):
+        if c.arch == "phi3":         # Phi-3 files keep q, k and v rows in one fused matrix
+            return [(f"{p}.attn_qkv.weight", "matrix", (H, (c.n_heads + 2 * c.n_kv_heads) * hd)), (f"{p}.attn_output.weight", "matrix", (c.n_heads * hd, H))]
         t = [(f"{p}.attn_q.weight", "matrix", (H, c.n_heads * hd * (2 if q_gate else 1))), (f"{p}.attn_k.weight", "matrix", (H, c.n_kv_heads * hd)),
              (f"{p}.attn_v.weight", "matrix", (H, c.n_kv_heads * hd)), (f"{p}.attn_output.weight", "matrix", (c.n_heads * hd, H))]
         if c.arch in ("qwen2", "gpt-oss"):
@@ -138,6 +140,8 @@ def tensor_plan(c: ModelConfig) -> list:
                 t += [(f"{p}.ffn_gate_inp_shexp.weight", "vector", (H,)), (f"{p}.ffn_gate_shexp.weight", "matrix", (H, S)),
                       (f"{p}.ffn_up_shexp.weight", "matrix", (H, S)), (f"{p}.ffn_down_shexp.weight", "matrix", (S, H))]
             return t
+        if c.arch == "phi3":         # ... and gate | up rows in one ffn_up matrix
+            return [(f"{p}.ffn_up.weight", "matrix", (H, 2 * c.ffn)), (f"{p}.ffn_down.weight", "matrix", (c.ffn, H))]
         return [(f"{p}.ffn_gate.weight", "matrix", (H, c.ffn)), (f"{p}.ffn_up.weight", "matrix", (H, c.ffn)), (f"{p}.ffn_down.weight", "matrix", (c.ffn, H))]
 
     post = "post_attention_norm" if (c.arch == "gpt-oss" or c.is_hybrid) else "ffn_norm"

@@ -46,6 +46,26 @@ def test_synth_roundtrip_config_and_generate(ckpts, name):
     assert chat.finish_reason in ("stop", "length") and chat.error == ""
 
 
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-phi3", "tiny-granite", "tiny-qwen35"])
+def test_more_families_load_from_file_and_generate(tmp_path, name):
+    """Qwen2 (q/k/v biases), Phi-3 (fused attn_qkv and gate|up tensors), Granite (embedding / residual / attention / logit
+    scales) and the dense hybrid: file -> loader -> graph -> tokens; the file path equals the in-memory random-init path."""
+    cfg = preset(name)
+    path = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(cfg, path, quant="q8_0", seed=2)
+    r = GGUFReader(path)
+    got = read_config(r.kv, r.tensors.keys())
+    for f in ("arch", "n_layers", "hidden", "n_heads", "n_kv_heads", "ffn", "embedding_scale", "residual_scale", "attention_scale"):
+        assert getattr(got, f) == pytest.approx(getattr(cfg, f)), f
+    if name == "tiny-granite":
+        assert got.logit_scale == pytest.approx(cfg.logit_scale)
+    if name == "tiny-phi3":
+        assert "blk.0.attn_qkv.weight" in r.tensors and "blk.0.attn_q.weight" not in r.tensors and "blk.0.ffn_gate.weight" not in r.tensors
+    eng = Engine.load(path, "cpu", EngineOptions(max_ctx=512, max_seqs=2))
+    res = eng.generate("the sea and the sky", SamplingParams(max_tokens=5, temperature=0.0))
+    assert res.completion_tokens >= 1 and eng.generate("the sea and the sky", SamplingParams(max_tokens=5, temperature=0.0)).token_ids == res.token_ids
+
+
 def test_file_weights_equal_direct_dequant(ckpts):
     """A tensor read back through the loader decodes to the values the writer quantised."""
     from machx_inference_engine_b200.models.sources import GGUFSource
