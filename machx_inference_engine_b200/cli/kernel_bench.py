@@ -84,13 +84,79 @@ def report(name, ms_med, ms_min, flops=None, bytes_=None, extra=None):
     print(json.dumps(out))
 
 
+def bench_allreduce(a):
+    """Row-parallel projection + all-reduce + residual/RMSNorm on W ranks (run under torchrun): the fused peer-memory
+    path (all-to-all stores and the reduce-scatter form) against GEMM + NCCL all-reduce + norm.  Device-timed, max over
+    ranks.  The wire roofline is bytes that must leave a rank / 770 GB/s (measured peer copy, one direction)."""
+    import torch.distributed as dist
+    from ..ops import cuda as K
+    from ..ops.weights import WFormat, from_dense
+    from ..parallel.comm import init_from_env
+    from ..parallel.fused import FusedComm
+    par = init_from_env("cuda")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    W = par.world
+    T, H, Kfull = a.m, a.n, a.k
+    Kl = Kfull // W // 64 * 64
+    fc = FusedComm.create(par, dev, max_tokens=T, max_width=H)
+    torch.manual_seed(par.rank)
+    w = from_dense(torch.randn(1, H, Kl, device=dev) * 0.02, WFormat.BF16)
+    x = (torch.randn(T, Kl, device=dev) * 0.5).to(torch.bfloat16)
+    res = torch.zeros(T, H, device=dev)
+    nw = torch.ones(H, device=dev)
+
+    def timed(fn, iters=a.iters):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            par.barrier(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts.append(float(t))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    def fused(rs_world):
+        fc.RS_MIN_WORLD = rs_world
+        return timed(lambda: fc.rmsnorm(res, nw, 1e-5, fc.linear_all_reduce(x, w, None)))
+
+    def baseline():
+        def fn():
+            y = K.linear(x, w, out_f32=True)
+            dist.all_reduce(y)
+            K.rmsnorm(res, nw, 1e-5, delta=y)
+        return timed(fn)
+    gemm_only = timed(lambda: K.linear(x, w))
+    t_all, t_rs, t_nccl = fused(99), fused(2), baseline()
+    K.check_status()
+    if par.rank == 0:
+        bytes_all = (W - 1) * T * H * 2                     # bf16 partial to every peer
+        bytes_rs = 2 * (W - 1) * T * H * 2 // W             # rows to their owner + reduced rows back
+        flops = 2.0 * T * H * Kl
+        for name, ms, by in (("fused all-to-all stores", t_all, bytes_all), ("fused reduce-scatter + gather", t_rs, bytes_rs), ("gemm + NCCL all-reduce + norm", t_nccl, bytes_rs)):
+            wire_ms = by / 770e9 * 1e3
+            comp_ms = flops / (peaks()["bf16_tflops"] * 1e12) * 1e3
+            print(json.dumps({"path": name, "ranks": W, "T": T, "H": H, "K_per_rank": Kl, "ms": round(ms, 4), "gemm_alone_ms": round(gemm_only, 4),
+                              "wire_bytes_per_rank": by, "roofline_ms": round(max(wire_ms, comp_ms), 4),
+                              "fraction_of_roofline": round(max(wire_ms, comp_ms) / ms, 3)}))
+    sys.stdout.flush()
+    par.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
 def main(argv=None):
     from ..ops import cuda as K
     from ..ops import ref
     from ..ops.weights import WFormat, from_dense
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "moe_gemm", "gemv", "expert_gemv", "attention", "rmsnorm", "deltanet"])
+    ap.add_argument("kernel", choices=["gemm", "moe_gemm", "gemv", "expert_gemv", "attention", "rmsnorm", "deltanet", "allreduce"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=2880)
@@ -111,6 +177,8 @@ def main(argv=None):
     ap.add_argument("--gemv-path", default="auto", choices=["auto", "register", "stream"], help="which decode GEMV kernel to time")
     ap.add_argument("--layers", type=int, default=1, help="distinct weight copies cycled through so that weights are never L2-resident")
     a = ap.parse_args(argv)
+    if a.kernel == "allreduce":
+        return bench_allreduce(a)
     dev = torch.device("cuda:0")
     K.set_gemv_path(a.gemv_path)
     global GRAPH_REPS

@@ -58,6 +58,7 @@ class Sequence:
     finished: bool = False
     finish_reason: str = ""
     state_slot: int = -1
+    restore_hash: Optional[bytes] = None       # hybrid models: block hash whose recurrent-state snapshot has to be restored into the slot
     h_last: Optional[torch.Tensor] = None      # hidden state of the last computed position (speculative decoding)
     t_arrival: float = 0.0
     t_first_token: float = 0.0
@@ -177,16 +178,18 @@ class EngineOptions:
     graph_batch_sizes: tuple = (1, 2, 4, 8, 16, 32, 64)
     eos_ids: tuple = ()
     spec_k: int = 0                     # MTP draft length (hybrid models with an MTP head)
+    max_state_snapshots: int = 12       # hybrid models: recurrent-state snapshots kept for prefix reuse
     prefill_graphs: bool = True         # replay single-sequence prefill chunks of 512/1024/2048/4096/8192 tokens (or the full step budget) as CUDA graphs
 
 
 class Scheduler:
-    def __init__(self, opts: EngineOptions, bm: BlockManager, n_state_slots: int = 0):
+    def __init__(self, opts: EngineOptions, bm: BlockManager, n_state_slots: int = 0, state_prefix: Optional[Callable] = None):
         self.opts, self.bm = opts, bm
         self.waiting: deque = deque()
         self.running: list = []
         self.free_state = deque(range(n_state_slots))
         self.uses_state = n_state_slots > 0
+        self.state_prefix = state_prefix       # hashes -> number of leading blocks that end on a stored recurrent-state snapshot
 
     def add(self, seq: Sequence) -> None:
         self.waiting.append(seq)
@@ -227,8 +230,14 @@ class Scheduler:
             seq = self.waiting[0]
             if self.uses_state and not self.free_state:
                 break
-            if not seq.blocks and seq.n_computed == 0 and not self.uses_state:
+            if not seq.blocks and seq.n_computed == 0:
                 blocks, hashes = self.bm.match_prefix(seq.tokens)
+                if self.uses_state:
+                    # a recurrent model can resume only where its state was saved: keep the longest such prefix of the cached blocks
+                    keep = self.state_prefix(hashes) if (self.state_prefix and hashes) else 0
+                    self.bm.release(blocks[keep:])
+                    blocks, hashes = blocks[:keep], hashes[:keep]
+                    seq.restore_hash = hashes[-1] if keep else None
                 seq.blocks, seq.block_hashes = blocks, hashes
                 seq.n_computed = seq.n_cached_prefix = len(blocks) * KV_BLOCK
             n = min(budget, len(seq.tokens) - seq.n_computed)
@@ -282,8 +291,11 @@ class LLMEngine:
         self.kv = model.new_kv_cache(nb)
         n_state = o.max_seqs if getattr(model, "needs_state", False) else 0
         self.state = model.new_state(n_state + 1) if n_state else None      # the extra slot absorbs graph-padding rows
-        self.bm = BlockManager(nb, o.enable_prefix_cache and not n_state)
-        self.sched = Scheduler(o, self.bm, n_state)
+        self.bm = BlockManager(nb, o.enable_prefix_cache)
+        # recurrent-state snapshots at block boundaries, keyed by the chained block hash, LRU (the reference keeps KV slab +
+        # DeltaNet snapshot per trie endpoint: include/ie/prefix_cache.hpp:39-118, fleet_prefix_cache.hpp:36-98; max 12 entries)
+        self.state_cache: OrderedDict = OrderedDict()
+        self.sched = Scheduler(o, self.bm, n_state, state_prefix=self._state_prefix if n_state else None)
         self._ids = itertools.count()
         self._graphs: dict = {}
         self._graph_pool = None
@@ -291,6 +303,33 @@ class LLMEngine:
                       "spec_rounds": 0, "spec_drafted": 0, "spec_accepted": 0}
         self.eos_ids = set(o.eos_ids)
         self.spec_k = o.spec_k if (o.spec_k > 0 and getattr(model, "mtp", None) is not None and self.state is not None) else 0
+
+    # ------------------------------------------------------------------ recurrent-state prefix snapshots (hybrid models)
+    def _state_prefix(self, hashes: list) -> int:
+        for n in range(len(hashes), 0, -1):
+            if hashes[n - 1] in self.state_cache:
+                self.state_cache.move_to_end(hashes[n - 1])
+                return n
+        return 0
+
+    def _restore_states(self, plan: list) -> None:
+        for seq, _ in plan:
+            if seq.restore_hash is not None:
+                snap = self.state_cache.get(seq.restore_hash)
+                if snap is not None:
+                    self.state.restore(seq.state_slot, snap)
+                seq.restore_hash = None
+
+    def _save_states(self, plan: list) -> None:
+        if self.state is None or not self.opts.enable_prefix_cache:
+            return
+        for seq, n in plan:
+            if n > 1 and seq.n_computed % KV_BLOCK == 0 and seq.n_computed <= len(seq.prompt) and len(seq.block_hashes) >= seq.n_computed // KV_BLOCK > 0:
+                key = seq.block_hashes[seq.n_computed // KV_BLOCK - 1]
+                if key not in self.state_cache:
+                    self.state_cache[key] = self.state.snapshot(seq.state_slot)
+                    while len(self.state_cache) > self.opts.max_state_snapshots:
+                        self.state_cache.popitem(last=False)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids: list, params: Optional[SamplingParams] = None, on_token: Optional[Callable] = None) -> Sequence:
@@ -346,6 +385,8 @@ class LLMEngine:
             else:
                 self.stats["decode_tokens"] += 1
             self.bm.publish(seq)
+        self._save_states(plan)
+        for seq, n in plan:
             if seq.finished:
                 self.sched.finish(seq)
         self.stats["steps"] += 1
@@ -413,6 +454,8 @@ class LLMEngine:
         return t, k, p, m
 
     def _run(self, plan: list, sampled_rows: list) -> list:
+        if self.state is not None:
+            self._restore_states(plan)
         decode_only = all(n == 1 for _, n in plan) and len(sampled_rows) == len(plan)
         seqs = [plan[i][0] for i in sampled_rows]
         greedy = all(s.params.temperature <= 0 and s.params.repetition_penalty == 1.0 for s in seqs)

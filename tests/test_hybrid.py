@@ -132,3 +132,28 @@ def test_spec_decode_is_lossless_with_any_acceptance():
         m.mtp.draft = real
     assert seq.tokens[len(prompt):] == truth
     assert eng.stats["spec_accepted"] > 0 and eng.stats["spec_rounds"] < len(truth)
+
+
+def test_prefix_cache_restores_recurrent_state():
+    """A second request sharing a 256-token prefix resumes from the KV blocks AND the DeltaNet state saved at that boundary
+    (the reference keeps a state snapshot per prefix-trie endpoint); its continuation must equal a cold run."""
+    m = _model()
+    V = m.cfg.vocab
+    shared = [(i * 13 + 1) % V for i in range(300)]
+    sp = SamplingParams(max_tokens=8, ignore_eos=True)
+    cold = LLMEngine(m, EngineOptions(max_ctx=1024, max_seqs=2, max_batch_tokens=128, enable_prefix_cache=False)).generate([shared + [5, 6, 7]], sp)[0]
+    eng = LLMEngine(m, EngineOptions(max_ctx=1024, max_seqs=2, max_batch_tokens=128))
+    first = eng.generate([shared + [9, 9]], sp)[0]
+    assert len(eng.state_cache) == 2                       # snapshots after 128 and 256 prompt tokens
+    pre = eng.stats["prefill_tokens"]
+    seq = eng.add_request(shared + [5, 6, 7], sp)
+    while not seq.finished:
+        eng.step()
+    assert seq.n_cached_prefix == 256 and eng.stats["prefill_tokens"] - pre == len(shared) + 3 - 256
+    assert seq.tokens[len(seq.prompt):] == cold
+    # a prefix whose blocks are cached but whose snapshot was evicted falls back to the longest boundary that has one
+    eng.state_cache.popitem(last=True)
+    seq = eng.add_request(shared + [5, 6, 7], sp)
+    while not seq.finished:
+        eng.step()
+    assert seq.n_cached_prefix == 128 and seq.tokens[len(seq.prompt):] == cold
