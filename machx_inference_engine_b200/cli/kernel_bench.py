@@ -5,6 +5,8 @@ small cases that the committed ``ncu`` summaries under ``profiles/`` were captur
     python -m machx_inference_engine_b200.cli.kernel_bench gemm --m 2048 --n 5120 --k 2880 --fmt bf16
     python -m machx_inference_engine_b200.cli.kernel_bench gemv --n 201088 --k 2880 --fmt q8
     python -m machx_inference_engine_b200.cli.kernel_bench attention --tokens 2048 --heads 64 --kv-heads 8 --head-dim 64
+    python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 -m machx_inference_engine_b200.cli.kernel_bench \
+        allreduce --tokens 2048 --hidden 2880 --ffn 4096
 
 Each prints achieved TFLOP/s or GB/s and the fraction of the measured peak (MEASURED_PEAKS.json when
 present, otherwise the stated fallback).  Reference parity: bench/bench_{gemm_fp16,gemv_q4k,dequant,attention}.cpp.
@@ -98,7 +100,7 @@ def bench_allreduce(a):
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     W = par.world
-    T, H, Kfull = a.m, a.n, a.k
+    T, H, Kfull = a.tokens, a.hidden, a.ffn     # long option names only: torchrun's parser claims abbreviations like --m / --n
     Kl = Kfull // W // 64 * 64
     fc = FusedComm.create(par, dev, max_tokens=T, max_width=H)
     torch.manual_seed(par.rank)

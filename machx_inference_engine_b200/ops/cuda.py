@@ -69,7 +69,7 @@ def set_gemv_path(path) -> None:
 
 
 def set_pdl(on: bool) -> None:
-    """Programmatic dependent launch for the decode-chain kernels (default off): the next kernel's CTAs are scheduled while
+    """Programmatic dependent launch for the decode-chain kernels (default on): the next kernel's CTAs are scheduled while
     the previous kernel drains and the streaming GEMV prefetches its weights before its inputs exist."""
     _lib.cuda().mx_set_pdl(1 if on else 0)
 

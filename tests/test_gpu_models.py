@@ -108,6 +108,6 @@ def test_programmatic_dependent_launch_gives_identical_tokens():
                 outs[(pdl, graphs)] = eng.generate(prompts, sp)
             K.check_status()
     finally:
-        K.set_pdl(False)
+        K.set_pdl(True)
     assert outs[(True, False)] == outs[(False, False)]
     assert outs[(True, True)] == outs[(False, True)]
