@@ -5,10 +5,15 @@
     python -m machx_inference_engine_b200.cli.tools prompt-bench --gguf M.gguf [--runs 3]
     python -m machx_inference_engine_b200.cli.tools chunk-check  --gguf M.gguf | --model NAME [--chunks 64,256]
     python -m machx_inference_engine_b200.cli.tools soak         --gguf M.gguf | --model NAME --seconds 60
+    python -m machx_inference_engine_b200.cli.tools layer-dump   --gguf M.gguf --device cuda --out a.pt [--tokens FILE]
+    python -m machx_inference_engine_b200.cli.tools layer-diff   a.pt b.pt [--threshold 0.999]
+    python -m machx_inference_engine_b200.cli.tools layer-parity --gguf M.gguf          (CUDA kernels against the fp32 PyTorch path)
 
 Reference parity (behaviour, not code): tools/ie_perplexity.cpp (streaming negative log-likelihood), tools/ie_det_probe.cpp and
 ie_bug_monitor.cpp (run-to-run bit identity), tools/ie_prompt_bench.cpp (fixed prompts, first run discarded, median),
-tools/ie_validate_chunking.cpp (chunked prefill against whole-prompt prefill), scripts/soak_1h.sh (completions per hour, failures).
+tools/ie_validate_chunking.cpp (chunked prefill against whole-prompt prefill), scripts/soak_1h.sh (completions per hour, failures),
+tools/ie_dense_dump.cpp / ie_qwen35_dump.cpp / llama_dump.cpp + tools/diff_layers.sh (per-layer activation dumps of one prompt and their
+layer-by-layer cosine comparison; here the second implementation is this package's own fp32 PyTorch path instead of llama.cpp).
 """
 from __future__ import annotations
 
@@ -182,6 +187,78 @@ def cmd_soak(a) -> int:
     return 0 if stats["failed"] == 0 else 1
 
 
+def _dump(a, device):
+    """Per-layer activations of one prompt: the mixer output, the FFN output and the residual stream after every layer."""
+    import copy
+    b = copy.copy(a)
+    b.device = device
+    eng = _load(b, max_ctx=2048)
+    if a.tokens:
+        ids = [int(t) for t in open(a.tokens).read().split()]
+    else:
+        g = torch.Generator().manual_seed(4)
+        ids = torch.randint(0, eng.cfg.vocab, (a.tokens_n,), generator=g).tolist()
+    m = eng.model
+    taps: dict = {}
+
+    def tap(li, mixer, ffn, resid):
+        if not (torch.is_tensor(mixer) and torch.is_tensor(ffn)):
+            raise RuntimeError("layer dumps need a single-rank model (pending fused reductions are not tensors)")
+        d = taps.setdefault(li, {"mixer": [], "ffn": [], "resid": []})
+        d["mixer"].append(mixer.float().cpu())
+        d["ffn"].append(ffn.float().cpu())
+        d["resid"].append((resid.float() + ffn.float() * eng.cfg.residual_scale).cpu())
+    m.tap = tap
+    try:
+        logits = _all_logits(eng, ids, a.chunk)
+    finally:
+        m.tap = None
+    layers = [{k: torch.cat(v)[:len(ids)] for k, v in taps[li].items()} for li in sorted(taps)]
+    return {"ids": ids, "device": str(device), "arch": eng.cfg.arch, "layers": layers, "logits": logits}
+
+
+def _diff(da, db, threshold):
+    if da["ids"] != db["ids"]:
+        raise SystemExit("the two dumps were made from different prompts")
+    rows, first_bad = [], None
+    cosf = torch.nn.functional.cosine_similarity
+    for li, (la, lb) in enumerate(zip(da["layers"], db["layers"])):
+        r = {"layer": li}
+        for k in ("mixer", "ffn", "resid"):
+            c = cosf(la[k], lb[k], dim=1)
+            r[k + "_cos_min"] = round(float(c.min()), 6)
+            r[k + "_max_abs"] = round(float((la[k] - lb[k]).abs().max()), 5)
+        if first_bad is None and r["resid_cos_min"] < threshold:
+            first_bad = li
+        rows.append(r)
+    c = cosf(da["logits"], db["logits"], dim=1)
+    return {"layers": rows, "first_layer_below_threshold": first_bad, "threshold": threshold, "logits_cos_min": round(float(c.min()), 6),
+            "argmax_agree": round(float((da["logits"].argmax(-1) == db["logits"].argmax(-1)).float().mean()), 4)}
+
+
+def cmd_layer_dump(a) -> int:
+    d = _dump(a, a.device)
+    torch.save(d, a.out)
+    print(json.dumps({"out": a.out, "layers": len(d["layers"]), "positions": len(d["ids"]), "device": d["device"]}))
+    return 0
+
+
+def cmd_layer_diff(a) -> int:
+    r = _diff(torch.load(a.a, weights_only=False), torch.load(a.b, weights_only=False), a.threshold)
+    print(json.dumps(r if a.verbose else {k: v for k, v in r.items() if k != "layers"} | {"worst_layer": min(r["layers"], key=lambda x: x["resid_cos_min"])}))
+    return 0 if r["first_layer_below_threshold"] is None else 1
+
+
+def cmd_layer_parity(a) -> int:
+    """The same checkpoint on the CUDA kernels and on the fp32 PyTorch path, compared layer by layer."""
+    if not a.gguf:
+        raise SystemExit("layer-parity needs --gguf (both runs must load identical weights)")
+    other = "cuda" if torch.cuda.is_available() else "cpu"
+    r = _diff(_dump(a, "cpu"), _dump(a, other), a.threshold)
+    print(json.dumps({"against": other} | {k: v for k, v in r.items() if k != "layers"} | {"worst_layer": min(r["layers"], key=lambda x: x["resid_cos_min"])}))
+    return 0 if r["first_layer_below_threshold"] is None else 1
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="ie-tools")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -197,8 +274,11 @@ def main(argv=None) -> int:
     p = sub.add_parser("chunk-check"); common(p); p.add_argument("--chunks", default="64,256"); p.add_argument("--tokens-n", type=int, default=700)
     p = sub.add_parser("prompt-bench"); common(p); p.add_argument("--runs", type=int, default=3); p.add_argument("--max-tokens", type=int, default=64)
     p = sub.add_parser("soak"); common(p); p.add_argument("--seconds", type=float, default=60); p.add_argument("--concurrency", type=int, default=4)
+    p = sub.add_parser("layer-dump"); common(p); p.add_argument("--out", required=True); p.add_argument("--tokens"); p.add_argument("--tokens-n", type=int, default=96)
+    p = sub.add_parser("layer-diff"); p.add_argument("a"); p.add_argument("b"); p.add_argument("--threshold", type=float, default=0.999); p.add_argument("--verbose", action="store_true")
+    p = sub.add_parser("layer-parity"); common(p); p.add_argument("--tokens"); p.add_argument("--tokens-n", type=int, default=96); p.add_argument("--threshold", type=float, default=0.999)
     a = ap.parse_args(argv)
-    return {"perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
+    return {"layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
             "soak": cmd_soak}[a.cmd](a)
 
 

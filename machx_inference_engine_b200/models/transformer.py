@@ -359,6 +359,7 @@ class TransformerModel:
         # layer split (pipeline) plan: contiguous layer ranges, embedding on the first rank, head on the last
         # (LayerPlan::contiguous, src/model/dense_split.cpp:24-33)
         self.pp = par.mode == "pp" and par.world > 1
+        self.tap = None          # optional callable(layer, mixer_out, ffn_out, residual) used by the layer-dump tool
         self.layer_lo, self.layer_hi = ((par.rank * c.n_layers) // par.world, ((par.rank + 1) * c.n_layers) // par.world) if self.pp else (0, c.n_layers)
         self.first_stage, self.last_stage = (not self.pp or par.rank == 0), (not self.pp or par.rank == par.world - 1)
         self.tied = not src.has("output.weight") or c.tie_embeddings
@@ -426,6 +427,8 @@ class TransformerModel:
             a = self._mixer(li, L, h, fb, kv, state)
             h2 = self._norm(x, L["ffn_norm"], a)
             delta = L["moe"](h2, par) if "moe" in L else L["ffn"](h2, par)
+            if self.tap is not None:                 # per-layer dump hook of the parity tools (single rank, eager)
+                self.tap(li, a, delta, x)
         return x, delta
 
     def _head(self, x, delta, fb):

@@ -25,3 +25,25 @@ def test_soak_and_serve_bench(capsys):
     assert serve_bench.main(["--model", "tiny-gpt-oss", "--device", "cpu", "--requests", "5", "--min-prompt", "10", "--max-prompt", "150", "--decode", "6"]) == 0
     r = _last_json(capsys)
     assert r["errors"] == 0 and r["generated_tokens"] == 30 and r["ttft_p50_s"] > 0
+
+
+def test_layer_dump_and_diff(tmp_path, capsys):
+    from machx_inference_engine_b200.formats.model_config import preset
+    from machx_inference_engine_b200.formats.synth import write_synthetic_gguf
+    g = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(preset("tiny-qwen3next"), g, quant="q8_0", seed=5)
+    a, b = str(tmp_path / "a.pt"), str(tmp_path / "b.pt")
+    assert tools.main(["layer-dump", "--gguf", g, "--device", "cpu", "--out", a, "--tokens-n", "40", "--chunk", "16"]) == 0
+    assert _last_json(capsys)["positions"] == 40
+    assert tools.main(["layer-dump", "--gguf", g, "--device", "cpu", "--out", b, "--tokens-n", "40", "--chunk", "64"]) == 0
+    capsys.readouterr()
+    assert tools.main(["layer-diff", a, b]) == 0                      # chunked against whole-prompt: the same activations
+    r = _last_json(capsys)
+    assert r["first_layer_below_threshold"] is None and r["logits_cos_min"] > 0.999
+    import torch
+    d = torch.load(b, weights_only=False)
+    d["layers"][1]["resid"] = d["layers"][1]["resid"] + torch.randn_like(d["layers"][1]["resid"])
+    torch.save(d, b)
+    assert tools.main(["layer-diff", a, b]) == 1
+    assert _last_json(capsys)["first_layer_below_threshold"] == 1
+    assert tools.main(["layer-parity", "--gguf", g, "--device", "cpu", "--tokens-n", "24"]) == 0
