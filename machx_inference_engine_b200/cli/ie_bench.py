@@ -36,6 +36,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kprofile-decode", action="store_true", help="per-op device time of the decode steps")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--spec-k", type=int, default=0, help="MTP self-speculative decode with this draft length (models with an MTP head)")
+    ap.add_argument("--int8-kv", action="store_true", help="int8 KV cache with per-row scales")
     ap.add_argument("--baseline-comm", action="store_true")
     ap.add_argument("--device", default="cuda")
     args = ap.parse_args(argv)
@@ -65,7 +66,7 @@ def main(argv=None) -> int:
         model = build_model(cfg, dev, par, quant=quant, max_ctx=max_ctx)
     cfg = model.cfg
     eng = LLMEngine(model, EngineOptions(max_ctx=max_ctx, max_batch_tokens=max(lens), max_seqs=1, enable_prefix_cache=False, spec_k=args.spec_k,
-                                         cuda_graphs=cuda and not args.no_graphs and not args.kprofile_decode))
+                                         kv_dtype="int8" if args.int8_kv else "bf16", cuda_graphs=cuda and not args.no_graphs and not args.kprofile_decode))
 
     def sync():
         par.barrier()

@@ -15,7 +15,8 @@ import sys
 
 def _engine_options(a):
     from ..runtime.engine import EngineOptions
-    return EngineOptions(max_ctx=a.ctx, max_batch_tokens=min(a.ctx, a.chunk), max_seqs=a.max_seqs, spec_k=a.spec_k if a.spec else 0)
+    return EngineOptions(max_ctx=a.ctx, max_batch_tokens=min(a.ctx, a.chunk), max_seqs=a.max_seqs, spec_k=a.spec_k if a.spec else 0,
+                         kv_dtype="int8" if a.int8_kv else "bf16")
 
 
 def _relaunch_multi_gpu(a, argv) -> int:
@@ -55,7 +56,7 @@ def main(argv=None) -> int:
         p.add_argument("--gpus", type=int, default=0, help="0 = decide from the memory plan")
         p.add_argument("--chunk", type=int, default=4096, help="prefill chunk (tokens per step)")
         p.add_argument("--max-seqs", type=int, default=64)
-        p.add_argument("--int8-kv", action="store_true", help="accepted for compatibility; the KV cache is bf16")
+        p.add_argument("--int8-kv", action="store_true", help="store K/V rows as int8 with a per-row scale (half the cache memory)")
         p.add_argument("--spec", action="store_true")
         p.add_argument("--spec-k", type=int, default=3)
         p.add_argument("--spec-head", default=None)

@@ -7,7 +7,10 @@
 // Every split writes an un-normalised partial (acc, m, l); the combine kernel merges the
 // splits and folds the per-head sink into the denominator exactly once.
 //
-// KV cache layout: [block][kv_head][block_size][head_dim] bf16, block_size a multiple of 64.
+// KV cache layout: [block][kv_head][block_size][head_dim] bf16, block_size a multiple of 64.  An int8 cache has the
+// same layout with one byte per element plus an fp32 scale per (block, kv head, token) row (value = q * scale); the
+// staging loop widens it to bf16, so the math below is shared.  kv_dequant_pages_kernel expands the pages of a prefill
+// batch into a bf16 scratch cache for the tensor-core prefill kernel.
 //
 // Reference parity: src/ops/attention.cpp:229-454 (naive / gpt-oss window + sink),
 // :685-1036 (split-K flash decode, sink folded in combine), :2456-2714 (wide tile prefill with
@@ -27,6 +30,8 @@ struct AttnParams {
   const __nv_bfloat16* q;      // [Tq][n_q][hd]
   const __nv_bfloat16* k_cache;
   const __nv_bfloat16* v_cache;
+  const float* k_scale;        // non-null: the caches hold int8 and these are the per-row scales [block][kv_head][block_size]
+  const float* v_scale;
   const int* block_table;      // [B][max_blocks]
   const int* seq_lens;         // [B] kv length including this step's tokens
   const int* cu_q;             // [B+1]
@@ -40,6 +45,39 @@ struct AttnParams {
   int window;                  // 0 = full causal
   float scale, softcap;
 };
+
+// bytes `first`, `first + 1` of w as signed 8-bit integers, times scale, packed as two bf16
+__device__ __forceinline__ uint32_t s8x2_to_bf16x2(uint32_t w, int first, float scale) {
+  const float a = (float)(int8_t)(w >> (8 * first)) * scale, b = (float)(int8_t)(w >> (8 * first + 8)) * scale;
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Pages of an int8 cache expanded to bf16: dst page (b * nb + j) = page block_table[b][j] of the source, for every page
+// that holds keys of sequence b.  One CTA per (j, b, kv head).
+__global__ void __launch_bounds__(256) kv_dequant_pages_kernel(const int8_t* __restrict__ k8, const int8_t* __restrict__ v8,
+                                                               const float* __restrict__ ks, const float* __restrict__ vs,
+                                                               const int* __restrict__ block_table, const int* __restrict__ seq_lens,
+                                                               __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int n_kv,
+                                                               int block_size, int hd, int max_blocks, int nb) {
+  pdl_prologue();
+  const int j = blockIdx.x, b = blockIdx.y, kvh = blockIdx.z;
+  if ((long long)j * block_size >= seq_lens[b]) return;
+  const int blk = block_table[(size_t)b * max_blocks + j];
+  const size_t src = ((size_t)blk * n_kv + kvh) * block_size, dst = (((size_t)b * nb + j) * n_kv + kvh) * block_size;
+  const int per_row = hd / 8;
+  for (int i = threadIdx.x; i < block_size * per_row; i += blockDim.x) {
+    const int r = i / per_row, c = (i % per_row) * 8;
+    const uint2 kq = *reinterpret_cast<const uint2*>(k8 + (src + r) * hd + c);
+    const uint2 vq = *reinterpret_cast<const uint2*>(v8 + (src + r) * hd + c);
+    const float sk_ = ks[src + r], sv_ = vs[src + r];
+    uint4 ko, vo;
+    ko.x = s8x2_to_bf16x2(kq.x, 0, sk_); ko.y = s8x2_to_bf16x2(kq.x, 2, sk_); ko.z = s8x2_to_bf16x2(kq.y, 0, sk_); ko.w = s8x2_to_bf16x2(kq.y, 2, sk_);
+    vo.x = s8x2_to_bf16x2(vq.x, 0, sv_); vo.y = s8x2_to_bf16x2(vq.x, 2, sv_); vo.z = s8x2_to_bf16x2(vq.y, 0, sv_); vo.w = s8x2_to_bf16x2(vq.y, 2, sv_);
+    *reinterpret_cast<uint4*>(dk + (dst + r) * hd + c) = ko;
+    *reinterpret_cast<uint4*>(dv + (dst + r) * hd + c) = vo;
+  }
+}
 
 template <int HD, int PPW>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_partial_kernel(const AttnParams p) {
@@ -95,12 +133,31 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_partial_kernel(const Attn
       const int key0 = tile * ATT_TILE;
       const int blk = p.block_table[(size_t)b * p.max_blocks + key0 / p.block_size];
       const size_t base = (((size_t)blk * p.n_kv + kvh) * p.block_size + key0 % p.block_size) * HD;
-      for (int i = threadIdx.x; i < ATT_TILE * HD / 8; i += blockDim.x) {
-        const int r = i / (HD / 8), c = (i % (HD / 8)) * 8;
-        const uint4 kv4 = *reinterpret_cast<const uint4*>(p.k_cache + base + (size_t)r * HD + c);
-        uint32_t* kd = reinterpret_cast<uint32_t*>(sk + r * KSTR + c);
-        kd[0] = kv4.x; kd[1] = kv4.y; kd[2] = kv4.z; kd[3] = kv4.w;
-        *reinterpret_cast<uint4*>(sv + r * HD + c) = *reinterpret_cast<const uint4*>(p.v_cache + base + (size_t)r * HD + c);
+      if (p.k_scale) {
+        const int8_t* k8 = reinterpret_cast<const int8_t*>(p.k_cache);
+        const int8_t* v8 = reinterpret_cast<const int8_t*>(p.v_cache);
+        const size_t srow = ((size_t)blk * p.n_kv + kvh) * p.block_size + key0 % p.block_size;
+        for (int i = threadIdx.x; i < ATT_TILE * HD / 8; i += blockDim.x) {
+          const int r = i / (HD / 8), c = (i % (HD / 8)) * 8;
+          const uint2 kq = *reinterpret_cast<const uint2*>(k8 + base + (size_t)r * HD + c);
+          const uint2 vq = *reinterpret_cast<const uint2*>(v8 + base + (size_t)r * HD + c);
+          const float ks = p.k_scale[srow + r], vs = p.v_scale[srow + r];
+          uint32_t* kd = reinterpret_cast<uint32_t*>(sk + r * KSTR + c);
+          kd[0] = s8x2_to_bf16x2(kq.x, 0, ks); kd[1] = s8x2_to_bf16x2(kq.x, 2, ks);
+          kd[2] = s8x2_to_bf16x2(kq.y, 0, ks); kd[3] = s8x2_to_bf16x2(kq.y, 2, ks);
+          uint4 vv;
+          vv.x = s8x2_to_bf16x2(vq.x, 0, vs); vv.y = s8x2_to_bf16x2(vq.x, 2, vs);
+          vv.z = s8x2_to_bf16x2(vq.y, 0, vs); vv.w = s8x2_to_bf16x2(vq.y, 2, vs);
+          *reinterpret_cast<uint4*>(sv + r * HD + c) = vv;
+        }
+      } else {
+        for (int i = threadIdx.x; i < ATT_TILE * HD / 8; i += blockDim.x) {
+          const int r = i / (HD / 8), c = (i % (HD / 8)) * 8;
+          const uint4 kv4 = *reinterpret_cast<const uint4*>(p.k_cache + base + (size_t)r * HD + c);
+          uint32_t* kd = reinterpret_cast<uint32_t*>(sk + r * KSTR + c);
+          kd[0] = kv4.x; kd[1] = kv4.y; kd[2] = kv4.z; kd[3] = kv4.w;
+          *reinterpret_cast<uint4*>(sv + r * HD + c) = *reinterpret_cast<const uint4*>(p.v_cache + base + (size_t)r * HD + c);
+        }
       }
       __syncthreads();
 #pragma unroll
@@ -205,16 +262,17 @@ using namespace mx;
 
 // Scratch: o_part needs n_splits*Tq*n_q*hd floats, ml_part n_splits*Tq*n_q*2 floats.
 // max_q_len is the longest query segment of the batch (host knows it from cu_q).
-MX_HOST_API int mx_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table, const int* seq_lens,
-                             const int* cu_q, const float* sinks, void* out, float* o_part, float* ml_part, int B, int Tq, int max_q_len,
-                             int n_q, int n_kv, int hd, int max_blocks, int block_size, int window, float scale, float softcap,
-                             int n_splits, cudaStream_t st) {
+static int attention_impl(const void* q, const void* k_cache, const void* v_cache, const float* k_scale, const float* v_scale,
+                          const int* block_table, const int* seq_lens, const int* cu_q, const float* sinks, void* out, float* o_part,
+                          float* ml_part, int B, int Tq, int max_q_len, int n_q, int n_kv, int hd, int max_blocks, int block_size, int window,
+                          float scale, float softcap, int n_splits, cudaStream_t st) {
   if (B <= 0 || Tq <= 0) return 0;
   if (block_size % ATT_TILE) return -110;
   if (n_q % n_kv) return -111;
   const int gqa = n_q / n_kv;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.k_scale = k_scale; p.v_scale = k_scale ? v_scale : nullptr;
   p.block_table = block_table; p.seq_lens = seq_lens; p.cu_q = cu_q; p.o_part = o_part; p.ml_part = ml_part;
   p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.max_blocks = max_blocks; p.block_size = block_size;
   p.n_splits = n_splits < 1 ? 1 : n_splits; p.Tq = Tq; p.window = window; p.scale = scale; p.softcap = softcap;
@@ -236,6 +294,35 @@ MX_HOST_API int mx_attention(const void* q, const void* k_cache, const void* v_c
 #undef MX_ATT
   if (rc) return rc;
   launch_pdl(attn_combine_kernel, dim3((Tq * n_q + 3) / 4), dim3(128), 0, st, o_part, ml_part, sinks, (__nv_bfloat16*)out, Tq, n_q, hd, p.n_splits);
+  return (int)cudaGetLastError();
+}
+
+MX_HOST_API int mx_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table, const int* seq_lens,
+                             const int* cu_q, const float* sinks, void* out, float* o_part, float* ml_part, int B, int Tq, int max_q_len,
+                             int n_q, int n_kv, int hd, int max_blocks, int block_size, int window, float scale, float softcap,
+                             int n_splits, cudaStream_t st) {
+  return attention_impl(q, k_cache, v_cache, nullptr, nullptr, block_table, seq_lens, cu_q, sinks, out, o_part, ml_part, B, Tq, max_q_len, n_q,
+                        n_kv, hd, max_blocks, block_size, window, scale, softcap, n_splits, st);
+}
+
+// The same over an int8 cache with per-row scales (see the layout note at the top of this file).
+MX_HOST_API int mx_attention_kv8(const void* q, const void* k_cache, const void* v_cache, const float* k_scale, const float* v_scale,
+                                 const int* block_table, const int* seq_lens, const int* cu_q, const float* sinks, void* out, float* o_part,
+                                 float* ml_part, int B, int Tq, int max_q_len, int n_q, int n_kv, int hd, int max_blocks, int block_size,
+                                 int window, float scale, float softcap, int n_splits, cudaStream_t st) {
+  if (!k_scale || !v_scale) return -113;
+  return attention_impl(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, cu_q, sinks, out, o_part, ml_part, B, Tq, max_q_len, n_q,
+                        n_kv, hd, max_blocks, block_size, window, scale, softcap, n_splits, st);
+}
+
+// dst_k / dst_v: bf16 [B * nb][n_kv][block_size][hd]; page (b, j) is filled when j * block_size < seq_lens[b].
+MX_HOST_API int mx_kv_dequant_pages(const void* k8, const void* v8, const float* k_scale, const float* v_scale, const int* block_table,
+                                    const int* seq_lens, void* dst_k, void* dst_v, int B, int n_kv, int block_size, int hd, int max_blocks,
+                                    int nb, cudaStream_t st) {
+  if (B <= 0 || nb <= 0) return 0;
+  if (hd % 8) return -114;
+  launch_pdl(kv_dequant_pages_kernel, dim3(nb, B, n_kv), dim3(256), 0, st, (const int8_t*)k8, (const int8_t*)v8, k_scale, v_scale, block_table,
+             seq_lens, (__nv_bfloat16*)dst_k, (__nv_bfloat16*)dst_v, n_kv, block_size, hd, max_blocks, nb);
   return (int)cudaGetLastError();
 }
 

@@ -110,6 +110,8 @@ struct QkvPostParams {
   __nv_bfloat16* gate_out;    // [T][n_q][hd] when q_gate != 0
   __nv_bfloat16* k_cache;     // [blocks][n_kv][block_size][hd]
   __nv_bfloat16* v_cache;
+  float* k_scale;             // non-null: the caches hold int8, one fp32 scale per (block, kv head, token) row
+  float* v_scale;
   int T, n_q, n_kv, hd, n_rot, block_size;
   int q_gate;                 // 1: q columns hold per-head [q(hd) | gate(hd)]
   int norm_one_plus_w;
@@ -176,7 +178,18 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
     if (slot < 0) return;
     const long long blk = slot / p.block_size, off = slot % p.block_size;
     __nv_bfloat16* cache = kind == 1 ? p.k_cache : p.v_cache;
-    dst = cache + ((blk * p.n_kv + hh) * p.block_size + off) * hd;
+    const long long row = (blk * p.n_kv + hh) * p.block_size + off;
+    if (p.k_scale) {          // symmetric int8 per row: scale = max|x| / 127
+      float amax = 0.f;
+      for (int i = lane; i < hd; i += 32) amax = fmaxf(amax, fabsf(v[i]));
+      amax = warp_max(amax);
+      const float sc = amax > 0.f ? amax / 127.f : 1.f, inv = 1.f / sc;
+      int8_t* d8 = reinterpret_cast<int8_t*>(cache) + row * hd;
+      for (int i = lane; i < hd; i += 32) d8[i] = (int8_t)max(-127, min(127, __float2int_rn(v[i] * inv)));
+      if (lane == 0) (kind == 1 ? p.k_scale : p.v_scale)[row] = sc;
+      return;
+    }
+    dst = cache + row * hd;
   }
   for (int i = lane; i < hd; i += 32) dst[i] = __float2bfloat16(v[i]);
 }
@@ -296,16 +309,31 @@ MX_HOST_API int mx_rmsnorm(float* x, const void* delta, int delta_is_f32, const 
   return (int)cudaGetLastError();
 }
 
+MX_HOST_API int mx_qkv_post_kv8(const void* qkv, const float* bias, const float* q_norm_w, const float* k_norm_w, const int* positions,
+                                const float* rope_cos, const float* rope_sin, const long long* slot_map, void* q_out, void* gate_out,
+                                void* k_cache, void* v_cache, float* k_scale, float* v_scale, int T, int n_q, int n_kv, int hd, int n_rot,
+                                int block_size, int q_gate, int norm_one_plus_w, float eps, int max_pos, cudaStream_t st);
+
 MX_HOST_API int mx_qkv_post(const void* qkv, const float* bias, const float* q_norm_w, const float* k_norm_w, const int* positions,
                             const float* rope_cos, const float* rope_sin, const long long* slot_map, void* q_out, void* gate_out,
                             void* k_cache, void* v_cache, int T, int n_q, int n_kv, int hd, int n_rot, int block_size, int q_gate,
                             int norm_one_plus_w, float eps, int max_pos, cudaStream_t st) {
+  return mx_qkv_post_kv8(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_map, q_out, gate_out, k_cache, v_cache, nullptr,
+                         nullptr, T, n_q, n_kv, hd, n_rot, block_size, q_gate, norm_one_plus_w, eps, max_pos, st);
+}
+
+// k_scale / v_scale non-null: k_cache / v_cache are int8 [blocks][n_kv][block_size][hd] and the rows are quantised on the way in.
+MX_HOST_API int mx_qkv_post_kv8(const void* qkv, const float* bias, const float* q_norm_w, const float* k_norm_w, const int* positions,
+                                const float* rope_cos, const float* rope_sin, const long long* slot_map, void* q_out, void* gate_out,
+                                void* k_cache, void* v_cache, float* k_scale, float* v_scale, int T, int n_q, int n_kv, int hd, int n_rot,
+                                int block_size, int q_gate, int norm_one_plus_w, float eps, int max_pos, cudaStream_t st) {
   if (T <= 0) return 0;
   if (hd > 512) return -108;
   QkvPostParams p;
   p.qkv = (const __nv_bfloat16*)qkv; p.bias = bias; p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.positions = positions;
   p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.slot_map = slot_map; p.q_out = (__nv_bfloat16*)q_out; p.gate_out = (__nv_bfloat16*)gate_out;
   p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
+  p.k_scale = k_scale; p.v_scale = k_scale ? v_scale : nullptr;
   p.T = T; p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.n_rot = n_rot; p.block_size = block_size; p.q_gate = q_gate;
   p.norm_one_plus_w = norm_one_plus_w; p.eps = eps; p.max_pos = max_pos;
   const int units = T * (n_q + 2 * n_kv);

@@ -47,6 +47,7 @@ class ForwardBatch:
     q_lens_host: Optional[list] = None          # host copy of per-sequence query lengths (hybrid scan scheduling)
     start_host: Optional[list] = None           # host copy of per-sequence start positions (0 = fresh state)
     want_hidden: bool = False                   # also return the pre-final-norm hidden rows (MTP)
+    max_kv_len: int = 0                         # host copy of max(seq_lens); 0 = unknown (the block table's capacity is assumed)
 
     @property
     def T(self) -> int:
@@ -58,22 +59,35 @@ class ForwardBatch:
 
 
 class KVCache:
-    """Paged KV: per attention layer ``k, v [num_blocks, n_kv_local, KV_BLOCK, head_dim]`` bf16.
+    """Paged KV: per attention layer ``k, v [num_blocks, n_kv_local, KV_BLOCK, head_dim]`` bf16, or int8 with one fp32 scale
+    per (block, kv head, token) row in ``ks, vs [num_blocks, n_kv_local, KV_BLOCK]`` (value = q * scale, scale = max|x| / 127).
 
-    The reference cache is contiguous per sequence (include/ie/kv_cache.hpp:27-114); pages make
-    continuous batching and block-level prefix sharing possible.
+    The reference cache is contiguous per sequence (include/ie/kv_cache.hpp:27-114) and keeps int8 rows beside it when
+    ``--int8-kv`` is given (src/core/kv_cache.cpp:182-240, src/ops/attention.cpp:145-229); pages make continuous batching
+    and block-level prefix sharing possible, and here the int8 rows replace the bf16 ones instead of shadowing them.
     """
 
-    def __init__(self, n_layers: int, num_blocks: int, n_kv: int, head_dim: int, device, attn_layers: Optional[list[int]] = None):
+    def __init__(self, n_layers: int, num_blocks: int, n_kv: int, head_dim: int, device, attn_layers: Optional[list[int]] = None,
+                 dtype: str = "bf16"):
+        if dtype not in ("bf16", "int8"):
+            raise ValueError(f"unknown KV cache dtype {dtype!r}")
         self.num_blocks = num_blocks
         self.block_size = KV_BLOCK
+        self.dtype = dtype
         layers = attn_layers if attn_layers is not None else list(range(n_layers))
-        self.k = {l: torch.zeros(num_blocks, n_kv, KV_BLOCK, head_dim, dtype=torch.bfloat16, device=device) for l in layers}
-        self.v = {l: torch.zeros(num_blocks, n_kv, KV_BLOCK, head_dim, dtype=torch.bfloat16, device=device) for l in layers}
+        td = torch.bfloat16 if dtype == "bf16" else torch.int8
+        self.k = {l: torch.zeros(num_blocks, n_kv, KV_BLOCK, head_dim, dtype=td, device=device) for l in layers}
+        self.v = {l: torch.zeros(num_blocks, n_kv, KV_BLOCK, head_dim, dtype=td, device=device) for l in layers}
+        self.ks = {l: torch.ones(num_blocks, n_kv, KV_BLOCK, dtype=torch.float32, device=device) for l in layers} if dtype == "int8" else None
+        self.vs = {l: torch.ones(num_blocks, n_kv, KV_BLOCK, dtype=torch.float32, device=device) for l in layers} if dtype == "int8" else None
+
+    def scales(self, layer: int):
+        return (self.ks[layer], self.vs[layer]) if self.ks is not None else None
 
     @staticmethod
-    def bytes_per_block(n_attn_layers: int, n_kv: int, head_dim: int) -> int:
-        return 2 * n_attn_layers * n_kv * KV_BLOCK * head_dim * 2
+    def bytes_per_block(n_attn_layers: int, n_kv: int, head_dim: int, dtype: str = "bf16") -> int:
+        per_row = head_dim * 2 if dtype == "bf16" else head_dim + 4
+        return 2 * n_attn_layers * n_kv * KV_BLOCK * per_row
 
     def copy_blocks(self, src: list[int], dst: list[int]) -> None:
         if not src:
@@ -83,6 +97,9 @@ class KVCache:
         for l in self.k:
             self.k[l][d] = self.k[l][s]
             self.v[l][d] = self.v[l][s]
+            if self.ks is not None:
+                self.ks[l][d] = self.ks[l][s]
+                self.vs[l][d] = self.vs[l][s]
 
 
 # ---------------------------------------------------------------------------------------------
@@ -197,9 +214,9 @@ class AttentionBlock:
         qkv = self.qkv(h)
         q, gate = ops.qkv_post(qkv, None, self.q_norm, self.k_norm, fb.positions, rope[0], rope[1], fb.slot_map, kv.k[self.layer],
                                kv.v[self.layer], self.n_q, self.n_kv, self.hd, self.n_rot, q_gate=self.q_gate,
-                               norm_one_plus_w=self.norm_one_plus_w, eps=self.eps)
+                               norm_one_plus_w=self.norm_one_plus_w, eps=self.eps, kv_scales=kv.scales(self.layer))
         a = ops.attention(q, kv.k[self.layer], kv.v[self.layer], fb.block_table, fb.seq_lens, fb.cu_q, fb.max_q_len, sinks=self.sinks,
-                          window=self.window, scale=self.scale)
+                          window=self.window, scale=self.scale, kv_scales=kv.scales(self.layer), max_kv_len=fb.max_kv_len)
         a = a.reshape(a.shape[0], self.n_q * self.hd)
         if gate is not None:
             a = ops.sigmoid_mul(a, gate.reshape(a.shape))
@@ -400,8 +417,8 @@ class TransformerModel:
             L["ffn"] = DenseFFN(c, l, src, par)
         return L
 
-    def new_kv_cache(self, num_blocks: int) -> KVCache:
-        return KVCache(self.cfg.n_layers, num_blocks, self.n_kv_local, self.cfg.head_dim, self.device, self.attn_layers)
+    def new_kv_cache(self, num_blocks: int, dtype: str = "bf16") -> KVCache:
+        return KVCache(self.cfg.n_layers, num_blocks, self.n_kv_local, self.cfg.head_dim, self.device, self.attn_layers, dtype=dtype)
 
     def weight_bytes(self) -> int:
         n = (self.embed_w.nbytes if self.embed_w is not None else 0) + (0 if (self.tied or self.lm_head is None) else self.lm_head.w.nbytes)

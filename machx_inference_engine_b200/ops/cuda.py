@@ -162,15 +162,20 @@ def deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, sta
 
 
 def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_map, k_cache, v_cache, n_q, n_kv, hd, n_rot,
-             q_gate=False, norm_one_plus_w=False, eps=1e-6):
+             q_gate=False, norm_one_plus_w=False, eps=1e-6, kv_scales=None):
     T = qkv.shape[0]
     q = torch.empty(T, n_q, hd, dtype=torch.bfloat16, device=qkv.device)
     gate = torch.empty(T, n_q, hd, dtype=torch.bfloat16, device=qkv.device) if q_gate else None
     bs = k_cache.shape[2]
     max_pos = rope_cos.shape[0] if rope_cos is not None else 1
-    _check(_lib.cuda().mx_qkv_post(_p(qkv), _p(bias), _p(q_norm_w), _p(k_norm_w), _p(positions), _p(rope_cos), _p(rope_sin),
-                                   _p(slot_map), _p(q), _p(gate), _p(k_cache), _p(v_cache), T, n_q, n_kv, hd, n_rot, bs, int(q_gate),
-                                   int(norm_one_plus_w), C.c_float(eps), max_pos, _stream()), "qkv_post")
+    if kv_scales is not None:
+        assert k_cache.dtype == torch.int8 and kv_scales[0].dtype == torch.float32
+    else:
+        assert k_cache.dtype == torch.bfloat16
+    ks, vs = kv_scales if kv_scales is not None else (None, None)
+    _check(_lib.cuda().mx_qkv_post_kv8(_p(qkv), _p(bias), _p(q_norm_w), _p(k_norm_w), _p(positions), _p(rope_cos), _p(rope_sin),
+                                       _p(slot_map), _p(q), _p(gate), _p(k_cache), _p(v_cache), _p(ks), _p(vs), T, n_q, n_kv, hd, n_rot, bs,
+                                       int(q_gate), int(norm_one_plus_w), C.c_float(eps), max_pos, _stream()), "qkv_post")
     _count()
     return q, gate
 
@@ -283,12 +288,43 @@ def attention_prefill_tc(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q
     return out
 
 
-def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0, n_splits=None):
+_kv8_scratch: dict = {}
+
+
+def _dequant_pages(k_cache, v_cache, kv_scales, block_table, seq_lens, max_kv_len):
+    """The pages of this batch of an int8 cache as a bf16 scratch cache [B * nb, n_kv, bs, hd] with its own block table."""
+    _, n_kv, bs, hd = k_cache.shape
+    B = seq_lens.numel()
+    nb = block_table.shape[1] if max_kv_len <= 0 else min(block_table.shape[1], (max_kv_len + bs - 1) // bs)
+    need = 2 * B * nb * n_kv * bs * hd
+    buf = _kv8_scratch.get(k_cache.device)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros(need, dtype=torch.bfloat16, device=k_cache.device)      # zeros: pages that are never filled stay finite
+        _kv8_scratch[k_cache.device] = buf
+    dk = buf[: need // 2].view(B * nb, n_kv, bs, hd)
+    dv = buf[need // 2: need].view(B * nb, n_kv, bs, hd)
+    key = (k_cache.device, "table", B, nb)
+    table = _kv8_scratch.get(key)
+    if table is None:
+        table = torch.arange(B * nb, dtype=torch.int32, device=k_cache.device).view(B, nb)
+        _kv8_scratch[key] = table
+    _check(_lib.cuda().mx_kv_dequant_pages(_p(k_cache), _p(v_cache), _p(kv_scales[0]), _p(kv_scales[1]), _p(block_table), _p(seq_lens),
+                                           _p(dk), _p(dv), B, n_kv, bs, hd, block_table.shape[1], nb, _stream()), "kv_dequant_pages")
+    _count()
+    return dk, dv, table
+
+
+def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0, n_splits=None,
+              kv_scales=None, max_kv_len=0):
     Tq, n_q, hd = q.shape
     n_kv, bs = k_cache.shape[1], k_cache.shape[2]
     B = seq_lens.numel()
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    assert (k_cache.dtype == torch.int8) == (kv_scales is not None)
     if max_q_len >= TC_PREFILL_MIN_Q and hd in (64, 128) and bs == 128 and not softcap and n_splits is None:
+        if kv_scales is not None:       # the tensor-core kernel reads bf16 pages: expand this batch's pages first
+            dk, dv, table = _dequant_pages(k_cache, v_cache, kv_scales, block_table, seq_lens, max_kv_len)
+            return attention_prefill_tc(q, dk, dv, table, seq_lens, cu_q, max_q_len, sinks=sinks, window=window, scale=scale)
         return attention_prefill_tc(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=sinks, window=window, scale=scale)
     if n_splits is None:
         # decode-sized problems: split the KV range so that ~2 CTAs per SM exist
@@ -304,9 +340,15 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
     o_part = buf[: n_splits * Tq * n_q * hd]
     ml_part = buf[n_splits * Tq * n_q * hd: need]
     out = torch.empty(Tq, n_q, hd, dtype=torch.bfloat16, device=q.device)
-    _check(_lib.cuda().mx_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), _p(seq_lens), _p(cu_q), _p(sinks), _p(out),
-                                    _p(o_part), _p(ml_part), B, Tq, int(max_q_len), n_q, n_kv, hd, block_table.shape[1], bs, int(window),
-                                    C.c_float(scale), C.c_float(softcap), int(n_splits), _stream()), "attention")
+    if kv_scales is not None:
+        _check(_lib.cuda().mx_attention_kv8(_p(q), _p(k_cache), _p(v_cache), _p(kv_scales[0]), _p(kv_scales[1]), _p(block_table), _p(seq_lens),
+                                            _p(cu_q), _p(sinks), _p(out), _p(o_part), _p(ml_part), B, Tq, int(max_q_len), n_q, n_kv, hd,
+                                            block_table.shape[1], bs, int(window), C.c_float(scale), C.c_float(softcap), int(n_splits),
+                                            _stream()), "attention_kv8")
+    else:
+        _check(_lib.cuda().mx_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), _p(seq_lens), _p(cu_q), _p(sinks), _p(out),
+                                        _p(o_part), _p(ml_part), B, Tq, int(max_q_len), n_q, n_kv, hd, block_table.shape[1], bs, int(window),
+                                        C.c_float(scale), C.c_float(softcap), int(n_splits), _stream()), "attention")
     _count(2)
     return out
 

@@ -124,8 +124,8 @@ def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE
 
 
 def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_map, k_cache, v_cache, n_q, n_kv, hd, n_rot,
-             q_gate=False, norm_one_plus_w=False, eps=1e-6):
-    """Returns (q [T,n_q,hd] bf16, gate or None); writes K/V into the paged cache."""
+             q_gate=False, norm_one_plus_w=False, eps=1e-6, kv_scales=None):
+    """Returns (q [T,n_q,hd] bf16, gate or None); writes K/V into the paged cache (int8 rows + scales when kv_scales is given)."""
     T = qkv.shape[0]
     x = qkv.to(torch.float32)
     if bias is not None:
@@ -160,13 +160,21 @@ def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_
     bs = k_cache.shape[2]
     ok = slot_map >= 0
     blk, off = (slot_map[ok] // bs).long(), (slot_map[ok] % bs).long()
+    if kv_scales is not None:
+        for cache, sc, t in ((k_cache, kv_scales[0], k[ok]), (v_cache, kv_scales[1], v[ok])):
+            amax = t.abs().amax(-1)
+            scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+            cache[blk, :, off] = torch.round(t * (1.0 / scale).unsqueeze(-1)).clamp(-127, 127).to(torch.int8)
+            sc[blk, :, off] = scale
+        return qpart.to(torch.bfloat16).contiguous(), gate
     k_cache[blk, :, off] = k[ok].to(k_cache.dtype)
     v_cache[blk, :, off] = v[ok].to(v_cache.dtype)
     return qpart.to(torch.bfloat16).contiguous(), gate
 
 
-def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0, n_splits=1):
-    """q [Tq,n_q,hd]; caches [blocks,n_kv,bs,hd]; returns bf16 [Tq,n_q,hd]."""
+def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0, n_splits=1,
+              kv_scales=None, max_kv_len=0):
+    """q [Tq,n_q,hd]; caches [blocks,n_kv,bs,hd] (bf16, or int8 with kv_scales = (k_scale, v_scale) [blocks,n_kv,bs]); returns bf16 [Tq,n_q,hd]."""
     Tq, n_q, hd = q.shape
     n_kv, bs = k_cache.shape[1], k_cache.shape[2]
     gqa = n_q // n_kv
@@ -180,8 +188,11 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
         L = int(seq_lens[b])
         nblk = (L + bs - 1) // bs
         blocks = block_table[b, :nblk].long()
-        K = k_cache[blocks].permute(1, 0, 2, 3).reshape(n_kv, nblk * bs, hd)[:, :L].to(torch.float32)
-        V = v_cache[blocks].permute(1, 0, 2, 3).reshape(n_kv, nblk * bs, hd)[:, :L].to(torch.float32)
+        Kp, Vp = k_cache[blocks].to(torch.float32), v_cache[blocks].to(torch.float32)
+        if kv_scales is not None:
+            Kp, Vp = Kp * kv_scales[0][blocks].unsqueeze(-1), Vp * kv_scales[1][blocks].unsqueeze(-1)
+        K = Kp.permute(1, 0, 2, 3).reshape(n_kv, nblk * bs, hd)[:, :L]
+        V = Vp.permute(1, 0, 2, 3).reshape(n_kv, nblk * bs, hd)[:, :L]
         qq = q[q0:q1].to(torch.float32) * scale                                 # [t, n_q, hd]
         Kh = K.repeat_interleave(gqa, dim=0)
         Vh = V.repeat_interleave(gqa, dim=0)

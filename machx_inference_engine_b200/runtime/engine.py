@@ -180,6 +180,7 @@ class EngineOptions:
     spec_k: int = 0                     # MTP draft length (hybrid models with an MTP head)
     max_state_snapshots: int = 12       # hybrid models: recurrent-state snapshots kept for prefix reuse
     prefill_graphs: bool = True         # replay single-sequence prefill chunks of 512/1024/2048/4096/8192 tokens (or the full step budget) as CUDA graphs
+    kv_dtype: str = "bf16"              # "int8": K/V rows stored as int8 with a per-row scale (halves the cache; `--int8-kv`)
 
 
 class Scheduler:
@@ -285,10 +286,10 @@ class LLMEngine:
         if o.kv_memory_fraction > 0 and self.device.type == "cuda":
             free, _ = torch.cuda.mem_get_info(self.device)
             from ..models.transformer import KVCache
-            per = max(1, KVCache.bytes_per_block(len(model.attn_layers), model.n_kv_local, cfg.head_dim))
+            per = max(1, KVCache.bytes_per_block(len(model.attn_layers), model.n_kv_local, cfg.head_dim, o.kv_dtype))
             nb = max(blocks_per_seq + 1, int(free * o.kv_memory_fraction) // per)
         self.max_blocks_per_seq = blocks_per_seq
-        self.kv = model.new_kv_cache(nb)
+        self.kv = model.new_kv_cache(nb, o.kv_dtype) if o.kv_dtype != "bf16" else model.new_kv_cache(nb)
         n_state = o.max_seqs if getattr(model, "needs_state", False) else 0
         self.state = model.new_state(n_state + 1) if n_state else None      # the extra slot absorbs graph-padding rows
         self.bm = BlockManager(nb, o.enable_prefix_cache)
@@ -467,7 +468,8 @@ class LLMEngine:
                      and len(plan) <= max(self.opts.graph_batch_sizes) and not nccl_path and not self.spec_k)
         if use_graph:
             return self._run_graph(plan)
-        if (self.opts.cuda_graphs and self.opts.prefill_graphs and self.device.type == "cuda" and not nccl_path and len(plan) == 1
+        if (self.opts.cuda_graphs and self.opts.prefill_graphs and self.opts.kv_dtype == "bf16" and self.device.type == "cuda" and not nccl_path
+                and len(plan) == 1
                 and (plan[0][1] in (512, 1024, 2048, 4096, 8192) or (plan[0][1] == self.opts.max_batch_tokens and plan[0][1] % KV_BLOCK == 0
                                                                       and plan[0][1] >= 256)) and not self.spec_k):
             return self._run_prefill_graph(plan, sampled_rows, seqs)
@@ -475,6 +477,7 @@ class LLMEngine:
         dev = self._to_device(host)
         fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], max_q,
                           logit_rows=dev["logit_rows"] if sampled_rows else dev["cu_q"][1:2].long() - 1)
+        fb.max_kv_len = max(s.n_computed + n for s, n in plan)
         if self.state is not None:
             fb.state_slots_host = [s.state_slot for s, _ in plan]
             fb.state_slots = dev["state_slots"]

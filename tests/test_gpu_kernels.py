@@ -388,6 +388,63 @@ def test_attention_decode_and_prefill(hd, n_q, n_kv, window):
     assert torch.allclose(got.float(), torch.full_like(got.float(), 0.25), atol=2e-3)
 
 
+def _quantise_cache(c):
+    """bf16 pages -> (int8 pages, per-row fp32 scales) with the cache's own rule: scale = max|x| / 127."""
+    f = c.float()
+    amax = f.abs().amax(-1)
+    sc = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    return torch.round(f / sc.unsqueeze(-1)).clamp(-127, 127).to(torch.int8), sc
+
+
+def test_qkv_post_int8_cache_rows():
+    T, bs, nblk, n_q, n_kv, hd = 37, 128, 3, 8, 2, 128
+    cols = n_q * hd + 2 * n_kv * hd
+    qkv = (torch.randn(T, cols, device=dev()) * 3).to(torch.bfloat16)
+    kn = torch.rand(hd, device=dev())
+    pos = torch.arange(50, 50 + T, dtype=torch.int32, device=dev())
+    cos, sin = _rope_tables(256, hd)
+    slots = (torch.arange(T, device=dev()) + 120).to(torch.int64)
+    slots[5] = -1
+    got = [torch.zeros(nblk, n_kv, bs, hd, dtype=torch.int8, device=dev()) for _ in range(2)]
+    gs = [torch.ones(nblk, n_kv, bs, device=dev()) for _ in range(2)]
+    want = [torch.zeros(nblk, n_kv, bs, hd, dtype=torch.bfloat16, device=dev()) for _ in range(2)]
+    q1, _ = K().qkv_post(qkv, None, kn, kn, pos, cos, sin, slots, got[0], got[1], n_q, n_kv, hd, hd, kv_scales=(gs[0], gs[1]))
+    q2, _ = ref.qkv_post(qkv, None, kn, kn, pos, cos, sin, slots, want[0], want[1], n_q, n_kv, hd, hd)
+    assert rel_err(q1, q2) < 1e-2
+    for g8, sc, w in zip(got, gs, want):
+        deq = g8.float() * sc.unsqueeze(-1)
+        # every element within one quantisation step (plus the oracle's own bf16 rounding) of the unquantised row
+        assert bool(((deq - w.float()).abs() <= sc.unsqueeze(-1) * 0.51 + w.float().abs() * 0.005 + 1e-6).all())
+        wmax = w.float().abs().amax(-1)
+        written = wmax > 0
+        assert torch.allclose(sc[written], wmax[written] / 127.0, rtol=1e-2)
+        assert bool((sc[~written] == 1).all()) and bool((g8[~written] == 0).all())     # untouched rows (incl. the skipped token)
+
+
+@pytest.mark.parametrize("hd,n_q,n_kv", [(64, 16, 2), (128, 8, 2), (256, 4, 1)])
+@pytest.mark.parametrize("window", [0, 128])
+def test_attention_int8_cache(hd, n_q, n_kv, window):
+    sinks = torch.randn(n_q, device=dev())
+    # decode over int8 pages, several split counts
+    q, kc, vc, bt, sl, cu = _paged_case(3, [1, 1, 1], [1, 300, 515], n_q, n_kv, hd)
+    (k8, ks), (v8, vs) = _quantise_cache(kc), _quantise_cache(vc)
+    want = ref.attention(q, k8, v8, bt, sl, cu, 1, sinks=sinks, window=window, kv_scales=(ks, vs))
+    assert rel_err(want, ref.attention(q, kc, vc, bt, sl, cu, 1, sinks=sinks, window=window)) < 3e-2      # the format itself is close to bf16
+    for splits in (1, 3, None):
+        got = K().attention(q, k8, v8, bt, sl, cu, 1, sinks=sinks, window=window, n_splits=splits, kv_scales=(ks, vs))
+        assert rel_err(got, want) < 1e-2, splits
+    # prefill: CUDA-core kernel (soft-cap) and, for head dims it supports, page expansion + the tensor-core kernel
+    q, kc, vc, bt, sl, cu = _paged_case(3, [70, 5, 130], [70, 205, 400], n_q, n_kv, hd, seed=1)
+    (k8, ks), (v8, vs) = _quantise_cache(kc), _quantise_cache(vc)
+    got = K().attention(q, k8, v8, bt, sl, cu, 130, window=window, softcap=30.0, kv_scales=(ks, vs))
+    assert rel_err(got, ref.attention(q, k8, v8, bt, sl, cu, 130, window=window, softcap=30.0, kv_scales=(ks, vs))) < 1e-2
+    want = ref.attention(q, k8, v8, bt, sl, cu, 130, sinks=sinks, window=window, kv_scales=(ks, vs))
+    for max_kv in (0, 400):
+        got = K().attention(q, k8, v8, bt, sl, cu, 130, sinks=sinks, window=window, kv_scales=(ks, vs), max_kv_len=max_kv)
+        K().check_status()
+        assert rel_err(got, want) < 1.5e-2, max_kv
+
+
 @pytest.mark.parametrize("hd,n_q,n_kv", [(64, 16, 2), (128, 8, 2)])
 @pytest.mark.parametrize("window", [0, 128])
 @pytest.mark.parametrize("use_sinks", [False, True])
