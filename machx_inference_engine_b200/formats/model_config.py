@@ -266,6 +266,15 @@ def preset(name: str) -> ModelConfig:
         "tiny-qwen35": ModelConfig(arch="qwen35", n_layers=4, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=2048,
                                    rms_eps=1e-6, rope_theta=1e7, n_rot=32, ctx_train=4096, full_attn_interval=4, ssm_inner=512,
                                    ssm_state=128, ssm_n_k_heads=2, ssm_n_v_heads=4, ssm_conv_kernel=4, nextn_predict_layers=1),
+        # "crown": Qwen3.6-35B-A3B (qwen36.cpp: 40 layers, full attention every 4th, 256 experts top-8 + shared expert, MTP block)
+        "qwen3.6-35b-a3b": ModelConfig(arch="qwen35moe", n_layers=40, hidden=2048, n_heads=16, n_kv_heads=2, head_dim=256, ffn=5120,
+                                       vocab=248320, rms_eps=1e-6, rope_theta=1e7, n_rot=64, ctx_train=262144, n_experts=256,
+                                       n_experts_used=8, expert_ffn=512, shared_expert_ffn=512, full_attn_interval=4, ssm_inner=4096,
+                                       ssm_state=128, ssm_n_k_heads=16, ssm_n_v_heads=32, ssm_conv_kernel=4, nextn_predict_layers=1),
+        "tiny-qwen35moe": ModelConfig(arch="qwen35moe", n_layers=4, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=2048,
+                                      rms_eps=1e-6, rope_theta=1e7, n_rot=32, ctx_train=4096, n_experts=8, n_experts_used=2,
+                                      expert_ffn=256, shared_expert_ffn=256, full_attn_interval=4, ssm_inner=512, ssm_state=128,
+                                      ssm_n_k_heads=2, ssm_n_v_heads=4, ssm_conv_kernel=4, nextn_predict_layers=1),
         "qwen3.6-27b": ModelConfig(arch="qwen35", n_layers=64, hidden=5120, n_heads=24, n_kv_heads=4, head_dim=256, ffn=17408, vocab=248320,
                                    rms_eps=1e-6, rope_theta=1e7, n_rot=64, ctx_train=262144, full_attn_interval=4, ssm_inner=6144,
                                    ssm_state=128, ssm_n_k_heads=16, ssm_n_v_heads=48, ssm_conv_kernel=4, nextn_predict_layers=1),

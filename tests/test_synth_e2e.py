@@ -46,7 +46,7 @@ def test_synth_roundtrip_config_and_generate(ckpts, name):
     assert chat.finish_reason in ("stop", "length") and chat.error == ""
 
 
-@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-phi3", "tiny-granite", "tiny-qwen35"])
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-phi3", "tiny-granite", "tiny-qwen35", "tiny-qwen35moe"])
 def test_more_families_load_from_file_and_generate(tmp_path, name):
     """Qwen2 (q/k/v biases), Phi-3 (fused attn_qkv and gate|up tensors), Granite (embedding / residual / attention / logit
     scales) and the dense hybrid: file -> loader -> graph -> tokens; the file path equals the in-memory random-init path."""
