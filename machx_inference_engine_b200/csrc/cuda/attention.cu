@@ -289,6 +289,7 @@ static int attention_impl(const void* q, const void* k_cache, const void* v_cach
     case 64: rc = MX_ATT(64); break;
     case 128: rc = MX_ATT(128); break;
     case 256: rc = MX_ATT(256); break;
+    case 512: rc = MX_ATT(512); break;      // Gemma-4 global layers
     default: return -112;
   }
 #undef MX_ATT

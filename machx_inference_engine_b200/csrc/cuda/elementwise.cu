@@ -115,6 +115,7 @@ struct QkvPostParams {
   int T, n_q, n_kv, hd, n_rot, block_size;
   int q_gate;                 // 1: q columns hold per-head [q(hd) | gate(hd)]
   int norm_one_plus_w;
+  int v_norm;                 // 1: V rows get a weightless RMS norm (Gemma-4)
   float eps;
   int max_pos;
 };
@@ -156,6 +157,10 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / hd + p.eps);
     for (int i = lane; i < hd; i += 32) v[i] = v[i] * inv * (p.norm_one_plus_w ? 1.f + nw[i] : nw[i]);
+  } else if (kind == 2 && p.v_norm) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / hd + p.eps);
+    for (int i = lane; i < hd; i += 32) v[i] *= inv;
   }
   __syncwarp();
   if (kind != 2 && p.n_rot > 0) {
@@ -334,7 +339,8 @@ MX_HOST_API int mx_qkv_post_kv8(const void* qkv, const float* bias, const float*
   p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.slot_map = slot_map; p.q_out = (__nv_bfloat16*)q_out; p.gate_out = (__nv_bfloat16*)gate_out;
   p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
   p.k_scale = k_scale; p.v_scale = k_scale ? v_scale : nullptr;
-  p.T = T; p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.n_rot = n_rot; p.block_size = block_size; p.q_gate = q_gate;
+  p.T = T; p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.n_rot = n_rot; p.block_size = block_size; p.q_gate = q_gate & 1;
+  p.v_norm = (q_gate >> 1) & 1;           // flag word: bit 0 = q columns carry a gate, bit 1 = weightless RMS norm on V
   p.norm_one_plus_w = norm_one_plus_w; p.eps = eps; p.max_pos = max_pos;
   const int units = T * (n_q + 2 * n_kv);
   launch_pdl(qkv_post_kernel, dim3((units + 3) / 4), dim3(128), 0, st, p);

@@ -1,7 +1,7 @@
 """Architecture detection and one typed config for every model family.
 
 Reference parity: src/loaders/model_config.cpp:8-359 and include/ie/model_config.hpp:12-254
-(``detect_arch``, ``read_dense_config``, ``read_{qwen35,qwen3moe,gptoss,qwen3next}_config``,
+(``detect_arch``, ``read_dense_config``, ``read_{qwen35,qwen3moe,gptoss,qwen3next,gemma4}_config``,
 template-family classification, sliding-window load guard, Granite scalars).  The reference
 keeps one struct per family; here one dataclass serves all graphs.
 """
@@ -13,7 +13,8 @@ from typing import Any, Mapping
 DENSE_ARCHS = ("llama", "qwen2", "qwen3", "phi3", "granite", "mistral")
 MOE_ARCHS = ("qwen3moe", "gpt-oss")
 HYBRID_ARCHS = ("qwen3next", "qwen35", "qwen35moe")
-SUPPORTED_ARCHS = DENSE_ARCHS + MOE_ARCHS + HYBRID_ARCHS
+GEMMA_ARCHS = ("gemma4",)
+SUPPORTED_ARCHS = DENSE_ARCHS + MOE_ARCHS + HYBRID_ARCHS + GEMMA_ARCHS
 
 
 class ConfigError(ValueError):
@@ -54,6 +55,13 @@ class ModelConfig:
     ssm_n_v_heads: int = 0
     ssm_conv_kernel: int = 0
     nextn_predict_layers: int = 0
+    # Gemma-4: two head geometries chosen per layer (include/ie/model_config.hpp:216-249); head_dim / n_rot / rope_theta above
+    # describe the global (full-attention) layers, the *_swa fields the sliding-window layers
+    head_dim_swa: int = 0
+    n_rot_swa: int = 0
+    rope_theta_swa: float = 10000.0
+    layer_swa: list = field(default_factory=list)        # per layer: True = sliding-window layer
+    layer_n_kv: list = field(default_factory=list)       # per layer: KV head count
     # Granite scalars
     embedding_scale: float = 1.0
     residual_scale: float = 1.0
@@ -80,10 +88,21 @@ class ModelConfig:
         return (layer + 1) % self.full_attn_interval == 0
 
     def layer_window(self, layer: int) -> int:
-        """Sliding window of a layer (0 = full).  gpt-oss windows the even layers (src/model/gptoss.cpp:133)."""
+        """Sliding window of a layer (0 = full).  gpt-oss windows the even layers (src/model/gptoss.cpp:133), Gemma-4 the
+        layers its pattern marks (src/model/gemma4.cpp:709-714)."""
         if self.arch == "gpt-oss":
             return self.sliding_window if layer % 2 == 0 else 0
+        if self.arch == "gemma4":
+            return self.sliding_window if self.layer_swa[layer] else 0
         return self.sliding_window
+
+    def layer_geometry(self, layer: int) -> tuple:
+        """(head_dim, n_kv_heads, n_rot, rope_theta) of a layer."""
+        if self.arch == "gemma4":
+            swa = bool(self.layer_swa[layer])
+            return (self.head_dim_swa if swa else self.head_dim, int(self.layer_n_kv[layer]), self.n_rot_swa if swa else self.n_rot,
+                    self.rope_theta_swa if swa else self.rope_theta)
+        return (self.head_dim, self.n_kv_heads, self.n_rot, self.rope_theta)
 
     def to_dict(self) -> dict:
         return asdict(self)
@@ -132,9 +151,11 @@ def read_config(kv: Mapping[str, Any], tensor_names=()) -> ModelConfig:
     c.n_layers = int(get("block_count", required=True))
     c.hidden = int(get("embedding_length", required=True))
     c.n_heads = int(get("attention.head_count", required=True))
-    c.n_kv_heads = int(get("attention.head_count_kv", c.n_heads))
-    if isinstance(kv.get(f"{arch}.attention.head_count_kv"), list):       # per-layer arrays: take the max
-        c.n_kv_heads = max(int(v) for v in kv[f"{arch}.attention.head_count_kv"] if v) or c.n_heads
+    hkv = get("attention.head_count_kv", c.n_heads)
+    if isinstance(hkv, (list, tuple)):                                     # per-layer arrays: take the max
+        c.n_kv_heads = max([int(v) for v in hkv if v] or [c.n_heads])
+    else:
+        c.n_kv_heads = int(hkv)
     c.ffn = int(get("feed_forward_length", 0) or 0)
     c.head_dim = int(get("attention.key_length", c.hidden // c.n_heads))
     c.n_rot = int(get("rope.dimension_count", c.head_dim))
@@ -164,6 +185,24 @@ def read_config(kv: Mapping[str, Any], tensor_names=()) -> ModelConfig:
     c.rope_scaling_factor = float(get("rope.scaling.factor", 1.0))
     c.rope_orig_ctx = int(get("rope.scaling.original_context_length", 0) or 0)
 
+    if arch == "gemma4":
+        c.head_dim_swa = int(get("attention.key_length_swa", required=True))
+        c.n_rot_swa = int(get("rope.dimension_count_swa", c.head_dim_swa))
+        c.rope_theta_swa = float(get("rope.freq_base_swa", 10000.0))
+        pat = get("attention.sliding_window_pattern", None)
+        c.layer_swa = [bool(v) for v in pat] if isinstance(pat, (list, tuple)) else [False] * c.n_layers
+        hk = get("attention.head_count_kv", required=True)
+        c.layer_n_kv = [int(v) for v in hk] if isinstance(hk, (list, tuple)) else [int(hk)] * c.n_layers
+        if len(c.layer_swa) != c.n_layers or len(c.layer_n_kv) != c.n_layers:
+            raise ConfigError("gemma4: per-layer arrays do not match block_count")
+        if any(c.n_heads % max(v, 1) for v in c.layer_n_kv):
+            raise ConfigError("gemma4: attention.head_count is not a multiple of a layer's head_count_kv")
+        c.embedding_scale = float(c.hidden) ** 0.5
+        c.attention_scale = 1.0                 # q and k are RMS-normalised per head; the reference's net scale is 1
+        if int(get("expert_count", 0) or 0) > 0:
+            c.n_experts = int(get("expert_count"))
+            c.n_experts_used = int(get("expert_used_count", required=True))
+            c.expert_ffn = int(get("expert_feed_forward_length", required=True))
     if arch in ("qwen3moe", "gpt-oss", "qwen3next", "qwen35moe"):
         c.n_experts = int(get("expert_count", required=True))
         c.n_experts_used = int(get("expert_used_count", required=True))
@@ -224,6 +263,14 @@ def config_to_kv(c: ModelConfig) -> dict:
         kv[f"{a}.ssm.conv_kernel"] = c.ssm_conv_kernel
         if c.nextn_predict_layers:
             kv[f"{a}.nextn_predict_layers"] = c.nextn_predict_layers
+    if a == "gemma4":
+        kv[f"{a}.attention.head_count_kv"] = [int(v) for v in c.layer_n_kv]
+        kv[f"{a}.attention.sliding_window_pattern"] = [bool(v) for v in c.layer_swa]
+        kv[f"{a}.attention.key_length_swa"] = c.head_dim_swa
+        kv[f"{a}.attention.value_length_swa"] = c.head_dim_swa
+        kv[f"{a}.rope.dimension_count_swa"] = c.n_rot_swa or c.head_dim_swa
+        kv[f"{a}.rope.freq_base_swa"] = float(c.rope_theta_swa)
+        kv[f"{a}.final_logit_softcapping"] = float(c.final_logit_softcap)
     if a == "granite":
         kv[f"{a}.embedding_scale"] = float(c.embedding_scale)
         kv[f"{a}.residual_scale"] = float(c.residual_scale)
@@ -278,6 +325,15 @@ def preset(name: str) -> ModelConfig:
         "qwen3.6-27b": ModelConfig(arch="qwen35", n_layers=64, hidden=5120, n_heads=24, n_kv_heads=4, head_dim=256, ffn=17408, vocab=248320,
                                    rms_eps=1e-6, rope_theta=1e7, n_rot=64, ctx_train=262144, full_attn_interval=4, ssm_inner=6144,
                                    ssm_state=128, ssm_n_k_heads=16, ssm_n_v_heads=48, ssm_conv_kernel=4, nextn_predict_layers=1),
+        # Gemma-4 shape in miniature: sliding layers with more, narrower KV heads and one global layer with wide heads; MoE dual path
+        "tiny-gemma4": ModelConfig(arch="gemma4", n_layers=3, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=2048,
+                                   rms_eps=1e-6, rope_theta=1e6, n_rot=128, ctx_train=4096, sliding_window=128, head_dim_swa=64, n_rot_swa=64,
+                                   rope_theta_swa=10000.0, layer_swa=[True, True, False], layer_n_kv=[2, 2, 1], n_experts=8, n_experts_used=2,
+                                   expert_ffn=128, final_logit_softcap=30.0, embedding_scale=16.0, attention_scale=1.0, tie_embeddings=True),
+        "tiny-gemma4-dense": ModelConfig(arch="gemma4", n_layers=3, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=2048,
+                                         rms_eps=1e-6, rope_theta=1e6, n_rot=128, ctx_train=4096, sliding_window=128, head_dim_swa=64,
+                                         n_rot_swa=64, rope_theta_swa=10000.0, layer_swa=[True, True, False], layer_n_kv=[2, 2, 1],
+                                         final_logit_softcap=30.0, embedding_scale=16.0, attention_scale=1.0, tie_embeddings=True),
         "tiny-qwen2": ModelConfig(arch="qwen2", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=2048,
                                   rms_eps=1e-6, rope_theta=1e6, n_rot=64, ctx_train=4096),
         "tiny-phi3": ModelConfig(arch="phi3", n_layers=2, hidden=256, n_heads=4, n_kv_heads=4, head_dim=64, ffn=512, vocab=2048,

@@ -93,10 +93,12 @@ def synthetic_tokenizer_kv(cfg: ModelConfig) -> dict:
 
 
 def tensor_plan(c: ModelConfig) -> list:
-    """[(name, kind, dims)] for every tensor of the architecture; ``kind`` in matrix | expert | norm | vector | conv | ssm_a.
+    """[(name, kind, dims)] for every tensor of the architecture; ``kind`` in matrix | expert | router | router_sharp | norm | qnorm | vector | conv | ssm_a.
     ``dims`` are ggml-ordered."""
     H, hd = c.hidden, c.head_dim
     out = [("token_embd.weight", "matrix", (H, c.vocab)), ("output_norm.weight", "norm", (H,))]
+    if c.arch == "gemma4":
+        return out + _gemma4_plan(c)
     if not c.tie_embeddings:
         out.append(("output.weight", "matrix", (H, c.vocab)))
     q_gate = c.is_hybrid
@@ -159,10 +161,35 @@ def tensor_plan(c: ModelConfig) -> list:
     return out
 
 
+def _gemma4_plan(c: ModelConfig) -> list:
+    """Gemma-4 tensors (src/model/gemma4.cpp:160-290): per-layer head geometry, no attn_v on the global layers (V is the raw K
+    projection), sandwich norms, a dense GeGLU FFN on every layer and, on MoE checkpoints, a routed path with a fused gate|up bank."""
+    H, out = c.hidden, []
+    for l in range(c.n_layers):
+        p = f"blk.{l}"
+        hd, n_kv, _, _ = c.layer_geometry(l)
+        out += [(f"{p}.attn_norm.weight", "norm", (H,)), (f"{p}.attn_q.weight", "matrix", (H, c.n_heads * hd)),
+                (f"{p}.attn_k.weight", "matrix", (H, n_kv * hd))]
+        if c.layer_swa[l]:
+            out.append((f"{p}.attn_v.weight", "matrix", (H, n_kv * hd)))
+        out += [(f"{p}.attn_output.weight", "matrix", (c.n_heads * hd, H)), (f"{p}.attn_q_norm.weight", "qnorm", (hd,)),
+                (f"{p}.attn_k_norm.weight", "norm", (hd,)), (f"{p}.post_attention_norm.weight", "norm", (H,)),
+                (f"{p}.ffn_norm.weight", "norm", (H,)), (f"{p}.ffn_gate.weight", "matrix", (H, c.ffn)), (f"{p}.ffn_up.weight", "matrix", (H, c.ffn)),
+                (f"{p}.ffn_down.weight", "matrix", (c.ffn, H)), (f"{p}.post_ffw_norm.weight", "norm", (H,)),
+                (f"{p}.layer_output_scale.weight", "norm", (1,))]
+        if c.is_moe:
+            E, F = c.n_experts, c.expert_ffn
+            out += [(f"{p}.ffn_gate_inp.weight", "router_sharp", (H, E)), (f"{p}.ffn_gate_inp.scale", "norm", (H,)),
+                    (f"{p}.pre_ffw_norm_2.weight", "norm", (H,)), (f"{p}.post_ffw_norm_1.weight", "norm", (H,)),
+                    (f"{p}.post_ffw_norm_2.weight", "norm", (H,)), (f"{p}.ffn_gate_up_exps.weight", "expert", (H, 2 * F, E)),
+                    (f"{p}.ffn_down_exps.weight", "expert", (F, H, E)), (f"{p}.ffn_down_exps.scale", "norm", (E,))]
+    return out
+
+
 def _matrix_type(name: str, kind: str, K: int, quant: str, n_layers: int) -> int:
     from ..models.sources import _N_LAYERS_HINT, default_policy
     from ..ops.weights import WFormat
-    if kind == "router":
+    if kind in ("router", "router_sharp"):
         return GGMLType.F32
     _N_LAYERS_HINT["n"] = n_layers
     fmt = default_policy("", quant)(name)
@@ -182,6 +209,8 @@ def _payload(name: str, kind: str, dims: tuple, ttype: int, seed: int) -> Callab
         n = int(np.prod(dims))
         if kind == "norm":
             return (1.0 + 0.05 * g.standard_normal(n)).astype(np.float32)
+        if kind == "qnorm":      # Gemma-4 attends with scale 1 on RMS-normalised q and k: a small q gain keeps random-init scores moderate
+            return (0.25 + 0.02 * g.standard_normal(n)).astype(np.float32)
         if kind == "ssm_a":
             return (-np.exp(0.5 * g.standard_normal(n))).astype(np.float32)
         if kind == "vector":
@@ -190,7 +219,8 @@ def _payload(name: str, kind: str, dims: tuple, ttype: int, seed: int) -> Callab
             return (0.3 * g.standard_normal(n)).astype(np.float32)
         rows = n // dims[0]
         if ttype == GGMLType.F32:
-            return (0.02 * g.standard_normal(n)).astype(np.float32)
+            # Gemma-4 feeds its router rms(x) / sqrt(H): unit-scale weights give logits of order one (decisive routing)
+            return ((2.0 if kind == "router_sharp" else 0.02) * g.standard_normal(n)).astype(np.float32)
         step = max(1, (1 << 24) // dims[0])            # quantise in slabs of <= 16 M elements
         out = []
         for r0 in range(0, rows, step):
@@ -222,7 +252,7 @@ def write_synthetic_gguf(cfg: ModelConfig, path: str, quant: str = "q8_0", seed:
         w.add_kv(k, v)
     n = 0
     for name, kind, dims in tensor_plan(cfg):
-        t = _matrix_type(name, kind, dims[0], quant, cfg.n_layers) if kind in ("matrix", "expert", "router") else GGMLType.F32
+        t = _matrix_type(name, kind, dims[0], quant, cfg.n_layers) if kind in ("matrix", "expert", "router", "router_sharp") else GGMLType.F32
         w.add_tensor(name, dims, int(t), _payload(name, kind, dims, int(t), seed))
         n += 1
     w.write(path)

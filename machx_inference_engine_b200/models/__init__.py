@@ -11,6 +11,9 @@ def _graph_class(cfg: ModelConfig):
     if cfg.is_hybrid:
         from .hybrid import HybridModel
         return HybridModel
+    if cfg.arch == "gemma4":
+        from .gemma4 import Gemma4Model
+        return Gemma4Model
     from .transformer import TransformerModel
     return TransformerModel
 

@@ -142,7 +142,7 @@ class SynthSource:
 
     def vector(self, name: str, n: int) -> torch.Tensor:
         g = self._gen(name)
-        if name.endswith("norm.weight") or "_norm" in name:
+        if name.endswith("norm.weight") or "_norm" in name or name.endswith(".scale") or name.endswith("layer_output_scale.weight"):
             return (1.0 + 0.05 * torch.randn(n, generator=g, device=self.gen_device)).to(self.device)
         if name.endswith("ssm_a"):
             return (-torch.exp(torch.randn(n, generator=g, device=self.gen_device) * 0.5)).to(self.device)

@@ -68,7 +68,7 @@ class KVCache:
     """
 
     def __init__(self, n_layers: int, num_blocks: int, n_kv: int, head_dim: int, device, attn_layers: Optional[list[int]] = None,
-                 dtype: str = "bf16"):
+                 dtype: str = "bf16", geometry: Optional[dict] = None):
         if dtype not in ("bf16", "int8"):
             raise ValueError(f"unknown KV cache dtype {dtype!r}")
         self.num_blocks = num_blocks
@@ -76,10 +76,11 @@ class KVCache:
         self.dtype = dtype
         layers = attn_layers if attn_layers is not None else list(range(n_layers))
         td = torch.bfloat16 if dtype == "bf16" else torch.int8
-        self.k = {l: torch.zeros(num_blocks, n_kv, KV_BLOCK, head_dim, dtype=td, device=device) for l in layers}
-        self.v = {l: torch.zeros(num_blocks, n_kv, KV_BLOCK, head_dim, dtype=td, device=device) for l in layers}
-        self.ks = {l: torch.ones(num_blocks, n_kv, KV_BLOCK, dtype=torch.float32, device=device) for l in layers} if dtype == "int8" else None
-        self.vs = {l: torch.ones(num_blocks, n_kv, KV_BLOCK, dtype=torch.float32, device=device) for l in layers} if dtype == "int8" else None
+        geo = {l: ((geometry or {}).get(l) or (n_kv, head_dim)) for l in layers}       # per layer (n_kv, head_dim): Gemma-4 mixes two
+        self.k = {l: torch.zeros(num_blocks, geo[l][0], KV_BLOCK, geo[l][1], dtype=td, device=device) for l in layers}
+        self.v = {l: torch.zeros(num_blocks, geo[l][0], KV_BLOCK, geo[l][1], dtype=td, device=device) for l in layers}
+        self.ks = {l: torch.ones(num_blocks, geo[l][0], KV_BLOCK, dtype=torch.float32, device=device) for l in layers} if dtype == "int8" else None
+        self.vs = {l: torch.ones(num_blocks, geo[l][0], KV_BLOCK, dtype=torch.float32, device=device) for l in layers} if dtype == "int8" else None
 
     def scales(self, layer: int):
         return (self.ks[layer], self.vs[layer]) if self.ks is not None else None
@@ -154,6 +155,10 @@ class AttentionBlock:
     def __init__(self, cfg: ModelConfig, layer: int, src, par: ParallelCtx, prefix: Optional[str] = None, q_gate: bool = False):
         c = cfg
         p = prefix or f"blk.{layer}"
+        if c.arch == "gemma4":           # per-layer head geometry: the rest of this constructor sees a config of this layer's shape
+            from dataclasses import replace
+            hd_l, n_kv_l, n_rot_l, _ = c.layer_geometry(layer)
+            c = replace(c, head_dim=hd_l, n_kv_heads=n_kv_l, n_rot=n_rot_l)
         hd, H = c.head_dim, c.hidden
         tp = par.world if par.mode == "tp" else 1
         self.layer = layer
@@ -181,7 +186,13 @@ class AttentionBlock:
         else:
             wq = src.matrix(f"{p}.attn_q.weight", c.n_heads * q_rows_per_head, H)
             wk = src.matrix(f"{p}.attn_k.weight", c.n_kv_heads * hd, H)
-            wv = src.matrix(f"{p}.attn_v.weight", c.n_kv_heads * hd, H)
+            has_v = True
+            if c.arch == "gemma4":       # files simply lack attn_v on the global layers; random-init graphs decide by the pattern
+                has_v = src.has(f"{p}.attn_v.weight") if getattr(src, "r", None) is not None else bool(c.layer_swa[layer])
+            if not has_v:
+                wv = wk                  # V is the raw K projection (src/model/gemma4.cpp:178-183,660)
+            else:
+                wv = src.matrix(f"{p}.attn_v.weight", c.n_kv_heads * hd, H)
         if c.arch == "llama" and getattr(src, "r", None) is not None:
             wq, wk = unpermute_llama_qk(wq, c.n_heads, hd), unpermute_llama_qk(wk, c.n_kv_heads, hd)
         has_bias = c.arch in ("qwen2", "gpt-oss") and src.has(f"{p}.attn_q.bias")
@@ -198,7 +209,8 @@ class AttentionBlock:
         if tp > 1:
             wo = wo.slice_k(q_lo * hd, (q_lo + self.n_q) * hd, requant=True)
         self.o = Linear(wo, bo, reduce=tp > 1)
-        qk_norm = c.arch in ("qwen3", "qwen3moe", "qwen3next", "qwen35", "qwen35moe") and src.has(f"{p}.attn_q_norm.weight")
+        qk_norm = c.arch in ("qwen3", "qwen3moe", "qwen3next", "qwen35", "qwen35moe", "gemma4") and src.has(f"{p}.attn_q_norm.weight")
+        self.v_norm = c.arch == "gemma4"       # weightless RMS norm on V (src/model/gemma4.cpp:663)
         self.q_norm = src.vector(f"{p}.attn_q_norm.weight", hd) if qk_norm else None
         self.k_norm = src.vector(f"{p}.attn_k_norm.weight", hd) if qk_norm else None
         self.sinks = None
@@ -214,7 +226,8 @@ class AttentionBlock:
         qkv = self.qkv(h)
         q, gate = ops.qkv_post(qkv, None, self.q_norm, self.k_norm, fb.positions, rope[0], rope[1], fb.slot_map, kv.k[self.layer],
                                kv.v[self.layer], self.n_q, self.n_kv, self.hd, self.n_rot, q_gate=self.q_gate,
-                               norm_one_plus_w=self.norm_one_plus_w, eps=self.eps, kv_scales=kv.scales(self.layer))
+                               norm_one_plus_w=self.norm_one_plus_w, eps=self.eps, kv_scales=kv.scales(self.layer),
+                               **({"v_norm": True} if self.v_norm else {}))
         a = ops.attention(q, kv.k[self.layer], kv.v[self.layer], fb.block_table, fb.seq_lens, fb.cu_q, fb.max_q_len, sinks=self.sinks,
                           window=self.window, scale=self.scale, kv_scales=kv.scales(self.layer), max_kv_len=fb.max_kv_len)
         a = a.reshape(a.shape[0], self.n_q * self.hd)
@@ -294,10 +307,16 @@ class MoEFFN:
         rw = src.matrix(f"{p}.ffn_gate_inp.weight", E, H)
         self.router = Linear(rw if rw.fmt == ops.WFormat.BF16 else QuantWeight(**_as_bf16(rw)))
         self.router_bias = src.vector(f"{p}.ffn_gate_inp.bias", E) if with_bias else None
-        g = src.matrix(f"{p}.ffn_gate_exps.weight", F, H, E, experts=rng)
-        u = src.matrix(f"{p}.ffn_up_exps.weight", F, H, E, experts=rng)
+        if c.arch == "gemma4":           # one bank [E, gate rows | up rows, H] (src/model/gemma4.cpp:267-289)
+            gu = src.matrix(f"{p}.ffn_gate_up_exps.weight", 2 * F, H, E, experts=rng)
+            g, u = gu.slice_rows(0, F), gu.slice_rows(F, 2 * F)
+            del gu
+        else:
+            g = src.matrix(f"{p}.ffn_gate_exps.weight", F, H, E, experts=rng)
+            u = src.matrix(f"{p}.ffn_up_exps.weight", F, H, E, experts=rng)
         self.gate_up = QuantWeight.interleave_gate_up(g, u)
         del g, u
+        self.expert_scale = None         # optional per-expert factor on the down projection's output, folded into the routing weight
         self.down = src.matrix(f"{p}.ffn_down_exps.weight", H, F, E, experts=rng)
         self.gu_bias = self.down_bias = None
         if with_bias:
@@ -312,11 +331,14 @@ class MoEFFN:
         self.shared = None          # optional always-on expert (hybrid families): its partial joins the sum before the reduction
         self._arange = {}
 
-    def __call__(self, h: torch.Tensor, par: ParallelCtx) -> torch.Tensor:
-        """Returns this rank's fp32 contribution [T, H] (already reduced when EP > 1)."""
+    def __call__(self, h: torch.Tensor, par: ParallelCtx, router_h: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Returns this rank's fp32 contribution [T, H] (already reduced when EP > 1).  ``router_h``: the router's own input
+        when it differs from the experts' (Gemma-4)."""
         T = h.shape[0]
-        logits = self.router(h, out_f32=True)
+        logits = self.router(h if router_h is None else router_h, out_f32=True)
         idx, w = ops.moe_route(logits, self.router_bias, self.K, True)
+        if self.expert_scale is not None:
+            w = w * self.expert_scale[idx.long()]
         local = self.e_hi - self.e_lo
         # expert parallelism on the peer-memory path: the combine writes its partial into every rank's inbox itself
         fuse_push = self.reduce and par.fused is not None and h.is_cuda and self.shared is None
@@ -453,10 +475,10 @@ class TransformerModel:
         rs = c.residual_scale
         rows = fb.logit_rows if fb.logit_rows is not None else (fb.cu_q[1:].long() - 1)
         xr = x.index_select(0, rows)
-        dr = delta.index_select(0, rows).contiguous()        # (a pending fused reduction is summed here)
+        dr = delta.index_select(0, rows).contiguous() if delta is not None else None       # (a pending fused reduction is summed here)
         hidden = None
         if fb.want_hidden:
-            hidden = xr + dr.to(torch.float32) * rs
+            hidden = xr + dr.to(torch.float32) * rs if dr is not None else xr.clone()
         hn = ops.rmsnorm(xr, self.out_norm, c.rms_eps, delta=dr, one_plus_w=self.one_plus_w, delta_scale=rs)
         logits = self.lm_head(hn, out_f32=True)
         if self.vocab_hi - self.vocab_lo != c.vocab:

@@ -162,7 +162,7 @@ def deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, sta
 
 
 def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_map, k_cache, v_cache, n_q, n_kv, hd, n_rot,
-             q_gate=False, norm_one_plus_w=False, eps=1e-6, kv_scales=None):
+             q_gate=False, norm_one_plus_w=False, eps=1e-6, kv_scales=None, v_norm=False):
     T = qkv.shape[0]
     q = torch.empty(T, n_q, hd, dtype=torch.bfloat16, device=qkv.device)
     gate = torch.empty(T, n_q, hd, dtype=torch.bfloat16, device=qkv.device) if q_gate else None
@@ -175,7 +175,7 @@ def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_
     ks, vs = kv_scales if kv_scales is not None else (None, None)
     _check(_lib.cuda().mx_qkv_post_kv8(_p(qkv), _p(bias), _p(q_norm_w), _p(k_norm_w), _p(positions), _p(rope_cos), _p(rope_sin),
                                        _p(slot_map), _p(q), _p(gate), _p(k_cache), _p(v_cache), _p(ks), _p(vs), T, n_q, n_kv, hd, n_rot, bs,
-                                       int(q_gate), int(norm_one_plus_w), C.c_float(eps), max_pos, _stream()), "qkv_post")
+                                       int(q_gate) | (2 if v_norm else 0), int(norm_one_plus_w), C.c_float(eps), max_pos, _stream()), "qkv_post")
     _count()
     return q, gate
 

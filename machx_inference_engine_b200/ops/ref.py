@@ -124,7 +124,7 @@ def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE
 
 
 def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_map, k_cache, v_cache, n_q, n_kv, hd, n_rot,
-             q_gate=False, norm_one_plus_w=False, eps=1e-6, kv_scales=None):
+             q_gate=False, norm_one_plus_w=False, eps=1e-6, kv_scales=None, v_norm=False):
     """Returns (q [T,n_q,hd] bf16, gate or None); writes K/V into the paged cache (int8 rows + scales when kv_scales is given)."""
     T = qkv.shape[0]
     x = qkv.to(torch.float32)
@@ -147,6 +147,8 @@ def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_
         return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * g
 
     qpart, k = norm(qpart, q_norm_w), norm(k, k_norm_w)
+    if v_norm:
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
     if n_rot > 0:
         half = n_rot // 2
         pos = positions.long().clamp(0, rope_cos.shape[0] - 1)

@@ -331,7 +331,8 @@ def _rope_tables(max_pos, n_rot, theta=10000.0):
 
 @pytest.mark.parametrize("cfg", [dict(n_q=4, n_kv=2, hd=64, n_rot=64, gate=False, norm=False, bias=True),
                                  dict(n_q=8, n_kv=2, hd=128, n_rot=128, gate=False, norm=True, bias=False),
-                                 dict(n_q=4, n_kv=1, hd=256, n_rot=64, gate=True, norm=True, bias=False)])
+                                 dict(n_q=4, n_kv=1, hd=256, n_rot=64, gate=True, norm=True, bias=False),
+                                 dict(n_q=4, n_kv=1, hd=512, n_rot=512, gate=False, norm=True, bias=False, v_norm=True)])
 def test_qkv_post(cfg):
     T, bs, nblk = 19, 128, 4
     n_q, n_kv, hd = cfg["n_q"], cfg["n_kv"], cfg["hd"]
@@ -346,8 +347,9 @@ def test_qkv_post(cfg):
     slots[3] = -1
     kc = [torch.zeros(nblk, n_kv, bs, hd, dtype=torch.bfloat16, device=dev()) for _ in range(2)]
     vc = [torch.zeros_like(kc[0]) for _ in range(2)]
-    q1, g1 = K().qkv_post(qkv, bias, qn, kn, pos, cos, sin, slots, kc[0], vc[0], n_q, n_kv, hd, cfg["n_rot"], q_gate=cfg["gate"])
-    q2, g2 = ref.qkv_post(qkv, bias, qn, kn, pos, cos, sin, slots, kc[1], vc[1], n_q, n_kv, hd, cfg["n_rot"], q_gate=cfg["gate"])
+    extra = {"v_norm": True} if cfg.get("v_norm") else {}       # Gemma-4: weightless RMS norm on V, head_dim 512
+    q1, g1 = K().qkv_post(qkv, bias, qn, kn, pos, cos, sin, slots, kc[0], vc[0], n_q, n_kv, hd, cfg["n_rot"], q_gate=cfg["gate"], **extra)
+    q2, g2 = ref.qkv_post(qkv, bias, qn, kn, pos, cos, sin, slots, kc[1], vc[1], n_q, n_kv, hd, cfg["n_rot"], q_gate=cfg["gate"], **extra)
     assert rel_err(q1, q2) < 1e-2 and rel_err(kc[0], kc[1]) < 1e-2 and rel_err(vc[0], vc[1]) < 1e-2
     if cfg["gate"]:
         assert rel_err(g1, g2) < 1e-2
@@ -367,7 +369,7 @@ def _paged_case(B, q_lens, kv_lens, n_q, n_kv, hd, bs=128, seed=0):
     return q, kc, vc, bt, sl, cu
 
 
-@pytest.mark.parametrize("hd,n_q,n_kv", [(64, 16, 2), (128, 8, 2), (256, 4, 1)])
+@pytest.mark.parametrize("hd,n_q,n_kv", [(64, 16, 2), (128, 8, 2), (256, 4, 1), (512, 4, 2)])
 @pytest.mark.parametrize("window", [0, 128])
 def test_attention_decode_and_prefill(hd, n_q, n_kv, window):
     sinks = torch.randn(n_q, device=dev())

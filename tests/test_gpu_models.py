@@ -111,3 +111,46 @@ def test_programmatic_dependent_launch_gives_identical_tokens():
         K.set_pdl(True)
     assert outs[(True, False)] == outs[(False, False)]
     assert outs[(True, True)] == outs[(False, True)]
+
+
+@pytest.mark.parametrize("name", ["tiny-gemma4-dense", "tiny-gemma4"])
+def test_gemma4_file_on_cuda_matches_cpu_path(tmp_path, name):
+    """Per-layer head geometry (head_dim 64 / 128 pages), V norm, sandwich norms, GeGLU dual path, soft-cap: the CUDA kernels against
+    the fp32 PyTorch path on the same file, whole-prompt and chunked prefill, then graphed decode through the engine."""
+    from machx_inference_engine_b200.formats.synth import write_synthetic_gguf
+    from machx_inference_engine_b200.models import load_model
+    from machx_inference_engine_b200.models.transformer import KV_BLOCK, ForwardBatch
+    cfg = preset(name)
+    path = str(tmp_path / "g.gguf")
+    write_synthetic_gguf(cfg, path, quant="q8_0", seed=4)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, cfg.vocab, (300,), generator=g).tolist()
+
+    def all_logits(model, chunk):
+        d = model.device
+        nb = (len(ids) + KV_BLOCK - 1) // KV_BLOCK
+        kv = model.new_kv_cache(nb + 1)
+        bt = torch.arange(1, nb + 1, dtype=torch.int32, device=d).reshape(1, nb)
+        out = []
+        for lo in range(0, len(ids), chunk):
+            hi = min(len(ids), lo + chunk)
+            pos = torch.arange(lo, hi, dtype=torch.int32, device=d)
+            slot = torch.tensor([(1 + p // KV_BLOCK) * KV_BLOCK + p % KV_BLOCK for p in range(lo, hi)], dtype=torch.int64, device=d)
+            fb = ForwardBatch(torch.tensor(ids[lo:hi], dtype=torch.int32, device=d), pos, slot, bt, torch.tensor([hi], dtype=torch.int32, device=d),
+                              torch.tensor([0, hi - lo], dtype=torch.int32, device=d), hi - lo, logit_rows=torch.arange(hi - lo, device=d))
+            out.append(model.forward(fb, kv).float().cpu())
+        return torch.cat(out)
+    cpu, _ = load_model(path, torch.device("cpu"), max_ctx=1024)
+    gpu, _ = load_model(path, torch.device("cuda:0"), max_ctx=1024)
+    want = all_logits(cpu, 300)
+    for chunk in (300, 77):
+        cos = torch.nn.functional.cosine_similarity(all_logits(gpu, chunk), want, dim=1)
+        if cfg.is_moe:
+            assert float(cos.median()) > 0.999 and float((cos > 0.99).float().mean()) > 0.9, (chunk, float(cos.median()))
+        else:
+            assert float(cos.min()) > 0.998, (chunk, float(cos.min()))
+    outs = {}
+    for key, m in (("cpu", cpu), ("gpu", gpu)):
+        eng = LLMEngine(m, EngineOptions(max_ctx=1024, max_batch_tokens=128, max_seqs=2, cuda_graphs=True))
+        outs[key] = eng.generate([ids[:150]], SamplingParams(max_tokens=8))[0]
+    assert outs["cpu"][0] == outs["gpu"][0] and sum(a == b for a, b in zip(outs["cpu"], outs["gpu"])) >= 5, outs
