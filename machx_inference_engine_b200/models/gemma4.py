@@ -81,7 +81,11 @@ class Gemma4Model(TransformerModel):
 
     # ---- forward
     def _buffers(self, T: int):
+        """(zeros, accumulator) fp32 [T, H].  Under graph capture they come from the graph's pool: a captured kernel keeps the raw
+        address, and the shared pair below is re-allocated when a longer batch arrives."""
         H = self.cfg.hidden
+        if self.device.type == "cuda" and torch.cuda.is_current_stream_capturing():
+            return torch.zeros(T, H, dtype=torch.float32, device=self.device), torch.empty(T, H, dtype=torch.float32, device=self.device)
         if self._zero is None or self._zero.shape[0] < T:
             n = max(T, 256)
             self._zero = torch.zeros(n, H, dtype=torch.float32, device=self.device)

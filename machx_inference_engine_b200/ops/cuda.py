@@ -331,12 +331,17 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
         ctas = B * n_kv * max(1, (max_q_len * (n_q // n_kv) + 31) // 32)
         max_kv_tiles = max(1, (block_table.shape[1] * bs) // 64)
         n_splits = max(1, min(max_kv_tiles, 32, (2 * 148) // max(ctas, 1)))
-    key = (q.device, n_splits * Tq * n_q * hd)
-    buf = _attn_scratch.get(q.device)
     need = n_splits * Tq * n_q * (hd + 2)
-    if buf is None or buf.numel() < need:
-        buf = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
-        _attn_scratch[q.device] = buf
+    if torch.cuda.is_current_stream_capturing():
+        # a captured kernel keeps the raw address: the scratch must live exactly as long as the graph, so it comes from the
+        # graph's own pool.  (The shared buffer below is re-allocated when a larger request arrives; a graph that had
+        # captured its old address would then write through a dangling pointer.)
+        buf = torch.empty(need, dtype=torch.float32, device=q.device)
+    else:
+        buf = _attn_scratch.get(q.device)
+        if buf is None or buf.numel() < need:
+            buf = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+            _attn_scratch[q.device] = buf
     o_part = buf[: n_splits * Tq * n_q * hd]
     ml_part = buf[n_splits * Tq * n_q * hd: need]
     out = torch.empty(Tq, n_q, hd, dtype=torch.bfloat16, device=q.device)

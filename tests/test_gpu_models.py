@@ -159,3 +159,26 @@ def test_gemma4_file_on_cuda_matches_cpu_path(tmp_path, name):
     assert outs["cpu"][0] == outs["gpu"][0], outs
     if not cfg.is_moe:
         assert sum(a == b for a, b in zip(outs["cpu"], outs["gpu"])) >= 5, outs
+
+
+def test_decode_graph_survives_growth_of_the_shared_attention_scratch():
+    """A decode graph is captured while the shared split-KV scratch is small; a long prompt of a head_dim-256 model (CUDA-core
+    prefill attention) then needs a larger scratch, which re-allocates the shared buffer, and the next graph capture empties the
+    allocator's cache.  The captured decode kernels must not depend on the old buffer: the graph owns its scratch."""
+    import dataclasses
+    cfg = dataclasses.replace(preset("tiny-llama"), head_dim=256, n_rot=256)
+    g = torch.Generator().manual_seed(7)
+    short = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    long = torch.randint(0, cfg.vocab, (2048,), generator=g).tolist()
+    outs = {}
+    for graphs in (False, True):
+        model = build_model(cfg, torch.device("cuda:0"), quant="q8_0", max_ctx=4096, gen_device="cpu")
+        eng = LLMEngine(model, EngineOptions(max_ctx=4096, max_batch_tokens=2048, max_seqs=2, cuda_graphs=graphs, enable_prefix_cache=False))
+        a = eng.generate([short], SamplingParams(max_tokens=6))[0]
+        b = eng.generate([long], SamplingParams(max_tokens=6))[0]
+        c = eng.generate([short], SamplingParams(max_tokens=6))[0]
+        outs[graphs] = (a, b, c)
+    from machx_inference_engine_b200.ops import cuda as K
+    K.check_status()
+    assert outs[True] == outs[False], outs
+    assert outs[True][0] == outs[True][2]
