@@ -67,7 +67,12 @@ struct SmemLayout {
   static constexpr int RAW_MAIN = kDequant ? RAW_THREADS * RawSlot<FMT>::MAIN : 0;     // per stage: main bytes, then aux bytes
   static constexpr int RAW_STAGE = kDequant ? RAW_THREADS * (RawSlot<FMT>::MAIN + RawSlot<FMT>::AUX) : 0;
   static constexpr int RAW_OFFSET = BAR_OFFSET + 512;
-  static constexpr int TOTAL = RAW_OFFSET + kRawDepth * RAW_STAGE + 1024;   // + alignment slack
+  // Epilogue staging for peer stores (TMA-fed weights only; the decode configuration has no room): per epilogue warp 32 rows of
+  // 128 bytes (+16 bytes of padding against bank conflicts), so that a store instruction covers four whole 128-byte row segments.
+  static constexpr int STG_ROW = 144;
+  static constexpr int STG_BYTES = kDequant ? 0 : 4 * 32 * STG_ROW;
+  static constexpr int STG_OFFSET = RAW_OFFSET + kRawDepth * RAW_STAGE;
+  static constexpr int TOTAL = STG_OFFSET + STG_BYTES + 1024;   // + alignment slack
   static_assert(TOTAL <= 232448, "shared memory plan exceeds 227 KB");
 };
 
@@ -232,6 +237,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r);
         tmem_ld_wait();
         const int col0 = nt * BN + c0;
+        if constexpr (!kDequant && BN >= 64) {
+          // Fused all-reduce, TMA-fed weights: a thread owns one row, so direct stores put 32 different rows (16 bytes each) into
+          // one instruction, which NVLink carries as 32 small packets.  The rows go through shared memory instead and leave as
+          // 128-byte segments, four rows per instruction.
+          if (p.peer.world && p.act == ACT_NONE && (p.N & 7) == 0 && (p.ldc & 7) == 0) {
+            const int eb = p.out_f32 == 1 ? 4 : 2;                 // bytes per element of the inbox slot
+            const int cpf = 128 / eb;                              // columns per 128-byte segment: 32 (fp32) or 64 (bf16 / fp16)
+            uint8_t* stg = smem + L::STG_OFFSET + q * (32 * L::STG_ROW);
+            uint8_t* mine = stg + lane * L::STG_ROW + (c0 % cpf) * eb;
+            const bool live = row_ok && col0 < p.N;
+            if (eb == 4) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live) {
+                  o4.x = (__uint_as_float(r[j]) + (bias && col0 + j < p.N ? bias[col0 + j] : 0.f)) * rs;
+                  o4.y = (__uint_as_float(r[j + 1]) + (bias && col0 + j + 1 < p.N ? bias[col0 + j + 1] : 0.f)) * rs;
+                  o4.z = (__uint_as_float(r[j + 2]) + (bias && col0 + j + 2 < p.N ? bias[col0 + j + 2] : 0.f)) * rs;
+                  o4.w = (__uint_as_float(r[j + 3]) + (bias && col0 + j + 3 < p.N ? bias[col0 + j + 3] : 0.f)) * rs;
+                }
+                *reinterpret_cast<float4*>(mine + j * 4) = o4;
+              }
+            } else {
+              const bool h = p.out_f32 == 2;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float t[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t[i] = live ? (__uint_as_float(r[j + i]) + (bias && col0 + j + i < p.N ? bias[col0 + j + i] : 0.f)) * rs : 0.f;
+                *reinterpret_cast<uint4*>(mine + j * 2) = h ? make_uint4(pack_f16(t[0], t[1]), pack_f16(t[2], t[3]), pack_f16(t[4], t[5]), pack_f16(t[6], t[7]))
+                                                            : make_uint4(pack_bf16(t[0], t[1]), pack_bf16(t[2], t[3]), pack_bf16(t[4], t[5]), pack_bf16(t[6], t[7]));
+              }
+            }
+            if ((c0 + 32) % cpf == 0 || c0 + 32 >= BN) {
+              __syncwarp();
+              const int seg_col0 = nt * BN + (c0 / cpf) * cpf;     // first column of the staged segment
+              const int piece = lane & 7;                           // 16-byte piece of the 128-byte segment
+              const int pcol = seg_col0 + piece * (16 / eb);
+              const int n_dst = peer_count(p.peer);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int rl = 4 * j + (lane >> 3);
+                const int grow = mt * BM + q * 32 + rl;
+                if (grow < p.M && pcol < p.N) {
+                  const uint4 val = *reinterpret_cast<const uint4*>(stg + rl * L::STG_ROW + piece * 16);
+                  const int dst0 = peer_first(p.peer, grow);
+                  for (int dst = dst0; dst < dst0 + n_dst; ++dst)
+                    *reinterpret_cast<uint4*>(peer_slot(p.peer, dst, next_seq) + ((size_t)grow * p.ldc + pcol) * eb) = val;
+                }
+              }
+              __syncwarp();
+            }
+            continue;
+          }
+        }
         if (!row_ok || col0 >= p.N) continue;
         float v[32];
 #pragma unroll
