@@ -195,20 +195,49 @@ __global__ void moe_combine_push_kernel(const __nv_bfloat16* __restrict__ yp, co
   pdl_prologue();
   const int t = blockIdx.x;
   const int next_seq = *po.seq + 1;
-  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
-    float a0 = 0.f, a1 = 0.f;
-    for (int k = 0; k < K; ++k) {
-      const int pos = pair_to_packed[(size_t)t * K + k];
-      if (pos < 0) continue;
-      const uint32_t v = *reinterpret_cast<const uint32_t*>(yp + (size_t)pos * H + i);
-      const float ww = w[(size_t)t * K + k];
-      a0 = fmaf(ww, bf16_lo(v), a0);
-      a1 = fmaf(ww, bf16_hi(v), a1);
+  const int d0 = peer_first(po, t), nd = peer_count(po);
+  if ((H & 7) == 0) {
+    // eight columns per thread: a warp's store instruction covers 512 (bf16) or 1024 (fp32) contiguous bytes of the peer's row
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = 0.f;
+      for (int k = 0; k < K; ++k) {
+        const int pos = pair_to_packed[(size_t)t * K + k];
+        if (pos < 0) continue;
+        const uint4 v = *reinterpret_cast<const uint4*>(yp + (size_t)pos * H + i);
+        const float ww = w[(size_t)t * K + k];
+        a[0] = fmaf(ww, bf16_lo(v.x), a[0]); a[1] = fmaf(ww, bf16_hi(v.x), a[1]);
+        a[2] = fmaf(ww, bf16_lo(v.y), a[2]); a[3] = fmaf(ww, bf16_hi(v.y), a[3]);
+        a[4] = fmaf(ww, bf16_lo(v.z), a[4]); a[5] = fmaf(ww, bf16_hi(v.z), a[5]);
+        a[6] = fmaf(ww, bf16_lo(v.w), a[6]); a[7] = fmaf(ww, bf16_hi(v.w), a[7]);
+      }
+      for (int d = d0; d < d0 + nd; ++d) {
+        if constexpr (sizeof(OT) == 4) {
+          float* o = reinterpret_cast<float*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i;
+          *reinterpret_cast<float4*>(o) = make_float4(a[0], a[1], a[2], a[3]);
+          *reinterpret_cast<float4*>(o + 4) = make_float4(a[4], a[5], a[6], a[7]);
+        } else {
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) =
+              make_uint4(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]), pack_bf16(a[4], a[5]), pack_bf16(a[6], a[7]));
+        }
+      }
     }
-    const int d0 = peer_first(po, t);
-    for (int d = d0; d < d0 + peer_count(po); ++d) {
-      if constexpr (sizeof(OT) == 4) *reinterpret_cast<float2*>(reinterpret_cast<float*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) = make_float2(a0, a1);
-      else *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) = pack_bf16(a0, a1);
+  } else {
+    for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+      float a0 = 0.f, a1 = 0.f;
+      for (int k = 0; k < K; ++k) {
+        const int pos = pair_to_packed[(size_t)t * K + k];
+        if (pos < 0) continue;
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(yp + (size_t)pos * H + i);
+        const float ww = w[(size_t)t * K + k];
+        a0 = fmaf(ww, bf16_lo(v), a0);
+        a1 = fmaf(ww, bf16_hi(v), a1);
+      }
+      for (int d = d0; d < d0 + nd; ++d) {
+        if constexpr (sizeof(OT) == 4) *reinterpret_cast<float2*>(reinterpret_cast<float*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) = make_float2(a0, a1);
+        else *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(peer_slot(po, d, next_seq)) + (size_t)t * H + i) = pack_bf16(a0, a1);
+      }
     }
   }
   peer_publish(po, next_seq);
