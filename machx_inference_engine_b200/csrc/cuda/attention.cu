@@ -160,43 +160,70 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_partial_kernel(const Attn
         }
       }
       __syncthreads();
+      // Scores of the warp's PPW pairs against the tile's 64 keys (a lane owns keys lane and lane + 32).  One pass over the key
+      // row serves all pairs: a key element is read from shared memory once and multiplied into PPW dot products.
+      if (round0 + warp * PPW >= total_pairs) continue;          // this warp has no live pair (barriers sit at the loop top)
+      float p0[PPW], p1[PPW];
+      {
+        float sc[PPW][2];
+        {
+          // both keys of the lane in one pass: a query element read from shared memory feeds two dot products
+          const uint32_t* kr0 = reinterpret_cast<const uint32_t*>(sk + lane * KSTR);
+          const uint32_t* kr1 = reinterpret_cast<const uint32_t*>(sk + (lane + 32) * KSTR);
+          const float* qv = sq + warp * PPW * HD;
+          float d0[PPW], d1[PPW];
 #pragma unroll
-      for (int pi = 0; pi < PPW; ++pi) {
-        const int pl = warp * PPW + pi, pr = round0 + pl;
-        if (pr >= total_pairs) continue;
-        const int qpos = pos0 + pr / gqa;
-        const float* qv = sq + pl * HD;
-        float s[2];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int j = lane + 32 * half, kpos = key0 + j;
-          const uint32_t* kr = reinterpret_cast<const uint32_t*>(sk + j * KSTR);
-          float d = 0.f;
+          for (int pi = 0; pi < PPW; ++pi) d0[pi] = d1[pi] = 0.f;
 #pragma unroll 8
           for (int c = 0; c < HD / 2; ++c) {
-            const uint32_t kk = kr[c];
-            const float2 qq = *reinterpret_cast<const float2*>(qv + 2 * c);
-            d = fmaf(qq.x, bf16_lo(kk), d);
-            d = fmaf(qq.y, bf16_hi(kk), d);
+            const uint32_t ka = kr0[c], kb = kr1[c];
+            const float a0 = bf16_lo(ka), a1 = bf16_hi(ka), b0 = bf16_lo(kb), b1 = bf16_hi(kb);
+#pragma unroll
+            for (int pi = 0; pi < PPW; ++pi) {
+              const float2 qq = *reinterpret_cast<const float2*>(qv + pi * HD + 2 * c);
+              d0[pi] = fmaf(qq.x, a0, d0[pi]); d0[pi] = fmaf(qq.y, a1, d0[pi]);
+              d1[pi] = fmaf(qq.x, b0, d1[pi]); d1[pi] = fmaf(qq.y, b1, d1[pi]);
+            }
           }
-          if (p.softcap > 0.f) d = p.softcap * tanhf(d / p.softcap);
-          const bool ok = kpos < seq_len && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
-          s[half] = ok ? d : -INFINITY;
+#pragma unroll
+          for (int pi = 0; pi < PPW; ++pi) {
+            const int pr = round0 + warp * PPW + pi;
+            const int qpos = pos0 + pr / gqa;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const int kpos = key0 + lane + 32 * half;
+              float dd = half ? d1[pi] : d0[pi];
+              if (p.softcap > 0.f) dd = p.softcap * tanhf(dd / p.softcap);
+              const bool ok = pr < total_pairs && kpos < seq_len && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+              sc[pi][half] = ok ? dd : -INFINITY;
+            }
+          }
         }
-        const float tmax = warp_max(fmaxf(s[0], s[1]));
-        const float m_new = fmaxf(m[pi], tmax);
-        const float corr = __expf(m[pi] - m_new);
-        const float p0 = __expf(s[0] - m_new), p1 = __expf(s[1] - m_new);
-        l[pi] = l[pi] * corr + warp_sum(p0 + p1);
-        m[pi] = m_new;
 #pragma unroll
-        for (int j = 0; j < HD / 32; ++j) acc[pi][j] *= corr;
-#pragma unroll 4
-        for (int j = 0; j < ATT_TILE; ++j) {
-          const float pj = __shfl_sync(0xffffffffu, j < 32 ? p0 : p1, j & 31);
-          const __nv_bfloat16* vr = sv + j * HD;
+        for (int pi = 0; pi < PPW; ++pi) {
+          const float tmax = warp_max(fmaxf(sc[pi][0], sc[pi][1]));
+          const float m_new = fmaxf(m[pi], tmax);
+          const float corr = __expf(m[pi] - m_new);
+          p0[pi] = __expf(sc[pi][0] - m_new);
+          p1[pi] = __expf(sc[pi][1] - m_new);
+          l[pi] = l[pi] * corr + warp_sum(p0[pi] + p1[pi]);
+          m[pi] = m_new;
 #pragma unroll
-          for (int c = 0; c < HD / 32; ++c) acc[pi][c] = fmaf(pj, __bfloat162float(vr[lane + 32 * c]), acc[pi][c]);
+          for (int c = 0; c < HD / 32; ++c) acc[pi][c] *= corr;
+        }
+      }
+      // P V: a value element is read once per key and feeds all PPW pairs
+#pragma unroll 2
+      for (int j = 0; j < ATT_TILE; ++j) {
+        const __nv_bfloat16* vr = sv + j * HD;
+        float vv[HD / 32];
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) vv[c] = __bfloat162float(vr[lane + 32 * c]);
+#pragma unroll
+        for (int pi = 0; pi < PPW; ++pi) {
+          const float pj = __shfl_sync(0xffffffffu, j < 32 ? p0[pi] : p1[pi], j & 31);
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) acc[pi][c] = fmaf(pj, vv[c], acc[pi][c]);
         }
       }
     }
