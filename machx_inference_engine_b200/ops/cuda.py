@@ -202,6 +202,9 @@ def _gemm_a(x, w: QuantWeight):
     return x if x.dtype == want else x.to(want)
 
 
+DEQUANT_ONCE_MIN_M = 1024      # dense quantised GEMMs with at least this many rows decode the weight once to bf16 first
+
+
 def _out_kind(dtype) -> int:
     return {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}[dtype]
 
@@ -220,6 +223,13 @@ def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limi
                            C.c_float(act_limit), _vp(0), _vp(0), M, 1, _stream()), "gemv")
     else:
         xa = _gemm_a(x, w)
+        if M >= DEQUANT_ONCE_MIN_M and fmt != int(WFormat.BF16):
+            # long chunk, quantised dense weight: decode it once to bf16 and multiply with the TMA-fed kernel (the in-kernel decode
+            # repeats per 128-row activation tile).  The scratch matrix is an ordinary allocation: stream-ordered, graph-safe.
+            wb = torch.empty(w.N, w.K, dtype=torch.bfloat16, device=x.device)
+            _check(lib.mx_dequant_bf16(fmt, p0, p1, p2, p3, C.c_longlong(w.N), w.K, _p(wb), _stream()), "dequant_bf16")
+            _count()
+            fmt, p0, p1, p2, p3 = int(WFormat.BF16), _p(wb), _vp(0), _vp(0), _vp(0)
         _check(lib.mx_gemm(_p(xa), fmt, p0, p1, p2, p3, 1, _p(out), n_out, int(out_f32), _p(bias), _p(row_scale), act,
                            C.c_float(act_alpha), C.c_float(act_limit), M, w.N, w.K, _vp(0), _vp(0), _pick_bn(M, w.N), _stream()), "gemm")
     _count()

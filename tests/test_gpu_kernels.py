@@ -110,6 +110,25 @@ def test_gemm_tcgen05(fmt, shape):
         assert rel_err(got, want) < 6e-3, (bn, rel_err(got, want))
 
 
+@pytest.mark.parametrize("fmt", [WFormat.Q8, WFormat.Q4K, WFormat.Q6K, WFormat.MXFP4])
+def test_linear_long_chunk_decodes_the_weight_once(fmt):
+    """At 1024 rows and more `linear` decodes a quantised dense weight to bf16 once and runs the TMA-fed kernel: the same values as
+    the in-kernel decode (both multiply bf16 weights), with and without a gated epilogue."""
+    M, N, Kd = 1100, 640, 1024
+    assert M >= K().DEQUANT_ONCE_MIN_M
+    qw = make_weight(fmt, N, Kd)
+    x = (torch.randn(M, Kd, device=dev()) * 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device=dev())
+    got = K().linear(x, qw, bias=bias, out_f32=True)
+    K().check_status()
+    assert rel_err(got, ref.linear(x, qw, bias=bias, out_f32=True)) < 6e-3
+    assert rel_err(got, K().gemm(x, qw, bias=bias, out_f32=True)) < 1e-3
+    got = K().linear(x, qw, act=ref.ACT_SWIGLU)
+    assert rel_err(got, K().gemm(x, qw, act=ref.ACT_SWIGLU)) < 2e-3
+    # below the threshold nothing changes: same kernel as `gemm`
+    assert torch.equal(K().linear(x[:512], qw, bias=bias, out_f32=True), K().gemm(x[:512].contiguous(), qw, bias=bias, out_f32=True))
+
+
 def test_gemm_ragged_k_and_bf16_out():
     M, N, Kd = 130, 72, 2880      # K = 45 * 64, N not a multiple of 32
     qw = make_weight(WFormat.MXFP4, N, Kd)
