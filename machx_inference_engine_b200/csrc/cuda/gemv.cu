@@ -377,7 +377,7 @@ static int launch_gemv(const GemvParams& p, int slots, cudaStream_t st) {
 
 }  // namespace mx
 
-// Whole-matrix decode to bf16 (one thread per 32-element block).  Long prefill chunks of a quantised dense layer decode the weight
+// Whole-matrix decode to bf16 (one thread per 32-element block).  Prefill chunks of a quantised dense layer decode the weight
 // once into a scratch matrix and run the TMA-fed bf16 GEMM on it: the in-kernel decode of the tensor-core GEMM repeats for every
 // 128-row tile of activations and bounds it near 460 TFLOP/s, the bf16 kernel runs at about 1100.
 namespace mx {

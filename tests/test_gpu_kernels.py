@@ -112,7 +112,7 @@ def test_gemm_tcgen05(fmt, shape):
 
 @pytest.mark.parametrize("fmt", [WFormat.Q8, WFormat.Q4K, WFormat.Q6K, WFormat.MXFP4])
 def test_linear_long_chunk_decodes_the_weight_once(fmt):
-    """At 1024 rows and more `linear` decodes a quantised dense weight to bf16 once and runs the TMA-fed kernel: the same values as
+    """From DEQUANT_ONCE_MIN_M rows on `linear` decodes a quantised dense weight to bf16 once and runs the TMA-fed kernel: the same values as
     the in-kernel decode (both multiply bf16 weights), with and without a gated epilogue."""
     M, N, Kd = 1100, 640, 1024
     assert M >= K().DEQUANT_ONCE_MIN_M
@@ -126,7 +126,8 @@ def test_linear_long_chunk_decodes_the_weight_once(fmt):
     got = K().linear(x, qw, act=ref.ACT_SWIGLU)
     assert rel_err(got, K().gemm(x, qw, act=ref.ACT_SWIGLU)) < 2e-3
     # below the threshold nothing changes: same kernel as `gemm`
-    assert torch.equal(K().linear(x[:512], qw, bias=bias, out_f32=True), K().gemm(x[:512].contiguous(), qw, bias=bias, out_f32=True))
+    n = K().DEQUANT_ONCE_MIN_M - 16
+    assert n > 8 and torch.equal(K().linear(x[:n].contiguous(), qw, bias=bias, out_f32=True), K().gemm(x[:n].contiguous(), qw, bias=bias, out_f32=True))
 
 
 def test_gemm_ragged_k_and_bf16_out():
