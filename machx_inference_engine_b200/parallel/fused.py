@@ -127,6 +127,13 @@ class FusedComm:
             if M * w.N * 2 > self.slot_bytes:
                 raise ValueError(f"fused all-reduce slot too small for [{M},{w.N}]")
             rs = self._rs_rows(M)
+            if fmt != int(K.WFormat.BF16) and M >= K.DEQUANT_ONCE_MIN_M:
+                # quantised row-parallel weight: decode it once to bf16 (see ops.cuda.linear); the TMA-fed kernel is also the one
+                # whose epilogue stages its peer stores into 128-byte row segments
+                wb = torch.empty(w.N, w.K, dtype=torch.bfloat16, device=x.device)
+                K._check(lib.mx_dequant_bf16(fmt, p0, p1, p2, p3, C.c_longlong(w.N), w.K, K._p(wb), st), "dequant_bf16")
+                K._count()
+                fmt, p0, p1, p2, p3 = int(K.WFormat.BF16), K._p(wb), _vp(0), _vp(0), _vp(0)
             K._check(lib.mx_gemm_allreduce(K._p(x), fmt, p0, p1, p2, p3, _vp(0), 0, M, w.N, w.K, K._pick_bn(M, w.N), self._ptr_array, self.world,
                                            self.rank, C.c_longlong(self.slot_bytes), K._p(self.seq), K._p(self.ticket), rs, st), "gemm_allreduce")
             K._count()
