@@ -177,6 +177,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--graph-reps", type=int, default=0, help="time N back-to-back calls inside one CUDA graph (per-call time without launch gaps)")
     ap.add_argument("--gemv-path", default="auto", choices=["auto", "register", "stream"], help="which decode GEMV kernel to time")
+    ap.add_argument("--decode-once", action="store_true", help="gemm: time ops.linear (weight decoded once to bf16 + TMA-fed kernel)")
     ap.add_argument("--layers", type=int, default=1, help="distinct weight copies cycled through so that weights are never L2-resident")
     a = ap.parse_args(argv)
     if a.kernel == "allreduce":
@@ -202,10 +203,13 @@ def main(argv=None):
         i = [0]
 
         def fn():
-            K.gemm(x, ws[i[0] % a.layers], bn=a.bn or None)
+            if a.decode_once:         # the model's `linear`: quantised weight decoded once to bf16, then the TMA-fed kernel
+                K.linear(x, ws[i[0] % a.layers])
+            else:                     # the tcgen05 kernel with in-kernel weight decode
+                K.gemm(x, ws[i[0] % a.layers], bn=a.bn or None)
             i[0] += 1
         med, mn = timeit(fn, a.iters)
-        report(f"gemm[{a.fmt}] {a.m}x{a.n}x{a.k}", med, mn, flops=2.0 * a.m * a.n * a.k, bytes_=ws[0].nbytes + x.numel() * 2 + a.m * a.n * 2)
+        report(f"gemm[{a.fmt}{', decode-once' if a.decode_once else ''}] {a.m}x{a.n}x{a.k}", med, mn, flops=2.0 * a.m * a.n * a.k, bytes_=ws[0].nbytes + x.numel() * 2 + a.m * a.n * 2)
     elif a.kernel == "moe_gemm":
         T, E, H, F, k = a.tokens, a.experts, a.hidden, a.ffn, a.topk
         gu = weight(2 * F, H, E)
