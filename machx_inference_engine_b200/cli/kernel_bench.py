@@ -186,7 +186,7 @@ def main(argv=None):
     K.set_gemv_path(a.gemv_path)
     global GRAPH_REPS
     GRAPH_REPS = a.graph_reps
-    fmt = {"bf16": WFormat.BF16, "q8": WFormat.Q8, "q4k": WFormat.Q4K, "q6k": WFormat.Q6K, "mxfp4": WFormat.MXFP4}[a.fmt]
+    fmt = {"bf16": WFormat.BF16, "q8": WFormat.Q8, "q4k": WFormat.Q4K, "q6k": WFormat.Q6K, "mxfp4": WFormat.MXFP4, "mxf4t": WFormat.MXFP4}[a.fmt]
     torch.manual_seed(0)
 
     def weight(N, Kd, E=1):
@@ -210,6 +210,55 @@ def main(argv=None):
             i[0] += 1
         med, mn = timeit(fn, a.iters)
         report(f"gemm[{a.fmt}{', decode-once' if a.decode_once else ''}] {a.m}x{a.n}x{a.k}", med, mn, flops=2.0 * a.m * a.n * a.k, bytes_=ws[0].nbytes + x.numel() * 2 + a.m * a.n * 2)
+    elif a.kernel == "moe_gemm" and a.fmt == "mxf4t":
+        # the block-scaled tensor-core kernel: MXFP4 tiles x MXFP8 activations (a.layers distinct banks keep the weights out of L2)
+        from ..ops.weights import to_mxf4_tiles
+        T, E, H, F, k = a.tokens, a.experts, a.hidden, a.ffn, a.topk
+        banks = [tuple(to_mxf4_tiles(weight(n, kd, E)) for n, kd in ((F, H), (F, H), (H, F))) for _ in range(a.layers)]
+        x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+        idx, w = K.moe_route(torch.randn(T, E, device=dev), None, k)
+        pair = T <= 8
+        i = [0]
+        if pair:
+            n = T * k
+            te = idx.reshape(-1)
+            xq, sfb = K.moe_quant(x, n, n, 1, x_div=k)
+            kw = dict(default_valid=1)
+            args = (te, n, 1)
+        else:
+            pk = K.moe_pack(idx, E)
+            mt = pk.tile_expert.numel()
+            xq, sfb = K.moe_quant(x, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
+            kw = dict(tile_valid=pk.tile_valid, num_tiles=pk.num_tiles)
+            args = (pk.tile_expert, mt, 128)
+        hmid = K.mxf4_gemm(banks[0][0], banks[0][1], xq, sfb, *args, act=ref.ACT_SWIGLU_OAI, **kw)
+        if pair:
+            aq, sfa = K.moe_quant(hmid, n, n, 1)
+        else:
+            aq, sfa = K.moe_quant(hmid, pk.max_rows, mt, 128, src_index=pk.packed_token, identity=True, row_limit=pk.num_tiles)
+
+        def f_gu():
+            g, u, _ = banks[i[0] % a.layers]
+            K.mxf4_gemm(g, u, xq, sfb, *args, act=ref.ACT_SWIGLU_OAI, **kw)
+            i[0] += 1
+
+        def f_dn():
+            d = banks[i[0] % a.layers][2]
+            K.mxf4_gemm(d, None, aq, sfa, *args, **kw)
+            i[0] += 1
+        wb = banks[0][0].nbytes
+        med, mn = timeit(f_gu, a.iters)
+        report(f"moe gate+up[mxf4 block-scaled] T={T} E={E} top{k} 2x{F}x{H}", med, mn, flops=2.0 * T * k * 2 * F * H,
+               bytes_=2 * wb * (min(E, T * k) / E if pair else 1.0))
+        med, mn = timeit(f_dn, a.iters)
+        report(f"moe down[mxf4 block-scaled] T={T} E={E} top{k} {H}x{F}", med, mn, flops=2.0 * T * k * F * H,
+               bytes_=banks[0][2].nbytes * (min(E, T * k) / E if pair else 1.0))
+        if pair:
+            med, mn = timeit(lambda: K.moe_quant(x, n, n, 1, x_div=k), a.iters)
+        else:
+            med, mn = timeit(lambda: K.moe_quant(x, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles), a.iters)
+        report(f"moe activation quantiser T={T} top{k} H={H}", med, mn, bytes_=T * k * H * 3.0)
+        K.check_status()
     elif a.kernel == "moe_gemm":
         T, E, H, F, k = a.tokens, a.experts, a.hidden, a.ffn, a.topk
         gu = weight(2 * F, H, E)

@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 
 // Single-CTA packer.  n = T*K pairs.  Outputs:
 //   counts[E], seg_start[E+1] (padded starts, multiples of 128), packed_token[P] (-1 = pad),
-//   pair_to_packed[n], tile_expert[max_tiles], num_tiles[1], packed_rows[1]
+//   pair_to_packed[n], tile_expert[max_tiles], tile_valid[max_tiles] (optional: live rows per tile), num_tiles[1], packed_rows[1]
 // e_lo/e_hi restrict packing to the experts owned by this rank (expert parallelism): pairs routed
 // elsewhere get pair_to_packed = -1.
 // Stable counting sort in three passes: every warp owns a contiguous chunk of the pair list and histograms it
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ topk_idx, int n, int K, int E, int e_lo, int e_hi,
                                                         int* __restrict__ counts, int* __restrict__ seg_start, int* __restrict__ packed_token,
                                                         int* __restrict__ pair_to_packed, int* __restrict__ tile_expert, int* __restrict__ num_tiles,
-                                                        int max_rows, int tile) {
+                                                        int max_rows, int tile, int* __restrict__ tile_valid) {
   pdl_prologue();
   extern __shared__ int s_hist[];            // [nwarps][E]
   __shared__ int s_cnt[1024];
@@ -106,7 +106,10 @@ __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ 
       s_start[e] = off;
       // tile = 128: segments padded to whole GEMM tiles and a tile -> expert map; tile = 1: compact segments (GEMV path)
       const int padded = (s_cnt[e] + tile - 1) / tile * tile;
-      if (tile > 1) for (int tix = 0; tix < padded / tile; ++tix) tile_expert[tiles++] = e;
+      if (tile > 1) for (int tix = 0; tix < padded / tile; ++tix) {
+        if (tile_valid) tile_valid[tiles] = min(tile, s_cnt[e] - tix * tile);      // live rows of this tile
+        tile_expert[tiles++] = e;
+      }
       off += padded;
     }
     s_start[E] = off;
@@ -272,13 +275,14 @@ MX_HOST_API int mx_moe_route(const float* logits, const float* bias, int T, int 
 
 // num_tiles must hold 2 ints: [0] live 128-row tiles, [1] packed row count.
 MX_HOST_API int mx_moe_pack(const int* topk_idx, int n_pairs, int K, int E, int e_lo, int e_hi, int* counts, int* seg_start,
-                            int* packed_token, int* pair_to_packed, int* tile_expert, int* num_tiles, int max_rows, int tile, cudaStream_t st) {
+                            int* packed_token, int* pair_to_packed, int* tile_expert, int* num_tiles, int max_rows, int tile, int* tile_valid,
+                            cudaStream_t st) {
   if (E > 1024 || (tile != 1 && tile != MOE_TILE)) return -120;
   const int pack_smem = 32 * E * (int)sizeof(int);
   static bool pack_attr = false;
   if (!pack_attr) { cudaFuncSetAttribute(moe_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * (int)sizeof(int)); pack_attr = true; }
   launch_pdl(moe_pack_kernel, dim3(1), dim3(1024), pack_smem, st, topk_idx, n_pairs, K, E, e_lo, e_hi, counts, seg_start, packed_token, pair_to_packed, tile_expert,
-                                      num_tiles, max_rows, tile);
+                                      num_tiles, max_rows, tile, tile_valid);
   return (int)cudaGetLastError();
 }
 

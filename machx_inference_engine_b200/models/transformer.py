@@ -294,6 +294,9 @@ class MoEFFN:
     the pairs routed to its own experts and contributes a partial sum that the caller reduces.
     """
 
+    MXF4_TENSOR_CORE = True      # class switch (tests compare against the bf16-activation path by turning it off)
+    MXF4_PAIR_MAX_TOKENS = 8     # up to this many tokens every (token, expert) pair is its own tile: no packing pass
+
     def __init__(self, cfg: ModelConfig, layer: int, src, par: ParallelCtx, act: int, with_bias: bool, prefix: Optional[str] = None):
         c = cfg
         p = prefix or f"blk.{layer}"
@@ -314,16 +317,30 @@ class MoEFFN:
         else:
             g = src.matrix(f"{p}.ffn_gate_exps.weight", F, H, E, experts=rng)
             u = src.matrix(f"{p}.ffn_up_exps.weight", F, H, E, experts=rng)
-        self.gate_up = QuantWeight.interleave_gate_up(g, u)
-        del g, u
+        d = src.matrix(f"{p}.ffn_down_exps.weight", H, F, E, experts=rng)
+        # MXFP4 banks on a GPU run on the block-scaled tensor-core kernel: gate / up / down stay three banks in its tiled layout
+        self.mx = None
+        # all-MXFP4 expert banks multiply MXFP8 activations (e4m3 + a power-of-two scale per 32): the arithmetic of the block-scaled
+        # tensor-core kernel, and the arithmetic the CPU path restates so that both produce the same numbers
+        self.a8 = g.fmt == u.fmt == d.fmt == ops.WFormat.MXFP4 and act in (ACT_SWIGLU, ACT_SWIGLU_OAI) and self.MXF4_TENSOR_CORE
+        if g.p0.is_cuda and self.a8:
+            from ..ops.weights import to_mxf4_tiles
+            self.mx = (to_mxf4_tiles(g), to_mxf4_tiles(u), to_mxf4_tiles(d))
+            self.gate_up = self.down = None
+        else:
+            self.gate_up = QuantWeight.interleave_gate_up(g, u)
+            self.down = d
+        del g, u, d
         self.expert_scale = None         # optional per-expert factor on the down projection's output, folded into the routing weight
-        self.down = src.matrix(f"{p}.ffn_down_exps.weight", H, F, E, experts=rng)
-        self.gu_bias = self.down_bias = None
+        self.gu_bias = self.down_bias = self.g_bias = self.u_bias = None
         if with_bias:
             gb = src.table(f"{p}.ffn_gate_exps.bias", (E, F))[self.e_lo:self.e_hi]
             ub = src.table(f"{p}.ffn_up_exps.bias", (E, F))[self.e_lo:self.e_hi]
             n = self.e_hi - self.e_lo
-            self.gu_bias = torch.cat([gb.reshape(n, F // 16, 16), ub.reshape(n, F // 16, 16)], dim=2).reshape(n, 2 * F).contiguous()
+            if self.mx is not None:
+                self.g_bias, self.u_bias = gb.contiguous(), ub.contiguous()
+            else:
+                self.gu_bias = torch.cat([gb.reshape(n, F // 16, 16), ub.reshape(n, F // 16, 16)], dim=2).reshape(n, 2 * F).contiguous()
             self.down_bias = src.table(f"{p}.ffn_down_exps.bias", (E, H))[self.e_lo:self.e_hi].contiguous()
         self.act = act
         self.reduce = ep > 1
@@ -342,7 +359,20 @@ class MoEFFN:
         local = self.e_hi - self.e_lo
         # expert parallelism on the peer-memory path: the combine writes its partial into every rank's inbox itself
         fuse_push = self.reduce and par.fused is not None and h.is_cuda and self.shared is None
-        if T <= 8:
+        if self.mx is not None:
+            y, p2p = self._mx_experts(h, idx)
+            if fuse_push:
+                return par.fused.moe_combine_push(y, p2p, w)
+            out = ops.moe_combine(y, ops.ref.MoePacking(None, None, None, p2p, None, None, y.shape[0], self.K), w)
+        elif self.a8:
+            # CPU restatement of the block-scaled path: same rounding points, fp32 math
+            q8 = lambda t: ops.ref.mxfp8_roundtrip(t).to(torch.bfloat16)
+            slot_e = idx.reshape(-1)
+            a = ops.expert_gemv(q8(h), self.gate_up, slot_e, x_div=self.K, bias=self.gu_bias, act=self.act, e_lo=self.e_lo)
+            y = ops.expert_gemv(q8(a), self.down, slot_e, x_div=1, bias=self.down_bias, e_lo=self.e_lo)
+            pk = ops.ref.MoePacking(None, None, None, torch.arange(T * self.K, dtype=torch.int32, device=h.device), None, None, T * self.K, self.K)
+            out = ops.moe_combine(y, pk, w)
+        elif T <= 8:
             # decode: one GEMV slot per (token, expert) pair, weights streamed once per pair; under expert
             # parallelism the slots of experts that live on other ranks contribute zero rows here
             slot_e = idx.reshape(-1)
@@ -380,6 +410,37 @@ class MoEFFN:
         if self.reduce:
             out = par.fused.push(out) if (par.fused is not None and out.is_cuda) else par.all_reduce(out)
         return out
+
+
+def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor):
+    """Expert projections on the block-scaled MXFP4 kernel.  Returns (y bf16 [rows, H], pair_to_packed int32 [T*K])."""
+    from ..ops import cuda as K_
+    gate, up, down = self.mx
+    T = h.shape[0]
+    ep = dict(e_lo=self.e_lo)
+    if T <= self.MXF4_PAIR_MAX_TOKENS:
+        # decode: pair i = (token i // K, slot i % K) is tile i with one live row; no sort, no gather
+        n = T * self.K
+        te = idx.reshape(-1)
+        xq, sfb = K_.moe_quant(h, n, n, 1, x_div=self.K)
+        a = K_.mxf4_gemm(gate, up, xq, sfb, te, n, 1, default_valid=1, bias0=self.g_bias, bias1=self.u_bias, act=self.act, **ep)
+        aq, sfa = K_.moe_quant(a, n, n, 1)
+        y = K_.mxf4_gemm(down, None, aq, sfa, te, n, 1, default_valid=1, bias0=self.down_bias, zero_out=self.reduce, **ep)
+        key = (T, h.device)
+        if key not in self._arange:
+            self._arange[key] = torch.arange(n, dtype=torch.int32, device=h.device)
+        return y, self._arange[key]
+    pk = ops.moe_pack(idx, self.E, self.e_lo, self.e_hi)
+    mt = pk.tile_expert.numel()
+    xq, sfb = K_.moe_quant(h, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
+    a = K_.mxf4_gemm(gate, up, xq, sfb, pk.tile_expert, mt, 128, tile_valid=pk.tile_valid, num_tiles=pk.num_tiles, bias0=self.g_bias,
+                     bias1=self.u_bias, act=self.act, **ep)
+    aq, sfa = K_.moe_quant(a, pk.max_rows, mt, 128, src_index=pk.packed_token, identity=True, row_limit=pk.num_tiles)
+    y = K_.mxf4_gemm(down, None, aq, sfa, pk.tile_expert, mt, 128, tile_valid=pk.tile_valid, num_tiles=pk.num_tiles, bias0=self.down_bias, **ep)
+    return y, pk.pair_to_packed
+
+
+MoEFFN._mx_experts = _mx_experts
 
 
 def _as_bf16(w: QuantWeight) -> dict:

@@ -394,11 +394,42 @@ def moe_pack(topk_idx, E, e_lo=0, e_hi=None, tile=MOE_TILE):
     packed_token = torch.empty(max_rows, dtype=torch.int32, device=dev)
     pair_to_packed = torch.empty(n, dtype=torch.int32, device=dev)
     tile_expert = torch.zeros(max(max_rows // MOE_TILE, 1), dtype=torch.int32, device=dev)
+    tile_valid = torch.zeros(max(max_rows // MOE_TILE, 1), dtype=torch.int32, device=dev) if tile > 1 else None
     num_tiles = torch.empty(2, dtype=torch.int32, device=dev)
     _check(_lib.cuda().mx_moe_pack(_p(topk_idx), n, K, E, e_lo, e_hi, _p(counts), _p(seg), _p(packed_token), _p(pair_to_packed),
-                                   _p(tile_expert), _p(num_tiles), max_rows, int(tile), _stream()), "moe_pack")
+                                   _p(tile_expert), _p(num_tiles), max_rows, int(tile), _p(tile_valid), _stream()), "moe_pack")
     _count()
-    return MoePacking(counts, seg, packed_token, pair_to_packed, tile_expert, num_tiles, max_rows, K)
+    return MoePacking(counts, seg, packed_token, pair_to_packed, tile_expert, num_tiles, max_rows, K, tile_valid)
+
+
+def moe_quant(x, rows, max_tiles, rows_per_tile, src_index=None, identity=False, x_div=1, row_limit=None):
+    """bf16 rows -> MXFP8 rows + scale atoms for :func:`mxf4_gemm` (see ``mx_moe_quant``).  Returns (xq [rows, KB*128] uint8,
+    sfb [KB, max_tiles, 512] uint8).  Rows that are skipped (negative index, beyond ``row_limit``) are left unwritten."""
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    K = x.shape[1]
+    KB = (K + 127) // 128
+    xq = torch.empty(rows, KB * 128, dtype=torch.uint8, device=x.device)
+    sfb = torch.empty(KB, max_tiles, 512, dtype=torch.uint8, device=x.device)
+    _check(_lib.cuda().mx_moe_quant(_p(x), x.stride(0), _p(src_index), int(identity), int(x_div), _p(row_limit), int(rows), K, int(max_tiles),
+                                    int(rows_per_tile), _p(xq), _p(sfb), _stream()), "moe_quant")
+    _count()
+    return xq, sfb
+
+
+def mxf4_gemm(w0: QuantWeight, w1: Optional[QuantWeight], xq, sfb, tile_expert, max_tiles, row_stride, tile_valid=None, default_valid=128,
+              num_tiles=None, e_lo=0, bias0=None, bias1=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, zero_out=False):
+    """Block-scaled MXFP4 x MXFP8 grouped GEMM on the tensor cores (``csrc/cuda/gemm_mxf4.cu``).  ``w0`` (and ``w1``: the up bank of a
+    gated pair, with ``act``) are MXF4T banks; ``xq``/``sfb`` come from :func:`moe_quant`.  Returns bf16 [rows, N]; rows that belong to
+    no live tile are left unwritten unless ``zero_out``."""
+    assert w0.fmt == WFormat.MXF4T and (w1 is None or (w1.fmt == WFormat.MXF4T and w1.N == w0.N and w1.K == w0.K and w1.E == w0.E))
+    rows = xq.shape[0]
+    out = (torch.zeros if zero_out else torch.empty)(rows, w0.N, dtype=torch.bfloat16, device=xq.device)
+    _check(_lib.cuda().mx_mxf4_gemm(_p(w0.p0), _p(w0.p1), _p(w1.p0) if w1 is not None else _vp(0), _p(w1.p1) if w1 is not None else _vp(0),
+                                    w0.E, _p(xq), _p(sfb), rows, w0.N, w0.K, _p(tile_expert), _p(tile_valid), int(default_valid), _p(num_tiles),
+                                    int(max_tiles), int(row_stride), int(e_lo), _p(bias0), _p(bias1), _p(out), w0.N, int(act),
+                                    C.c_float(act_alpha), C.c_float(act_limit), _stream()), "mxf4 gemm")
+    _count()
+    return out
 
 
 def expert_group_gemv(x, w: QuantWeight, pk: MoePacking, x_index=None, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, e_lo=0):

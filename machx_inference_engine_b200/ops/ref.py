@@ -334,6 +334,7 @@ class MoePacking:
     num_tiles: torch.Tensor       # [2]: live tiles, packed rows
     max_rows: int
     K: int
+    tile_valid: Optional[torch.Tensor] = None   # [max_tiles] live rows of each tile (block-scaled MXFP4 kernel)
 
 
 def moe_max_rows(n_pairs: int, n_local_experts: int) -> int:
@@ -369,7 +370,12 @@ def moe_pack(topk_idx, E, e_lo=0, e_hi=None, tile=MOE_TILE):
     te = torch.zeros(max_tiles, dtype=torch.int32, device=dev)
     te[: tile_expert.numel()] = tile_expert
     num_tiles = torch.tensor([int(tiles.sum()), int(seg[E])], dtype=torch.int32, device=dev)
-    return MoePacking(counts.to(torch.int32), seg.to(torch.int32), packed_token, pair_to_packed, te, num_tiles, max_rows, K)
+    tv = torch.zeros(max_tiles, dtype=torch.int32, device=dev)
+    if tile > 1 and tile_expert.numel():
+        first = torch.repeat_interleave(torch.cumsum(tiles, 0) - tiles, tiles)           # first tile of each tile's expert
+        within = torch.arange(tile_expert.numel(), device=dev) - first
+        tv[: tile_expert.numel()] = torch.clamp(counts[tile_expert.long()] - within * tile, max=tile).to(torch.int32)
+    return MoePacking(counts.to(torch.int32), seg.to(torch.int32), packed_token, pair_to_packed, te, num_tiles, max_rows, K, tv)
 
 
 def moe_gather(x, pk: MoePacking, f16=False):
@@ -377,6 +383,18 @@ def moe_gather(x, pk: MoePacking, f16=False):
     ok = pk.packed_token >= 0
     xp[ok] = x[pk.packed_token[ok].long()].to(xp.dtype)
     return xp
+
+
+def mxfp8_roundtrip(x: torch.Tensor) -> torch.Tensor:
+    """``x`` [..., K] (K a multiple of 32) rounded the way the activation quantiser of the block-scaled MXFP4 kernel rounds it:
+    per 32 elements a power-of-two scale, the smallest that keeps the block inside e4m3's range (448), then round-to-nearest
+    e4m3.  Returns the decoded fp32 values."""
+    xs = x.to(torch.float32).reshape(*x.shape[:-1], x.shape[-1] // 32, 32)
+    amax = xs.abs().amax(dim=-1, keepdim=True)
+    ex = torch.floor(torch.log2(amax.clamp_min(1e-38))) - 8.0
+    ex = torch.where(amax * torch.exp2(-ex) > 448.0, ex + 1.0, ex).clamp_(-126.0, 126.0)
+    q = (xs * torch.exp2(-ex)).to(torch.float8_e4m3fn).to(torch.float32)
+    return torch.where(amax > 0, q * torch.exp2(ex), torch.zeros_like(q)).reshape(x.shape)
 
 
 def expert_group_gemv(x, w: QuantWeight, pk: MoePacking, x_index=None, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, e_lo=0):

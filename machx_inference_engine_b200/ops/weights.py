@@ -12,6 +12,10 @@ Q6K       ``p0`` lo nibbles [E,N,K/2] (natural order), ``p1`` hi 2-bit plane [E,
           ``p2`` int8 sub-block scales [E,N,K/16], ``p3`` fp16 super scale [E,N,K/256]
 MXFP4     ``p0`` E2M1 codes [E,N,K/2] (natural order: byte i = e[2i] | e[2i+1]<<4),
           ``p1`` e8m0 exponent [E,N,K/32]
+MXF4T     the same codes cut into tiles of 128 rows x 128 elements, ``p0`` [E,NB,KB,128,64] (N and K
+          zero-padded to whole tiles), so that one TMA box is one contiguous 8 KiB run; ``p1`` the
+          exponents as 512-byte atoms [E,NB,KB,512] in the order the tensor core's scale-factor
+          registers want: row r, k-block q of a tile at byte (r % 32) * 16 + (r // 32) * 4 + q
 ========  =====================================================================================
 
 The rows of the small scale planes (Q8 ``p1``, Q6K ``p3``, MXFP4 ``p1``) are zero-padded to 16 bytes
@@ -39,6 +43,7 @@ class WFormat(IntEnum):
     Q4K = 2
     Q6K = 3
     MXFP4 = 4
+    MXF4T = 5      # MXFP4 in 128 x 128 tiles for the block-scaled tensor-core kernel (see to_mxf4_tiles)
 
 
 def _pad_last(t: torch.Tensor, mult: int) -> torch.Tensor:
@@ -188,6 +193,8 @@ class QuantWeight:
             sc = self.p2.to(torch.float32).unsqueeze(-1)
             d = self.p3[..., :K // 256].to(torch.float32).repeat_interleave(16, dim=-1).unsqueeze(-1)
             w = q.to(torch.float32) * sc * d
+        elif self.fmt == WFormat.MXF4T:
+            return from_mxf4_tiles(self).dequantize(dtype)
         elif self.fmt == WFormat.MXFP4:
             codes = self.p0.to(torch.int64)
             c = torch.stack([codes & 15, codes >> 4], dim=-1).reshape(E, N, K // 32, 32)
@@ -271,6 +278,33 @@ def from_ggml(raw: torch.Tensor, ttype: int, N: int, K: int, E: int = 1, keep_q8
         f = quant.dequantize(raw.cpu().numpy(), t, E * N * K)
         return QuantWeight(WFormat.BF16, N, K, E, torch.from_numpy(f).reshape(E, N, K).to(torch.bfloat16).to(dev).contiguous())
     raise ValueError(f"unsupported ggml tensor type {t}")
+
+
+def to_mxf4_tiles(w: QuantWeight) -> QuantWeight:
+    """MXFP4 planes -> the tiled layout of the block-scaled tensor-core kernel (csrc/cuda/gemm_mxf4.cu).  Padding rows and
+    columns hold code 0 (= +0.0) and exponent 127 (scale 1), so they contribute nothing."""
+    assert w.fmt == WFormat.MXFP4
+    E, N, K = w.E, w.N, w.K
+    NB, KB = (N + 127) // 128, (K + 127) // 128
+    dev = w.p0.device
+    codes = torch.zeros(E, NB * 128, KB * 64, dtype=torch.uint8, device=dev)
+    codes[:, :N, :K // 2] = w.p0
+    tiles = codes.reshape(E, NB, 128, KB, 64).permute(0, 1, 3, 2, 4).contiguous()
+    ex = torch.full((E, NB * 128, KB * 4), 127, dtype=torch.uint8, device=dev)
+    ex[:, :N, :K // 32] = w.p1[..., :K // 32]
+    # row r = r1 * 32 + r0 of a tile, k-block q  ->  [r0][r1][q]
+    atoms = ex.reshape(E, NB, 4, 32, KB, 4).permute(0, 1, 4, 3, 2, 5).contiguous().reshape(E, NB, KB, 512)
+    return QuantWeight(WFormat.MXF4T, N, K, E, tiles, atoms)
+
+
+def from_mxf4_tiles(w: QuantWeight) -> QuantWeight:
+    """Inverse of :func:`to_mxf4_tiles` (oracle / CPU path)."""
+    assert w.fmt == WFormat.MXF4T
+    E, N, K = w.E, w.N, w.K
+    NB, KB = w.p0.shape[1], w.p0.shape[2]
+    codes = w.p0.permute(0, 1, 3, 2, 4).reshape(E, NB * 128, KB * 64)[:, :N, :K // 2].contiguous()
+    ex = w.p1.reshape(E, NB, KB, 32, 4, 4).permute(0, 1, 4, 3, 2, 5).reshape(E, NB * 128, KB * 4)[:, :N, :K // 32]
+    return QuantWeight(WFormat.MXFP4, N, K, E, codes, _pad_last(ex, 16))
 
 
 # ------------------------------------------------------------------ torch-side quantisers (device synthesis)

@@ -146,6 +146,8 @@ def test_torch_quantisers(fmt, tol):
 def test_weight_surgery():
     w = torch.randn(1, 64, 512) * 0.05
     for fmt in W.WFormat:
+        if fmt == W.WFormat.MXF4T:       # a tiled layout made from whole MXFP4 banks: sliced before tiling (checked below)
+            continue
         qw = W.from_dense(w, fmt)
         full = qw.dequantize()[0]
         assert torch.equal(qw.slice_rows(16, 48).dequantize()[0], full[16:48])
@@ -156,3 +158,19 @@ def test_weight_surgery():
         assert torch.equal(W.QuantWeight.cat_rows([g, u]).dequantize()[0], full)
     with pytest.raises(ValueError):
         W.from_dense(w, W.WFormat.Q4K).slice_k(32, 512)
+
+
+def test_mxf4_tiles_roundtrip_and_padding():
+    # ragged N and K (not multiples of the 128 x 128 tile): the tiled layout decodes to the same values, experts slice, and
+    # the padding holds code 0 / exponent 127; the scale atom order is row r, k-block q -> (r % 32) * 16 + (r // 32) * 4 + q
+    w = W.from_dense(torch.randn(3, 200, 288) * 0.05, W.WFormat.MXFP4)
+    t = W.to_mxf4_tiles(w)
+    assert t.p0.shape == (3, 2, 3, 128, 64) and t.p1.shape == (3, 2, 3, 512)
+    assert torch.equal(t.dequantize(), w.dequantize())
+    assert torch.equal(t.slice_experts(1, 3).dequantize(), w.dequantize()[1:3])
+    back = W.from_mxf4_tiles(t)
+    assert torch.equal(back.p0, w.p0) and torch.equal(back.p1[..., :9], w.p1[..., :9])
+    r, q, nb, kb = 70, 1, 1, 2                     # global row 198, k-block 9 (elements 288..319 do not exist -> only q = 0 is real)
+    assert int(t.p1[0, nb, kb, (r % 32) * 16 + (r // 32) * 4 + 0]) == int(w.p1[0, 128 + r, 8])
+    assert int(t.p1[0, nb, kb, (r % 32) * 16 + (r // 32) * 4 + q]) == 127
+    assert int(t.p0[0, 1, :, 72:, :].max()) == 0 and int(t.p0[0, :, 2, :, 16:].max()) == 0

@@ -1,0 +1,188 @@
+"""The block-scaled MXFP4 x MXFP8 grouped GEMM (csrc/cuda/gemm_mxf4.cu) and its activation quantiser against fp32 PyTorch.
+
+The oracle multiplies the decoded weights with activations rounded by ``ref.mxfp8_roundtrip`` (the same rounding rule as the
+kernel), so the comparison isolates the kernel's data movement and accumulation; a second, looser check against the
+unrounded activations bounds what the 8-bit activations cost.
+"""
+import pytest
+import torch
+
+from machx_inference_engine_b200.ops import ref
+from machx_inference_engine_b200.ops.weights import WFormat, from_dense, to_mxf4_tiles
+
+pytestmark = pytest.mark.gpu
+
+
+def K():
+    from machx_inference_engine_b200.ops import cuda
+    return cuda
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+def bank(N, Kd, E, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    w = from_dense(torch.randn(E, N, Kd, generator=g) * 0.05, WFormat.MXFP4).to(dev())
+    return w, to_mxf4_tiles(w)
+
+
+def decode_quant(xq, sfb, rows, Kd, rows_per_tile):
+    """(xq, sfb) of moe_quant -> fp32 [rows, Kd]."""
+    KB = sfb.shape[0]
+    r = torch.arange(rows, device=xq.device)
+    tile, rin = r // rows_per_tile, r % rows_per_tile
+    idx = ((rin % 32) * 16 + (rin // 32) * 4)[:, None] + torch.arange(4, device=xq.device)[None, :]      # [rows, 4] bytes in the atom
+    ex = torch.stack([sfb[kb][tile].long().gather(1, idx) for kb in range(KB)], dim=1)                 # [rows, KB, 4]
+    scale = torch.exp2(ex.reshape(rows, KB * 4).float() - 127.0)
+    vals = xq.view(torch.float8_e4m3fn).float().reshape(rows, KB * 4, 32) * scale.unsqueeze(-1)
+    return vals.reshape(rows, KB * 128)[:, :Kd]
+
+
+@pytest.mark.parametrize("Kd", [2880, 256])
+def test_activation_quantiser_matches_the_oracle_rounding(Kd):
+    torch.manual_seed(0)
+    rows = 200
+    x = (torch.randn(rows, Kd, device=dev()) * torch.rand(rows, 1, device=dev()) * 8).to(torch.bfloat16)
+    x[3] = 0
+    x[5, :40] *= 1000.0
+    xq, sfb = K().moe_quant(x, rows, 2, 128)
+    torch.cuda.synchronize()
+    got = decode_quant(xq, sfb, rows, Kd, 128)
+    want = ref.mxfp8_roundtrip(x)
+    assert torch.equal(got, want), rel_err(got, want)
+    # the columns between K and the padded width are zeros
+    if xq.shape[1] > Kd:
+        assert int(xq[:, Kd:].view(torch.int8).abs().max()) == 0
+    # what 8-bit activations cost on their own
+    assert rel_err(want, x) < 4e-2
+
+
+def _oracle(x_rows, W, e, bias):
+    y = ref.mxfp8_roundtrip(x_rows) @ W[e].t()
+    return y if bias is None else y + bias[e]
+
+
+@pytest.mark.parametrize("N,Kd", [(300, 2880), (128, 128), (2880, 512)])
+def test_grouped_gemm_packed_segments(N, Kd):
+    torch.manual_seed(1)
+    E, topk, T = 6, 2, 330
+    w, wt = bank(N, Kd, E, 3)
+    W = w.dequantize()
+    x = torch.randn(T, Kd, device=dev()).to(torch.bfloat16)
+    # skewed routing: expert 0 gets many rows (several tiles, both halves), expert 5 none
+    logits = torch.randn(T, E, device=dev())
+    logits[:, 0] += 2.0
+    logits[:, 5] -= 50.0
+    idx, _ = K().moe_route(logits, None, topk)
+    pk = K().moe_pack(idx, E)
+    pk_r = ref.moe_pack(idx, E)
+    nt = int(pk.num_tiles[0])
+    assert torch.equal(pk.tile_valid[:nt], pk_r.tile_valid[:nt])
+    mt = pk.tile_expert.numel()
+    xq, sfb = K().moe_quant(x, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
+    bias = torch.randn(E, N, device=dev()) * 0.1
+    y = K().mxf4_gemm(wt, None, xq, sfb, pk.tile_expert, mt, 128, tile_valid=pk.tile_valid, num_tiles=pk.num_tiles, bias0=bias)
+    K().check_status()
+    nrows = int(pk.num_tiles[1])
+    tok = pk.packed_token[:nrows]
+    live = tok >= 0
+    row_e = torch.repeat_interleave(pk.tile_expert[:nt].long(), 128)[:nrows]
+    want = torch.zeros(nrows, N, device=dev())
+    for e in range(E):
+        m = live & (row_e == e)
+        if m.any():
+            want[m] = _oracle(x[tok[m].long()], W, e, bias)
+    assert rel_err(y[:nrows][live], want[live]) < 4e-3            # bf16 output rounding
+    exact = torch.zeros_like(want)
+    for e in range(E):
+        m = live & (row_e == e)
+        if m.any():
+            exact[m] = x[tok[m].long()].float() @ W[e].t() + bias[e]
+    assert rel_err(y[:nrows][live], exact[live]) < 4e-2
+
+
+@pytest.mark.parametrize("act", [ref.ACT_SWIGLU, ref.ACT_SWIGLU_OAI])
+def test_gated_pair_of_banks_and_the_whole_expert_ffn(act):
+    torch.manual_seed(2)
+    E, topk, T, H, F = 8, 4, 150, 512, 320
+    g, gt = bank(F, H, E, 5)
+    u, ut = bank(F, H, E, 6)
+    d, dt = bank(H, F, E, 7)
+    Wg, Wu, Wd = g.dequantize(), u.dequantize(), d.dequantize()
+    x = torch.randn(T, H, device=dev()).to(torch.bfloat16)
+    idx, w = K().moe_route(torch.randn(T, E, device=dev()), None, topk)
+    pk = K().moe_pack(idx, E)
+    mt = pk.tile_expert.numel()
+    gb, ub, db = (torch.randn(E, n, device=dev()) * 0.1 for n in (F, F, H))
+    xq, sfb = K().moe_quant(x, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
+    a = K().mxf4_gemm(gt, ut, xq, sfb, pk.tile_expert, mt, 128, tile_valid=pk.tile_valid, num_tiles=pk.num_tiles, bias0=gb, bias1=ub, act=act)
+    aq, sfa = K().moe_quant(a, pk.max_rows, mt, 128, src_index=pk.packed_token, identity=True, row_limit=pk.num_tiles)
+    y = K().mxf4_gemm(dt, None, aq, sfa, pk.tile_expert, mt, 128, tile_valid=pk.tile_valid, num_tiles=pk.num_tiles, bias0=db)
+    out = K().moe_combine(y, pk, w)
+    K().check_status()
+    want = torch.zeros(T, H, device=dev())
+    exact = torch.zeros(T, H, device=dev())
+    xf = x.float()
+    for t in range(T):
+        for s in range(topk):
+            e = int(idx[t, s])
+            xr = ref.mxfp8_roundtrip(x[t:t + 1])
+            av = ref._act(act, xr @ Wg[e].t() + gb[e], xr @ Wu[e].t() + ub[e], 1.702, 7.0).to(torch.bfloat16)
+            yv = (ref.mxfp8_roundtrip(av) @ Wd[e].t() + db[e]).to(torch.bfloat16).float()
+            want[t] += w[t, s] * yv[0]
+            ae = ref._act(act, xf[t:t + 1] @ Wg[e].t() + gb[e], xf[t:t + 1] @ Wu[e].t() + ub[e], 1.702, 7.0)
+            exact[t] += w[t, s] * (ae @ Wd[e].t() + db[e])[0]
+    assert rel_err(out, want) < 1e-2
+    assert rel_err(out, exact) < 5e-2
+
+
+def test_pair_mode_decode_rows_and_foreign_experts():
+    torch.manual_seed(3)
+    E, topk, T, H, F = 8, 4, 3, 2880, 256
+    g, gt = bank(F, H, E, 8)
+    u, ut = bank(F, H, E, 9)
+    Wg, Wu = g.dequantize(), u.dequantize()
+    x = torch.randn(T, H, device=dev()).to(torch.bfloat16)
+    idx, _ = K().moe_route(torch.randn(T, E, device=dev()), None, topk)
+    n = T * topk
+    te = idx.reshape(-1)
+    xq, sfb = K().moe_quant(x, n, n, 1, x_div=topk)
+    a = K().mxf4_gemm(gt, ut, xq, sfb, te, n, 1, default_valid=1, act=ref.ACT_SWIGLU_OAI)
+    K().check_status()
+    for i in range(n):
+        e = int(te[i])
+        xr = ref.mxfp8_roundtrip(x[i // topk: i // topk + 1])
+        want = ref._act(ref.ACT_SWIGLU_OAI, xr @ Wg[e].t(), xr @ Wu[e].t(), 1.702, 7.0)
+        assert rel_err(a[i:i + 1], want) < 6e-3, i
+    # expert parallelism: the bank holds experts [2, 5); pairs of other experts are skipped and stay zero
+    lo, hi = 2, 5
+    a2 = K().mxf4_gemm(gt.slice_experts(lo, hi), ut.slice_experts(lo, hi), xq, sfb, te, n, 1, default_valid=1, act=ref.ACT_SWIGLU_OAI, e_lo=lo,
+                       zero_out=True)
+    K().check_status()
+    own = (te >= lo) & (te < hi)
+    assert torch.equal(a2[own], a[own]) and int(a2[~own].abs().max() if (~own).any() else 0) == 0
+
+
+def test_run_twice_is_bit_identical():
+    torch.manual_seed(4)
+    E, T, H, F = 4, 260, 256, 256
+    _, wt = bank(F, H, E, 11)
+    x = torch.randn(T, H, device=dev()).to(torch.bfloat16)
+    idx, _ = K().moe_route(torch.randn(T, E, device=dev()), None, 2)
+    pk = K().moe_pack(idx, E)
+    mt = pk.tile_expert.numel()
+    outs = []
+    for _ in range(2):
+        xq, sfb = K().moe_quant(x, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
+        y = K().mxf4_gemm(wt, None, xq, sfb, pk.tile_expert, mt, 128, tile_valid=pk.tile_valid, num_tiles=pk.num_tiles, zero_out=True)
+        nrows = int(pk.num_tiles[1])
+        live = pk.packed_token[:nrows] >= 0
+        outs.append(y[:nrows][live].clone())
+    assert torch.equal(outs[0], outs[1])

@@ -63,7 +63,11 @@ def test_tp2_on_cpu_ranks_matches_single_rank(name, quant):
     one = _run(1, name, quant, "cpu")
     two = _run(2, name, quant, "cpu")
     assert two["world"] == 2
-    _close(one, two, cos=0.999, arg=0.95)
+    # MXFP4 experts multiply MXFP8 activations: a rank count changes the fp32 summation order of the attention output by parts in
+    # 1e-3 (bf16 rounding of the partials), and the 3-bit mantissa of e4m3 turns a fraction of those into one-step flips of an
+    # expert input; the logits of the two layouts agree to about 0.997 instead of 0.9996
+    moe = quant == "mxfp4"
+    _close(one, two, cos=0.996 if moe else 0.999, arg=0.93 if moe else 0.95)
 
 
 @pytest.mark.parametrize("name,quant", [("tiny-llama", "q8_0"), ("tiny-qwen3next", "q8_0")])
