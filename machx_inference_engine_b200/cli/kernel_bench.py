@@ -214,49 +214,39 @@ def main(argv=None):
         # the block-scaled tensor-core kernel: MXFP4 tiles x MXFP8 activations (a.layers distinct banks keep the weights out of L2)
         from ..ops.weights import to_mxf4_tiles
         T, E, H, F, k = a.tokens, a.experts, a.hidden, a.ffn, a.topk
-        banks = [tuple(to_mxf4_tiles(weight(n, kd, E)) for n, kd in ((F, H), (F, H), (H, F))) for _ in range(a.layers)]
+        banks = [(to_mxf4_tiles(weight(F, H, E), weight(F, H, E)), to_mxf4_tiles(weight(H, F, E))) for _ in range(a.layers)]
         x = torch.randn(T, H, device=dev).to(torch.bfloat16)
         idx, w = K.moe_route(torch.randn(T, E, device=dev), None, k)
         pair = T <= 8
         i = [0]
         if pair:
             n = T * k
-            te = idx.reshape(-1)
-            xq, sfb = K.moe_quant(x, n, n, 1, x_div=k)
+            quant = lambda: K.moe_quant(x, n, n, 1, x_div=k)
             kw = dict(default_valid=1)
-            args = (te, n, 1)
+            args = (idx.reshape(-1), n, 1)
         else:
             pk = K.moe_pack(idx, E)
             mt = pk.tile_expert.numel()
-            xq, sfb = K.moe_quant(x, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
+            quant = lambda: K.moe_quant(x, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
             kw = dict(tile_valid=pk.tile_valid, num_tiles=pk.num_tiles)
             args = (pk.tile_expert, mt, 128)
-        hmid = K.mxf4_gemm(banks[0][0], banks[0][1], xq, sfb, *args, act=ref.ACT_SWIGLU_OAI, **kw)
-        if pair:
-            aq, sfa = K.moe_quant(hmid, n, n, 1)
-        else:
-            aq, sfa = K.moe_quant(hmid, pk.max_rows, mt, 128, src_index=pk.packed_token, identity=True, row_limit=pk.num_tiles)
+        xq, sfx = quant()
+        aq, sfa = K.mxf4_gemm(banks[0][0], xq, sfx, *args, act=ref.ACT_SWIGLU_OAI, **kw)
 
         def f_gu():
-            g, u, _ = banks[i[0] % a.layers]
-            K.mxf4_gemm(g, u, xq, sfb, *args, act=ref.ACT_SWIGLU_OAI, **kw)
+            K.mxf4_gemm(banks[i[0] % a.layers][0], xq, sfx, *args, act=ref.ACT_SWIGLU_OAI, **kw)
             i[0] += 1
 
         def f_dn():
-            d = banks[i[0] % a.layers][2]
-            K.mxf4_gemm(d, None, aq, sfa, *args, **kw)
+            K.mxf4_gemm(banks[i[0] % a.layers][1], aq, sfa, *args, **kw)
             i[0] += 1
-        wb = banks[0][0].nbytes
+        touched = min(E, T * k) / E if pair else 1.0
         med, mn = timeit(f_gu, a.iters)
         report(f"moe gate+up[mxf4 block-scaled] T={T} E={E} top{k} 2x{F}x{H}", med, mn, flops=2.0 * T * k * 2 * F * H,
-               bytes_=2 * wb * (min(E, T * k) / E if pair else 1.0))
+               bytes_=banks[0][0].nbytes * touched)
         med, mn = timeit(f_dn, a.iters)
-        report(f"moe down[mxf4 block-scaled] T={T} E={E} top{k} {H}x{F}", med, mn, flops=2.0 * T * k * F * H,
-               bytes_=banks[0][2].nbytes * (min(E, T * k) / E if pair else 1.0))
-        if pair:
-            med, mn = timeit(lambda: K.moe_quant(x, n, n, 1, x_div=k), a.iters)
-        else:
-            med, mn = timeit(lambda: K.moe_quant(x, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles), a.iters)
+        report(f"moe down[mxf4 block-scaled] T={T} E={E} top{k} {H}x{F}", med, mn, flops=2.0 * T * k * F * H, bytes_=banks[0][1].nbytes * touched)
+        med, mn = timeit(quant, a.iters)
         report(f"moe activation quantiser T={T} top{k} H={H}", med, mn, bytes_=T * k * H * 3.0)
         K.check_status()
     elif a.kernel == "moe_gemm":

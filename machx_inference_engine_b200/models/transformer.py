@@ -325,7 +325,7 @@ class MoEFFN:
         self.a8 = g.fmt == u.fmt == d.fmt == ops.WFormat.MXFP4 and act in (ACT_SWIGLU, ACT_SWIGLU_OAI) and self.MXF4_TENSOR_CORE
         if g.p0.is_cuda and self.a8:
             from ..ops.weights import to_mxf4_tiles
-            self.mx = (to_mxf4_tiles(g), to_mxf4_tiles(u), to_mxf4_tiles(d))
+            self.mx = (to_mxf4_tiles(g, u), to_mxf4_tiles(d))
             self.gate_up = self.down = None
         else:
             self.gate_up = QuantWeight.interleave_gate_up(g, u)
@@ -415,28 +415,26 @@ class MoEFFN:
 def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor):
     """Expert projections on the block-scaled MXFP4 kernel.  Returns (y bf16 [rows, H], pair_to_packed int32 [T*K])."""
     from ..ops import cuda as K_
-    gate, up, down = self.mx
+    gate_up, down = self.mx
     T = h.shape[0]
     ep = dict(e_lo=self.e_lo)
     if T <= self.MXF4_PAIR_MAX_TOKENS:
         # decode: pair i = (token i // K, slot i % K) is tile i with one live row; no sort, no gather
         n = T * self.K
         te = idx.reshape(-1)
-        xq, sfb = K_.moe_quant(h, n, n, 1, x_div=self.K)
-        a = K_.mxf4_gemm(gate, up, xq, sfb, te, n, 1, default_valid=1, bias0=self.g_bias, bias1=self.u_bias, act=self.act, **ep)
-        aq, sfa = K_.moe_quant(a, n, n, 1)
-        y = K_.mxf4_gemm(down, None, aq, sfa, te, n, 1, default_valid=1, bias0=self.down_bias, zero_out=self.reduce, **ep)
+        xq, sfx = K_.moe_quant(h, n, n, 1, x_div=self.K)
+        aq, sfa = K_.mxf4_gemm(gate_up, xq, sfx, te, n, 1, default_valid=1, bias0=self.g_bias, bias1=self.u_bias, act=self.act, **ep)
+        y = K_.mxf4_gemm(down, aq, sfa, te, n, 1, default_valid=1, bias0=self.down_bias, zero_out=self.reduce, **ep)
         key = (T, h.device)
         if key not in self._arange:
             self._arange[key] = torch.arange(n, dtype=torch.int32, device=h.device)
         return y, self._arange[key]
     pk = ops.moe_pack(idx, self.E, self.e_lo, self.e_hi)
     mt = pk.tile_expert.numel()
-    xq, sfb = K_.moe_quant(h, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
-    a = K_.mxf4_gemm(gate, up, xq, sfb, pk.tile_expert, mt, 128, tile_valid=pk.tile_valid, num_tiles=pk.num_tiles, bias0=self.g_bias,
-                     bias1=self.u_bias, act=self.act, **ep)
-    aq, sfa = K_.moe_quant(a, pk.max_rows, mt, 128, src_index=pk.packed_token, identity=True, row_limit=pk.num_tiles)
-    y = K_.mxf4_gemm(down, None, aq, sfa, pk.tile_expert, mt, 128, tile_valid=pk.tile_valid, num_tiles=pk.num_tiles, bias0=self.down_bias, **ep)
+    tiles = dict(tile_valid=pk.tile_valid, num_tiles=pk.num_tiles)
+    xq, sfx = K_.moe_quant(h, pk.max_rows, mt, 128, src_index=pk.packed_token, row_limit=pk.num_tiles)
+    aq, sfa = K_.mxf4_gemm(gate_up, xq, sfx, pk.tile_expert, mt, 128, bias0=self.g_bias, bias1=self.u_bias, act=self.act, **tiles, **ep)
+    y = K_.mxf4_gemm(down, aq, sfa, pk.tile_expert, mt, 128, bias0=self.down_bias, **tiles, **ep)
     return y, pk.pair_to_packed
 
 

@@ -402,34 +402,60 @@ def moe_pack(topk_idx, E, e_lo=0, e_hi=None, tile=MOE_TILE):
     return MoePacking(counts, seg, packed_token, pair_to_packed, tile_expert, num_tiles, max_rows, K, tile_valid)
 
 
-def moe_quant(x, rows, max_tiles, rows_per_tile, src_index=None, identity=False, x_div=1, row_limit=None):
+def _profiled(name):
+    """The ops that only exist on the GPU report to the per-op profiler themselves (the CPU/GPU dispatcher wraps the others)."""
+    def deco(fn):
+        import functools
+        from ..utils.profiler import profiler as _prof
+
+        @functools.wraps(fn)
+        def wrapped(*args, **kwargs):
+            if _prof.enabled:
+                return _prof.record(name, fn, args, kwargs)
+            return fn(*args, **kwargs)
+        return wrapped
+    return deco
+
+
+@_profiled("moe_quant")
+def moe_quant(x, rows, max_tiles, rows_per_tile, src_index=None, x_div=1, row_limit=None):
     """bf16 rows -> MXFP8 rows + scale atoms for :func:`mxf4_gemm` (see ``mx_moe_quant``).  Returns (xq [rows, KB*128] uint8,
-    sfb [KB, max_tiles, 512] uint8).  Rows that are skipped (negative index, beyond ``row_limit``) are left unwritten."""
+    sfx [KB, max_tiles, 512] uint8).  Rows that are skipped (negative index, beyond ``row_limit``) are left unwritten."""
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1
     K = x.shape[1]
     KB = (K + 127) // 128
     xq = torch.empty(rows, KB * 128, dtype=torch.uint8, device=x.device)
-    sfb = torch.empty(KB, max_tiles, 512, dtype=torch.uint8, device=x.device)
-    _check(_lib.cuda().mx_moe_quant(_p(x), x.stride(0), _p(src_index), int(identity), int(x_div), _p(row_limit), int(rows), K, int(max_tiles),
-                                    int(rows_per_tile), _p(xq), _p(sfb), _stream()), "moe_quant")
+    sfx = torch.empty(KB, max_tiles, 512, dtype=torch.uint8, device=x.device)
+    _check(_lib.cuda().mx_moe_quant(_p(x), x.stride(0), _p(src_index), int(x_div), _p(row_limit), int(rows), K, int(max_tiles),
+                                    int(rows_per_tile), _p(xq), _p(sfx), _stream()), "moe_quant")
     _count()
-    return xq, sfb
+    return xq, sfx
 
 
-def mxf4_gemm(w0: QuantWeight, w1: Optional[QuantWeight], xq, sfb, tile_expert, max_tiles, row_stride, tile_valid=None, default_valid=128,
-              num_tiles=None, e_lo=0, bias0=None, bias1=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, zero_out=False):
-    """Block-scaled MXFP4 x MXFP8 grouped GEMM on the tensor cores (``csrc/cuda/gemm_mxf4.cu``).  ``w0`` (and ``w1``: the up bank of a
-    gated pair, with ``act``) are MXF4T banks; ``xq``/``sfb`` come from :func:`moe_quant`.  Returns bf16 [rows, N]; rows that belong to
-    no live tile are left unwritten unless ``zero_out``."""
-    assert w0.fmt == WFormat.MXF4T and (w1 is None or (w1.fmt == WFormat.MXF4T and w1.N == w0.N and w1.K == w0.K and w1.E == w0.E))
+@_profiled("mxf4_gemm")
+def mxf4_gemm(w: QuantWeight, xq, sfx, tile_expert, max_tiles, row_stride, tile_valid=None, default_valid=128, num_tiles=None, e_lo=0,
+              bias0=None, bias1=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, zero_out=False):
+    """Block-scaled MXFP4 x MXFP8 grouped GEMM on the tensor cores (``csrc/cuda/gemm_mxf4.cu``).  ``w`` is an MXF4T bank and
+    ``xq``/``sfx`` come from :func:`moe_quant` or from a gated call of this function.  A plain bank returns bf16 [rows, N]; a gated
+    pair (``w.dual``, with ``act``) returns the activation already quantised for the next projection: (oq [rows, N rounded up to
+    128] uint8, osf scale atoms).  Rows that belong to no live tile are left unwritten unless ``zero_out``."""
+    assert w.fmt == WFormat.MXF4T
     rows = xq.shape[0]
-    out = (torch.zeros if zero_out else torch.empty)(rows, w0.N, dtype=torch.bfloat16, device=xq.device)
-    _check(_lib.cuda().mx_mxf4_gemm(_p(w0.p0), _p(w0.p1), _p(w1.p0) if w1 is not None else _vp(0), _p(w1.p1) if w1 is not None else _vp(0),
-                                    w0.E, _p(xq), _p(sfb), rows, w0.N, w0.K, _p(tile_expert), _p(tile_valid), int(default_valid), _p(num_tiles),
-                                    int(max_tiles), int(row_stride), int(e_lo), _p(bias0), _p(bias1), _p(out), w0.N, int(act),
-                                    C.c_float(act_alpha), C.c_float(act_limit), _stream()), "mxf4 gemm")
+    dev = xq.device
+    out = oq = osf = None
+    oq_ld = 0
+    if w.dual:
+        oq_ld = (w.N + 127) // 128 * 128
+        oq = torch.empty(rows, oq_ld, dtype=torch.uint8, device=dev)
+        osf = torch.empty(oq_ld // 128, max_tiles, 512, dtype=torch.uint8, device=dev)
+    else:
+        out = (torch.zeros if zero_out else torch.empty)(rows, w.N, dtype=torch.bfloat16, device=dev)
+    _check(_lib.cuda().mx_mxf4_gemm(_p(w.p0), _p(w.p1), int(w.dual), w.E, _p(xq), _p(sfx), rows, w.N, w.K, _p(tile_expert), _p(tile_valid),
+                                    int(default_valid), _p(num_tiles), int(max_tiles), int(row_stride), int(e_lo), _p(bias0), _p(bias1),
+                                    _p(out), w.N, _p(oq), _p(osf), oq_ld, int(act), C.c_float(act_alpha), C.c_float(act_limit), _stream()),
+           "mxf4 gemm")
     _count()
-    return out
+    return (oq, osf) if w.dual else out
 
 
 def expert_group_gemv(x, w: QuantWeight, pk: MoePacking, x_index=None, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, e_lo=0):

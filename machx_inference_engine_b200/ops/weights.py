@@ -12,10 +12,11 @@ Q6K       ``p0`` lo nibbles [E,N,K/2] (natural order), ``p1`` hi 2-bit plane [E,
           ``p2`` int8 sub-block scales [E,N,K/16], ``p3`` fp16 super scale [E,N,K/256]
 MXFP4     ``p0`` E2M1 codes [E,N,K/2] (natural order: byte i = e[2i] | e[2i+1]<<4),
           ``p1`` e8m0 exponent [E,N,K/32]
-MXF4T     the same codes cut into tiles of 128 rows x 128 elements, ``p0`` [E,NB,KB,128,64] (N and K
-          zero-padded to whole tiles), so that one TMA box is one contiguous 8 KiB run; ``p1`` the
-          exponents as 512-byte atoms [E,NB,KB,512] in the order the tensor core's scale-factor
-          registers want: row r, k-block q of a tile at byte (r % 32) * 16 + (r // 32) * 4 + q
+MXF4T     the same codes cut into tiles of 192 rows x 128 elements, ``p0`` [E,FB,KB,192,64] (rows and K
+          zero-padded to whole tiles), so that one TMA box is one contiguous 12 KiB run; ``p1`` the
+          exponents as 512-byte atoms [E,FB,KB,2,512] in the order the tensor core's scale-factor
+          registers want: row r, k-block q of an atom at byte (r % 32) * 16 + (r // 32) * 4 + q.
+          A gated pair shares one bank: 96 gate rows + the same 96 up rows per tile (``dual``)
 ========  =====================================================================================
 
 The rows of the small scale planes (Q8 ``p1``, Q6K ``p3``, MXFP4 ``p1``) are zero-padded to 16 bytes
@@ -75,6 +76,7 @@ class QuantWeight:
     p2: Optional[torch.Tensor] = None
     p3: Optional[torch.Tensor] = None
     _dense_cache: Optional[torch.Tensor] = field(default=None, repr=False)
+    dual: bool = False               # MXF4T only: the bank interleaves a gate and an up matrix (N = rows of each)
 
     # -------------------------------------------------------------- basics
     def planes(self) -> list[Optional[torch.Tensor]]:
@@ -86,7 +88,7 @@ class QuantWeight:
 
     def to(self, device) -> "QuantWeight":
         mv = lambda t: None if t is None else t.to(device).contiguous()
-        return QuantWeight(self.fmt, self.N, self.K, self.E, mv(self.p0), mv(self.p1), mv(self.p2), mv(self.p3))
+        return QuantWeight(self.fmt, self.N, self.K, self.E, mv(self.p0), mv(self.p1), mv(self.p2), mv(self.p3), dual=self.dual)
 
     @property
     def nbytes(self) -> int:
@@ -95,7 +97,7 @@ class QuantWeight:
     # -------------------------------------------------------------- row / column surgery
     def _map_planes(self, fn) -> "QuantWeight":
         out = [None if t is None else fn(t) for t in self.planes()]
-        return QuantWeight(self.fmt, self.N, self.K, self.E, *out)
+        return QuantWeight(self.fmt, self.N, self.K, self.E, *out, dual=self.dual)
 
     def select_rows(self, idx: torch.Tensor) -> "QuantWeight":
         """Rows (output features) ``idx`` of every expert."""
@@ -194,7 +196,10 @@ class QuantWeight:
             d = self.p3[..., :K // 256].to(torch.float32).repeat_interleave(16, dim=-1).unsqueeze(-1)
             w = q.to(torch.float32) * sc * d
         elif self.fmt == WFormat.MXF4T:
-            return from_mxf4_tiles(self).dequantize(dtype)
+            planes = from_mxf4_tiles(self)
+            if self.dual:                 # gate rows, then up rows
+                return torch.cat([planes[0].dequantize(dtype), planes[1].dequantize(dtype)], dim=1)
+            return planes.dequantize(dtype)
         elif self.fmt == WFormat.MXFP4:
             codes = self.p0.to(torch.int64)
             c = torch.stack([codes & 15, codes >> 4], dim=-1).reshape(E, N, K // 32, 32)
@@ -280,31 +285,71 @@ def from_ggml(raw: torch.Tensor, ttype: int, N: int, K: int, E: int = 1, keep_q8
     raise ValueError(f"unsupported ggml tensor type {t}")
 
 
-def to_mxf4_tiles(w: QuantWeight) -> QuantWeight:
-    """MXFP4 planes -> the tiled layout of the block-scaled tensor-core kernel (csrc/cuda/gemm_mxf4.cu).  Padding rows and
-    columns hold code 0 (= +0.0) and exponent 127 (scale 1), so they contribute nothing."""
-    assert w.fmt == WFormat.MXFP4
+MXF4_TILE_ROWS = 192
+
+
+def _mxf4_atoms(ex: torch.Tensor) -> torch.Tensor:
+    """Exponent bytes [E, FB, 192, KB*4] -> scale atoms [E, FB, KB, 2, 512]: the 192 rows of a tile fill one and a half atoms of
+    128 rows (the rest holds 127); row r = r1 * 32 + r0 of an atom, k-block q at byte r0 * 16 + r1 * 4 + q."""
+    E, FB, _, K4 = ex.shape
+    KB = K4 // 4
+    full = torch.full((E, FB, 256, K4), 127, dtype=torch.uint8, device=ex.device)
+    full[:, :, :MXF4_TILE_ROWS] = ex
+    return full.reshape(E, FB, 2, 4, 32, KB, 4).permute(0, 1, 5, 2, 4, 3, 6).contiguous().reshape(E, FB, KB, 2, 512)
+
+
+def _mxf4_pad(w: QuantWeight, rows: int, KB: int):
+    """Codes and exponents of an MXFP4 plane weight padded to ``rows`` x KB*128 (code 0 = +0.0, exponent 127 = scale 1)."""
     E, N, K = w.E, w.N, w.K
-    NB, KB = (N + 127) // 128, (K + 127) // 128
     dev = w.p0.device
-    codes = torch.zeros(E, NB * 128, KB * 64, dtype=torch.uint8, device=dev)
+    codes = torch.zeros(E, rows, KB * 64, dtype=torch.uint8, device=dev)
     codes[:, :N, :K // 2] = w.p0
-    tiles = codes.reshape(E, NB, 128, KB, 64).permute(0, 1, 3, 2, 4).contiguous()
-    ex = torch.full((E, NB * 128, KB * 4), 127, dtype=torch.uint8, device=dev)
+    ex = torch.full((E, rows, KB * 4), 127, dtype=torch.uint8, device=dev)
     ex[:, :N, :K // 32] = w.p1[..., :K // 32]
-    # row r = r1 * 32 + r0 of a tile, k-block q  ->  [r0][r1][q]
-    atoms = ex.reshape(E, NB, 4, 32, KB, 4).permute(0, 1, 4, 3, 2, 5).contiguous().reshape(E, NB, KB, 512)
-    return QuantWeight(WFormat.MXF4T, N, K, E, tiles, atoms)
+    return codes, ex
 
 
-def from_mxf4_tiles(w: QuantWeight) -> QuantWeight:
-    """Inverse of :func:`to_mxf4_tiles` (oracle / CPU path)."""
+def to_mxf4_tiles(w: QuantWeight, up: Optional[QuantWeight] = None) -> QuantWeight:
+    """MXFP4 planes -> the tiled layout of the block-scaled tensor-core kernel (csrc/cuda/gemm_mxf4.cu): tiles of 192 rows x 128
+    elements, ``p0`` [E, FB, KB, 192, 64] codes and ``p1`` [E, FB, KB, 2, 512] scale atoms.  With ``up`` (``w`` = gate) tile fb
+    holds gate rows 96 fb .. 96 fb + 95 followed by the same rows of ``up``; a single matrix puts rows 192 fb .. 192 fb + 191
+    into tile fb."""
+    assert w.fmt == WFormat.MXFP4 and (up is None or (up.fmt == WFormat.MXFP4 and (up.N, up.K, up.E) == (w.N, w.K, w.E)))
+    E, N, K = w.E, w.N, w.K
+    KB = (K + 127) // 128
+    if up is None:
+        FB = (N + MXF4_TILE_ROWS - 1) // MXF4_TILE_ROWS
+        codes, ex = _mxf4_pad(w, FB * MXF4_TILE_ROWS, KB)
+        codes = codes.reshape(E, FB, MXF4_TILE_ROWS, KB, 64)
+        ex = ex.reshape(E, FB, MXF4_TILE_ROWS, KB * 4)
+    else:
+        half = MXF4_TILE_ROWS // 2
+        FB = (N + half - 1) // half
+        cg, eg = _mxf4_pad(w, FB * half, KB)
+        cu, eu = _mxf4_pad(up, FB * half, KB)
+        codes = torch.cat([cg.reshape(E, FB, half, KB, 64), cu.reshape(E, FB, half, KB, 64)], dim=2)
+        ex = torch.cat([eg.reshape(E, FB, half, KB * 4), eu.reshape(E, FB, half, KB * 4)], dim=2)
+        del cg, cu, eg, eu
+    tiles = codes.permute(0, 1, 3, 2, 4).contiguous()
+    return QuantWeight(WFormat.MXF4T, N, K, E, tiles, _mxf4_atoms(ex), dual=up is not None)
+
+
+def from_mxf4_tiles(w: QuantWeight):
+    """Inverse of :func:`to_mxf4_tiles` (oracle / CPU path): the MXFP4 plane weight, or (gate, up) for a gated pair."""
     assert w.fmt == WFormat.MXF4T
     E, N, K = w.E, w.N, w.K
-    NB, KB = w.p0.shape[1], w.p0.shape[2]
-    codes = w.p0.permute(0, 1, 3, 2, 4).reshape(E, NB * 128, KB * 64)[:, :N, :K // 2].contiguous()
-    ex = w.p1.reshape(E, NB, KB, 32, 4, 4).permute(0, 1, 4, 3, 2, 5).reshape(E, NB * 128, KB * 4)[:, :N, :K // 32]
-    return QuantWeight(WFormat.MXFP4, N, K, E, codes, _pad_last(ex, 16))
+    FB, KB = w.p0.shape[1], w.p0.shape[2]
+    codes = w.p0.permute(0, 1, 3, 2, 4)                                               # [E, FB, 192, KB, 64]
+    ex = w.p1.reshape(E, FB, KB, 2, 32, 4, 4).permute(0, 1, 3, 5, 4, 2, 6).reshape(E, FB, 256, KB * 4)[:, :, :MXF4_TILE_ROWS]
+
+    def plane(c, e):
+        rows = c.shape[1] * c.shape[2]
+        return QuantWeight(WFormat.MXFP4, N, K, E, c.reshape(E, rows, KB * 64)[:, :N, :K // 2].contiguous(),
+                           _pad_last(e.reshape(E, rows, KB * 4)[:, :N, :K // 32], 16))
+    if not w.dual:
+        return plane(codes, ex)
+    half = MXF4_TILE_ROWS // 2
+    return plane(codes[:, :, :half], ex[:, :, :half]), plane(codes[:, :, half:], ex[:, :, half:])
 
 
 # ------------------------------------------------------------------ torch-side quantisers (device synthesis)

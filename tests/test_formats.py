@@ -161,16 +161,24 @@ def test_weight_surgery():
 
 
 def test_mxf4_tiles_roundtrip_and_padding():
-    # ragged N and K (not multiples of the 128 x 128 tile): the tiled layout decodes to the same values, experts slice, and
+    # ragged N and K (not multiples of the 192 x 128 tile): the tiled layout decodes to the same values, experts slice, and
     # the padding holds code 0 / exponent 127; the scale atom order is row r, k-block q -> (r % 32) * 16 + (r // 32) * 4 + q
     w = W.from_dense(torch.randn(3, 200, 288) * 0.05, W.WFormat.MXFP4)
     t = W.to_mxf4_tiles(w)
-    assert t.p0.shape == (3, 2, 3, 128, 64) and t.p1.shape == (3, 2, 3, 512)
+    assert t.p0.shape == (3, 2, 3, 192, 64) and t.p1.shape == (3, 2, 3, 2, 512) and not t.dual
     assert torch.equal(t.dequantize(), w.dequantize())
     assert torch.equal(t.slice_experts(1, 3).dequantize(), w.dequantize()[1:3])
     back = W.from_mxf4_tiles(t)
     assert torch.equal(back.p0, w.p0) and torch.equal(back.p1[..., :9], w.p1[..., :9])
-    r, q, nb, kb = 70, 1, 1, 2                     # global row 198, k-block 9 (elements 288..319 do not exist -> only q = 0 is real)
-    assert int(t.p1[0, nb, kb, (r % 32) * 16 + (r // 32) * 4 + 0]) == int(w.p1[0, 128 + r, 8])
-    assert int(t.p1[0, nb, kb, (r % 32) * 16 + (r // 32) * 4 + q]) == 127
-    assert int(t.p0[0, 1, :, 72:, :].max()) == 0 and int(t.p0[0, :, 2, :, 16:].max()) == 0
+    assert int(t.p0[0, 1, :, 8:, :].max()) == 0 and int(t.p0[0, :, 2, :, 16:].max()) == 0      # rows >= 200, k >= 288
+    # tile 1 row 5 = matrix row 197; k-block 9 does not exist (K = 288 = 9 blocks): its scale is the unit exponent
+    assert int(t.p1[0, 1, 2, 0, 5 * 16 + 0]) == int(w.p1[0, 197, 8]) and int(t.p1[0, 1, 2, 0, 5 * 16 + 1]) == 127
+    # a gated pair: tile fb holds gate rows 96 fb.. then the same up rows; rows 128..191 of a tile live in the second atom
+    u = W.from_dense(torch.randn(3, 200, 288) * 0.05, W.WFormat.MXFP4)
+    gu = W.to_mxf4_tiles(w, u)
+    assert gu.dual and gu.p0.shape == (3, 3, 3, 192, 64)
+    g2, u2 = W.from_mxf4_tiles(gu)
+    assert torch.equal(g2.p0, w.p0) and torch.equal(u2.p0, u.p0)
+    assert torch.equal(gu.p0[1, 1, 0, 96 + 7], u.p0[1, 96 + 7, :64]) and torch.equal(gu.p0[1, 1, 0, 7], w.p0[1, 96 + 7, :64])
+    r = 96 + 40          # tile row 136 = up row 96 + 40 of tile 1 -> atom 1, row 8
+    assert int(gu.p1[2, 1, 1, 1, 8 * 16 + 0 * 4 + 3]) == int(u.p1[2, 96 + 40, 7])
