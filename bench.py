@@ -45,11 +45,19 @@ class ClockSampler:
     Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        # nvidia-smi numbers physical GPUs and ignores CUDA_VISIBLE_DEVICES: address the device that cuda:<index> really is by
+        # its UUID, so that on a shared machine the clocks reported are this process's GPU's
+        self.index, self.rows, self.proc = str(index), [], None
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            self.index = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            pass
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index), "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", self.index, "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()

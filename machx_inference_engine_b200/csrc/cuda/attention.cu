@@ -272,11 +272,11 @@ static int launch_partial(const AttnParams& p, cudaStream_t st) {
   constexpr int PAIRS = ATT_WARPS * PPW;
   const size_t smem = (size_t)PAIRS * HD * 4 + (size_t)ATT_TILE * (HD + 2) * 2 + (size_t)ATT_TILE * HD * 2;
   auto kern = attn_partial_kernel<HD, PPW>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.mark();
   }
   dim3 grid(p.B * p.max_q_tiles, p.n_kv, p.n_splits);
   launch_pdl(kern, dim3(grid), dim3(ATT_WARPS * 32), smem, st, p);

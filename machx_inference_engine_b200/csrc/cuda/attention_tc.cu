@@ -291,11 +291,11 @@ static int launch_fa(const void* q, const void* k_cache, const void* v_cache, co
     if (r) return r;
   }
   auto kern = fa_prefill_kernel<HD>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.mark();
   }
   dim3 grid(B * p.max_q_tiles, p.n_q);
   kern<<<grid, 192, L::TOTAL, st>>>(tq, tk, tv, p);

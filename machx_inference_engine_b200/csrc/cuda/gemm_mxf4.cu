@@ -26,7 +26,6 @@
 #include "host_util.h"
 
 #include <cuda_fp8.h>
-#include <mutex>
 
 namespace mx {
 
@@ -496,17 +495,11 @@ MX_HOST_API int mx_mxf4_gemm(const void* w, const void* sfw, int dual, int n_exp
   if ((r = make_tmap_u8(&tx128, xq, Kp, x_rows, Kp, 128))) return r;
   const long long items = (long long)max_tiles * p.FB;
   const int grid = items < sm_count() ? (int)items : sm_count();
-  static std::mutex mu;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  {
-    std::lock_guard<std::mutex> lk(mu);
-    if (!configured[dev & 63]) {
-      cudaError_t e = cudaFuncSetAttribute(mxf4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XLayout::TOTAL);
-      if (e != cudaSuccess) return (int)e;
-      configured[dev & 63] = true;
-    }
+  static DeviceOnce configured;
+  if (configured.pending()) {
+    cudaError_t e = cudaFuncSetAttribute(mxf4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XLayout::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured.mark();
   }
   launch_pdl(mxf4_gemm_kernel, dim3(grid), dim3(192), XLayout::TOTAL, st, tw, tx16, tx32, tx64, tx128, p);
   return (int)cudaGetLastError();

@@ -460,11 +460,11 @@ template <int FMT, int BN, int SA, int SB>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
   using L = SmemLayout<FMT, BN, SA, SB>;
   auto kern = gemm_kernel<FMT, BN, SA, SB>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.mark();
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < sm_count() ? tiles : sm_count();

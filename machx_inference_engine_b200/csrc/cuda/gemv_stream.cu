@@ -450,10 +450,11 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
 template <int FMT, int MM, bool GATED, int NG>
 static int gs_launch(const GsParams& p, int smem, cudaStream_t st) {
   constexpr int THREADS = (GsCfg<FMT>::WARPS + 1) * 32;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(gemv_stream_kernel<FMT, MM, GATED, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done = true;
+  static DeviceOnce attr_done;
+  if (attr_done.pending()) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<FMT, MM, GATED, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_done.mark();
   }
   const int units = p.slots * p.nblk;
   const int per_sm = smem <= 113 * 1024 ? 2 : 1;

@@ -4,7 +4,19 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace mx {
+// "Has this kernel's attribute been set on the current device yet": function attributes such as the dynamic shared-memory
+// limit are per device, so a launcher keeps one latch bit per device ordinal (a process may drive several GPUs).  Two threads
+// that race through `pending()` both set the attribute, which is harmless.
+struct DeviceOnce {
+  std::atomic<unsigned long long> done{0};
+  static int ordinal() { int d = 0; cudaGetDevice(&d); return d & 63; }
+  bool pending() const { return !((done.load(std::memory_order_acquire) >> ordinal()) & 1ull); }
+  void mark() { done.fetch_or(1ull << ordinal(), std::memory_order_release); }
+};
+
 int* status_word();
 int sm_count();
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,

@@ -279,8 +279,12 @@ MX_HOST_API int mx_moe_pack(const int* topk_idx, int n_pairs, int K, int E, int 
                             cudaStream_t st) {
   if (E > 1024 || (tile != 1 && tile != MOE_TILE)) return -120;
   const int pack_smem = 32 * E * (int)sizeof(int);
-  static bool pack_attr = false;
-  if (!pack_attr) { cudaFuncSetAttribute(moe_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * (int)sizeof(int)); pack_attr = true; }
+  static DeviceOnce pack_attr;
+  if (pack_attr.pending()) {
+    cudaError_t e = cudaFuncSetAttribute(moe_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * (int)sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    pack_attr.mark();
+  }
   launch_pdl(moe_pack_kernel, dim3(1), dim3(1024), pack_smem, st, topk_idx, n_pairs, K, E, e_lo, e_hi, counts, seg_start, packed_token, pair_to_packed, tile_expert,
                                       num_tiles, max_rows, tile, tile_valid);
   return (int)cudaGetLastError();

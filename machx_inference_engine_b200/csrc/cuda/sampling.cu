@@ -44,6 +44,10 @@ __device__ __forceinline__ ValIdx block_argmax(ValIdx x, ValIdx* sh) {
   return sh[0];
 }
 
+// A row of NaN logits never beats the initial {-inf, 0x7fffffff}: the id that leaves the sampler is always a row index (0 then),
+// so that nothing downstream (token history, detokeniser, callbacks) sees an out-of-range id.
+__device__ __forceinline__ int valid_id(int i, int V) { return (i < 0 || i >= V) ? 0 : i; }
+
 __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out) {
   pdl_prologue();
   __shared__ ValIdx sh[32];
@@ -51,7 +55,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __res
   ValIdx best{-INFINITY, 0x7fffffff};
   for (int i = threadIdx.x; i < V; i += blockDim.x) best = better(best, ValIdx{row[i], i});
   best = block_argmax(best, sh);
-  if (threadIdx.x == 0) out[blockIdx.x] = best.i;
+  if (threadIdx.x == 0) out[blockIdx.x] = valid_id(best.i, V);
 }
 
 // Wide vocabularies: ARGMAX_CHUNKS CTAs per row reduce a slice each into a device scratch slot, and the last CTA of a
@@ -88,7 +92,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_split_kernel(const float*
       z.i = __shfl_xor_sync(0xffffffffu, y.i, o);
       y = better(y, z);
     }
-    if (threadIdx.x == 0) { out[r] = y.i; g_argmax_ticket[r] = 0; }
+    if (threadIdx.x == 0) { out[r] = valid_id(y.i, V); g_argmax_ticket[r] = 0; }
   }
 }
 
@@ -178,7 +182,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const SampleParams
       for (int n = 0; n < keep; ++n) { c += win_v[n]; if (u < c) { pick = win_i[n]; break; } }
     }
     s_pick = pick;
-    p.out[r] = s_pick;
+    p.out[r] = valid_id(s_pick, p.V);
   }
 }
 

@@ -74,8 +74,15 @@ def set_pdl(on: bool) -> None:
     _lib.cuda().mx_set_pdl(1 if on else 0)
 
 
+_sm_count = 0
+
+
 def sm_count() -> int:
-    return _lib.cuda().mx_sm_count()
+    """Streaming multiprocessors of the current device (148 on a B200), asked once."""
+    global _sm_count
+    if not _sm_count:
+        _sm_count = int(_lib.cuda().mx_sm_count())
+    return _sm_count
 
 
 # ------------------------------------------------------------------ elementwise
@@ -186,7 +193,7 @@ GEMV_MAX_M = 8
 
 def _pick_bn(M: int, N: int) -> int:
     # small-M problems are weight-read bound: use narrow tiles so every SM streams weights
-    sms = 148
+    sms = sm_count()
     if M <= 128:
         for bn in (128, 64, 32):
             if (N + bn - 1) // bn >= sms:
@@ -345,7 +352,7 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
         # decode-sized problems: split the KV range so that ~2 CTAs per SM exist
         ctas = B * n_kv * max(1, (max_q_len * (n_q // n_kv) + 31) // 32)
         max_kv_tiles = max(1, (block_table.shape[1] * bs) // 64)
-        n_splits = max(1, min(max_kv_tiles, 32, (2 * 148) // max(ctas, 1)))
+        n_splits = max(1, min(max_kv_tiles, 32, (2 * sm_count()) // max(ctas, 1)))
     need = n_splits * Tq * n_q * (hd + 2)
     if torch.cuda.is_current_stream_capturing():
         # a captured kernel keeps the raw address: the scratch must live exactly as long as the graph, so it comes from the

@@ -59,6 +59,7 @@ class Sequence:
     finish_reason: str = ""
     state_slot: int = -1
     restore_hash: Optional[bytes] = None       # hybrid models: block hash whose recurrent-state snapshot has to be restored into the slot
+    restore_snap: Optional[object] = None      # ... and the snapshot itself, held from the prefix match until the restore (see Scheduler.schedule)
     h_last: Optional[torch.Tensor] = None      # hidden state of the last computed position (speculative decoding)
     t_arrival: float = 0.0
     t_first_token: float = 0.0
@@ -235,10 +236,14 @@ class Scheduler:
                 blocks, hashes = self.bm.match_prefix(seq.tokens)
                 if self.uses_state:
                     # a recurrent model can resume only where its state was saved: keep the longest such prefix of the cached blocks
-                    keep = self.state_prefix(hashes) if (self.state_prefix and hashes) else 0
+                    # The snapshot is held by the sequence from here on: admission can be deferred for any number of steps (no free
+                    # blocks), and in the meantime other sequences may push it out of the LRU snapshot cache.  Resuming at the cached
+                    # position without it would continue on the slot's previous occupant's state.
+                    keep, snap = self.state_prefix(hashes) if (self.state_prefix and hashes) else (0, None)
                     self.bm.release(blocks[keep:])
                     blocks, hashes = blocks[:keep], hashes[:keep]
                     seq.restore_hash = hashes[-1] if keep else None
+                    seq.restore_snap = snap if keep else None
                 seq.blocks, seq.block_hashes = blocks, hashes
                 seq.n_computed = seq.n_cached_prefix = len(blocks) * KV_BLOCK
             n = min(budget, len(seq.tokens) - seq.n_computed)
@@ -257,6 +262,7 @@ class Scheduler:
         self.running.remove(seq)
         self.bm.release(seq.blocks)
         seq.blocks, seq.block_hashes, seq.n_computed = [], [], 0
+        seq.restore_hash = seq.restore_snap = None
         if seq.state_slot >= 0:
             self.free_state.append(seq.state_slot)
             seq.state_slot = -1
@@ -306,20 +312,23 @@ class LLMEngine:
         self.spec_k = o.spec_k if (o.spec_k > 0 and getattr(model, "mtp", None) is not None and self.state is not None) else 0
 
     # ------------------------------------------------------------------ recurrent-state prefix snapshots (hybrid models)
-    def _state_prefix(self, hashes: list) -> int:
+    def _state_prefix(self, hashes: list):
+        """(number of leading blocks that end on a stored snapshot, that snapshot)."""
         for n in range(len(hashes), 0, -1):
-            if hashes[n - 1] in self.state_cache:
+            snap = self.state_cache.get(hashes[n - 1])
+            if snap is not None:
                 self.state_cache.move_to_end(hashes[n - 1])
-                return n
-        return 0
+                return n, snap
+        return 0, None
 
     def _restore_states(self, plan: list) -> None:
         for seq, _ in plan:
             if seq.restore_hash is not None:
-                snap = self.state_cache.get(seq.restore_hash)
-                if snap is not None:
-                    self.state.restore(seq.state_slot, snap)
-                seq.restore_hash = None
+                snap = seq.restore_snap if seq.restore_snap is not None else self.state_cache.get(seq.restore_hash)
+                if snap is None:          # cannot happen while the sequence holds its snapshot; never resume on a foreign state
+                    raise RuntimeError("recurrent-state snapshot of a matched prefix is gone")
+                self.state.restore(seq.state_slot, snap)
+                seq.restore_hash = seq.restore_snap = None
 
     def _save_states(self, plan: list) -> None:
         if self.state is None or not self.opts.enable_prefix_cache:
@@ -373,6 +382,10 @@ class LLMEngine:
         for row, i in enumerate(sampled_rows):
             seq, n = plan[i]
             tok = int(tokens[row])
+            if not 0 <= tok < self.model.cfg.vocab:       # never hand an id outside the vocabulary to the history / detokeniser / callbacks
+                seq.finished, seq.finish_reason = True, "error"
+                out.append((seq, -1, True))
+                continue
             if seq.n_generated == 0:
                 seq.t_first_token = time.perf_counter()
             seq.tokens.append(tok)

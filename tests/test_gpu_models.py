@@ -50,9 +50,13 @@ def test_logits_cosine_prefill_and_graph_decode():
         fb = ForwardBatch(torch.tensor(ids, dtype=torch.int32, device=d), pos, slot, bt, torch.tensor([T], dtype=torch.int32, device=d),
                           torch.tensor([0, T], dtype=torch.int32, device=d), T, logit_rows=torch.arange(T, device=d))
         res[dev] = m.forward(fb, kv).float().cpu()
-    assert _cos(res["cpu"], res["cuda:0"]) > 0.999
+    # The CPU oracle restates the experts' arithmetic (MXFP8 inputs, fp32 math).  The two paths still sum in different orders, and
+    # a difference of one bf16 step in an expert input becomes, for a fraction of the elements, one e4m3 step (6 %): measured
+    # cosine 0.9983 where the bf16-activation path of the dense layers gives 0.9996.  The kernel itself is checked against its
+    # exact specification in test_gpu_mxf4.py (relative error 4e-3, the bf16 output rounding).
+    assert _cos(res["cpu"], res["cuda:0"]) > 0.997
     agree = (res["cpu"].argmax(-1) == res["cuda:0"].argmax(-1)).float().mean()
-    assert agree > 0.95
+    assert agree > 0.93
     # What the 8-bit expert activations cost: the same model with bf16 activations into the experts (the CPU oracle with the
     # MXFP8 rounding switched off).  e4m3 keeps 3 mantissa bits, about 2.5 % rms error per expert GEMM input.
     from machx_inference_engine_b200.models.transformer import MoEFFN

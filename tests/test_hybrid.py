@@ -157,3 +157,27 @@ def test_prefix_cache_restores_recurrent_state():
     while not seq.finished:
         eng.step()
     assert seq.n_cached_prefix == 128 and seq.tokens[len(seq.prompt):] == cold
+
+
+def test_deferred_admission_keeps_its_state_snapshot():
+    """A request matches a cached prefix, cannot be admitted for a while (the block pool is held by another request), and in the
+    meantime the recurrent-state snapshot of that prefix is pushed out of the LRU cache.  It must still resume from the state that
+    belongs to its prefix (the sequence holds the snapshot from match to restore) and produce what a cold run produces."""
+    m = _model()
+    V = m.cfg.vocab
+    shared = [(i * 13 + 1) % V for i in range(300)]
+    sp = SamplingParams(max_tokens=8, ignore_eos=True)
+    cold = LLMEngine(m, EngineOptions(max_ctx=1024, max_seqs=2, max_batch_tokens=128, enable_prefix_cache=False)).generate([shared + [5, 6, 7]], sp)[0]
+    # six usable blocks: two stay cached for the shared prefix, the blocker takes the other four
+    eng = LLMEngine(m, EngineOptions(max_ctx=1024, max_seqs=2, max_batch_tokens=256, num_blocks=7))
+    eng.generate([shared + [9, 9]], sp)
+    assert len(eng.state_cache) == 1                        # one 256-token chunk: one snapshot, at the 256-token boundary
+    blocker = eng.add_request([(i * 7 + 3) % V for i in range(484)], SamplingParams(max_tokens=4, ignore_eos=True))
+    eng.step()                                              # first 256 tokens of the blocker
+    late = eng.add_request(shared + [5, 6, 7], sp)
+    eng.step()                                              # the blocker's rest leaves 28 tokens of budget: `late` matches, finds no block
+    assert late in eng.sched.waiting and late.restore_hash is not None and late.n_cached_prefix == 256
+    eng.state_cache.clear()                                 # what other traffic does to a 12-entry LRU in the meantime
+    while not late.finished:
+        eng.step()
+    assert blocker.finished and late.tokens[len(late.prompt):] == cold
