@@ -105,6 +105,7 @@ def main():
     ap.add_argument("--baseline-comm", action="store_true", help="plain NCCL all-reduce instead of the fused GEMM+all-reduce kernels")
     ap.add_argument("--pdl", type=int, default=-1, help="1/0: programmatic dependent launch for the decode chain (default: the library's setting)")
     ap.add_argument("--reduce-scatter", type=int, default=-1, help="ranks from which prefill collectives take the reduce-scatter form (default: the library's)")
+    ap.add_argument("--replicated", action="store_true", help="keep the activations replicated on every rank (fused all-reduce) instead of the row-sharded prefill")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -139,6 +140,9 @@ def main():
         par.fused.RS_MIN_WORLD = args.reduce_scatter
     note("process group + comm ready")
     cfg = preset(args.model)
+    if par.fused is not None and not args.replicated:
+        from machx_inference_engine_b200.parallel.sharded import attach
+        attach(par, dev, cfg, max(args.prefill, 128 * par.world))
     quant = args.quant or ("mxfp4" if cfg.arch == "gpt-oss" else "q4_k_m" if cfg.arch == "llama" else "q8_0")
     P, D = args.prefill, args.decode
     max_ctx = ((P + D + 16 + 127) // 128) * 128

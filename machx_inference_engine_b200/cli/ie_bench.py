@@ -38,6 +38,7 @@ def main(argv=None) -> int:
     ap.add_argument("--spec-k", type=int, default=0, help="MTP self-speculative decode with this draft length (models with an MTP head)")
     ap.add_argument("--int8-kv", action="store_true", help="int8 KV cache with per-row scales")
     ap.add_argument("--baseline-comm", action="store_true")
+    ap.add_argument("--replicated", action="store_true", help="multi-GPU: replicated activations + fused all-reduce instead of the row-sharded prefill")
     ap.add_argument("--device", default="cuda")
     args = ap.parse_args(argv)
 
@@ -65,6 +66,9 @@ def main(argv=None) -> int:
         quant = args.quant or ("mxfp4" if cfg.arch == "gpt-oss" else "q4_k_m")
         model = build_model(cfg, dev, par, quant=quant, max_ctx=max_ctx)
     cfg = model.cfg
+    if cuda and par.fused is not None and not args.replicated:
+        from ..parallel.sharded import attach
+        attach(par, dev, cfg, max(lens))                     # row-sharded prefill for chunks that divide over the ranks
     eng = LLMEngine(model, EngineOptions(max_ctx=max_ctx, max_batch_tokens=max(lens), max_seqs=1, enable_prefix_cache=False, spec_k=args.spec_k,
                                          kv_dtype="int8" if args.int8_kv else "bf16", cuda_graphs=cuda and not args.no_graphs and not args.kprofile_decode))
 

@@ -46,6 +46,11 @@ struct GemmParams {
   int group_m;                  // tile rasterisation group (see tile_coords)
   int* status;
   PeerOut peer;                 // world > 0: the tile is stored into every rank's inbox (fused all-reduce), not into C
+  // all-gather -> GEMM: A is a gather buffer whose row chunks are stored by their owner ranks (shard.cu); the TMA producer waits for
+  // the owner's flag before it loads the first tile of a chunk, and m-tiles are walked starting at this rank's own chunk
+  const int* a_flags;           // [world] flags of the gather buffer (this rank's copy), null = plain A
+  const int* a_seq;             // device word: the sequence number the flags have to reach
+  int a_rows_per_src, a_world, m_rot;
 };
 
 constexpr int kRawDepth = 10;   // k-iterations of packed weight bytes kept in flight per producer thread
@@ -80,12 +85,13 @@ struct SmemLayout {
 // fastest, then n.  group_m = 1 (grouped / MoE problems) keeps one m-tile's activations hot in L2
 // while its n-tiles stream the expert's weights exactly once; dense problems use a group of 8 so a
 // wave of CTAs shares both a band of A and a band of W.
-__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mt, int& nt) {
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mt, int& nt, int m_rot = 0) {
   const int per_group = group_m * n_tiles;
   const int g = t / per_group, r = t - g * per_group;
   const int gm = min(group_m, m_tiles - g * group_m);
   mt = g * group_m + r % gm;
   nt = r / gm;
+  if (m_rot) { mt += m_rot; if (mt >= m_tiles) mt -= m_tiles; }
 }
 
 __device__ __forceinline__ float act_apply(int act, float g, float u, float alpha, float limit) {
@@ -167,8 +173,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int mt, nt;
-        tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
+        tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt, p.m_rot);
         const int e = p.tile_expert ? p.tile_expert[mt] : 0;
+        if (p.a_flags) {
+          // the rows of this m-tile come from one owner rank: wait (bounded) until that rank's stores have been published
+          const int src = min((mt * BM) / p.a_rows_per_src, p.a_world - 1);
+          const int want = *p.a_seq;
+          if (ld_acquire_sys(p.a_flags + src) - want < 0) {
+            const long long t0 = clock64();
+            while (ld_acquire_sys(p.a_flags + src) - want < 0) {
+              __nanosleep(64);
+              if (*abort_flag || clock64() - t0 > 2000000000ll) { *abort_flag = 1; atomicCAS(p.status, 0, ERR_PEER_FLAG_TIMEOUT); ok = false; break; }
+            }
+            if (!ok) break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");      // the peer's stores, acquired above, before this thread's TMA reads
+        }
         for (int kl = 0; kl < kl_iters; ++kl, ++it) {
           const uint32_t s = it % LA, ph = (it / LA) & 1;
           if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, p.status, ERR_MBAR_TIMEOUT_PRODUCER, abort_flag))) break;
@@ -222,7 +242,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_n) {
       int mt, nt;
-      tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
+      tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt, p.m_rot);
       const int e = p.tile_expert ? p.tile_expert[mt] : 0;
       const uint32_t acc = tile_n & 1, acc_ph = (tile_n >> 1) & 1;
       if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag))) break;
@@ -382,7 +402,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       prow_ok = false;
       if (pt < total_tiles && live) {
         int pmt, pnt;
-        tile_coords(pt, m_tiles, p.num_n_tiles, p.group_m, pmt, pnt);
+        tile_coords(pt, m_tiles, p.num_n_tiles, p.group_m, pmt, pnt, p.m_rot);
         const int n = pnt * BN + rl;
         if (n < p.N) {
           const int pe = p.tile_expert ? p.tile_expert[pmt] : 0;
@@ -405,7 +425,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int mt, nt;
-      tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt);
+      tile_coords(t, m_tiles, p.num_n_tiles, p.group_m, mt, nt, p.m_rot);
       const bool row_ok = live && nt * BN + rl < p.N;
       for (int kl = 0; kl < kl_iters && ok; ++kl) {
         if (!(ok = mbar_wait(bar_bempty + 8 * sb, phb ^ 1, p.status, ERR_MBAR_TIMEOUT_DEQUANT, abort_flag))) break;
@@ -496,10 +516,11 @@ static int dispatch_fmt(int fmt, const CUtensorMap& ta, const CUtensorMap& tb, c
 //   tile_expert / num_m_tiles_dev: grouped mode (both null for a plain GEMM)
 //   bn         32, 64 or 128 (tile width); the caller picks small tiles for small M
 // Returns 0 or a CUDA / driver error code.
+struct GatherIn { const int* flags; const int* seq; int rows_per_src, world, m_rot; };
 static int gemm_impl(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, int n_experts,
                      void* c, int ldc, int out_f32, const float* bias, const float* row_scale, int act, float act_alpha,
                      float act_limit, int M, int N, int K, const int* tile_expert, const int* num_m_tiles_dev, int bn,
-                     const mx::PeerOut* peer, cudaStream_t stream);
+                     const mx::PeerOut* peer, cudaStream_t stream, const GatherIn* gin = nullptr);
 
 MX_HOST_API int mx_gemm(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, int n_experts,
                         void* c, int ldc, int out_f32, const float* bias, const float* row_scale, int act, float act_alpha,
@@ -507,6 +528,17 @@ MX_HOST_API int mx_gemm(const void* a, int wfmt, const void* w0, const void* w1,
                         cudaStream_t stream) {
   return gemm_impl(a, wfmt, w0, w1, w2, w3, n_experts, c, ldc, out_f32, bias, row_scale, act, act_alpha, act_limit, M, N, K, tile_expert,
                    num_m_tiles_dev, bn, nullptr, stream);
+}
+
+// all-gather -> GEMM: `a` is this rank's gather buffer [M,K]; rows [s * rows_per_src, (s + 1) * rows_per_src) are valid once
+// flags[s] >= *seq.  m-tiles are taken starting at tile m_rot (this rank's own rows), so the math starts before the peers' rows
+// have arrived.  Optional reduce-scatter epilogue as in mx_gemm_allreduce when world > 0.
+MX_HOST_API int mx_gemm_gathered(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, void* c, int ldc,
+                                 int out_f32, const float* bias, int act, float act_alpha, float act_limit, int M, int N, int K, int bn,
+                                 const int* flags, const int* seq, int rows_per_src, int src_world, int m_rot, cudaStream_t stream) {
+  GatherIn g{flags, seq, rows_per_src, src_world, m_rot};
+  return gemm_impl(a, wfmt, w0, w1, w2, w3, 1, c, ldc, out_f32, bias, nullptr, act, act_alpha, act_limit, M, N, K, nullptr, nullptr, bn, nullptr,
+                   stream, &g);
 }
 
 namespace mx { PeerOut make_peer_out(const void* const* inbox, int world, int my_rank, long long slot_bytes, int* seq, int* ticket); }
@@ -526,7 +558,7 @@ MX_HOST_API int mx_gemm_allreduce(const void* a, int wfmt, const void* w0, const
 static int gemm_impl(const void* a, int wfmt, const void* w0, const void* w1, const void* w2, const void* w3, int n_experts,
                      void* c, int ldc, int out_f32, const float* bias, const float* row_scale, int act, float act_alpha,
                      float act_limit, int M, int N, int K, const int* tile_expert, const int* num_m_tiles_dev, int bn,
-                     const mx::PeerOut* peer, cudaStream_t stream) {
+                     const mx::PeerOut* peer, cudaStream_t stream, const GatherIn* gin) {
   using namespace mx;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (K % 8) return -101;
@@ -546,6 +578,13 @@ static int gemm_impl(const void* a, int wfmt, const void* w0, const void* w1, co
   if (peer) p.peer = *peer; else p.peer.world = 0;
   p.group_m = tile_expert ? 1 : 8;
   p.status = status_word();
+  p.a_flags = nullptr; p.a_seq = nullptr; p.a_rows_per_src = 0; p.a_world = 0; p.m_rot = 0;
+  if (gin) {
+    if (gin->rows_per_src % BM) return -106;            // a 128-row tile must not straddle two owners
+    p.a_flags = gin->flags; p.a_seq = gin->seq; p.a_rows_per_src = gin->rows_per_src; p.a_world = gin->world;
+    p.m_rot = gin->m_rot % p.num_m_tiles;
+    p.group_m = 1;                                      // m-major walk: all n-tiles of a row chunk before the next chunk is needed
+  }
 
   CUtensorMap ta, tb;
   {

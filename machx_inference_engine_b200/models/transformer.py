@@ -236,6 +236,25 @@ class AttentionBlock:
         return self.o(a, par)
 
 
+def _attn_gathered(self, sc, T: int, gbuf: int, fb: ForwardBatch, kv: KVCache, rope, par: ParallelCtx):
+    """Row-sharded prefill: qkv on the gathered rows (all-gather -> GEMM), attention over this rank's heads, and the output
+    projection with the reduce-scatter epilogue (each row's partial goes to the rank that owns the row)."""
+    qkv = sc.linear_gathered(self.qkv, T, gbuf)
+    q, gate = ops.qkv_post(qkv, None, self.q_norm, self.k_norm, fb.positions, rope[0], rope[1], fb.slot_map, kv.k[self.layer],
+                           kv.v[self.layer], self.n_q, self.n_kv, self.hd, self.n_rot, q_gate=self.q_gate,
+                           norm_one_plus_w=self.norm_one_plus_w, eps=self.eps, kv_scales=kv.scales(self.layer),
+                           **({"v_norm": True} if self.v_norm else {}))
+    a = ops.attention(q, kv.k[self.layer], kv.v[self.layer], fb.block_table, fb.seq_lens, fb.cu_q, fb.max_q_len, sinks=self.sinks,
+                      window=self.window, scale=self.scale, kv_scales=kv.scales(self.layer), max_kv_len=fb.max_kv_len)
+    a = a.reshape(a.shape[0], self.n_q * self.hd)
+    if gate is not None:
+        a = ops.sigmoid_mul(a, gate.reshape(a.shape))
+    return par.fused.linear_all_reduce(a, self.o.w, self.o.bias, rs_rows=T // par.world)
+
+
+AttentionBlock.forward_gathered = _attn_gathered
+
+
 class DenseFFN:
     def __init__(self, cfg: ModelConfig, layer: int, src, par: ParallelCtx, prefix: Optional[str] = None, act: int = ACT_SWIGLU,
                  ffn: Optional[int] = None, suffix: str = ""):
@@ -273,6 +292,20 @@ class DenseFFN:
             il = torch.cat([g.reshape(-1, F // 16, 16), u.reshape(-1, F // 16, 16)], dim=2).reshape(-1, 2 * F)
             a = ops.glu(il.contiguous(), self.act)
         return self.down(a, par)
+
+
+def _ffn_gathered(self, sc, T: int, gbuf: int, par: ParallelCtx):
+    if self.gate_up is not None:
+        a = sc.linear_gathered(self.gate_up, T, gbuf)
+    else:
+        g, u = sc.linear_gathered(self.split[0], T, gbuf), sc.linear_gathered(self.split[1], T, gbuf)
+        F = g.shape[1]
+        il = torch.cat([g.reshape(-1, F // 16, 16), u.reshape(-1, F // 16, 16)], dim=2).reshape(-1, 2 * F)
+        a = ops.glu(il.contiguous(), self.act)
+    return par.fused.linear_all_reduce(a, self.down.w, self.down.bias, rs_rows=T // par.world)
+
+
+DenseFFN.forward_gathered = _ffn_gathered
 
 
 def _even_chunks(n: int, parts: int, gran: int) -> list[tuple[int, int]]:
@@ -441,6 +474,25 @@ def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor):
 MoEFFN._mx_experts = _mx_experts
 
 
+def _moe_sharded(self, h: torch.Tensor, sc) -> torch.Tensor:
+    """Row-sharded prefill: this rank routes only its own rows ``h`` [R, H], the rows travel as MXFP8 to the ranks that own their
+    experts, and the expert outputs come back to be summed here.  Returns the fp32 contribution [R, H]."""
+    from ..ops import cuda as K_
+    gate_up, down = self.mx
+    logits = self.router(h, out_f32=True)
+    idx, w = ops.moe_route(logits, self.router_bias, self.K, True)
+    if self.expert_scale is not None:
+        w = w * self.expert_scale[idx.long()]
+    xq, sfx, plan = sc.dispatch(h, idx)
+    tiles = dict(tile_valid=plan.tile_valid, num_tiles=plan.num_tiles, e_lo=self.e_lo)
+    aq, sfa = K_.mxf4_gemm(gate_up, xq, sfx, plan.tile_expert, plan.max_tiles, 128, bias0=self.g_bias, bias1=self.u_bias, act=self.act, **tiles)
+    y = K_.mxf4_gemm(down, aq, sfa, plan.tile_expert, plan.max_tiles, 128, bias0=self.down_bias, **tiles)
+    return sc.combine(y, plan, w)
+
+
+MoEFFN.forward_sharded = _moe_sharded
+
+
 def _as_bf16(w: QuantWeight) -> dict:
     d = w.dequantize(torch.bfloat16)
     return dict(fmt=ops.WFormat.BF16, N=w.N, K=w.K, E=w.E, p0=d.contiguous())
@@ -514,9 +566,62 @@ class TransformerModel:
         if self.pp:
             return self._forward_pipeline(fb, kv, state)
         c = self.cfg
+        if self._can_shard(fb, state):
+            return self._forward_sharded(fb, kv)
         x = ops.embed(self.embed_w, fb.ids, c.embedding_scale)
         x, delta = self._run_layers(x, None, fb, kv, state)
         return self._head(x, delta, fb)
+
+    # ---- row-sharded prefill (tensor / expert parallel ranks each keep T / W rows of the residual stream)
+    def _can_shard(self, fb: ForwardBatch, state) -> bool:
+        par = self.par
+        sc = getattr(par, "sharded", None)
+        if sc is None or par.fused is None or state is not None or self.tap is not None or fb.want_hidden or type(self) is not TransformerModel:
+            return False
+        if not sc.can_shard(fb.T) or fb.T < self.SHARD_MIN_TOKENS:
+            return False
+        return all(("moe" not in L) or (L["moe"].mx is not None and L["moe"].shared is None) for L in self.layers)
+
+    SHARD_MIN_TOKENS = 512
+
+    def _forward_sharded(self, fb: ForwardBatch, kv: KVCache) -> torch.Tensor:
+        """Prefill with the residual stream sharded by rows: per layer one all-gather (fused into the qkv GEMM's operand load), one
+        reduce-scatter (the output projection's epilogue) and, for expert layers, an all-to-all of MXFP8 rows and bf16 results; dense
+        FFN layers take a second gather / scatter pair.  Norms, routing, packing and quantisation run on T / W rows."""
+        c, par = self.cfg, self.par
+        sc = par.sharded
+        T = fb.T
+        row0, R = sc.rows(T)
+        x = ops.embed(self.embed_w, fb.ids[row0:row0 + R].contiguous(), c.embedding_scale)
+        rs = c.residual_scale
+        nk = dict(one_plus_w=self.one_plus_w, delta_scale=rs)
+        delta = None
+        for L in self.layers:
+            _, g = sc.norm(x, L["attn_norm"], c.rms_eps, T, delta=delta, gather=True, **nk)
+            a = L["attn"].forward_gathered(sc, T, g, fb, kv, self.rope, par)
+            if "moe" in L:
+                h2, _ = sc.norm(x, L["ffn_norm"], c.rms_eps, T, delta=a, want_local=True, **nk)
+                delta = L["moe"].forward_sharded(h2, sc)
+            else:
+                _, g2 = sc.norm(x, L["ffn_norm"], c.rms_eps, T, delta=a, gather=True, **nk)
+                delta = L["ffn"].forward_gathered(sc, T, g2, par)
+        sc.norm(x, self.out_norm, c.rms_eps, T, delta=delta, **nk)            # folds the last delta into the residual rows
+        # the rows that need logits, replicated: each rank contributes the ones it owns
+        rows = fb.logit_rows if fb.logit_rows is not None else (fb.cu_q[1:].long() - 1)
+        local = rows.long() - row0
+        mine = ((local >= 0) & (local < R)).unsqueeze(-1)
+        xr = torch.where(mine, x.index_select(0, local.clamp(0, R - 1)), torch.zeros((), dtype=x.dtype, device=x.device))
+        if par.world > 1:
+            par.all_reduce(xr)
+        hn = ops.rmsnorm(xr, self.out_norm, c.rms_eps, one_plus_w=self.one_plus_w)
+        logits = self.lm_head(hn, out_f32=True)
+        if self.vocab_hi - self.vocab_lo != c.vocab:
+            logits = par.all_gather_cols(logits)
+        if c.logit_scale != 1.0:
+            logits = logits * c.logit_scale
+        if c.final_logit_softcap > 0:
+            logits = torch.tanh(logits / c.final_logit_softcap) * c.final_logit_softcap
+        return logits
 
     def _run_layers(self, x, delta, fb, kv, state):
         par = self.par

@@ -25,6 +25,7 @@ class ParallelCtx:
     world: int = 1
     group: Optional[object] = None
     fused: Optional[object] = None          # parallel.fused.FusedComm when the peer-memory path is on
+    sharded: Optional[object] = None        # parallel.sharded.ShardedComm: row-sharded prefill (needs `fused` for its reduce-scatter)
     mode: str = "tp"                        # "tp": tensor/expert parallel, "pp": layer split
     _ctrl: Optional[object] = None          # gloo group for host-side control messages (step plans)
 

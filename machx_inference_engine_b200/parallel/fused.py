@@ -67,8 +67,10 @@ class FusedComm:
         rc = lib.mx_ipc_export(_vp(self._base), h)
         if rc != 0:
             raise RuntimeError(f"cudaIpcGetMemHandle failed ({rc})")
-        handles = [None] * self.world
-        dist.all_gather_object(handles, (bytes(h.raw), 0), group=par.group)
+        handles = [(bytes(h.raw), 0)]
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, (bytes(h.raw), 0), group=par.group)
         self.peer_ptrs = []
         self._opened = []
         for r, (hb, off) in enumerate(handles):
@@ -112,7 +114,9 @@ class FusedComm:
             d.gathered = True
 
     # ---- producers -----------------------------------------------------------------------
-    def linear_all_reduce(self, x: torch.Tensor, w: QuantWeight, bias: Optional[torch.Tensor]) -> ReducedDelta:
+    def linear_all_reduce(self, x: torch.Tensor, w: QuantWeight, bias: Optional[torch.Tensor], rs_rows: Optional[int] = None) -> ReducedDelta:
+        """``rs_rows``: force the reduce-scatter epilogue with that many rows per owner and leave the partials in the owners'
+        inboxes (the row-sharded prefill path consumes them with ``ShardedComm.norm``)."""
         M = x.shape[0]
         fmt, p0, p1, p2, p3 = K._planes(w)
         lib = _lib.cuda()
@@ -126,7 +130,7 @@ class FusedComm:
             bf16 = True
             if M * w.N * 2 > self.slot_bytes:
                 raise ValueError(f"fused all-reduce slot too small for [{M},{w.N}]")
-            rs = self._rs_rows(M)
+            rs = self._rs_rows(M) if rs_rows is None else int(rs_rows)
             if fmt != int(K.WFormat.BF16) and M >= K.DEQUANT_ONCE_MIN_M:
                 # quantised row-parallel weight: decode it once to bf16 (see ops.cuda.linear); the TMA-fed kernel is also the one
                 # whose epilogue stages its peer stores into 128-byte row segments

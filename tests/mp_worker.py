@@ -26,7 +26,7 @@ def main():
     if device == "cuda":
         dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(dev)
-        if comm in ("fused", "fused-rs") and par.world > 1:
+        if comm in ("fused", "fused-rs", "sharded") and par.world > 1:
             from machx_inference_engine_b200.parallel.fused import FusedComm
             par.fused = FusedComm.create(par, dev, max_tokens=1024, max_width=4096)
             if comm == "fused-rs":          # force the reduce-scatter form (normally from 4 ranks up) so that two GPUs exercise it
@@ -34,16 +34,25 @@ def main():
     else:
         dev = torch.device("cpu")
     cfg = preset(name)
-    model = build_model(cfg, dev, par, quant=quant, max_ctx=1024, gen_device="cpu")
-    eng = LLMEngine(model, EngineOptions(max_ctx=1024, max_batch_tokens=512, max_seqs=4))
+    n_pre = int(os.environ.get("MX_TEST_PREFILL", "200"))     # 1024 lets the sharded path take the chunk on 2, 4 and 8 ranks
+    ctx = max(1024, (n_pre + 8 + 255) // 128 * 128)
+    if comm == "sharded" and par.fused is not None:      # row-sharded prefill for chunks that divide over the ranks
+        from machx_inference_engine_b200.models.transformer import TransformerModel
+        from machx_inference_engine_b200.parallel.sharded import attach
+        attach(par, dev, cfg, ctx)
+        TransformerModel.SHARD_MIN_TOKENS = 128
+    model = build_model(cfg, dev, par, quant=quant, max_ctx=ctx, gen_device="cpu")
+    eng = LLMEngine(model, EngineOptions(max_ctx=ctx, max_batch_tokens=512, max_seqs=4))
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (37, 260, 9)]
     outs = eng.generate(prompts, SamplingParams(max_tokens=10))
     # teacher-forced logits of every position of one prompt: prefill chunk, then single-token steps (the decode kernels)
     from machx_inference_engine_b200.models.transformer import KV_BLOCK, ForwardBatch
     ids = prompts[1]
-    kv = model.new_kv_cache(6)
-    bt = torch.arange(1, 5, dtype=torch.int32, device=dev).unsqueeze(0)
+    ids = (ids * ((n_pre + 8) // len(ids) + 1))[: n_pre + 8]
+    n_blk = (n_pre + 8 + 127) // 128
+    kv = model.new_kv_cache(n_blk + 2)
+    bt = torch.arange(1, n_blk + 1, dtype=torch.int32, device=dev).unsqueeze(0)
 
     hybrid = getattr(model, "needs_state", False)
     st = model.new_state(2) if hybrid else None
@@ -57,7 +66,7 @@ def main():
             fb.state_slots, fb.state_slots_host, fb.start_host = torch.tensor([1], dtype=torch.int32, device=dev), [1], [lo]
             return model.forward(fb, kv, st).float().cpu()
         return model.forward(fb, kv).float().cpu()
-    logits = torch.cat([fwd(0, 200)] + [fwd(i, i + 1) for i in range(200, 208)])
+    logits = torch.cat([fwd(0, n_pre)] + [fwd(i, i + 1) for i in range(n_pre, n_pre + 8)])
     if comm == "pp":
         # a long single-sequence chunk goes through the stages as token micro-batches: same logits as one piece
         ids = (ids * 3)[:600]

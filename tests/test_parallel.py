@@ -130,3 +130,25 @@ def test_tp2_on_gpus_fused_and_nccl_match_single_gpu(name, quant):
     # reduce-scatter form of the fused collective (owner sums its rows and re-broadcasts them as bf16)
     rs = _run(2, name, quant, "cuda", "fused-rs")
     _close(one, rs, cos=0.995 if moe else 0.999, arg=0.93 if moe else 0.95)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("name,quant", [("tiny-gpt-oss", "mxfp4"), ("tiny-llama", "q8_0")])
+def test_row_sharded_prefill_on_gpus_matches_single_gpu(name, quant, world):
+    """The residual stream sharded by rows over 2, 4 and 8 ranks: all-gather -> GEMM, GEMM -> reduce-scatter and the expert
+    all-to-all (dispatch / return) against one GPU.  The 1024-token teacher-forced chunk divides over every world size; the
+    eight single-token steps after it take the replicated decode path on the same ranks."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    if name == "tiny-llama" and world > 4:
+        pytest.skip("four attention heads do not split over eight ranks")
+    os.environ["MX_TEST_PREFILL"] = "1024"
+    try:
+        one = _run(1, name, quant, "cuda")
+        sh = _run(world, name, quant, "cuda", "sharded")
+    finally:
+        del os.environ["MX_TEST_PREFILL"]
+    assert sh["world"] == world
+    moe = "llama" not in name
+    _close(one, sh, cos=0.995 if moe else 0.999, arg=0.93 if moe else 0.95)
