@@ -105,6 +105,9 @@ def main():
     ap.add_argument("--baseline-comm", action="store_true", help="plain NCCL all-reduce instead of the fused GEMM+all-reduce kernels")
     ap.add_argument("--pdl", type=int, default=-1, help="1/0: programmatic dependent launch for the decode chain (default: the library's setting)")
     ap.add_argument("--reduce-scatter", type=int, default=-1, help="ranks from which prefill collectives take the reduce-scatter form (default: the library's)")
+    ap.add_argument("--baseline", action="store_true",
+                    help="library baseline arm: the same model graph with plain PyTorch ops (cuBLAS bf16 GEMMs on decoded weights, ATen kernels) "
+                         "and NCCL all-reduce; no kernel of this engine runs")
     ap.add_argument("--replicated", action="store_true", help="keep the activations replicated on every rank (fused all-reduce) instead of the row-sharded prefill")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -124,6 +127,13 @@ def main():
         if os.environ.get("MX_BENCH_VERBOSE"):
             print(f"[bench +{time.time() - t_start:6.1f}s rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
 
+    if args.baseline:
+        from machx_inference_engine_b200 import ops as _ops
+        from machx_inference_engine_b200.models.transformer import MoEFFN
+        _ops.set_backend("torch")
+        MoEFFN.MXF4_TENSOR_CORE = False        # bf16 activations into the experts: what a library GEMM multiplies
+        args.baseline_comm = True
+        args.decode = min(args.decode, 16)     # the eager per-token loop of the baseline is slow; 16 tokens time it well enough
     par = init_from_env("cuda")
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -151,7 +161,14 @@ def main():
     torch.cuda.synchronize()
     build_s = time.time() - t0
     note(f"model built in {build_s:.1f}s")
-    eng = LLMEngine(model, EngineOptions(max_ctx=max_ctx, max_batch_tokens=max(P, 1), max_seqs=1, enable_prefix_cache=False))
+    if args.baseline:
+        # decoded bf16 weights stay resident as far as memory allows (all of them from two GPUs up for the 120b shape); the rest
+        # is decoded per call
+        from machx_inference_engine_b200.ops import ref as _ref
+        free, _ = torch.cuda.mem_get_info(dev)
+        _ref.set_matmul_dtype(torch.bfloat16, dense_budget_bytes=max(0, free - (24 << 30)))
+    eng = LLMEngine(model, EngineOptions(max_ctx=max_ctx, max_batch_tokens=max(P, 1), max_seqs=1, enable_prefix_cache=False,
+                                         cuda_graphs=not args.baseline, prefill_graphs=not args.baseline))
 
     g = torch.Generator().manual_seed(1234)
     n_prompts = args.warmup + args.steps + 4
@@ -238,14 +255,15 @@ def main():
             "vs_baseline": round(value / base, 2) if base else None, "dtype": "bf16", "data": "synthetic (random-init weights, random token ids)",
             "config": {"model": args.model, "global_batch": 1, "seq_len": P, "decode_tokens": D, "weights": quant,
                        "parallelism": f"tp{args.gpus}+ep{args.gpus}" if args.gpus > 1 else "tp1",
-                       "comm": ("nccl-baseline" if args.baseline_comm else "fused-gemm-allreduce") if args.gpus > 1 else "none",
+                       "comm": ("nccl-baseline" if args.baseline_comm else ("fused-gemm-allreduce" if par.sharded is None else "row-sharded: all-gather->GEMM, GEMM->reduce-scatter, expert all-to-all")) if args.gpus > 1 else "none",
+                       "compute": "pytorch ops (cuBLAS bf16, ATen), no engine kernel" if args.baseline else "engine kernels (sm_100a)",
                        "l2": "inputs (weights) larger than L2; no flush", "model_build_s": round(build_s, 1),
                        "weight_gb_per_gpu": round(model.weight_bytes() / 1e9, 2)},
             "decode_tok_s": round(nd / (dec_ms / 1e3), 1), "decode_ms_per_token": round(dec_ms / max(nd, 1), 3),
             "decode_vs_baseline": round(nd / (dec_ms / 1e3) / BASELINE_DECODE_TOK_S[args.model], 2) if args.model in BASELINE_DECODE_TOK_S else None,
             "e2e": {"value": round(P / (e2e_ms / 1e3), 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "decode_tok_s": round(nd / (dec_wall_ms / 1e3), 1)},
-            "gpu_launches": int(launches), "clocks": clocks, "impl": "ours",
+            "gpu_launches": 0 if args.baseline else int(launches), "clocks": clocks, "impl": "library-baseline" if args.baseline else "ours",
         }
         print(json.dumps(line))
     sys.stdout.flush()

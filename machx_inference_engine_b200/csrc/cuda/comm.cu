@@ -13,15 +13,21 @@
 
 namespace mx {
 
-// Bounded wait until every source's flag reached `seq`.  One thread per CTA polls, the CTA follows.
+// How long a consumer waits for its peers' flags, in SM clock cycles (about one second by default); mx_set_wait_limit_cycles
+// lowers it for the test that lets a wait run out.
+__device__ long long g_wait_limit_cycles = 2000000000ll;
+
+// Bounded wait until every source's flag reached `seq`.  One thread per CTA polls (with a short sleep between polls, so that
+// thousands of waiting CTAs do not saturate the path the flag arrives on), the CTA follows.
 __device__ __forceinline__ bool wait_all_flags(const int* flags, int world, int seq, int* status) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
     int ok = 1;
-    const long long t0 = clock64();
+    const long long t0 = clock64(), limit = g_wait_limit_cycles;
     for (int r = 0; r < world; ++r) {
       while (ld_acquire_sys(flags + r) - seq < 0) {
-        if (clock64() - t0 > 2000000000ll) { atomicCAS(status, 0, ERR_PEER_FLAG_TIMEOUT); ok = 0; break; }
+        __nanosleep(32);
+        if (clock64() - t0 > limit) { atomicCAS(status, 0, ERR_PEER_FLAG_TIMEOUT); ok = 0; break; }
       }
       if (!ok) break;
     }
@@ -180,6 +186,12 @@ using namespace mx;
 
 // The inbox is a dedicated cudaMalloc allocation (IPC handles describe whole allocations), zero-filled
 // so that flags and sequence numbers start at 0.
+// Time limit of the consumers' flag waits on the current device, in SM cycles (default 2e9, about a second).
+MX_HOST_API int mx_set_wait_limit_cycles(long long cycles) {
+  if (cycles < 1000) return -1;
+  return (int)cudaMemcpyToSymbol(g_wait_limit_cycles, &cycles, sizeof cycles);
+}
+
 MX_HOST_API void* mx_raw_alloc(long long bytes) {
   void* p = nullptr;
   if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) return nullptr;

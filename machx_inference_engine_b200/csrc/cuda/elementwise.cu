@@ -96,6 +96,57 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(float* __restrict__ x, con
   }
 }
 
+// Residual add + RMSNorm whose delta is the expert combine: delta[t] = sum_k cw[t,k] * yp[pair_to_packed[t*K+k]] (slot order,
+// pairs with a negative position contribute nothing), so that the weighted sum of the expert outputs never exists as a tensor.
+__global__ void __launch_bounds__(256) rmsnorm_combine_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ yp, const int* __restrict__ pair_to_packed,
+                                                              const float* __restrict__ cw, int K, const float* __restrict__ w,
+                                                              __nv_bfloat16* __restrict__ out, float eps, int H, int one_plus_w, float delta_scale) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  float* xr = x + (size_t)t * H;
+  __shared__ float red[8];
+  __shared__ int s_pos[32];
+  __shared__ float s_w[32];
+  if (threadIdx.x < K) {
+    s_pos[threadIdx.x] = pair_to_packed[(size_t)t * K + threadIdx.x];
+    s_w[threadIdx.x] = cw[(size_t)t * K + threadIdx.x];
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(xr + i);
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < K; ++k) {
+      const int pos = s_pos[k];
+      if (pos < 0) continue;
+      const uint2 yv = *reinterpret_cast<const uint2*>(yp + (size_t)pos * H + i);
+      const float ww = s_w[k];
+      d.x = fmaf(ww, bf16_lo(yv.x), d.x); d.y = fmaf(ww, bf16_hi(yv.x), d.y);
+      d.z = fmaf(ww, bf16_lo(yv.y), d.z); d.w = fmaf(ww, bf16_hi(yv.y), d.w);
+    }
+    v.x += d.x * delta_scale; v.y += d.y * delta_scale; v.z += d.z * delta_scale; v.w += d.w * delta_scale;
+    *reinterpret_cast<float4*>(xr + i) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) red[0] = rsqrtf(v / H + eps);
+  }
+  __syncthreads();
+  const float inv = red[0];
+  if (!out) return;
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(xr + i);
+    float4 g = *reinterpret_cast<const float4*>(w + i);
+    if (one_plus_w) { g.x += 1.f; g.y += 1.f; g.z += 1.f; g.w += 1.f; }
+    *reinterpret_cast<uint2*>(out + (size_t)t * H + i) = make_uint2(pack_bf16(v.x * inv * g.x, v.y * inv * g.y), pack_bf16(v.z * inv * g.z, v.w * inv * g.w));
+  }
+}
+
 // ------------------------------------------------------------------ qkv_post
 struct QkvPostParams {
   const __nv_bfloat16* qkv;   // [T][q_cols + 2*n_kv*hd]
@@ -311,6 +362,16 @@ MX_HOST_API int mx_rmsnorm(float* x, const void* delta, int delta_is_f32, const 
   if (H % 4) return -107;
   if (delta_is_f32) launch_pdl(rmsnorm_kernel<float>, dim3(T), dim3(256), 0, st, x, (const float*)delta, dbias, w, (__nv_bfloat16*)out_bf16, eps, H, one_plus_w, delta_scale, write_x);
   else launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, st, x, (const __nv_bfloat16*)delta, dbias, w, (__nv_bfloat16*)out_bf16, eps, H, one_plus_w, delta_scale, write_x);
+  return (int)cudaGetLastError();
+}
+
+// x[t] += delta_scale * sum_k cw[t,k] * yp[pair_to_packed[t*K+k]];  out = rmsnorm(x) * w   (K <= 32)
+MX_HOST_API int mx_rmsnorm_combine(float* x, const void* yp, const int* pair_to_packed, const float* cw, int K, const float* w, void* out_bf16,
+                                   float eps, int T, int H, int one_plus_w, float delta_scale, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 4 || K > 32 || K < 1) return -107;
+  launch_pdl(rmsnorm_combine_kernel, dim3(T), dim3(256), 0, st, x, (const __nv_bfloat16*)yp, pair_to_packed, cw, K, w, (__nv_bfloat16*)out_bf16, eps, H,
+             one_plus_w, delta_scale);
   return (int)cudaGetLastError();
 }
 

@@ -24,6 +24,7 @@
 // and the MXFP4 GEMV family of src/ops/gemv_mxfp4.cpp:94-323 for the expert projections.
 #include "common.cuh"
 #include "host_util.h"
+#include "moe_route.cuh"
 
 #include <cuda_fp8.h>
 
@@ -405,6 +406,53 @@ __global__ void __launch_bounds__(128) moe_quant_kernel(const __nv_bfloat16* __r
   }
 }
 
+// Decode (a handful of tokens): routing and quantisation in one launch.  One CTA per token: warp 0 picks the top-k experts while
+// all threads round the token's row to MXFP8; the row is then written once per (token, slot) pair, each pair being its own
+// one-row tile of the grouped GEMM (pair mode of mx_mxf4_gemm).
+__global__ void __launch_bounds__(128) moe_route_quant_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int E, int Kt, int renorm,
+                                                              int* __restrict__ topk_idx, float* __restrict__ topk_w, const __nv_bfloat16* __restrict__ x,
+                                                              int ldx, int K, int KB, int max_tiles, uint8_t* __restrict__ xq, uint8_t* __restrict__ sfx) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  if ((threadIdx.x >> 5) == 0) route_token_warp(logits, bias, t, E, Kt, renorm, topk_idx, topk_w);
+  const int Kp = KB * XT_K;
+  for (int blk = threadIdx.x; blk < KB * 4; blk += blockDim.x) {
+    const int k0 = blk * 32;
+    float v[32];
+    float amax = 0.f;
+    if (k0 < K) {
+      const uint4* s = reinterpret_cast<const uint4*>(x + (size_t)t * ldx + k0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 raw = s[i];
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          v[8 * i + 2 * jj] = bf16_lo(w[jj]);
+          v[8 * i + 2 * jj + 1] = bf16_hi(w[jj]);
+          amax = fmaxf(amax, fmaxf(fabsf(v[8 * i + 2 * jj]), fabsf(v[8 * i + 2 * jj + 1])));
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = 0.f;
+    }
+    float inv;
+    const uint32_t eb = mxfp8_scale(amax, &inv);
+    const uint4 lo = make_uint4(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv), e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv),
+                                e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv), e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv));
+    const uint4 hi = make_uint4(e4m3x4(v[16] * inv, v[17] * inv, v[18] * inv, v[19] * inv), e4m3x4(v[20] * inv, v[21] * inv, v[22] * inv, v[23] * inv),
+                                e4m3x4(v[24] * inv, v[25] * inv, v[26] * inv, v[27] * inv), e4m3x4(v[28] * inv, v[29] * inv, v[30] * inv, v[31] * inv));
+    for (int k = 0; k < Kt; ++k) {
+      const size_t r = (size_t)t * Kt + k;            // pair = tile r, row 0 of its atom
+      uint4* d = reinterpret_cast<uint4*>(xq + r * Kp + k0);
+      d[0] = lo;
+      d[1] = hi;
+      sfx[((size_t)(blk >> 2) * max_tiles + r) * SF_ATOM + sf_atom_offset(0, blk & 3)] = (uint8_t)eb;
+    }
+  }
+}
+
 typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -455,6 +503,18 @@ MX_HOST_API int mx_moe_quant(const void* x, int ldx, const int* src_index, int x
   const int KB = (K + XT_K - 1) / XT_K;
   launch_pdl(moe_quant_kernel, dim3(rows), dim3(128), 0, st, (const __nv_bfloat16*)x, ldx, src_index, x_div, row_limit, K, KB, max_tiles,
              rows_per_tile, (uint8_t*)xq, (uint8_t*)sfx);
+  return (int)cudaGetLastError();
+}
+
+// Router top-k (see mx_moe_route) and MXFP8 quantisation of T token rows in pair mode: xq [T*Kt][KB*128], sfx [KB][max_tiles][512]
+// with max_tiles >= T*Kt; pair t*Kt+k is tile t*Kt+k.
+MX_HOST_API int mx_moe_route_quant(const float* logits, const float* bias, int T, int E, int Kt, int renorm, int* topk_idx, float* topk_w,
+                                   const void* x, int ldx, int K, int max_tiles, void* xq, void* sfx, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (E > 1024 || Kt > 32 || Kt > E || K % 32 || ldx % 8 || max_tiles < T * Kt) return -120;
+  const int KB = (K + XT_K - 1) / XT_K;
+  launch_pdl(moe_route_quant_kernel, dim3(T), dim3(128), 0, st, logits, bias, E, Kt, renorm, topk_idx, topk_w, (const __nv_bfloat16*)x, ldx, K, KB,
+             max_tiles, (uint8_t*)xq, (uint8_t*)sfx);
   return (int)cudaGetLastError();
 }
 

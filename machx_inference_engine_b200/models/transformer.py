@@ -386,16 +386,27 @@ class MoEFFN:
         when it differs from the experts' (Gemma-4)."""
         T = h.shape[0]
         logits = self.router(h if router_h is None else router_h, out_f32=True)
-        idx, w = ops.moe_route(logits, self.router_bias, self.K, True)
+        pre = None
+        if self.mx is not None and T <= self.MXF4_PAIR_MAX_TOKENS:
+            # decode: routing and the MXFP8 rounding of the token rows share one launch
+            from ..ops.cuda import moe_route_quant
+            idx, w, xq, sfx = moe_route_quant(logits, self.router_bias, self.K, h)
+            pre = (xq, sfx)
+        else:
+            idx, w = ops.moe_route(logits, self.router_bias, self.K, True)
         if self.expert_scale is not None:
             w = w * self.expert_scale[idx.long()]
         local = self.e_hi - self.e_lo
         # expert parallelism on the peer-memory path: the combine writes its partial into every rank's inbox itself
         fuse_push = self.reduce and par.fused is not None and h.is_cuda and self.shared is None
         if self.mx is not None:
-            y, p2p = self._mx_experts(h, idx)
+            y, p2p = self._mx_experts(h, idx, pre)
             if fuse_push:
                 return par.fused.moe_combine_push(y, p2p, w)
+            if self.shared is None and not self.reduce and self.K <= 32:
+                # single rank: the weighted sum is formed inside the residual add + norm that consumes it
+                from ..ops.cuda import CombineDelta
+                return CombineDelta(y, p2p, w.contiguous())
             out = ops.moe_combine(y, ops.ref.MoePacking(None, None, None, p2p, None, None, y.shape[0], self.K), w)
         elif self.a8:
             # CPU restatement of the block-scaled path: same rounding points, fp32 math
@@ -445,8 +456,9 @@ class MoEFFN:
         return out
 
 
-def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor):
-    """Expert projections on the block-scaled MXFP4 kernel.  Returns (y bf16 [rows, H], pair_to_packed int32 [T*K])."""
+def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor, pre=None):
+    """Expert projections on the block-scaled MXFP4 kernel.  Returns (y bf16 [rows, H], pair_to_packed int32 [T*K]).  ``pre``: the
+    pair-mode (xq, sfx) when the router launch has already quantised the rows."""
     from ..ops import cuda as K_
     gate_up, down = self.mx
     T = h.shape[0]
@@ -455,7 +467,7 @@ def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor):
         # decode: pair i = (token i // K, slot i % K) is tile i with one live row; no sort, no gather
         n = T * self.K
         te = idx.reshape(-1)
-        xq, sfx = K_.moe_quant(h, n, n, 1, x_div=self.K)
+        xq, sfx = pre if pre is not None else K_.moe_quant(h, n, n, 1, x_div=self.K)
         aq, sfa = K_.mxf4_gemm(gate_up, xq, sfx, te, n, 1, default_valid=1, bias0=self.g_bias, bias1=self.u_bias, act=self.act, **ep)
         y = K_.mxf4_gemm(down, aq, sfa, te, n, 1, default_valid=1, bias0=self.down_bias, zero_out=self.reduce, **ep)
         key = (T, h.device)
@@ -631,6 +643,8 @@ class TransformerModel:
             h2 = self._norm(x, L["ffn_norm"], a)
             delta = L["moe"](h2, par) if "moe" in L else L["ffn"](h2, par)
             if self.tap is not None:                 # per-layer dump hook of the parity tools (single rank, eager)
+                if not isinstance(delta, torch.Tensor) and hasattr(delta, "materialize"):
+                    delta = delta.materialize()
                 self.tap(li, a, delta, x)
         return x, delta
 
@@ -714,6 +728,9 @@ class TransformerModel:
         """Residual add + RMSNorm; a delta that still lives as per-rank partials in the collective inbox is summed here."""
         c = self.cfg
         if delta is not None and not isinstance(delta, torch.Tensor):
+            if hasattr(delta, "pair_to_packed"):       # an expert combine that has not been formed (ops.cuda.CombineDelta)
+                from ..ops.cuda import rmsnorm_combine
+                return rmsnorm_combine(x, w, c.rms_eps, delta, one_plus_w=self.one_plus_w, delta_scale=c.residual_scale)
             return self.par.fused.rmsnorm(x, w, c.rms_eps, delta, one_plus_w=self.one_plus_w, delta_scale=c.residual_scale)
         return ops.rmsnorm(x, w, c.rms_eps, delta=delta, one_plus_w=self.one_plus_w, delta_scale=c.residual_scale)
 

@@ -19,6 +19,18 @@ _NAMES = [
 ]
 
 
+_BACKEND = ["auto"]
+
+
+def set_backend(name: str) -> None:
+    """"auto": CUDA tensors run the engine's kernels, CPU tensors the PyTorch oracle.  "torch": every op runs the PyTorch
+    restatement wherever its tensors live -- on a GPU that is cuBLAS / ATen kernels only, the library baseline the benchmarks
+    compare the engine's own kernels with."""
+    if name not in ("auto", "torch"):
+        raise ValueError(name)
+    _BACKEND[0] = name
+
+
 def _first_tensor(args, kwargs):
     import torch
     for a in list(args) + list(kwargs.values()):
@@ -36,7 +48,7 @@ def _make(name):
 
     @functools.wraps(ref_fn)
     def op(*args, **kwargs):
-        if _first_tensor(args, kwargs).is_cuda:
+        if _BACKEND[0] == "auto" and _first_tensor(args, kwargs).is_cuda:
             from . import cuda
             fn = getattr(cuda, name)
             if _prof.enabled:
@@ -53,5 +65,5 @@ def _make(name):
 for _n in _NAMES:
     globals()[_n] = _make(_n)
 
-__all__ = _NAMES + ["QuantWeight", "WFormat", "from_dense", "from_ggml", "MoePacking", "moe_max_rows", "ACT_NONE", "ACT_SWIGLU",
+__all__ = _NAMES + ["set_backend", "QuantWeight", "WFormat", "from_dense", "from_ggml", "MoePacking", "moe_max_rows", "ACT_NONE", "ACT_SWIGLU",
                     "ACT_SWIGLU_OAI", "ACT_GEGLU", "MOE_TILE"]

@@ -85,6 +85,21 @@ def sm_count() -> int:
     return _sm_count
 
 
+def _profiled(name):
+    """The ops that only exist on the GPU report to the per-op profiler themselves (the CPU/GPU dispatcher wraps the others)."""
+    def deco(fn):
+        import functools
+        from ..utils.profiler import profiler as _prof
+
+        @functools.wraps(fn)
+        def wrapped(*args, **kwargs):
+            if _prof.enabled:
+                return _prof.record(name, fn, args, kwargs)
+            return fn(*args, **kwargs)
+        return wrapped
+    return deco
+
+
 # ------------------------------------------------------------------ elementwise
 def embed(w: QuantWeight, ids, scale: float = 1.0):
     T = ids.numel()
@@ -103,6 +118,33 @@ def rmsnorm(x, w, eps, delta=None, dbias=None, one_plus_w=False, delta_scale=1.0
         assert delta.is_contiguous() and delta.shape == x.shape
     _check(_lib.cuda().mx_rmsnorm(_p(x), _p(delta), is_f32, _p(dbias), _p(w), _p(out), C.c_float(eps), T, H, int(one_plus_w),
                                   C.c_float(delta_scale), int(write_x), _stream()), "rmsnorm")
+    _count()
+    return out
+
+
+class CombineDelta:
+    """The weighted sum of expert outputs that has not been formed: ``y`` [rows, H] bf16, the packed position of every (token, slot)
+    pair (negative = not on this rank) and the routing weights [T, K].  ``rmsnorm_combine`` folds it into the residual inside the
+    next norm; ``materialize`` forms it."""
+
+    def __init__(self, y, pair_to_packed, w):
+        self.y, self.pair_to_packed, self.w = y, pair_to_packed, w
+        self.shape = (w.shape[0], y.shape[1])
+
+    def materialize(self):
+        return moe_combine(self.y, MoePacking(None, None, None, self.pair_to_packed, None, None, self.y.shape[0], self.w.shape[1]), self.w)
+
+    def index_select(self, dim, rows):
+        assert dim == 0
+        return self.materialize().index_select(0, rows)
+
+
+@_profiled("rmsnorm_combine")
+def rmsnorm_combine(x, w, eps, d: "CombineDelta", one_plus_w=False, delta_scale=1.0, want_out=True):
+    T, H = x.shape
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if want_out else None
+    _check(_lib.cuda().mx_rmsnorm_combine(_p(x), _p(d.y), _p(d.pair_to_packed), _p(d.w), d.w.shape[1], _p(w), _p(out), C.c_float(eps), T, H,
+                                          int(one_plus_w), C.c_float(delta_scale), _stream()), "rmsnorm_combine")
     _count()
     return out
 
@@ -297,15 +339,15 @@ _attn_scratch: dict = {}
 TC_PREFILL_MIN_Q = 64      # query segments at least this long take the tensor-core kernel
 
 
-def attention_prefill_tc(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None):
-    """tcgen05 FlashAttention (head_dim 64 / 128, page size 128)."""
+def attention_prefill_tc(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0):
+    """tcgen05 FlashAttention (head_dim 64 / 128 / 256, page size 128, optional logit soft-cap)."""
     Tq, n_q, hd = q.shape
     n_kv, bs = k_cache.shape[1], k_cache.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
     out = torch.empty(Tq, n_q, hd, dtype=torch.bfloat16, device=q.device)
     _check(_lib.cuda().mx_attention_prefill_tc(_p(q), _p(k_cache), _p(v_cache), _p(block_table), _p(seq_lens), _p(cu_q), _p(sinks), _p(out),
                                                seq_lens.numel(), Tq, int(max_q_len), n_q, n_kv, hd, block_table.shape[1], k_cache.shape[0], bs,
-                                               int(window), C.c_float(scale), _stream()), "attention_prefill_tc")
+                                               int(window), C.c_float(scale), C.c_float(softcap or 0.0), _stream()), "attention_prefill_tc")
     _count()
     return out
 
@@ -343,11 +385,12 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
     B = seq_lens.numel()
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
     assert (k_cache.dtype == torch.int8) == (kv_scales is not None)
-    if max_q_len >= TC_PREFILL_MIN_Q and hd in (64, 128) and bs == 128 and not softcap and n_splits is None:
+    if max_q_len >= TC_PREFILL_MIN_Q and hd in (64, 128, 256) and bs == 128 and n_splits is None:
         if kv_scales is not None:       # the tensor-core kernel reads bf16 pages: expand this batch's pages first
             dk, dv, table = _dequant_pages(k_cache, v_cache, kv_scales, block_table, seq_lens, max_kv_len)
-            return attention_prefill_tc(q, dk, dv, table, seq_lens, cu_q, max_q_len, sinks=sinks, window=window, scale=scale)
-        return attention_prefill_tc(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=sinks, window=window, scale=scale)
+            return attention_prefill_tc(q, dk, dv, table, seq_lens, cu_q, max_q_len, sinks=sinks, window=window, scale=scale, softcap=softcap)
+        return attention_prefill_tc(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=sinks, window=window, scale=scale,
+                                    softcap=softcap)
     if n_splits is None:
         # decode-sized problems: split the KV range so that ~2 CTAs per SM exist
         ctas = B * n_kv * max(1, (max_q_len * (n_q // n_kv) + 31) // 32)
@@ -409,21 +452,6 @@ def moe_pack(topk_idx, E, e_lo=0, e_hi=None, tile=MOE_TILE):
     return MoePacking(counts, seg, packed_token, pair_to_packed, tile_expert, num_tiles, max_rows, K, tile_valid)
 
 
-def _profiled(name):
-    """The ops that only exist on the GPU report to the per-op profiler themselves (the CPU/GPU dispatcher wraps the others)."""
-    def deco(fn):
-        import functools
-        from ..utils.profiler import profiler as _prof
-
-        @functools.wraps(fn)
-        def wrapped(*args, **kwargs):
-            if _prof.enabled:
-                return _prof.record(name, fn, args, kwargs)
-            return fn(*args, **kwargs)
-        return wrapped
-    return deco
-
-
 @_profiled("moe_quant")
 def moe_quant(x, rows, max_tiles, rows_per_tile, src_index=None, x_div=1, row_limit=None):
     """bf16 rows -> MXFP8 rows + scale atoms for :func:`mxf4_gemm` (see ``mx_moe_quant``).  Returns (xq [rows, KB*128] uint8,
@@ -437,6 +465,23 @@ def moe_quant(x, rows, max_tiles, rows_per_tile, src_index=None, x_div=1, row_li
                                     int(rows_per_tile), _p(xq), _p(sfx), _stream()), "moe_quant")
     _count()
     return xq, sfx
+
+
+@_profiled("moe_route_quant")
+def moe_route_quant(logits, bias, k, x, renorm=True):
+    """Decode: router top-k and pair-mode MXFP8 quantisation of the T rows of ``x`` in one launch.  Returns (idx, w, xq, sfx)."""
+    T, E = logits.shape
+    Kd = x.shape[1]
+    KB = (Kd + 127) // 128
+    n = T * k
+    idx = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    xq = torch.empty(n, KB * 128, dtype=torch.uint8, device=x.device)
+    sfx = torch.empty(KB, n, 512, dtype=torch.uint8, device=x.device)
+    _check(_lib.cuda().mx_moe_route_quant(_p(logits), _p(bias), T, E, k, int(renorm), _p(idx), _p(w), _p(x), x.stride(0), Kd, n, _p(xq), _p(sfx),
+                                          _stream()), "moe_route_quant")
+    _count()
+    return idx, w, xq, sfx
 
 
 @_profiled("mxf4_gemm")

@@ -18,15 +18,59 @@ ACT_NONE, ACT_SWIGLU, ACT_SWIGLU_OAI, ACT_GEGLU = 0, 1, 2, 3
 MOE_TILE = 128
 
 
-def _dense(w: QuantWeight) -> torch.Tensor:
+# Matmul dtype of this module.  fp32 = the numerical oracle of the tests.  The library-baseline arm of the benchmarks (plain PyTorch
+# = cuBLAS GEMMs + NCCL on the same model, no kernel of this engine) switches it to bf16 so that its GEMMs run on the tensor cores.
+_MM_DTYPE = torch.float32
+_DENSE_BUDGET = [None]          # bytes of decoded weights that may stay resident (None = unlimited); what does not fit is decoded per call
+
+
+def set_matmul_dtype(dtype, dense_budget_bytes=None) -> None:
+    global _MM_DTYPE
+    _MM_DTYPE = dtype
+    _DENSE_BUDGET[0] = dense_budget_bytes
+
+
+def _mm(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
+    """a [M,K] @ b_t [N,K]^T in the module's matmul dtype, fp32 result."""
+    if _MM_DTYPE == torch.float32:
+        return a.to(torch.float32) @ b_t.to(torch.float32).t()
+    return (a.to(_MM_DTYPE) @ b_t.to(_MM_DTYPE).t()).to(torch.float32)
+
+
+class _LazyBank:
+    """Expert bank decoded one expert at a time (and kept while the residency budget lasts)."""
+
+    def __init__(self, w: QuantWeight):
+        self.w, self.cache = w, {}
+
+    def __getitem__(self, e):
+        if isinstance(e, torch.Tensor):
+            return torch.stack([self[int(i)] for i in e.tolist()])
+        d = self.cache.get(e)
+        if d is None:
+            d = self.w.slice_experts(e, e + 1).dequantize(_MM_DTYPE)[0]
+            nbytes = d.numel() * d.element_size()
+            if _DENSE_BUDGET[0] is None or _DENSE_BUDGET[0] >= nbytes:
+                self.cache[e] = d
+                if _DENSE_BUDGET[0] is not None:
+                    _DENSE_BUDGET[0] -= nbytes
+        return d
+
+
+def _dense(w: QuantWeight):
     if w._dense_cache is None:
-        w._dense_cache = w.dequantize(torch.float32)
+        if _DENSE_BUDGET[0] is not None and w.E > 1:
+            w._dense_cache = _LazyBank(w)
+        else:
+            w._dense_cache = w.dequantize(_MM_DTYPE)
+            if _DENSE_BUDGET[0] is not None:
+                _DENSE_BUDGET[0] -= w._dense_cache.numel() * w._dense_cache.element_size()
     return w._dense_cache
 
 
 def embed(w: QuantWeight, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     tbl = _dense(w)[0]
-    return tbl[ids.long().clamp(0, w.N - 1)] * scale
+    return tbl[ids.long().clamp(0, w.N - 1)].to(torch.float32) * scale
 
 
 def rmsnorm(x, w, eps, delta=None, dbias=None, one_plus_w=False, delta_scale=1.0, write_x=True, want_out=True):
@@ -69,7 +113,7 @@ def glu(x, act, alpha=1.702, limit=7.0):
 
 
 def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None):
-    y = x.to(torch.float32) @ _dense(w)[0].t()
+    y = _mm(x, _dense(w)[0])
     if bias is not None:
         y = y + bias
     if act != ACT_NONE:
@@ -91,7 +135,7 @@ def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=AC
     te = tile_expert[:nt].tolist()
     for t, e in enumerate(te):
         rows = slice(t * MOE_TILE, min((t + 1) * MOE_TILE, P))
-        y = xp[rows].to(torch.float32) @ W[e].t()
+        y = _mm(xp[rows], W[e])
         if bias is not None:
             y = y + bias[e]
         if act != ACT_NONE:
@@ -111,7 +155,7 @@ def expert_gemv(x, w: QuantWeight, slot_expert, x_div=1, bias=None, act=ACT_NONE
     se = slot_expert.long() - e_lo
     owned = (se >= 0) & (se < w.E)
     se = se.clamp(0, w.E - 1)
-    y = torch.einsum("sk,snk->sn", xe, W[se])
+    y = torch.einsum("sk,snk->sn", xe.to(_MM_DTYPE), W[se]).to(torch.float32)
     if bias is not None:
         y = y + bias[se]
     if act != ACT_NONE:
@@ -198,7 +242,7 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
         qq = q[q0:q1].to(torch.float32) * scale                                 # [t, n_q, hd]
         Kh = K.repeat_interleave(gqa, dim=0)
         Vh = V.repeat_interleave(gqa, dim=0)
-        s = torch.einsum("thd,hkd->htk", qq, Kh)
+        s = torch.einsum("thd,hkd->htk", qq.to(_MM_DTYPE), Kh.to(_MM_DTYPE)).to(torch.float32)
         if softcap and softcap > 0:
             s = softcap * torch.tanh(s / softcap)
         qpos = torch.arange(L - (q1 - q0), L, device=q.device).unsqueeze(-1)
@@ -212,7 +256,7 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
             p = torch.softmax(torch.cat([s, sk], dim=-1), dim=-1)[..., :-1]
         else:
             p = torch.softmax(s, dim=-1)
-        out[q0:q1] = torch.einsum("htk,hkd->thd", p, Vh)
+        out[q0:q1] = torch.einsum("htk,hkd->thd", p.to(_MM_DTYPE), Vh.to(_MM_DTYPE)).to(torch.float32)
     return out.to(torch.bfloat16)
 
 
@@ -411,7 +455,7 @@ def expert_group_gemv(x, w: QuantWeight, pk: MoePacking, x_index=None, bias=None
             continue
         rows = torch.arange(s0, s0 + c, device=x.device)
         xin = xf[x_index[rows].long()] if x_index is not None else xf[rows]
-        y = xin @ W[el].T
+        y = _mm(xin, W[el])
         if bias is not None:
             y = y + bias[el]
         if act != ACT_NONE:

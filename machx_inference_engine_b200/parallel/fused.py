@@ -114,6 +114,7 @@ class FusedComm:
             d.gathered = True
 
     # ---- producers -----------------------------------------------------------------------
+    @K._profiled("gemm_allreduce")
     def linear_all_reduce(self, x: torch.Tensor, w: QuantWeight, bias: Optional[torch.Tensor], rs_rows: Optional[int] = None) -> ReducedDelta:
         """``rs_rows``: force the reduce-scatter epilogue with that many rows per owner and leave the partials in the owners'
         inboxes (the row-sharded prefill path consumes them with ``ShardedComm.norm``)."""
@@ -154,6 +155,7 @@ class FusedComm:
         K._count()
         return ReducedDelta(self, t.shape[0], t.shape[1], t.dtype == torch.bfloat16)
 
+    @K._profiled("moe_combine_push")
     def moe_combine_push(self, yp: torch.Tensor, pair_to_packed: torch.Tensor, w: torch.Tensor) -> ReducedDelta:
         """MoE combine fused with the expert-parallel all-reduce: sum_k w[t,k] * yp[pos(t,k)] goes straight into every rank's
         inbox (fp32 for decode-sized batches, bf16 for prefill, like the row-parallel GEMM partials)."""
@@ -176,6 +178,7 @@ class FusedComm:
         K._count()
         return out
 
+    @K._profiled("rmsnorm_reduce")
     def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, d: ReducedDelta, one_plus_w: bool = False, delta_scale: float = 1.0,
                 want_out: bool = True) -> Optional[torch.Tensor]:
         T, H = x.shape

@@ -135,6 +135,7 @@ class ShardedComm:
         return self.rank * R, R
 
     # ------------------------------------------------------------------ norm (+ reduce-scatter consumer, + all-gather producer)
+    @K._profiled("shard_norm")
     def norm(self, x: torch.Tensor, w: torch.Tensor, eps: float, T: int, delta=None, one_plus_w: bool = False, delta_scale: float = 1.0,
              want_local: bool = False, gather: bool = False):
         """``x`` [R, H] fp32 += delta; returns (local bf16 rows or None, gather-buffer index or None).  ``delta``: None, a local
@@ -164,6 +165,7 @@ class ShardedComm:
         return out, (gbuf if gather else None)
 
     # ------------------------------------------------------------------ all-gather -> GEMM
+    @K._profiled("gemm_gathered")
     def linear_gathered(self, lin, T: int, gbuf: int, out_f32: bool = False) -> torch.Tensor:
         """Column-parallel projection of the gathered rows [T, H] (gather buffer ``gbuf``); ``lin`` is a Linear or a MultiLinear."""
         parts = getattr(lin, "parts", None) or [lin]
@@ -191,6 +193,7 @@ class ShardedComm:
         return out
 
     # ------------------------------------------------------------------ expert all-to-all
+    @K._profiled("moe_dispatch")
     def dispatch(self, h: torch.Tensor, idx: torch.Tensor):
         """Routes this rank's rows ``h`` [R, H] (bf16) to the ranks that own their top-k experts ``idx`` [R, K].  Returns
         (xq view, sfx scale atoms, DispatchPlan): the inputs of the grouped expert GEMM over this rank's own experts."""
@@ -212,6 +215,7 @@ class ShardedComm:
         K._count(3)
         return self.xq_view, sfx, DispatchPlan(pair_pos, tile_expert, tile_valid, num_tiles, self.max_tiles)
 
+    @K._profiled("moe_return+combine")
     def combine(self, y: torch.Tensor, plan: DispatchPlan, w: torch.Tensor) -> torch.Tensor:
         """Sends every expert output row ``y`` [packed rows, H] (bf16) back to its token's owner and returns this rank's
         weighted sums [R, H] fp32."""

@@ -467,20 +467,39 @@ def test_attention_int8_cache(hd, n_q, n_kv, window):
         assert rel_err(got, want) < 1.5e-2, max_kv
 
 
-@pytest.mark.parametrize("hd,n_q,n_kv", [(64, 16, 2), (128, 8, 2)])
+@pytest.mark.parametrize("hd,n_q,n_kv", [(64, 16, 2), (128, 8, 2), (256, 4, 2)])
 @pytest.mark.parametrize("window", [0, 128])
-@pytest.mark.parametrize("use_sinks", [False, True])
-def test_attention_prefill_tensor_core(hd, n_q, n_kv, window, use_sinks):
+@pytest.mark.parametrize("use_sinks,softcap", [(False, 0.0), (True, 0.0), (False, 30.0)])
+def test_attention_prefill_tensor_core(hd, n_q, n_kv, window, use_sinks, softcap):
     # tcgen05 FlashAttention against the oracle: ragged batch, fresh prompts and continued contexts,
     # tiles on the diagonal, at the window edge and at the sequence end
     sinks = torch.randn(n_q, device=dev()) if use_sinks else None
     q, kc, vc, bt, sl, cu = _paged_case(4, [300, 64, 129, 128], [300, 700, 129, 1024], n_q, n_kv, hd, seed=2)
-    got = K().attention_prefill_tc(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window)
+    got = K().attention_prefill_tc(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window, softcap=softcap)
     K().check_status()
-    want = ref.attention(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window)
+    want = ref.attention(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window, softcap=softcap)
     assert rel_err(got, want) < 1.5e-2
     # the dispatcher sends long query segments to the same kernel
-    assert torch.equal(K().attention(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window), got)
+    assert torch.equal(K().attention(q, kc, vc, bt, sl, cu, 300, sinks=sinks, window=window, softcap=softcap), got)
+
+
+@pytest.mark.parametrize("hd", [64, 128, 256])
+def test_attention_prefill_rescales_its_accumulator_when_the_maximum_grows(hd):
+    # keys whose scores grow along the sequence: the running maximum rises by far more than 2^8 between tiles, so the output
+    # accumulator in TMEM has to be rescaled in place several times; and a flat case in which it never is
+    n_q, n_kv = 4, 2
+    for growth in (0.0, 0.06):
+        q, kc, vc, bt, sl, cu = _paged_case(2, [700, 256], [700, 1024], n_q, n_kv, hd, seed=7)
+        ramp = 1.0 + growth * torch.arange(128, device=dev(), dtype=torch.float32).view(1, 1, 128, 1)
+        page_rank = torch.zeros(kc.shape[0], device=dev())
+        for b in range(bt.shape[0]):
+            page_rank[bt[b].long()] = torch.arange(bt.shape[1], device=dev(), dtype=torch.float32)
+        kc = (kc.float() * (ramp + growth * 128 * page_rank.view(-1, 1, 1, 1))).to(torch.bfloat16)
+        q = (q.float().abs() * 2).to(torch.bfloat16)
+        got = K().attention_prefill_tc(q, kc, vc, bt, sl, cu, 700)
+        K().check_status()
+        want = ref.attention(q, kc, vc, bt, sl, cu, 700)
+        assert rel_err(got, want) < 2e-2, growth
 
 
 def test_sampling():

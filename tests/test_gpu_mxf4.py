@@ -208,3 +208,33 @@ def test_run_twice_is_bit_identical():
         live = pk.packed_token[:nrows] >= 0
         outs.append(y[:nrows][live].clone())
     assert torch.equal(outs[0], outs[1])
+
+
+def test_decode_fusions_match_their_unfused_forms():
+    """route + quantise in one launch, and the expert combine folded into the residual add + RMSNorm: bit-identical to the
+    separate kernels."""
+    torch.manual_seed(9)
+    T, H, E, topk = 5, 2880, 32, 4
+    x = torch.randn(T, H, device=dev()).to(torch.bfloat16)
+    logits = torch.randn(T, E, device=dev())
+    rb = torch.randn(E, device=dev()) * 0.1
+    idx, w = K().moe_route(logits, rb, topk)
+    xq, sfx = K().moe_quant(x, T * topk, T * topk, 1, x_div=topk)
+    idx2, w2, xq2, sfx2 = K().moe_route_quant(logits, rb, topk, x)
+    K().check_status()
+    assert torch.equal(idx, idx2) and torch.equal(w, w2) and torch.equal(xq, xq2)
+    rows = torch.arange(T * topk, device=dev())
+    for kb in range(sfx.shape[0]):
+        assert torch.equal(sfx[kb, rows, :4], sfx2[kb, rows, :4])          # row 0 of each pair's atom: bytes 0..3
+    # combine inside the norm
+    y = torch.randn(T * topk + 3, H, device=dev()).to(torch.bfloat16)
+    p2p = torch.arange(T * topk, dtype=torch.int32, device=dev())
+    p2p[2] = -1                                                            # a pair that lives on another rank
+    res = torch.randn(T, H, device=dev())
+    nw = torch.rand(H, device=dev()) + 0.5
+    d = K().CombineDelta(y, p2p, w)
+    x1, x2 = res.clone(), res.clone()
+    out1 = K().rmsnorm(x1, nw, 1e-5, delta=d.materialize(), delta_scale=0.5)
+    out2 = K().rmsnorm_combine(x2, nw, 1e-5, d, delta_scale=0.5)
+    K().check_status()
+    assert torch.equal(x1, x2) and torch.equal(out1, out2)

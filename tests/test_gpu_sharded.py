@@ -101,3 +101,47 @@ def test_dispatch_plan_is_the_stable_counting_sort_of_the_packer():
         assert torch.allclose(out, h.float() * w.sum(dim=1, keepdim=True), rtol=1e-2, atol=1e-2)
     finally:
         sc.close()
+
+
+def test_a_flag_that_nobody_sets_ends_the_wait_with_a_status_and_leaves_the_gpu_usable():
+    """Failure detection on the device without a fault: consumers wait for their peers' flags with a time limit.  Here the
+    expected sequence number is raised by hand, so the flag this (only) rank waits for never arrives; with the limit lowered to a
+    few milliseconds the kernels return, the status word reports the peer-flag code, and the next ordinary launch works."""
+    import ctypes as C
+    from machx_inference_engine_b200 import _lib
+    from machx_inference_engine_b200.ops import cuda as K
+    from machx_inference_engine_b200.parallel.fused import FusedComm, ReducedDelta
+    from machx_inference_engine_b200.parallel.sharded import ShardedComm
+    dev = torch.device("cuda:0")
+    par = ParallelCtx()
+    R, H, topk = 128, 256, 2
+    # (1) the sharded path's combine: limit 2^22 cycles (about 2 ms)
+    sc = ShardedComm(par, dev, H, 128, n_experts=4, top_k=topk, wait_cycles_log2=22)
+    try:
+        sc.seq[3] += 1                                   # FL_RET: expect a return that no kernel will publish
+        w = torch.full((R, topk), 0.5, device=dev)
+        out = torch.empty(R, H, dtype=torch.float32, device=dev)
+        K._check(_lib.cuda().mx_moe_combine_wait(sc._ws_ref, K._p(w), K._p(out), R, H, topk, K._stream()), "moe_combine_wait")
+        with pytest.raises(K.KernelError, match="peer flag"):
+            K.check_status()
+    finally:
+        sc.close()
+    # (2) the fused all-reduce's consumer (residual add + RMSNorm over the inbox): same, through the library-wide limit
+    lib = _lib.cuda()
+    assert lib.mx_set_wait_limit_cycles(C.c_longlong(1 << 22)) == 0
+    fc = FusedComm.create(par, dev, max_tokens=128, max_width=H)
+    try:
+        fc.seq += 1                                      # a partial that no producer has pushed
+        x = torch.randn(8, H, device=dev)
+        with pytest.raises(K.KernelError, match="peer flag"):
+            fc.rmsnorm(x, torch.ones(H, device=dev), 1e-5, ReducedDelta(fc, 8, H, bf16=False))
+            K.check_status()
+    finally:
+        assert lib.mx_set_wait_limit_cycles(C.c_longlong(2000000000)) == 0
+        fc.close()
+    # the context is intact: an ordinary kernel runs and is correct
+    x = torch.randn(4, H, device=dev)
+    got = K.rmsnorm(x, torch.ones(H, device=dev), 1e-5)
+    K.check_status()
+    want = ref.rmsnorm(x.clone(), torch.ones(H, device=dev), 1e-5)
+    assert torch.allclose(got.float(), want.float(), atol=2e-2)
