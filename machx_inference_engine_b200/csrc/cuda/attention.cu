@@ -4,8 +4,11 @@
 // One CTA owns (query tile, kv head, kv split).  Each 64-key K/V tile is staged in shared
 // memory once and shared by every (query token, query head) pair of the group; a warp runs
 // the online softmax for its pairs with one key per lane, so there is no per-key reduction.
-// Every split writes an un-normalised partial (acc, m, l); the combine kernel merges the
-// splits and folds the per-head sink into the denominator exactly once.
+// Every split writes an un-normalised partial (acc, m, l); the CTA of a (query tile, kv head)
+// group that finishes last (an atomic ticket per group, reset by its last taker) merges the
+// splits and folds the per-head sink into the denominator exactly once, so that decode is one
+// launch.  Splits that would get no key tile exit at once and are not counted.  The separate
+// combine kernel remains for batches with more groups than there are tickets.
 //
 // KV cache layout: [block][kv_head][block_size][head_dim] bf16, block_size a multiple of 64.  An int8 cache has the
 // same layout with one byte per element plus an fp32 scale per (block, kv head, token) row (value = q * scale); the
@@ -37,6 +40,9 @@ struct AttnParams {
   const int* cu_q;             // [B+1]
   float* o_part;               // [splits][Tq][n_q][hd]
   float* ml_part;              // [splits][Tq][n_q][2]
+  int* tickets;                // non-null: one counter per (batch entry, query tile, kv head) group; the last split merges
+  const float* sinks;          // [n_q] or null (used by the merging CTA)
+  __nv_bfloat16* out;          // [Tq][n_q][hd] (written by the merging CTA)
   int B, n_q, n_kv, max_blocks, block_size;
   int q_tile;                  // query tokens per CTA
   int max_q_tiles;             // per sequence
@@ -107,6 +113,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_partial_kernel(const Attn
   const int n_tiles = tile_hi - tile_lo;
   const int per = (n_tiles + p.n_splits - 1) / p.n_splits;
   const int my_lo = tile_lo + split * per, my_hi = min(tile_hi, my_lo + per);
+  // splits that own at least one key tile (n_tiles >= 1: a query always sees its own position's tile)
+  const int eff = p.tickets ? (n_tiles + per - 1) / per : p.n_splits;
+  if (split >= eff) return;
 
   const int total_pairs = nt * gqa;
   for (int round0 = 0; round0 < total_pairs; round0 += PAIRS) {
@@ -239,6 +248,51 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_partial_kernel(const Attn
       if (lane == 0) { p.ml_part[row * 2] = m[pi]; p.ml_part[row * 2 + 1] = l[pi]; }
     }
   }
+  if (!p.tickets) return;
+  // ---- the group's last CTA merges the splits
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* tk = p.tickets + (size_t)blockIdx.x * p.n_kv + kvh;
+    const int prev = atomicAdd(tk, 1);
+    s_last = prev == eff - 1;
+    if (s_last) *tk = 0;                 // every counted split has arrived: the counter is ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const size_t sstride = (size_t)p.Tq * p.n_q;
+  for (int pr = warp; pr < total_pairs; pr += ATT_WARPS) {
+    const int tq = pr / gqa, hq = kvh * gqa + pr % gqa;
+    const size_t r = (size_t)(q_begin + t0 + tq) * p.n_q + hq;
+    float M = p.sinks ? p.sinks[hq] : -1e30f;
+    for (int s = lane; s < eff; s += 32) M = fmaxf(M, __ldcg(p.ml_part + (s * sstride + r) * 2));
+    M = warp_max(M);
+    float L = 0.f;
+    for (int s = lane; s < eff; s += 32) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ml_part + (s * sstride + r) * 2));
+      L += ml.y * __expf(ml.x - M);
+    }
+    L = warp_sum(L) + (p.sinks ? __expf(p.sinks[hq] - M) : 0.f);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    float acc[HD / 32];
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) acc[c] = 0.f;
+    for (int s0 = 0; s0 < eff; s0 += 32) {
+      const float sc_l = s0 + lane < eff ? __expf(__ldcg(p.ml_part + ((s0 + lane) * sstride + r) * 2) - M) : 0.f;
+      const int cnt = min(32, eff - s0);
+#pragma unroll 4
+      for (int j = 0; j < cnt; ++j) {
+        const float sc = __shfl_sync(0xffffffffu, sc_l, j);
+        const float* op = p.o_part + ((s0 + j) * sstride + r) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) acc[c] = fmaf(__ldcg(op + lane + 32 * c), sc, acc[c]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) p.out[r * HD + lane + 32 * c] = __float2bfloat16(acc[c] * inv);
+  }
 }
 
 // out[t][h][:] = sum_s acc_s e^{m_s - M} / (sum_s l_s e^{m_s - M} + e^{sink_h - M})
@@ -267,6 +321,12 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
   }
 }
 
+// Tickets of the fused merge: zero at load, and every launch leaves its counters at zero again.  Consecutive launches rotate
+// through the slots, so that two launches that overlap (programmatic dependent launch lets the next kernel's CTAs start while
+// this one drains) never count on the same words.
+constexpr int ATT_TICKET_SLOTS = 8, ATT_TICKETS_PER_SLOT = 2048;
+static __device__ int g_attn_tickets[ATT_TICKET_SLOTS * ATT_TICKETS_PER_SLOT];
+
 template <int HD, int PPW>
 static int launch_partial(const AttnParams& p, cudaStream_t st) {
   constexpr int PAIRS = ATT_WARPS * PPW;
@@ -287,6 +347,22 @@ static int launch_partial(const AttnParams& p, cudaStream_t st) {
 
 using namespace mx;
 
+// pairs per warp (1 for decode-sized work, 4 when there are many query tokens), query tokens per CTA, query tiles per sequence
+static void att_tiling(int max_q_len, int gqa, int& ppw, int& q_tile, int& max_q_tiles) {
+  ppw = (max_q_len * gqa > ATT_WARPS * 2) ? 4 : (max_q_len * gqa > ATT_WARPS ? 2 : 1);
+  const int pairs = ATT_WARPS * ppw;
+  q_tile = pairs / gqa > 0 ? pairs / gqa : 1;
+  if (q_tile > max_q_len) q_tile = max_q_len;
+  max_q_tiles = (max_q_len + q_tile - 1) / q_tile;
+}
+
+// Kernels one attention call launches: 1 when the split merge runs inside the partial kernel, 2 with the separate combine.
+MX_HOST_API int mx_attention_launches(int B, int max_q_len, int n_q, int n_kv) {
+  int ppw, q_tile, max_q_tiles;
+  att_tiling(max_q_len, n_q / (n_kv > 0 ? n_kv : 1), ppw, q_tile, max_q_tiles);
+  return (long long)B * max_q_tiles * n_kv <= ATT_TICKETS_PER_SLOT ? 1 : 2;
+}
+
 // Scratch: o_part needs n_splits*Tq*n_q*hd floats, ml_part n_splits*Tq*n_q*2 floats.
 // max_q_len is the longest query segment of the batch (host knows it from cu_q).
 static int attention_impl(const void* q, const void* k_cache, const void* v_cache, const float* k_scale, const float* v_scale,
@@ -303,12 +379,23 @@ static int attention_impl(const void* q, const void* k_cache, const void* v_cach
   p.block_table = block_table; p.seq_lens = seq_lens; p.cu_q = cu_q; p.o_part = o_part; p.ml_part = ml_part;
   p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.max_blocks = max_blocks; p.block_size = block_size;
   p.n_splits = n_splits < 1 ? 1 : n_splits; p.Tq = Tq; p.window = window; p.scale = scale; p.softcap = softcap;
-  // pairs per warp: 1 for decode-sized work, 4 when there are many query tokens
-  const int ppw = (max_q_len * gqa > ATT_WARPS * 2) ? 4 : (max_q_len * gqa > ATT_WARPS ? 2 : 1);
-  const int pairs = ATT_WARPS * ppw;
-  p.q_tile = pairs / gqa > 0 ? pairs / gqa : 1;
-  if (p.q_tile > max_q_len) p.q_tile = max_q_len;
-  p.max_q_tiles = (max_q_len + p.q_tile - 1) / p.q_tile;
+  int ppw;
+  att_tiling(max_q_len, gqa, ppw, p.q_tile, p.max_q_tiles);
+  p.tickets = nullptr; p.sinks = sinks; p.out = (__nv_bfloat16*)out;
+  const long long groups = (long long)B * p.max_q_tiles * n_kv;
+  if (groups <= ATT_TICKETS_PER_SLOT) {
+    static int* base[64] = {nullptr};
+    static unsigned turn[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!base[dev]) {
+      void* a = nullptr;
+      if (cudaGetSymbolAddress(&a, g_attn_tickets) != cudaSuccess) return -115;
+      base[dev] = (int*)a;
+    }
+    p.tickets = base[dev] + (size_t)(turn[dev]++ % ATT_TICKET_SLOTS) * ATT_TICKETS_PER_SLOT;
+  }
   int rc;
 #define MX_ATT(HD_)                                                        \
   (ppw == 4 ? launch_partial<HD_, 4>(p, st) : ppw == 2 ? launch_partial<HD_, 2>(p, st) : launch_partial<HD_, 1>(p, st))
@@ -320,7 +407,7 @@ static int attention_impl(const void* q, const void* k_cache, const void* v_cach
     default: return -112;
   }
 #undef MX_ATT
-  if (rc) return rc;
+  if (rc || p.tickets) return rc;
   launch_pdl(attn_combine_kernel, dim3((Tq * n_q + 3) / 4), dim3(128), 0, st, o_part, ml_part, sinks, (__nv_bfloat16*)out, Tq, n_q, hd, p.n_splits);
   return (int)cudaGetLastError();
 }

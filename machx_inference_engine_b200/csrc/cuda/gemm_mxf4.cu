@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "host_util.h"
 #include "moe_route.cuh"
+#include "mxfp8.cuh"
 
 #include <cuda_fp8.h>
 
@@ -34,14 +35,13 @@ constexpr int XT_M = 128;        // token rows per tile (instruction M)
 constexpr int XT_K = 128;        // elements of K per stage (4 instructions of K = 32)
 constexpr int XT_N = 192;        // weight rows per tile (instruction N)
 constexpr int XT_HALF = XT_N / 2;
-constexpr int SF_ATOM = 512;     // bytes of one scale-factor atom: 128 rows x 4 k-blocks
-
-// scale-factor atom: row r (0..127), k-block q (0..3) -> byte (r % 32) * 16 + (r / 32) * 4 + q
-__host__ __device__ constexpr int sf_atom_offset(int r, int q) { return (r & 31) * 16 + (r >> 5) * 4 + q; }
+constexpr int XT_FEW = 8;        // tiles with at most this many live rows take the epilogue that spreads one row over a warp
 
 struct Mxf4Params {
   int N, K;                       // output features (dual: of gate and of up each), logical K
   int FB, KB;                     // feature blocks (96 features dual, 192 single), 128-element k blocks
+  int KS, KBS;                    // single mode: K is cut into KS ranges of KBS k-blocks, range s writes its partial sums to rows
+  long long split_rows;           // s * split_rows + row of `out` (the consumer adds them up); KS = 1: no split
   int dual;
   int max_tiles;                  // host bound on token tiles; scale atoms of the activations are [KB][max_tiles][512]
   int row_stride;                 // first row of token tile j is j * row_stride (128: padded expert segments, 1: one pair per tile)
@@ -73,7 +73,9 @@ struct XLayout {
   static constexpr int STAGE = SF + 2048;
   static constexpr int STAGES = 5;
   static constexpr int BAR_OFFSET = STAGES * STAGE;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;       // barriers + alignment slack
+  static constexpr int EPI_OFFSET = BAR_OFFSET + 256;         // few-row epilogue: XT_FEW accumulator rows as fp32
+  static constexpr int EPI_BYTES = XT_FEW * XT_N * 4;
+  static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024; // + alignment slack
   static_assert(STAGE % 1024 == 0, "stage tiles must stay 1024-byte aligned");
   static_assert(TOTAL <= 232448, "shared memory plan exceeds 227 KB");
 };
@@ -118,6 +120,9 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// barrier of the four epilogue warps
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
 __device__ __forceinline__ float mxf4_act(int act, float g, float u, float alpha, float limit) {
   if (act == 2) {
     g = fminf(g, limit);
@@ -127,24 +132,10 @@ __device__ __forceinline__ float mxf4_act(int act, float g, float u, float alpha
   return __fdividef(g, 1.f + __expf(-g)) * u;
 }
 
-// e8m0 scale of a 32-element block with maximum magnitude amax: the smallest power of two that keeps the block inside e4m3's
-// range (448).  Returns the biased exponent byte; *inv = 1 / scale.
-__device__ __forceinline__ uint32_t mxfp8_scale(float amax, float* inv) {
-  if (!(amax > 0.f)) { *inv = 1.f; return 127u; }
-  int ex = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 8;           // floor(log2 amax) - 8, biased
-  ex = max(1, min(ex, 253));
-  if (amax * __uint_as_float((uint32_t)(254 - ex) << 23) > 448.f) ex = min(ex + 1, 253);
-  *inv = __uint_as_float((uint32_t)(254 - ex) << 23);
-  return (uint32_t)ex;
-}
-__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
-  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return (uint32_t)lo | ((uint32_t)hi << 16);
-}
-
-// work item t -> (token tile j, feature block fb); returns the tile's live rows (<= 0: nothing to do)
-__device__ __forceinline__ int item_decode(const Mxf4Params& p, int t, int& j, int& fb) {
+// work item t -> (token tile j, feature block fb, k range ks); returns the tile's live rows (<= 0: nothing to do)
+__device__ __forceinline__ int item_decode(const Mxf4Params& p, int t, int& j, int& fb, int& ks) {
+  ks = 0;
+  if (p.KS > 1) { ks = t % p.KS; t /= p.KS; }
   j = t / p.FB;
   fb = t - j * p.FB;
   const int e = p.tile_expert[j] - p.e_lo;
@@ -185,7 +176,7 @@ mxf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   pdl_prologue();           // everything below reads what earlier kernels of the stream wrote
 
   const int m_tiles = p.num_tiles_dev ? min(*p.num_tiles_dev, p.max_tiles) : p.max_tiles;
-  const int total = m_tiles * p.FB;
+  const int total = m_tiles * p.FB * p.KS;
 
   if (warp == 0) {
     // ------------------------------------------------ producer: TMA tiles + bulk copies of the scale atoms
@@ -196,19 +187,20 @@ mxf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       const size_t sfx_step = (size_t)p.max_tiles * SF_ATOM;
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        int j, fb;
-        const int nv = item_decode(p, t, j, fb);
+        int j, fb, ks;
+        const int nv = item_decode(p, t, j, fb, ks);
         if (nv <= 0) continue;
+        const int kb0 = ks * p.KBS, kb1 = min(p.KB, kb0 + p.KBS);
         const int box = nv <= 16 ? 16 : (nv <= 32 ? 32 : (nv <= 64 ? 64 : 128));
         const CUtensorMap* tx = box == 16 ? &tmap_x16 : (box == 32 ? &tmap_x32 : (box == 64 ? &tmap_x64 : &tmap_x128));
         const long long wt = ((long long)(p.tile_expert[j] - p.e_lo) * p.FB + fb) * p.KB;   // first weight tile of this slab
         const int row0 = j * p.row_stride;
         // a packed-4-bit TMA load counts its packed bytes on the barrier (half of what it writes to shared memory)
         const uint32_t bytes = L::B_BYTES / 2 + 2 * SF_ATOM + box * XT_K + SF_ATOM;
-        int wy = (int)(wt * XT_N), kx = 0;
-        const uint8_t* sw = p.sfw + wt * (2 * SF_ATOM);
-        const uint8_t* sx = p.sfx + (size_t)j * SF_ATOM;
-        for (int kb = 0; kb < p.KB; ++kb) {
+        int wy = (int)((wt + kb0) * XT_N), kx = kb0 * XT_K;
+        const uint8_t* sw = p.sfw + (wt + kb0) * (2 * SF_ATOM);
+        const uint8_t* sx = p.sfx + (size_t)j * SF_ATOM + (size_t)kb0 * sfx_step;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(ebar, ph, p.status, ERR_MBAR_TIMEOUT_PRODUCER, abort_flag))) break;
           mbar_expect_tx(fbar, bytes);
           tma_load_2d(st + L::B, &tmap_w, fbar, 0, wy);
@@ -227,14 +219,15 @@ mxf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       uint32_t s = 0, ph = 0, st = smem_base, fbar = bar_full, ebar = bar_empty, sfsel = 0, item_n = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        int j, fb;
-        if (item_decode(p, t, j, fb) <= 0) continue;
+        int j, fb, ks;
+        if (item_decode(p, t, j, fb, ks) <= 0) continue;
+        const int kb0 = ks * p.KBS, kb1 = min(p.KB, kb0 + p.KBS);
         const uint32_t acc = item_n & 1, acc_ph = (item_n >> 1) & 1;
         ++item_n;
         if (!(ok = mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, p.status, ERR_MBAR_TIMEOUT_MMA, abort_flag))) break;
         tc_fence_after();
         const uint32_t d = tmem_base + acc * XT_N;
-        for (int kb = 0; kb < p.KB; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(fbar, ph, p.status, ERR_MBAR_TIMEOUT_MMA, abort_flag))) break;
           tc_fence_after();
           const uint32_t sf = tmem_base + SF_COL + sfsel;               // four scale buffers rotate between consecutive stages
@@ -243,7 +236,7 @@ mxf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           tmem_cp_sf(sf + 4, st + L::SF + SF_ATOM);                     // weight scales: rows 0..127 -> columns 4..7
           tmem_cp_sf(sf + 8, st + L::SF + 2 * SF_ATOM);                 //                rows 128..191 -> columns 8, 9
           const uint32_t a = desc_lo(st + L::A), b = desc_lo(st + L::B);
-          umma_mxf4<false>(d, a, b, MXF4_IDESC, sf, sf + 4, (uint32_t)kb);
+          umma_mxf4<false>(d, a, b, MXF4_IDESC, sf, sf + 4, (uint32_t)(kb - kb0));
 #pragma unroll
           for (int kk = 1; kk < 4; ++kk)        // 32 elements = 32 bytes per k-step: +2 in the descriptor's 16-byte units
             umma_mxf4<true>(d, a + 2 * kk, b + 2 * kk, MXF4_IDESC + kk * MXF4_IDESC_KSTEP, sf, sf + 4);
@@ -261,8 +254,8 @@ mxf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     uint32_t item_n = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-      int j, fb;
-      const int nv = item_decode(p, t, j, fb);
+      int j, fb, ks;
+      const int nv = item_decode(p, t, j, fb, ks);
       if (nv <= 0) continue;
       const uint32_t acc = item_n & 1, acc_ph = (item_n >> 1) & 1;
       ++item_n;
@@ -272,6 +265,76 @@ mxf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       const bool row_ok = rin < nv;
       const size_t row = (size_t)j * p.row_stride + rin;
       const uint32_t tl = tmem_base + ((uint32_t)(q * 32) << 16) + acc * XT_N;
+      if (nv <= XT_FEW) {
+        // Few live rows (decode: one pair per tile; batched decode: a couple of rows per expert).  With lane = row only a few
+        // threads of one warp would do the whole epilogue, so the rows go through shared memory and every warp takes
+        // (row, 32- or 64-column block) items with lane = column.
+        float* epi = reinterpret_cast<float*>(smem + L::EPI_OFFSET);
+        if (q == 0) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < XT_N; c0 += 32) {
+            uint32_t g[32];
+            tmem_ld_32x32(tl + c0, g);
+            tmem_ld_wait();
+            if (lane < nv) {
+              float4* d4 = reinterpret_cast<float4*>(epi + lane * XT_N + c0);
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                d4[c] = make_float4(__uint_as_float(g[4 * c]), __uint_as_float(g[4 * c + 1]), __uint_as_float(g[4 * c + 2]), __uint_as_float(g[4 * c + 3]));
+            }
+          }
+        }
+        epi_sync();
+        tc_fence_before();
+        mbar_arrive(bar_tempty + 8 * acc);         // the accumulator is free while the rows are finished from shared memory
+        const int we = warp - 2;
+        if (p.dual) {
+          const float* bg = p.bias0 ? p.bias0 + (size_t)e * p.N : nullptr;
+          const float* bu = p.bias1 ? p.bias1 + (size_t)e * p.N : nullptr;
+          for (int it = we; it < nv * 3; it += 4) {
+            const int r = it / 3, b = it - r * 3;
+            const int f0 = fb * XT_HALF + b * 32;
+            if (f0 >= p.N) continue;
+            const size_t orow = (size_t)j * p.row_stride + r;
+            const float gv = epi[r * XT_N + b * 32 + lane] + (bg ? __ldg(bg + f0 + lane) : 0.f);
+            const float uv = epi[r * XT_N + XT_HALF + b * 32 + lane] + (bu ? __ldg(bu + f0 + lane) : 0.f);
+            const float v = __bfloat162float(__float2bfloat16(mxf4_act(p.act, gv, uv, p.act_alpha, p.act_limit)));
+            float inv;
+            const uint32_t eb = mxfp8_scale(warp_max(fabsf(v)), &inv);
+            p.oq[orow * p.oq_ld + f0 + lane] = (uint8_t)__nv_cvt_float_to_fp8(v * inv, __NV_SATFINITE, __NV_E4M3);
+            const int blk = f0 >> 5;
+            if (lane == 0) p.osf[((size_t)(blk >> 2) * p.max_tiles + j) * SF_ATOM + sf_atom_offset(r, blk & 3)] = (uint8_t)eb;
+          }
+          if (fb == p.FB - 1) {
+            for (int it = we; it < nv; it += 4) {
+              const size_t orow = (size_t)j * p.row_stride + it;
+              for (int f0 = p.N; f0 < p.oq_ld; f0 += 32) {
+                p.oq[orow * p.oq_ld + f0 + lane] = 0;
+                const int blk = f0 >> 5;
+                if (lane == 0) p.osf[((size_t)(blk >> 2) * p.max_tiles + j) * SF_ATOM + sf_atom_offset(it, blk & 3)] = 127;
+              }
+            }
+          }
+        } else {
+          const float* bs = (p.bias0 && ks == 0) ? p.bias0 + (size_t)e * p.N : nullptr;
+          for (int it = we; it < nv * 3; it += 4) {
+            const int r = it / 3, b = it - r * 3;
+            const int f = fb * XT_N + b * 64 + 2 * lane;
+            if (f >= p.N) continue;
+            __nv_bfloat16* orow = p.out + ((size_t)ks * p.split_rows + (size_t)j * p.row_stride + r) * p.ldo;
+            const float v0 = epi[r * XT_N + b * 64 + 2 * lane] + (bs ? __ldg(bs + f) : 0.f);
+            if (f + 1 < p.N) {
+              const float v1 = epi[r * XT_N + b * 64 + 2 * lane + 1] + (bs ? __ldg(bs + f + 1) : 0.f);
+              if ((p.ldo & 1) == 0) *reinterpret_cast<uint32_t*>(orow + f) = pack_bf16(v0, v1);
+              else { orow[f] = __float2bfloat16(v0); orow[f + 1] = __float2bfloat16(v1); }
+            } else {
+              orow[f] = __float2bfloat16(v0);
+            }
+          }
+        }
+        epi_sync();                                // the next item's rows overwrite the staging buffer
+        continue;
+      }
       if (q * 32 < nv) {                           // warps whose 32 rows are all beyond the tile's live rows have nothing to read
         if (p.dual) {
           const float* bg = p.bias0 ? p.bias0 + (size_t)e * p.N : nullptr;
@@ -318,8 +381,8 @@ mxf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             }
           }
         } else {
-          const float* bs = p.bias0 ? p.bias0 + (size_t)e * p.N : nullptr;
-          __nv_bfloat16* out = p.out + row * p.ldo;
+          const float* bs = (p.bias0 && ks == 0) ? p.bias0 + (size_t)e * p.N : nullptr;
+          __nv_bfloat16* out = p.out + ((size_t)ks * p.split_rows + row) * p.ldo;
 #pragma unroll 1
           for (int c0 = 0; c0 < XT_N; c0 += 32) {
             uint32_t g[32];
@@ -528,8 +591,9 @@ MX_HOST_API int mx_moe_route_quant(const float* logits, const float* bias, int T
 MX_HOST_API int mx_mxf4_gemm(const void* w, const void* sfw, int dual, int n_experts, const void* xq, const void* sfx, int x_rows, int N, int K,
                              const int* tile_expert, const int* tile_valid, int default_valid, const int* num_tiles_dev, int max_tiles,
                              int row_stride, int e_lo, const float* bias0, const float* bias1, void* out, int ldo, void* oq, void* osf, int oq_ld,
-                             int act, float act_alpha, float act_limit, cudaStream_t st) {
+                             int act, float act_alpha, float act_limit, int ksplit, cudaStream_t st) {
   if (max_tiles <= 0 || x_rows <= 0) return 0;
+  if (ksplit < 1 || (dual && ksplit != 1)) return -104;
   if (K % 32 || (row_stride != 1 && row_stride != 128)) return -101;
   if (dual && (act == 0 || N % 32 || oq_ld % 128 || oq_ld < N || !oq || !osf)) return -102;
   if (!dual && !out) return -103;
@@ -537,6 +601,9 @@ MX_HOST_API int mx_mxf4_gemm(const void* w, const void* sfw, int dual, int n_exp
   p.N = N; p.K = K; p.dual = dual;
   p.FB = dual ? (N + XT_HALF - 1) / XT_HALF : (N + XT_N - 1) / XT_N;
   p.KB = (K + XT_K - 1) / XT_K;
+  p.KBS = (p.KB + ksplit - 1) / ksplit;
+  p.KS = (p.KB + p.KBS - 1) / p.KBS;             // every range owns at least one k-block
+  p.split_rows = x_rows;
   p.max_tiles = max_tiles; p.row_stride = row_stride; p.e_lo = e_lo; p.n_experts = n_experts;
   p.num_tiles_dev = num_tiles_dev; p.tile_expert = tile_expert; p.tile_valid = tile_valid; p.default_valid = default_valid;
   p.sfw = (const uint8_t*)sfw; p.sfx = (const uint8_t*)sfx;
@@ -553,7 +620,7 @@ MX_HOST_API int mx_mxf4_gemm(const void* w, const void* sfw, int dual, int n_exp
   if ((r = make_tmap_u8(&tx32, xq, Kp, x_rows, Kp, 32))) return r;
   if ((r = make_tmap_u8(&tx64, xq, Kp, x_rows, Kp, 64))) return r;
   if ((r = make_tmap_u8(&tx128, xq, Kp, x_rows, Kp, 128))) return r;
-  const long long items = (long long)max_tiles * p.FB;
+  const long long items = (long long)max_tiles * p.FB * p.KS;
   const int grid = items < sm_count() ? (int)items : sm_count();
   static DeviceOnce configured;
   if (configured.pending()) {

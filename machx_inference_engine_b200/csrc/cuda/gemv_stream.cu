@@ -14,23 +14,63 @@
 //           another rank give zeros), optional gated activation over 16-row interleaved gate/up rows
 // Fused epilogues: bias, per-slot scale, SwiGLU / clamped SwiGLU / GeGLU, stores into every rank's all-reduce inbox.
 //
+// Fused prologue (dense mode, bf16 / Q8 weights): the activation rows are formed in the kernel as RMSNorm(x + delta) * w from the fp32
+// residual rows, where delta is a bf16 tensor or the expert combine sum_k cw[k] * yp[pos[k]]; every CTA computes the few rows for
+// itself (they are a few KB and sit in L2), CTA 0 also writes the updated residual to a second buffer (other CTAs still read the old
+// one) and, when asked, the normalised rows.  Fused tail (router GEMV): the CTA that finishes last (an atomic ticket) reads the
+// logits, picks the top-k experts per token and writes the token rows as MXFP8 pair tiles for the block-scaled expert GEMM.
+//
 // Reference parity: src/ops/gemv_fp16.cpp:64, gemv_q8dot.cpp:276-680, gemv_mxfp4.cpp:94-323, moe_fused.cpp:101-541.
 #include "common.cuh"
 #include "comm.cuh"
 #include "dequant.cuh"
 #include "host_util.h"
+#include "moe_route.cuh"
+#include "mxfp8.cuh"
 
 namespace mx {
 
 constexpr int GS_MAX_STAGES = 4;
 constexpr int GS_MAX_XROWS = 8;
+constexpr int GS_MAX_CK = 8;      // pairs per token the fused combine + norm prologue takes
+constexpr int GS_NORM_MAX_K = 4096;   // row length the fused norm prologue holds in registers (8 float4 per thread at 128 threads)
+constexpr int GS_NORM_MAX_M = 2;      // rows: they are normalised one after the other, so more rows go through the separate kernel
 
 template <int FMT> struct GsCfg;
 template <> struct GsCfg<WF_BF16> { static constexpr int WARPS = 4, RPW = 1; };
 template <> struct GsCfg<WF_Q8> { static constexpr int WARPS = 8, RPW = 1; };
 template <> struct GsCfg<WF_MXFP4> { static constexpr int WARPS = 8, RPW = 2; };
 
+// activation rows = RMSNorm(x + delta_scale * delta) * w
+struct GsNorm {
+  const float* x;               // [M][K] fp32 residual rows; null: the kernel reads bf16 rows from GsParams::x
+  float* x_out;                 // x + delta (a buffer other than x), written by CTA 0; null when there is no delta
+  const __nv_bfloat16* delta;   // [M][K] or null
+  const __nv_bfloat16* yp;      // combine form of delta: packed expert outputs [rows][K] ...
+  const int* pos;               // ... [M][ck] row of yp per (token, slot) pair, < 0: no contribution
+  const float* cw;              // ... [M][ck] weights
+  int ck;
+  const float* w;               // [K]
+  float eps, delta_scale;
+  int one_plus_w;
+  __nv_bfloat16* h_out;         // optional: the normalised rows [M][K], written by CTA 0
+};
+// router tail: y holds fp32 logits [M][N]
+struct GsRoute {
+  int* ticket;                  // null: no tail
+  const float* bias;
+  int Kt, renorm;
+  int* topk_idx;                // [M][Kt]
+  float* topk_w;                // [M][w_copies][Kt]
+  int w_copies;
+  uint8_t* xq;                  // [M * Kt][KB * 128] e4m3: one row per (token, slot) pair
+  uint8_t* sfx;                 // scale atoms [KB][max_tiles][512], pair r is row 0 of tile r
+  int KB, max_tiles;
+};
+
 struct GsParams {
+  GsNorm norm;
+  GsRoute route;
   WeightRef w;
   const __nv_bfloat16* x;   // [n_xrows][K]
   void* y;
@@ -352,6 +392,73 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
         }
         if (lane == 0) xscale[m] = exp2f((float)-sh);
       }
+    } else if (p.norm.x) {
+      // residual add + RMSNorm in place of a separate launch.  All consumer threads work on one row at a time and keep their
+      // elements in registers between the sum of squares and the scaling (K <= GS_NORM_MAX_K, checked by the host), so a row
+      // costs one round trip to L2; rows follow one another, which is why the host sends only a couple of rows this way.
+      const GsNorm& nm = p.norm;
+      const bool writer = blockIdx.x == 0;
+      constexpr int NT = WARPS * 32, NV = GS_NORM_MAX_K / (4 * NT);
+      float* red = xscale;                      // GS_MAX_XROWS floats, unused by these formats
+      for (int m = 0; m < p.n_xrows; ++m) {
+        const float* xr = nm.x + (size_t)m * K;
+        int pos[GS_MAX_CK];
+        float cwv[GS_MAX_CK];
+#pragma unroll
+        for (int k = 0; k < GS_MAX_CK; ++k) {
+          const bool live = nm.yp && k < nm.ck;
+          pos[k] = live ? nm.pos[(size_t)m * nm.ck + k] : -1;
+          cwv[k] = live ? nm.cw[(size_t)m * nm.ck + k] : 0.f;
+        }
+        float4 v[NV];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const int i = (threadIdx.x + j * NT) * 4;
+          v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (i < K) {
+            v[j] = *reinterpret_cast<const float4*>(xr + i);
+            if (nm.yp) {
+              float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int k = 0; k < GS_MAX_CK; ++k) {
+                if (pos[k] < 0) continue;
+                const uint2 yv = *reinterpret_cast<const uint2*>(nm.yp + (size_t)pos[k] * K + i);
+                d.x = fmaf(cwv[k], bf16_lo(yv.x), d.x); d.y = fmaf(cwv[k], bf16_hi(yv.x), d.y);
+                d.z = fmaf(cwv[k], bf16_lo(yv.y), d.z); d.w = fmaf(cwv[k], bf16_hi(yv.y), d.w);
+              }
+              v[j].x += d.x * nm.delta_scale; v[j].y += d.y * nm.delta_scale; v[j].z += d.z * nm.delta_scale; v[j].w += d.w * nm.delta_scale;
+            } else if (nm.delta) {
+              const uint2 dv = *reinterpret_cast<const uint2*>(nm.delta + (size_t)m * K + i);
+              v[j].x += bf16_lo(dv.x) * nm.delta_scale; v[j].y += bf16_hi(dv.x) * nm.delta_scale;
+              v[j].z += bf16_lo(dv.y) * nm.delta_scale; v[j].w += bf16_hi(dv.y) * nm.delta_scale;
+            }
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+          }
+        }
+        ss = warp_sum(ss);
+        consumer_sync(NT);                      // (the previous row's readers of `red` are done)
+        if (lane == 0) red[warp] = ss;
+        consumer_sync(NT);
+        float tot = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < WARPS; ++wv) tot += red[wv];
+        const float inv = rsqrtf(tot / K + nm.eps);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const int i = (threadIdx.x + j * NT) * 4;
+          if (i < K) {
+            float4 g = *reinterpret_cast<const float4*>(nm.w + i);
+            if (nm.one_plus_w) { g.x += 1.f; g.y += 1.f; g.z += 1.f; g.w += 1.f; }
+            const uint2 o = make_uint2(pack_bf16(v[j].x * inv * g.x, v[j].y * inv * g.y), pack_bf16(v[j].z * inv * g.z, v[j].w * inv * g.w));
+            *reinterpret_cast<uint2*>(xs + ((size_t)m * K + i) * 2) = o;
+            if (writer) {
+              if (nm.x_out) *reinterpret_cast<float4*>(nm.x_out + (size_t)m * K + i) = v[j];
+              if (nm.h_out) *reinterpret_cast<uint2*>(nm.h_out + (size_t)m * K + i) = o;
+            }
+          }
+        }
+      }
     } else {
       const int n16 = p.n_xrows * K / 8;
       for (int i = threadIdx.x; i < n16; i += WARPS * 32) reinterpret_cast<uint4*>(xs)[i] = __ldg(reinterpret_cast<const uint4*>(p.x) + i);
@@ -445,6 +552,60 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
     pdl_wait();                               // (producer warp: its lanes take part in the block-wide publish)
     peer_publish(p.peer, next_seq);
   }
+  if (p.route.ticket) {
+    // ---- router tail: the last CTA to finish routes the tokens and writes their MXFP8 pair tiles
+    __shared__ int s_last;
+    pdl_wait();
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int prev = atomicAdd(p.route.ticket, 1);
+      s_last = prev == (int)gridDim.x - 1;
+      if (s_last) *p.route.ticket = 0;        // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const GsRoute& rt = p.route;
+    for (int t = warp; t < p.M; t += WARPS + 1) route_token_warp((const float*)p.y, rt.bias, t, p.N, rt.Kt, rt.renorm, rt.topk_idx, rt.topk_w, rt.w_copies);
+    // xs holds the normalised bf16 rows this CTA multiplied: one thread per (row, 32-element block)
+    const int Kp = rt.KB * MXF_KBLOCK, nblk = rt.KB * 4;
+    for (int u = threadIdx.x; u < p.M * nblk; u += blockDim.x) {
+      const int t = u / nblk, blk = u - t * nblk, k0 = blk * 32;
+      float v[32];
+      float amax = 0.f;
+      if (k0 < K) {
+        const uint4* src = reinterpret_cast<const uint4*>(xs + ((size_t)t * K + k0) * 2);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 raw = src[i];
+          const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            v[8 * i + 2 * jj] = bf16_lo(w4[jj]);
+            v[8 * i + 2 * jj + 1] = bf16_hi(w4[jj]);
+            amax = fmaxf(amax, fmaxf(fabsf(v[8 * i + 2 * jj]), fabsf(v[8 * i + 2 * jj + 1])));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      float inv;
+      const uint32_t eb = mxfp8_scale(amax, &inv);
+      const uint4 lo = make_uint4(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv), e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv),
+                                  e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv), e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv));
+      const uint4 hi = make_uint4(e4m3x4(v[16] * inv, v[17] * inv, v[18] * inv, v[19] * inv), e4m3x4(v[20] * inv, v[21] * inv, v[22] * inv, v[23] * inv),
+                                  e4m3x4(v[24] * inv, v[25] * inv, v[26] * inv, v[27] * inv), e4m3x4(v[28] * inv, v[29] * inv, v[30] * inv, v[31] * inv));
+      for (int k = 0; k < rt.Kt; ++k) {
+        const size_t r = (size_t)t * rt.Kt + k;
+        uint4* d = reinterpret_cast<uint4*>(rt.xq + r * Kp + k0);
+        d[0] = lo;
+        d[1] = hi;
+        rt.sfx[((size_t)(blk >> 2) * rt.max_tiles + r) * SF_ATOM + sf_atom_offset(0, blk & 3)] = (uint8_t)eb;
+      }
+    }
+  }
 }
 
 template <int FMT, int MM, bool GATED, int NG>
@@ -502,9 +663,20 @@ static int gs_dispatch(GsParams& p, cudaStream_t st) {
 
 // Returns 0 when the kernel was launched, 1 when the shape / format is not taken by this path (the caller falls
 // back to the register-streamed kernels), a CUDA error code otherwise.
+static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* y, const float* bias, int M, int N, int K, int out_f32, int act,
+                             float act_alpha, float act_limit, const int* slot_expert, const float* slot_scale, int slots, int x_div, int e_lo,
+                             int e_hi, const PeerOut* peer, const GsNorm* norm, const GsRoute* route, cudaStream_t st);
+
 int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const float* bias, int M, int N, int K, int out_f32, int act,
                     float act_alpha, float act_limit, const int* slot_expert, const float* slot_scale, int slots, int x_div, int e_lo,
                     int e_hi, const PeerOut* peer, cudaStream_t st) {
+  return gemv_stream_fused(wfmt, w, x, y, bias, M, N, K, out_f32, act, act_alpha, act_limit, slot_expert, slot_scale, slots, x_div, e_lo, e_hi, peer,
+                           nullptr, nullptr, st);
+}
+
+static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* y, const float* bias, int M, int N, int K, int out_f32, int act,
+                             float act_alpha, float act_limit, const int* slot_expert, const float* slot_scale, int slots, int x_div, int e_lo,
+                             int e_hi, const PeerOut* peer, const GsNorm* norm, const GsRoute* route, cudaStream_t st) {
   if (wfmt != WF_BF16 && wfmt != WF_Q8 && wfmt != WF_MXFP4) return 1;
   if (K % 32 && !(wfmt == WF_BF16 && K % 8 == 0)) return 1;
   if (act != 0 && wfmt != WF_MXFP4) return 1;                // gated epilogue: one feature per warp needs RPW == 2
@@ -522,6 +694,9 @@ int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const 
   if (rb0 % 16) return 1;
   if (((uintptr_t)w.p0 & 15) || (w.p1 && ((uintptr_t)w.p1 & 15)) || ((uintptr_t)x & 15)) return 1;
   if (peer) p.peer = *peer; else p.peer.world = 0;
+  if (norm) p.norm = *norm; else p.norm.x = nullptr;
+  if (route) p.route = *route; else p.route.ticket = nullptr;
+  if ((norm || route) && (wfmt == WF_MXFP4 || p.slot_mode)) return 1;
   switch (wfmt) {
     case WF_BF16: return gs_dispatch<WF_BF16>(p, st);
     case WF_Q8: return gs_dispatch<WF_Q8>(p, st);
@@ -529,4 +704,47 @@ int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const 
   }
 }
 
+// One ticket word per launch of a router GEMV with the routing tail; launches rotate through the words (see attention.cu).
+constexpr int GS_TICKET_SLOTS = 8;
+static __device__ int g_gs_tickets[GS_TICKET_SLOTS];
+
 }  // namespace mx
+
+using namespace mx;
+
+// y[M][N] = (RMSNorm(x + delta_scale * delta) * norm_w) W^T + bias for M <= 2 rows of at most 4096 elements, W bf16 or Q8 (dense, one expert).
+//   x fp32 [M][K]; delta: bf16 [M][K] (delta != null), or the expert combine sum_k cw[m][k] * yp[pos[m][k]] (yp != null, ck <= 8), or none.
+//   x_out (required with a delta, must not alias x): the updated residual; h_out (optional): the normalised rows as bf16.
+//   route (E = N experts, fp32 logits in y): topk_idx [M][Kt], topk_w [M][w_copies][Kt] and the rows as MXFP8 pair tiles xq / sfx (see mx_moe_route_quant).
+// Returns 1 when the shape or format is not taken (the caller runs the separate kernels instead).
+MX_HOST_API int mx_gemv_norm(int wfmt, const void* w0, const void* w1, const float* x, float* x_out, const void* delta, const void* yp, const int* pos,
+                             const float* cw, int ck, const float* norm_w, float eps, int one_plus_w, float delta_scale, void* h_out, void* y,
+                             const float* bias, int M, int N, int K, int out_f32, int route, const float* route_bias, int Kt, int renorm,
+                             int* topk_idx, float* topk_w, int w_copies, void* xq, void* sfx, int max_tiles, cudaStream_t st) {
+  if (M < 1 || M > GS_NORM_MAX_M || K % 8 || K > GS_NORM_MAX_K || ck > GS_MAX_CK) return 1;
+  if ((delta || yp) && (!x_out || x_out == x)) return -150;
+  GsNorm nm;
+  nm.x = x; nm.x_out = (delta || yp) ? x_out : nullptr; nm.delta = yp ? nullptr : (const __nv_bfloat16*)delta;
+  nm.yp = (const __nv_bfloat16*)yp; nm.pos = pos; nm.cw = cw; nm.ck = yp ? ck : 0;
+  nm.w = norm_w; nm.eps = eps; nm.delta_scale = delta_scale; nm.one_plus_w = one_plus_w; nm.h_out = (__nv_bfloat16*)h_out;
+  GsRoute rt;
+  rt.ticket = nullptr;
+  if (route) {
+    if (!out_f32 || N > 1024 || Kt > 32 || Kt > N || K % 32 || max_tiles < M * Kt) return -151;
+    static int* base[64] = {nullptr};
+    static unsigned turn[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!base[dev]) {
+      void* a = nullptr;
+      if (cudaGetSymbolAddress(&a, g_gs_tickets) != cudaSuccess) return -152;
+      base[dev] = (int*)a;
+    }
+    rt.ticket = base[dev] + turn[dev]++ % GS_TICKET_SLOTS;
+    rt.bias = route_bias; rt.Kt = Kt; rt.renorm = renorm; rt.topk_idx = topk_idx; rt.topk_w = topk_w; rt.w_copies = w_copies < 1 ? 1 : w_copies;
+    rt.xq = (uint8_t*)xq; rt.sfx = (uint8_t*)sfx; rt.KB = (K + MXF_KBLOCK - 1) / MXF_KBLOCK; rt.max_tiles = max_tiles;
+  }
+  return gemv_stream_fused(wfmt, WeightRef{w0, w1, nullptr, nullptr}, x, y, bias, M, N, K, out_f32, 0, 0.f, 0.f, nullptr, nullptr, 0, 1, 0, 1 << 30,
+                           nullptr, &nm, route ? &rt : nullptr, st);
+}

@@ -1,12 +1,13 @@
 // Router top-k for one token, executed by one warp: weights = softmax over the selected logits (renorm) or softmax over all.
-// Lane k < K ends up holding the k-th selection; E <= 1024, K <= 32.
+// Lane k < K ends up holding the k-th selection; E <= 1024, K <= 32.  The logits are read past L1: the caller may be the last CTA
+// of the kernel that produced them.
 #pragma once
 #include "common.cuh"
 
 namespace mx {
 
 __device__ __forceinline__ void route_token_warp(const float* __restrict__ logits, const float* __restrict__ bias, int t, int E, int K, int renorm,
-                                                 int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+                                                 int* __restrict__ topk_idx, float* __restrict__ topk_w, int w_copies = 1) {
   const int lane = threadIdx.x & 31;
   float v[32];
   const int per = (E + 31) / 32;
@@ -14,7 +15,7 @@ __device__ __forceinline__ void route_token_warp(const float* __restrict__ logit
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     const int e = lane + 32 * i;
-    v[i] = (i < per && e < E) ? logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f) : -INFINITY;
+    v[i] = (i < per && e < E) ? __ldcg(logits + (size_t)t * E + e) + (bias ? bias[e] : 0.f) : -INFINITY;
     mx_all = fmaxf(mx_all, v[i]);
   }
   mx_all = warp_max(mx_all);
@@ -45,7 +46,9 @@ __device__ __forceinline__ void route_token_warp(const float* __restrict__ logit
   }
   if (lane < K) {
     topk_idx[(size_t)t * K + lane] = my_e;
-    topk_w[(size_t)t * K + lane] = my_w / (renorm ? sel_sum : denom_all);
+    // w_copies > 1: the weight row is [w_copies][K] (a consumer that sums several partial rows per pair reads one weight per partial)
+    const float wv = my_w / (renorm ? sel_sum : denom_all);
+    for (int c = 0; c < w_copies; ++c) topk_w[((size_t)t * w_copies + c) * K + lane] = wv;
   }
 }
 

@@ -223,7 +223,10 @@ class AttentionBlock:
         self.norm_one_plus_w = c.arch in ("qwen35", "qwen35moe")      # Qwen3-Next files store 1 + w already
 
     def __call__(self, h: torch.Tensor, fb: ForwardBatch, kv: KVCache, rope, par: ParallelCtx) -> torch.Tensor:
-        qkv = self.qkv(h)
+        return self.attend(self.qkv(h), fb, kv, rope, par)
+
+    def attend(self, qkv: torch.Tensor, fb: ForwardBatch, kv: KVCache, rope, par: ParallelCtx) -> torch.Tensor:
+        """Everything after the qkv projection: head epilogue + cache write, attention, output projection."""
         q, gate = ops.qkv_post(qkv, None, self.q_norm, self.k_norm, fb.positions, rope[0], rope[1], fb.slot_map, kv.k[self.layer],
                                kv.v[self.layer], self.n_q, self.n_kv, self.hd, self.n_rot, q_gate=self.q_gate,
                                norm_one_plus_w=self.norm_one_plus_w, eps=self.eps, kv_scales=kv.scales(self.layer),
@@ -385,9 +388,16 @@ class MoEFFN:
         """Returns this rank's fp32 contribution [T, H] (already reduced when EP > 1).  ``router_h``: the router's own input
         when it differs from the experts' (Gemma-4)."""
         T = h.shape[0]
-        logits = self.router(h if router_h is None else router_h, out_f32=True)
         pre = None
-        if self.mx is not None and T <= self.MXF4_PAIR_MAX_TOKENS:
+        ksplit = 1
+        if not isinstance(router_h, tuple):
+            logits = self.router(h if router_h is None else router_h, out_f32=True)
+        if isinstance(router_h, tuple):
+            # decode: the router GEMV's launch has already routed and quantised the rows (ops.cuda.gemv_norm)
+            idx, w, xq, sfx = router_h
+            pre = (xq, sfx)
+            ksplit = w.shape[1] // self.K
+        elif self.mx is not None and T <= self.MXF4_PAIR_MAX_TOKENS:
             # decode: routing and the MXFP8 rounding of the token rows share one launch
             from ..ops.cuda import moe_route_quant
             idx, w, xq, sfx = moe_route_quant(logits, self.router_bias, self.K, h)
@@ -400,7 +410,7 @@ class MoEFFN:
         # expert parallelism on the peer-memory path: the combine writes its partial into every rank's inbox itself
         fuse_push = self.reduce and par.fused is not None and h.is_cuda and self.shared is None
         if self.mx is not None:
-            y, p2p = self._mx_experts(h, idx, pre)
+            y, p2p = self._mx_experts(h, idx, pre, ksplit)
             if fuse_push:
                 return par.fused.moe_combine_push(y, p2p, w)
             if self.shared is None and not self.reduce and self.K <= 32:
@@ -456,9 +466,10 @@ class MoEFFN:
         return out
 
 
-def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor, pre=None):
+def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor, pre=None, ksplit: int = 1):
     """Expert projections on the block-scaled MXFP4 kernel.  Returns (y bf16 [rows, H], pair_to_packed int32 [T*K]).  ``pre``: the
-    pair-mode (xq, sfx) when the router launch has already quantised the rows."""
+    pair-mode (xq, sfx) when the router launch has already quantised the rows.  ``ksplit`` (pair mode): the down projection leaves
+    that many partial rows per pair, and pair_to_packed lists them all ([T, ksplit, K])."""
     from ..ops import cuda as K_
     gate_up, down = self.mx
     T = h.shape[0]
@@ -469,10 +480,13 @@ def _mx_experts(self, h: torch.Tensor, idx: torch.Tensor, pre=None):
         te = idx.reshape(-1)
         xq, sfx = pre if pre is not None else K_.moe_quant(h, n, n, 1, x_div=self.K)
         aq, sfa = K_.mxf4_gemm(gate_up, xq, sfx, te, n, 1, default_valid=1, bias0=self.g_bias, bias1=self.u_bias, act=self.act, **ep)
-        y = K_.mxf4_gemm(down, aq, sfa, te, n, 1, default_valid=1, bias0=self.down_bias, zero_out=self.reduce, **ep)
-        key = (T, h.device)
+        y = K_.mxf4_gemm(down, aq, sfa, te, n, 1, default_valid=1, bias0=self.down_bias, zero_out=self.reduce, ksplit=ksplit, **ep)
+        key = (T, ksplit, h.device)
         if key not in self._arange:
-            self._arange[key] = torch.arange(n, dtype=torch.int32, device=h.device)
+            # pair (t, k) sits at row t * K + k of every K range's block of n rows
+            base = torch.arange(n, dtype=torch.int32, device=h.device).reshape(T, 1, self.K)
+            off = (torch.arange(ksplit, dtype=torch.int32, device=h.device) * n).reshape(1, ksplit, 1)
+            self._arange[key] = (base + off).reshape(-1).contiguous()
         return y, self._arange[key]
     pk = ops.moe_pack(idx, self.E, self.e_lo, self.e_hi)
     mt = pk.tile_expert.numel()
@@ -635,8 +649,46 @@ class TransformerModel:
             logits = torch.tanh(logits / c.final_logit_softcap) * c.final_logit_softcap
         return logits
 
+    FUSED_DECODE = True      # class switch: tests compare the fused decode chain with the kernel-per-op one
+    FUSED_DECODE_QKV = True      # ... the attention norm inside the qkv GEMV
+    FUSED_DECODE_ROUTER = True   # ... the FFN norm, routing and quantisation inside the router GEMV
+    DOWN_KSPLIT = 2              # one-token decode: K ranges of the experts' down projection (1 = no split)
+
+    def _run_layers_decode(self, x, delta, fb, kv):
+        """Single-rank decode (one or two rows): both norms of a layer run inside the GEMV that consumes them (qkv; router, whose launch
+        also routes and quantises), so a layer is qkv -> head epilogue -> attention -> o-proj -> router -> gate|up -> down."""
+        from ..ops import cuda as K_
+        c, par = self.cfg, self.par
+        nk = dict(one_plus_w=self.one_plus_w, delta_scale=c.residual_scale)
+        for L in self.layers:
+            at = L["attn"]
+            r = None
+            if self.FUSED_DECODE_QKV and isinstance(at.qkv, Linear):
+                r = K_.gemv_norm(x, L["attn_norm"], c.rms_eps, at.qkv.w, at.qkv.bias, delta=delta, **nk)
+            if r is None:
+                qkv = at.qkv(self._norm(x, L["attn_norm"], delta))
+            else:
+                qkv, x, _ = r
+            a = at.attend(qkv, fb, kv, self.rope, par)
+            moe = L.get("moe")
+            r = None
+            if self.FUSED_DECODE_ROUTER and moe is not None and moe.mx is not None and moe.expert_scale is None and moe.shared is None:
+                # with one token the down projection has too few (pair, column block) items for the chip: it splits K in two
+                copies = self.DOWN_KSPLIT if x.shape[0] * moe.K <= 4 else 1
+                r = K_.gemv_norm(x, L["ffn_norm"], c.rms_eps, moe.router.w, moe.router.bias, delta=a, route=(moe.router_bias, moe.K, True, copies), **nk)
+            if r is not None:
+                _, x, _, idx, w, xq, sfx = r
+                delta = moe(a, par, router_h=(idx, w, xq, sfx))        # (`a` only gives the row count here)
+            else:
+                h2 = self._norm(x, L["ffn_norm"], a)
+                delta = moe(h2, par) if moe is not None else L["ffn"](h2, par)
+        return x, delta
+
     def _run_layers(self, x, delta, fb, kv, state):
         par = self.par
+        if (self.FUSED_DECODE and x.is_cuda and x.shape[0] <= 2 and par.world == 1 and self.tap is None and state is None
+                and type(self) is TransformerModel and ops.backend() != "torch"):
+            return self._run_layers_decode(x, delta, fb, kv)
         for li, L in enumerate(self.layers):
             h = self._norm(x, L["attn_norm"], delta)
             a = self._mixer(li, L, h, fb, kv, state)

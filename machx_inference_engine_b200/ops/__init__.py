@@ -31,6 +31,10 @@ def set_backend(name: str) -> None:
     _BACKEND[0] = name
 
 
+def backend() -> str:
+    return _BACKEND[0]
+
+
 def _first_tensor(args, kwargs):
     import torch
     for a in list(args) + list(kwargs.values()):

@@ -419,7 +419,7 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
         _check(_lib.cuda().mx_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), _p(seq_lens), _p(cu_q), _p(sinks), _p(out),
                                         _p(o_part), _p(ml_part), B, Tq, int(max_q_len), n_q, n_kv, hd, block_table.shape[1], bs, int(window),
                                         C.c_float(scale), C.c_float(softcap), int(n_splits), _stream()), "attention")
-    _count(2)
+    _count(_lib.cuda().mx_attention_launches(B, int(max_q_len), n_q, n_kv))
     return out
 
 
@@ -484,13 +484,63 @@ def moe_route_quant(logits, bias, k, x, renorm=True):
     return idx, w, xq, sfx
 
 
+GEMV_NORM_MAX_M = 2      # the fused prologue normalises its rows one after the other; more rows take the separate kernel
+
+
+@_profiled("gemv_norm")
+def gemv_norm(x, norm_w, eps, w: QuantWeight, bias=None, delta=None, one_plus_w=False, delta_scale=1.0, out_f32=False, want_h=False, route=None):
+    """Decode (at most GEMV_NORM_MAX_M rows of at most 4096 elements): residual add + RMSNorm + dense GEMV in one launch (``csrc/cuda/gemv_stream.cu``).  ``x`` fp32 [T, H] is
+    not modified; ``delta`` is None, a bf16 [T, H] tensor or a :class:`CombineDelta`.  Returns None when the shape or the weight format
+    is not taken, else ``(y, x_new, h)``: the product, the updated residual (``x`` itself without a delta) and, with ``want_h``, the
+    normalised rows.  ``route = (router_bias, k, renorm, w_copies)`` makes ``w`` the router: the last CTA also picks the top-k experts
+    and writes the rows as MXFP8 pair tiles, and the result is ``(logits, x_new, h, idx, topk_w, xq, sfx)`` with ``topk_w`` of shape
+    [T, w_copies * k] (the k weights repeated: one per partial row when the down projection splits K)."""
+    T, H = x.shape
+    if T > GEMV_NORM_MAX_M or H > 4096 or w.E != 1 or w.fmt not in (WFormat.BF16, WFormat.Q8) or x.dtype != torch.float32 or not x.is_contiguous():
+        return None
+    comb = delta if isinstance(delta, CombineDelta) else None
+    if delta is not None and comb is None and not (isinstance(delta, torch.Tensor) and delta.dtype == torch.bfloat16 and delta.is_contiguous()):
+        return None
+    if comb is not None and comb.w.shape[1] > 8:
+        return None
+    dev = x.device
+    fmt, p0, p1, _, _ = _planes(w)
+    y = torch.empty(T, w.N, dtype=torch.float32 if (out_f32 or route is not None) else torch.bfloat16, device=dev)
+    x_new = torch.empty_like(x) if delta is not None else x
+    h = torch.empty(T, H, dtype=torch.bfloat16, device=dev) if want_h else None
+    idx = tw = xq = sfx = None
+    rb, k, renorm, n, copies = None, 0, 1, 0, 1
+    if route is not None:
+        rb, k, renorm, copies = route
+        KB = (H + 127) // 128
+        n = T * k
+        idx = torch.empty(T, k, dtype=torch.int32, device=dev)
+        tw = torch.empty(T, copies * k, dtype=torch.float32, device=dev)
+        xq = torch.empty(n, KB * 128, dtype=torch.uint8, device=dev)
+        sfx = torch.empty(KB, n, 512, dtype=torch.uint8, device=dev)
+    rc = _lib.cuda().mx_gemv_norm(fmt, p0, p1, _p(x), _p(x_new) if delta is not None else _vp(0), _p(delta) if (delta is not None and comb is None) else _vp(0),
+                                  _p(comb.y) if comb is not None else _vp(0), _p(comb.pair_to_packed) if comb is not None else _vp(0),
+                                  _p(comb.w) if comb is not None else _vp(0), comb.w.shape[1] if comb is not None else 0, _p(norm_w), C.c_float(eps),
+                                  int(one_plus_w), C.c_float(delta_scale), _p(h), _p(y), _p(bias), T, w.N, w.K, int(y.dtype == torch.float32),
+                                  int(route is not None), _p(rb), k, int(bool(renorm)), _p(idx), _p(tw), copies, _p(xq), _p(sfx), n, _stream())
+    if rc == 1:
+        return None
+    _check(rc, "gemv_norm")
+    _count()
+    if route is not None:
+        return y, x_new, h, idx, tw, xq, sfx
+    return y, x_new, h
+
+
 @_profiled("mxf4_gemm")
 def mxf4_gemm(w: QuantWeight, xq, sfx, tile_expert, max_tiles, row_stride, tile_valid=None, default_valid=128, num_tiles=None, e_lo=0,
-              bias0=None, bias1=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, zero_out=False):
+              bias0=None, bias1=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, zero_out=False, ksplit=1):
     """Block-scaled MXFP4 x MXFP8 grouped GEMM on the tensor cores (``csrc/cuda/gemm_mxf4.cu``).  ``w`` is an MXF4T bank and
     ``xq``/``sfx`` come from :func:`moe_quant` or from a gated call of this function.  A plain bank returns bf16 [rows, N]; a gated
     pair (``w.dual``, with ``act``) returns the activation already quantised for the next projection: (oq [rows, N rounded up to
-    128] uint8, osf scale atoms).  Rows that belong to no live tile are left unwritten unless ``zero_out``."""
+    128] uint8, osf scale atoms).  Rows that belong to no live tile are left unwritten unless ``zero_out``.  ``ksplit`` > 1 (plain banks):
+    K is cut into that many ranges and the result has ``ksplit`` x rows rows, range s in rows [s * rows, (s + 1) * rows): partial sums
+    that the consumer adds (decode, where a handful of pairs would otherwise leave most SMs idle)."""
     assert w.fmt == WFormat.MXF4T
     rows = xq.shape[0]
     dev = xq.device
@@ -501,10 +551,14 @@ def mxf4_gemm(w: QuantWeight, xq, sfx, tile_expert, max_tiles, row_stride, tile_
         oq = torch.empty(rows, oq_ld, dtype=torch.uint8, device=dev)
         osf = torch.empty(oq_ld // 128, max_tiles, 512, dtype=torch.uint8, device=dev)
     else:
-        out = (torch.zeros if zero_out else torch.empty)(rows, w.N, dtype=torch.bfloat16, device=dev)
+        if ksplit > 1:
+            kb = (w.K + 127) // 128
+            per = (kb + ksplit - 1) // ksplit
+            ksplit = (kb + per - 1) // per
+        out = (torch.zeros if zero_out else torch.empty)(ksplit * rows, w.N, dtype=torch.bfloat16, device=dev)
     _check(_lib.cuda().mx_mxf4_gemm(_p(w.p0), _p(w.p1), int(w.dual), w.E, _p(xq), _p(sfx), rows, w.N, w.K, _p(tile_expert), _p(tile_valid),
                                     int(default_valid), _p(num_tiles), int(max_tiles), int(row_stride), int(e_lo), _p(bias0), _p(bias1),
-                                    _p(out), w.N, _p(oq), _p(osf), oq_ld, int(act), C.c_float(act_alpha), C.c_float(act_limit), _stream()),
+                                    _p(out), w.N, _p(oq), _p(osf), oq_ld, int(act), C.c_float(act_alpha), C.c_float(act_limit), int(ksplit), _stream()),
            "mxf4 gemm")
     _count()
     return (oq, osf) if w.dual else out

@@ -204,3 +204,40 @@ def test_decode_graph_survives_growth_of_the_shared_attention_scratch():
     K.check_status()
     assert outs[True] == outs[False], outs
     assert outs[True][0] == outs[True][2]
+
+
+@pytest.mark.parametrize("name,quant", [("tiny-gpt-oss", "mxfp4"), ("tiny-llama", "q8_0"), ("tiny-qwen3", "bf16")])
+@pytest.mark.parametrize("B", [1, 2])
+def test_fused_decode_chain_matches_the_kernel_per_op_chain(name, quant, B):
+    """A decode step with the norms inside the GEMVs (and, for MXFP4 experts, routing + quantisation in the router's launch and a
+    K-split down projection) against the same step running one kernel per op, from the same cache state: the logits agree up to
+    summation order and the bf16 rounding of the split partial sums."""
+    from machx_inference_engine_b200.models.transformer import KV_BLOCK, ForwardBatch, TransformerModel
+    cfg = preset(name)
+    d = torch.device("cuda:0")
+    m = build_model(cfg, d, quant=quant, max_ctx=512, gen_device="cpu")
+    kv = m.new_kv_cache(2 * B + 1)
+    g = torch.Generator().manual_seed(6)
+    P = 70
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=d)
+    bt = torch.arange(1, 2 * B + 1, dtype=torch.int32, device=d).reshape(B, 2)
+    for b in range(B):                                    # prefill each sequence (more than 8 rows: not the fused chain)
+        ids = torch.randint(0, cfg.vocab, (P,), generator=g).to(d).to(torch.int32)
+        pos = torch.arange(P, dtype=torch.int32, device=d)
+        slot = bt[b][(pos // KV_BLOCK).long()].long() * KV_BLOCK + (pos % KV_BLOCK).long()
+        m.forward(ForwardBatch(ids, pos, slot, bt[b:b + 1], i32([P]), i32([0, P]), P), kv)
+    ids = torch.randint(0, cfg.vocab, (B,), generator=g).to(d).to(torch.int32)
+    pos = i32([P] * B)
+    slot = bt[:, 0].long() * KV_BLOCK + P
+    fb = ForwardBatch(ids, pos, slot, bt, i32([P + 1] * B), i32(list(range(B + 1))), 1)
+    out = {}
+    try:
+        for fused in (True, False):
+            TransformerModel.FUSED_DECODE = fused
+            out[fused] = m.forward(fb, kv).float()
+    finally:
+        TransformerModel.FUSED_DECODE = True
+    from machx_inference_engine_b200.ops import cuda as K
+    K.check_status()
+    assert _cos(out[True], out[False]) > (0.998 if quant == "mxfp4" else 0.9999)
+    assert (out[True].argmax(-1) == out[False].argmax(-1)).all()

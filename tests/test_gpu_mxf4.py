@@ -238,3 +238,77 @@ def test_decode_fusions_match_their_unfused_forms():
     out2 = K().rmsnorm_combine(x2, nw, 1e-5, d, delta_scale=0.5)
     K().check_status()
     assert torch.equal(x1, x2) and torch.equal(out1, out2)
+
+
+def test_down_projection_k_split_partials_add_up():
+    """ksplit = 2 leaves two partial rows per pair (k-blocks [0, 12) and [12, 23) of K = 2880); their sum is the unsplit product up to
+    the bf16 rounding of each partial, and the bias is added once."""
+    torch.manual_seed(12)
+    E, topk, H, F = 8, 4, 512, 2880
+    d, dt = bank(H, F, E, 13)
+    bias = torch.randn(E, H, device=dev()) * 0.1
+    a = torch.randn(1, F, device=dev()).to(torch.bfloat16)
+    te = torch.tensor([5, 1, 6, 2], dtype=torch.int32, device=dev())
+    aq, sfa = K().moe_quant(a, topk, topk, 1, x_div=topk)
+    y1 = K().mxf4_gemm(dt, aq, sfa, te, topk, 1, default_valid=1, bias0=bias)
+    y2 = K().mxf4_gemm(dt, aq, sfa, te, topk, 1, default_valid=1, bias0=bias, ksplit=2)
+    K().check_status()
+    assert y2.shape == (2 * topk, H)
+    assert rel_err(y2[:topk].float() + y2[topk:].float(), y1) < 8e-3
+    Wd = d.dequantize()
+    aw = decode_quant(aq, sfa, topk, F, 1)
+    for i in range(topk):
+        e = int(te[i])
+        lo = aw[i:i + 1, :12 * 128] @ Wd[e][:, :12 * 128].t() + bias[e]
+        hi = aw[i:i + 1, 12 * 128:] @ Wd[e][:, 12 * 128:].t()
+        assert rel_err(y2[i:i + 1], lo) < 6e-3 and rel_err(y2[topk + i:topk + i + 1], hi) < 6e-3, i
+
+
+@pytest.mark.parametrize("T,kind", [(1, "none"), (2, "bf16"), (1, "combine"), (2, "combine")])
+def test_norm_fused_into_the_gemv_and_router_tail(T, kind):
+    """Residual add + RMSNorm inside the GEMV that consumes it, against the separate kernels; the router form also routes and writes
+    the MXFP8 pair tiles in the same launch."""
+    torch.manual_seed(20 + T)
+    H, N, E, topk = 2880, 640, 32, 4
+    res = torch.randn(T, H, device=dev())
+    nw = torch.rand(H, device=dev()) + 0.5
+    w = from_dense(torch.randn(1, N, H) * 0.02, WFormat.BF16).to(dev())
+    bias = torch.randn(N, device=dev()) * 0.1
+    delta = None
+    if kind == "bf16":
+        delta = torch.randn(T, H, device=dev()).to(torch.bfloat16)
+    elif kind == "combine":
+        y = torch.randn(T * topk + 2, H, device=dev()).to(torch.bfloat16)
+        p2p = torch.randperm(T * topk + 2, device=dev())[:T * topk].to(torch.int32)
+        p2p[1] = -1
+        delta = K().CombineDelta(y, p2p, torch.rand(T, topk, device=dev()))
+    assert K().gemv_norm(torch.randn(3, H, device=dev()), nw, 1e-5, w, bias) is None        # more rows: not taken
+    # separate kernels
+    x1 = res.clone()
+    if kind == "combine":
+        h1 = K().rmsnorm_combine(x1, nw, 1e-5, delta, delta_scale=0.5)
+    else:
+        h1 = K().rmsnorm(x1, nw, 1e-5, delta=delta, delta_scale=0.5)
+    y1 = K().linear(h1, w, bias=bias)
+    # fused
+    x0 = res.clone()
+    y2, x2, h2 = K().gemv_norm(x0, nw, 1e-5, w, bias, delta=delta, delta_scale=0.5, want_h=True)
+    K().check_status()
+    assert torch.equal(x0, res)                                  # the input residual is not modified
+    assert rel_err(x2, x1) < 1e-6 and rel_err(h2, h1) < 4e-3 and rel_err(y2, y1) < 6e-3
+    # router form
+    rw = from_dense(torch.randn(1, E, H) * 0.05, WFormat.BF16).to(dev())
+    rb = torch.randn(E, device=dev()) * 0.1
+    for copies in (1, 2):
+        logits, x3, h3, idx, tw, xq, sfx = K().gemv_norm(res.clone(), nw, 1e-5, rw, None, delta=delta, delta_scale=0.5, want_h=True,
+                                                         route=(rb, topk, True, copies))
+        K().check_status()
+        assert torch.equal(h3, h2) and torch.equal(x3, x2)
+        idx_w, tw_w = K().moe_route(logits, rb, topk)
+        xq_w, sfx_w = K().moe_quant(h3, T * topk, T * topk, 1, x_div=topk)
+        assert torch.equal(idx, idx_w) and torch.equal(xq, xq_w)
+        assert torch.equal(tw.reshape(T, copies, topk), tw_w.unsqueeze(1).expand(T, copies, topk))
+        rows = torch.arange(T * topk, device=dev())
+        for kb in range(sfx.shape[0]):
+            assert torch.equal(sfx[kb, rows, :4], sfx_w[kb, rows, :4])
+        assert rel_err(logits, K().linear(h3, rw, out_f32=True)) < 1e-5
