@@ -42,7 +42,7 @@ def _load(a):
     from ..formats.memory_plan import plan_placement
     if par.rank == 0:
         print(plan_placement(a.model, n_gpus=max(par.world, 1), ctx=a.ctx).describe(), file=sys.stderr)
-    return Engine.load(a.model, dev, _engine_options(a), par), par
+    return Engine.load(a.model, dev, _engine_options(a), par, spec_head=a.spec_head), par
 
 
 def main(argv=None) -> int:
@@ -59,7 +59,7 @@ def main(argv=None) -> int:
         p.add_argument("--int8-kv", action="store_true", help="store K/V rows as int8 with a per-row scale (half the cache memory)")
         p.add_argument("--spec", action="store_true")
         p.add_argument("--spec-k", type=int, default=3)
-        p.add_argument("--spec-head", default=None)
+        p.add_argument("--spec-head", default=None, help="draft-head GGUF for --spec (Gemma-4: the gemma4-assistant file)")
         p.add_argument("--cpu", action="store_true")
 
     p = sub.add_parser("run"); common(p)

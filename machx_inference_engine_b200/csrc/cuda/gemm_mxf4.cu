@@ -473,11 +473,11 @@ __global__ void __launch_bounds__(128) moe_quant_kernel(const __nv_bfloat16* __r
 // all threads round the token's row to MXFP8; the row is then written once per (token, slot) pair, each pair being its own
 // one-row tile of the grouped GEMM (pair mode of mx_mxf4_gemm).
 __global__ void __launch_bounds__(128) moe_route_quant_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int E, int Kt, int renorm,
-                                                              int* __restrict__ topk_idx, float* __restrict__ topk_w, const __nv_bfloat16* __restrict__ x,
+                                                              int* __restrict__ topk_idx, float* __restrict__ topk_w, int w_copies, const __nv_bfloat16* __restrict__ x,
                                                               int ldx, int K, int KB, int max_tiles, uint8_t* __restrict__ xq, uint8_t* __restrict__ sfx) {
   pdl_prologue();
   const int t = blockIdx.x;
-  if ((threadIdx.x >> 5) == 0) route_token_warp(logits, bias, t, E, Kt, renorm, topk_idx, topk_w);
+  if ((threadIdx.x >> 5) == 0) route_token_warp(logits, bias, t, E, Kt, renorm, topk_idx, topk_w, w_copies);
   const int Kp = KB * XT_K;
   for (int blk = threadIdx.x; blk < KB * 4; blk += blockDim.x) {
     const int k0 = blk * 32;
@@ -570,13 +570,14 @@ MX_HOST_API int mx_moe_quant(const void* x, int ldx, const int* src_index, int x
 }
 
 // Router top-k (see mx_moe_route) and MXFP8 quantisation of T token rows in pair mode: xq [T*Kt][KB*128], sfx [KB][max_tiles][512]
-// with max_tiles >= T*Kt; pair t*Kt+k is tile t*Kt+k.
-MX_HOST_API int mx_moe_route_quant(const float* logits, const float* bias, int T, int E, int Kt, int renorm, int* topk_idx, float* topk_w,
+// with max_tiles >= T*Kt; pair t*Kt+k is tile t*Kt+k.  topk_w is [T][w_copies][Kt]: the weights repeated (one per partial row when
+// the down projection that follows splits K).
+MX_HOST_API int mx_moe_route_quant(const float* logits, const float* bias, int T, int E, int Kt, int renorm, int* topk_idx, float* topk_w, int w_copies,
                                    const void* x, int ldx, int K, int max_tiles, void* xq, void* sfx, cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > 1024 || Kt > 32 || Kt > E || K % 32 || ldx % 8 || max_tiles < T * Kt) return -120;
   const int KB = (K + XT_K - 1) / XT_K;
-  launch_pdl(moe_route_quant_kernel, dim3(T), dim3(128), 0, st, logits, bias, E, Kt, renorm, topk_idx, topk_w, (const __nv_bfloat16*)x, ldx, K, KB,
+  launch_pdl(moe_route_quant_kernel, dim3(T), dim3(128), 0, st, logits, bias, E, Kt, renorm, topk_idx, topk_w, w_copies < 1 ? 1 : w_copies, (const __nv_bfloat16*)x, ldx, K, KB,
              max_tiles, (uint8_t*)xq, (uint8_t*)sfx);
   return (int)cudaGetLastError();
 }

@@ -258,3 +258,46 @@ def write_synthetic_gguf(cfg: ModelConfig, path: str, quant: str = "q8_0", seed:
     w.write(path)
     import os
     return {"tensors": n, "bytes": os.path.getsize(path)}
+
+
+def assistant_tensor_plan(a) -> list:
+    """Tensors of a ``gemma4-assistant`` head file (src/model/gemma4_assistant.cpp:75-150); ``a`` is an
+    ``models.gemma4_assistant.AssistantConfig``."""
+    H, BB = a.hidden, a.backbone
+    out = [("token_embd.weight", "matrix", (H, a.vocab)), ("output_norm.weight", "norm", (H,)),
+           ("nextn.pre_projection.weight", "matrix", (2 * BB, H)), ("nextn.post_projection.weight", "matrix", (H, BB))]
+    for l in range(a.n_layers):
+        p, hd = f"blk.{l}", a.head_dim[l]
+        out += [(f"{p}.attn_norm.weight", "norm", (H,)), (f"{p}.attn_q_norm.weight", "qnorm", (hd,)),
+                (f"{p}.post_attention_norm.weight", "norm", (H,)), (f"{p}.ffn_norm.weight", "norm", (H,)),
+                (f"{p}.post_ffw_norm.weight", "norm", (H,)), (f"{p}.layer_output_scale.weight", "norm", (1,)),
+                (f"{p}.attn_q.weight", "matrix", (H, a.n_q_heads * hd)), (f"{p}.attn_output.weight", "matrix", (a.n_q_heads * hd, H)),
+                (f"{p}.ffn_gate.weight", "matrix", (H, a.ffn)), (f"{p}.ffn_up.weight", "matrix", (H, a.ffn)), (f"{p}.ffn_down.weight", "matrix", (a.ffn, H))]
+    return out
+
+
+def write_synthetic_assistant_gguf(a, path: str, quant: str = "q8_0", seed: int = 0) -> dict:
+    """Random-init ``gemma4-assistant`` head for a Gemma-4 target (``a``: AssistantConfig), with the metadata keys its loader reads."""
+    w = GGUFWriter()
+    k = lambda s: f"gemma4-assistant.{s}"
+    swa = [i for i, s in enumerate(a.is_swa) if s]
+    glb = [i for i, s in enumerate(a.is_swa) if not s]
+    kv = {"general.architecture": "gemma4-assistant", "general.name": "synthetic gemma4 assistant head", k("block_count"): a.n_layers,
+          k("embedding_length"): a.hidden, k("feed_forward_length"): a.ffn, k("attention.head_count"): a.n_q_heads,
+          k("attention.head_count_kv"): [int(v) for v in a.n_kv_heads], k("attention.layer_norm_rms_epsilon"): float(a.rms_eps),
+          k("attention.sliding_window"): a.sliding_window, k("attention.sliding_window_pattern"): [bool(s) for s in a.is_swa]}
+    if glb:
+        kv.update({k("attention.key_length"): a.head_dim[glb[0]], k("rope.dimension_count"): a.n_rot[glb[0]], k("rope.freq_base"): float(a.rope_theta[glb[0]])})
+    if swa:
+        kv.update({k("attention.key_length_swa"): a.head_dim[swa[0]], k("rope.dimension_count_swa"): a.n_rot[swa[0]],
+                   k("rope.freq_base_swa"): float(a.rope_theta[swa[0]])})
+    for key, v in kv.items():
+        w.add_kv(key, v)
+    n = 0
+    for name, kind, dims in assistant_tensor_plan(a):
+        t = _matrix_type(name, kind, dims[0], quant, a.n_layers) if kind == "matrix" else GGMLType.F32
+        w.add_tensor(name, dims, int(t), _payload("assistant." + name, kind, dims, int(t), seed))
+        n += 1
+    w.write(path)
+    import os
+    return {"tensors": n, "bytes": os.path.getsize(path)}

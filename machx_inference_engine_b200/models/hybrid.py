@@ -205,9 +205,10 @@ class MtpHead:
         self._bt = torch.zeros(1, 1, dtype=torch.int32, device=dev)
         self._cu = torch.tensor([0, 1], dtype=torch.int32, device=dev)
 
-    def draft(self, h_last: torch.Tensor, tok: int, k: int) -> list:
+    def draft(self, h_last: torch.Tensor, tok: int, k: int, ctx=None) -> list:
         """Greedy draft of ``k`` tokens from the hidden state (fp32 [1, H], before the final norm) of the last
-        committed position and the token sampled there."""
+        committed position and the token sampled there.  (``ctx``, the engine's view of the sequence, is not needed: this head keeps
+        its own one-page cache.)"""
         m, c = self.model, self.model.cfg
         dev = m.device
         out = []

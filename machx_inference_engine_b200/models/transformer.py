@@ -332,6 +332,7 @@ class MoEFFN:
 
     MXF4_TENSOR_CORE = True      # class switch (tests compare against the bf16-activation path by turning it off)
     MXF4_PAIR_MAX_TOKENS = 8     # up to this many tokens every (token, expert) pair is its own tile: no packing pass
+    DOWN_KSPLIT = 3              # one-token decode: K ranges of the down projection (their partial rows are summed by the combine)
 
     def __init__(self, cfg: ModelConfig, layer: int, src, par: ParallelCtx, act: int, with_bias: bool, prefix: Optional[str] = None):
         c = cfg
@@ -400,7 +401,10 @@ class MoEFFN:
         elif self.mx is not None and T <= self.MXF4_PAIR_MAX_TOKENS:
             # decode: routing and the MXFP8 rounding of the token rows share one launch
             from ..ops.cuda import moe_route_quant
-            idx, w, xq, sfx = moe_route_quant(logits, self.router_bias, self.K, h)
+            # one token on one rank: the down projection has too few (pair, column block) items for the chip and splits K
+            if T * self.K <= 4 and not self.reduce and self.shared is None and self.expert_scale is None:
+                ksplit = self.DOWN_KSPLIT
+            idx, w, xq, sfx = moe_route_quant(logits, self.router_bias, self.K, h, w_copies=ksplit)
             pre = (xq, sfx)
         else:
             idx, w = ops.moe_route(logits, self.router_bias, self.K, True)
@@ -649,10 +653,12 @@ class TransformerModel:
             logits = torch.tanh(logits / c.final_logit_softcap) * c.final_logit_softcap
         return logits
 
-    FUSED_DECODE = True      # class switch: tests compare the fused decode chain with the kernel-per-op one
+    # Decode with the norms inside the GEMVs that consume them (ops.cuda.gemv_norm).  Measured on gpt-oss-120b / 20b decode at
+    # context 2048: 3.87 / 2.65 ms per token against 3.70 / 2.50 with one kernel per op: every CTA of the GEMV repeats the norm's
+    # reads from L2, which costs more than the launch it saves under programmatic dependent launch.  Off; tests keep it honest.
+    FUSED_DECODE = False
     FUSED_DECODE_QKV = True      # ... the attention norm inside the qkv GEMV
     FUSED_DECODE_ROUTER = True   # ... the FFN norm, routing and quantisation inside the router GEMV
-    DOWN_KSPLIT = 2              # one-token decode: K ranges of the experts' down projection (1 = no split)
 
     def _run_layers_decode(self, x, delta, fb, kv):
         """Single-rank decode (one or two rows): both norms of a layer run inside the GEMV that consumes them (qkv; router, whose launch
@@ -674,7 +680,7 @@ class TransformerModel:
             r = None
             if self.FUSED_DECODE_ROUTER and moe is not None and moe.mx is not None and moe.expert_scale is None and moe.shared is None:
                 # with one token the down projection has too few (pair, column block) items for the chip: it splits K in two
-                copies = self.DOWN_KSPLIT if x.shape[0] * moe.K <= 4 else 1
+                copies = moe.DOWN_KSPLIT if x.shape[0] * moe.K <= 4 else 1
                 r = K_.gemv_norm(x, L["ffn_norm"], c.rms_eps, moe.router.w, moe.router.bias, delta=a, route=(moe.router_bias, moe.K, True, copies), **nk)
             if r is not None:
                 _, x, _, idx, w, xq, sfx = r

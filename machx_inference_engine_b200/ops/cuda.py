@@ -468,17 +468,18 @@ def moe_quant(x, rows, max_tiles, rows_per_tile, src_index=None, x_div=1, row_li
 
 
 @_profiled("moe_route_quant")
-def moe_route_quant(logits, bias, k, x, renorm=True):
-    """Decode: router top-k and pair-mode MXFP8 quantisation of the T rows of ``x`` in one launch.  Returns (idx, w, xq, sfx)."""
+def moe_route_quant(logits, bias, k, x, renorm=True, w_copies=1):
+    """Decode: router top-k and pair-mode MXFP8 quantisation of the T rows of ``x`` in one launch.  Returns (idx, w, xq, sfx); ``w`` is
+    [T, w_copies * k], the k weights repeated (one per partial row when the down projection splits K)."""
     T, E = logits.shape
     Kd = x.shape[1]
     KB = (Kd + 127) // 128
     n = T * k
     idx = torch.empty(T, k, dtype=torch.int32, device=logits.device)
-    w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    w = torch.empty(T, w_copies * k, dtype=torch.float32, device=logits.device)
     xq = torch.empty(n, KB * 128, dtype=torch.uint8, device=x.device)
     sfx = torch.empty(KB, n, 512, dtype=torch.uint8, device=x.device)
-    _check(_lib.cuda().mx_moe_route_quant(_p(logits), _p(bias), T, E, k, int(renorm), _p(idx), _p(w), _p(x), x.stride(0), Kd, n, _p(xq), _p(sfx),
+    _check(_lib.cuda().mx_moe_route_quant(_p(logits), _p(bias), T, E, k, int(renorm), _p(idx), _p(w), int(w_copies), _p(x), x.stride(0), Kd, n, _p(xq), _p(sfx),
                                           _stream()), "moe_route_quant")
     _count()
     return idx, w, xq, sfx

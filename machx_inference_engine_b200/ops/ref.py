@@ -203,6 +203,8 @@ def qkv_post(qkv, bias, q_norm_w, k_norm_w, positions, rope_cos, rope_sin, slot_
             return torch.cat([a * c - b * s, a * s + b * c, t[..., n_rot:]], dim=-1)
 
         qpart, k = rope(qpart), rope(k)
+    if n_kv == 0:                   # queries only (a draft head that reads another model's cache)
+        return qpart.to(torch.bfloat16).contiguous(), gate
     bs = k_cache.shape[2]
     ok = slot_map >= 0
     blk, off = (slot_map[ok] // bs).long(), (slot_map[ok] % bs).long()

@@ -65,10 +65,15 @@ class Engine:
 
     # ------------------------------------------------------------------ loading
     @classmethod
-    def load(cls, path: str, device="cuda", opts: Optional[EngineOptions] = None, par=None) -> "Engine":
+    def load(cls, path: str, device="cuda", opts: Optional[EngineOptions] = None, par=None, spec_head: Optional[str] = None) -> "Engine":
+        """``spec_head``: a separate draft-head checkpoint (Gemma-4's ``gemma4-assistant`` GGUF); heads stored inside the model file
+        (Qwen3-Next's MTP layer) need none."""
         from ..models import load_model
         opts = opts or EngineOptions()
         model, reader = load_model(path, device, par, max_ctx=opts.max_ctx)
+        if spec_head:
+            from ..models.gemma4_assistant import load_assistant_head
+            load_assistant_head(model, spec_head)
         opts.max_ctx = min(opts.max_ctx, model.max_ctx)
         tok = Tokenizer.from_gguf_kv(reader.kv)
         return cls(model, tok, opts, model_id=str(reader.kv.get("general.name", "")) or path.rsplit("/", 1)[-1])

@@ -309,7 +309,9 @@ class LLMEngine:
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "graph_replays": 0, "h2d_bytes": 0, "d2h_bytes": 0,
                       "spec_rounds": 0, "spec_drafted": 0, "spec_accepted": 0}
         self.eos_ids = set(o.eos_ids)
-        self.spec_k = o.spec_k if (o.spec_k > 0 and getattr(model, "mtp", None) is not None and self.state is not None) else 0
+        # self-speculative decoding needs a draft head; models with recurrent state also need their state pool (for the rollback)
+        self.spec_k = o.spec_k if (o.spec_k > 0 and getattr(model, "mtp", None) is not None
+                                   and (self.state is not None or not getattr(model, "needs_state", False))) else 0
 
     # ------------------------------------------------------------------ recurrent-state prefix snapshots (hybrid models)
     def _state_prefix(self, hashes: list):
@@ -539,7 +541,9 @@ class LLMEngine:
         p0 = seq.n_computed
         if not self.sched._ensure_blocks(seq, p0 + K + 1):
             return None
-        drafts = self.model.mtp.draft(seq.h_last, seq.tokens[-1], K)
+        # (a head that reads the target's cache -- Gemma-4's assistant -- takes the sequence's pages and position; others ignore it)
+        ctx = {"kv": self.kv, "pos": p0, "block_table": torch.tensor([seq.blocks], dtype=torch.int32, device=self.device)}
+        drafts = self.model.mtp.draft(seq.h_last, seq.tokens[-1], K, ctx)
         base = list(seq.tokens)
         seq.tokens = base + drafts
         try:
@@ -550,17 +554,21 @@ class LLMEngine:
         dev = self._to_device(host)
         fb = ForwardBatch(dev["ids"], dev["positions"], dev["slot_map"], dev["block_table"], dev["seq_lens"], dev["cu_q"], max_q,
                           logit_rows=dev["logit_rows"], want_hidden=True)
-        fb.state_slots_host = [seq.state_slot]
-        fb.state_slots = dev["state_slots"]
         fb.q_lens_host, fb.start_host = [K + 1], [p0]
-        logits, hidden = self.model.forward(fb, self.kv, self.state, checkpoint=True)
+        if self.state is not None:
+            fb.state_slots_host = [seq.state_slot]
+            fb.state_slots = dev["state_slots"]
+            logits, hidden = self.model.forward(fb, self.kv, self.state, checkpoint=True)
+        else:
+            # no recurrent state: rejected drafts leave stale keys behind the committed position, and the next forward overwrites them
+            logits, hidden = self.model.forward(fb, self.kv, None)
         targ = ops.argmax(logits).cpu().tolist()
         self.stats["d2h_bytes"] += 4 * (K + 1)
         n = 0
         while n < K and drafts[n] == targ[n]:
             n += 1
         accepted = n + 1                       # verified input rows kept: the pending token and n drafts
-        if accepted < K + 1:
+        if accepted < K + 1 and self.state is not None:
             self.state.commit(seq.state_slot, accepted - 1)
         seq.h_last = hidden[accepted - 1:accepted].clone()
         seq.n_computed = p0 + accepted

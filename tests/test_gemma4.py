@@ -1,5 +1,6 @@
 """Gemma-4 graph against an independent plain-PyTorch restatement of the layer math (dense tensors read back from the file,
 whole-sequence attention with explicit masks): config round trip, file path, chunked prefill, paged decode."""
+import dataclasses
 import math
 
 import pytest
@@ -135,3 +136,56 @@ def test_engine_serves_gemma4_with_decode_and_int8_cache(tmp_path):
     lg = _forward_all(model, full, len(full))
     assert [int(t) for t in lg[len(ids) - 1:len(full) - 1].argmax(-1)] == outs["bf16"]
     assert outs["int8"][0] == outs["bf16"][0]
+
+
+def test_assistant_head_file_round_trip_and_lossless_spec_decode(tmp_path):
+    """The gemma4-assistant draft head: its file format (metadata keys + tensors) loads, its queries read the target's cache (the head
+    writes none), and greedy self-speculative decoding with it yields exactly the tokens of plain greedy decoding, whatever it drafts."""
+    from machx_inference_engine_b200.formats.synth import write_synthetic_assistant_gguf
+    from machx_inference_engine_b200.models.gemma4_assistant import load_assistant_head, read_assistant_config, synth_assistant_config
+    from machx_inference_engine_b200.formats.gguf import GGUFReader
+    cfg = preset("tiny-gemma4-dense")
+    path, hpath = str(tmp_path / "g.gguf"), str(tmp_path / "head.gguf")
+    write_synthetic_gguf(cfg, path, quant="q8_0", seed=3)
+    acfg = synth_assistant_config(cfg, n_layers=3, hidden=128, ffn=256)
+    assert acfg.is_swa == [True, True, False] and acfg.head_dim == [64, 64, 128] and acfg.n_kv_heads == [2, 2, 1]
+    write_synthetic_assistant_gguf(acfg, hpath, quant="q8_0", seed=4)
+    r = GGUFReader(hpath)
+    back = read_assistant_config(r.kv, r.tensors)
+    assert abs(back.rms_eps - acfg.rms_eps) < 1e-9 and dataclasses.replace(back, rms_eps=acfg.rms_eps) == acfg
+    model, _ = load_model(path, torch.device("cpu"), max_ctx=512)
+    ids = [(i * 11 + 5) % cfg.vocab for i in range(150)]
+    sp = SamplingParams(max_tokens=14, temperature=0.0, ignore_eos=True)
+    truth = LLMEngine(model, EngineOptions(max_ctx=512, max_batch_tokens=64, max_seqs=2)).generate([ids], sp)[0]
+    head = load_assistant_head(model, hpath)
+    assert model.mtp is head and [L["shared"] for L in head.layers] == [1, 1, 2]
+    eng = LLMEngine(model, EngineOptions(max_ctx=512, max_batch_tokens=64, max_seqs=2, spec_k=3))
+    assert eng.spec_k == 3
+    assert eng.generate([ids], sp)[0] == truth
+    assert eng.stats["spec_rounds"] > 0 and eng.stats["spec_drafted"] == 3 * eng.stats["spec_rounds"]
+    # drafts that are right (taken from the known continuation) are accepted: fewer rounds than tokens
+    eng = LLMEngine(model, EngineOptions(max_ctx=512, max_batch_tokens=64, max_seqs=2, spec_k=3))
+    seq = eng.add_request(ids, sp)
+    real = head.draft
+    seen = []
+
+    def oracle(h, tok, k, ctx):
+        seen.append((int(ctx["pos"]), tuple(ctx["block_table"].shape)))
+        g = len(seq.tokens) - len(ids)
+        real(h, tok, 1, ctx)                         # the real head still runs on the live cache and position
+        return (list(truth[g:g + k]) + [0] * k)[:k]
+    head.draft = oracle
+    try:
+        while not seq.finished:
+            eng.step()
+    finally:
+        head.draft = real
+    assert seq.tokens[len(ids):] == truth
+    assert eng.stats["spec_accepted"] > 0 and eng.stats["spec_rounds"] < len(truth)
+    assert seen[0][0] == len(ids) and all(b[0] == 1 for _, b in seen)
+    # a head of another width or vocabulary is refused
+    bad = synth_assistant_config(dataclasses.replace(cfg, hidden=128), n_layers=2)
+    bpath = str(tmp_path / "bad.gguf")
+    write_synthetic_assistant_gguf(bad, bpath)
+    with pytest.raises(ValueError):
+        load_assistant_head(model, bpath)

@@ -236,8 +236,40 @@ def test_fused_decode_chain_matches_the_kernel_per_op_chain(name, quant, B):
             TransformerModel.FUSED_DECODE = fused
             out[fused] = m.forward(fb, kv).float()
     finally:
-        TransformerModel.FUSED_DECODE = True
+        TransformerModel.FUSED_DECODE = False
     from machx_inference_engine_b200.ops import cuda as K
     K.check_status()
     assert _cos(out[True], out[False]) > (0.998 if quant == "mxfp4" else 0.9999)
     assert (out[True].argmax(-1) == out[False].argmax(-1)).all()
+
+
+def test_gemma4_assistant_head_on_cuda_matches_cpu_path(tmp_path):
+    """One draft step of the gemma4-assistant head (queries only; keys and values are the target's cache pages of head_dim 64 and 128)
+    on the CUDA kernels against the fp32 PyTorch path, on the same two files and the same prefilled prompt."""
+    from machx_inference_engine_b200.formats.synth import write_synthetic_assistant_gguf, write_synthetic_gguf
+    from machx_inference_engine_b200.models import load_model
+    from machx_inference_engine_b200.models.gemma4_assistant import load_assistant_head, synth_assistant_config
+    from machx_inference_engine_b200.models.transformer import KV_BLOCK, ForwardBatch
+    cfg = preset("tiny-gemma4-dense")
+    path, hpath = str(tmp_path / "g.gguf"), str(tmp_path / "h.gguf")
+    write_synthetic_gguf(cfg, path, quant="q8_0", seed=4)
+    write_synthetic_assistant_gguf(synth_assistant_config(cfg, n_layers=3, hidden=128, ffn=256), hpath, quant="q8_0", seed=5)
+    ids = torch.randint(0, cfg.vocab, (200,), generator=torch.Generator().manual_seed(3)).tolist()
+    res = {}
+    for dev in ("cpu", "cuda:0"):
+        d = torch.device(dev)
+        model, _ = load_model(path, d, max_ctx=512)
+        head = load_assistant_head(model, hpath)
+        kv = model.new_kv_cache(3)
+        T = len(ids)
+        bt = torch.tensor([[1, 2]], dtype=torch.int32, device=d)
+        pos = torch.arange(T, dtype=torch.int32, device=d)
+        slot = bt[0][(pos // KV_BLOCK).long()].long() * KV_BLOCK + (pos % KV_BLOCK).long()
+        fb = ForwardBatch(torch.tensor(ids, dtype=torch.int32, device=d), pos, slot, bt, torch.tensor([T], dtype=torch.int32, device=d),
+                          torch.tensor([0, T], dtype=torch.int32, device=d), T, want_hidden=True)
+        logits, hidden = model.forward(fb, kv)
+        tok = int(logits.argmax(-1)[0]) if dev == "cpu" else res["cpu"][2]
+        lg, hn = head.step(hidden.float(), tok, T, kv, bt)
+        res[dev] = (lg.float().cpu(), hn.float().cpu(), tok)
+    assert _cos(res["cpu"][0], res["cuda:0"][0]) > 0.998 and _cos(res["cpu"][1], res["cuda:0"][1]) > 0.998
+    assert int(res["cpu"][0].argmax()) == int(res["cuda:0"][0].argmax())

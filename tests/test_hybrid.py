@@ -117,7 +117,7 @@ def test_spec_decode_is_lossless_with_any_acceptance():
     rnd = [0]
     real = m.mtp.draft
 
-    def fake(h, tok, k):
+    def fake(h, tok, k, ctx=None):
         g = len(seq.tokens) - len(prompt)
         d = (list(truth[g:g + k]) + [0] * k)[:k]
         rnd[0] += 1
