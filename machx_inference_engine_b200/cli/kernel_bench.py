@@ -325,9 +325,11 @@ def main(argv=None):
         kv = (ai // (n_v // n_k)).to(torch.int32)
         sa, db = -torch.rand(n_v, device=dev) - 0.05, torch.zeros(n_v, device=dev)
         S = torch.zeros(1, n_v, Dh, Dh, device=dev)
-        med, mn = timeit(lambda: K.deltanet_scan(xin, n_k, ab, ai, ai + n_v, kv, sa, db, S, slots, cu, n_v), a.iters)
-        report(f"deltanet_scan T={T} n_k={n_k} n_v={n_v}", med, mn, flops=6.0 * T * n_v * Dh * Dh, bytes_=T * Cc * 2 + T * n_v * Dh * 4,
-               extra={"us_per_token": round(med * 1e3 / T, 3)})
+        for chunked in ((False, True) if T >= 128 else (False,)):
+            med, mn = timeit(lambda: K.deltanet_scan(xin, n_k, ab, ai, ai + n_v, kv, sa, db, S, slots, cu, n_v, chunked=chunked), a.iters)
+            report(f"deltanet_scan[{'chunked, tensor cores' if chunked else 'sequential'}] T={T} n_k={n_k} n_v={n_v}", med, mn,
+                   flops=6.0 * T * n_v * Dh * Dh, bytes_=T * Cc * 2 + T * n_v * Dh * 4, extra={"us_per_token": round(med * 1e3 / T, 3)})
+        K.check_status()
     K.check_status()
     return 0
 

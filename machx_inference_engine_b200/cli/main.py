@@ -69,6 +69,7 @@ def main(argv=None) -> int:
     p.add_argument("--host", default="127.0.0.1")
     p.add_argument("--port", type=int, default=11435)
     p = sub.add_parser("bench"); p.add_argument("rest", nargs=argparse.REMAINDER)
+    p = sub.add_parser("perf", help="optimisation-loop tools: ledger / roofline / viz (cli/perf.py)"); p.add_argument("rest", nargs=argparse.REMAINDER)
     p = sub.add_parser("import"); p.add_argument("hf_dir"); p.add_argument("out"); p.add_argument("--tokenizer-gguf", default=None); p.add_argument("--stream", action="store_true")
     p = sub.add_parser("pull"); p.add_argument("name"); p.add_argument("--dir", default=os.path.expanduser("~/.cache/ie/models"))
     p = sub.add_parser("inspect"); p.add_argument("gguf"); p.add_argument("--tensors", action="store_true")
@@ -78,6 +79,9 @@ def main(argv=None) -> int:
     if a.cmd == "bench":
         from .ie_bench import main as bench_main
         return bench_main(a.rest)
+    if a.cmd == "perf":
+        from .perf import main as perf_main
+        return perf_main(a.rest)
     if a.cmd == "import":
         from ..formats.hf_import import import_to_gguf
         import_to_gguf(a.hf_dir, a.out, tokenizer_gguf=a.tokenizer_gguf, stream=a.stream)

@@ -303,6 +303,7 @@ int mx_ggufw_end(void* w_) {
 // ---- codecs ----
 int mx_dequantize(int32_t type, const void* src, float* dst, uint64_t n) { return mx::dequantize(type, src, dst, n); }
 int mx_quantize(int32_t type, const float* src, void* dst, uint64_t nrows, uint64_t ncols, int nthreads) { return mx::quantize(type, src, dst, nrows, ncols, nthreads); }
+void mx_quantize_set_kquant_fit(int mode) { mx::set_kquant_fit(mode); }
 uint64_t mx_bytes_for(int32_t type, uint64_t n) { return mx::bytes_for(type, n); }
 int mx_type_block_elems(int32_t type) { return mx::type_traits(type).block_elems; }
 int mx_type_block_bytes(int32_t type) { return mx::type_traits(type).block_bytes; }

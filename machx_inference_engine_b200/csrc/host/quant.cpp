@@ -182,11 +182,72 @@ static void fit_scale_min(const float* x, int n, int qmax, float& s, float& m) {
   }
 }
 
+// The same fit by the importance-weighted grid search ggml's K-quant encoders use (make_qkx2_quants: src/loaders/quantize_q4k.cpp:22-81
+// in the reference): weights w_i = rms(x) + |x_i|, candidate inverse scales (rmin + rdelta * step + qmax) / (max - min), for each a
+// weighted least-squares (scale, min) over the rounded codes, the candidate with the smallest weighted squared error wins.
+static void fit_scale_min_search(const float* x, int n, int qmax, float rmin, float rdelta, int nstep, float& s, float& m) {
+  float lo = x[0], hi = x[0];
+  double sx2 = 0;
+  for (int i = 0; i < n; ++i) { lo = std::min(lo, x[i]); hi = std::max(hi, x[i]); sx2 += (double)x[i] * x[i]; }
+  lo = std::min(lo, 0.f);
+  if (hi <= lo) { s = 0; m = -lo; return; }
+  const float av = (float)std::sqrt(sx2 / n);
+  float w[64];
+  double sw = 0, swx = 0;
+  for (int i = 0; i < n; ++i) { w[i] = av + std::fabs(x[i]); sw += w[i]; swx += (double)w[i] * x[i]; }
+  auto err_of = [&](float sc, float mn, float inv) {
+    double e = 0;
+    for (int i = 0; i < n; ++i) {
+      const int q = std::clamp(nearest_int(inv * (x[i] - mn)), 0, qmax);
+      const double d = (double)sc * q + mn - x[i];
+      e += w[i] * d * d;
+    }
+    return e;
+  };
+  float best_s = (hi - lo) / qmax, best_min = lo;
+  double best = err_of(best_s, best_min, qmax / (hi - lo));
+  for (int is = 0; is <= nstep; ++is) {
+    const float inv = (rmin + rdelta * is + qmax) / (hi - lo);
+    double sl = 0, sl2 = 0, sxl = 0;
+    for (int i = 0; i < n; ++i) {
+      const int q = std::clamp(nearest_int(inv * (x[i] - lo)), 0, qmax);
+      sl += (double)w[i] * q; sl2 += (double)w[i] * q * q; sxl += (double)w[i] * q * x[i];
+    }
+    const double det = sw * sl2 - sl * sl;
+    if (det <= 0) continue;
+    double ts = (sw * sxl - swx * sl) / det, tm = (sl2 * swx - sl * sxl) / det;
+    if (tm > 0) { tm = 0; ts = sl2 > 0 ? sxl / sl2 : ts; }
+    if (ts <= 0) continue;
+    const double e = err_of((float)ts, (float)tm, inv);
+    if (e < best) { best = e; best_s = (float)ts; best_min = (float)tm; }
+  }
+  s = best_s; m = -best_min;
+}
+
+static double fit_error(const float* x, int n, int qmax, float s, float m) {
+  double e = 0;
+  for (int i = 0; i < n; ++i) {
+    const int q = s > 0 ? std::clamp(nearest_int((x[i] + m) / s), 0, qmax) : 0;
+    const double d = (double)s * q - m - x[i];
+    e += d * d;
+  }
+  return e;
+}
+
+// 0: per sub-block the better (plain squared error) of the two fits; 1: the alternating least-squares fit only; 2: the grid search only
+static int g_kquant_fit = 0;
+void set_kquant_fit(int mode) { g_kquant_fit = mode; }
+
 static void enc_q4k_q5k(const float* x, uint8_t* b, bool five) {
   const int qmax = five ? 31 : 15;
   float s[8], m[8], smax = 0, mmax = 0;
   for (int j = 0; j < 8; ++j) {
-    fit_scale_min(x + 32 * j, 32, qmax, s[j], m[j]);
+    const float* xs = x + 32 * j;
+    float s1 = 0, m1 = 0, s2 = 0, m2 = 0;
+    if (g_kquant_fit != 2) fit_scale_min(xs, 32, qmax, s1, m1);
+    if (g_kquant_fit != 1) fit_scale_min_search(xs, 32, qmax, five ? -0.5f : -1.f, 0.1f, five ? 15 : 20, s2, m2);
+    const bool second = g_kquant_fit == 2 || (g_kquant_fit == 0 && fit_error(xs, 32, qmax, s2, m2) < fit_error(xs, 32, qmax, s1, m1));
+    s[j] = second ? s2 : s1; m[j] = second ? m2 : m1;
     smax = std::max(smax, s[j]); mmax = std::max(mmax, m[j]);
   }
   float d = smax / 63.f, dm = mmax / 63.f;

@@ -87,5 +87,7 @@ int dequantize(int32_t t, const void* src, float* dst, size_t n);
 // src holds nrows*ncols floats (row-major); dst receives the packed rows.
 // ncols must be a multiple of the type's block size. Uses up to nthreads workers.
 int quantize(int32_t t, const float* src, void* dst, size_t nrows, size_t ncols, int nthreads);
+// Q4_K / Q5_K sub-block fit: 0 = better of the two per sub-block (default), 1 = alternating least squares, 2 = ggml-style weighted grid search
+void set_kquant_fit(int mode);
 
 }  // namespace mx

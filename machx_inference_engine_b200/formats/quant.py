@@ -36,3 +36,9 @@ def quantize(x: np.ndarray, ttype: int, nthreads: int | None = None) -> np.ndarr
     if rc != 0:
         raise ValueError(f"cannot quantize to ggml type {ttype}")
     return out
+
+
+def set_kquant_fit(mode: int) -> None:
+    """Q4_K / Q5_K sub-block fit of :func:`quantize`: 0 = per sub-block the better of the two fits below (default), 1 = alternating
+    least squares, 2 = the importance-weighted grid search of ggml's K-quant encoders."""
+    _lib.host().mx_quantize_set_kquant_fit(int(mode))

@@ -198,11 +198,31 @@ def conv1d_silu(x, w, state, state_slots, cu_q, max_q_len, ckpt=None):
     return y
 
 
-def deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, state_slots, cu_q, n_v, eps=1e-6, ckpt=None):
+DELTANET_CHUNKED_MIN_T = 128      # batches of at least this many tokens take the chunked tensor-core scan (no checkpoints there)
+
+
+@_profiled("deltanet_scan")
+def deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, state_slots, cu_q, n_v, eps=1e-6, ckpt=None, chunked=None):
+    """``chunked``: None picks the chunked (WY) tensor-core kernel for prefill-sized batches without checkpoints and the sequential
+    kernel otherwise; True / False force one (tests, benches)."""
     T = qkv.shape[0]
     D = 128
     assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and ab.dtype == torch.bfloat16 and ab.stride(1) == 1 and state.dtype == torch.float32
     out = torch.empty(T, n_v * D, dtype=torch.float32, device=qkv.device)
+    if chunked is None:
+        chunked = ckpt is None and T >= DELTANET_CHUNKED_MIN_T
+    if chunked:
+        assert ckpt is None, "the chunked scan keeps no per-position checkpoints"
+        B = cu_q.numel() - 1
+        lib = _lib.cuda()
+        lib.mx_deltanet_chunk_ws_bytes.restype = C.c_longlong
+        ws = torch.empty(int(lib.mx_deltanet_chunk_ws_bytes(T, B, n_v)), dtype=torch.uint8, device=qkv.device)
+        egl = torch.empty((T // 64 + B) * n_v, dtype=torch.float32, device=qkv.device)
+        _check(lib.mx_deltanet_scan_chunked(_p(qkv), qkv.stride(0), 0, n_k * D, 2 * n_k * D, _p(ab), ab.stride(0), _p(a_idx), _p(b_idx), _p(k_of_v),
+                                            _p(ssm_a), _p(dt_bias), _p(state), _p(state_slots), _p(cu_q), B, T, n_v, D,
+                                            C.c_float(1.0 / math.sqrt(D)), C.c_float(eps), _p(out), _p(ws), _p(egl), _stream()), "deltanet_scan_chunked")
+        _count(2)
+        return out
     _check(_lib.cuda().mx_deltanet_scan(_p(qkv), qkv.stride(0), 0, n_k * D, 2 * n_k * D, _p(ab), ab.stride(0), _p(a_idx), _p(b_idx), _p(k_of_v),
                                         _p(ssm_a), _p(dt_bias), _p(state), _p(state_slots), _p(cu_q), cu_q.numel() - 1, n_v, D,
                                         C.c_float(1.0 / math.sqrt(D)), C.c_float(eps), _p(out), _p(ckpt), _stream()), "deltanet_scan")

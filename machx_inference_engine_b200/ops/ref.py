@@ -356,6 +356,58 @@ def deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, sta
 
 
 # ------------------------------------------------------------------ MoE
+DELTANET_CHUNK = 64
+
+
+def deltanet_scan_chunked(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, state_slots, cu_q, n_v, eps=1e-6, chunk=DELTANET_CHUNK):
+    """The same recurrence as :func:`deltanet_scan` in its chunked (WY) form: the arithmetic of the tensor-core scan kernel, stated
+    in fp32.  Within a chunk of C tokens with cumulative log-decay G_i, the per-token corrections U (rows u_i = d_i) solve
+        (I + A) U = beta * V - diag(beta e^G) K S0^T,      A_ij = beta_i e^{G_i - G_j} (k_i . k_j) for j < i,
+    so with T = (I + A)^-1:  U = T (beta V) - T (beta e^G K) S0^T;  the outputs are O = diag(e^G) Q S0^T + (M * Q K^T) U with
+    M_ij = e^{G_i - G_j} for j <= i, and the state leaves the chunk as S = e^{G_last} S0 + U^T diag(e^{G_last - G}) K.
+    Sequences are padded to whole chunks with beta = 0, g = 0, k = 0 rows (identity steps).  No per-position checkpoints."""
+    T, D = qkv.shape[0], 128
+    x = qkv.to(torch.float32)
+    q = x[:, :n_k * D].reshape(T, n_k, D)
+    k = x[:, n_k * D:2 * n_k * D].reshape(T, n_k, D)
+    v = x[:, 2 * n_k * D:].reshape(T, n_v, D)
+    q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + eps) / math.sqrt(D)
+    k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + eps)
+    kv = k_of_v.long()
+    q, k = q[:, kv], k[:, kv]                                        # [T, n_v, D]
+    abf = ab.to(torch.float32)
+    g = ssm_a * torch.nn.functional.softplus(abf[:, a_idx.long()] + dt_bias)      # [T, n_v]
+    beta = torch.sigmoid(abf[:, b_idx.long()])
+    out = torch.empty(T, n_v, D, dtype=torch.float32, device=qkv.device)
+    cu = cu_q.tolist()
+    C = chunk
+    tril = torch.tril(torch.ones(C, C, device=qkv.device), diagonal=-1).bool()
+    for b in range(len(cu) - 1):
+        t0, t1 = cu[b], cu[b + 1]
+        if t1 <= t0:
+            continue
+        slot = int(state_slots[b])
+        S = state[slot].clone()                                      # [n_v, D(v), D(k)]
+        for c0 in range(t0, t1, C):
+            n = min(C, t1 - c0)
+            pad = lambda t: torch.cat([t[c0:c0 + n], t.new_zeros((C - n,) + t.shape[1:])]) if n < C else t[c0:c0 + n]
+            qc, kc, vc, gc, bc = (pad(t).transpose(0, 1) for t in (q, k, v, g, beta))      # [n_v, C, ...]
+            G = gc.cumsum(-1)                                        # [n_v, C]
+            dec = torch.exp(G.unsqueeze(-1) - G.unsqueeze(-2))       # e^{G_i - G_j}
+            A = (bc.unsqueeze(-1) * dec * (kc @ kc.transpose(-1, -2))).masked_fill(~tril, 0.0)
+            Tm = torch.linalg.solve_triangular(torch.eye(C, device=A.device) + A, torch.eye(C, device=A.device).expand_as(A), upper=False)
+            Wv = Tm @ (bc.unsqueeze(-1) * vc)                        # [n_v, C, D(v)]
+            Wk = Tm @ ((bc * torch.exp(G)).unsqueeze(-1) * kc)       # [n_v, C, D(k)]
+            U = Wv - Wk @ S.transpose(-1, -2)
+            Mqk = (dec * (qc @ kc.transpose(-1, -2))).masked_fill(torch.triu(torch.ones(C, C, device=A.device), diagonal=1).bool(), 0.0)
+            O = torch.exp(G).unsqueeze(-1) * (qc @ S.transpose(-1, -2)) + Mqk @ U
+            Gl = G[:, -1]
+            S = torch.exp(Gl).reshape(n_v, 1, 1) * S + U.transpose(-1, -2) @ (torch.exp(Gl.unsqueeze(-1) - G).unsqueeze(-1) * kc)
+            out[c0:c0 + n] = O.transpose(0, 1)[:n]
+        state[slot] = S
+    return out.reshape(T, n_v * D)
+
+
 def moe_route(logits, bias, k, renorm=True):
     x = logits.to(torch.float32)
     if bias is not None:

@@ -182,3 +182,28 @@ def test_mxf4_tiles_roundtrip_and_padding():
     assert torch.equal(gu.p0[1, 1, 0, 96 + 7], u.p0[1, 96 + 7, :64]) and torch.equal(gu.p0[1, 1, 0, 7], w.p0[1, 96 + 7, :64])
     r = 96 + 40          # tile row 136 = up row 96 + 40 of tile 1 -> atom 1, row 8
     assert int(gu.p1[2, 1, 1, 1, 8 * 16 + 0 * 4 + 3]) == int(u.p1[2, 96 + 40, 7])
+
+
+def test_kquant_fits_compared():
+    """RMS error of the two Q4_K / Q5_K sub-block fits (alternating least squares; ggml's importance-weighted grid search) and of
+    the default, which takes the better of the two per sub-block, on Gaussian and on heavy-tailed rows."""
+    from machx_inference_engine_b200.formats import quant
+    from machx_inference_engine_b200.formats.gguf import GGMLType
+    rng = np.random.default_rng(3)
+    data = {"gauss": rng.standard_normal((64, 1024)).astype(np.float32) * 0.02,
+            "heavy": (rng.standard_t(3, size=(64, 1024)) * 0.02).astype(np.float32)}
+    try:
+        for t in (GGMLType.Q4_K, GGMLType.Q5_K):
+            for name, x in data.items():
+                rms = {}
+                for mode in (0, 1, 2):
+                    quant.set_kquant_fit(mode)
+                    back = quant.dequantize(quant.quantize(x, int(t)), int(t), x.size).reshape(x.shape)
+                    rms[mode] = float(np.sqrt(np.mean((back - x) ** 2)) / np.sqrt(np.mean(x ** 2)))
+                # the default is at least as good as either fit alone (up to the effect of the shared 6-bit super-block scales)
+                assert rms[0] <= min(rms[1], rms[2]) * 1.01, (t, name, rms)
+                # both fits are sound K-quant encoders: 4-bit ~ 7-9 % relative RMS, 5-bit about half of that
+                assert rms[1] < (0.10 if t == GGMLType.Q4_K else 0.05) and rms[2] < (0.10 if t == GGMLType.Q4_K else 0.05), (t, name, rms)
+                print(f"{GGMLType(t).name} {name}: best-of-both {rms[0]:.4f}  alternating-LS {rms[1]:.4f}  weighted-grid {rms[2]:.4f}")
+    finally:
+        quant.set_kquant_fit(0)
