@@ -73,20 +73,26 @@ struct PrepSmem {
   static constexpr int AK = 0;                 // [K ; Q] normalised, bf16, two K atoms (32 KiB)
   static constexpr int A1 = 32768;             // image of [e^G Q ; W_k]
   static constexpr int KDT = 65536;            // image of (e^{G_last - G} K)^T
-  static constexpr int SA = 81920;             // A fp32 [64][64]
-  static constexpr int MISC = 98304;           // gates, norms, barrier
-  static constexpr int TOTAL = MISC + 2048 + 1024;
+  static constexpr int MISC = 81920;           // barrier, TMEM slot, abort flag
+  static constexpr int TOTAL = MISC + 256 + 1024;
 };
 
-__global__ void __launch_bounds__(256) dn_chunk_prep_kernel(const ChunkParams p) {
+// (shared-window load: a pointer derived from the aligned dynamic base would compile to a generic load)
+__device__ __forceinline__ float lds_bf16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return __uint_as_float((uint32_t)v << 16);
+}
+
+__global__ void __launch_bounds__(256, 2) dn_chunk_prep_kernel(const ChunkParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
-  float* sA = reinterpret_cast<float*>(smem + PrepSmem::SA);
-  float* sg = reinterpret_cast<float*>(smem + PrepSmem::MISC);          // g, then G (cumulative)
-  float* sbeta = sg + DC;
-  float* sinvk = sbeta + DC;
-  uint64_t* bar = reinterpret_cast<uint64_t*>(sinvk + DC);
+  // Arrays the threads read in their inner loops are static: the dynamic window's pointers come from integer arithmetic (the 1024-byte
+  // alignment), so dereferencing them compiles to generic loads, which take the long-latency path.
+  __shared__ __align__(16) float sA[DC * DC];                          // A, fp32
+  __shared__ float sg[DC], sbeta[DC];                                  // g then G (cumulative), beta
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + PrepSmem::MISC);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -98,6 +104,20 @@ __global__ void __launch_bounds__(256) dn_chunk_prep_kernel(const ChunkParams p)
   if (tid == 0) { mbar_init(smem_u32(bar), 1); *abort_flag = 0; fence_mbar_init(); }
   if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), 64); tmem_relinquish(); }
 
+  // A warp owns rows warp, warp + 8, ...; their loads are issued together and before the gate arithmetic, so that the eight rows cost
+  // one trip to memory and that trip overlaps the gates and their prefix sum.
+  uint2 qraw[DC / 8], kraw[DC / 8], vraw[DC / 8];
+#pragma unroll
+  for (int it = 0; it < DC / 8; ++it) {
+    const int r = warp + 8 * it;
+    qraw[it] = kraw[it] = vraw[it] = make_uint2(0u, 0u);
+    if (r < n) {
+      const bf16* row = p.qkv + (size_t)(t0 + r) * p.ld + lane * 4;
+      qraw[it] = *reinterpret_cast<const uint2*>(row + p.q_off + kh * DD);
+      kraw[it] = *reinterpret_cast<const uint2*>(row + p.k_off + kh * DD);
+      vraw[it] = *reinterpret_cast<const uint2*>(row + p.v_off + h * DD);
+    }
+  }
   // gates
   if (tid < DC) {
     float g = 0.f, be = 0.f;
@@ -114,25 +134,28 @@ __global__ void __launch_bounds__(256) dn_chunk_prep_kernel(const ChunkParams p)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (tid == 0) {
-    float acc = 0.f;
-    for (int i = 0; i < DC; ++i) { acc += sg[i]; sg[i] = acc; }
+  if (warp == 0) {                       // inclusive prefix sum of the 64 gates: lane l holds elements 2l and 2l + 1
+    const float g0 = sg[2 * lane], g1 = sg[2 * lane + 1];
+    float v = g0 + g1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    sg[2 * lane] = v - g1;
+    sg[2 * lane + 1] = v;
   }
   __syncthreads();
   const float Gl = sg[DC - 1];
 
   // rows: L2 norms, the [K ; Q] operand, e^G Q and (e^{G_last - G} K)^T
-  for (int r = warp; r < DC; r += 8) {
-    float q[4] = {0.f, 0.f, 0.f, 0.f}, k[4] = {0.f, 0.f, 0.f, 0.f};
-    if (r < n) {
-      const bf16* row = p.qkv + (size_t)(t0 + r) * p.ld + kh * DD + lane * 4;
-      const uint2 qv = *reinterpret_cast<const uint2*>(row + p.q_off), kv = *reinterpret_cast<const uint2*>(row + p.k_off);
-      q[0] = bf16_lo(qv.x); q[1] = bf16_hi(qv.x); q[2] = bf16_lo(qv.y); q[3] = bf16_hi(qv.y);
-      k[0] = bf16_lo(kv.x); k[1] = bf16_hi(kv.x); k[2] = bf16_lo(kv.y); k[3] = bf16_hi(kv.y);
-    }
+#pragma unroll
+  for (int it = 0; it < DC / 8; ++it) {
+    const int r = warp + 8 * it;
+    const float q[4] = {bf16_lo(qraw[it].x), bf16_hi(qraw[it].x), bf16_lo(qraw[it].y), bf16_hi(qraw[it].y)};
+    const float k[4] = {bf16_lo(kraw[it].x), bf16_hi(kraw[it].x), bf16_lo(kraw[it].y), bf16_hi(kraw[it].y)};
     const float iq = rsqrtf(warp_sum(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]) + p.eps) * p.q_scale;
     const float ik = rsqrtf(warp_sum(k[0] * k[0] + k[1] * k[1] + k[2] * k[2] + k[3] * k[3]) + p.eps);
-    if (lane == 0) sinvk[r] = ik;
     const float eg = __expf(sg[r]), ed = __expf(Gl - sg[r]);
     const uint32_t atom = (uint32_t)(lane >> 4) * 16384u, chunk = (lane & 15) >> 1, half = (lane & 1) * 8;
     *reinterpret_cast<uint2*>(smem + PrepSmem::AK + atom + sw128_offset(r, chunk) + half) =
@@ -144,6 +167,8 @@ __global__ void __launch_bounds__(256) dn_chunk_prep_kernel(const ChunkParams p)
 #pragma unroll
     for (int i = 0; i < 4; ++i)          // transposed: element (k index, position r)
       *reinterpret_cast<bf16*>(smem + PrepSmem::KDT + sw128_offset(lane * 4 + i, r >> 3) + (r & 7) * 2) = __float2bfloat16(k[i] * ik * ed);
+    // the raw v row waits in rows 64..127 of the [e^G Q ; W_k] image (W_k lands there after the substitution has read it)
+    *reinterpret_cast<uint2*>(smem + PrepSmem::A1 + atom + 8192 + r * 128 + (lane & 15) * 8) = vraw[it];
   }
   fence_proxy_async();
   __syncthreads();
@@ -162,52 +187,64 @@ __global__ void __launch_bounds__(256) dn_chunk_prep_kernel(const ChunkParams p)
   const bool ok = mbar_wait(mbar, 0, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag, 32);
   tc_fence_after();
   uint8_t* ws = p.ws + ((size_t)blockIdx.x * p.n_v + h) * WS_BYTES;
-  if (ok && warp < 4) {
-    const int row = warp * 32 + lane;
-    uint32_t c0[32], c1[32];
-    tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16), c0);
-    tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + 32, c1);
-    tmem_ld_wait();
-    if (row < DC) {
+  {
+    // accumulator rows: warps w and w + 4 share TMEM lanes 32 (w % 4) .. + 31 and take columns 0..31 and 32..63
+    const int row = (warp & 3) * 32 + lane, col0 = (warp >> 2) * 32;
+    uint32_t c[32];
+    if (ok) {
+      tmem_ld_32x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + col0, c);
+      tmem_ld_wait();
+    }
+    if (ok && row < DC) {
       const int i = row;
       const float Gi = sg[i], bi = sbeta[i];
 #pragma unroll
-      for (int j = 0; j < DC; ++j) {
-        const float kk = __uint_as_float(j < 32 ? c0[j & 31] : c1[j & 31]);
-        sA[i * DC + j] = j < i ? bi * __expf(Gi - sg[j]) * kk : 0.f;
+      for (int jj = 0; jj < 32; jj += 4) {
+        float a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = col0 + jj + u;
+          a[u] = j < i ? bi * __expf(Gi - sg[j]) * __uint_as_float(c[jj + u]) : 0.f;
+        }
+        *reinterpret_cast<float4*>(sA + i * DC + col0 + jj) = make_float4(a[0], a[1], a[2], a[3]);
       }
-    } else {
+    } else if (ok) {
       const int i = row - DC;
       const float Gi = sg[i];
-      float m[DC];
 #pragma unroll
-      for (int j = 0; j < DC; ++j) {
-        const float qk = __uint_as_float(j < 32 ? c0[j & 31] : c1[j & 31]);
-        m[j] = j <= i ? __expf(Gi - sg[j]) * qk : 0.f;
+      for (int ch = 0; ch < 4; ++ch) {
+        float m[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int j = col0 + 8 * ch + u;
+          m[u] = j <= i ? __expf(Gi - sg[j]) * __uint_as_float(c[8 * ch + u]) : 0.f;
+        }
+        *reinterpret_cast<uint4*>(ws + WS_MQK + sw128_offset(i, (col0 >> 3) + ch)) =
+            make_uint4(pack_bf16(m[0], m[1]), pack_bf16(m[2], m[3]), pack_bf16(m[4], m[5]), pack_bf16(m[6], m[7]));
       }
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch)
-        *reinterpret_cast<uint4*>(ws + WS_MQK + sw128_offset(i, ch)) =
-            make_uint4(pack_bf16(m[8 * ch], m[8 * ch + 1]), pack_bf16(m[8 * ch + 2], m[8 * ch + 3]), pack_bf16(m[8 * ch + 4], m[8 * ch + 5]),
-                       pack_bf16(m[8 * ch + 6], m[8 * ch + 7]));
     }
   }
   tc_fence_before();
   __syncthreads();
 
-  // (I + A) W = [beta V | beta e^G K]: thread c owns column c of the right-hand side
-  if (ok) {
+  // (I + A) W = [beta V | beta e^G K]: thread c owns column c of the right-hand side.  (Runs also after a wait that ran out: the block
+  // contains a barrier, and what it then writes is never read, the status word being set.)
+  {
     float w[DC];
     const int c = tid;
+    // right-hand sides from shared memory: the staged v rows, and the normalised k rows of the [K ; Q] operand (rows past the
+    // sequence's end are zero in both, and so is their beta)
     if (c < DD) {
+      const uint32_t va = sbase + PrepSmem::A1 + (uint32_t)(c >> 6) * 16384u + 8192u + (c & 63) * 2;
 #pragma unroll
-      for (int i = 0; i < DC; ++i)
-        w[i] = i < n ? sbeta[i] * __bfloat162float(p.qkv[(size_t)(t0 + i) * p.ld + p.v_off + h * DD + c]) : 0.f;
+      for (int i = 0; i < DC; ++i) w[i] = sbeta[i] * lds_bf16(va + i * 128);
     } else {
+      const int e = c - DD;
+      const uint32_t ka = sbase + PrepSmem::AK + (uint32_t)(e >> 6) * 16384u + (e & 7) * 2;
 #pragma unroll
-      for (int i = 0; i < DC; ++i)
-        w[i] = i < n ? sbeta[i] * __expf(sg[i]) * sinvk[i] * __bfloat162float(p.qkv[(size_t)(t0 + i) * p.ld + p.k_off + kh * DD + (c - DD)]) : 0.f;
+      for (int i = 0; i < DC; ++i) w[i] = sbeta[i] * __expf(sg[i]) * lds_bf16(ka + sw128_offset(i, (e & 63) >> 3));
     }
+    __syncthreads();                     // every v row has been read: W_k may overwrite them
 #pragma unroll
     for (int i = 1; i < DC; ++i) {
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
@@ -261,6 +298,11 @@ struct ScanSmem {
   static_assert(TOTAL <= 232448, "shared memory plan exceeds 227 KB");
 };
 
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ void dc_bulk(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
@@ -367,10 +409,10 @@ __global__ void __launch_bounds__(128, 1) dn_chunk_scan_kernel(const ChunkParams
       tmem_ld_32x32(tmem_base + tm_lane, c0);
       tmem_ld_32x32(tmem_base + tm_lane + 32, c1);
       tmem_ld_wait();
-      const float4* wv = reinterpret_cast<const float4*>(smem + stg * L::STAGE + L::WV);
+      const uint32_t wv = st + L::WV + i * 16;          // (shared-window loads: a pointer derived from the aligned base would be generic)
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
-        const float4 w0 = wv[(2 * ch) * DC + i], w1 = wv[(2 * ch + 1) * DC + i];
+        const float4 w0 = lds_f4(wv + (2 * ch) * DC * 16), w1 = lds_f4(wv + (2 * ch + 1) * DC * 16);
         const uint32_t* src = ch < 4 ? c0 : c1;
         const int o = (ch & 3) * 8;
         *reinterpret_cast<uint4*>(smem + L::U + sw128_offset(i, ch)) =

@@ -85,13 +85,21 @@ def test_batched_decode_moe_path_matches_single_sequence():
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, cfg.vocab, (int(n),), generator=g).tolist() for n in torch.randint(5, 60, (16,), generator=g)]
     sp = SamplingParams(max_tokens=6, ignore_eos=True)
-    alone = [LLMEngine(model, EngineOptions(max_ctx=512, max_seqs=1)).generate([p], sp)[0] for p in prompts[:6]]
-    for limit in (0, 64):
-        for L in model.layers:
-            L["moe"].group_gemv_max_tokens = limit
-        together = LLMEngine(model, EngineOptions(max_ctx=512, max_seqs=16, max_batch_tokens=2048)).generate(prompts, sp)
-        same = sum(int(a == b) for x, y in zip(alone, together) for a, b in zip(x, y))
-        assert all(x[0] == y[0] for x, y in zip(alone, together)) and same >= 0.8 * sum(len(x) for x in alone), limit
+    from machx_inference_engine_b200.models.transformer import MoEFFN
+    # A lone token splits the K range of its down projection and sums bf16 partial rows; a batch does not.  Greedy tokens of a
+    # random-init model follow near-ties, so this comparison runs both sides on the same arithmetic (the split itself is checked
+    # in test_gpu_mxf4.py and in the decode-chain test below).
+    ks, MoEFFN.DOWN_KSPLIT = MoEFFN.DOWN_KSPLIT, 1
+    try:
+        alone = [LLMEngine(model, EngineOptions(max_ctx=512, max_seqs=1)).generate([p], sp)[0] for p in prompts[:6]]
+        for limit in (0, 64):
+            for L in model.layers:
+                L["moe"].group_gemv_max_tokens = limit
+            together = LLMEngine(model, EngineOptions(max_ctx=512, max_seqs=16, max_batch_tokens=2048)).generate(prompts, sp)
+            same = sum(int(a == b) for x, y in zip(alone, together) for a, b in zip(x, y))
+            assert all(x[0] == y[0] for x, y in zip(alone, together)) and same >= 0.8 * sum(len(x) for x in alone), limit
+    finally:
+        MoEFFN.DOWN_KSPLIT = ks
 
 
 @pytest.mark.parametrize("name,quant", [("tiny-gpt-oss", "mxfp4"), ("tiny-qwen3next", "q8_0")])
