@@ -250,6 +250,114 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
   for (int i = lane; i < hd; i += 32) dst[i] = __float2bfloat16(v[i]);
 }
 
+// Prefill form of the same epilogue: one CTA per token.  The token's position, cache slot and rope row are fetched once (the
+// rope row into shared memory) and the warps walk the token's heads, a lane holding HD / 32 consecutive elements of a head (one
+// vector load) and reaching its rotation partner with one shuffle.  The per-head math is that of qkv_post_kernel; the host picks
+// this form for batches of many tokens when n_rot / 2 is a multiple of the lane's element count (every model so far).
+template <int HD>
+__global__ void __launch_bounds__(128) qkv_post_token_kernel(const QkvPostParams p) {
+  constexpr int EPL = HD / 32;                 // elements per lane
+  pdl_prologue();
+  __shared__ float s_cos[256], s_sin[256];
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int half = p.n_rot / 2;
+  if (half > 0) {
+    int pos = p.positions[t];
+    pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      s_cos[i] = p.rope_cos[(size_t)pos * half + i];
+      s_sin[i] = p.rope_sin[(size_t)pos * half + i];
+    }
+  }
+  const long long slot = p.slot_map[t];
+  __syncthreads();
+  const int heads_total = p.n_q + 2 * p.n_kv;
+  const int q_stride = p.q_gate ? 2 * HD : HD;
+  const int q_cols = p.n_q * q_stride;
+  const int row_cols = q_cols + 2 * p.n_kv * HD;
+  const __nv_bfloat16* row = p.qkv + (size_t)t * row_cols;
+  const int e0 = lane * EPL;                   // first element of this lane
+  const int dl = half / EPL;                   // lane distance to the rotation partner
+  for (int h = warp; h < heads_total; h += 4) {
+    int kind, hh, col0;                        // kind 0 q, 1 k, 2 v
+    if (h < p.n_q) { kind = 0; hh = h; col0 = h * q_stride; }
+    else if (h < p.n_q + p.n_kv) { kind = 1; hh = h - p.n_q; col0 = q_cols + hh * HD; }
+    else { kind = 2; hh = h - p.n_q - p.n_kv; col0 = q_cols + p.n_kv * HD + hh * HD; }
+    if (kind != 0 && slot < 0) continue;       // this token's K/V rows are not stored
+    float v[EPL];
+    {
+      uint32_t raw[EPL / 2];
+      if constexpr (EPL == 2) raw[0] = *reinterpret_cast<const uint32_t*>(row + col0 + e0);
+      else if constexpr (EPL == 4) { const uint2 r2 = *reinterpret_cast<const uint2*>(row + col0 + e0); raw[0] = r2.x; raw[1] = r2.y; }
+      else {
+#pragma unroll
+        for (int c = 0; c < EPL / 8; ++c) {
+          const uint4 r4 = *reinterpret_cast<const uint4*>(row + col0 + e0 + 8 * c);
+          raw[4 * c] = r4.x; raw[4 * c + 1] = r4.y; raw[4 * c + 2] = r4.z; raw[4 * c + 3] = r4.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < EPL / 2; ++j) { v[2 * j] = bf16_lo(raw[j]); v[2 * j + 1] = bf16_hi(raw[j]); }
+    }
+    if (p.bias) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) v[j] += p.bias[col0 + e0 + j];
+    }
+    if (kind == 0 && p.q_gate) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        float g = __bfloat162float(row[col0 + HD + e0 + j]);
+        if (p.bias) g += p.bias[col0 + HD + e0 + j];
+        p.gate_out[((size_t)t * p.n_q + hh) * HD + e0 + j] = __float2bfloat16(g);
+      }
+    }
+    const float* nw = kind == 0 ? p.q_norm_w : (kind == 1 ? p.k_norm_w : nullptr);
+    if (nw || (kind == 2 && p.v_norm)) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) ss += v[j] * v[j];
+      const float inv = rsqrtf(warp_sum(ss) / HD + p.eps);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) v[j] *= nw ? inv * (p.norm_one_plus_w ? 1.f + nw[e0 + j] : nw[e0 + j]) : inv;
+    }
+    if (kind != 2 && half > 0) {
+      const bool lo = e0 < half, in = e0 < p.n_rot;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], dl);
+        if (in) {
+          const int f = (lo ? e0 : e0 - half) + j;
+          v[j] = lo ? v[j] * s_cos[f] - other * s_sin[f] : other * s_sin[f] + v[j] * s_cos[f];
+        }
+      }
+    }
+    if (kind == 0) {
+      __nv_bfloat16* dst = p.q_out + ((size_t)t * p.n_q + hh) * HD + e0;
+#pragma unroll
+      for (int j = 0; j < EPL; j += 2) *reinterpret_cast<uint32_t*>(dst + j) = pack_bf16(v[j], v[j + 1]);
+      continue;
+    }
+    const long long blk = slot / p.block_size, off = slot % p.block_size;
+    const long long crow = (blk * p.n_kv + hh) * p.block_size + off;
+    __nv_bfloat16* cache = kind == 1 ? p.k_cache : p.v_cache;
+    if (p.k_scale) {          // symmetric int8 per row: scale = max|x| / 127
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      amax = warp_max(amax);
+      const float sc = amax > 0.f ? amax / 127.f : 1.f, inv = 1.f / sc;
+      int8_t* d8 = reinterpret_cast<int8_t*>(cache) + crow * HD + e0;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) d8[j] = (int8_t)max(-127, min(127, __float2int_rn(v[j] * inv)));
+      if (lane == 0) (kind == 1 ? p.k_scale : p.v_scale)[crow] = sc;
+    } else {
+      __nv_bfloat16* dst = cache + crow * HD + e0;
+#pragma unroll
+      for (int j = 0; j < EPL; j += 2) *reinterpret_cast<uint32_t*>(dst + j) = pack_bf16(v[j], v[j + 1]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ GLU over interleaved-16 columns
 __device__ __forceinline__ float glu_act(int act, float g, float u, float alpha, float limit) {
   if (act == 1) return g / (1.f + __expf(-g)) * u;
@@ -403,6 +511,19 @@ MX_HOST_API int mx_qkv_post_kv8(const void* qkv, const float* bias, const float*
   p.T = T; p.n_q = n_q; p.n_kv = n_kv; p.hd = hd; p.n_rot = n_rot; p.block_size = block_size; p.q_gate = q_gate & 1;
   p.v_norm = (q_gate >> 1) & 1;           // flag word: bit 0 = q columns carry a gate, bit 1 = weightless RMS norm on V
   p.norm_one_plus_w = norm_one_plus_w; p.eps = eps; p.max_pos = max_pos;
+  const int half = n_rot / 2, epl = hd / 32;
+  const int row_cols = n_q * (p.q_gate ? 2 * hd : hd) + 2 * n_kv * hd;
+  // many tokens: the token-major form (vector loads need the row start and every head start on an element-count boundary)
+  if (T >= 64 && (hd == 64 || hd == 128 || hd == 256 || hd == 512) && half <= 256 && half % epl == 0 && ((half / epl) & (half / epl - 1)) == 0 &&
+      n_rot <= hd && row_cols % 8 == 0 && ((uintptr_t)qkv & 15) == 0) {
+    switch (hd) {
+      case 64: launch_pdl(qkv_post_token_kernel<64>, dim3(T), dim3(128), 0, st, p); break;
+      case 128: launch_pdl(qkv_post_token_kernel<128>, dim3(T), dim3(128), 0, st, p); break;
+      case 256: launch_pdl(qkv_post_token_kernel<256>, dim3(T), dim3(128), 0, st, p); break;
+      default: launch_pdl(qkv_post_token_kernel<512>, dim3(T), dim3(128), 0, st, p); break;
+    }
+    return (int)cudaGetLastError();
+  }
   const int units = T * (n_q + 2 * n_kv);
   launch_pdl(qkv_post_kernel, dim3((units + 3) / 4), dim3(128), 0, st, p);
   return (int)cudaGetLastError();

@@ -34,6 +34,11 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 // (hist[warp][expert] in shared memory), a scan over the warps turns the histograms into per-warp write cursors,
 // and each warp walks its chunk again placing 32 pairs per step (rank among equal experts by __match_any_sync).
 // Rows of an expert therefore keep increasing pair order and the result does not depend on timing.
+// The kernel is a chain of short phases, so every phase is written for latency: a warp fetches its pairs eight steps at a time
+// (independent loads), the expert offsets come from a block-wide prefix sum (expert e = thread e), and every expert writes its own
+// tile table entries.
+constexpr int PACK_BATCH = 8;
+
 __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ topk_idx, int n, int K, int E, int e_lo, int e_hi,
                                                         int* __restrict__ counts, int* __restrict__ seg_start, int* __restrict__ packed_token,
                                                         int* __restrict__ pair_to_packed, int* __restrict__ tile_expert, int* __restrict__ num_tiles,
@@ -42,15 +47,22 @@ __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ 
   extern __shared__ int s_hist[];            // [nwarps][E]
   __shared__ int s_cnt[1024];
   __shared__ int s_start[1025];
+  __shared__ int s_wsum[32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int chunk = ((n + nwarps - 1) / nwarps + 31) & ~31;
   const int c0 = warp * chunk, c1 = min(n, c0 + chunk);
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) s_hist[i] = 0;
   __syncthreads();
-  for (int base = c0; base < c1; base += 32) {
-    const int i = base + lane;
-    const int e = i < c1 ? topk_idx[i] : -1;
-    if (e >= e_lo && e < e_hi) atomicAdd(&s_hist[warp * E + e], 1);
+  for (int base = c0; base < c1; base += 32 * PACK_BATCH) {
+    int ev[PACK_BATCH];
+#pragma unroll
+    for (int u = 0; u < PACK_BATCH; ++u) {
+      const int i = base + 32 * u + lane;
+      ev[u] = i < c1 ? topk_idx[i] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < PACK_BATCH; ++u)
+      if (ev[u] >= e_lo && ev[u] < e_hi) atomicAdd(&s_hist[warp * E + ev[u]], 1);
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -63,44 +75,83 @@ __global__ void __launch_bounds__(1024) moe_pack_kernel(const int* __restrict__ 
     s_cnt[e] = run;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int off = 0, tiles = 0;
-    for (int e = 0; e < E; ++e) {
-      s_start[e] = off;
-      // tile = 128: segments padded to whole GEMM tiles and a tile -> expert map; tile = 1: compact segments (GEMV path)
-      const int padded = (s_cnt[e] + tile - 1) / tile * tile;
-      if (tile > 1) for (int tix = 0; tix < padded / tile; ++tix) {
-        if (tile_valid) tile_valid[tiles] = min(tile, s_cnt[e] - tix * tile);      // live rows of this tile
-        tile_expert[tiles++] = e;
-      }
-      off += padded;
+  {
+    // exclusive prefix sum of the padded segment lengths over the experts (E <= 1024 = one expert per thread)
+    // tile = 128: segments padded to whole GEMM tiles and a tile -> expert map; tile = 1: compact segments (GEMV path)
+    const int e = threadIdx.x;
+    const int cnt = e < E ? s_cnt[e] : 0;
+    const int padded = (cnt + tile - 1) / tile * tile;
+    int v = padded;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
     }
-    s_start[E] = off;
-    num_tiles[0] = tiles;
-    num_tiles[1] = off;
+    if (lane == 31) s_wsum[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      int w = lane < nwarps ? s_wsum[lane] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += u;
+      }
+      s_wsum[lane] = w;                      // inclusive over warps
+    }
+    __syncthreads();
+    const int start = v - padded + (warp ? s_wsum[warp - 1] : 0);
+    if (e < E) {
+      s_start[e] = start;
+      seg_start[e] = start;
+      counts[e] = cnt;
+      if (tile > 1) {
+        const int t0 = start / tile;         // every earlier segment is a whole number of tiles
+        for (int tix = 0; tix < padded / tile; ++tix) {
+          if (tile_valid) tile_valid[t0 + tix] = min(tile, cnt - tix * tile);      // live rows of this tile
+          tile_expert[t0 + tix] = e;
+        }
+      }
+    }
+    if (threadIdx.x == blockDim.x - 1) {
+      const int off = s_wsum[nwarps - 1];
+      s_start[E] = off;
+      seg_start[E] = off;
+      num_tiles[0] = tile > 1 ? off / tile : 0;
+      num_tiles[1] = off;
+    }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e <= E; e += blockDim.x) { seg_start[e] = s_start[e]; if (e < E) counts[e] = s_cnt[e]; }
   const int total = s_start[E];
   for (int i = threadIdx.x; i < max_rows; i += blockDim.x) if (i < total) packed_token[i] = -1;
   __syncthreads();
-  for (int base = c0; base < c1; base += 32) {
-    const int i = base + lane;
-    const int e = i < c1 ? topk_idx[i] : -1;
-    const bool owned = e >= e_lo && e < e_hi;
-    const unsigned m = __match_any_sync(0xffffffffu, owned ? e : E + lane);
-    int cur = 0;
-    if (owned) cur = s_hist[warp * E + e];
-    __syncwarp();
-    if (owned) {
-      const int dst = s_start[e] + cur + __popc(m & ((1u << lane) - 1));
-      packed_token[dst] = i / K;
-      pair_to_packed[i] = dst;
-      if (lane == 31 - __clz(m)) s_hist[warp * E + e] = cur + __popc(m);      // the highest lane of the group advances the cursor
-    } else if (i < c1) {
-      pair_to_packed[i] = -1;
+  for (int base0 = c0; base0 < c1; base0 += 32 * PACK_BATCH) {
+    int ev[PACK_BATCH];
+#pragma unroll
+    for (int u = 0; u < PACK_BATCH; ++u) {
+      const int i = base0 + 32 * u + lane;
+      ev[u] = i < c1 ? topk_idx[i] : -1;
     }
-    __syncwarp();
+#pragma unroll
+    for (int u = 0; u < PACK_BATCH; ++u) {
+      const int base = base0 + 32 * u;
+      if (base >= c1) break;                 // warp-uniform
+      const int i = base + lane;
+      const int e = ev[u];
+      const bool owned = e >= e_lo && e < e_hi;
+      const unsigned m = __match_any_sync(0xffffffffu, owned ? e : E + lane);
+      int cur = 0;
+      if (owned) cur = s_hist[warp * E + e];
+      __syncwarp();
+      if (owned) {
+        const int dst = s_start[e] + cur + __popc(m & ((1u << lane) - 1));
+        packed_token[dst] = i / K;
+        pair_to_packed[i] = dst;
+        if (lane == 31 - __clz(m)) s_hist[warp * E + e] = cur + __popc(m);      // the highest lane of the group advances the cursor
+      } else if (i < c1) {
+        pair_to_packed[i] = -1;
+      }
+      __syncwarp();
+    }
   }
 }
 

@@ -193,6 +193,8 @@ __global__ void __launch_bounds__(256) shard_norm_kernel(const ShardNormArgs a, 
 // Outputs (local): pair_pos[n] = row of the pair inside the owner's packed buffer; for this rank's own experts the tile
 // table of the grouped GEMM: tile_expert[], tile_valid[], num_tiles[0] = live 128-row tiles, num_tiles[1] = packed rows.
 // Shared memory: int cnt_all[W][E], int hist[nwarps][E], int seg[E], int base[E].
+constexpr int PLAN_BATCH = 8;
+
 __global__ void __launch_bounds__(1024) moe_dispatch_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int e_per_rank, const ShardWs ws,
                                                                 int* __restrict__ pair_pos, int* __restrict__ tile_expert, int* __restrict__ tile_valid,
                                                                 int* __restrict__ num_tiles, int max_tiles, int* status) {
@@ -211,9 +213,17 @@ __global__ void __launch_bounds__(1024) moe_dispatch_plan_kernel(const int* __re
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) s_hist[i] = 0;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
-  for (int b = c0; b < c1; b += 32) {
-    const int i = b + lane;
-    if (i < c1) atomicAdd(&s_hist[warp * E + topk_idx[i]], 1);
+  // (the kernel is a chain of short phases: a warp fetches its pairs eight steps at a time, so a pass costs one trip to memory)
+  for (int b0 = c0; b0 < c1; b0 += 32 * PLAN_BATCH) {
+    int ev[PLAN_BATCH];
+#pragma unroll
+    for (int u = 0; u < PLAN_BATCH; ++u) {
+      const int i = b0 + 32 * u + lane;
+      ev[u] = i < c1 ? topk_idx[i] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < PLAN_BATCH; ++u)
+      if (ev[u] >= 0) atomicAdd(&s_hist[warp * E + ev[u]], 1);
   }
   __syncthreads();
   // per expert: warp histograms -> exclusive cursors; my count goes to every rank's matrix row `me`
@@ -248,37 +258,50 @@ __global__ void __launch_bounds__(1024) moe_dispatch_plan_kernel(const int* __re
     for (int s = 0; s < me; ++s) b += s_all[s * E + e];
     s_base[e] = b;
   }
-  // tile table of my own experts
-  if (threadIdx.x == 0) {
-    int tiles = 0, rows = 0;
-    for (int e = me * e_per_rank; e < min(E, (me + 1) * e_per_rank); ++e) {
+  // tile table of my own experts: every expert writes its own entries (its first tile is its segment start / 128)
+  {
+    const int e_first = me * e_per_rank, e_last = min(E, (me + 1) * e_per_rank) - 1;
+    const int e = e_first + threadIdx.x;
+    if (e <= e_last) {
       int tot = 0;
       for (int s = 0; s < W; ++s) tot += s_all[s * E + e];
-      for (int r = 0; r < tot && tiles < max_tiles; r += 128) {
-        tile_expert[tiles] = e;
-        tile_valid[tiles] = min(128, tot - r);
-        ++tiles;
+      const int t0 = s_seg[e] >> 7;
+      for (int r = 0, k = 0; r < tot && t0 + k < max_tiles; r += 128, ++k) {
+        tile_expert[t0 + k] = e;
+        tile_valid[t0 + k] = min(128, tot - r);
       }
-      rows += (tot + 127) & ~127;
+      if (e == e_last) {
+        const int rows = s_seg[e] + ((tot + 127) & ~127);
+        num_tiles[0] = min(rows >> 7, max_tiles);
+        num_tiles[1] = rows;
+        ws.seq[FL_COUNT] = next;
+      }
     }
-    num_tiles[0] = tiles;
-    num_tiles[1] = rows;
-    ws.seq[FL_COUNT] = next;
   }
   __syncthreads();
   // stable placement: pairs of one expert keep their pair order
-  for (int b = c0; b < c1; b += 32) {
-    const int i = b + lane;
-    const int e = i < c1 ? topk_idx[i] : -1;
-    const unsigned m = __match_any_sync(0xffffffffu, e >= 0 ? e : E + lane);
-    int cur = 0;
-    if (e >= 0) cur = s_hist[warp * E + e];
-    __syncwarp();
-    if (e >= 0) {
-      pair_pos[i] = s_base[e] + cur + __popc(m & ((1u << lane) - 1));
-      if (lane == 31 - __clz(m)) s_hist[warp * E + e] = cur + __popc(m);
+  for (int b0 = c0; b0 < c1; b0 += 32 * PLAN_BATCH) {
+    int ev[PLAN_BATCH];
+#pragma unroll
+    for (int u = 0; u < PLAN_BATCH; ++u) {
+      const int i = b0 + 32 * u + lane;
+      ev[u] = i < c1 ? topk_idx[i] : -1;
     }
-    __syncwarp();
+#pragma unroll
+    for (int u = 0; u < PLAN_BATCH; ++u) {
+      if (b0 + 32 * u >= c1) break;          // warp-uniform
+      const int i = b0 + 32 * u + lane;
+      const int e = ev[u];
+      const unsigned m = __match_any_sync(0xffffffffu, e >= 0 ? e : E + lane);
+      int cur = 0;
+      if (e >= 0) cur = s_hist[warp * E + e];
+      __syncwarp();
+      if (e >= 0) {
+        pair_pos[i] = s_base[e] + cur + __popc(m & ((1u << lane) - 1));
+        if (lane == 31 - __clz(m)) s_hist[warp * E + e] = cur + __popc(m);
+      }
+      __syncwarp();
+    }
   }
 }
 

@@ -403,7 +403,8 @@ class MoEFFN:
             from ..ops.cuda import moe_route_quant
             # one token on one rank: the down projection has too few (pair, column block) items for the chip and splits K
             if T * self.K <= 4 and not self.reduce and self.shared is None and self.expert_scale is None:
-                ksplit = self.DOWN_KSPLIT
+                from ..ops.cuda import mxf4_ksplit
+                ksplit = mxf4_ksplit(self.mx[1].K, self.DOWN_KSPLIT)
             idx, w, xq, sfx = moe_route_quant(logits, self.router_bias, self.K, h, w_copies=ksplit)
             pre = (xq, sfx)
         else:
@@ -680,7 +681,7 @@ class TransformerModel:
             r = None
             if self.FUSED_DECODE_ROUTER and moe is not None and moe.mx is not None and moe.expert_scale is None and moe.shared is None:
                 # with one token the down projection has too few (pair, column block) items for the chip: it splits K in two
-                copies = moe.DOWN_KSPLIT if x.shape[0] * moe.K <= 4 else 1
+                copies = K_.mxf4_ksplit(moe.mx[1].K, moe.DOWN_KSPLIT) if x.shape[0] * moe.K <= 4 else 1
                 r = K_.gemv_norm(x, L["ffn_norm"], c.rms_eps, moe.router.w, moe.router.bias, delta=a, route=(moe.router_bias, moe.K, True, copies), **nk)
             if r is not None:
                 _, x, _, idx, w, xq, sfx = r

@@ -553,6 +553,13 @@ def gemv_norm(x, norm_w, eps, w: QuantWeight, bias=None, delta=None, one_plus_w=
     return y, x_new, h
 
 
+def mxf4_ksplit(K: int, want: int) -> int:
+    """K ranges ``mxf4_gemm(..., ksplit=want)`` really uses for a reduction length K: every range owns at least one 128-element block."""
+    kb = (K + 127) // 128
+    per = (kb + max(want, 1) - 1) // max(want, 1)
+    return (kb + per - 1) // per
+
+
 @_profiled("mxf4_gemm")
 def mxf4_gemm(w: QuantWeight, xq, sfx, tile_expert, max_tiles, row_stride, tile_valid=None, default_valid=128, num_tiles=None, e_lo=0,
               bias0=None, bias1=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, zero_out=False, ksplit=1):
@@ -572,10 +579,7 @@ def mxf4_gemm(w: QuantWeight, xq, sfx, tile_expert, max_tiles, row_stride, tile_
         oq = torch.empty(rows, oq_ld, dtype=torch.uint8, device=dev)
         osf = torch.empty(oq_ld // 128, max_tiles, 512, dtype=torch.uint8, device=dev)
     else:
-        if ksplit > 1:
-            kb = (w.K + 127) // 128
-            per = (kb + ksplit - 1) // ksplit
-            ksplit = (kb + per - 1) // per
+        ksplit = mxf4_ksplit(w.K, ksplit)
         out = (torch.zeros if zero_out else torch.empty)(ksplit * rows, w.N, dtype=torch.bfloat16, device=dev)
     _check(_lib.cuda().mx_mxf4_gemm(_p(w.p0), _p(w.p1), int(w.dual), w.E, _p(xq), _p(sfx), rows, w.N, w.K, _p(tile_expert), _p(tile_valid),
                                     int(default_valid), _p(num_tiles), int(max_tiles), int(row_stride), int(e_lo), _p(bias0), _p(bias1),

@@ -202,8 +202,9 @@ class ShardedComm:
         dev = self.device
         n = R * Kt
         pair_pos = torch.empty(n, dtype=torch.int32, device=dev)
-        tile_expert = torch.zeros(self.max_tiles, dtype=torch.int32, device=dev)
-        tile_valid = torch.zeros(self.max_tiles, dtype=torch.int32, device=dev)
+        # (entries past the live tile count are never read: the grouped GEMM and the return kernel stop at num_tiles)
+        tile_expert = torch.empty(self.max_tiles, dtype=torch.int32, device=dev)
+        tile_valid = torch.empty(self.max_tiles, dtype=torch.int32, device=dev)
         num_tiles = torch.empty(2, dtype=torch.int32, device=dev)
         K._check(lib.mx_moe_dispatch_plan(self._ws_ref, K._p(idx), n, self.E, self.e_per_rank, K._p(pair_pos), K._p(tile_expert), K._p(tile_valid),
                                           K._p(num_tiles), self.max_tiles, K._stream()), "moe_dispatch_plan")

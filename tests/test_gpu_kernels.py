@@ -353,8 +353,9 @@ def _rope_tables(max_pos, n_rot, theta=10000.0):
                                  dict(n_q=8, n_kv=2, hd=128, n_rot=128, gate=False, norm=True, bias=False),
                                  dict(n_q=4, n_kv=1, hd=256, n_rot=64, gate=True, norm=True, bias=False),
                                  dict(n_q=4, n_kv=1, hd=512, n_rot=512, gate=False, norm=True, bias=False, v_norm=True)])
-def test_qkv_post(cfg):
-    T, bs, nblk = 19, 128, 4
+@pytest.mark.parametrize("T", [19, 100])          # 100 rows: the token-major (prefill) form of the kernel
+def test_qkv_post(cfg, T):
+    bs, nblk = 128, 4
     n_q, n_kv, hd = cfg["n_q"], cfg["n_kv"], cfg["hd"]
     cols = n_q * hd * (2 if cfg["gate"] else 1) + 2 * n_kv * hd
     qkv = torch.randn(T, cols, device=dev()).to(torch.bfloat16)
@@ -418,8 +419,9 @@ def _quantise_cache(c):
     return torch.round(f / sc.unsqueeze(-1)).clamp(-127, 127).to(torch.int8), sc
 
 
-def test_qkv_post_int8_cache_rows():
-    T, bs, nblk, n_q, n_kv, hd = 37, 128, 3, 8, 2, 128
+@pytest.mark.parametrize("T", [37, 90])
+def test_qkv_post_int8_cache_rows(T):
+    bs, nblk, n_q, n_kv, hd = 128, 3, 8, 2, 128
     cols = n_q * hd + 2 * n_kv * hd
     qkv = (torch.randn(T, cols, device=dev()) * 3).to(torch.bfloat16)
     kn = torch.rand(hd, device=dev())
