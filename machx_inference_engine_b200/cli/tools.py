@@ -8,12 +8,17 @@
     python -m machx_inference_engine_b200.cli.tools layer-dump   --gguf M.gguf --device cuda --out a.pt [--tokens FILE]
     python -m machx_inference_engine_b200.cli.tools layer-diff   a.pt b.pt [--threshold 0.999]
     python -m machx_inference_engine_b200.cli.tools layer-parity --gguf M.gguf          (CUDA kernels against the fp32 PyTorch path)
+    python -m machx_inference_engine_b200.cli.tools spec-accept  --gguf M.gguf | --model NAME [--spec-k 3] [--accept 0.0,0.5,0.8,1.0]
+    python -m machx_inference_engine_b200.cli.tools kv-scale     --gguf M.gguf | --model NAME [--tokens-n 512]
+    python -m machx_inference_engine_b200.cli.tools partial-stack --gguf M.gguf | --model NAME [--layers 1,2,4]
 
 Reference parity (behaviour, not code): tools/ie_perplexity.cpp (streaming negative log-likelihood), tools/ie_det_probe.cpp and
 ie_bug_monitor.cpp (run-to-run bit identity), tools/ie_prompt_bench.cpp (fixed prompts, first run discarded, median),
 tools/ie_validate_chunking.cpp (chunked prefill against whole-prompt prefill), scripts/soak_1h.sh (completions per hour, failures),
 tools/ie_dense_dump.cpp / ie_qwen35_dump.cpp / llama_dump.cpp + tools/diff_layers.sh (per-layer activation dumps of one prompt and their
-layer-by-layer cosine comparison; here the second implementation is this package's own fp32 PyTorch path instead of llama.cpp).
+layer-by-layer cosine comparison; here the second implementation is this package's own fp32 PyTorch path instead of llama.cpp),
+tools/ie_qwen35_mtp_accept.cpp (draft acceptance and the decode speed-up it buys), tools/ie_kv_scale.cpp (what the int8 KV cache costs
+in logit accuracy), tools/ie_partial_stack_eval.cpp (the model cut after its first n layers, to find the layer where two builds part).
 """
 from __future__ import annotations
 
@@ -54,7 +59,8 @@ def _all_logits(eng, ids, chunk):
     """Teacher-forced logits [len(ids), vocab] obtained through the engine's scheduler with prefill chunks of `chunk` tokens."""
     from ..runtime.engine import EngineOptions, LLMEngine, SamplingParams
     m = eng.model
-    llm = LLMEngine(m, EngineOptions(max_ctx=eng.llm.opts.max_ctx, max_batch_tokens=chunk, max_seqs=1, enable_prefix_cache=False, cuda_graphs=False))
+    llm = LLMEngine(m, EngineOptions(max_ctx=eng.llm.opts.max_ctx, max_batch_tokens=chunk, max_seqs=1, enable_prefix_cache=False, cuda_graphs=False,
+                                     kv_dtype=eng.llm.opts.kv_dtype))
     orig_build = llm._build_batch
 
     def build(plan, sampled_rows, pad_to=0):          # ask for the logits of every row of every chunk
@@ -259,6 +265,103 @@ def cmd_layer_parity(a) -> int:
     return 0 if r["first_layer_below_threshold"] is None else 1
 
 
+def cmd_spec_accept(a) -> int:
+    """Self-speculative decoding: acceptance of the model's own draft head, and decode tokens/s as a function of acceptance.  The
+    speed-up curve is measured, not modelled: the head still runs every round (its cost is paid), then a fraction `p` of its draft
+    positions is replaced by the true greedy continuation (known from a plain run) and the rest by a wrong token, so the verify
+    forward accepts as a head of that quality would."""
+    import random
+    from ..runtime.engine import EngineOptions, LLMEngine, SamplingParams
+    eng = _load(a, max_ctx=2048)
+    m = eng.model
+    if getattr(m, "mtp", None) is None:
+        raise SystemExit("this model has no draft head (Qwen3-Next / Qwen3.5 files carry one; Gemma-4 takes --spec-head on ie run / serve)")
+    V = m.cfg.vocab
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, V, (a.prompt_n,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=a.max_tokens, ignore_eos=True)
+    mk = lambda k: LLMEngine(m, EngineOptions(max_ctx=2048, max_batch_tokens=a.chunk, max_seqs=1, enable_prefix_cache=False, spec_k=k))
+
+    def timed(llm, hook=None):
+        seq = llm.add_request(prompt, sp)
+        llm.step()                                   # prefill
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while not seq.finished:
+            if hook:
+                hook(seq)
+            llm.step()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        return seq.tokens[len(prompt):], (len(seq.tokens) - len(prompt) - 1) / dt
+    truth, plain_tps = timed(mk(0))
+    llm = mk(a.spec_k)
+    own, own_tps = timed(llm)
+    st = llm.stats
+    rows = [{"draft": "model's own head", "acceptance": round(st["spec_accepted"] / max(st["spec_drafted"], 1), 3), "tok_s": round(own_tps, 1),
+             "speedup": round(own_tps / plain_tps, 3), "lossless": own == truth}]
+    real = m.mtp.draft
+    for p_acc in [float(x) for x in a.accept.split(",")]:
+        rnd = random.Random(5)
+        llm = mk(a.spec_k)
+        cur = {}
+
+        def draft(h, tok, k, ctx=None):
+            real(h, tok, k, ctx)                     # the head's cost stays in the measurement
+            gpos = len(cur["seq"].tokens) - len(prompt)
+            want = (list(truth[gpos:gpos + k]) + [0] * k)[:k]
+            return [t if rnd.random() < p_acc else (t + 1) % V for t in want]
+        m.mtp.draft = draft
+        try:
+            out, tps = timed(llm, hook=lambda s: cur.__setitem__("seq", s))
+        finally:
+            m.mtp.draft = real
+        st = llm.stats
+        rows.append({"draft": f"oracle, per-position hit rate {p_acc}", "acceptance": round(st["spec_accepted"] / max(st["spec_drafted"], 1), 3),
+                     "tok_s": round(tps, 1), "speedup": round(tps / plain_tps, 3), "lossless": out == truth})
+    print(json.dumps({"plain_tok_s": round(plain_tps, 1), "spec_k": a.spec_k, "rows": rows}))
+    return 0 if all(r["lossless"] for r in rows) else 1
+
+
+def cmd_kv_scale(a) -> int:
+    """What the int8 KV cache (one scale per cached row) costs: teacher-forced logits of one prompt with the bf16 cache and with the
+    int8 cache, cosine and arg-max agreement per position, and the negative log-likelihood of the prompt under both."""
+    from ..runtime.engine import EngineOptions
+    res = {}
+    eng = _load(a, max_ctx=2048)
+    ids = torch.randint(0, eng.cfg.vocab, (a.tokens_n,), generator=torch.Generator().manual_seed(3)).tolist()
+    for dt in ("bf16", "int8"):
+        res[dt] = _all_logits(type(eng)(eng.model, eng.tok, EngineOptions(max_ctx=2048, kv_dtype=dt)), ids, a.chunk)
+    cos = torch.nn.functional.cosine_similarity(res["bf16"], res["int8"], dim=1)
+    tgt = torch.tensor(ids[1:])
+    nll = {k: float(-torch.log_softmax(v[:-1].float(), -1).gather(1, tgt[:, None]).mean()) for k, v in res.items()}
+    print(json.dumps({"positions": len(ids), "cos_min": float(cos.min()), "cos_mean": float(cos.mean()),
+                      "argmax_agree": float((res["bf16"].argmax(-1) == res["int8"].argmax(-1)).float().mean()), "nll_bf16": nll["bf16"], "nll_int8": nll["int8"]}))
+    return 0
+
+
+def cmd_partial_stack(a) -> int:
+    """Logits of the model cut after its first n layers (final norm and head applied to that residual), for each n asked: two builds
+    or two devices that part at layer n show it here without a per-layer dump."""
+    eng = _load(a, max_ctx=2048)
+    m = eng.model
+    ids = torch.randint(0, eng.cfg.vocab, (a.tokens_n,), generator=torch.Generator().manual_seed(3)).tolist()
+    full = list(m.layers)
+    out = []
+    try:
+        for n in [int(x) for x in a.layers.split(",")] + [len(full)]:
+            m.layers = full[:max(1, min(n, len(full)))]
+            lg = _all_logits(eng, ids, a.chunk)
+            out.append({"layers": len(m.layers), "logit_rms": float(lg.float().pow(2).mean().sqrt()), "argmax_checksum": int(lg.argmax(-1).sum()),
+                        "last_argmax": int(lg[-1].argmax())})
+    finally:
+        m.layers = full
+    print(json.dumps({"positions": len(ids), "cuts": out}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="ie-tools")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -277,8 +380,12 @@ def main(argv=None) -> int:
     p = sub.add_parser("layer-dump"); common(p); p.add_argument("--out", required=True); p.add_argument("--tokens"); p.add_argument("--tokens-n", type=int, default=96)
     p = sub.add_parser("layer-diff"); p.add_argument("a"); p.add_argument("b"); p.add_argument("--threshold", type=float, default=0.999); p.add_argument("--verbose", action="store_true")
     p = sub.add_parser("layer-parity"); common(p); p.add_argument("--tokens"); p.add_argument("--tokens-n", type=int, default=96); p.add_argument("--threshold", type=float, default=0.999)
+    p = sub.add_parser("spec-accept"); common(p); p.add_argument("--spec-k", type=int, default=3); p.add_argument("--accept", default="0.0,0.5,0.8,1.0")
+    p.add_argument("--prompt-n", type=int, default=256); p.add_argument("--max-tokens", type=int, default=96)
+    p = sub.add_parser("kv-scale"); common(p); p.add_argument("--tokens-n", type=int, default=512)
+    p = sub.add_parser("partial-stack"); common(p); p.add_argument("--layers", default="1,2"); p.add_argument("--tokens-n", type=int, default=128)
     a = ap.parse_args(argv)
-    return {"layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
+    return {"spec-accept": cmd_spec_accept, "kv-scale": cmd_kv_scale, "partial-stack": cmd_partial_stack, "layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
             "soak": cmd_soak}[a.cmd](a)
 
 

@@ -47,3 +47,22 @@ def test_layer_dump_and_diff(tmp_path, capsys):
     assert tools.main(["layer-diff", a, b]) == 1
     assert _last_json(capsys)["first_layer_below_threshold"] == 1
     assert tools.main(["layer-parity", "--gguf", g, "--device", "cpu", "--tokens-n", "24"]) == 0
+
+
+def test_spec_accept_kv_scale_partial_stack(capsys):
+    # acceptance and speed-up of self-speculative decoding: the random-init head accepts nothing, perfect drafts accept everything,
+    # and every variant reproduces plain greedy decoding
+    assert tools.main(["spec-accept", "--model", "tiny-qwen3next", "--device", "cpu", "--max-tokens", "20", "--prompt-n", "40", "--accept", "0.0,1.0"]) == 0
+    r = _last_json(capsys)
+    acc = {row["draft"]: row for row in r["rows"]}
+    assert all(row["lossless"] for row in r["rows"]) and acc["oracle, per-position hit rate 1.0"]["acceptance"] == 1.0
+    assert acc["oracle, per-position hit rate 0.0"]["acceptance"] == 0.0
+    assert acc["oracle, per-position hit rate 1.0"]["tok_s"] > acc["oracle, per-position hit rate 0.0"]["tok_s"]
+    # int8 KV rows against bf16 rows
+    assert tools.main(["kv-scale", "--model", "tiny-llama", "--device", "cpu", "--tokens-n", "150"]) == 0
+    r = _last_json(capsys)
+    assert r["cos_min"] > 0.999 and abs(r["nll_bf16"] - r["nll_int8"]) < 0.01
+    # the model cut after one layer differs from the whole model; the last cut is the whole model
+    assert tools.main(["partial-stack", "--model", "tiny-llama", "--device", "cpu", "--layers", "1", "--tokens-n", "48"]) == 0
+    r = _last_json(capsys)
+    assert [c["layers"] for c in r["cuts"]] == [1, 2] and r["cuts"][0]["argmax_checksum"] != r["cuts"][1]["argmax_checksum"]
