@@ -133,6 +133,38 @@ def test_tp2_on_gpus_fused_and_nccl_match_single_gpu(name, quant):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("name,quant", [("tiny-llama", "q8_0"), ("tiny-gpt-oss", "mxfp4")])
+def test_tp4_on_gpus_fused_forms_match_single_gpu(name, quant):
+    """Four ranks, replicated activations: the fused GEMM / GEMV + all-reduce (direct form, and the reduce-scatter form with the
+    owner's re-broadcast, which also covers the expert combine pushed with scattered rows) against one GPU."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    one = _run(1, name, quant, "cuda")
+    moe = "llama" not in name
+    for comm in ("fused", "fused-rs"):
+        res = _run(4, name, quant, "cuda", comm)
+        assert res["world"] == 4
+        _close(one, res, cos=0.995 if moe else 0.999, arg=0.93 if moe else 0.95)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,quant", [("tiny-llama", "q8_0"), ("tiny-qwen3next", "q8_0")])
+def test_layer_split_on_gpus_matches_single_gpu(name, quant):
+    """Pipeline (layer split) over two GPUs with NCCL point-to-point hand-offs: same logits as one GPU; micro-batched prefill equals
+    whole-chunk prefill."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    one = _run(1, name, quant, "cuda")
+    two = _run(2, name, quant, "cuda", comm="pp")
+    n = one["logits"].shape[0]
+    _close(one, {"logits": two["logits"][:n], "tokens": two["tokens"]}, cos=0.999, arg=0.95)
+    rest = two["logits"][n:]
+    if rest.numel():
+        half = rest.shape[0] // 2
+        assert torch.allclose(rest[:half], rest[half:], atol=5e-2, rtol=5e-2)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("name,quant", [("tiny-gpt-oss", "mxfp4"), ("tiny-llama", "q8_0")])
 def test_row_sharded_prefill_on_gpus_matches_single_gpu(name, quant, world):
