@@ -331,6 +331,7 @@ class MoEFFN:
     """
 
     MXF4_TENSOR_CORE = True      # class switch (tests compare against the bf16-activation path by turning it off)
+    EXPERT_TP = False            # True: split every expert's FFN width over the ranks even when the expert count divides (tests)
     MXF4_PAIR_MAX_TOKENS = 8     # up to this many tokens every (token, expert) pair is its own tile: no packing pass
     DOWN_KSPLIT = 3              # one-token decode: K ranges of the down projection (their partial rows are summed by the combine)
 
@@ -339,11 +340,19 @@ class MoEFFN:
         p = prefix or f"blk.{layer}"
         H, F, E = c.hidden, c.expert_ffn, c.n_experts
         ep = par.world if par.mode == "tp" else 1
-        if E % ep:
-            raise ValueError(f"{E} experts do not split over {ep} ranks")
+        # Experts are sharded whole (expert parallelism) when their count divides by the ranks.  Otherwise (or with EXPERT_TP) every
+        # rank keeps all experts and a slice of each one's FFN width, cut on the 32-element blocks of the quantised formats and not
+        # necessarily even (src/model/gptoss_tp.cpp:343-354 in the reference): gate / up rows [lo, hi), the matching input columns of
+        # down, the down bias on rank 0 only; every rank then holds a partial sum for every pair, reduced like any row-parallel output.
+        self.expert_tp = ep > 1 and (E % ep != 0 or self.EXPERT_TP)
         self.E, self.K = E, c.n_experts_used
-        self.e_lo, self.e_hi = (par.rank * (E // ep), (par.rank + 1) * (E // ep)) if ep > 1 else (0, E)
+        self.e_lo, self.e_hi = (par.rank * (E // ep), (par.rank + 1) * (E // ep)) if (ep > 1 and not self.expert_tp) else (0, E)
         rng = (self.e_lo, self.e_hi)
+        f_lo, f_hi = 0, F
+        if self.expert_tp:
+            if F % 32 or F // 32 < ep:
+                raise ValueError(f"expert FFN width {F} cannot be cut into {ep} slices of whole 32-element blocks")
+            f_lo, f_hi = _even_chunks(F, ep, 32)[par.rank]
         rw = src.matrix(f"{p}.ffn_gate_inp.weight", E, H)
         self.router = Linear(rw if rw.fmt == ops.WFormat.BF16 else QuantWeight(**_as_bf16(rw)))
         self.router_bias = src.vector(f"{p}.ffn_gate_inp.bias", E) if with_bias else None
@@ -355,6 +364,8 @@ class MoEFFN:
             g = src.matrix(f"{p}.ffn_gate_exps.weight", F, H, E, experts=rng)
             u = src.matrix(f"{p}.ffn_up_exps.weight", F, H, E, experts=rng)
         d = src.matrix(f"{p}.ffn_down_exps.weight", H, F, E, experts=rng)
+        if self.expert_tp:
+            g, u, d = g.slice_rows(f_lo, f_hi), u.slice_rows(f_lo, f_hi), d.slice_k(f_lo, f_hi, requant=True)
         # MXFP4 banks on a GPU run on the block-scaled tensor-core kernel: gate / up / down stay three banks in its tiled layout
         self.mx = None
         # all-MXFP4 expert banks multiply MXFP8 activations (e4m3 + a power-of-two scale per 32): the arithmetic of the block-scaled
@@ -371,14 +382,17 @@ class MoEFFN:
         self.expert_scale = None         # optional per-expert factor on the down projection's output, folded into the routing weight
         self.gu_bias = self.down_bias = self.g_bias = self.u_bias = None
         if with_bias:
-            gb = src.table(f"{p}.ffn_gate_exps.bias", (E, F))[self.e_lo:self.e_hi]
-            ub = src.table(f"{p}.ffn_up_exps.bias", (E, F))[self.e_lo:self.e_hi]
+            gb = src.table(f"{p}.ffn_gate_exps.bias", (E, F))[self.e_lo:self.e_hi, f_lo:f_hi]
+            ub = src.table(f"{p}.ffn_up_exps.bias", (E, F))[self.e_lo:self.e_hi, f_lo:f_hi]
+            F = f_hi - f_lo
             n = self.e_hi - self.e_lo
             if self.mx is not None:
                 self.g_bias, self.u_bias = gb.contiguous(), ub.contiguous()
             else:
                 self.gu_bias = torch.cat([gb.reshape(n, F // 16, 16), ub.reshape(n, F // 16, 16)], dim=2).reshape(n, 2 * F).contiguous()
             self.down_bias = src.table(f"{p}.ffn_down_exps.bias", (E, H))[self.e_lo:self.e_hi].contiguous()
+            if self.expert_tp and par.rank != 0:
+                self.down_bias = torch.zeros_like(self.down_bias)      # the bias joins the reduced sum once
         self.act = act
         self.reduce = ep > 1
         self.group_gemv_max_tokens = 0   # > 0: batches of up to that many tokens take the expert-major GEMV path
@@ -611,7 +625,7 @@ class TransformerModel:
             return False
         if not sc.can_shard(fb.T) or fb.T < self.SHARD_MIN_TOKENS:
             return False
-        return all(("moe" not in L) or (L["moe"].mx is not None and L["moe"].shared is None) for L in self.layers)
+        return all(("moe" not in L) or (L["moe"].mx is not None and L["moe"].shared is None and not L["moe"].expert_tp) for L in self.layers)
 
     SHARD_MIN_TOKENS = 512
 

@@ -34,6 +34,9 @@ def main():
     else:
         dev = torch.device("cpu")
     cfg = preset(name)
+    if os.environ.get("MX_TEST_EXPERT_TP"):              # split every expert's FFN width over the ranks instead of sharding experts whole
+        from machx_inference_engine_b200.models.transformer import MoEFFN
+        MoEFFN.EXPERT_TP = True
     n_pre = int(os.environ.get("MX_TEST_PREFILL", "200"))     # 1024 lets the sharded path take the chunk on 2, 4 and 8 ranks
     ctx = max(1024, (n_pre + 8 + 255) // 128 * 128)
     if comm == "sharded" and par.fused is not None:      # row-sharded prefill for chunks that divide over the ranks

@@ -70,6 +70,21 @@ def test_tp2_on_cpu_ranks_matches_single_rank(name, quant):
     _close(one, two, cos=0.996 if moe else 0.999, arg=0.93 if moe else 0.95)
 
 
+@pytest.mark.parametrize("name,quant", [("tiny-gpt-oss", "mxfp4"), ("tiny-qwen3moe", "q8_0")])
+def test_within_expert_tp_on_cpu_ranks_matches_single_rank(name, quant):
+    """Every expert's FFN width cut over two ranks (the form taken when the expert count does not divide by the ranks): gate / up rows
+    and the matching down columns per rank, down bias on rank 0, partial sums reduced."""
+    one = _run(1, name, quant, "cpu")
+    os.environ["MX_TEST_EXPERT_TP"] = "1"
+    try:
+        two = _run(2, name, quant, "cpu")
+    finally:
+        del os.environ["MX_TEST_EXPERT_TP"]
+    assert two["world"] == 2
+    moe8 = quant == "mxfp4"
+    _close(one, two, cos=0.996 if moe8 else 0.999, arg=0.93 if moe8 else 0.95)
+
+
 @pytest.mark.parametrize("name,quant", [("tiny-llama", "q8_0"), ("tiny-qwen3next", "q8_0")])
 def test_layer_split_on_cpu_ranks_matches_single_rank(name, quant):
     """Pipeline (layer split) over two gloo ranks: same logits as one rank; micro-batched prefill equals whole-chunk prefill."""
@@ -130,6 +145,21 @@ def test_tp2_on_gpus_fused_and_nccl_match_single_gpu(name, quant):
     # reduce-scatter form of the fused collective (owner sums its rows and re-broadcasts them as bf16)
     rs = _run(2, name, quant, "cuda", "fused-rs")
     _close(one, rs, cos=0.995 if moe else 0.999, arg=0.93 if moe else 0.95)
+
+
+@pytest.mark.gpu
+def test_within_expert_tp_on_gpus_matches_single_gpu():
+    """Every expert's FFN width cut over two GPUs (block-scaled MXFP4 banks of half width, partial sums through the fused all-reduce)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    one = _run(1, "tiny-gpt-oss", "mxfp4", "cuda")
+    os.environ["MX_TEST_EXPERT_TP"] = "1"
+    try:
+        two = _run(2, "tiny-gpt-oss", "mxfp4", "cuda", "fused")
+    finally:
+        del os.environ["MX_TEST_EXPERT_TP"]
+    assert two["world"] == 2
+    _close(one, two, cos=0.995, arg=0.93)
 
 
 @pytest.mark.gpu
