@@ -476,8 +476,9 @@ class LLMEngine:
         seqs = [plan[i][0] for i in sampled_rows]
         greedy = all(s.params.temperature <= 0 and s.params.repetition_penalty == 1.0 for s in seqs)
         par = getattr(self.model, "par", None)
-        # graphs hold only this library's kernels: the NCCL baseline path (no fused collectives) runs eagerly
-        nccl_path = par is not None and par.enabled and par.fused is None
+        # graphs hold only this library's kernels: the NCCL baseline path (no fused collectives) and the layer split (NCCL
+        # point-to-point hand-offs between the stages) run eagerly
+        nccl_path = par is not None and par.enabled and (par.fused is None or par.mode == "pp")
         use_graph = (decode_only and greedy and self.opts.cuda_graphs and self.device.type == "cuda"
                      and (self.state is None or all(s.n_computed > 0 for s, _ in plan))
                      and len(plan) <= max(self.opts.graph_batch_sizes) and not nccl_path and not self.spec_k)
