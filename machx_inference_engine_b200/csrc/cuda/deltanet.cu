@@ -55,6 +55,73 @@ __global__ void __launch_bounds__(128) conv1d_silu_kernel(const bf16* __restrict
     for (int p = 0; p + 1 < Kc; ++p) *reinterpret_cast<uint32_t*>(state + ((size_t)slot * (Kc - 1) + p) * C + c) = pack_bf16(v0[p + 1], v1[p + 1]);
 }
 
+// Prefill form: a thread owns four channels and walks a strip of CONV_STRIP tokens with the Kc-tap window in registers, so an
+// input element is read about once (plus Kc-1 per strip) instead of Kc times and the taps are loaded once per strip.  Sequence
+// starts inside a strip reload the window from the stored state.
+constexpr int CONV_STRIP = 16;
+
+template <int KC>
+__global__ void __launch_bounds__(128) conv1d_silu_strip_kernel(const bf16* __restrict__ x, int ld, int C, const float* __restrict__ w,
+                                                                const bf16* __restrict__ state, const int* __restrict__ slots,
+                                                                const int* __restrict__ cu_q, int B, int T, bf16* __restrict__ y,
+                                                                bf16* __restrict__ ckpt) {
+  pdl_prologue();
+  const int c = (blockIdx.x * 128 + threadIdx.x) * 4;
+  if (c >= C) return;
+  const int t_lo = blockIdx.y * CONV_STRIP, t_hi = min(T, t_lo + CONV_STRIP);
+  float wt[KC][4];                         // [tap][channel]
+#pragma unroll
+  for (int j = 0; j < KC; ++j)
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) wt[j][ch] = w[(size_t)(c + ch) * KC + j];
+  float win[KC][4];                        // win[j] = input at t - (KC - 1) + j
+  auto unpack = [](const uint2 raw, float (&o)[4]) {
+    o[0] = bf16_lo(raw.x); o[1] = bf16_hi(raw.x); o[2] = bf16_lo(raw.y); o[3] = bf16_hi(raw.y);
+  };
+  uint2 cur[CONV_STRIP];                   // the strip's own inputs, fetched together (one trip to memory)
+#pragma unroll
+  for (int i = 0; i < CONV_STRIP; ++i)
+    cur[i] = t_lo + i < t_hi ? *reinterpret_cast<const uint2*>(x + (size_t)(t_lo + i) * ld + c) : make_uint2(0u, 0u);
+  int b = 0;
+  while (b + 1 < B && cu_q[b + 1] <= t_lo) ++b;
+  int t_start = cu_q[b], t_next = cu_q[b + 1];
+  bool fresh = true;                       // the window has to be (re)loaded: first token of the strip or of a sequence
+#pragma unroll
+  for (int i = 0; i < CONV_STRIP; ++i) {
+    const int t = t_lo + i;
+    if (t >= t_hi) break;
+    while (t >= t_next && b + 1 < B) { ++b; t_start = cu_q[b]; t_next = cu_q[b + 1]; fresh = true; }
+    if (fresh) {
+      const int slot = slots[b];
+#pragma unroll
+      for (int j = 0; j < KC - 1; ++j) {
+        const int src = t - (KC - 1) + j;
+        unpack(src >= t_start ? *reinterpret_cast<const uint2*>(x + (size_t)src * ld + c)
+                              : *reinterpret_cast<const uint2*>(state + ((size_t)slot * (KC - 1) + (KC - 1 + src - t_start)) * C + c), win[j]);
+      }
+      fresh = false;
+    }
+    unpack(cur[i], win[KC - 1]);
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < KC; ++j)
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) a[ch] = fmaf(wt[j][ch], win[j][ch], a[ch]);
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) a[ch] = __fdividef(a[ch], 1.f + __expf(-a[ch]));
+    *reinterpret_cast<uint2*>(y + (size_t)t * C + c) = make_uint2(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]));
+    if (ckpt)
+#pragma unroll
+      for (int pp = 0; pp < KC - 1; ++pp)
+        *reinterpret_cast<uint2*>(ckpt + ((size_t)t * (KC - 1) + pp) * C + c) =
+            make_uint2(pack_bf16(win[pp + 1][0], win[pp + 1][1]), pack_bf16(win[pp + 1][2], win[pp + 1][3]));
+#pragma unroll
+    for (int j = 0; j < KC - 1; ++j)         // slide
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) win[j][ch] = win[j + 1][ch];
+  }
+}
+
 // New streaming state after a multi-token step: the last Kc-1 inputs of every sequence.  One thread owns a channel
 // pair of a sequence and walks p upwards, so an old entry is read (at p + q_len) before it is overwritten.
 __global__ void conv1d_state_kernel(const bf16* __restrict__ x, int ld, int C, int Kc, bf16* __restrict__ state, const int* __restrict__ slots,
@@ -248,8 +315,16 @@ MX_HOST_API int mx_conv1d_silu(const void* x, int ld, int C, int Kc, const float
   if (T <= 0) return 0;
   if (Kc < 2 || Kc > 8 || (C & 1) || (ld & 1)) return -101;
   const int fuse = max_q_len == 1;
-  dim3 grid((C / 2 + 127) / 128, T);
-  launch_pdl(conv1d_silu_kernel, dim3(grid), dim3(128), 0, st, (const bf16*)x, ld, C, Kc, w, (bf16*)state, slots, cu_q, B, (bf16*)y, (bf16*)ckpt, fuse);
+  if (!fuse && T >= 4 * CONV_STRIP && (Kc == 4 || Kc == 3) && (C & 3) == 0 && (ld & 3) == 0 && ((uintptr_t)x & 7) == 0 && ((uintptr_t)state & 7) == 0) {
+    dim3 grid((C / 4 + 127) / 128, (T + CONV_STRIP - 1) / CONV_STRIP);
+    if (Kc == 4)
+      launch_pdl(conv1d_silu_strip_kernel<4>, dim3(grid), dim3(128), 0, st, (const bf16*)x, ld, C, w, (const bf16*)state, slots, cu_q, B, T, (bf16*)y, (bf16*)ckpt);
+    else
+      launch_pdl(conv1d_silu_strip_kernel<3>, dim3(grid), dim3(128), 0, st, (const bf16*)x, ld, C, w, (const bf16*)state, slots, cu_q, B, T, (bf16*)y, (bf16*)ckpt);
+  } else {
+    dim3 grid((C / 2 + 127) / 128, T);
+    launch_pdl(conv1d_silu_kernel, dim3(grid), dim3(128), 0, st, (const bf16*)x, ld, C, Kc, w, (bf16*)state, slots, cu_q, B, (bf16*)y, (bf16*)ckpt, fuse);
+  }
   if (!fuse) {
     dim3 g2((C / 2 + 127) / 128, B);
     launch_pdl(conv1d_state_kernel, dim3(g2), dim3(128), 0, st, (const bf16*)x, ld, C, Kc, (bf16*)state, slots, cu_q);

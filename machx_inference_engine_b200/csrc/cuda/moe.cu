@@ -161,13 +161,16 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
 }
 // to_f16: convert the bf16 rows to fp16 while copying (MXFP4 expert GEMMs run in fp16 x fp16 mode)
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ packed_token, const int* __restrict__ total_rows,
-                                  __nv_bfloat16* __restrict__ xp, int H, int to_f16) {
+                                  __nv_bfloat16* __restrict__ xp, int H, int to_f16, int zero_pad) {
   pdl_prologue();
   const int r = blockIdx.x;
   if (r >= total_rows[1]) return;
   const int t = packed_token[r];
   uint4* dst = reinterpret_cast<uint4*>(xp + (size_t)r * H);
   if (t < 0) {
+    // tile padding: unless asked, the row is left as it is.  The grouped GEMM's output row depends on its own input row only and
+    // nothing refers to padding rows afterwards, and at ten experts per token the padding is as many rows as the live ones.
+    if (!zero_pad) return;
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
   } else {
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * H);
@@ -305,10 +308,11 @@ MX_HOST_API int mx_moe_pack(const int* topk_idx, int n_pairs, int K, int E, int 
 }
 
 MX_HOST_API int mx_moe_gather(const void* x, const int* packed_token, const int* num_tiles, void* xp, int H, int max_rows, int to_f16,
-                              cudaStream_t st) {
+                              int zero_pad, cudaStream_t st) {
   if (max_rows <= 0) return 0;
   if (H % 8) return -101;
-  launch_pdl(moe_gather_kernel, dim3(max_rows), dim3(128), 0, st, (const __nv_bfloat16*)x, packed_token, num_tiles, (__nv_bfloat16*)xp, H, to_f16);
+  launch_pdl(moe_gather_kernel, dim3(max_rows), dim3(128), 0, st, (const __nv_bfloat16*)x, packed_token, num_tiles, (__nv_bfloat16*)xp, H, to_f16,
+             zero_pad);
   return (int)cudaGetLastError();
 }
 

@@ -201,7 +201,6 @@ def conv1d_silu(x, w, state, state_slots, cu_q, max_q_len, ckpt=None):
 DELTANET_CHUNKED_MIN_T = 128      # batches of at least this many tokens take the chunked tensor-core scan (no checkpoints there)
 
 
-@_profiled("deltanet_scan")
 def deltanet_scan(qkv, n_k, ab, a_idx, b_idx, k_of_v, ssm_a, dt_bias, state, state_slots, cu_q, n_v, eps=1e-6, ckpt=None, chunked=None):
     """``chunked``: None picks the chunked (WY) tensor-core kernel for prefill-sized batches without checkpoints and the sequential
     kernel otherwise; True / False force one (tests, benches)."""
@@ -603,10 +602,12 @@ def expert_group_gemv(x, w: QuantWeight, pk: MoePacking, x_index=None, bias=None
     return out
 
 
-def moe_gather(x, pk: MoePacking, f16=False):
+def moe_gather(x, pk: MoePacking, f16=False, zero_pad=False):
+    """Rows of ``x`` in packed order.  Padding rows of the expert tiles are left unwritten unless ``zero_pad`` (no consumer reads them:
+    a grouped GEMM row depends on its own input row only)."""
     H = x.shape[1]
     xp = torch.empty(pk.max_rows, H, dtype=torch.float16 if f16 else torch.bfloat16, device=x.device)
-    _check(_lib.cuda().mx_moe_gather(_p(x), _p(pk.packed_token), _p(pk.num_tiles), _p(xp), H, pk.max_rows, int(f16), _stream()), "moe_gather")
+    _check(_lib.cuda().mx_moe_gather(_p(x), _p(pk.packed_token), _p(pk.num_tiles), _p(xp), H, pk.max_rows, int(f16), int(zero_pad), _stream()), "moe_gather")
     _count()
     return xp
 

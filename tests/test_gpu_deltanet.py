@@ -24,7 +24,7 @@ def rel_err(a, b):
     return float((a - b).norm() / (b.norm() + 1e-12))
 
 
-@pytest.mark.parametrize("lens,Kc", [([37], 4), ([1, 1, 1], 4), ([5, 1, 130, 2], 4), ([3, 2], 3)])
+@pytest.mark.parametrize("lens,Kc", [([37], 4), ([1, 1, 1], 4), ([5, 1, 130, 2], 4), ([3, 2], 3), ([70, 201], 4), ([100, 1, 30], 3)])
 def test_conv1d_silu(lens, Kc):
     torch.manual_seed(0)
     C, pad = 384, 40

@@ -170,8 +170,10 @@ def test_grouped_gemm_and_moe_pipeline(fmt):
     assert torch.equal(pk.packed_token[:nrows], pk_r.packed_token[:nrows])
     assert torch.equal(pk.pair_to_packed, pk_r.pair_to_packed)
     assert torch.equal(pk.tile_expert[: int(pk.num_tiles[0])], pk_r.tile_expert[: int(pk.num_tiles[0])])
-    xp = K().moe_gather(x, pk)
+    xp = K().moe_gather(x, pk, zero_pad=True)
     assert torch.equal(xp[:nrows], ref.moe_gather(x, pk_r)[:nrows])
+    live = pk_r.packed_token[:nrows] >= 0                               # default: padding rows are left unwritten
+    assert torch.equal(K().moe_gather(x, pk)[:nrows][live], ref.moe_gather(x, pk_r)[:nrows][live])
     gu = make_weight(fmt, 2 * F, H, E=E, seed=3)
     dn = make_weight(fmt, H, F, E=E, seed=4)
     gb = torch.randn(E, 2 * F, device=dev()) * 0.1
