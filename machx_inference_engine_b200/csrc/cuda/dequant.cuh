@@ -79,7 +79,12 @@ __device__ __forceinline__ float magic128(uint32_t v) {
   // result bytes: [3]=0x43, [2]=v.byte[I], [1]=0, [0]=0
   return __uint_as_float(__byte_perm(v, 0x00000043u, 0x4055 | (I << 8)));
 }
-// float(32768 + byte) : 0x47000000 has ulp 2^-8*... use bf16-style placement: value = 2^15 + byte*2^8?  (unused)
+// float(2^23 + byte i of `v`) built with one byte permute: exact for all 256 byte values (the int -> float conversion instruction
+// issues at a quarter of the rate of the permute + add it replaces)
+template <int I>
+__device__ __forceinline__ float magic23(uint32_t v) {
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440 | I));     // bytes: [3] = 0x4B, [2] = [1] = 0, [0] = v.byte[I]
+}
 
 // ------------------------------------------------------------------ decode to 32 floats
 template <int FMT>
@@ -103,12 +108,14 @@ __device__ __forceinline__ void decode32_f32<WF_Q8>(const RowPtrs& r, int kb, fl
   const float d = __half2float(__ldg(reinterpret_cast<const __half*>(r.p1) + kb));
   const uint4 a = ldg16(r.p0 + (size_t)kb * 32), b = ldg16(r.p0 + (size_t)kb * 32 + 16);
   const uint32_t q[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  constexpr float OFF = 8388736.f;                  // 2^23 + 128 (see magic23)
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    w[4 * i + 0] = d * (float)(int8_t)(q[i] & 0xFF);
-    w[4 * i + 1] = d * (float)(int8_t)((q[i] >> 8) & 0xFF);
-    w[4 * i + 2] = d * (float)(int8_t)((q[i] >> 16) & 0xFF);
-    w[4 * i + 3] = d * (float)(int8_t)(q[i] >> 24);
+    const uint32_t u = q[i] ^ 0x80808080u;
+    w[4 * i + 0] = d * (magic23<0>(u) - OFF);
+    w[4 * i + 1] = d * (magic23<1>(u) - OFF);
+    w[4 * i + 2] = d * (magic23<2>(u) - OFF);
+    w[4 * i + 3] = d * (magic23<3>(u) - OFF);
   }
 }
 
@@ -348,14 +355,12 @@ __device__ __forceinline__ void raw_decode(const uint8_t* slot, const uint8_t* a
     const float d = __half2float(*reinterpret_cast<const __half*>(aux + 2 * half));
     const uint4 a = *reinterpret_cast<const uint4*>(slot), b = *reinterpret_cast<const uint4*>(slot + 16);
     const uint32_t q[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    const float c = -128.f * d;
+    constexpr float OFF = 8388736.f;                // 2^23 + 128: (2^23 + byte) - OFF is the signed value, exactly
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const uint32_t u = q[i] ^ 0x80808080u;        // signed -> offset-128 unsigned bytes
-      // 128 + byte trick only holds for bytes < 128: split into (byte>>1)*2 + (byte&1) is costly, use two ranges
-      const float f0 = (float)(int)(u & 0xFF), f1 = (float)(int)((u >> 8) & 0xFF), f2 = (float)(int)((u >> 16) & 0xFF), f3 = (float)(int)(u >> 24);
-      o[2 * i] = pack_bf16(fmaf(f0, d, c), fmaf(f1, d, c));
-      o[2 * i + 1] = pack_bf16(fmaf(f2, d, c), fmaf(f3, d, c));
+      o[2 * i] = pack_bf16((magic23<0>(u) - OFF) * d, (magic23<1>(u) - OFF) * d);
+      o[2 * i + 1] = pack_bf16((magic23<2>(u) - OFF) * d, (magic23<3>(u) - OFF) * d);
     }
   } else if constexpr (FMT == WF_Q4K) {
     const uint4 hdr = *reinterpret_cast<const uint4*>(aux);
