@@ -111,7 +111,9 @@ class Linear:
                  act_limit: float = 7.0, reduce: bool = False):
         self.w, self.bias, self.act, self.act_alpha, self.act_limit, self.reduce = w, bias, act, act_alpha, act_limit, reduce
 
-    def __call__(self, x: torch.Tensor, par: Optional[ParallelCtx] = None, out_f32: bool = False) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, par: Optional[ParallelCtx] = None, out_f32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is not None:        # (column-parallel projections only: a caller-provided slice of a shared output)
+            return ops.linear(x, self.w, bias=self.bias, act=self.act, act_alpha=self.act_alpha, act_limit=self.act_limit, out_f32=out_f32, out=out)
         if self.reduce and par is not None and par.enabled:
             # the bias of a row-parallel layer is added once, after the reduction
             if par.fused is not None and x.is_cuda:
@@ -126,9 +128,16 @@ class MultiLinear:
 
     def __init__(self, parts: list[Linear]):
         self.parts = parts
+        self.widths = [p.w.N // 2 if p.act != ACT_NONE else p.w.N for p in parts]
 
     def __call__(self, x, par=None, out_f32=False):
-        return torch.cat([p(x, par, out_f32) for p in self.parts], dim=1)
+        # every part writes its own column slice of one output (no concatenation pass)
+        out = torch.empty(x.shape[0], sum(self.widths), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+        lo = 0
+        for p, n in zip(self.parts, self.widths):
+            p(x, par, out_f32, out=out[:, lo:lo + n])
+            lo += n
+        return out
 
 
 def _fuse_rows(ws: list[QuantWeight], biases: list[Optional[torch.Tensor]]):

@@ -282,18 +282,27 @@ def _out_kind(dtype) -> int:
     return {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}[dtype]
 
 
-def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None):
+def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None, out=None):
+    """``out``: write into this [M, n_out] view (unit column stride; a column slice of a wider matrix is fine), so that projections
+    whose weights differ in format can share one output without a concatenation."""
     assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[-1] == w.K and w.E == 1
     M = x.shape[0]
     n_out = w.N // 2 if act != ACT_NONE else w.N
-    out = torch.empty(M, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    if out is None:
+        out = torch.empty(M, n_out, dtype=odt, device=x.device)
+    assert out.shape == (M, n_out) and out.dtype == odt and (M == 0 or out.stride(1) == 1)
     if M == 0:
         return out
     fmt, p0, p1, p2, p3 = _planes(w)
     lib = _lib.cuda()
     if M <= GEMV_MAX_M and row_scale is None:
-        _check(lib.mx_gemv(fmt, p0, p1, p2, p3, _p(x), _p(out), _p(bias), M, w.N, w.K, int(out_f32), act, C.c_float(act_alpha),
+        # the GEMV kernels write dense rows: a strided view of more than one row goes through a dense buffer
+        dst = out if (M == 1 or out.stride(0) == n_out) else torch.empty(M, n_out, dtype=odt, device=x.device)
+        _check(lib.mx_gemv(fmt, p0, p1, p2, p3, _p(x), _p(dst), _p(bias), M, w.N, w.K, int(out_f32), act, C.c_float(act_alpha),
                            C.c_float(act_limit), _vp(0), _vp(0), M, 1, _stream()), "gemv")
+        if dst is not out:
+            out.copy_(dst)
     else:
         xa = _gemm_a(x, w)
         if M >= DEQUANT_ONCE_MIN_M and fmt != int(WFormat.BF16):
@@ -303,7 +312,7 @@ def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limi
             _check(lib.mx_dequant_bf16(fmt, p0, p1, p2, p3, C.c_longlong(w.N), w.K, _p(wb), _stream()), "dequant_bf16")
             _count()
             fmt, p0, p1, p2, p3 = int(WFormat.BF16), _p(wb), _vp(0), _vp(0), _vp(0)
-        _check(lib.mx_gemm(_p(xa), fmt, p0, p1, p2, p3, 1, _p(out), n_out, int(out_f32), _p(bias), _p(row_scale), act,
+        _check(lib.mx_gemm(_p(xa), fmt, p0, p1, p2, p3, 1, _p(out), out.stride(0), int(out_f32), _p(bias), _p(row_scale), act,
                            C.c_float(act_alpha), C.c_float(act_limit), M, w.N, w.K, _vp(0), _vp(0), _pick_bn(M, w.N), _stream()), "gemm")
     _count()
     return out

@@ -112,7 +112,9 @@ def glu(x, act, alpha=1.702, limit=7.0):
     return _act(act, g, u, alpha, limit).to(torch.bfloat16)
 
 
-def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None):
+def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None, out=None):
+    if out is not None:
+        return out.copy_(linear(x, w, bias, act, act_alpha, act_limit, out_f32, row_scale))
     y = _mm(x, _dense(w)[0])
     if bias is not None:
         y = y + bias
