@@ -176,6 +176,7 @@ def main(argv=None):
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--graph-reps", type=int, default=0, help="time N back-to-back calls inside one CUDA graph (per-call time without launch gaps)")
+    ap.add_argument("--gated", action="store_true", help="gemv: the rows are 16-row interleaved gate / up pairs and the epilogue is SwiGLU")
     ap.add_argument("--gemv-path", default="auto", choices=["auto", "register", "stream"], help="which decode GEMV kernel to time")
     ap.add_argument("--decode-once", action="store_true", help="gemm: time ops.linear (weight decoded once to bf16 + TMA-fed kernel)")
     ap.add_argument("--layers", type=int, default=1, help="distinct weight copies cycled through so that weights are never L2-resident")
@@ -272,10 +273,10 @@ def main(argv=None):
         i = [0]
 
         def fn():
-            K.linear(x, ws[i[0] % len(ws)])
+            K.linear(x, ws[i[0] % len(ws)], act=ref.ACT_SWIGLU if a.gated else ref.ACT_NONE)
             i[0] += 1
         med, mn = timeit(fn, a.iters)
-        report(f"gemv[{a.fmt}] {a.n}x{a.k}", med, mn, bytes_=ws[0].nbytes)
+        report(f"gemv[{a.fmt}{' gated' if a.gated else ''}] {a.n}x{a.k}", med, mn, bytes_=ws[0].nbytes)
     elif a.kernel == "expert_gemv":
         E, H, F, k = a.experts, a.hidden, a.ffn, a.topk
         gu = weight(2 * F, H, E)

@@ -470,7 +470,7 @@ int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const 
                     float act_alpha, float act_limit, const int* slot_expert, const float* slot_scale, int slots, int x_div, int e_lo,
                     int e_hi, const PeerOut* peer, cudaStream_t st);
 }
-// 0: pick per case (the streaming kernel where it measured faster: bf16 matrices and the gated MXFP4 expert GEMV),
+// 0: pick per case (the streaming kernel where it measured faster: bf16 and Q4_K matrices and the gated MXFP4 expert GEMV),
 // 1: register-streamed kernels only, 2: streaming kernel wherever it applies (tests, A/B timing)
 static int g_gemv_path = 0;
 MX_HOST_API void mx_gemv_set_path(int path) { g_gemv_path = path; }
@@ -492,7 +492,7 @@ static int gemv_impl(int wfmt, const void* w0, const void* w1, const void* w2, c
   if (K % 32 && !(wfmt == WF_BF16 && K % 8 == 0 && act == 0)) return -102;
   if ((wfmt == WF_Q4K || wfmt == WF_Q6K) && (K % 256)) return -103;
   if (!slot_expert && act == 0 && (M < 1 || M > GEMV_MAX_M)) return -106;
-  if (g_gemv_path == 2 || (g_gemv_path == 0 && (wfmt == WF_BF16 || (wfmt == WF_MXFP4 && act != 0)))) {
+  if (g_gemv_path == 2 || (g_gemv_path == 0 && (wfmt == WF_BF16 || wfmt == WF_Q4K || (wfmt == WF_MXFP4 && act != 0)))) {
     const int rc = gemv_stream_try(wfmt, WeightRef{w0, w1, w2, w3}, x, y, bias, M, N, K, out_f32, act, act_alpha, act_limit, slot_expert,
                                    slot_scale, slots, x_div, g_e_lo, g_e_hi, peer, stream);
     if (rc != 1) return rc;

@@ -3,11 +3,11 @@
 // 4-8 consumer warps.  A weight row block is one contiguous run per plane, so a stage is one or two bulk copies;
 // the bytes in flight per SM are set by the ring (about 100 KB), not by registers or occupancy, which is what a
 // 1-3 us kernel needs to get near HBM speed.  Formats: bf16, Q8 (int8 + fp16 scale per 32), MXFP4 (E2M1 nibbles +
-// e8m0 scale per 32).  MXFP4 rows are multiplied in packed fp16: the E2M1 codes become f16x2 words by byte permutes,
+// e8m0 scale per 32), Q4_K (native 144-byte blocks; the codes meet block-scaled 16-bit activations in dp4a, see the staging code).  MXFP4 rows are multiplied in packed fp16: the E2M1 codes become f16x2 words by byte permutes,
 // the activation row is staged once as f16 scaled into range, 16-term partial sums run in HFMA2 and are folded
 // into fp32 with the block scale.
 //
-// Modes (same contract as the register-streamed kernels in gemv.cu, which remain the path for Q4_K / Q6_K and for
+// Modes (same contract as the register-streamed kernels in gemv.cu, which remain the path for Q6_K and for
 // shapes this kernel does not take):
 //   dense : y[m][n] for m < M, all rows share each decoded weight
 //   slots : one activation row per slot (MoE decode: slot -> expert id -> weight slab; slots of experts owned by
@@ -40,6 +40,7 @@ template <int FMT> struct GsCfg;
 template <> struct GsCfg<WF_BF16> { static constexpr int WARPS = 4, RPW = 1; };
 template <> struct GsCfg<WF_Q8> { static constexpr int WARPS = 8, RPW = 1; };
 template <> struct GsCfg<WF_MXFP4> { static constexpr int WARPS = 8, RPW = 2; };
+template <> struct GsCfg<WF_Q4K> { static constexpr int WARPS = 8, RPW = 2; };
 
 // activation rows = RMSNorm(x + delta_scale * delta) * w
 struct GsNorm {
@@ -91,11 +92,17 @@ struct GsParams {
   PeerOut peer;
 };
 
-template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes0(int K) { return FMT == WF_BF16 ? K * 2 : (FMT == WF_Q8 ? K : K / 2); }
-template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes1(int K) {
-  return FMT == WF_BF16 ? 0 : (FMT == WF_Q8 ? q8_d_stride(K) * 2 : mxfp4_e_stride(K));
+template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes0(int K) {
+  return FMT == WF_BF16 ? K * 2 : (FMT == WF_Q8 ? K : (FMT == WF_Q4K ? K / 256 * 144 : K / 2));
 }
-template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row0(int K, int KC) { return FMT == WF_BF16 ? KC * 2 : gs_row_bytes0<FMT>(K); }
+template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes1(int K) {
+  return (FMT == WF_BF16 || FMT == WF_Q4K) ? 0 : (FMT == WF_Q8 ? q8_d_stride(K) * 2 : mxfp4_e_stride(K));
+}
+template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row0(int K, int KC) {
+  return FMT == WF_BF16 ? KC * 2 : (FMT == WF_Q4K ? KC / 256 * 144 : gs_row_bytes0<FMT>(K));
+}
+// bytes of one staged activation row.  Q4_K: nine planes of K/64 (+1 pad) 16-byte words, see the staging code in the kernel.
+template <int FMT> __host__ __device__ __forceinline__ int gs_xrow_bytes(int K) { return FMT == WF_Q4K ? 9 * ((K >> 6) + 1) * 16 : K * 2; }
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -158,13 +165,16 @@ template <int FMT> struct Gran;
 template <> struct Gran<WF_BF16> { static constexpr int GE = 8, XR = 4, NGMAX = 16; };     // 8 bf16 = one 16-byte word
 template <> struct Gran<WF_Q8> { static constexpr int GE = 16, XR = 8, NGMAX = 8; };       // 16 int8
 template <> struct Gran<WF_MXFP4> { static constexpr int GE = 32, XR = 16, NGMAX = 4; };   // 32 nibbles
+template <> struct Gran<WF_Q4K> { static constexpr int GE = 64, XR = 36, NGMAX = 1; };     // 32 bytes of a Q4_K block: two sub-blocks
 
 // The MXFP4 path keeps its f16 activation row in four planes (plane i holds elements 8i..8i+7 of every 32-element
 // granule), so that consecutive lanes read consecutive 16-byte words of each plane.
+// The Q4_K path holds the row as block-scaled 16-bit integers split into a high and a low int8 (see the staging code), in
+// eight planes plus a ninth with the scales and sums of the granule's two sub-blocks.  g counts granules from the row start.
 template <int FMT>
 __device__ __forceinline__ void load_xg(const uint8_t* __restrict__ xrow, int g, int K, uint32_t (&xr)[Gran<FMT>::XR]) {
-  const uint4* p = reinterpret_cast<const uint4*>(xrow) + (FMT == WF_MXFP4 ? g : g * (Gran<FMT>::XR / 4));
-  const int step = FMT == WF_MXFP4 ? (K >> 5) : 1;
+  const uint4* p = reinterpret_cast<const uint4*>(xrow) + ((FMT == WF_MXFP4 || FMT == WF_Q4K) ? g : g * (Gran<FMT>::XR / 4));
+  const int step = FMT == WF_MXFP4 ? (K >> 5) : (FMT == WF_Q4K ? (K >> 6) + 1 : 1);
 #pragma unroll
   for (int i = 0; i < Gran<FMT>::XR / 4; ++i) {
     const uint4 v = p[i * step];
@@ -177,6 +187,7 @@ template <int FMT> struct WG;
 template <> struct WG<WF_BF16> { uint4 v; };
 template <> struct WG<WF_Q8> { float w[16]; float d; };
 template <> struct WG<WF_MXFP4> { uint32_t t[16]; float sc; };
+template <> struct WG<WF_Q4K> { uint32_t a[8], b[8]; float dA, dB, mA, mB; };   // 4-bit codes as bytes (sub-blocks 2j / 2j+1), d * scale, dmin * min
 
 template <int FMT>
 __device__ __forceinline__ void decode_g(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, int g, WG<FMT>& o) {
@@ -189,6 +200,30 @@ __device__ __forceinline__ void decode_g(const uint8_t* __restrict__ w0, const u
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       o.w[4 * i] = s8_to_float<0>(q[i]); o.w[4 * i + 1] = s8_to_float<1>(q[i]); o.w[4 * i + 2] = s8_to_float<2>(q[i]); o.w[4 * i + 3] = s8_to_float<3>(q[i]);
+    }
+  } else if constexpr (FMT == WF_Q4K) {
+    // granule g = 64 elements: group j = g & 3 of block g >> 2.  Byte i of the 32-byte group holds element i of sub-block 2j in its
+    // low nibble and element i of sub-block 2j+1 in its high nibble.
+    const uint8_t* blk = w0 + (size_t)(g >> 2) * 144;
+    const int j = g & 3;
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j), q1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * j);
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    // the 6-bit scales and minima of the two sub-blocks, two bytes each (same packing as q4k_scale_min)
+    const int sh = (j & 1) * 16;
+    const uint32_t s0 = hdr.y >> sh, s1 = hdr.z >> sh, s2 = hdr.w >> sh;
+    const uint32_t sc2 = j < 2 ? (s0 & 0x3F3Fu) : ((s2 & 0x0F0Fu) | ((s0 >> 2) & 0x3030u));
+    const uint32_t mn2 = j < 2 ? (s1 & 0x3F3Fu) : (((s2 >> 4) & 0x0F0Fu) | ((s1 >> 2) & 0x3030u));
+    o.dA = d * (__uint_as_float(0x4B000000u | (sc2 & 0xFFu)) - 8388608.f);
+    o.dB = d * (__uint_as_float(0x4B000000u | (sc2 >> 8)) - 8388608.f);
+    o.mA = dmin * (__uint_as_float(0x4B000000u | (mn2 & 0xFFu)) - 8388608.f);
+    o.mB = dmin * (__uint_as_float(0x4B000000u | (mn2 >> 8)) - 8388608.f);
+    const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o.a[i] = q[i] & 0x0F0F0F0Fu;
+      o.b[i] = (q[i] >> 4) & 0x0F0F0F0Fu;
     }
   } else {
     const uint4 v = reinterpret_cast<const uint4*>(w0)[g];
@@ -220,6 +255,20 @@ __device__ __forceinline__ float dot_g(const WG<FMT>& w, const uint32_t (&xr)[Gr
       s1 = fmaf(w.w[2 * i + 1], bf16_hi(xr[i]), s1);
     }
     return (s0 + s1) * w.d;
+  } else if constexpr (FMT == WF_Q4K) {
+    // exact integer dot products of the 4-bit codes with the high and the low byte of the 16-bit activations; the
+    // minima multiply the plain sums of the activations
+    int ah = 0, al = 0, bh = 0, bl = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int pa = 4 * (k >> 1) + (k & 1), pb = 16 + pa;
+      ah = __dp4a((int)w.a[k], (int)xr[pa], ah);
+      al = __dp4a((int)w.a[k], (int)xr[pa + 2], al);
+      bh = __dp4a((int)w.b[k], (int)xr[pb], bh);
+      bl = __dp4a((int)w.b[k], (int)xr[pb + 2], bl);
+    }
+    const float fa = (float)(ah * 256 + al) * __uint_as_float(xr[32]), fb = (float)(bh * 256 + bl) * __uint_as_float(xr[33]);
+    return fmaf(w.dA, fa, fmaf(w.dB, fb, -fmaf(w.mA, __uint_as_float(xr[34]), w.mB * __uint_as_float(xr[35]))));
   } else {
     uint32_t a0 = 0u, a1 = 0u;
 #pragma unroll
@@ -234,7 +283,7 @@ __device__ __forceinline__ float dot_g(const WG<FMT>& w, const uint32_t (&xr)[Gr
 // one weight row (one k chunk of it) against MM activation rows; CACHED: the lane's x granules are in registers
 template <int FMT, int MM, bool CACHED, int NG>
 __device__ __forceinline__ void gs_row(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, int ng, int lane,
-                                       const uint32_t (&xc)[CACHED ? NG : 1][Gran<FMT>::XR], const uint8_t* __restrict__ xs, int K, int k0,
+                                       const uint32_t (&xc)[CACHED ? NG : 1][Gran<FMT>::XR], const uint8_t* __restrict__ xs, int K, int gbase,
                                        const float* __restrict__ xscale, float (&acc)[MM]) {
   if constexpr (CACHED) {
 #pragma unroll
@@ -255,7 +304,7 @@ __device__ __forceinline__ void gs_row(const uint8_t* __restrict__ w0, const uin
 #pragma unroll
         for (int m = 0; m < MM; ++m) {
           uint32_t xr[Gran<FMT>::XR];
-          load_xg<FMT>(xs + ((size_t)m * K + k0) * 2, g, K, xr);
+          load_xg<FMT>(xs + (size_t)m * gs_xrow_bytes<FMT>(K), gbase + g, K, xr);
           acc[m] += dot_g<FMT>(wg, xr, FMT == WF_MXFP4 ? xscale[m] : 1.f);
         }
       }
@@ -274,7 +323,8 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
   const int r0b = gs_stage_row0<FMT>(K, p.KC), r1b = g1;                 // bytes per row inside a stage
   const int plane1_off = RB * r0b;
   const int stage_bytes = RB * (r0b + r1b);
-  const int x_bytes = (p.n_xrows * K * 2 + 15) & ~15;
+  const int xrow_bytes = gs_xrow_bytes<FMT>(K);
+  const int x_bytes = (p.n_xrows * xrow_bytes + 15) & ~15;
   uint8_t* xs = smem;
   uint8_t* stages = smem + x_bytes;
   const int NST = p.nst;
@@ -326,8 +376,16 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
             const int f0 = blk * FB, nf = min(FB, F - f0);
             const int grow = 32 * (f0 >> 4) + (f0 & 15);
             mbar_expect_tx(full, 2u * nf * (r0b + r1b));
-            bulk_g2s(dst, b0 + (size_t)grow * g0, nf * r0b, full);
-            bulk_g2s(dst + FB * r0b, b0 + (size_t)(grow + 16) * g0, nf * r0b, full);
+            if (p.nkc == 1) {
+              bulk_g2s(dst, b0 + (size_t)grow * g0, nf * r0b, full);
+              bulk_g2s(dst + FB * r0b, b0 + (size_t)(grow + 16) * g0, nf * r0b, full);
+            } else {
+              // k chunk of every gate row and of every up row (chunked formats have no second plane)
+              for (int r = 0; r < nf; ++r) {
+                bulk_g2s(dst + r * r0b, b0 + (size_t)(grow + r) * g0 + (size_t)kc * r0b, r0b, full);
+                bulk_g2s(dst + (FB + r) * r0b, b0 + (size_t)(grow + 16 + r) * g0 + (size_t)kc * r0b, r0b, full);
+              }
+            }
             if (r1b) {
               bulk_g2s(dst + plane1_off, b1 + (size_t)grow * g1, nf * r1b, full);
               bulk_g2s(dst + plane1_off + FB * r1b, b1 + (size_t)(grow + 16) * g1, nf * r1b, full);
@@ -391,6 +449,49 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
           }
         }
         if (lane == 0) xscale[m] = exp2f((float)-sh);
+      }
+    } else if constexpr (FMT == WF_Q4K) {
+      // Each 32-element sub-block of a row becomes 16-bit integers X = rint(x * 32512 / amax), split as X = 256 h + l with h, l in
+      // int8, so that a 4-bit code times an activation is two exact dp4a terms.  A thread converts one 8-element chunk and its
+      // three neighbours hold the rest of the sub-block.  Layout of a row: plane c (0..7) holds, for every 64-element granule,
+      // the words {h[0..3], h[4..7], l[0..3], l[4..7]} of the granule's chunk c; plane 8 holds {scale A, scale B, sum A, sum B}.
+      const int nch = K >> 3, pstep = (K >> 6) + 1;
+      for (int m = 0; m < p.n_xrows; ++m) {
+        const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)m * K);
+        uint4* row = reinterpret_cast<uint4*>(xs + (size_t)m * xrow_bytes);
+        for (int c = threadIdx.x; c < nch; c += WARPS * 32) {          // K % 256 == 0: whole warps take part
+          const uint4 v = __ldg(xr + c);
+          const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+          float f[8];
+          float amax = 0.f, sum = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            f[2 * i] = bf16_lo(q[i]);
+            f[2 * i + 1] = bf16_hi(q[i]);
+            amax = fmaxf(amax, fmaxf(fabsf(f[2 * i]), fabsf(f[2 * i + 1])));
+            sum += f[2 * i] + f[2 * i + 1];
+          }
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          const float inv = amax > 0.f ? 32512.f / amax : 0.f;
+          uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int X = __float2int_rn(f[i] * inv);
+            const int h = (X + 128) >> 8, l = X - (h << 8);
+            hw[i >> 2] |= (uint32_t)(h & 0xFF) << (8 * (i & 3));
+            lw[i >> 2] |= (uint32_t)(l & 0xFF) << (8 * (i & 3));
+          }
+          const int g = c >> 3, cc = c & 7;
+          row[cc * pstep + g] = make_uint4(hw[0], hw[1], lw[0], lw[1]);
+          if ((c & 3) == 0) {
+            float* aux = reinterpret_cast<float*>(row + 8 * pstep + g);
+            aux[cc >> 2] = amax * (1.f / 32512.f);
+            aux[2 + (cc >> 2)] = sum;
+          }
+        }
       }
     } else if (p.norm.x) {
       // residual add + RMSNorm in place of a separate launch.  All consumer threads work on one row at a time and keep their
@@ -481,7 +582,7 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
         el = owned ? e - p.e_lo : 0;
       }
       const int xrow = p.slot_mode ? slot / p.x_div : 0;
-      const uint8_t* xbase = xs + (size_t)xrow * K * 2;
+      const uint8_t* xbase = xs + (size_t)xrow * xrow_bytes;
       float acc[GATED ? 2 : RPW][MM];
 #pragma unroll
       for (int r = 0; r < (GATED ? 2 : RPW); ++r)
@@ -493,7 +594,7 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
             x_tag = xrow * p.nkc + kc;
 #pragma unroll
             for (int j = 0; j < NG; ++j)
-              if (lane + 32 * j < ng) load_xg<FMT>(xbase + (size_t)kc * p.KC * 2, lane + 32 * j, K, xc[j]);
+              if (lane + 32 * j < ng) load_xg<FMT>(xbase, kc * ng + lane + 32 * j, K, xc[j]);
           }
           const int s = it % NST;
           ok = mbar_wait(bar0 + 8 * s, (it / NST) & 1, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag);
@@ -503,7 +604,7 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
           for (int r = 0; r < (GATED ? 2 : RPW); ++r) {
             // gated: the warp owns one feature of the block; its gate row sits at `warp`, its up row FB rows further
             const int srow = GATED ? (r == 0 ? 0 : FB) + warp : warp * RPW + r;
-            gs_row<FMT, MM, CACHED, NG>(st + (size_t)srow * r0b, st + plane1_off + (size_t)srow * r1b, ng, lane, xc, xbase, K, kc * p.KC,
+            gs_row<FMT, MM, CACHED, NG>(st + (size_t)srow * r0b, st + plane1_off + (size_t)srow * r1b, ng, lane, xc, xbase, K, kc * ng,
                                     xscale + xrow, acc[r]);
           }
           __syncwarp();
@@ -645,11 +746,20 @@ static int gs_dispatch(GsParams& p, cudaStream_t st) {
     if (p.K % n) return 1;
     p.nkc = n; p.KC = p.K / n;
   }
+  if (FMT == WF_Q4K && p.K > 32 * Gran<FMT>::NGMAX * Gran<FMT>::GE) {
+    // whole 256-element blocks per chunk, as few chunks as possible
+    int n = 2;
+    while (n < 64 && (p.K % n || (p.K / n) % 256 || p.K / n > 32 * Gran<FMT>::NGMAX * Gran<FMT>::GE)) ++n;
+    if (n >= 64) return 1;
+    p.nkc = n; p.KC = p.K / n;
+  }
   if (p.KC / Gran<FMT>::GE > 32 * Gran<FMT>::NGMAX || p.KC % Gran<FMT>::GE) return 1;
+  if (gated && p.nkc > 1 && gs_row_bytes1<FMT>(p.K)) return 1;
+  if (FMT == WF_Q4K && p.KC / Gran<FMT>::GE < 16) return 1;      // fewer than half of the lanes would have a granule
   if (FMT == WF_MXFP4 && p.K > 4096) return 1;
   p.nblk = gated ? (p.N / 2 + RB / 2 - 1) / (RB / 2) : (p.N + RB - 1) / RB;
   const int stage = RB * (gs_stage_row0<FMT>(p.K, p.KC) + gs_row_bytes1<FMT>(p.K));
-  const int fixed = ((p.n_xrows * p.K * 2 + 15) & ~15) + 2 * GS_MAX_STAGES * 8 + GS_MAX_XROWS * 4 + 16;
+  const int fixed = ((p.n_xrows * gs_xrow_bytes<FMT>(p.K) + 15) & ~15) + 2 * GS_MAX_STAGES * 8 + GS_MAX_XROWS * 4 + 16;
   p.nst = GS_MAX_STAGES;
   while (p.nst > 2 && fixed + p.nst * stage > 113 * 1024) --p.nst;        // two CTAs per SM when three stages still fit
   if (fixed + p.nst * stage > 113 * 1024) p.nst = min(GS_MAX_STAGES, max(2, (200 * 1024 - fixed) / stage));
@@ -657,7 +767,9 @@ static int gs_dispatch(GsParams& p, cudaStream_t st) {
   if (smem > 200 * 1024 || p.nst < 2) return 1;
   // granules per lane: 3/4 of the maximum covers K <= 3072 with a quarter fewer registers
   constexpr int NGS = Gran<FMT>::NGMAX * 3 / 4;
-  if (p.KC / Gran<FMT>::GE <= 32 * NGS) return gs_dispatch_ng<FMT, NGS>(p, smem, gated, st);
+  if constexpr (NGS >= 1) {
+    if (p.KC / Gran<FMT>::GE <= 32 * NGS) return gs_dispatch_ng<FMT, NGS>(p, smem, gated, st);
+  }
   return gs_dispatch_ng<FMT, Gran<FMT>::NGMAX>(p, smem, gated, st);
 }
 
@@ -677,9 +789,10 @@ int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const 
 static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* y, const float* bias, int M, int N, int K, int out_f32, int act,
                              float act_alpha, float act_limit, const int* slot_expert, const float* slot_scale, int slots, int x_div, int e_lo,
                              int e_hi, const PeerOut* peer, const GsNorm* norm, const GsRoute* route, cudaStream_t st) {
-  if (wfmt != WF_BF16 && wfmt != WF_Q8 && wfmt != WF_MXFP4) return 1;
+  if (wfmt != WF_BF16 && wfmt != WF_Q8 && wfmt != WF_MXFP4 && wfmt != WF_Q4K) return 1;
   if (K % 32 && !(wfmt == WF_BF16 && K % 8 == 0)) return 1;
-  if (act != 0 && wfmt != WF_MXFP4) return 1;                // gated epilogue: one feature per warp needs RPW == 2
+  if (wfmt == WF_Q4K && K % 256) return 1;
+  if (act != 0 && wfmt != WF_MXFP4 && wfmt != WF_Q4K) return 1;      // gated epilogue: one feature per warp needs RPW == 2
   if (act != 0 && (N % 32)) return 1;
   GsParams p;
   p.w = w; p.x = (const __nv_bfloat16*)x; p.y = y; p.bias = bias; p.slot_expert = slot_expert; p.slot_scale = slot_scale;
@@ -690,16 +803,17 @@ static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* 
   p.n_xrows = p.slot_mode ? (p.slots + p.x_div - 1) / p.x_div : M;
   if (p.n_xrows < 1 || p.n_xrows > GS_MAX_XROWS) return 1;
   // every plane row must start on a 16-byte boundary for the bulk copies
-  const int rb0 = wfmt == WF_BF16 ? K * 2 : (wfmt == WF_Q8 ? K : K / 2);
+  const int rb0 = wfmt == WF_BF16 ? K * 2 : (wfmt == WF_Q8 ? K : (wfmt == WF_Q4K ? K / 256 * 144 : K / 2));
   if (rb0 % 16) return 1;
   if (((uintptr_t)w.p0 & 15) || (w.p1 && ((uintptr_t)w.p1 & 15)) || ((uintptr_t)x & 15)) return 1;
   if (peer) p.peer = *peer; else p.peer.world = 0;
   if (norm) p.norm = *norm; else p.norm.x = nullptr;
   if (route) p.route = *route; else p.route.ticket = nullptr;
-  if ((norm || route) && (wfmt == WF_MXFP4 || p.slot_mode)) return 1;
+  if ((norm || route) && (wfmt == WF_MXFP4 || wfmt == WF_Q4K || p.slot_mode)) return 1;
   switch (wfmt) {
     case WF_BF16: return gs_dispatch<WF_BF16>(p, st);
     case WF_Q8: return gs_dispatch<WF_Q8>(p, st);
+    case WF_Q4K: return gs_dispatch<WF_Q4K>(p, st);
     default: return gs_dispatch<WF_MXFP4>(p, st);
   }
 }
