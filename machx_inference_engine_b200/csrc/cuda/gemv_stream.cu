@@ -3,11 +3,12 @@
 // 4-8 consumer warps.  A weight row block is one contiguous run per plane, so a stage is one or two bulk copies;
 // the bytes in flight per SM are set by the ring (about 100 KB), not by registers or occupancy, which is what a
 // 1-3 us kernel needs to get near HBM speed.  Formats: bf16, Q8 (int8 + fp16 scale per 32), MXFP4 (E2M1 nibbles +
-// e8m0 scale per 32), Q4_K (native 144-byte blocks; the codes meet block-scaled 16-bit activations in dp4a, see the staging code).  MXFP4 rows are multiplied in packed fp16: the E2M1 codes become f16x2 words by byte permutes,
+// e8m0 scale per 32), Q4_K (native 144-byte blocks) and Q6_K (four planes).  Q8, Q4_K and Q6_K codes meet block-scaled 16-bit
+// activations in dp4a (exact integer partial sums, see the staging code).  MXFP4 rows are multiplied in packed fp16: the E2M1 codes become f16x2 words by byte permutes,
 // the activation row is staged once as f16 scaled into range, 16-term partial sums run in HFMA2 and are folded
 // into fp32 with the block scale.
 //
-// Modes (same contract as the register-streamed kernels in gemv.cu, which remain the path for Q6_K and for
+// Modes (same contract as the register-streamed kernels in gemv.cu, which remain the path for the
 // shapes this kernel does not take):
 //   dense : y[m][n] for m < M, all rows share each decoded weight
 //   slots : one activation row per slot (MoE decode: slot -> expert id -> weight slab; slots of experts owned by
@@ -36,11 +37,17 @@ constexpr int GS_MAX_CK = 8;      // pairs per token the fused combine + norm pr
 constexpr int GS_NORM_MAX_K = 4096;   // row length the fused norm prologue holds in registers (8 float4 per thread at 128 threads)
 constexpr int GS_NORM_MAX_M = 2;      // rows: they are normalised one after the other, so more rows go through the separate kernel
 
+// Q8 weights against block-scaled 16-bit activations in dp4a: chosen inside this file for WF_Q8 launches without the norm prologue
+// or the router tail (those write and read the activation rows as bf16)
+constexpr int WF_Q8I = 16;
+
 template <int FMT> struct GsCfg;
 template <> struct GsCfg<WF_BF16> { static constexpr int WARPS = 4, RPW = 1; };
 template <> struct GsCfg<WF_Q8> { static constexpr int WARPS = 8, RPW = 1; };
 template <> struct GsCfg<WF_MXFP4> { static constexpr int WARPS = 8, RPW = 2; };
 template <> struct GsCfg<WF_Q4K> { static constexpr int WARPS = 8, RPW = 2; };
+template <> struct GsCfg<WF_Q8I> { static constexpr int WARPS = 8, RPW = 1; };
+template <> struct GsCfg<WF_Q6K> { static constexpr int WARPS = 8, RPW = 2; };
 
 // activation rows = RMSNorm(x + delta_scale * delta) * w
 struct GsNorm {
@@ -93,16 +100,34 @@ struct GsParams {
 };
 
 template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes0(int K) {
-  return FMT == WF_BF16 ? K * 2 : (FMT == WF_Q8 ? K : (FMT == WF_Q4K ? K / 256 * 144 : K / 2));
+  return FMT == WF_BF16 ? K * 2 : ((FMT == WF_Q8 || FMT == WF_Q8I) ? K : (FMT == WF_Q4K ? K / 256 * 144 : K / 2));      // MXFP4 nibbles, Q6_K low nibbles
 }
 template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes1(int K) {
-  return (FMT == WF_BF16 || FMT == WF_Q4K) ? 0 : (FMT == WF_Q8 ? q8_d_stride(K) * 2 : mxfp4_e_stride(K));
+  return (FMT == WF_BF16 || FMT == WF_Q4K) ? 0 : ((FMT == WF_Q8 || FMT == WF_Q8I) ? q8_d_stride(K) * 2 : (FMT == WF_Q6K ? K / 4 : mxfp4_e_stride(K)));
 }
+// Q6_K only: the int8 sub-block scales and the fp16 block scales
+template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes2(int K) { return FMT == WF_Q6K ? K / 16 : 0; }
+template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes3(int K) { return FMT == WF_Q6K ? q6k_d_stride(K) * 2 : 0; }
+// bytes of one row inside a stage: the whole row, or its k chunk for the formats that are chunked (bf16, Q4_K, Q8 in the dp4a form)
 template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row0(int K, int KC) {
-  return FMT == WF_BF16 ? KC * 2 : (FMT == WF_Q4K ? KC / 256 * 144 : gs_row_bytes0<FMT>(K));
+  return FMT == WF_BF16 ? KC * 2 : (FMT == WF_Q4K ? KC / 256 * 144 : (FMT == WF_Q8I ? KC : (FMT == WF_Q6K ? KC / 2 : gs_row_bytes0<FMT>(K))));
+}
+template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row1(int K, int KC) {
+  return (FMT == WF_Q8I && KC != K) ? KC / 16 : (FMT == WF_Q6K ? KC / 4 : gs_row_bytes1<FMT>(K));
+}
+template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row2(int K, int KC) { return FMT == WF_Q6K ? KC / 16 : 0; }
+// (the fp16 block scales of a Q6_K row are a few 16-byte words: every chunk of the row brings the whole run)
+template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row_all(int K, int KC) {
+  return gs_stage_row0<FMT>(K, KC) + gs_stage_row1<FMT>(K, KC) + gs_stage_row2<FMT>(K, KC) + gs_row_bytes3<FMT>(K);
 }
 // bytes of one staged activation row.  Q4_K: nine planes of K/64 (+1 pad) 16-byte words, see the staging code in the kernel.
-template <int FMT> __host__ __device__ __forceinline__ int gs_xrow_bytes(int K) { return FMT == WF_Q4K ? 9 * ((K >> 6) + 1) * 16 : K * 2; }
+template <int FMT> __host__ __device__ __forceinline__ int gs_xplane_step(int K) {
+  return (FMT == WF_Q4K || FMT == WF_Q6K) ? (K >> 6) + 1 : (FMT == WF_Q8I ? ((K >> 5) | 1) : 0);
+}
+template <int FMT> __host__ __device__ __forceinline__ int gs_xrow_bytes(int K) {
+  return FMT == WF_Q4K ? 9 * gs_xplane_step<FMT>(K) * 16
+                       : (FMT == WF_Q6K ? 10 * gs_xplane_step<FMT>(K) * 16 : (FMT == WF_Q8I ? 5 * gs_xplane_step<FMT>(K) * 16 : K * 2));
+}
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -166,6 +191,8 @@ template <> struct Gran<WF_BF16> { static constexpr int GE = 8, XR = 4, NGMAX = 
 template <> struct Gran<WF_Q8> { static constexpr int GE = 16, XR = 8, NGMAX = 8; };       // 16 int8
 template <> struct Gran<WF_MXFP4> { static constexpr int GE = 32, XR = 16, NGMAX = 4; };   // 32 nibbles
 template <> struct Gran<WF_Q4K> { static constexpr int GE = 64, XR = 36, NGMAX = 1; };     // 32 bytes of a Q4_K block: two sub-blocks
+template <> struct Gran<WF_Q6K> { static constexpr int GE = 64, XR = 40, NGMAX = 1; };     // four 16-element sub-blocks
+template <> struct Gran<WF_Q8I> { static constexpr int GE = 32, XR = 17, NGMAX = 3; };     // one Q8 block
 
 // The MXFP4 path keeps its f16 activation row in four planes (plane i holds elements 8i..8i+7 of every 32-element
 // granule), so that consecutive lanes read consecutive 16-byte words of each plane.
@@ -173,13 +200,15 @@ template <> struct Gran<WF_Q4K> { static constexpr int GE = 64, XR = 36, NGMAX =
 // eight planes plus a ninth with the scales and sums of the granule's two sub-blocks.  g counts granules from the row start.
 template <int FMT>
 __device__ __forceinline__ void load_xg(const uint8_t* __restrict__ xrow, int g, int K, uint32_t (&xr)[Gran<FMT>::XR]) {
-  const uint4* p = reinterpret_cast<const uint4*>(xrow) + ((FMT == WF_MXFP4 || FMT == WF_Q4K) ? g : g * (Gran<FMT>::XR / 4));
-  const int step = FMT == WF_MXFP4 ? (K >> 5) : (FMT == WF_Q4K ? (K >> 6) + 1 : 1);
+  constexpr bool PLANES = FMT == WF_MXFP4 || FMT == WF_Q4K || FMT == WF_Q6K || FMT == WF_Q8I;
+  const uint4* p = reinterpret_cast<const uint4*>(xrow) + (PLANES ? g : g * (Gran<FMT>::XR / 4));
+  const int step = FMT == WF_MXFP4 ? (K >> 5) : (PLANES ? gs_xplane_step<FMT>(K) : 1);
 #pragma unroll
   for (int i = 0; i < Gran<FMT>::XR / 4; ++i) {
     const uint4 v = p[i * step];
     xr[4 * i] = v.x; xr[4 * i + 1] = v.y; xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
   }
+  if constexpr (FMT == WF_Q8I) xr[16] = *reinterpret_cast<const uint32_t*>(p + 4 * step);      // the block's scale (first word of the last plane)
 }
 
 // decoded weight granule, ready to be multiplied with any number of activation rows
@@ -187,10 +216,19 @@ template <int FMT> struct WG;
 template <> struct WG<WF_BF16> { uint4 v; };
 template <> struct WG<WF_Q8> { float w[16]; float d; };
 template <> struct WG<WF_MXFP4> { uint32_t t[16]; float sc; };
+template <> struct WG<WF_Q6K> { uint32_t ev[8], od[8]; float ds[4]; };          // 6-bit codes of the even / odd elements, d * sub-block scale
+template <> struct WG<WF_Q8I> { uint32_t q[8]; float d; };
 template <> struct WG<WF_Q4K> { uint32_t a[8], b[8]; float dA, dB, mA, mB; };   // 4-bit codes as bytes (sub-blocks 2j / 2j+1), d * scale, dmin * min
 
+// the second pair of planes and the first block of the chunk (index into the row's block scales) are Q6_K's
+struct GsPlanes23 {
+  const uint8_t* w2;
+  const uint8_t* w3;
+  int dblk0;
+};
+
 template <int FMT>
-__device__ __forceinline__ void decode_g(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, int g, WG<FMT>& o) {
+__device__ __forceinline__ void decode_g(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, const GsPlanes23& w23, int g, WG<FMT>& o) {
   if constexpr (FMT == WF_BF16) {
     o.v = reinterpret_cast<const uint4*>(w0)[g];
   } else if constexpr (FMT == WF_Q8) {
@@ -201,6 +239,28 @@ __device__ __forceinline__ void decode_g(const uint8_t* __restrict__ w0, const u
     for (int i = 0; i < 4; ++i) {
       o.w[4 * i] = s8_to_float<0>(q[i]); o.w[4 * i + 1] = s8_to_float<1>(q[i]); o.w[4 * i + 2] = s8_to_float<2>(q[i]); o.w[4 * i + 3] = s8_to_float<3>(q[i]);
     }
+  } else if constexpr (FMT == WF_Q6K) {
+    // granule g = 64 elements: 32 bytes of low nibbles (byte i = e[2i] | e[2i+1] << 4), four words of high bit pairs (one per 16
+    // elements: byte b holds e[2b], e[2b+1], e[8+2b], e[9+2b] from bit 0 up), four int8 scales, the block's fp16 scale
+    const uint4 l0 = reinterpret_cast<const uint4*>(w0)[2 * g], l1 = reinterpret_cast<const uint4*>(w0)[2 * g + 1];
+    const uint4 hv = reinterpret_cast<const uint4*>(w1)[g];
+    const uint32_t scw = reinterpret_cast<const uint32_t*>(w23.w2)[g];
+    const float d = __half2float(reinterpret_cast<const __half*>(w23.w3)[w23.dblk0 + (g >> 2)]);
+    // int8 -> float: 2^23 + (s ^ 0x80) - (2^23 + 128)
+    const uint32_t su = scw ^ 0x80808080u;
+    o.ds[0] = d * s8_to_float<0>(su); o.ds[1] = d * s8_to_float<1>(su); o.ds[2] = d * s8_to_float<2>(su); o.ds[3] = d * s8_to_float<3>(su);
+    const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+    const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t h = hw[i >> 1] >> ((i & 1) * 4);
+      o.ev[i] = (lw[i] & 0x0F0F0F0Fu) | ((h & 0x03030303u) << 4);
+      o.od[i] = ((lw[i] >> 4) & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
+    }
+  } else if constexpr (FMT == WF_Q8I) {
+    const uint4 a = reinterpret_cast<const uint4*>(w0)[2 * g], b = reinterpret_cast<const uint4*>(w0)[2 * g + 1];
+    o.d = __half2float(reinterpret_cast<const __half*>(w1)[g]);
+    o.q[0] = a.x; o.q[1] = a.y; o.q[2] = a.z; o.q[3] = a.w; o.q[4] = b.x; o.q[5] = b.y; o.q[6] = b.z; o.q[7] = b.w;
   } else if constexpr (FMT == WF_Q4K) {
     // granule g = 64 elements: group j = g & 3 of block g >> 2.  Byte i of the 32-byte group holds element i of sub-block 2j in its
     // low nibble and element i of sub-block 2j+1 in its high nibble.
@@ -255,6 +315,32 @@ __device__ __forceinline__ float dot_g(const WG<FMT>& w, const uint32_t (&xr)[Gr
       s1 = fmaf(w.w[2 * i + 1], bf16_hi(xr[i]), s1);
     }
     return (s0 + s1) * w.d;
+  } else if constexpr (FMT == WF_Q6K) {
+    // per 16-element sub-block: exact integer dot product of the codes with the 16-bit activations, then
+    // d * scale * (D * activation scale - 32 * sum of the activations)
+    float r = 0.f;
+#pragma unroll
+    for (int sb = 0; sb < 4; ++sb) {
+      int dh = 0, dl = 0;
+#pragma unroll
+      for (int c = 2 * sb; c < 2 * sb + 2; ++c) {
+        dh = __dp4a((int)w.ev[c], (int)xr[4 * c], dh);
+        dh = __dp4a((int)w.od[c], (int)xr[4 * c + 1], dh);
+        dl = __dp4a((int)w.ev[c], (int)xr[4 * c + 2], dl);
+        dl = __dp4a((int)w.od[c], (int)xr[4 * c + 3], dl);
+      }
+      r = fmaf(w.ds[sb], fmaf((float)(dh * 256 + dl), __uint_as_float(xr[32 + (sb >> 1)]), -32.f * __uint_as_float(xr[36 + sb])), r);
+    }
+    return r;
+  } else if constexpr (FMT == WF_Q8I) {
+    int ah = 0, al = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int pa = 4 * (k >> 1) + (k & 1);
+      ah = __dp4a((int)w.q[k], (int)xr[pa], ah);
+      al = __dp4a((int)w.q[k], (int)xr[pa + 2], al);
+    }
+    return (float)(ah * 256 + al) * (w.d * __uint_as_float(xr[16]));
   } else if constexpr (FMT == WF_Q4K) {
     // exact integer dot products of the 4-bit codes with the high and the low byte of the 16-bit activations; the
     // minima multiply the plain sums of the activations
@@ -282,7 +368,7 @@ __device__ __forceinline__ float dot_g(const WG<FMT>& w, const uint32_t (&xr)[Gr
 
 // one weight row (one k chunk of it) against MM activation rows; CACHED: the lane's x granules are in registers
 template <int FMT, int MM, bool CACHED, int NG>
-__device__ __forceinline__ void gs_row(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, int ng, int lane,
+__device__ __forceinline__ void gs_row(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, const GsPlanes23& w23, int ng, int lane,
                                        const uint32_t (&xc)[CACHED ? NG : 1][Gran<FMT>::XR], const uint8_t* __restrict__ xs, int K, int gbase,
                                        const float* __restrict__ xscale, float (&acc)[MM]) {
   if constexpr (CACHED) {
@@ -291,7 +377,7 @@ __device__ __forceinline__ void gs_row(const uint8_t* __restrict__ w0, const uin
       const int g = lane + 32 * j;
       if (g < ng) {
         WG<FMT> wg;
-        decode_g<FMT>(w0, w1, g, wg);
+        decode_g<FMT>(w0, w1, w23, g, wg);
         acc[0] += dot_g<FMT>(wg, xc[j], 1.f);
       }
     }
@@ -299,7 +385,7 @@ __device__ __forceinline__ void gs_row(const uint8_t* __restrict__ w0, const uin
 #pragma unroll 1
     for (int g = lane; g < ng; g += 32) {
       WG<FMT> wg;
-      decode_g<FMT>(w0, w1, g, wg);
+      decode_g<FMT>(w0, w1, w23, g, wg);
       {
 #pragma unroll
         for (int m = 0; m < MM; ++m) {
@@ -319,10 +405,10 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int K = p.K;
-  const int g0 = gs_row_bytes0<FMT>(K), g1 = gs_row_bytes1<FMT>(K);      // global row strides
-  const int r0b = gs_stage_row0<FMT>(K, p.KC), r1b = g1;                 // bytes per row inside a stage
-  const int plane1_off = RB * r0b;
-  const int stage_bytes = RB * (r0b + r1b);
+  const int g0 = gs_row_bytes0<FMT>(K), g1 = gs_row_bytes1<FMT>(K), g2 = gs_row_bytes2<FMT>(K), g3 = gs_row_bytes3<FMT>(K);      // global row strides
+  const int r0b = gs_stage_row0<FMT>(K, p.KC), r1b = gs_stage_row1<FMT>(K, p.KC), r2b = gs_stage_row2<FMT>(K, p.KC), r3b = g3;   // bytes per row inside a stage
+  const int plane1_off = RB * r0b, plane2_off = plane1_off + RB * r1b, plane3_off = plane2_off + RB * r2b;
+  const int stage_bytes = RB * (r0b + r1b + r2b + r3b);
   const int xrow_bytes = gs_xrow_bytes<FMT>(K);
   const int x_bytes = (p.n_xrows * xrow_bytes + 15) & ~15;
   uint8_t* xs = smem;
@@ -360,11 +446,15 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
         const int slot = u / p.nblk, blk = u - slot * p.nblk;
         const uint8_t* b0 = (const uint8_t*)p.w.p0;
         const uint8_t* b1 = (const uint8_t*)p.w.p1;
+        const uint8_t* b2 = (const uint8_t*)p.w.p2;
+        const uint8_t* b3 = (const uint8_t*)p.w.p3;
         if (p.slot_expert) {
           const int e = p.slot_expert[slot];
           if (e < p.e_lo || e >= p.e_hi) continue;
           b0 += (size_t)(e - p.e_lo) * p.N * g0;
           b1 += (size_t)(e - p.e_lo) * p.N * g1;
+          b2 += (size_t)(e - p.e_lo) * p.N * g2;
+          b3 += (size_t)(e - p.e_lo) * p.N * g3;
         }
         for (int kc = 0; kc < p.nkc && ok; ++kc, ++it) {
           const int s = it % NST;
@@ -392,13 +482,19 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
             }
           } else {
             const int row0 = blk * RB, nr = min(RB, p.N - row0);
-            mbar_expect_tx(full, (uint32_t)nr * (r0b + r1b));
+            mbar_expect_tx(full, (uint32_t)nr * (r0b + r1b + r2b + r3b));
             if (p.nkc == 1) {
               bulk_g2s(dst, b0 + (size_t)row0 * g0, nr * r0b, full);
+              if (r1b) bulk_g2s(dst + plane1_off, b1 + (size_t)row0 * g1, nr * r1b, full);
+              if (r2b) bulk_g2s(dst + plane2_off, b2 + (size_t)row0 * g2, nr * r2b, full);
             } else {
-              for (int r = 0; r < nr; ++r) bulk_g2s(dst + r * r0b, b0 + (size_t)(row0 + r) * g0 + (size_t)kc * r0b, r0b, full);
+              for (int r = 0; r < nr; ++r) {
+                bulk_g2s(dst + r * r0b, b0 + (size_t)(row0 + r) * g0 + (size_t)kc * r0b, r0b, full);
+                if (r1b) bulk_g2s(dst + plane1_off + r * r1b, b1 + (size_t)(row0 + r) * g1 + (size_t)kc * r1b, r1b, full);
+                if (r2b) bulk_g2s(dst + plane2_off + r * r2b, b2 + (size_t)(row0 + r) * g2 + (size_t)kc * r2b, r2b, full);
+              }
             }
-            if (r1b) bulk_g2s(dst + plane1_off, b1 + (size_t)row0 * g1, nr * r1b, full);
+            if (r3b) bulk_g2s(dst + plane3_off, b3 + (size_t)row0 * g3, nr * r3b, full);     // whole runs of block scales, every chunk
           }
         }
       }
@@ -450,17 +546,23 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
         }
         if (lane == 0) xscale[m] = exp2f((float)-sh);
       }
-    } else if constexpr (FMT == WF_Q4K) {
+    } else if constexpr (FMT == WF_Q4K || FMT == WF_Q6K || FMT == WF_Q8I) {
       // Each 32-element sub-block of a row becomes 16-bit integers X = rint(x * 32512 / amax), split as X = 256 h + l with h, l in
-      // int8, so that a 4-bit code times an activation is two exact dp4a terms.  A thread converts one 8-element chunk and its
-      // three neighbours hold the rest of the sub-block.  Layout of a row: plane c (0..7) holds, for every 64-element granule,
-      // the words {h[0..3], h[4..7], l[0..3], l[4..7]} of the granule's chunk c; plane 8 holds {scale A, scale B, sum A, sum B}.
-      const int nch = K >> 3, pstep = (K >> 6) + 1;
+      // int8, so that a weight code times an activation is two exact dp4a terms.  A thread converts one 8-element chunk and its
+      // three neighbours hold the rest of the sub-block.  Layout of a row: plane c (0..CPG-1) holds, for every granule, the words
+      // {h[0..3], h[4..7], l[0..3], l[4..7]} of the granule's chunk c; the last plane holds the scales and then the sums of the
+      // granule's sub-blocks (Q4_K: two sub-blocks in a 64-element granule; Q8: one).  Q6_K: a chunk's even elements fill the first
+      // word of h and of l, its odd elements the second (the order in which the 6-bit codes are assembled); the second to last plane
+      // holds the two scales, the last the sums of the four 16-element sub-blocks.
+      constexpr int CPG = Gran<FMT>::GE / 8, NSUB = CPG / 4;
+      const int nch = K >> 3, pstep = gs_xplane_step<FMT>(K);
       for (int m = 0; m < p.n_xrows; ++m) {
         const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)m * K);
         uint4* row = reinterpret_cast<uint4*>(xs + (size_t)m * xrow_bytes);
-        for (int c = threadIdx.x; c < nch; c += WARPS * 32) {          // K % 256 == 0: whole warps take part
-          const uint4 v = __ldg(xr + c);
+        for (int c0 = 0; c0 < nch; c0 += WARPS * 32) {          // every lane of a warp runs the loop body: the shuffles are warp wide
+          const int c = c0 + threadIdx.x;
+          const bool live = c < nch;
+          const uint4 v = live ? __ldg(xr + c) : make_uint4(0u, 0u, 0u, 0u);
           const uint32_t q[4] = {v.x, v.y, v.z, v.w};
           float f[8];
           float amax = 0.f, sum = 0.f;
@@ -474,6 +576,7 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
           amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
           amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
           sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          const float sum16 = sum;
           sum += __shfl_xor_sync(0xffffffffu, sum, 2);
           const float inv = amax > 0.f ? 32512.f / amax : 0.f;
           uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
@@ -481,15 +584,21 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
           for (int i = 0; i < 8; ++i) {
             const int X = __float2int_rn(f[i] * inv);
             const int h = (X + 128) >> 8, l = X - (h << 8);
-            hw[i >> 2] |= (uint32_t)(h & 0xFF) << (8 * (i & 3));
-            lw[i >> 2] |= (uint32_t)(l & 0xFF) << (8 * (i & 3));
+            const int at = FMT == WF_Q6K ? (i & 1) * 4 + (i >> 1) : i;          // byte of the two-word group that element i goes to
+            hw[at >> 2] |= (uint32_t)(h & 0xFF) << (8 * (at & 3));
+            lw[at >> 2] |= (uint32_t)(l & 0xFF) << (8 * (at & 3));
           }
-          const int g = c >> 3, cc = c & 7;
-          row[cc * pstep + g] = make_uint4(hw[0], hw[1], lw[0], lw[1]);
-          if ((c & 3) == 0) {
-            float* aux = reinterpret_cast<float*>(row + 8 * pstep + g);
-            aux[cc >> 2] = amax * (1.f / 32512.f);
-            aux[2 + (cc >> 2)] = sum;
+          const int g = c / CPG, cc = c % CPG;
+          if (live) {
+            row[cc * pstep + g] = make_uint4(hw[0], hw[1], lw[0], lw[1]);
+            float* aux = reinterpret_cast<float*>(row + CPG * pstep + g);
+            if constexpr (FMT == WF_Q6K) {
+              if ((c & 3) == 0) aux[cc >> 2] = amax * (1.f / 32512.f);
+              if ((c & 1) == 0) reinterpret_cast<float*>(row + (CPG + 1) * pstep + g)[cc >> 1] = sum16;
+            } else if ((c & 3) == 0) {
+              aux[cc >> 2] = amax * (1.f / 32512.f);
+              aux[NSUB + (cc >> 2)] = sum;
+            }
           }
         }
       }
@@ -604,7 +713,8 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
           for (int r = 0; r < (GATED ? 2 : RPW); ++r) {
             // gated: the warp owns one feature of the block; its gate row sits at `warp`, its up row FB rows further
             const int srow = GATED ? (r == 0 ? 0 : FB) + warp : warp * RPW + r;
-            gs_row<FMT, MM, CACHED, NG>(st + (size_t)srow * r0b, st + plane1_off + (size_t)srow * r1b, ng, lane, xc, xbase, K, kc * ng,
+            const GsPlanes23 w23{st + plane2_off + (size_t)srow * r2b, st + plane3_off + (size_t)srow * r3b, kc * (p.KC >> 8)};
+            gs_row<FMT, MM, CACHED, NG>(st + (size_t)srow * r0b, st + plane1_off + (size_t)srow * r1b, w23, ng, lane, xc, xbase, K, kc * ng,
                                     xscale + xrow, acc[r]);
           }
           __syncwarp();
@@ -727,7 +837,10 @@ static int gs_launch(const GsParams& p, int smem, cudaStream_t st) {
 
 template <int FMT, int NG>
 static int gs_dispatch_ng(GsParams& p, int smem, bool gated, cudaStream_t st) {
-  if (gated) return gs_launch<FMT, 1, true, NG>(p, smem, st);
+  if (gated) {
+    if constexpr (FMT == WF_Q6K || FMT == WF_Q8I) return 1;       // no gated form (one row per warp, or four planes)
+    else return gs_launch<FMT, 1, true, NG>(p, smem, st);
+  }
   if (p.slot_mode || p.M == 1) return gs_launch<FMT, 1, false, NG>(p, smem, st);
   if (FMT == WF_MXFP4) return 1;
   if (p.M <= 2) return gs_launch<FMT, 2, false, NG>(p, smem, st);
@@ -746,7 +859,7 @@ static int gs_dispatch(GsParams& p, cudaStream_t st) {
     if (p.K % n) return 1;
     p.nkc = n; p.KC = p.K / n;
   }
-  if (FMT == WF_Q4K && p.K > 32 * Gran<FMT>::NGMAX * Gran<FMT>::GE) {
+  if ((FMT == WF_Q4K || FMT == WF_Q6K || FMT == WF_Q8I) && p.K > 32 * Gran<FMT>::NGMAX * Gran<FMT>::GE) {
     // whole 256-element blocks per chunk, as few chunks as possible
     int n = 2;
     while (n < 64 && (p.K % n || (p.K / n) % 256 || p.K / n > 32 * Gran<FMT>::NGMAX * Gran<FMT>::GE)) ++n;
@@ -755,10 +868,9 @@ static int gs_dispatch(GsParams& p, cudaStream_t st) {
   }
   if (p.KC / Gran<FMT>::GE > 32 * Gran<FMT>::NGMAX || p.KC % Gran<FMT>::GE) return 1;
   if (gated && p.nkc > 1 && gs_row_bytes1<FMT>(p.K)) return 1;
-  if (FMT == WF_Q4K && p.KC / Gran<FMT>::GE < 16) return 1;      // fewer than half of the lanes would have a granule
   if (FMT == WF_MXFP4 && p.K > 4096) return 1;
   p.nblk = gated ? (p.N / 2 + RB / 2 - 1) / (RB / 2) : (p.N + RB - 1) / RB;
-  const int stage = RB * (gs_stage_row0<FMT>(p.K, p.KC) + gs_row_bytes1<FMT>(p.K));
+  const int stage = RB * gs_stage_row_all<FMT>(p.K, p.KC);
   const int fixed = ((p.n_xrows * gs_xrow_bytes<FMT>(p.K) + 15) & ~15) + 2 * GS_MAX_STAGES * 8 + GS_MAX_XROWS * 4 + 16;
   p.nst = GS_MAX_STAGES;
   while (p.nst > 2 && fixed + p.nst * stage > 113 * 1024) --p.nst;        // two CTAs per SM when three stages still fit
@@ -789,9 +901,9 @@ int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const 
 static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* y, const float* bias, int M, int N, int K, int out_f32, int act,
                              float act_alpha, float act_limit, const int* slot_expert, const float* slot_scale, int slots, int x_div, int e_lo,
                              int e_hi, const PeerOut* peer, const GsNorm* norm, const GsRoute* route, cudaStream_t st) {
-  if (wfmt != WF_BF16 && wfmt != WF_Q8 && wfmt != WF_MXFP4 && wfmt != WF_Q4K) return 1;
+  if (wfmt != WF_BF16 && wfmt != WF_Q8 && wfmt != WF_MXFP4 && wfmt != WF_Q4K && wfmt != WF_Q6K) return 1;
   if (K % 32 && !(wfmt == WF_BF16 && K % 8 == 0)) return 1;
-  if (wfmt == WF_Q4K && K % 256) return 1;
+  if ((wfmt == WF_Q4K || wfmt == WF_Q6K) && K % 256) return 1;
   if (act != 0 && wfmt != WF_MXFP4 && wfmt != WF_Q4K) return 1;      // gated epilogue: one feature per warp needs RPW == 2
   if (act != 0 && (N % 32)) return 1;
   GsParams p;
@@ -806,14 +918,16 @@ static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* 
   const int rb0 = wfmt == WF_BF16 ? K * 2 : (wfmt == WF_Q8 ? K : (wfmt == WF_Q4K ? K / 256 * 144 : K / 2));
   if (rb0 % 16) return 1;
   if (((uintptr_t)w.p0 & 15) || (w.p1 && ((uintptr_t)w.p1 & 15)) || ((uintptr_t)x & 15)) return 1;
+  if (wfmt == WF_Q6K && (!w.p2 || !w.p3 || ((uintptr_t)w.p2 & 15) || ((uintptr_t)w.p3 & 15))) return 1;
   if (peer) p.peer = *peer; else p.peer.world = 0;
   if (norm) p.norm = *norm; else p.norm.x = nullptr;
   if (route) p.route = *route; else p.route.ticket = nullptr;
-  if ((norm || route) && (wfmt == WF_MXFP4 || wfmt == WF_Q4K || p.slot_mode)) return 1;
+  if ((norm || route) && (wfmt == WF_MXFP4 || wfmt == WF_Q4K || wfmt == WF_Q6K || p.slot_mode)) return 1;
   switch (wfmt) {
     case WF_BF16: return gs_dispatch<WF_BF16>(p, st);
-    case WF_Q8: return gs_dispatch<WF_Q8>(p, st);
+    case WF_Q8: return (norm || route) ? gs_dispatch<WF_Q8>(p, st) : gs_dispatch<WF_Q8I>(p, st);
     case WF_Q4K: return gs_dispatch<WF_Q4K>(p, st);
+    case WF_Q6K: return gs_dispatch<WF_Q6K>(p, st);
     default: return gs_dispatch<WF_MXFP4>(p, st);
   }
 }

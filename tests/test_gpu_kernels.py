@@ -228,7 +228,8 @@ def test_streaming_gemv_matches_register_gemv_and_oracle(fmt):
         assert rel_err(a, want) < 4e-3, (M, N, Kd)
         assert rel_err(b, want) < 4e-3, (M, N, Kd)
     # activations with a large dynamic range (fp16 staging of the MXFP4 path must not overflow or flush them)
-    if fmt == WFormat.MXFP4:
+    # (and the block-scaled 16-bit staging of the Q8 path must keep small elements beside large ones)
+    if fmt in (WFormat.MXFP4, WFormat.Q8):
         w = make_weight(fmt, 256, 2880, seed=5)
         x = torch.randn(1, 2880, device=dev())
         x[0, ::97] *= 3000.0
@@ -240,13 +241,14 @@ def test_streaming_gemv_matches_register_gemv_and_oracle(fmt):
         assert rel_err(got, ref.linear(x, w, out_f32=True)) < 4e-3
 
 
-def test_streaming_gemv_q4k():
-    """Q4_K through the bulk-copy streaming kernel (4-bit codes against block-scaled 16-bit activations in dp4a): plain rows with
-    one and several activation rows, a K that is split into chunks, the gated epilogue, activations with outliers."""
+@pytest.mark.parametrize("fmt", [WFormat.Q4K, WFormat.Q6K])
+def test_streaming_gemv_kquants(fmt):
+    """Q4_K / Q6_K through the bulk-copy streaming kernel (the codes against block-scaled 16-bit activations in dp4a): plain rows
+    with one and several activation rows, a K that is split into chunks, the gated epilogue (Q4_K), activations with outliers."""
     k = K()
     try:
         for (M, N, Kd) in [(1, 200, 4096), (1, 520, 1024), (3, 515, 1024), (8, 96, 2048), (1, 64, 14336), (2, 40, 14336), (1, 128, 5120)]:
-            w = make_weight(WFormat.Q4K, N, Kd, seed=N)
+            w = make_weight(fmt, N, Kd, seed=N)
             x = (torch.randn(M, Kd, device=dev()) * 3).to(torch.bfloat16)
             bias = torch.randn(N, device=dev())
             want = ref.linear(x, w, bias=bias, out_f32=True)
@@ -257,7 +259,7 @@ def test_streaming_gemv_q4k():
             k.check_status()
             assert rel_err(a, want) < 1e-3, (M, N, Kd)
             assert rel_err(b, want) < 4e-3, (M, N, Kd)
-        for (M, F, Kd) in [(1, 96, 1024), (2, 400, 4096), (1, 64, 6144)]:
+        for (M, F, Kd) in [(1, 96, 1024), (2, 400, 4096), (1, 64, 6144)] if fmt == WFormat.Q4K else []:
             w = make_weight(WFormat.Q4K, 2 * F, Kd, seed=F)
             x = torch.randn(M, Kd, device=dev()).to(torch.bfloat16)
             bias = torch.randn(2 * F, device=dev()) * 0.1
@@ -265,7 +267,7 @@ def test_streaming_gemv_q4k():
             for act in (ref.ACT_SWIGLU, ref.ACT_GEGLU):
                 got = k.linear(x, w, bias=bias, act=act, out_f32=True)
                 assert rel_err(got, ref.linear(x, w, bias=bias, act=act, out_f32=True)) < 3e-3, (M, F, Kd, act)
-        w = make_weight(WFormat.Q4K, 256, 4096, seed=5)
+        w = make_weight(fmt, 256, 4096, seed=5)
         x = torch.randn(1, 4096, device=dev())
         x[0, ::97] *= 3000.0
         x[0, 1::2] *= 1e-3
