@@ -437,8 +437,10 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
   const int F = p.N / 2;
 
   if (warp == WARPS) {
-    // ------------------------------------------------------------ producer: one lane issues the bulk copies
-    if (lane == 0) {
+    // ------------------------------------------------------------ producer warp: lane 0 waits for a free stage and announces the
+    // bytes; whole-row-block copies are issued by lane 0, the per-row copies of a k chunk by one lane per row (a single lane
+    // issues about one bulk copy per 120 cycles, which bounds a chunked matrix well below the memory rate)
+    {
       int it = 0;
       bool ok = true;
       if (p.slot_expert) pdl_wait();          // the expert ids come from the router kernel
@@ -459,42 +461,54 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
         for (int kc = 0; kc < p.nkc && ok; ++kc, ++it) {
           const int s = it % NST;
           const uint32_t full = bar0 + 8 * s, empty = bar0 + 8 * (GS_MAX_STAGES + s);
-          if (it >= NST) ok = mbar_wait(empty, ((it / NST) & 1) ^ 1, p.status, ERR_MBAR_TIMEOUT_PRODUCER, abort_flag);
+          if (it >= NST) {
+            if (lane == 0) ok = mbar_wait(empty, ((it / NST) & 1) ^ 1, p.status, ERR_MBAR_TIMEOUT_PRODUCER, abort_flag);
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          }
           if (!ok) break;
           const uint32_t dst = smem_u32(stages + (size_t)s * stage_bytes);
           if (GATED) {
             const int f0 = blk * FB, nf = min(FB, F - f0);
             const int grow = 32 * (f0 >> 4) + (f0 & 15);
-            mbar_expect_tx(full, 2u * nf * (r0b + r1b));
+            if (lane == 0) mbar_expect_tx(full, 2u * nf * (r0b + r1b));
+            __syncwarp();
             if (p.nkc == 1) {
-              bulk_g2s(dst, b0 + (size_t)grow * g0, nf * r0b, full);
-              bulk_g2s(dst + FB * r0b, b0 + (size_t)(grow + 16) * g0, nf * r0b, full);
-            } else {
-              // k chunk of every gate row and of every up row (chunked formats have no second plane)
-              for (int r = 0; r < nf; ++r) {
-                bulk_g2s(dst + r * r0b, b0 + (size_t)(grow + r) * g0 + (size_t)kc * r0b, r0b, full);
-                bulk_g2s(dst + (FB + r) * r0b, b0 + (size_t)(grow + 16 + r) * g0 + (size_t)kc * r0b, r0b, full);
+              if (lane == 0) {
+                bulk_g2s(dst, b0 + (size_t)grow * g0, nf * r0b, full);
+                bulk_g2s(dst + FB * r0b, b0 + (size_t)(grow + 16) * g0, nf * r0b, full);
               }
+            } else {
+              // k chunk of every gate row (lanes 0..nf-1) and of every up row (lanes 16..16+nf-1); chunked formats have no second plane
+              const int r = lane & 15, up = lane >> 4;
+              if (r < nf) bulk_g2s(dst + (up * FB + r) * r0b, b0 + (size_t)(grow + 16 * up + r) * g0 + (size_t)kc * r0b, r0b, full);
             }
-            if (r1b) {
+            if (r1b && lane == 0) {
               bulk_g2s(dst + plane1_off, b1 + (size_t)grow * g1, nf * r1b, full);
               bulk_g2s(dst + plane1_off + FB * r1b, b1 + (size_t)(grow + 16) * g1, nf * r1b, full);
             }
           } else {
             const int row0 = blk * RB, nr = min(RB, p.N - row0);
-            mbar_expect_tx(full, (uint32_t)nr * (r0b + r1b + r2b + r3b));
+            if (lane == 0) mbar_expect_tx(full, (uint32_t)nr * (r0b + r1b + r2b + r3b));
+            __syncwarp();
             if (p.nkc == 1) {
-              bulk_g2s(dst, b0 + (size_t)row0 * g0, nr * r0b, full);
-              if (r1b) bulk_g2s(dst + plane1_off, b1 + (size_t)row0 * g1, nr * r1b, full);
-              if (r2b) bulk_g2s(dst + plane2_off, b2 + (size_t)row0 * g2, nr * r2b, full);
+              if (lane == 0) {
+                bulk_g2s(dst, b0 + (size_t)row0 * g0, nr * r0b, full);
+                if (r1b) bulk_g2s(dst + plane1_off, b1 + (size_t)row0 * g1, nr * r1b, full);
+                if (r2b) bulk_g2s(dst + plane2_off, b2 + (size_t)row0 * g2, nr * r2b, full);
+              }
             } else {
-              for (int r = 0; r < nr; ++r) {
-                bulk_g2s(dst + r * r0b, b0 + (size_t)(row0 + r) * g0 + (size_t)kc * r0b, r0b, full);
-                if (r1b) bulk_g2s(dst + plane1_off + r * r1b, b1 + (size_t)(row0 + r) * g1 + (size_t)kc * r1b, r1b, full);
-                if (r2b) bulk_g2s(dst + plane2_off + r * r2b, b2 + (size_t)(row0 + r) * g2 + (size_t)kc * r2b, r2b, full);
+              // lanes 0..15: plane 0 (and 2) of row `lane`; lanes 16..31: plane 1 of row `lane - 16`
+              const int r = lane & 15, hi = lane >> 4;
+              for (int rr = r; rr < nr; rr += 16) {
+                if (hi == 0) {
+                  bulk_g2s(dst + rr * r0b, b0 + (size_t)(row0 + rr) * g0 + (size_t)kc * r0b, r0b, full);
+                  if (r2b) bulk_g2s(dst + plane2_off + rr * r2b, b2 + (size_t)(row0 + rr) * g2 + (size_t)kc * r2b, r2b, full);
+                } else if (r1b) {
+                  bulk_g2s(dst + plane1_off + rr * r1b, b1 + (size_t)(row0 + rr) * g1 + (size_t)kc * r1b, r1b, full);
+                }
               }
             }
-            if (r3b) bulk_g2s(dst + plane3_off, b3 + (size_t)row0 * g3, nr * r3b, full);     // whole runs of block scales, every chunk
+            if (r3b && lane == 0) bulk_g2s(dst + plane3_off, b3 + (size_t)row0 * g3, nr * r3b, full);     // whole runs of block scales, every chunk
           }
         }
       }
@@ -681,6 +695,11 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
     uint32_t xc[CACHED ? NG : 1][Gran<FMT>::XR];
     int x_tag = -1;                                         // (activation row, k chunk) held in xc
     const int ng = p.KC / Gran<FMT>::GE;
+    // A k chunk of at most 16 granules would leave half of the lanes idle: the two half-warps take the warp's two rows side by side
+    // (each lane accumulates for its own row; the warp-wide sums of the epilogue then see zeros from the other half).
+    constexpr bool HALF_OK = (FMT == WF_Q4K || FMT == WF_Q6K) && (GATED || RPW == 2);
+    const bool half = HALF_OK && ng <= 16;
+    const int xl = half ? (lane & 15) : lane;
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
       const int slot = u / p.nblk, blk = u - slot * p.nblk;
       bool owned = true;
@@ -703,12 +722,29 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
             x_tag = xrow * p.nkc + kc;
 #pragma unroll
             for (int j = 0; j < NG; ++j)
-              if (lane + 32 * j < ng) load_xg<FMT>(xbase, kc * ng + lane + 32 * j, K, xc[j]);
+              if (xl + 32 * j < ng) load_xg<FMT>(xbase, kc * ng + xl + 32 * j, K, xc[j]);
           }
           const int s = it % NST;
           ok = mbar_wait(bar0 + 8 * s, (it / NST) & 1, p.status, ERR_MBAR_TIMEOUT_EPILOGUE, abort_flag);
           if (!ok) break;
           const uint8_t* st = stages + (size_t)s * stage_bytes;
+          if (half) {
+            if constexpr (HALF_OK) {
+              const int hr = lane >> 4;
+              const int srow = GATED ? (hr == 0 ? 0 : FB) + warp : warp * RPW + hr;
+              const GsPlanes23 w23{st + plane2_off + (size_t)srow * r2b, st + plane3_off + (size_t)srow * r3b, kc * (p.KC >> 8)};
+              float a[MM];
+#pragma unroll
+              for (int m = 0; m < MM; ++m) a[m] = 0.f;
+              gs_row<FMT, MM, CACHED, NG>(st + (size_t)srow * r0b, st + plane1_off + (size_t)srow * r1b, w23, ng, xl, xc, xbase, K, kc * ng,
+                                      xscale + xrow, a);
+#pragma unroll
+              for (int m = 0; m < MM; ++m) {
+                acc[0][m] += hr == 0 ? a[m] : 0.f;
+                acc[1][m] += hr == 1 ? a[m] : 0.f;
+              }
+            }
+          } else
 #pragma unroll
           for (int r = 0; r < (GATED ? 2 : RPW); ++r) {
             // gated: the warp owns one feature of the block; its gate row sits at `warp`, its up row FB rows further
@@ -860,7 +896,8 @@ static int gs_dispatch(GsParams& p, cudaStream_t st) {
     p.nkc = n; p.KC = p.K / n;
   }
   if ((FMT == WF_Q4K || FMT == WF_Q6K || FMT == WF_Q8I) && p.K > 32 * Gran<FMT>::NGMAX * Gran<FMT>::GE) {
-    // whole 256-element blocks per chunk, as few chunks as possible
+    // whole 256-element blocks per chunk, as few chunks as possible: the per-row copies of a chunked matrix are bound by the
+    // rate of bulk-copy requests, not by bytes (chunks of at most 1024 elements are taken by half-warps, see the consumer loop)
     int n = 2;
     while (n < 64 && (p.K % n || (p.K / n) % 256 || p.K / n > 32 * Gran<FMT>::NGMAX * Gran<FMT>::GE)) ++n;
     if (n >= 64) return 1;

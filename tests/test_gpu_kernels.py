@@ -247,7 +247,7 @@ def test_streaming_gemv_kquants(fmt):
     with one and several activation rows, a K that is split into chunks, the gated epilogue (Q4_K), activations with outliers."""
     k = K()
     try:
-        for (M, N, Kd) in [(1, 200, 4096), (1, 520, 1024), (3, 515, 1024), (8, 96, 2048), (1, 64, 14336), (2, 40, 14336), (1, 128, 5120)]:
+        for (M, N, Kd) in [(1, 200, 4096), (1, 520, 1024), (3, 515, 1024), (8, 96, 2048), (1, 64, 14336), (2, 40, 14336), (1, 128, 5120), (1, 72, 17408), (1, 40, 1280)]:
             w = make_weight(fmt, N, Kd, seed=N)
             x = (torch.randn(M, Kd, device=dev()) * 3).to(torch.bfloat16)
             bias = torch.randn(N, device=dev())
