@@ -23,6 +23,7 @@ TypeTraits type_traits(int32_t t) {
     case T_Q4_0: return {32, 18, "Q4_0"};
     case T_Q8_0: return {32, 34, "Q8_0"};
     case T_MXFP4:return {32, 17, "MXFP4"};
+    case T_EXL3: return {1, 2, "EXL3"};        // trellis words (int16), dims {16 * bits, N / 16, K / 16}; decoded by exl3.cpp
     case T_Q4_K: return {256, 144, "Q4_K"};
     case T_Q5_K: return {256, 176, "Q5_K"};
     case T_Q6_K: return {256, 210, "Q6_K"};

@@ -31,6 +31,7 @@ class GGMLType(IntEnum):
     I64 = 27
     F64 = 28
     BF16 = 30
+    EXL3 = 37        # this engine family's id for a verbatim EXL3 trellis (int16 words; dims {16*bits, N/16, K/16})
     MXFP4 = 39
 
 

@@ -41,7 +41,7 @@ class HFMeta:
     rms_eps: float = 1e-6
     tie_word_embeddings: bool = False
     attention_bias: bool = False
-    quant_method: str = ""           # "" | awq | gptq
+    quant_method: str = ""           # "" | awq | gptq | exl3
     bits: int = 4
     group_size: int = 128
     version: str = "gemm"
@@ -75,8 +75,13 @@ def parse_hf_config(text: str) -> HFMeta:
         m.group_size = int(q.get("group_size", q.get("q_group_size", 128)))
         m.version = str(q.get("version", "gemm")).lower()
         m.desc_act = bool(q.get("desc_act", False))
+        if m.quant_method == "exl3":
+            # trellis layers carry their own width (bits = trellis.shape[-1] / 16, it may differ per layer); nothing else to parse
+            if m.arch not in ("llama",):
+                raise ImportError_(f"EXL3 import takes dense llama checkpoints, not '{m.arch}'")
+            return m
         if m.quant_method not in ("awq", "gptq"):
-            raise ImportError_(f"unsupported quant_method '{m.quant_method}' (awq | gptq)")
+            raise ImportError_(f"unsupported quant_method '{m.quant_method}' (awq | gptq | exl3)")
         if m.bits != 4:
             raise ImportError_(f"4-bit only (got {m.bits})")
         if m.quant_method == "awq" and m.version != "gemm":
@@ -182,6 +187,50 @@ def _pick_type(name: str, k: int) -> int:
     return int(want)
 
 
+def _add_exl3_tensors(w: GGUFWriter, st: SafetensorsModel, names: list, m: HFMeta) -> int:
+    """An EXL3 (exllamav3) checkpoint: every quantised linear is ``<module>.trellis`` int16 [K/16, N/16, 16*bits] with ``.suh`` [K] and
+    ``.svh`` [N]; they go into the GGUF unchanged (type 37, dims {16*bits, N/16, K/16}, and F16 siblings ``<name>.suh`` / ``.svh``), the
+    embedding stays F16, vectors become F32.  Q / K rows keep the Hugging Face order (the graph skips its llama re-ordering for these
+    layers).  Only the default codebook is handled: a layer with ``mcg`` / ``mul1`` tensors, or with the legacy packed ``su`` / ``sv``
+    sign fields, is refused.  Reference parity: src/loaders/hf_import.cpp:440-592."""
+    n_t = 0
+    for n in sorted(names, key=lambda s: (hf_to_gguf_name(s.replace(".trellis", ".weight")) or "~" + s)):
+        if n.endswith((".suh", ".svh")):
+            continue
+        if n.endswith((".mcg", ".mul1", ".su", ".sv")):
+            raise ImportError_(f"{n}: only EXL3 layers with the default codebook and fp16 suh / svh vectors are supported")
+        if n.endswith(".trellis"):
+            base = n[:-len(".trellis")]
+            g = hf_to_gguf_name(base + ".weight")
+            if not g:
+                continue
+            shp = st.shape(n)
+            if len(shp) != 3 or shp[2] % 16 or not 1 <= shp[2] // 16 <= 8:
+                raise ImportError_(f"{n}: trellis shape {tuple(shp)} is not [K/16, N/16, 16*bits]")
+            if not (st.has(base + ".suh") and st.has(base + ".svh")):
+                raise ImportError_(f"{base}: EXL3 layer is missing suh / svh")
+            tk, tn, wb = (int(v) for v in shp)
+            if (tk * 16) % 128 or (tn * 16) % 128 or st.shape(base + ".suh")[0] != tk * 16 or st.shape(base + ".svh")[0] != tn * 16:
+                raise ImportError_(f"{base}: EXL3 layer shapes do not fit ({tk * 16} x {tn * 16})")
+            root = g[:-len(".weight")]
+            w.add_tensor(g, [wb, tn, tk], int(GGMLType.EXL3), (lambda nn=n: np.ascontiguousarray(st.numpy(nn)).view(np.uint8).reshape(-1)))
+            for tag in (".suh", ".svh"):
+                w.add_tensor(root + tag, [int(st.shape(base + tag)[0])], int(GGMLType.F16),
+                             (lambda nn=base + tag: st.float32(nn).astype(np.float16).view(np.uint8).reshape(-1)))
+            n_t += 3
+            continue
+        g = hf_to_gguf_name(n)
+        if not g or (m.tie_word_embeddings and g == "output.weight"):
+            continue
+        shp = st.shape(n)
+        if len(shp) == 2:
+            w.add_tensor(g, [int(shp[1]), int(shp[0])], int(GGMLType.F16), (lambda nn=n: st.float32(nn).astype(np.float16).view(np.uint8).reshape(-1)))
+        else:
+            w.add_tensor(g, [int(np.prod(shp))], int(GGMLType.F32), (lambda nn=n: st.float32(nn).astype(np.float32).reshape(-1)))
+        n_t += 1
+    return n_t
+
+
 def import_to_gguf(hf_dir: str, out_path: str, tokenizer_gguf: Optional[str] = None, stream: bool = True, log=None) -> dict:
     log = log or (lambda s: print(s, file=sys.stderr))
     cfg_path = os.path.join(hf_dir, "config.json")
@@ -209,6 +258,12 @@ def import_to_gguf(hf_dir: str, out_path: str, tokenizer_gguf: Optional[str] = N
         raise ImportError_("no tokenizer: pass --tokenizer-gguf <file.gguf> or put tokenizer.json next to the weights")
     for k, v in kv.items():
         w.add_kv(k, v)
+
+    if m.quant_method == "exl3":
+        n_t = _add_exl3_tensors(w, st, names, m)
+        w.write(out_path)
+        log(f"[import] {n_t} tensors -> {out_path} ({os.path.getsize(out_path) / 1e6:.1f} MB), quant source: exl3 (trellis layers kept verbatim)")
+        return {"tensors": n_t, "arch": arch, "bytes": os.path.getsize(out_path)}
 
     # group the quantised triplets by module
     plan, done = [], set()

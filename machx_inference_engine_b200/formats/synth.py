@@ -193,6 +193,8 @@ def _matrix_type(name: str, kind: str, K: int, quant: str, n_layers: int) -> int
         return GGMLType.F32
     _N_LAYERS_HINT["n"] = n_layers
     fmt = default_policy("", quant)(name)
+    if fmt == WFormat.EXL3:
+        return GGMLType.EXL3 if kind == "matrix" else GGMLType.BF16        # expert stacks stay dense
     t = {WFormat.BF16: GGMLType.BF16, WFormat.Q8: GGMLType.Q8_0, WFormat.Q4K: GGMLType.Q4_K, WFormat.Q6K: GGMLType.Q6_K, WFormat.MXFP4: GGMLType.MXFP4}[fmt]
     if K % block_elems(t):
         t = GGMLType.Q8_0 if K % 32 == 0 else GGMLType.F16
@@ -235,6 +237,29 @@ def _payload(name: str, kind: str, dims: tuple, ttype: int, seed: int) -> Callab
     return make
 
 
+def _add_exl3(w, name: str, dims: tuple, quant: str, seed: int) -> int:
+    """A random EXL3 layer the way an imported checkpoint stores it: the trellis verbatim as type 37 with dims {16*bits, N/16, K/16} and the
+    sign / scale vectors as F16 siblings (src/loaders/hf_import.cpp:553-560).  Any bit stream is a valid trellis."""
+    from .exl3 import CODEBOOK_STD
+    K, N = dims
+    bits = int(quant[5:]) if quant.startswith("exl3-") else 4
+    root = name[:-len(".weight")]
+
+    def trellis():
+        return _rng(name, seed).integers(0, 256, size=(K // 16) * (N // 16) * 16 * bits * 2, dtype=np.uint8)
+
+    def vec(tag, n, scale):
+        def make():
+            g = _rng(root + tag, seed)
+            return ((g.integers(0, 2, size=n) * 2 - 1) * scale * (1.0 + 0.1 * g.random(n))).astype(np.float16).view(np.uint8).reshape(-1)
+        return make
+
+    w.add_tensor(name, (16 * bits, N // 16, K // 16), int(GGMLType.EXL3), trellis)
+    w.add_tensor(root + ".suh", (K,), int(GGMLType.F16), vec(".suh", K, 1.0))
+    w.add_tensor(root + ".svh", (N,), int(GGMLType.F16), vec(".svh", N, 0.02 / CODEBOOK_STD))
+    return 3
+
+
 def write_synthetic_gguf(cfg: ModelConfig, path: str, quant: str = "q8_0", seed: int = 0, tokenizer: bool = True,
                          extra_kv: Iterable = ()) -> dict:
     """Writes the checkpoint; returns {"tensors": n, "bytes": payload bytes}."""
@@ -253,6 +278,12 @@ def write_synthetic_gguf(cfg: ModelConfig, path: str, quant: str = "q8_0", seed:
     n = 0
     for name, kind, dims in tensor_plan(cfg):
         t = _matrix_type(name, kind, dims[0], quant, cfg.n_layers) if kind in ("matrix", "expert", "router", "router_sharp") else GGMLType.F32
+        if t == GGMLType.EXL3:
+            if dims[0] % 128 or dims[1] % 128:
+                t = GGMLType.BF16          # the 128-point rotations need multiples of 128 on both sides
+            else:
+                n += _add_exl3(w, name, dims, quant, seed)
+                continue
         w.add_tensor(name, dims, int(t), _payload(name, kind, dims, int(t), seed))
         n += 1
     w.write(path)

@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from ..formats.gguf import GGMLType, GGUFReader
-from ..ops.weights import QuantWeight, WFormat, from_dense, from_ggml
+from ..ops.weights import QuantWeight, WFormat, from_dense, from_exl3, from_ggml
 
 
 class GGUFSource:
@@ -27,6 +27,13 @@ class GGUFSource:
 
     def matrix(self, name: str, N: int, K: int, E: int = 1, experts: Optional[tuple[int, int]] = None) -> QuantWeight:
         t = self.r.tensor(name)
+        if int(t.type) == GGMLType.EXL3:
+            # a verbatim trellis {16*bits, N/16, K/16} with its sign / scale vectors beside it (<root>.suh, <root>.svh)
+            if E != 1 or len(t.dims) != 3 or (int(t.dims[2]) * 16, int(t.dims[1]) * 16) != (K, N):
+                raise ValueError(f"{name}: EXL3 trellis dims {tuple(t.dims)} do not describe a [{N}, {K}] matrix")
+            root = name[:-len(".weight")] if name.endswith(".weight") else name
+            tr = torch.from_numpy(np.frombuffer(np.array(t.raw(), copy=True), dtype=np.int16).reshape(K // 16, N // 16, int(t.dims[0])))
+            return from_exl3(tr.to(self.device), self.vector(root + ".suh", K), self.vector(root + ".svh", N))
         want = (K, N) if E == 1 else (K, N, E)
         if tuple(t.dims) != want:
             raise ValueError(f"{name}: expected ggml dims {want}, file has {tuple(t.dims)}")
@@ -57,15 +64,24 @@ def default_policy(arch: str, quant: str) -> Callable[[str], WFormat]:
 
     ``q4_k_m``: Q4_K projections, Q6_K output / half of attn_v and ffn_down (llama.cpp's recipe);
     ``q8_0``: everything Q8; ``mxfp4``: MXFP4 experts, bf16 attention, Q8 embeddings/head (gpt-oss);
-    ``bf16``: everything bf16.
+    ``bf16``: everything bf16; ``exl3`` / ``exl3-<bits>``: every projection and the head as EXL3 trellis layers (4 bits per
+    weight unless said), embeddings bf16 -- the layout of an imported EXL3 checkpoint (src/loaders/hf_import.cpp:536-592).
     """
     quant = quant.lower()
+    exl3_bits = 0
+    if quant == "exl3" or quant.startswith("exl3-"):
+        exl3_bits = int(quant[5:]) if quant.startswith("exl3-") else 4
+        if not 1 <= exl3_bits <= 8:
+            raise ValueError("EXL3 takes 1 to 8 bits per weight")
+        quant = "exl3"
 
     def pol(name: str) -> WFormat:
         if quant == "bf16":
             return WFormat.BF16
         if quant == "q8_0":
             return WFormat.Q8
+        if quant == "exl3":
+            return WFormat.BF16 if name == "token_embd.weight" else WFormat.EXL3
         if quant == "mxfp4":
             if "_exps" in name:
                 return WFormat.MXFP4
@@ -80,6 +96,7 @@ def default_policy(arch: str, quant: str) -> Callable[[str], WFormat]:
             return WFormat.Q4K
         raise ValueError(f"unknown quantisation recipe {quant}")
 
+    pol.exl3_bits = exl3_bits
     return pol
 
 
@@ -122,6 +139,12 @@ class SynthSource:
 
     def matrix(self, name: str, N: int, K: int, E: int = 1, experts: Optional[tuple[int, int]] = None) -> QuantWeight:
         fmt = self.policy(name)
+        if fmt == WFormat.EXL3:
+            if E == 1 and N % 128 == 0 and K % 128 == 0:
+                from ..formats import exl3
+                tr, suh, svh = exl3.random_layer(N, K, getattr(self.policy, "exl3_bits", 4) or 4, self._gen(name), self.std)
+                return from_exl3(tr, suh, svh).to(self.device)
+            fmt = WFormat.BF16            # expert stacks and shapes off the 128-point rotation stay dense
         gran = {WFormat.BF16: 8, WFormat.Q8: 32, WFormat.Q4K: 256, WFormat.Q6K: 256, WFormat.MXFP4: 32}[fmt]
         if K % gran:                      # llama.cpp's fallback for ragged rows
             fmt = WFormat.Q8 if K % 32 == 0 else WFormat.BF16

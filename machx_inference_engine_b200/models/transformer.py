@@ -25,6 +25,7 @@ import torch
 from .. import ops
 from ..formats.model_config import ModelConfig
 from ..ops import ACT_GEGLU, ACT_NONE, ACT_SWIGLU, ACT_SWIGLU_OAI, QuantWeight
+from ..ops.weights import WFormat
 from ..parallel.comm import ParallelCtx
 from ..utils.rope import rope_tables
 
@@ -141,7 +142,7 @@ class MultiLinear:
 
 
 def _fuse_rows(ws: list[QuantWeight], biases: list[Optional[torch.Tensor]]):
-    if all(w.fmt == ws[0].fmt for w in ws):
+    if all(w.fmt == ws[0].fmt for w in ws) and ws[0].fmt != WFormat.EXL3:
         b = None
         if any(bb is not None for bb in biases):
             b = torch.cat([bb if bb is not None else torch.zeros(w.N, device=w.device) for w, bb in zip(ws, biases)])
@@ -202,13 +203,14 @@ class AttentionBlock:
                 wv = wk                  # V is the raw K projection (src/model/gemma4.cpp:178-183,660)
             else:
                 wv = src.matrix(f"{p}.attn_v.weight", c.n_kv_heads * hd, H)
-        if c.arch == "llama" and getattr(src, "r", None) is not None:
+        if c.arch == "llama" and getattr(src, "r", None) is not None and wq.fmt != WFormat.EXL3:
+            # (imported EXL3 layers keep the Hugging Face row order, which is the half-split one: src/model/dense_transformer.cpp:165-212)
             wq, wk = unpermute_llama_qk(wq, c.n_heads, hd), unpermute_llama_qk(wk, c.n_kv_heads, hd)
         has_bias = c.arch in ("qwen2", "gpt-oss") and src.has(f"{p}.attn_q.bias")
         bq = src.vector(f"{p}.attn_q.bias", c.n_heads * q_rows_per_head) if has_bias else None
         bk = src.vector(f"{p}.attn_k.bias", c.n_kv_heads * hd) if has_bias else None
         bv = src.vector(f"{p}.attn_v.bias", c.n_kv_heads * hd) if has_bias else None
-        sl = lambda w, lo, n: w.slice_rows(lo, lo + n)
+        sl = lambda w, lo, n: w if (lo == 0 and n == w.N) else w.slice_rows(lo, lo + n)
         sb = lambda b, lo, n: None if b is None else b[lo:lo + n].contiguous()
         ws = [sl(wq, q_lo * q_rows_per_head, self.n_q * q_rows_per_head), sl(wk, kv_lo * hd, self.n_kv * hd), sl(wv, kv_lo * hd, self.n_kv * hd)]
         bs = [sb(bq, q_lo * q_rows_per_head, self.n_q * q_rows_per_head), sb(bk, kv_lo * hd, self.n_kv * hd), sb(bv, kv_lo * hd, self.n_kv * hd)]
@@ -286,7 +288,7 @@ class DenseFFN:
                 gran = 32 if F % 32 == 0 else 16          # finer than the weight's blocks: the shard is re-encoded
             lo, hi = _even_chunks(F, tp, gran)[par.rank]
             g, u, d = g.slice_rows(lo, hi), u.slice_rows(lo, hi), d.slice_k(lo, hi, requant=True)
-        if g.fmt == u.fmt:
+        if g.fmt == u.fmt and g.fmt != WFormat.EXL3:
             self.gate_up = Linear(QuantWeight.interleave_gate_up(g, u), act=act)
             self.split = None
         else:

@@ -10,12 +10,13 @@ import functools
 
 from . import ref
 from .ref import ACT_GEGLU, ACT_NONE, ACT_SWIGLU, ACT_SWIGLU_OAI, MOE_TILE, MoePacking, moe_max_rows
-from .weights import QuantWeight, WFormat, from_dense, from_ggml
+from .weights import QuantWeight, WFormat, from_dense, from_exl3, from_ggml
 from ..utils.profiler import profiler as _prof
 
 _NAMES = [
     "embed", "rmsnorm", "glu", "sigmoid_mul", "scaled_add", "gated_rmsnorm", "qkv_post", "linear", "grouped_linear", "expert_gemv", "expert_group_gemv",
     "attention", "gated_rmsnorm_heads", "conv1d_silu", "deltanet_scan", "moe_route", "moe_pack", "moe_gather", "moe_combine", "argmax", "rep_penalty", "sample",
+    "hadamard128",
 ]
 
 
@@ -69,5 +70,5 @@ def _make(name):
 for _n in _NAMES:
     globals()[_n] = _make(_n)
 
-__all__ = _NAMES + ["set_backend", "QuantWeight", "WFormat", "from_dense", "from_ggml", "MoePacking", "moe_max_rows", "ACT_NONE", "ACT_SWIGLU",
+__all__ = _NAMES + ["set_backend", "QuantWeight", "WFormat", "from_dense", "from_exl3", "from_ggml", "MoePacking", "moe_max_rows", "ACT_NONE", "ACT_SWIGLU",
                     "ACT_SWIGLU_OAI", "ACT_GEGLU", "MOE_TILE"]

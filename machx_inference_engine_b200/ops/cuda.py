@@ -287,6 +287,9 @@ def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limi
     whose weights differ in format can share one output without a concatenation."""
     assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[-1] == w.K and w.E == 1
     M = x.shape[0]
+    if w.fmt == WFormat.EXL3:
+        assert act == ACT_NONE and row_scale is None, "EXL3 layers have no fused activation or row scale"
+        return _exl3_linear(x, w, bias, out_f32, out)
     n_out = w.N // 2 if act != ACT_NONE else w.N
     odt = torch.float32 if out_f32 else torch.bfloat16
     if out is None:
@@ -316,6 +319,65 @@ def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limi
                            C.c_float(act_alpha), C.c_float(act_limit), M, w.N, w.K, _vp(0), _vp(0), _pick_bn(M, w.N), _stream()), "gemm")
     _count()
     return out
+
+
+EXL3_GEMV_MAX_M = 8
+
+
+def hadamard128(x, pre=None, post=None, bias=None, out_f32=False, out=None):
+    """Normalised 128-point Sylvester Hadamard transform of every aligned run of 128 elements of the rows of ``x`` (bf16 or fp32, unit
+    column stride): ``had128(x * pre) * post + bias`` with optional fp32 vectors.  ``out``: a [rows, n] view with unit column stride.
+    A 3-D fp32 ``x`` [parts, rows, n] (contiguous) stands for the sum of its parts (the partial sums of a K-split product)."""
+    nsum, sum_stride = 1, 0
+    if x.dim() == 3:
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        nsum, sum_stride = x.shape[0], x.shape[1] * x.shape[2]
+        x = x[0]
+    assert x.dim() == 2 and x.stride(1) == 1 and x.dtype in (torch.bfloat16, torch.float32) and x.shape[1] % 128 == 0
+    rows, n = x.shape
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    if out is None:
+        out = torch.empty(rows, n, dtype=odt, device=x.device)
+    assert out.shape == (rows, n) and out.dtype == odt and (rows == 0 or out.stride(1) == 1)
+    for v in (pre, post, bias):
+        assert v is None or (v.dtype == torch.float32 and v.numel() == n and v.is_contiguous())
+    if rows:
+        _check(_lib.cuda().mx_hadamard128_cuda(_p(x), int(x.dtype == torch.float32), _p(pre), _p(post), _p(bias), _p(out), int(out_f32),
+                                               C.c_longlong(rows), n, x.stride(0), out.stride(0), nsum, C.c_longlong(sum_stride), _stream()), "hadamard128")
+        _count()
+    return out
+
+
+def exl3_dequant(w: QuantWeight) -> torch.Tensor:
+    """The rotated weight W_rot of an EXL3 layer as bf16 [N, K] (without the Hadamard transforms and the sign / scale vectors)."""
+    assert w.fmt == WFormat.EXL3
+    wb = torch.empty(w.N, w.K, dtype=torch.bfloat16, device=w.device)
+    _check(_lib.cuda().mx_exl3_dequant_bf16(_p(w.p0), w.K // 16, w.N // 16, w.bits, _p(wb), _stream()), "exl3 dequant")
+    _count()
+    return wb
+
+
+def _exl3_linear(x, w: QuantWeight, bias, out_f32, out):
+    """y = had128(had128(x * suh) W_rot) * svh + bias: the trellis is decoded in registers for decode-sized batches and once to a bf16
+    scratch matrix for the tensor-core GEMM otherwise (src/ops/gemv_exl3.cpp:162 runs the same three steps)."""
+    M = x.shape[0]
+    lib = _lib.cuda()
+    xh = hadamard128(x, pre=w.p1[0])
+    if M == 0:
+        return hadamard128(torch.empty(0, w.N, dtype=torch.float32, device=x.device), out_f32=out_f32, out=out)
+    if M <= EXL3_GEMV_MAX_M:
+        # the K tiles are cut into ranges (more CTAs for narrow matrices); the partial sums meet in the Hadamard kernel below
+        ranges = lib.mx_exl3_gemv_ranges(w.K // 16, w.N // 16)
+        acc = torch.empty(ranges, M, w.N, dtype=torch.float32, device=x.device)
+        _check(lib.mx_exl3_gemv(_p(w.p0), w.K // 16, w.N // 16, w.bits, _p(xh), _p(acc), M, ranges, _stream()), "exl3 gemv")
+        _count()
+    else:
+        wb = exl3_dequant(w)
+        acc = torch.empty(M, w.N, dtype=torch.float32, device=x.device)
+        _check(lib.mx_gemm(_p(xh), int(WFormat.BF16), _p(wb), _vp(0), _vp(0), _vp(0), 1, _p(acc), w.N, 1, _vp(0), _vp(0), ACT_NONE, C.c_float(0.0),
+                           C.c_float(0.0), M, w.N, w.K, _vp(0), _vp(0), _pick_bn(M, w.N), _stream()), "gemm")
+        _count()
+    return hadamard128(acc, post=w.p2[0], bias=bias, out_f32=out_f32, out=out)
 
 
 def gemm(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, row_scale=None, bn=None):

@@ -126,6 +126,21 @@ def linear(x, w: QuantWeight, bias=None, act=ACT_NONE, act_alpha=1.702, act_limi
     return y if out_f32 else y.to(torch.bfloat16)
 
 
+def hadamard128(x, pre=None, post=None, bias=None, out_f32=False, out=None):
+    """``had128(x * pre) * post + bias`` over every aligned run of 128 elements of the rows (EXL3 layers; src/ops/hadamard.cpp:36)."""
+    from ..formats.exl3 import hadamard128 as _had
+    v = x.to(torch.float32)
+    if pre is not None:
+        v = v * pre
+    v = _had(v)
+    if post is not None:
+        v = v * post
+    if bias is not None:
+        v = v + bias
+    v = v if out_f32 else v.to(torch.bfloat16)
+    return v if out is None else out.copy_(v)
+
+
 def grouped_linear(xp, w: QuantWeight, tile_expert, num_tiles, bias=None, act=ACT_NONE, act_alpha=1.702, act_limit=7.0, out_f32=False, bn=128,
                    out_dtype=None):
     """xp: packed rows [P,K]; tile t (rows 128t..128t+127) uses expert tile_expert[t] for t < num_tiles[0]."""

@@ -17,6 +17,9 @@ MXF4T     the same codes cut into tiles of 192 rows x 128 elements, ``p0`` [E,FB
           exponents as 512-byte atoms [E,FB,KB,2,512] in the order the tensor core's scale-factor
           registers want: row r, k-block q of an atom at byte (r % 32) * 16 + (r // 32) * 4 + q.
           A gated pair shares one bank: 96 gate rows + the same 96 up rows per tile (``dual``)
+EXL3      ``p0`` the trellis int16 [1,K/16,N/16,16*bits] as stored in the checkpoint, ``p1`` suh fp32 [1,K],
+          ``p2`` svh fp32 [1,N]: y = had128(had128(x * suh) W_rot) * svh (see formats/exl3.py).  One matrix per
+          weight (no expert stacks), never concatenated or sliced: every projection has its own rotation
 ========  =====================================================================================
 
 The rows of the small scale planes (Q8 ``p1``, Q6K ``p3``, MXFP4 ``p1``) are zero-padded to 16 bytes
@@ -45,6 +48,7 @@ class WFormat(IntEnum):
     Q6K = 3
     MXFP4 = 4
     MXF4T = 5      # MXFP4 in 128 x 128 tiles for the block-scaled tensor-core kernel (see to_mxf4_tiles)
+    EXL3 = 6       # trellis-coded weights with Hadamard rotations on both sides (formats/exl3.py)
 
 
 def _pad_last(t: torch.Tensor, mult: int) -> torch.Tensor:
@@ -99,14 +103,25 @@ class QuantWeight:
         out = [None if t is None else fn(t) for t in self.planes()]
         return QuantWeight(self.fmt, self.N, self.K, self.E, *out, dual=self.dual)
 
+    def _no_exl3(self, what: str) -> None:
+        if self.fmt == WFormat.EXL3:
+            raise ValueError(f"an EXL3 weight cannot be {what}: its rows and columns are mixed by the layer's Hadamard rotations")
+
+    @property
+    def bits(self) -> int:
+        """EXL3: bits per weight of the trellis."""
+        return int(self.p0.shape[-1]) // 16
+
     def select_rows(self, idx: torch.Tensor) -> "QuantWeight":
         """Rows (output features) ``idx`` of every expert."""
+        self._no_exl3("row-permuted")
         idx = idx.to(self.device)
         w = self._map_planes(lambda t: t.index_select(1, idx).contiguous())
         w.N = int(idx.numel())
         return w
 
     def slice_rows(self, lo: int, hi: int) -> "QuantWeight":
+        self._no_exl3("sliced by rows")
         w = self._map_planes(lambda t: t[:, lo:hi].contiguous())
         w.N = hi - lo
         return w
@@ -123,6 +138,7 @@ class QuantWeight:
         """Input-dimension slice [lo, hi) (row-parallel shards).  Bounds must sit on block boundaries; with
         ``requant`` a slice that cuts a block is re-encoded instead (Q8 when the slice is a multiple of 32 wide,
         else bf16) -- the case of a 256-element super-block format sharded finer than its blocks."""
+        self._no_exl3("sliced along K")
         g = self.k_granule()
         if lo % g or hi % g:
             if not requant:
@@ -148,6 +164,7 @@ class QuantWeight:
     @staticmethod
     def cat_rows(ws: list["QuantWeight"]) -> "QuantWeight":
         f = ws[0]
+        f._no_exl3("concatenated")
         assert all(w.fmt == f.fmt and w.K == f.K and w.E == f.E for w in ws), "cannot concatenate mixed formats"
         outs = []
         for i in range(4):
@@ -159,6 +176,7 @@ class QuantWeight:
     def interleave_gate_up(gate: "QuantWeight", up: "QuantWeight") -> "QuantWeight":
         """Rows in groups of 16: [g0..g15, u0..u15, g16..g31, u16..u31, ...] (kernel epilogues rely on it)."""
         assert gate.fmt == up.fmt and gate.N == up.N and gate.K == up.K and gate.E == up.E
+        gate._no_exl3("interleaved")
         if gate.N % 16:
             raise ValueError("gate/up interleave needs a multiple of 16 output features")
         def il(a, b):
@@ -200,6 +218,10 @@ class QuantWeight:
             if self.dual:                 # gate rows, then up rows
                 return torch.cat([planes[0].dequantize(dtype), planes[1].dequantize(dtype)], dim=1)
             return planes.dequantize(dtype)
+        elif self.fmt == WFormat.EXL3:
+            # the dense matrix of the whole layer (rotations and sign / scale vectors included), so that x W^T is the layer
+            from ..formats import exl3
+            return exl3.effective_weight(self.p0[0], self.p1[0], self.p2[0]).to(self.p0.device).reshape(1, N, K).to(dtype)
         elif self.fmt == WFormat.MXFP4:
             codes = self.p0.to(torch.int64)
             c = torch.stack([codes & 15, codes >> 4], dim=-1).reshape(E, N, K // 32, 32)
@@ -276,6 +298,8 @@ def from_ggml(raw: torch.Tensor, ttype: int, N: int, K: int, E: int = 1, keep_q8
         c = torch.cat([qs & 15, qs >> 4], dim=-1)                                 # natural order codes [.., 32]
         p0 = (c[..., 0::2] | (c[..., 1::2] << 4)).to(torch.uint8).reshape(E, N, K // 2)
         return QuantWeight(WFormat.MXFP4, N, K, E, p0.contiguous(), _pad_last(e, 16))
+    if t == GGMLType.EXL3:
+        raise ValueError("an EXL3 trellis needs its suh / svh vectors: use from_exl3")
     if t in (GGMLType.Q5_K, GGMLType.Q4_0):
         # rare formats: decode once on the host and keep bf16 (the reference also widens these at load)
         import numpy as np
@@ -439,6 +463,17 @@ def quantize_q6k(w: torch.Tensor) -> QuantWeight:
     p1 = torch.stack(hb, dim=-1).reshape(E, N, K // 4).to(torch.uint8)
     return QuantWeight(WFormat.Q6K, N, K, E, p0.contiguous(), p1.contiguous(), sc.reshape(E, N, K // 16).to(torch.int8).contiguous(),
                        _pad_last(d16.reshape(E, N, K // 256), 8))
+
+
+def from_exl3(trellis: torch.Tensor, suh: torch.Tensor, svh: torch.Tensor) -> QuantWeight:
+    """trellis int16 [K/16, N/16, 16*bits], suh [K], svh [N] (any float type) -> the runtime weight."""
+    assert trellis.dtype == torch.int16 and trellis.dim() == 3
+    K, N = int(trellis.shape[0]) * 16, int(trellis.shape[1]) * 16
+    if K % 128 or N % 128 or suh.numel() != K or svh.numel() != N or not 1 <= int(trellis.shape[2]) // 16 <= 8 or int(trellis.shape[2]) % 16:
+        raise ValueError(f"inconsistent EXL3 layer: trellis {tuple(trellis.shape)}, suh {suh.numel()}, svh {svh.numel()}")
+    dev = trellis.device
+    return QuantWeight(WFormat.EXL3, N, K, 1, trellis.unsqueeze(0).contiguous(), suh.to(dev, torch.float32).reshape(1, K).contiguous(),
+                       svh.to(dev, torch.float32).reshape(1, N).contiguous())
 
 
 def from_dense(w: torch.Tensor, fmt: WFormat) -> QuantWeight:
