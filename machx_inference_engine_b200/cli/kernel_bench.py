@@ -187,10 +187,16 @@ def main(argv=None):
     K.set_gemv_path(a.gemv_path)
     global GRAPH_REPS
     GRAPH_REPS = a.graph_reps
-    fmt = {"bf16": WFormat.BF16, "q8": WFormat.Q8, "q4k": WFormat.Q4K, "q6k": WFormat.Q6K, "mxfp4": WFormat.MXFP4, "mxf4t": WFormat.MXFP4}[a.fmt]
+    exl3_bits = int(a.fmt[5:]) if a.fmt.startswith("exl3-") else (4 if a.fmt == "exl3" else 0)
+    fmt = WFormat.EXL3 if exl3_bits else {"bf16": WFormat.BF16, "q8": WFormat.Q8, "q4k": WFormat.Q4K, "q6k": WFormat.Q6K, "mxfp4": WFormat.MXFP4,
+                                          "mxf4t": WFormat.MXFP4}[a.fmt]
     torch.manual_seed(0)
 
     def weight(N, Kd, E=1):
+        if exl3_bits:       # (gemv / gemm --decode-once: the layer's three steps, Hadamard transforms included)
+            from ..formats import exl3
+            from ..ops.weights import from_exl3
+            return from_exl3(*exl3.random_layer(N, Kd, exl3_bits, torch.Generator(device=dev).manual_seed(N + Kd))).to(dev)
         parts = [from_dense(torch.randn(1, N, Kd, device=dev) * 0.02, fmt) for _ in range(E)]
         if E == 1:
             return parts[0]
