@@ -63,6 +63,20 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// Bytes as a 2-D tensor of 8-byte elements: rows of `row_bytes` (a multiple of 8) `row_stride` bytes apart (a multiple of 16), box of
+// box_bytes x box_rows, no swizzle: the tile lands in shared memory as box_rows dense rows of box_bytes.
+int make_tmap_bytes(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t row_stride, uint32_t box_bytes, uint32_t box_rows) {
+  EncodeTiledFn enc = encoder();
+  if (!enc) return -1;
+  if (row_bytes % 8 || box_bytes % 16 || box_bytes / 8 > 256 || box_rows > 256 || row_stride % 16 || ((uintptr_t)base & 15)) return -2;
+  cuuint64_t gdim[2] = {row_bytes / 8, rows};
+  cuuint64_t gstr[1] = {row_stride};
+  cuuint32_t b[2] = {box_bytes / 8, box_rows}, es[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), gdim, gstr, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 static bool g_pdl = true;
 bool pdl_enabled() { return g_pdl; }
 void set_pdl(bool on) { g_pdl = on; }

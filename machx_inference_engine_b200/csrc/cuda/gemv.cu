@@ -473,10 +473,10 @@ int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const 
 // 0: pick per case (the streaming kernel where it measured faster: bf16, Q8, Q4_K and Q6_K matrices and the gated MXFP4 expert GEMV),
 // 1: register-streamed kernels only, 2: streaming kernel wherever it applies (tests, A/B timing)
 static int g_gemv_path = 0;
-// Q4_K rows shorter than this leave most lanes of the streaming kernel without a 64-element granule
+// Q4_K / Q6_K rows shorter than this leave most lanes of the streaming kernel without a 64-element granule
 static int g_kq_stream_min_k = 1024;
-// Q6_K: the streaming kernel is bound by its decode arithmetic near 2.8 TB/s, the register-streamed kernel reaches 3.3 TB/s on a
-// vocabulary-sized matrix but half of that on a projection; rows that do not split into 2048-element chunks leave lanes idle
+// Q6_K: the streaming kernel is bound by its decode arithmetic (2.7-3.5 TB/s on projections), the register-streamed kernel reaches
+// 3.3 TB/s on a vocabulary-sized matrix but half of that on a projection
 static int g_q6k_stream_max_n = 32768;
 MX_HOST_API void mx_gemv_set_path(int path) { g_gemv_path = path; }
 
@@ -498,7 +498,7 @@ static int gemv_impl(int wfmt, const void* w0, const void* w1, const void* w2, c
   if ((wfmt == WF_Q4K || wfmt == WF_Q6K) && (K % 256)) return -103;
   if (!slot_expert && act == 0 && (M < 1 || M > GEMV_MAX_M)) return -106;
   if (g_gemv_path == 2 || (g_gemv_path == 0 && (wfmt == WF_BF16 || wfmt == WF_Q8 || (wfmt == WF_Q4K && K >= g_kq_stream_min_k) ||
-                                                (wfmt == WF_Q6K && act == 0 && K % 2048 == 0 && N <= g_q6k_stream_max_n) || (wfmt == WF_MXFP4 && act != 0)))) {
+                                                (wfmt == WF_Q6K && act == 0 && K >= g_kq_stream_min_k && N <= g_q6k_stream_max_n) || (wfmt == WF_MXFP4 && act != 0)))) {
     const int rc = gemv_stream_try(wfmt, WeightRef{w0, w1, w2, w3}, x, y, bias, M, N, K, out_f32, act, act_alpha, act_limit, slot_expert,
                                    slot_scale, slots, x_div, g_e_lo, g_e_hi, peer, stream);
     if (rc != 1) return rc;

@@ -2,7 +2,9 @@
 // ring with bulk asynchronous copies (cp.async.bulk + mbarrier transaction counts), one producer warp feeding
 // 4-8 consumer warps.  A weight row block is one contiguous run per plane, so a stage is one or two bulk copies;
 // the bytes in flight per SM are set by the ring (about 100 KB), not by registers or occupancy, which is what a
-// 1-3 us kernel needs to get near HBM speed.  Formats: bf16, Q8 (int8 + fp16 scale per 32), MXFP4 (E2M1 nibbles +
+// 1-3 us kernel needs to get near HBM speed.  Rows longer than one chunk are cut along K: a stage is then RB row segments
+// that are not contiguous, fetched by one tiled TMA load per plane (the plane as a 2-D byte tensor) -- one bulk copy per
+// segment is bound by the rate of copy requests (about 120 cycles each), not by bytes.  Formats: bf16, Q8 (int8 + fp16 scale per 32), MXFP4 (E2M1 nibbles +
 // e8m0 scale per 32), Q4_K (native 144-byte blocks) and Q6_K (four planes).  Q8, Q4_K and Q6_K codes meet block-scaled 16-bit
 // activations in dp4a (exact integer partial sums, see the staging code).  MXFP4 rows are multiplied in packed fp16: the E2M1 codes become f16x2 words by byte permutes,
 // the activation row is staged once as f16 scaled into range, 16-term partial sums run in HFMA2 and are folded
@@ -22,6 +24,7 @@
 // logits, picks the top-k experts per token and writes the token rows as MXFP8 pair tiles for the block-scaled expert GEMM.
 //
 // Reference parity: src/ops/gemv_fp16.cpp:64, gemv_q8dot.cpp:276-680, gemv_mxfp4.cpp:94-323, moe_fused.cpp:101-541.
+#include <cstring>
 #include "common.cuh"
 #include "comm.cuh"
 #include "dequant.cuh"
@@ -30,6 +33,8 @@
 #include "mxfp8.cuh"
 
 namespace mx {
+
+static int g_gs_tma = 1;          // tiled TMA loads for chunked stages (mx_gemv_stream_set_tma: A/B timing)
 
 constexpr int GS_MAX_STAGES = 4;
 constexpr int GS_MAX_XROWS = 8;
@@ -46,7 +51,7 @@ template <> struct GsCfg<WF_BF16> { static constexpr int WARPS = 4, RPW = 1; };
 template <> struct GsCfg<WF_Q8> { static constexpr int WARPS = 8, RPW = 1; };
 template <> struct GsCfg<WF_MXFP4> { static constexpr int WARPS = 8, RPW = 2; };
 template <> struct GsCfg<WF_Q4K> { static constexpr int WARPS = 8, RPW = 2; };
-template <> struct GsCfg<WF_Q8I> { static constexpr int WARPS = 8, RPW = 1; };
+template <> struct GsCfg<WF_Q8I> { static constexpr int WARPS = 8, RPW = 2; };
 template <> struct GsCfg<WF_Q6K> { static constexpr int WARPS = 8, RPW = 2; };
 
 // activation rows = RMSNorm(x + delta_scale * delta) * w
@@ -95,6 +100,8 @@ struct GsParams {
   int KC, nkc;              // k chunk in elements (whole rows unless bf16 rows are very long) and chunks per row
   int nblk;                 // row blocks (plain) or feature blocks (gated) per slot
   int nst;                  // ring depth (2..4), chosen so that two CTAs fit an SM where possible
+  int use_tma;              // chunked rows: one tiled TMA load per plane and stage (tensor maps over the planes) instead of one bulk copy per row
+  long long tma_rows;       // rows the tensor maps cover (experts x N)
   int* status;
   PeerOut peer;
 };
@@ -400,7 +407,8 @@ __device__ __forceinline__ void gs_row(const uint8_t* __restrict__ w0, const uin
 
 // NG: granules per lane and row chunk (compile time, so the activation slice stays in registers); two CTAs per SM
 template <int FMT, int MM, bool GATED, int NG>
-__global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_kernel(const GsParams p) {
+__global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2)
+gemv_stream_kernel(const GsParams p, const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, const __grid_constant__ CUtensorMap tm2) {
   constexpr int WARPS = GsCfg<FMT>::WARPS, RPW = GsCfg<FMT>::RPW, RB = WARPS * RPW, FB = RB / 2;
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -410,7 +418,8 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
   const int plane1_off = RB * r0b, plane2_off = plane1_off + RB * r1b, plane3_off = plane2_off + RB * r2b;
   const int stage_bytes = RB * (r0b + r1b + r2b + r3b);
   const int xrow_bytes = gs_xrow_bytes<FMT>(K);
-  const int x_bytes = (p.n_xrows * xrow_bytes + 15) & ~15;
+  // the stages start on a 128-byte boundary of the shared window (tiled TMA loads want it; the host adds the slack)
+  const int x_bytes = ((p.n_xrows * xrow_bytes + 127) & ~127) + (int)((128u - (smem_u32(smem) & 127u)) & 127u);
   uint8_t* xs = smem;
   uint8_t* stages = smem + x_bytes;
   const int NST = p.nst;
@@ -450,9 +459,11 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
         const uint8_t* b1 = (const uint8_t*)p.w.p1;
         const uint8_t* b2 = (const uint8_t*)p.w.p2;
         const uint8_t* b3 = (const uint8_t*)p.w.p3;
+        int tma_row0 = 0;          // first row of this slot's matrix in the tensor maps
         if (p.slot_expert) {
           const int e = p.slot_expert[slot];
           if (e < p.e_lo || e >= p.e_hi) continue;
+          tma_row0 = (e - p.e_lo) * p.N;
           b0 += (size_t)(e - p.e_lo) * p.N * g0;
           b1 += (size_t)(e - p.e_lo) * p.N * g1;
           b2 += (size_t)(e - p.e_lo) * p.N * g2;
@@ -470,6 +481,19 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
           if (GATED) {
             const int f0 = blk * FB, nf = min(FB, F - f0);
             const int grow = 32 * (f0 >> 4) + (f0 & 15);
+            if (p.use_tma) {
+              // two boxes of FB rows per plane (rows past the block's last feature are loaded and ignored; rows past the matrix read zeros)
+              if (lane == 0) {
+                mbar_expect_tx(full, 2u * FB * (r0b + r1b));
+                tma_load_2d(dst, &tm0, full, kc * (r0b >> 3), tma_row0 + grow);
+                tma_load_2d(dst + FB * r0b, &tm0, full, kc * (r0b >> 3), tma_row0 + grow + 16);
+                if (r1b) {
+                  tma_load_2d(dst + plane1_off, &tm1, full, kc * (r1b >> 3), tma_row0 + grow);
+                  tma_load_2d(dst + plane1_off + FB * r1b, &tm1, full, kc * (r1b >> 3), tma_row0 + grow + 16);
+                }
+              }
+              continue;
+            }
             if (lane == 0) mbar_expect_tx(full, 2u * nf * (r0b + r1b));
             __syncwarp();
             if (p.nkc == 1) {
@@ -478,16 +502,29 @@ __global__ void __launch_bounds__((GsCfg<FMT>::WARPS + 1) * 32, 2) gemv_stream_k
                 bulk_g2s(dst + FB * r0b, b0 + (size_t)(grow + 16) * g0, nf * r0b, full);
               }
             } else {
-              // k chunk of every gate row (lanes 0..nf-1) and of every up row (lanes 16..16+nf-1); chunked formats have no second plane
+              // k chunk of every gate row (lanes 0..nf-1) and of every up row (lanes 16..16+nf-1), both planes
               const int r = lane & 15, up = lane >> 4;
-              if (r < nf) bulk_g2s(dst + (up * FB + r) * r0b, b0 + (size_t)(grow + 16 * up + r) * g0 + (size_t)kc * r0b, r0b, full);
+              if (r < nf) {
+                bulk_g2s(dst + (up * FB + r) * r0b, b0 + (size_t)(grow + 16 * up + r) * g0 + (size_t)kc * r0b, r0b, full);
+                if (r1b) bulk_g2s(dst + plane1_off + (up * FB + r) * r1b, b1 + (size_t)(grow + 16 * up + r) * g1 + (size_t)kc * r1b, r1b, full);
+              }
             }
-            if (r1b && lane == 0) {
+            if (r1b && lane == 0 && p.nkc == 1) {
               bulk_g2s(dst + plane1_off, b1 + (size_t)grow * g1, nf * r1b, full);
               bulk_g2s(dst + plane1_off + FB * r1b, b1 + (size_t)(grow + 16) * g1, nf * r1b, full);
             }
           } else {
             const int row0 = blk * RB, nr = min(RB, p.N - row0);
+            if (p.use_tma) {
+              if (lane == 0) {
+                mbar_expect_tx(full, (uint32_t)RB * (r0b + r1b + r2b) + (uint32_t)nr * r3b);
+                tma_load_2d(dst, &tm0, full, kc * (r0b >> 3), tma_row0 + row0);
+                if (r1b) tma_load_2d(dst + plane1_off, &tm1, full, kc * (r1b >> 3), tma_row0 + row0);
+                if (r2b) tma_load_2d(dst + plane2_off, &tm2, full, kc * (r2b >> 3), tma_row0 + row0);
+                if (r3b) bulk_g2s(dst + plane3_off, b3 + (size_t)row0 * g3, nr * r3b, full);
+              }
+              continue;
+            }
             if (lane == 0) mbar_expect_tx(full, (uint32_t)nr * (r0b + r1b + r2b + r3b));
             __syncwarp();
             if (p.nkc == 1) {
@@ -867,14 +904,35 @@ static int gs_launch(const GsParams& p, int smem, cudaStream_t st) {
   const int units = p.slots * p.nblk;
   const int per_sm = smem <= 113 * 1024 ? 2 : 1;
   const int grid = min(units, sm_count() * per_sm);
-  launch_pdl(gemv_stream_kernel<FMT, MM, GATED, NG>, dim3(grid), dim3(THREADS), (size_t)smem, st, p);
+  // Chunked rows: a stage is RB row segments that are not contiguous in memory.  One tiled TMA load per plane fetches them all
+  // (the planes as 2-D byte tensors [rows][row bytes], box = chunk bytes x rows of the stage); segments wider than a box (bf16) and
+  // expert stacks of unknown extent keep the per-row bulk copies.
+  CUtensorMap tm[3];
+  std::memset(tm, 0, sizeof(tm));
+  GsParams q = p;
+  q.use_tma = 0;
+  if (g_gs_tma && p.nkc > 1 && p.tma_rows > 0) {
+    constexpr int RB = GsCfg<FMT>::WARPS * GsCfg<FMT>::RPW;
+    const uint32_t box_rows = GATED ? RB / 2 : RB;
+    const int cb[3] = {gs_stage_row0<FMT>(p.K, p.KC), gs_stage_row1<FMT>(p.K, p.KC), gs_stage_row2<FMT>(p.K, p.KC)};
+    const int rbytes[3] = {gs_row_bytes0<FMT>(p.K), gs_row_bytes1<FMT>(p.K), gs_row_bytes2<FMT>(p.K)};
+    const void* base[3] = {p.w.p0, p.w.p1, p.w.p2};
+    bool ok = true;
+    for (int i = 0; i < 3 && ok; ++i) {
+      if (!cb[i]) continue;
+      // the tensor's rows are the used bytes of each plane row (chunks x chunk bytes); the pitch is the plane's row stride
+      ok = cb[i] <= 2048 && make_tmap_bytes(&tm[i], base[i], (uint64_t)cb[i] * p.nkc, (uint64_t)p.tma_rows, (uint64_t)rbytes[i], (uint32_t)cb[i], box_rows) == 0;
+    }
+    q.use_tma = ok ? 1 : 0;
+  }
+  launch_pdl(gemv_stream_kernel<FMT, MM, GATED, NG>, dim3(grid), dim3(THREADS), (size_t)smem, st, q, tm[0], tm[1], tm[2]);
   return (int)cudaGetLastError();
 }
 
 template <int FMT, int NG>
 static int gs_dispatch_ng(GsParams& p, int smem, bool gated, cudaStream_t st) {
   if (gated) {
-    if constexpr (FMT == WF_Q6K || FMT == WF_Q8I) return 1;       // no gated form (one row per warp, or four planes)
+    if constexpr (FMT == WF_Q6K || GsCfg<FMT>::RPW != 2) return 1;       // no gated form (four planes, or one row per warp)
     else return gs_launch<FMT, 1, true, NG>(p, smem, st);
   }
   if (p.slot_mode || p.M == 1) return gs_launch<FMT, 1, false, NG>(p, smem, st);
@@ -904,11 +962,11 @@ static int gs_dispatch(GsParams& p, cudaStream_t st) {
     p.nkc = n; p.KC = p.K / n;
   }
   if (p.KC / Gran<FMT>::GE > 32 * Gran<FMT>::NGMAX || p.KC % Gran<FMT>::GE) return 1;
-  if (gated && p.nkc > 1 && gs_row_bytes1<FMT>(p.K)) return 1;
+  if (gated && p.nkc > 1 && gs_row_bytes1<FMT>(p.K) && FMT != WF_Q8I) return 1;
   if (FMT == WF_MXFP4 && p.K > 4096) return 1;
   p.nblk = gated ? (p.N / 2 + RB / 2 - 1) / (RB / 2) : (p.N + RB - 1) / RB;
   const int stage = RB * gs_stage_row_all<FMT>(p.K, p.KC);
-  const int fixed = ((p.n_xrows * gs_xrow_bytes<FMT>(p.K) + 15) & ~15) + 2 * GS_MAX_STAGES * 8 + GS_MAX_XROWS * 4 + 16;
+  const int fixed = ((p.n_xrows * gs_xrow_bytes<FMT>(p.K) + 127) & ~127) + 128 + 2 * GS_MAX_STAGES * 8 + GS_MAX_XROWS * 4 + 16;
   p.nst = GS_MAX_STAGES;
   while (p.nst > 2 && fixed + p.nst * stage > 113 * 1024) --p.nst;        // two CTAs per SM when three stages still fit
   if (fixed + p.nst * stage > 113 * 1024) p.nst = min(GS_MAX_STAGES, max(2, (200 * 1024 - fixed) / stage));
@@ -941,7 +999,7 @@ static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* 
   if (wfmt != WF_BF16 && wfmt != WF_Q8 && wfmt != WF_MXFP4 && wfmt != WF_Q4K && wfmt != WF_Q6K) return 1;
   if (K % 32 && !(wfmt == WF_BF16 && K % 8 == 0)) return 1;
   if ((wfmt == WF_Q4K || wfmt == WF_Q6K) && K % 256) return 1;
-  if (act != 0 && wfmt != WF_MXFP4 && wfmt != WF_Q4K) return 1;      // gated epilogue: one feature per warp needs RPW == 2
+  if (act != 0 && wfmt != WF_MXFP4 && wfmt != WF_Q4K && !(wfmt == WF_Q8 && !norm && !route)) return 1;      // gated epilogue: one feature per warp needs RPW == 2
   if (act != 0 && (N % 32)) return 1;
   GsParams p;
   p.w = w; p.x = (const __nv_bfloat16*)x; p.y = y; p.bias = bias; p.slot_expert = slot_expert; p.slot_scale = slot_scale;
@@ -956,6 +1014,8 @@ static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* 
   if (rb0 % 16) return 1;
   if (((uintptr_t)w.p0 & 15) || (w.p1 && ((uintptr_t)w.p1 & 15)) || ((uintptr_t)x & 15)) return 1;
   if (wfmt == WF_Q6K && (!w.p2 || !w.p3 || ((uintptr_t)w.p2 & 15) || ((uintptr_t)w.p3 & 15))) return 1;
+  p.use_tma = 0;
+  p.tma_rows = slot_expert ? ((e_hi > e_lo && e_hi - e_lo <= 65536) ? (long long)(e_hi - e_lo) * N : 0) : N;
   if (peer) p.peer = *peer; else p.peer.world = 0;
   if (norm) p.norm = *norm; else p.norm.x = nullptr;
   if (route) p.route = *route; else p.route.ticket = nullptr;
@@ -968,6 +1028,10 @@ static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* 
     default: return gs_dispatch<WF_MXFP4>(p, st);
   }
 }
+
+}  // namespace mx
+MX_HOST_API void mx_gemv_stream_set_tma(int on) { mx::g_gs_tma = on ? 1 : 0; }
+namespace mx {
 
 // One ticket word per launch of a router GEMV with the routing tail; launches rotate through the words (see attention.cu).
 constexpr int GS_TICKET_SLOTS = 8;

@@ -21,6 +21,7 @@ int* status_word();
 int sm_count();
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                    const uint32_t* box, int swizzle128);
+int make_tmap_bytes(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t row_stride, uint32_t box_bytes, uint32_t box_rows);
 bool pdl_enabled();
 
 // Kernel launch with the programmatic-dependent-launch attribute (see pdl_* in common.cuh).

@@ -68,6 +68,11 @@ def set_gemv_path(path) -> None:
     _lib.cuda().mx_gemv_set_path(code)
 
 
+def set_gemv_tma(on: bool) -> None:
+    """Streaming GEMV with chunked rows (K above one chunk): one tiled TMA load per plane and stage (default) or one bulk copy per row."""
+    _lib.cuda().mx_gemv_stream_set_tma(int(bool(on)))
+
+
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launch for the decode-chain kernels (default on): the next kernel's CTAs are scheduled while
     the previous kernel drains and the streaming GEMV prefetches its weights before its inputs exist."""

@@ -81,7 +81,7 @@ def test_gemv(fmt, M):
     assert rel_err(got, want) < 2e-3
 
 
-@pytest.mark.parametrize("fmt", [WFormat.BF16, WFormat.MXFP4, WFormat.Q4K])
+@pytest.mark.parametrize("fmt", [WFormat.BF16, WFormat.MXFP4, WFormat.Q4K, WFormat.Q8])
 def test_gemv_gated(fmt):
     F, Kd = 96, 512
     qw = make_weight(fmt, 2 * F, Kd)
@@ -227,6 +227,17 @@ def test_streaming_gemv_matches_register_gemv_and_oracle(fmt):
         k.check_status()
         assert rel_err(a, want) < 4e-3, (M, N, Kd)
         assert rel_err(b, want) < 4e-3, (M, N, Kd)
+    if fmt == WFormat.Q8:
+        # gated epilogue of the dp4a form: whole rows (K <= 3072) and K chunks with both planes copied per row
+        for (M, F, Kd) in [(1, 96, 2880), (2, 208, 4096), (1, 64, 14336)]:       # (F a multiple of 16)
+            w = make_weight(fmt, 2 * F, Kd, seed=F)
+            x = torch.randn(M, Kd, device=dev()).to(torch.bfloat16)
+            bias = torch.randn(2 * F, device=dev()) * 0.1
+            k.set_gemv_path("stream")
+            got = k.linear(x, w, bias=bias, act=ref.ACT_SWIGLU, out_f32=True)
+            k.set_gemv_path("auto")
+            k.check_status()
+            assert rel_err(got, ref.linear(x, w, bias=bias, act=ref.ACT_SWIGLU, out_f32=True)) < 3e-3, (M, F, Kd)
     # activations with a large dynamic range (fp16 staging of the MXFP4 path must not overflow or flush them)
     # (and the block-scaled 16-bit staging of the Q8 path must keep small elements beside large ones)
     if fmt in (WFormat.MXFP4, WFormat.Q8):
@@ -277,6 +288,28 @@ def test_streaming_gemv_kquants(fmt):
         assert rel_err(k.linear(x, w, out_f32=True), ref.linear(x, w, out_f32=True)) < 1e-3
         k.check_status()
     finally:
+        k.set_gemv_path("auto")
+
+
+def test_streaming_gemv_chunk_copies_both_ways():
+    """Chunked rows arrive by tiled TMA loads (default) or by one bulk copy per row: the same numbers either way, for every chunked
+    format, plain and gated, with a last row block that is cut by the matrix edge."""
+    k = K()
+    try:
+        k.set_gemv_path("stream")
+        for fmt, N, Kd, act in [(WFormat.Q4K, 200, 4096, ref.ACT_NONE), (WFormat.Q4K, 2 * 208, 6144, ref.ACT_SWIGLU), (WFormat.Q6K, 72, 14336, ref.ACT_NONE),
+                                (WFormat.Q8, 100, 14336, ref.ACT_NONE), (WFormat.Q8, 2 * 112, 4096, ref.ACT_SWIGLU), (WFormat.Q4K, 40, 5120, ref.ACT_NONE)]:
+            w = make_weight(fmt, N, Kd, seed=N)
+            x = torch.randn(1, Kd, device=dev()).to(torch.bfloat16)
+            outs = []
+            for tma in (True, False):
+                k.set_gemv_tma(tma)
+                outs.append(k.linear(x, w, act=act, out_f32=True))
+            k.check_status()
+            assert torch.equal(outs[0], outs[1]), (fmt, N, Kd)
+            assert rel_err(outs[0], ref.linear(x, w, act=act, out_f32=True)) < 3e-3, (fmt, N, Kd)
+    finally:
+        k.set_gemv_tma(True)
         k.set_gemv_path("auto")
 
 
