@@ -475,9 +475,6 @@ int gemv_stream_try(int wfmt, const WeightRef& w, const void* x, void* y, const 
 static int g_gemv_path = 0;
 // Q4_K / Q6_K rows shorter than this leave most lanes of the streaming kernel without a 64-element granule
 static int g_kq_stream_min_k = 1024;
-// Q6_K: the streaming kernel is bound by its decode arithmetic (2.7-3.5 TB/s on projections), the register-streamed kernel reaches
-// 3.3 TB/s on a vocabulary-sized matrix but half of that on a projection
-static int g_q6k_stream_max_n = 32768;
 MX_HOST_API void mx_gemv_set_path(int path) { g_gemv_path = path; }
 
 // Row-parallel GEMV fused with the all-reduce: fp32 partials [M][N] land in every rank's inbox (see comm.cuh).
@@ -498,7 +495,7 @@ static int gemv_impl(int wfmt, const void* w0, const void* w1, const void* w2, c
   if ((wfmt == WF_Q4K || wfmt == WF_Q6K) && (K % 256)) return -103;
   if (!slot_expert && act == 0 && (M < 1 || M > GEMV_MAX_M)) return -106;
   if (g_gemv_path == 2 || (g_gemv_path == 0 && (wfmt == WF_BF16 || wfmt == WF_Q8 || (wfmt == WF_Q4K && K >= g_kq_stream_min_k) ||
-                                                (wfmt == WF_Q6K && act == 0 && K >= g_kq_stream_min_k && N <= g_q6k_stream_max_n) || (wfmt == WF_MXFP4 && act != 0)))) {
+                                                (wfmt == WF_Q6K && act == 0 && K >= g_kq_stream_min_k) || (wfmt == WF_MXFP4 && act != 0)))) {
     const int rc = gemv_stream_try(wfmt, WeightRef{w0, w1, w2, w3}, x, y, bias, M, N, K, out_f32, act, act_alpha, act_limit, slot_expert,
                                    slot_scale, slots, x_div, g_e_lo, g_e_hi, peer, stream);
     if (rc != 1) return rc;

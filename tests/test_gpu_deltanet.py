@@ -123,28 +123,41 @@ def test_gated_rmsnorm_heads_strided_z():
 
 @pytest.mark.parametrize("spec_k", [0, 3])
 def test_hybrid_model_matches_cpu_oracle(spec_k):
+    """Greedy tokens of the engine on the GPU (plain and self-speculative) against the CPU oracle.  Random-init logits and router scores
+    have near-ties, and one flipped token changes everything after it, so free-running continuations are compared only in their first
+    token; the steps after it are compared one at a time from the oracle's own context: the GPU engine gets the prompt plus the oracle's
+    first i tokens and must produce the oracle's next two (one from the prefill path, one from a decode step)."""
     cfg = preset("tiny-qwen3next")
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (37, 150)]
-    outs = {}
-    for dev in ("cpu", "cuda:0"):
-        model = build_model(cfg, torch.device(dev), quant="q8_0", max_ctx=512, gen_device="cpu")
-        eng = LLMEngine(model, EngineOptions(max_ctx=512, max_batch_tokens=64, max_seqs=2, spec_k=spec_k if dev != "cpu" else 0))
-        outs[dev] = [eng.generate([p], SamplingParams(max_tokens=10, ignore_eos=True))[0] for p in prompts]
-    assert all(x[0] == y[0] for x, y in zip(outs["cpu"], outs["cuda:0"])), outs
-    same = sum(int(a == b) for x, y in zip(outs["cpu"], outs["cuda:0"]) for a, b in zip(x, y))
-    # random-init logits have near-ties, so later greedy tokens may legitimately differ; the teacher-forced test below is the strict one
-    assert same >= 0.4 * sum(len(x) for x in outs["cpu"]), outs
+    cpu = LLMEngine(build_model(cfg, torch.device("cpu"), quant="q8_0", max_ctx=512, gen_device="cpu"), EngineOptions(max_ctx=512, max_batch_tokens=64, max_seqs=2))
+    gpu = LLMEngine(build_model(cfg, torch.device("cuda:0"), quant="q8_0", max_ctx=512, gen_device="cpu"),
+                    EngineOptions(max_ctx=512, max_batch_tokens=64, max_seqs=2, spec_k=spec_k))
+    want = [cpu.generate([p], SamplingParams(max_tokens=10, ignore_eos=True))[0] for p in prompts]
+    free = [gpu.generate([p], SamplingParams(max_tokens=10, ignore_eos=True))[0] for p in prompts]
+    assert all(x[0] == y[0] and len(y) == 10 for x, y in zip(want, free)), (want, free)
+    assert free == [gpu.generate([p], SamplingParams(max_tokens=10, ignore_eos=True))[0] for p in prompts]       # deterministic
+    first = second = valid = total = 0
+    for p, toks in zip(prompts, want):
+        for i in range(0, len(toks) - 1):
+            got = gpu.generate([p + toks[:i]], SamplingParams(max_tokens=2, ignore_eos=True))[0]
+            total += 1
+            first += int(got[0] == toks[i])
+            if got[0] == toks[i]:
+                valid += 1
+                second += int(got[1] == toks[i + 1])
+    assert first >= 0.75 * total and second >= 0.75 * valid, (first, second, valid, total)
 
 
 @pytest.mark.parametrize("name", ["tiny-qwen35", "tiny-qwen3next"])
 def test_hybrid_logits_cosine_chunked(name):
-    """Teacher-forced logits over a prompt fed in three chunks (state carried between forwards) and a decode step.
+    """Teacher-forced logits over a prompt fed in three chunks (state carried between forwards) and six decode steps (the one-row
+    GEMV / expert-GEMV path; its rows are also held to a bound of their own, since six rows would vanish in the mean over 206).
     The dense hybrid must agree row by row; with random-init routers the MoE hybrid can pick a different expert on a
     near-tie, which changes single rows, so it is held to the mean."""
     from machx_inference_engine_b200.models.transformer import KV_BLOCK, ForwardBatch
     cfg = preset(name)
-    ids = torch.randint(0, cfg.vocab, (201,), generator=torch.Generator().manual_seed(1)).tolist()
+    ids = torch.randint(0, cfg.vocab, (206,), generator=torch.Generator().manual_seed(1)).tolist()
     res = {}
     for dev in ("cpu", "cuda:0"):
         d = torch.device(dev)
@@ -152,7 +165,7 @@ def test_hybrid_logits_cosine_chunked(name):
         kv, st = m.new_kv_cache(6), m.new_state(2)
         bt = torch.arange(1, 5, dtype=torch.int32, device=d).unsqueeze(0)
         outs, t0 = [], 0
-        for n in (64, 72, 64, 1):
+        for n in (64, 72, 64, 1, 1, 1, 1, 1, 1):
             pos = torch.arange(t0, t0 + n, dtype=torch.int32, device=d)
             slot = bt[0][(pos // KV_BLOCK).long()].long() * KV_BLOCK + (pos % KV_BLOCK).long()
             fb = ForwardBatch(torch.tensor(ids[t0:t0 + n], dtype=torch.int32, device=d), pos, slot, bt,
@@ -169,3 +182,4 @@ def test_hybrid_logits_cosine_chunked(name):
         assert (a.argmax(-1) == b.argmax(-1)).float().mean() > 0.9
     else:
         assert float(cos.mean()) > 0.98 and float(cos.median()) > 0.999, cos
+        assert float(cos[-6:].median()) > 0.999 and float(cos[-6:].min()) > 0.9, cos[-6:]

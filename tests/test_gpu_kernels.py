@@ -313,11 +313,12 @@ def test_streaming_gemv_chunk_copies_both_ways():
         k.set_gemv_path("auto")
 
 
-def test_streaming_expert_gemv_with_foreign_experts():
+@pytest.mark.parametrize("fmt", [WFormat.MXFP4, WFormat.Q8, WFormat.Q4K])
+def test_streaming_expert_gemv_with_foreign_experts(fmt):
     k = K()
     E, H, F, topk = 8, 512, 256, 4
-    gu = make_weight(WFormat.MXFP4, 2 * F, H, E=E, seed=1)
-    dn = make_weight(WFormat.MXFP4, H, F, E=E, seed=2)
+    gu = make_weight(fmt, 2 * F, H, E=E, seed=1)
+    dn = make_weight(fmt, H, F, E=E, seed=2)
     gub, dnb = torch.randn(E, 2 * F, device=dev()), torch.randn(E, H, device=dev())
     x = torch.randn(2, H, device=dev()).to(torch.bfloat16)
     se = torch.tensor([1, 6, 2, 7, 0, 3, 5, 2], dtype=torch.int32, device=dev())
