@@ -176,6 +176,7 @@ def main(argv=None):
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--graph-reps", type=int, default=0, help="time N back-to-back calls inside one CUDA graph (per-call time without launch gaps)")
+    ap.add_argument("--bf16-wide", type=int, default=None, help="gemv over bf16 weights: 1 = eight consumer warps per CTA, 0 = four")
     ap.add_argument("--no-tma", action="store_true", help="gemv: chunked rows through one bulk copy per row instead of tiled TMA loads")
     ap.add_argument("--gated", action="store_true", help="gemv: the rows are 16-row interleaved gate / up pairs and the epilogue is SwiGLU")
     ap.add_argument("--gemv-path", default="auto", choices=["auto", "register", "stream"], help="which decode GEMV kernel to time")
@@ -187,6 +188,8 @@ def main(argv=None):
     dev = torch.device("cuda:0")
     K.set_gemv_path(a.gemv_path)
     K.set_gemv_tma(not a.no_tma)
+    if a.bf16_wide is not None:
+        K.set_gemv_bf16_wide(bool(a.bf16_wide))
     global GRAPH_REPS
     GRAPH_REPS = a.graph_reps
     exl3_bits = int(a.fmt[5:]) if a.fmt.startswith("exl3-") else (4 if a.fmt == "exl3" else 0)

@@ -34,6 +34,7 @@
 
 namespace mx {
 
+static int g_gs_bf16_wide = 0;    // bf16 matrices with eight consumer warps per CTA (mx_gemv_stream_set_bf16_wide: A/B timing)
 static int g_gs_tma = 1;          // tiled TMA loads for chunked stages (mx_gemv_stream_set_tma: A/B timing)
 
 constexpr int GS_MAX_STAGES = 4;
@@ -46,8 +47,13 @@ constexpr int GS_NORM_MAX_M = 2;      // rows: they are normalised one after the
 // or the router tail (those write and read the activation rows as bf16)
 constexpr int WF_Q8I = 16;
 
+// bf16 with eight consumer warps per CTA instead of four (chosen at run time, see g_gs_bf16_wide)
+constexpr int WF_BF16W = 17;
+__host__ __device__ constexpr bool gs_is_bf16(int f) { return f == WF_BF16 || f == WF_BF16W; }
+
 template <int FMT> struct GsCfg;
 template <> struct GsCfg<WF_BF16> { static constexpr int WARPS = 4, RPW = 1; };
+template <> struct GsCfg<WF_BF16W> { static constexpr int WARPS = 8, RPW = 1; };
 template <> struct GsCfg<WF_Q8> { static constexpr int WARPS = 8, RPW = 1; };
 template <> struct GsCfg<WF_MXFP4> { static constexpr int WARPS = 8, RPW = 2; };
 template <> struct GsCfg<WF_Q4K> { static constexpr int WARPS = 8, RPW = 2; };
@@ -107,17 +113,17 @@ struct GsParams {
 };
 
 template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes0(int K) {
-  return FMT == WF_BF16 ? K * 2 : ((FMT == WF_Q8 || FMT == WF_Q8I) ? K : (FMT == WF_Q4K ? K / 256 * 144 : K / 2));      // MXFP4 nibbles, Q6_K low nibbles
+  return gs_is_bf16(FMT) ? K * 2 : ((FMT == WF_Q8 || FMT == WF_Q8I) ? K : (FMT == WF_Q4K ? K / 256 * 144 : K / 2));      // MXFP4 nibbles, Q6_K low nibbles
 }
 template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes1(int K) {
-  return (FMT == WF_BF16 || FMT == WF_Q4K) ? 0 : ((FMT == WF_Q8 || FMT == WF_Q8I) ? q8_d_stride(K) * 2 : (FMT == WF_Q6K ? K / 4 : mxfp4_e_stride(K)));
+  return (gs_is_bf16(FMT) || FMT == WF_Q4K) ? 0 : ((FMT == WF_Q8 || FMT == WF_Q8I) ? q8_d_stride(K) * 2 : (FMT == WF_Q6K ? K / 4 : mxfp4_e_stride(K)));
 }
 // Q6_K only: the int8 sub-block scales and the fp16 block scales
 template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes2(int K) { return FMT == WF_Q6K ? K / 16 : 0; }
 template <int FMT> __host__ __device__ __forceinline__ int gs_row_bytes3(int K) { return FMT == WF_Q6K ? q6k_d_stride(K) * 2 : 0; }
 // bytes of one row inside a stage: the whole row, or its k chunk for the formats that are chunked (bf16, Q4_K, Q8 in the dp4a form)
 template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row0(int K, int KC) {
-  return FMT == WF_BF16 ? KC * 2 : (FMT == WF_Q4K ? KC / 256 * 144 : (FMT == WF_Q8I ? KC : (FMT == WF_Q6K ? KC / 2 : gs_row_bytes0<FMT>(K))));
+  return gs_is_bf16(FMT) ? KC * 2 : (FMT == WF_Q4K ? KC / 256 * 144 : (FMT == WF_Q8I ? KC : (FMT == WF_Q6K ? KC / 2 : gs_row_bytes0<FMT>(K))));
 }
 template <int FMT> __host__ __device__ __forceinline__ int gs_stage_row1(int K, int KC) {
   return (FMT == WF_Q8I && KC != K) ? KC / 16 : (FMT == WF_Q6K ? KC / 4 : gs_row_bytes1<FMT>(K));
@@ -195,6 +201,7 @@ __device__ __forceinline__ float s8_to_float(uint32_t vx) {
 // in registers for the whole kernel.
 template <int FMT> struct Gran;
 template <> struct Gran<WF_BF16> { static constexpr int GE = 8, XR = 4, NGMAX = 16; };     // 8 bf16 = one 16-byte word
+template <> struct Gran<WF_BF16W> : Gran<WF_BF16> {};
 template <> struct Gran<WF_Q8> { static constexpr int GE = 16, XR = 8, NGMAX = 8; };       // 16 int8
 template <> struct Gran<WF_MXFP4> { static constexpr int GE = 32, XR = 16, NGMAX = 4; };   // 32 nibbles
 template <> struct Gran<WF_Q4K> { static constexpr int GE = 64, XR = 36, NGMAX = 1; };     // 32 bytes of a Q4_K block: two sub-blocks
@@ -221,6 +228,7 @@ __device__ __forceinline__ void load_xg(const uint8_t* __restrict__ xrow, int g,
 // decoded weight granule, ready to be multiplied with any number of activation rows
 template <int FMT> struct WG;
 template <> struct WG<WF_BF16> { uint4 v; };
+template <> struct WG<WF_BF16W> : WG<WF_BF16> {};
 template <> struct WG<WF_Q8> { float w[16]; float d; };
 template <> struct WG<WF_MXFP4> { uint32_t t[16]; float sc; };
 template <> struct WG<WF_Q6K> { uint32_t ev[8], od[8]; float ds[4]; };          // 6-bit codes of the even / odd elements, d * sub-block scale
@@ -236,7 +244,7 @@ struct GsPlanes23 {
 
 template <int FMT>
 __device__ __forceinline__ void decode_g(const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1, const GsPlanes23& w23, int g, WG<FMT>& o) {
-  if constexpr (FMT == WF_BF16) {
+  if constexpr (gs_is_bf16(FMT)) {
     o.v = reinterpret_cast<const uint4*>(w0)[g];
   } else if constexpr (FMT == WF_Q8) {
     const uint4 a = reinterpret_cast<const uint4*>(w0)[g];
@@ -307,7 +315,7 @@ __device__ __forceinline__ void decode_g(const uint8_t* __restrict__ w0, const u
 
 template <int FMT>
 __device__ __forceinline__ float dot_g(const WG<FMT>& w, const uint32_t (&xr)[Gran<FMT>::XR], float xscale) {
-  if constexpr (FMT == WF_BF16) {
+  if constexpr (gs_is_bf16(FMT)) {
     float s = bf16_lo(w.v.x) * bf16_lo(xr[0]);
     s = fmaf(bf16_hi(w.v.x), bf16_hi(xr[0]), s);
     s = fmaf(bf16_lo(w.v.y), bf16_lo(xr[1]), s); s = fmaf(bf16_hi(w.v.y), bf16_hi(xr[1]), s);
@@ -947,7 +955,7 @@ static int gs_dispatch(GsParams& p, cudaStream_t st) {
   constexpr int WARPS = GsCfg<FMT>::WARPS, RPW = GsCfg<FMT>::RPW, RB = WARPS * RPW;
   const bool gated = p.act != 0;
   p.KC = p.K; p.nkc = 1;
-  if (FMT == WF_BF16 && p.K > 4096) {
+  if (gs_is_bf16(FMT) && p.K > 4096) {
     int n = (p.K + 4095) / 4096;
     while (n < 64 && (p.K % n || (p.K / n) % 8)) ++n;
     if (p.K % n) return 1;
@@ -1021,7 +1029,7 @@ static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* 
   if (route) p.route = *route; else p.route.ticket = nullptr;
   if ((norm || route) && (wfmt == WF_MXFP4 || wfmt == WF_Q4K || wfmt == WF_Q6K || p.slot_mode)) return 1;
   switch (wfmt) {
-    case WF_BF16: return gs_dispatch<WF_BF16>(p, st);
+    case WF_BF16: return g_gs_bf16_wide ? gs_dispatch<WF_BF16W>(p, st) : gs_dispatch<WF_BF16>(p, st);
     case WF_Q8: return (norm || route) ? gs_dispatch<WF_Q8>(p, st) : gs_dispatch<WF_Q8I>(p, st);
     case WF_Q4K: return gs_dispatch<WF_Q4K>(p, st);
     case WF_Q6K: return gs_dispatch<WF_Q6K>(p, st);
@@ -1031,6 +1039,7 @@ static int gemv_stream_fused(int wfmt, const WeightRef& w, const void* x, void* 
 
 }  // namespace mx
 MX_HOST_API void mx_gemv_stream_set_tma(int on) { mx::g_gs_tma = on ? 1 : 0; }
+MX_HOST_API void mx_gemv_stream_set_bf16_wide(int on) { mx::g_gs_bf16_wide = on ? 1 : 0; }
 namespace mx {
 
 // One ticket word per launch of a router GEMV with the routing tail; launches rotate through the words (see attention.cu).

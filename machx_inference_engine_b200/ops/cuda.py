@@ -68,6 +68,11 @@ def set_gemv_path(path) -> None:
     _lib.cuda().mx_gemv_set_path(code)
 
 
+def set_gemv_bf16_wide(on: bool) -> None:
+    """Streaming GEMV over bf16 weights with eight consumer warps per CTA instead of four (MX_GEMV_BF16_WIDE=0/1 sets it at import)."""
+    _lib.cuda().mx_gemv_stream_set_bf16_wide(int(bool(on)))
+
+
 def set_gemv_tma(on: bool) -> None:
     """Streaming GEMV with chunked rows (K above one chunk): one tiled TMA load per plane and stage (default) or one bulk copy per row."""
     _lib.cuda().mx_gemv_stream_set_tma(int(bool(on)))
@@ -281,6 +286,8 @@ import os as _os
 # Llama-3-8B Q4_K_M, ms per prefill step without -> with: 64 rows 12.3 -> 11.6, 256 rows 16.5 -> 12.8, 512 rows 27.5 -> 17.2,
 # 2048 rows 89.6 -> 46.2; batches of 9..63 rows were not measured and keep the in-kernel decode
 DEQUANT_ONCE_MIN_M = int(_os.environ.get("MX_DEQUANT_ONCE_MIN_M", "64"))
+if _os.environ.get("MX_GEMV_BF16_WIDE") is not None:
+    set_gemv_bf16_wide(_os.environ["MX_GEMV_BF16_WIDE"] not in ("", "0"))
 
 
 def _out_kind(dtype) -> int:

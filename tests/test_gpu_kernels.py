@@ -291,6 +291,23 @@ def test_streaming_gemv_kquants(fmt):
         k.set_gemv_path("auto")
 
 
+def test_streaming_gemv_bf16_eight_warps():
+    """The optional bf16 configuration with eight consumer warps per CTA gives the same numbers as the default one."""
+    k = K()
+    try:
+        for (M, N, Kd) in [(1, 2880, 2880), (2, 200, 4096), (1, 64, 14336)]:
+            w = make_weight(WFormat.BF16, N, Kd, seed=N)
+            x = torch.randn(M, Kd, device=dev()).to(torch.bfloat16)
+            outs = []
+            for wide in (False, True):
+                k.set_gemv_bf16_wide(wide)
+                outs.append(k.linear(x, w, out_f32=True))
+            k.check_status()
+            assert torch.equal(outs[0], outs[1]), (M, N, Kd)
+    finally:
+        k.set_gemv_bf16_wide(False)
+
+
 def test_streaming_gemv_chunk_copies_both_ways():
     """Chunked rows arrive by tiled TMA loads (default) or by one bulk copy per row: the same numbers either way, for every chunked
     format, plain and gated, with a last row block that is cut by the matrix edge."""
