@@ -29,23 +29,41 @@ __device__ __forceinline__ float exl3_code_value(uint32_t code) {
 
 // The warp holds the tile's 8 * bits words (word j in lane j % 32, register j / 32); returns this lane's eight weights.
 // WIDE: more than 4 bits per weight, i.e. more than 32 words per tile (the second register is in use).
+// The eight windows of a lane are consecutive: they cover bits [start, start + 7 bits + 16) of the cyclic stream with
+// start = 8 lane bits + bits - 16, i.e. at most 75 bits (three words) up to 4 bits per weight and 103 bits (four words) above.  The lane
+// fetches those words once by shuffles and cuts its windows out of them with funnel shifts.
 template <bool WIDE>
 __device__ __forceinline__ void exl3_decode8(uint32_t w_lo, uint32_t w_hi, int bits, int lane, float (&v)[8]) {
-  const int nbits = bits * 256;
+  constexpr int NW = WIDE ? 4 : 3;
+  const int nwords = bits * 8;
+  int start = lane * 8 * bits + bits - 16;
+  if (start < 0) start += nwords * 32;
+  const int wb = start >> 5, off0 = start & 31;
+  uint32_t w[NW];
+#pragma unroll
+  for (int k = 0; k < NW; ++k) {
+    int idx = wb + k;
+    if (idx >= nwords) idx -= nwords;
+    uint32_t a = __shfl_sync(0xffffffffu, w_lo, idx & 31);
+    if constexpr (WIDE) {
+      const uint32_t b = __shfl_sync(0xffffffffu, w_hi, idx & 31);
+      a = idx < 32 ? a : b;
+    }
+    w[k] = a;
+  }
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const int t = lane * 8 + j;
-    const int last = (t + 1) * bits - 1;                 // in [bits - 1, nbits - 1]
-    int first = last - 15;
-    if (first < 0) first += nbits;
-    const int i0 = first >> 5, i1 = last >> 5;
-    uint32_t a = __shfl_sync(0xffffffffu, w_lo, i0 & 31), b = __shfl_sync(0xffffffffu, w_lo, i1 & 31);
+    const int o = off0 + j * bits;                 // first bit of window j inside w[]
+    const int k = o >> 5;                          // <= 1 (2 when WIDE)
+    uint32_t hi, lo;
     if constexpr (WIDE) {
-      const uint32_t a_hi = __shfl_sync(0xffffffffu, w_hi, i0 & 31), b_hi = __shfl_sync(0xffffffffu, w_hi, i1 & 31);
-      a = i0 < 32 ? a : a_hi;
-      b = i1 < 32 ? b : b_hi;
+      hi = k == 0 ? w[0] : (k == 1 ? w[1] : w[2]);
+      lo = k == 0 ? w[1] : (k == 1 ? w[2] : w[3]);
+    } else {
+      hi = k == 0 ? w[0] : w[1];
+      lo = k == 0 ? w[1] : w[2];
     }
-    const uint32_t code = __funnelshift_r(b, a, 31 - (last & 31)) & 0xffffu;
+    const uint32_t code = __funnelshift_l(lo, hi, o & 31) >> 16;       // bits [o, o + 16), most significant bit first
     v[j] = exl3_code_value(code);
   }
 }
