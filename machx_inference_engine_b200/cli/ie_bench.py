@@ -39,8 +39,12 @@ def main(argv=None) -> int:
     ap.add_argument("--int8-kv", action="store_true", help="int8 KV cache with per-row scales")
     ap.add_argument("--baseline-comm", action="store_true")
     ap.add_argument("--replicated", action="store_true", help="multi-GPU: replicated activations + fused all-reduce instead of the row-sharded prefill")
+    ap.add_argument("--expert-budget-gb", type=float, default=None, help="expert banks past this many GB stay in host memory and are staged per forward")
     ap.add_argument("--device", default="cuda")
     args = ap.parse_args(argv)
+    if args.expert_budget_gb is not None:
+        from ..models import spill
+        spill.configure(args.expert_budget_gb)
 
     from ..formats.model_config import preset
     from ..models import build_model, load_model

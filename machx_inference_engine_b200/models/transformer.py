@@ -390,6 +390,15 @@ class MoEFFN:
             self.gate_up = QuantWeight.interleave_gate_up(g, u)
             self.down = d
         del g, u, d
+        # banks past the device's expert budget live in host memory and are staged per forward (models/spill.py)
+        self._spill = None
+        from . import spill as _spill_mod
+        sp = _spill_mod.active()
+        if sp is not None:
+            banks = list(self.mx) if self.mx is not None else [self.gate_up, self.down]
+            if not sp.admit(sum(b.nbytes for b in banks)):
+                self._spill = (sp, [sp.to_host(i, b) for i, b in enumerate(banks)])
+                self._stage_banks()
         self.expert_scale = None         # optional per-expert factor on the down projection's output, folded into the routing weight
         self.gu_bias = self.down_bias = self.g_bias = self.u_bias = None
         if with_bias:
@@ -410,9 +419,20 @@ class MoEFFN:
         self.shared = None          # optional always-on expert (hybrid families): its partial joins the sum before the reduction
         self._arange = {}
 
+    def _stage_banks(self) -> None:
+        """Spilled layer: copy the banks from host memory into the shared staging area and point the layer at them."""
+        sp, host = self._spill
+        banks = [sp.fetch(i, b) for i, b in enumerate(host)]
+        if self.mx is not None:
+            self.mx = (banks[0], banks[1])
+        else:
+            self.gate_up, self.down = banks
+
     def __call__(self, h: torch.Tensor, par: ParallelCtx, router_h: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Returns this rank's fp32 contribution [T, H] (already reduced when EP > 1).  ``router_h``: the router's own input
         when it differs from the experts' (Gemma-4)."""
+        if self._spill is not None:
+            self._stage_banks()
         T = h.shape[0]
         pre = None
         ksplit = 1
@@ -636,7 +656,8 @@ class TransformerModel:
             return False
         if not sc.can_shard(fb.T) or fb.T < self.SHARD_MIN_TOKENS:
             return False
-        return all(("moe" not in L) or (L["moe"].mx is not None and L["moe"].shared is None and not L["moe"].expert_tp) for L in self.layers)
+        return all(("moe" not in L) or (L["moe"].mx is not None and L["moe"].shared is None and not L["moe"].expert_tp and L["moe"]._spill is None)
+                   for L in self.layers)
 
     SHARD_MIN_TOKENS = 512
 

@@ -281,3 +281,27 @@ def test_gemma4_assistant_head_on_cuda_matches_cpu_path(tmp_path):
         res[dev] = (lg.float().cpu(), hn.float().cpu(), tok)
     assert _cos(res["cpu"][0], res["cuda:0"][0]) > 0.998 and _cos(res["cpu"][1], res["cuda:0"][1]) > 0.998
     assert int(res["cpu"][0].argmax()) == int(res["cuda:0"][0].argmax())
+
+
+def test_spilled_expert_banks_on_gpu():
+    """Expert banks held in page-locked host memory and staged into one device buffer per forward (models/spill.py): the same tokens as
+    the resident graph, with CUDA-graphed decode steps (the copies become graph nodes), for the block-scaled MXFP4 banks and for Q8 banks."""
+    from machx_inference_engine_b200.models import spill
+    g = torch.Generator().manual_seed(3)
+    try:
+        for name, quant in (("tiny-gpt-oss", "mxfp4"), ("tiny-qwen3moe", "q8_0")):
+            cfg = preset(name)
+            prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (21, 150)]
+            outs = []
+            for budget in (None, 0.0):
+                acc = spill.configure(budget)
+                model = build_model(cfg, torch.device("cuda:0"), quant=quant, max_ctx=512, gen_device="cpu")
+                if budget is not None:
+                    assert acc.layers_spilled == cfg.n_layers and all(L["moe"]._spill is not None for L in model.layers)
+                    host = model.layers[0]["moe"]._spill[1][0]
+                    assert not host.p0.is_cuda and host.p0.is_pinned()
+                eng = LLMEngine(model, EngineOptions(max_ctx=512, max_batch_tokens=128, max_seqs=2, cuda_graphs=True))
+                outs.append(eng.generate(prompts, SamplingParams(max_tokens=8)))
+            assert outs[0] == outs[1], (name, outs)
+    finally:
+        spill.configure(None)
