@@ -11,6 +11,7 @@
     python -m machx_inference_engine_b200.cli.tools spec-accept  --gguf M.gguf | --model NAME [--spec-k 3] [--accept 0.0,0.5,0.8,1.0]
     python -m machx_inference_engine_b200.cli.tools kv-scale     --gguf M.gguf | --model NAME [--tokens-n 512]
     python -m machx_inference_engine_b200.cli.tools partial-stack --gguf M.gguf | --model NAME [--layers 1,2,4]
+    python -m machx_inference_engine_b200.cli.tools bug-monitor  --gguf M.gguf | --model NAME [--chains 8] [--iters 32] [--batched] [--live]
 
 Reference parity (behaviour, not code): tools/ie_perplexity.cpp (streaming negative log-likelihood), tools/ie_det_probe.cpp and
 ie_bug_monitor.cpp (run-to-run bit identity), tools/ie_prompt_bench.cpp (fixed prompts, first run discarded, median),
@@ -362,6 +363,101 @@ def cmd_partial_stack(a) -> int:
     return 0
 
 
+def _fingerprint(t: torch.Tensor) -> tuple:
+    """Exact content fingerprint of a tensor computed on its device: the sum of its bit patterns and a position-weighted sum (int64
+    arithmetic wraps, which is fine for equality)."""
+    v = t.detach().contiguous().view(-1)
+    v = v.view(torch.int32 if v.element_size() == 4 else (torch.int16 if v.element_size() == 2 else torch.int8)).to(torch.int64)
+    w = torch.arange(v.numel(), device=v.device, dtype=torch.int64) % 8191 + 1
+    return (int(v.sum()), int((v * w).sum()))
+
+
+def cmd_bug_monitor(a) -> int:
+    """N identical decode chains, each with its own KV blocks and recurrent-state slot, stepped side by side; after every step the
+    persistent buffers of every chain (per layer: DeltaNet state and conv window, or the K and V rows; then the logits) are
+    fingerprinted and compared with chain 0 in producer order.  Reports the first buffer that differs per chain and pins the first
+    divergence ever seen (step, chain, buffer).  ``--batched`` runs the chains as one batch instead of one forward each, which also
+    checks that a sequence does not depend on its batch neighbours.  ``--inject step,chain,layer`` flips one bit in that chain's state
+    (or K rows) before that step: the self-test of the monitor."""
+    from ..models.transformer import KV_BLOCK, ForwardBatch
+    eng = _load(a, max_ctx=2048)
+    m, cfg = eng.model, eng.cfg
+    dev = m.device
+    N, iters = a.chains, a.iters
+    prompt = torch.randint(0, cfg.vocab, (a.tokens_n,), generator=torch.Generator().manual_seed(5)).tolist()
+    T0 = len(prompt)
+    nb = (T0 + iters + KV_BLOCK - 1) // KV_BLOCK
+    kv = m.new_kv_cache(1 + N * nb)
+    st = m.new_state(N) if hasattr(m, "new_state") else None
+    tables = [torch.arange(1 + c * nb, 1 + (c + 1) * nb, dtype=torch.int32, device=dev) for c in range(N)]
+    inject = tuple(int(x) for x in a.inject.split(",")) if a.inject else None
+
+    def batch(chains, toks, pos0):
+        ids, pos, slot, cu, lens = [], [], [], [0], []
+        for c, t in zip(chains, toks):
+            p = torch.arange(pos0, pos0 + len(t), dtype=torch.int32, device=dev)
+            ids += t
+            pos.append(p)
+            slot.append(tables[c][(p // KV_BLOCK).long()].long() * KV_BLOCK + (p % KV_BLOCK).long())
+            cu.append(cu[-1] + len(t))
+            lens.append(pos0 + len(t))
+        return ForwardBatch(torch.tensor(ids, dtype=torch.int32, device=dev), torch.cat(pos), torch.cat(slot), torch.stack([tables[c] for c in chains]),
+                            torch.tensor(lens, dtype=torch.int32, device=dev), torch.tensor(cu, dtype=torch.int32, device=dev), max(len(t) for t in toks),
+                            state_slots=torch.tensor(chains, dtype=torch.int32, device=dev), state_slots_host=list(chains),
+                            q_lens_host=[len(t) for t in toks], start_host=[pos0] * len(chains), max_kv_len=max(lens))
+
+    def step(toks, pos0):
+        groups = [list(range(N))] if a.batched else [[c] for c in range(N)]
+        out = [None] * N
+        for g in groups:
+            lg = m.forward(batch(g, [toks[c] for c in g], pos0), kv, st) if st is not None else m.forward(batch(g, [toks[c] for c in g], pos0), kv)
+            for i, c in enumerate(g):
+                out[c] = lg[i]
+        return out
+
+    def buffers(c, n_pos):
+        """(tag, tensor) of chain c in producer order."""
+        rows = tables[c][: (n_pos + KV_BLOCK - 1) // KV_BLOCK].long()
+        for li in m.layer_ids if hasattr(m, "layer_ids") else range(cfg.n_layers):
+            if st is not None and li in st.S:
+                yield f"DN_state[{li}]", st.S[li][c]
+                yield f"DN_conv[{li}]", st.conv[li][c]
+            elif li in kv.k:
+                yield f"KV_K[{li}]", kv.k[li][rows]
+                yield f"KV_V[{li}]", kv.v[li][rows]
+
+    first, diverged_now, t_dec = None, [], 0.0
+    logits = step([prompt] * N, 0)
+    toks = [[int(l.argmax())] for l in logits]
+    for it in range(iters):
+        pos = T0 + it
+        if inject and inject[0] == it:
+            _, c, li = inject
+            tgt = st.S[li][c] if (st is not None and li in st.S) else kv.k[li][tables[c][0].long()]
+            flat = tgt.view(-1).view(torch.int32 if tgt.element_size() == 4 else torch.int16)
+            flat[0] ^= 1
+        t0 = time.perf_counter()
+        logits = step(toks, pos)
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        t_dec += time.perf_counter() - t0
+        ref = [(tag, _fingerprint(t)) for tag, t in buffers(0, pos + 1)] + [("logits", _fingerprint(logits[0]))]
+        diverged_now = []
+        for c in range(1, N):
+            mine = [(tag, _fingerprint(t)) for tag, t in buffers(c, pos + 1)] + [("logits", _fingerprint(logits[c]))]
+            bad = next((tag for (tag, x), (_, y) in zip(mine, ref) if x != y), None)
+            if bad is not None:
+                diverged_now.append({"chain": c, "buffer": bad})
+                if first is None:
+                    first = {"step": it, "chain": c, "buffer": bad}
+        if a.live:
+            print(f"step {it:4d}  {'DIVERGED ' + json.dumps(diverged_now) if diverged_now else 'ok'}", file=sys.stderr)
+        toks = [[int(l.argmax())] for l in logits]
+    print(json.dumps({"chains": N, "steps": iters, "batched": bool(a.batched), "diverged": first is not None, "first_divergence": first,
+                      "diverged_at_end": diverged_now, "decode_tok_s_per_chain": iters / t_dec if t_dec > 0 else None}))
+    return 1 if (first is not None and not inject) else 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="ie-tools")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -383,9 +479,12 @@ def main(argv=None) -> int:
     p = sub.add_parser("spec-accept"); common(p); p.add_argument("--spec-k", type=int, default=3); p.add_argument("--accept", default="0.0,0.5,0.8,1.0")
     p.add_argument("--prompt-n", type=int, default=256); p.add_argument("--max-tokens", type=int, default=96)
     p = sub.add_parser("kv-scale"); common(p); p.add_argument("--tokens-n", type=int, default=512)
+    p = sub.add_parser("bug-monitor"); common(p); p.add_argument("--chains", type=int, default=8); p.add_argument("--iters", type=int, default=32)
+    p.add_argument("--tokens-n", type=int, default=24); p.add_argument("--batched", action="store_true"); p.add_argument("--inject", default="")
+    p.add_argument("--live", action="store_true")
     p = sub.add_parser("partial-stack"); common(p); p.add_argument("--layers", default="1,2"); p.add_argument("--tokens-n", type=int, default=128)
     a = ap.parse_args(argv)
-    return {"spec-accept": cmd_spec_accept, "kv-scale": cmd_kv_scale, "partial-stack": cmd_partial_stack, "layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
+    return {"bug-monitor": cmd_bug_monitor, "spec-accept": cmd_spec_accept, "kv-scale": cmd_kv_scale, "partial-stack": cmd_partial_stack, "layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
             "soak": cmd_soak}[a.cmd](a)
 
 

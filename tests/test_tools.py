@@ -66,3 +66,19 @@ def test_spec_accept_kv_scale_partial_stack(capsys):
     assert tools.main(["partial-stack", "--model", "tiny-llama", "--device", "cpu", "--layers", "1", "--tokens-n", "48"]) == 0
     r = _last_json(capsys)
     assert [c["layers"] for c in r["cuts"]] == [1, 2] and r["cuts"][0]["argmax_checksum"] != r["cuts"][1]["argmax_checksum"]
+
+
+def test_bug_monitor_finds_an_injected_divergence(capsys):
+    """Identical decode chains stay bit-identical (one forward each, and as one batch); a single flipped bit in one chain's recurrent
+    state or K rows is reported with its step, chain and buffer (the reference's 8-chain monitor: tools/ie_bug_monitor.cpp)."""
+    for model in ("tiny-qwen3next", "tiny-llama"):
+        for extra in ([], ["--batched"]):
+            assert tools.main(["bug-monitor", "--model", model, "--device", "cpu", "--chains", "3", "--iters", "5"] + extra) == 0
+            r = _last_json(capsys)
+            assert r["diverged"] is False and r["chains"] == 3 and r["steps"] == 5
+    assert tools.main(["bug-monitor", "--model", "tiny-qwen3next", "--device", "cpu", "--chains", "3", "--iters", "5", "--inject", "2,1,1"]) == 0
+    r = _last_json(capsys)
+    assert r["first_divergence"] == {"step": 2, "chain": 1, "buffer": "DN_state[1]"}
+    assert tools.main(["bug-monitor", "--model", "tiny-llama", "--device", "cpu", "--chains", "4", "--iters", "5", "--batched", "--inject", "3,2,0"]) == 0
+    r = _last_json(capsys)
+    assert r["first_divergence"] == {"step": 3, "chain": 2, "buffer": "KV_K[0]"} and r["diverged_at_end"] == [{"chain": 2, "buffer": "KV_K[0]"}]
