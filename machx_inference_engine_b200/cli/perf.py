@@ -40,7 +40,7 @@ def _commit() -> str:
         return ""
 
 
-def judge(e: dict) -> tuple[bool, str]:
+def gate(e: dict) -> tuple[bool, str]:
     """(accepted, reason) of a ledger entry."""
     sp = e["baseline_ms"] / e["variant_ms"] if e["variant_ms"] > 0 else 0.0
     if sp <= 1.0:
@@ -71,7 +71,7 @@ def ledger_cmd(a) -> int:
              "baseline_ms": a.baseline_ms, "variant_ms": a.variant_ms, "quality_baseline": a.quality_baseline, "quality_variant": a.quality_variant,
              "quality_floor": a.quality_floor, "quality_tol_pct": a.quality_tol, "lower_is_better": a.lower_is_better, "commit": a.commit or _commit(),
              "notes": a.notes}
-        ok, why = judge(e)
+        ok, why = gate(e)
         e["speedup"] = round(a.baseline_ms / a.variant_ms, 4) if a.variant_ms > 0 else 0.0
         e["accepted"], e["reason"] = ok, why
         with open(a.file, "a") as f:
@@ -83,7 +83,7 @@ def ledger_cmd(a) -> int:
         if not rows:
             print("empty ledger")
             return 1
-        ok, why = judge(rows[-1])
+        ok, why = gate(rows[-1])
         print(("ACCEPT" if ok else "REJECT") + ": " + why)
         return 0 if ok else 1
     acc = [r for r in rows if r.get("accepted")]

@@ -110,7 +110,7 @@ def test_graph_matches_plain_pytorch_oracle(tmp_path, name):
         got = _forward_all(model, ids, chunk)
         cos = torch.nn.functional.cosine_similarity(got, want, dim=1)
         agree = float((got.argmax(-1) == want.argmax(-1)).float().mean())
-        if cfg.is_moe:      # a near-tie in a router can still pick another expert for a token: judge the bulk, bound the tail
+        if cfg.is_moe:      # a near-tie in a router can still pick another expert for a token: assess the bulk, bound the tail
             assert float(cos.median()) > 0.999 and float((cos > 0.99).float().mean()) > 0.9 and agree > 0.85, (chunk, float(cos.median()), agree)
         else:
             assert float(cos.min()) > 0.998 and agree > 0.9, (chunk, float(cos.min()), agree)

@@ -177,7 +177,7 @@ def test_gemma4_file_on_cuda_matches_cpu_path(tmp_path, name):
         cos = torch.nn.functional.cosine_similarity(all_logits(gpu, chunk), want, dim=1)
         if cfg.is_moe:
             # bf16 activations against the fp32 path: a near-tie in one of the three routers sends a token to another expert, so
-            # judge the bulk of the positions (a wrong scale or norm anywhere in the dual path would move the median far lower)
+            # assess the bulk of the positions (a wrong scale or norm anywhere in the dual path would move the median far lower)
             assert float(cos.median()) > 0.995 and float((cos > 0.98).float().mean()) > 0.8, (chunk, float(cos.median()))
         else:
             assert float(cos.min()) > 0.998, (chunk, float(cos.min()))
