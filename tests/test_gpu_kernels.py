@@ -330,10 +330,11 @@ def test_streaming_gemv_chunk_copies_both_ways():
         k.set_gemv_path("auto")
 
 
-@pytest.mark.parametrize("fmt", [WFormat.MXFP4, WFormat.Q8, WFormat.Q4K])
-def test_streaming_expert_gemv_with_foreign_experts(fmt):
+@pytest.mark.parametrize("fmt,H", [(WFormat.MXFP4, 512), (WFormat.Q8, 512), (WFormat.Q4K, 512), (WFormat.Q8, 4096), (WFormat.Q4K, 4096)])
+def test_streaming_expert_gemv_with_foreign_experts(fmt, H):
+    # H = 4096: the gate|up rows are cut into K chunks, fetched by tiled loads whose row coordinate carries the expert's offset
     k = K()
-    E, H, F, topk = 8, 512, 256, 4
+    E, F, topk = 8, 256, 4
     gu = make_weight(fmt, 2 * F, H, E=E, seed=1)
     dn = make_weight(fmt, H, F, E=E, seed=2)
     gub, dnb = torch.randn(E, 2 * F, device=dev()), torch.randn(E, H, device=dev())
