@@ -12,6 +12,8 @@
     python -m machx_inference_engine_b200.cli.tools kv-scale     --gguf M.gguf | --model NAME [--tokens-n 512]
     python -m machx_inference_engine_b200.cli.tools partial-stack --gguf M.gguf | --model NAME [--layers 1,2,4]
     python -m machx_inference_engine_b200.cli.tools bug-monitor  --gguf M.gguf | --model NAME [--chains 8] [--iters 32] [--batched] [--live]
+    python -m machx_inference_engine_b200.cli.tools kernel-monitor --gguf M.gguf | --model NAME [--decode 32] [--interval 8] [--int8-kv]
+    python -m machx_inference_engine_b200.cli.tools attn-profile [--ctx 1024,4096,16384] [--mode bf16|int8|both] [--q-heads 16 --kv-heads 2 --head-dim 256]
 
 Reference parity (behaviour, not code): tools/ie_perplexity.cpp (streaming negative log-likelihood), tools/ie_det_probe.cpp and
 ie_bug_monitor.cpp (run-to-run bit identity), tools/ie_prompt_bench.cpp (fixed prompts, first run discarded, median),
@@ -363,6 +365,101 @@ def cmd_partial_stack(a) -> int:
     return 0
 
 
+def cmd_kernel_monitor(a) -> int:
+    """Per-op device time of every decode step, in dispatch order, as a feed: one table per ``--interval`` steps on stderr (first
+    dispatch order, time per step, share bar) and a JSON summary at the end.  Runs the model on a fixed prompt without CUDA graphs so
+    that every op is timed on its own (src: tools/ie_kernel_monitor.cpp).  On the CPU path the times are wall-clock times of the
+    PyTorch restatement."""
+    from ..runtime.engine import EngineOptions, LLMEngine, SamplingParams
+    from ..utils.profiler import profiler
+    eng = _load(a, max_ctx=2048)
+    llm = LLMEngine(eng.model, EngineOptions(max_ctx=2048, max_batch_tokens=a.chunk, max_seqs=1, enable_prefix_cache=False, cuda_graphs=False,
+                                             kv_dtype="int8" if a.int8_kv else "bf16"))
+    ids = torch.randint(0, eng.cfg.vocab, (a.tokens_n,), generator=torch.Generator().manual_seed(7)).tolist()
+    seq = llm.add_request(ids, SamplingParams(max_tokens=a.warmup + a.decode + 2, ignore_eos=True))
+    while seq.n_generated < 1:
+        llm.step()                                   # prefill (chunked when the prompt is longer than a chunk)
+    for _ in range(a.warmup):
+        llm.step()
+    order, tot, win, steps = [], {}, {}, 0
+
+    def table(acc, n):
+        total = sum(v[1] for v in acc.values()) or 1.0
+        lines = [f"{'op (dispatch order)':<26}{'calls/step':>11}{'us/step':>11}{'share':>8}"]
+        for k in order:
+            if k in acc:
+                c, ms = acc[k]
+                lines.append(f"{k:<26}{c / n:>11.1f}{ms / n * 1e3:>11.1f}{ms / total * 100:>7.1f}% {'#' * int(round(ms / total * 40))}")
+        lines.append(f"{'TOTAL':<26}{'':>11}{total / n * 1e3:>11.1f}")
+        return "\n".join(lines)
+
+    for i in range(a.decode):
+        profiler.start()
+        llm.step()
+        profiler.stop()
+        for name, ms in profiler.harvest_ordered():
+            if name not in tot:
+                order.append(name)
+            for acc in (tot, win):
+                c = acc.setdefault(name, [0, 0.0])
+                c[0] += 1
+                c[1] += ms
+        steps += 1
+        if a.interval and steps % a.interval == 0:
+            print(f"-- steps {steps - a.interval + 1}..{steps}\n" + table(win, a.interval), file=sys.stderr)
+            win = {}
+    total = sum(v[1] for v in tot.values()) or 1.0
+    print(json.dumps({"steps": steps, "ms_per_step": total / max(steps, 1),
+                      "ops": [{"op": k, "calls_per_step": tot[k][0] / max(steps, 1), "us_per_step": tot[k][1] / max(steps, 1) * 1e3,
+                               "share": tot[k][1] / total} for k in order]}))
+    return 0
+
+
+def cmd_attn_profile(a) -> int:
+    """Decode attention alone at a list of context lengths, on synthetic paged caches (no model): time per call with the bf16 cache and
+    with the int8 cache, KV bytes per call and the rate they are read at (src: tools/ie_attn_profile.cpp)."""
+    from .. import ops
+    from ..models.transformer import KV_BLOCK
+    dev = torch.device(a.device if (a.device != "cuda" or torch.cuda.is_available()) else "cpu")
+    hq, hkv, hd = a.q_heads, a.kv_heads, a.head_dim
+    rows = []
+    for ctx in [int(x) for x in a.ctx.split(",")]:
+        nb = (ctx + KV_BLOCK - 1) // KV_BLOCK
+        q = torch.randn(1, hq, hd, device=dev).to(torch.bfloat16)
+        bt = torch.arange(1, nb + 1, dtype=torch.int32, device=dev).unsqueeze(0)
+        lens = torch.tensor([ctx], dtype=torch.int32, device=dev)
+        cu = torch.tensor([0, 1], dtype=torch.int32, device=dev)
+        row = {"ctx": ctx}
+        for mode in ([m for m in ("bf16", "int8") if a.mode in (m, "both")]):
+            # a.layers caches in turn, so that one call's keys are not the previous call's cache lines
+            caches = []
+            for _ in range(a.layers):
+                k = torch.randn(nb + 1, hkv, KV_BLOCK, hd, device=dev)
+                v = torch.randn(nb + 1, hkv, KV_BLOCK, hd, device=dev)
+                if mode == "int8":
+                    ks, vs = k.abs().amax(-1) / 127.0, v.abs().amax(-1) / 127.0
+                    caches.append(((k / ks.unsqueeze(-1)).round().to(torch.int8), (v / vs.unsqueeze(-1)).round().to(torch.int8), (ks.float().contiguous(), vs.float().contiguous())))
+                else:
+                    caches.append((k.to(torch.bfloat16), v.to(torch.bfloat16), None))
+            call = lambda i: ops.attention(q, caches[i % a.layers][0], caches[i % a.layers][1], bt, lens, cu, 1, scale=hd ** -0.5,
+                                           kv_scales=caches[i % a.layers][2], max_kv_len=ctx)
+            for i in range(a.warmup):
+                call(i)
+            if dev.type == "cuda":
+                torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for i in range(a.steps):
+                call(i)
+            if dev.type == "cuda":
+                torch.cuda.synchronize()
+            us = (time.perf_counter() - t0) / a.steps * 1e6
+            kv_bytes = 2 * ctx * hkv * hd * (1 if mode == "int8" else 2) + (2 * ctx * hkv * 4 if mode == "int8" else 0)
+            row[mode] = {"us_per_call": us, "kv_bytes": kv_bytes, "gb_s": kv_bytes / us / 1e3}
+        rows.append(row)
+    print(json.dumps({"q_heads": hq, "kv_heads": hkv, "head_dim": hd, "rows": rows}))
+    return 0
+
+
 def _fingerprint(t: torch.Tensor) -> tuple:
     """Exact content fingerprint of a tensor computed on its device: the sum of its bit patterns and a position-weighted sum (int64
     arithmetic wraps, which is fine for equality)."""
@@ -479,12 +576,18 @@ def main(argv=None) -> int:
     p = sub.add_parser("spec-accept"); common(p); p.add_argument("--spec-k", type=int, default=3); p.add_argument("--accept", default="0.0,0.5,0.8,1.0")
     p.add_argument("--prompt-n", type=int, default=256); p.add_argument("--max-tokens", type=int, default=96)
     p = sub.add_parser("kv-scale"); common(p); p.add_argument("--tokens-n", type=int, default=512)
+    p = sub.add_parser("kernel-monitor"); common(p); p.add_argument("--decode", type=int, default=32); p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--tokens-n", type=int, default=64); p.add_argument("--interval", type=int, default=8); p.add_argument("--int8-kv", action="store_true")
+    p = sub.add_parser("attn-profile"); p.add_argument("--device", default="cuda"); p.add_argument("--ctx", default="1024,4096,16384")
+    p.add_argument("--steps", type=int, default=20); p.add_argument("--warmup", type=int, default=4); p.add_argument("--layers", type=int, default=10)
+    p.add_argument("--mode", default="both", choices=["bf16", "int8", "both"]); p.add_argument("--q-heads", type=int, default=16)
+    p.add_argument("--kv-heads", type=int, default=2); p.add_argument("--head-dim", type=int, default=256)
     p = sub.add_parser("bug-monitor"); common(p); p.add_argument("--chains", type=int, default=8); p.add_argument("--iters", type=int, default=32)
     p.add_argument("--tokens-n", type=int, default=24); p.add_argument("--batched", action="store_true"); p.add_argument("--inject", default="")
     p.add_argument("--live", action="store_true")
     p = sub.add_parser("partial-stack"); common(p); p.add_argument("--layers", default="1,2"); p.add_argument("--tokens-n", type=int, default=128)
     a = ap.parse_args(argv)
-    return {"bug-monitor": cmd_bug_monitor, "spec-accept": cmd_spec_accept, "kv-scale": cmd_kv_scale, "partial-stack": cmd_partial_stack, "layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
+    return {"kernel-monitor": cmd_kernel_monitor, "attn-profile": cmd_attn_profile, "bug-monitor": cmd_bug_monitor, "spec-accept": cmd_spec_accept, "kv-scale": cmd_kv_scale, "partial-stack": cmd_partial_stack, "layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
             "soak": cmd_soak}[a.cmd](a)
 
 

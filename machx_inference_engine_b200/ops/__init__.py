@@ -62,6 +62,8 @@ def _make(name):
                     tag = "gemv" if args[0].shape[0] <= cuda.GEMV_MAX_M else "gemm"
                 return _prof.record(tag, fn, args, kwargs)
             return fn(*args, **kwargs)
+        if _prof.enabled:
+            return _prof.record_host(name, ref_fn, args, kwargs)
         return ref_fn(*args, **kwargs)
 
     return op

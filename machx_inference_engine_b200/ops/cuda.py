@@ -480,6 +480,9 @@ def _dequant_pages(k_cache, v_cache, kv_scales, block_table, seq_lens, max_kv_le
     return dk, dv, table
 
 
+ATTN_MAX_SPLITS = 32
+
+
 def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks=None, window=0, scale=None, softcap=0.0, n_splits=None,
               kv_scales=None, max_kv_len=0):
     Tq, n_q, hd = q.shape
@@ -497,7 +500,9 @@ def attention(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, sinks
         # decode-sized problems: split the KV range so that ~2 CTAs per SM exist
         ctas = B * n_kv * max(1, (max_q_len * (n_q // n_kv) + 31) // 32)
         max_kv_tiles = max(1, (block_table.shape[1] * bs) // 64)
-        n_splits = max(1, min(max_kv_tiles, 32, (2 * sm_count()) // max(ctas, 1)))
+        # (the cap: with two KV heads of 256 and one sequence, 128 ranges instead of 32 took a 16k context from 119 to 103 us but a 4k
+        # context from 48 to 54 us -- the last CTA's merge grows with the ranges; the kernel itself takes any number)
+        n_splits = max(1, min(max_kv_tiles, ATTN_MAX_SPLITS, (2 * sm_count()) // max(ctas, 1)))
     need = n_splits * Tq * n_q * (hd + 2)
     if torch.cuda.is_current_stream_capturing():
         # a captured kernel keeps the raw address: the scratch must live exactly as long as the graph, so it comes from the

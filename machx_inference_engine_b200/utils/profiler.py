@@ -31,16 +31,29 @@ class KernelProfiler:
         self._pending.append((name, e0, e1))
         return out
 
-    def harvest(self) -> dict:
-        """{name: (calls, total_ms)} sorted by total time; synchronises the device."""
+    def record_host(self, name, fn, args, kwargs):
+        """CPU path: wall-clock time of the op (the PyTorch restatement runs synchronously)."""
+        import time
+        t0 = time.perf_counter()
+        out = fn(*args, **kwargs)
+        self._pending.append((name, (time.perf_counter() - t0) * 1e3, None))
+        return out
+
+    def harvest_ordered(self) -> list:
+        """[(name, ms)] in dispatch order; synchronises the device."""
         import torch
         if torch.cuda.is_available():
             torch.cuda.synchronize()
-        agg = defaultdict(lambda: [0, 0.0])
-        for name, e0, e1 in self._pending:
-            agg[name][0] += 1
-            agg[name][1] += e0.elapsed_time(e1)
+        out = [(name, a if b is None else a.elapsed_time(b)) for name, a, b in self._pending]
         self._pending = []
+        return out
+
+    def harvest(self) -> dict:
+        """{name: (calls, total_ms)} sorted by total time; synchronises the device."""
+        agg = defaultdict(lambda: [0, 0.0])
+        for name, ms in self.harvest_ordered():
+            agg[name][0] += 1
+            agg[name][1] += ms
         return dict(sorted(((k, (v[0], v[1])) for k, v in agg.items()), key=lambda kv: -kv[1][1]))
 
     @staticmethod

@@ -82,3 +82,15 @@ def test_bug_monitor_finds_an_injected_divergence(capsys):
     assert tools.main(["bug-monitor", "--model", "tiny-llama", "--device", "cpu", "--chains", "4", "--iters", "5", "--batched", "--inject", "3,2,0"]) == 0
     r = _last_json(capsys)
     assert r["first_divergence"] == {"step": 3, "chain": 2, "buffer": "KV_K[0]"} and r["diverged_at_end"] == [{"chain": 2, "buffer": "KV_K[0]"}]
+
+
+def test_kernel_monitor_and_attn_profile(capsys):
+    assert tools.main(["kernel-monitor", "--model", "tiny-qwen3next", "--device", "cpu", "--decode", "4", "--warmup", "1", "--interval", "2", "--tokens-n", "20"]) == 0
+    r = _last_json(capsys)
+    ops = [o["op"] for o in r["ops"]]
+    assert r["steps"] == 4 and ops[0] == "embed" and {"deltanet_scan", "attention", "linear", "argmax"} <= set(ops)
+    assert abs(sum(o["share"] for o in r["ops"]) - 1.0) < 1e-6 and ops.index("embed") < ops.index("argmax")      # dispatch order
+    assert tools.main(["attn-profile", "--device", "cpu", "--ctx", "200,300", "--steps", "2", "--warmup", "1", "--layers", "2", "--q-heads", "4",
+                       "--kv-heads", "2", "--head-dim", "64"]) == 0
+    r = _last_json(capsys)
+    assert [x["ctx"] for x in r["rows"]] == [200, 300] and r["rows"][0]["int8"]["kv_bytes"] < r["rows"][0]["bf16"]["kv_bytes"]
