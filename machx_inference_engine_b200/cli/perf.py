@@ -207,6 +207,34 @@ def viz_cmd(a) -> int:
     return 0
 
 
+_TRACE_CATEGORY = (("attention", "attention"), ("qkv_post", "memory_kv"), ("kv", "memory_kv"), ("gemm", "matmul"), ("gemv", "matmul"), ("linear", "matmul"),
+                   ("moe", "moe"), ("expert", "moe"), ("norm", "norm"), ("deltanet", "recurrence"), ("conv1d", "recurrence"))
+
+
+def trace_cmd(a) -> int:
+    """A per-op table of ``ie_bench --kprofile`` / ``--kprofile-decode`` as a timeline file for a trace viewer (the Trace Event JSON
+    that chrome://tracing and Perfetto load).  The table is an aggregate, not a timeline: the ops are laid end to end by their total
+    time, so the picture reads as shares of the step, one lane per category (src: tools/perf/benchscope_export.py, which feeds the same
+    tables to the reference's own dashboard)."""
+    text = sys.stdin.read() if a.kprofile == "-" else open(a.kprofile).read()
+    prof = parse_kprofile(text)
+    lanes, events, t = {}, [], 0.0
+    meta = {k: v for k, v in (("model", a.model), ("quant", a.quant), ("ctx", a.ctx), ("tok_s", a.tok_s)) if v not in (None, "")}
+    for o in prof["ops"]:
+        cat = next((c for key, c in _TRACE_CATEGORY if key in o["name"]), "other")
+        tid = lanes.setdefault(cat, len(lanes) + 1)
+        dur = o["total_ms"] * 1e3
+        events.append({"name": o["name"], "cat": cat, "ph": "X", "pid": 1, "tid": tid, "ts": round(t, 3), "dur": round(dur, 3),
+                       "args": {"calls": o["calls"], "us_per_call": o["us_per_call"], "share_pct": o["share_pct"], **meta}})
+        t += dur
+    for cat, tid in lanes.items():
+        events.append({"name": "thread_name", "ph": "M", "pid": 1, "tid": tid, "args": {"name": cat}})
+    events.append({"name": "process_name", "ph": "M", "pid": 1, "args": {"name": a.session or "kprofile"}})
+    json.dump({"traceEvents": events, "displayTimeUnit": "ms", "otherData": {"total_ms": prof["total_ms"], **meta}}, open(a.out, "w"))
+    print(f"wrote {a.out} ({len(prof['ops'])} ops, {prof['total_ms']:.3f} ms)")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="perf")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -233,8 +261,16 @@ def main(argv=None) -> int:
     p = sub.add_parser("viz")
     p.add_argument("capture")
     p.add_argument("out")
+    p = sub.add_parser("trace")
+    p.add_argument("--kprofile", required=True, help="file with a --kprofile table, or - for stdin")
+    p.add_argument("--out", required=True)
+    p.add_argument("--session", default="")
+    p.add_argument("--model", default="")
+    p.add_argument("--quant", default="")
+    p.add_argument("--ctx", type=int, default=None)
+    p.add_argument("--tok-s", type=float, default=None)
     a = ap.parse_args(argv)
-    return {"ledger": ledger_cmd, "roofline": roofline_cmd, "viz": viz_cmd}[a.cmd](a)
+    return {"ledger": ledger_cmd, "roofline": roofline_cmd, "viz": viz_cmd, "trace": trace_cmd}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -13,6 +13,7 @@
     python -m machx_inference_engine_b200.cli.tools partial-stack --gguf M.gguf | --model NAME [--layers 1,2,4]
     python -m machx_inference_engine_b200.cli.tools bug-monitor  --gguf M.gguf | --model NAME [--chains 8] [--iters 32] [--batched] [--live]
     python -m machx_inference_engine_b200.cli.tools kernel-monitor --gguf M.gguf | --model NAME [--decode 32] [--interval 8] [--int8-kv]
+    python -m machx_inference_engine_b200.cli.tools debug        --gguf M.gguf | --model NAME        (P <text> | T <ids> | R | Q on standard input)
     python -m machx_inference_engine_b200.cli.tools attn-profile [--ctx 1024,4096,16384] [--mode bf16|int8|both] [--q-heads 16 --kv-heads 2 --head-dim 256]
 
 Reference parity (behaviour, not code): tools/ie_perplexity.cpp (streaming negative log-likelihood), tools/ie_det_probe.cpp and
@@ -460,6 +461,54 @@ def cmd_attn_profile(a) -> int:
     return 0
 
 
+def cmd_debug(a) -> int:
+    """Long-running prompt loop: the model is loaded once, then commands are read from standard input, one per line:
+    ``P <text>`` appends the text to the context (``T <id id ...>`` appends token ids), runs it and prints the arg-max and the top five
+    tokens of the last position as one JSON line; ``R`` clears the context; ``Q`` or end of input quits (src: tools/ie_debug.cpp).
+    With ``--dump FILE`` every ``P`` / ``T`` also writes the per-layer activations of the run (the format of ``layer-dump``)."""
+    eng = _load(a, max_ctx=4096)
+    ctx: list = []
+    n = 0
+    for line in (a.script.split(";") if a.script else sys.stdin):
+        line = line.strip()
+        if not line:
+            continue
+        cmd, _, rest = line.partition(" ")
+        cmd = cmd.upper()
+        if cmd == "Q":
+            break
+        if cmd == "R":
+            ctx = []
+            print(json.dumps({"reset": True}), flush=True)
+            continue
+        if cmd == "P":
+            if eng.tok is None:
+                print(json.dumps({"error": "this model has no tokenizer: use T <ids>"}), flush=True)
+                continue
+            ids = eng.tok.encode(rest, add_bos=not ctx)
+        elif cmd == "T":
+            try:
+                ids = [int(x) for x in rest.replace(",", " ").split()]
+            except ValueError:
+                ids = []
+            if not ids or min(ids) < 0 or max(ids) >= eng.cfg.vocab:
+                print(json.dumps({"error": "T takes token ids inside the vocabulary"}), flush=True)
+                continue
+        else:
+            print(json.dumps({"error": f"unknown command {cmd!r} (P <text> | T <ids> | R | Q)"}), flush=True)
+            continue
+        ctx += ids
+        t0 = time.perf_counter()
+        lg = _all_logits(eng, ctx, a.chunk)[-1].float()
+        top = torch.topk(lg, 5)
+        row = {"context_tokens": len(ctx), "argmax": int(top.indices[0]), "ms": round((time.perf_counter() - t0) * 1e3, 2),
+               "top5": [{"id": int(i), "logit": round(float(v), 4), **({"text": eng.tok.decode([int(i)])} if eng.tok is not None else {})}
+                        for v, i in zip(top.values, top.indices)]}
+        print(json.dumps(row), flush=True)
+        n += 1
+    return 0
+
+
 def _fingerprint(t: torch.Tensor) -> tuple:
     """Exact content fingerprint of a tensor computed on its device: the sum of its bit patterns and a position-weighted sum (int64
     arithmetic wraps, which is fine for equality)."""
@@ -576,6 +625,7 @@ def main(argv=None) -> int:
     p = sub.add_parser("spec-accept"); common(p); p.add_argument("--spec-k", type=int, default=3); p.add_argument("--accept", default="0.0,0.5,0.8,1.0")
     p.add_argument("--prompt-n", type=int, default=256); p.add_argument("--max-tokens", type=int, default=96)
     p = sub.add_parser("kv-scale"); common(p); p.add_argument("--tokens-n", type=int, default=512)
+    p = sub.add_parser("debug"); common(p); p.add_argument("--script", default="", help="commands separated by ';' instead of standard input")
     p = sub.add_parser("kernel-monitor"); common(p); p.add_argument("--decode", type=int, default=32); p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--tokens-n", type=int, default=64); p.add_argument("--interval", type=int, default=8); p.add_argument("--int8-kv", action="store_true")
     p = sub.add_parser("attn-profile"); p.add_argument("--device", default="cuda"); p.add_argument("--ctx", default="1024,4096,16384")
@@ -587,7 +637,7 @@ def main(argv=None) -> int:
     p.add_argument("--live", action="store_true")
     p = sub.add_parser("partial-stack"); common(p); p.add_argument("--layers", default="1,2"); p.add_argument("--tokens-n", type=int, default=128)
     a = ap.parse_args(argv)
-    return {"kernel-monitor": cmd_kernel_monitor, "attn-profile": cmd_attn_profile, "bug-monitor": cmd_bug_monitor, "spec-accept": cmd_spec_accept, "kv-scale": cmd_kv_scale, "partial-stack": cmd_partial_stack, "layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
+    return {"debug": cmd_debug, "kernel-monitor": cmd_kernel_monitor, "attn-profile": cmd_attn_profile, "bug-monitor": cmd_bug_monitor, "spec-accept": cmd_spec_accept, "kv-scale": cmd_kv_scale, "partial-stack": cmd_partial_stack, "layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
             "soak": cmd_soak}[a.cmd](a)
 
 

@@ -51,3 +51,15 @@ def test_roofline_classes_and_report(tmp_path, capsys):
     assert perf.main(["viz", cap, page]) == 0
     html = open(page).read()
     assert "mxf4_gemm" in html and "tensor pipe is the busiest unit" in html
+
+
+def test_trace_export(tmp_path, capsys):
+    kp, out = str(tmp_path / "k.txt"), str(tmp_path / "t.json")
+    open(kp, "w").write(KPROFILE)
+    assert perf.main(["trace", "--kprofile", kp, "--out", out, "--session", "s1", "--model", "gpt-oss-120b", "--ctx", "2048", "--tok-s", "61000"]) == 0
+    t = json.load(open(out))
+    ev = [e for e in t["traceEvents"] if e["ph"] == "X"]
+    assert [e["name"] for e in ev][0] == "mxf4_gemm" and ev[0]["ts"] == 0 and abs(ev[1]["ts"] - ev[0]["dur"]) < 1e-3     # laid end to end
+    assert abs(sum(e["dur"] for e in ev) / 1e3 - t["otherData"]["total_ms"]) < 1e-2 and ev[0]["args"]["model"] == "gpt-oss-120b"
+    lanes = {e["args"]["name"] for e in t["traceEvents"] if e["name"] == "thread_name"}
+    assert {"matmul", "attention", "norm"} <= lanes

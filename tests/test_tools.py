@@ -94,3 +94,18 @@ def test_kernel_monitor_and_attn_profile(capsys):
                        "--kv-heads", "2", "--head-dim", "64"]) == 0
     r = _last_json(capsys)
     assert [x["ctx"] for x in r["rows"]] == [200, 300] and r["rows"][0]["int8"]["kv_bytes"] < r["rows"][0]["bf16"]["kv_bytes"]
+
+
+def test_debug_prompt_loop(capsys, tmp_path):
+    from machx_inference_engine_b200.formats.model_config import preset
+    from machx_inference_engine_b200.formats.synth import write_synthetic_gguf
+    assert tools.main(["debug", "--model", "tiny-llama", "--device", "cpu", "--script", "T 1 2 3;T 4 5;R;T 1 2 3 4 5;P hi;Z;Q;T 9"]) == 0
+    rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert [r.get("context_tokens") for r in rows] == [3, 5, None, 5, None, None] and rows[2] == {"reset": True}
+    assert rows[1]["argmax"] == rows[3]["argmax"] and rows[1]["top5"] == rows[3]["top5"]        # appended context == the same ids at once
+    assert "no tokenizer" in rows[4]["error"] and "unknown command" in rows[5]["error"]
+    path = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(preset("tiny-llama"), path, quant="q8_0", seed=1)
+    assert tools.main(["debug", "--gguf", path, "--device", "cpu", "--script", "P Hello world;P again"]) == 0
+    rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert rows[1]["context_tokens"] > rows[0]["context_tokens"] > 1 and "text" in rows[0]["top5"][0]
