@@ -29,6 +29,7 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
 import statistics
 import sys
 import threading
@@ -52,11 +53,22 @@ def _load(a, max_ctx=4096, **opts):
     from ..runtime.engine import EngineOptions
     dev = torch.device(a.device if (a.device != "cuda" or torch.cuda.is_available()) else "cpu")
     eo = EngineOptions(max_ctx=max_ctx, **opts)
+    par = None
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # one rank per GPU (torchrun): every rank runs the same tool in lockstep over the sharded graph, rank 0 reports
+        # (the reference's multi-GPU perplexity / equality tools: tools/multi_gpu_ppl.cpp, tools/multi_gpu_equality_test.cpp)
+        from ..parallel.comm import init_from_env
+        par = init_from_env("cuda" if dev.type == "cuda" else "cpu")
+        if dev.type == "cuda":
+            dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+            torch.cuda.set_device(dev)
+            from ..parallel.fused import FusedComm
+            par.fused = FusedComm.create(par, dev)
     if a.gguf:
-        return Engine.load(a.gguf, dev, eo)
+        return Engine.load(a.gguf, dev, eo, par=par)
     cfg = preset(a.model)
     quant = a.quant or ("mxfp4" if cfg.arch == "gpt-oss" else "q8_0")
-    return Engine(build_model(cfg, dev, quant=quant, max_ctx=max_ctx), None, eo)
+    return Engine(build_model(cfg, dev, par, quant=quant, max_ctx=max_ctx), None, eo)
 
 
 def _all_logits(eng, ids, chunk):
@@ -637,6 +649,8 @@ def main(argv=None) -> int:
     p.add_argument("--live", action="store_true")
     p = sub.add_parser("partial-stack"); common(p); p.add_argument("--layers", default="1,2"); p.add_argument("--tokens-n", type=int, default=128)
     a = ap.parse_args(argv)
+    if int(os.environ.get("RANK", "0")) != 0:          # multi-rank runs: one report, from rank 0
+        sys.stdout = open(os.devnull, "w")
     return {"debug": cmd_debug, "kernel-monitor": cmd_kernel_monitor, "attn-profile": cmd_attn_profile, "bug-monitor": cmd_bug_monitor, "spec-accept": cmd_spec_accept, "kv-scale": cmd_kv_scale, "partial-stack": cmd_partial_stack, "layer-dump": cmd_layer_dump, "layer-diff": cmd_layer_diff, "layer-parity": cmd_layer_parity, "perplexity": cmd_perplexity, "det-probe": cmd_det_probe, "chunk-check": cmd_chunk_check, "prompt-bench": cmd_prompt_bench,
             "soak": cmd_soak}[a.cmd](a)
 

@@ -109,3 +109,23 @@ def test_debug_prompt_loop(capsys, tmp_path):
     assert tools.main(["debug", "--gguf", path, "--device", "cpu", "--script", "P Hello world;P again"]) == 0
     rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
     assert rows[1]["context_tokens"] > rows[0]["context_tokens"] > 1 and "text" in rows[0]["top5"][0]
+
+
+def test_perplexity_over_two_ranks_matches_one(capsys):
+    """The same tool under torchrun (two gloo ranks, tensor-parallel graph): rank 0 reports, and the number is the single-rank one up to
+    the summation order (the reference's multi-GPU perplexity / equality tools: tools/multi_gpu_ppl.cpp, tools/multi_gpu_equality_test.cpp)."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    assert tools.main(["perplexity", "--model", "tiny-llama", "--device", "cpu", "--ctx", "64"]) == 0
+    one = _last_json(capsys)
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", str(port),
+                        "-m", "machx_inference_engine_b200.cli.tools", "perplexity", "--model", "tiny-llama", "--device", "cpu", "--ctx", "64"],
+                       capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(rows) == 1 and rows[0]["tokens"] == one["tokens"]                     # one report for the job
+    assert abs(rows[0]["perplexity"] - one["perplexity"]) / one["perplexity"] < 2e-2
